@@ -1,0 +1,129 @@
+"""The CPU oracle against the golden vectors produced by the reference's own Python code.
+
+Tolerances: the oracle sums in fp32 in the reference kernels' lane order, the golden
+vectors come from torch's CPU reductions, so distances agree to 1e-5 relative to the sum
+of the absolute terms; gradients to 1e-5 relative (2e-5 where a K-long sum is re-ordered).
+Index sets, inverse maps and multiplicities are compared exactly.
+"""
+import numpy as np
+import pytest
+
+from oracle.oracle import TWO_PART_QUERY, reference_host_available
+
+OPS = ["l1", "l2", "box_out", "box_in", "rotate", "complex", "distmult"]
+SHAPES = ["selfcheck", "per_query_neg", "shared_neg", "positives"]
+
+
+def _case(golden, shape, op):
+    z = golden["ops"]
+    k = "%s/%s/" % (shape, op)
+    ent, q0 = z[k + "entity"], z[k + "q0"]
+    q1 = z[k + "q1"] if op in TWO_PART_QUERY else None
+    return k, z, ent, q0, q1
+
+
+def _close(a, b, rtol, scale):
+    np.testing.assert_allclose(a, b, rtol=rtol, atol=rtol * scale)
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("op", OPS)
+def test_forward_matches_reference_twin(oracle, golden, shape, op):
+    k, z, ent, q0, q1 = _case(golden, shape, op)
+    out = oracle.dist_forward(op, ent, q0, q1)
+    want = z[k + "out"]
+    if op == "l2":          # the reference takes the root outside the kernel (l2_dist.py:59,62)
+        out = np.sqrt(out)
+    # |sum| can be far below sum|terms| for the dot-product scores
+    scale = float(np.abs(want).max()) * (8.0 if op in ("complex", "distmult") else 1.0)
+    _close(out, want, 1e-5, scale)
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("op", OPS)
+def test_backward_matches_reference_autograd(oracle, golden, shape, op):
+    k, z, ent, q0, q1 = _case(golden, shape, op)
+    want_out = z[k + "out"]
+    # loss = 3.14 * sum(out ** 2); for l2 the op returns out ** 2 already
+    gout = np.full_like(want_out, 3.14) if op == "l2" else (6.28 * want_out).astype(np.float32)
+    g_ent, g_q0, g_q1 = oracle.dist_backward(op, gout, ent, q0, q1)
+    for got, key in ((g_ent, "g_entity"), (g_q0, "g_q0"), (g_q1, "g_q1")):
+        if got is None:
+            continue
+        want = z[k + key]
+        assert not np.isnan(got).any(), "oracle left elements unwritten"
+        _close(got, want, 2e-5, float(np.abs(want).max()))
+
+
+def test_model_logits(oracle, golden):
+    z = golden["logits"]
+    ent, c, o = z["logit/box/entity"], z["logit/box/center"], z["logit/box/offset"]
+    U = c.shape[1]
+
+    def per_branch(fn):
+        return np.stack([fn(u) for u in range(U)], axis=1).max(axis=1)
+
+    box = per_branch(lambda u: 12.0 - oracle.dist_forward("box_out", ent, c[:, u], o[:, u])
+                     - 0.02 * oracle.dist_forward("box_in", ent, c[:, u], o[:, u]))
+    np.testing.assert_allclose(box, z["logit/box/out"], rtol=1e-5, atol=1e-5)
+    vec = per_branch(lambda u: 12.0 - oracle.dist_forward("l1", ent, c[:, u]))
+    np.testing.assert_allclose(vec, z["logit/vec/out"], rtol=1e-5, atol=1e-5)
+    ent2, re, im = z["logit/rotate/entity"], z["logit/rotate/re"], z["logit/rotate/im"]
+    rot = per_branch(lambda u: 12.0 - oracle.dist_forward("rotate", ent2, re[:, u], im[:, u]))
+    np.testing.assert_allclose(rot, z["logit/rotate/out"], rtol=1e-5, atol=1e-5)
+
+
+def test_unique_and_merge_exact(oracle, golden):
+    z = golden["optimizer"]
+    for step in range(3):
+        idx, grad = z["opt/step%d/idx" % step], z["opt/step%d/grad" % step]
+        uniq, inverse, counts = oracle.unique_rows(idx)
+        assert np.array_equal(uniq, z["opt/step%d/uniq" % step])
+        assert np.array_equal(inverse.astype(np.int64), z["opt/step%d/inverse" % step])
+        assert np.array_equal(counts, np.bincount(inverse, minlength=len(uniq)))
+        merged = oracle.scatter_sum_rows(grad, inverse, len(uniq))
+        np.testing.assert_allclose(merged, z["opt/step%d/merged_grad" % step], rtol=1e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("opt,squeeze", [("adam", False), ("adam", True), ("adagrad", False),
+                                         ("adagrad", True), ("sgd", False)])
+def test_row_optimizers(oracle, golden, opt, squeeze):
+    z = golden["optimizer"]
+    tag = "opt/%s_%s/" % (opt, "rowwise" if squeeze else "full")
+    table = z["opt/table0"].copy()
+    N, D = table.shape
+    m = np.zeros((N, D), np.float32)
+    v = np.zeros((N, 1) if squeeze else (N, D), np.float32)
+    lr = float(z["opt/lr"])
+    for step in range(3):
+        uniq = z["opt/step%d/uniq" % step]
+        merged = z["opt/step%d/merged_grad" % step]
+        oracle.sparse_update_rows(opt, table, m, v, uniq, merged, lr, step + 1, squeeze)
+        np.testing.assert_allclose(table, z[tag + "table_after%d" % step], rtol=1e-5, atol=1e-7)
+        if opt == "adam":
+            np.testing.assert_allclose(m, z[tag + "m_after%d" % step], rtol=1e-5, atol=1e-8)
+        if opt != "sgd":
+            np.testing.assert_allclose(v, z[tag + "v_after%d" % step], rtol=1e-5, atol=1e-10)
+
+
+@pytest.mark.skipif(not reference_host_available(), reason="reference functor library not built")
+@pytest.mark.parametrize("op", OPS)
+def test_oracle_equals_reference_functors_bitwise(oracle, op):
+    """Same lane order, same per-element arithmetic: the restatement must reproduce the
+    reference's own functor source (compiled for the host) bit for bit, ties included."""
+    from oracle.oracle import ReferenceHost
+    ref = ReferenceHost()
+    rng = np.random.default_rng(5)
+    for (be, ne, bc, nc, dim) in [(3, 4, 3, 1, 37), (1, 6, 5, 1, 64), (4, 1, 1, 5, 33), (2, 6, 4, 3, 40)]:
+        mul = 2 if op in ("rotate", "complex") else 1
+        # a coarse grid of values makes exact ties (e == c, |e-c| == o) common
+        ent = rng.integers(-3, 4, (be, ne, dim * mul)).astype(np.float32) * 0.25
+        q0 = rng.integers(-3, 4, (bc, nc, dim)).astype(np.float32) * 0.25
+        q1 = (rng.integers(0, 4, (bc, nc, dim)).astype(np.float32) * 0.25) if op in TWO_PART_QUERY else None
+        a = oracle.dist_forward(op, ent, q0, q1)
+        b = ref.dist_forward(op, ent, q0, q1)
+        assert np.array_equal(a, b)
+        gout = rng.standard_normal(a.shape).astype(np.float32)
+        for x, y in zip(oracle.dist_backward(op, gout, ent, q0, q1), ref.dist_backward(op, gout, ent, q0, q1)):
+            if x is not None:
+                assert np.array_equal(x, y)
