@@ -1,0 +1,610 @@
+"""Benchmark of the distance-op + sparse-row-update hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One "step" is one training step of a multi-hop query-embedding model on one synthetic batch:
+row lookups -> query embedding (torch, the unchanged caller side) -> candidate scoring with the
+library's distance ops -> negative-sampling loss -> backward (query gradients + entity-row
+gradients) -> per-step de-duplication of touched rows -> fused row-wise Adam; plus the dense
+optimizer step of the small relation / intersection parameters.  The metric is queries per
+second (B queries per GPU per step).
+
+The default workload is the Freebase-scale Query2box configuration (B=1024 queries per GPU,
+K=1024 negatives per query, dim 400, row-wise second moment, nine query structures in
+rotation) with the entity table sized at 1/8 of 86,054,151 rows per GPU, so that per-GPU work
+is the same at every N ("weak" scaling; at N=8 the table is the full 86M rows).  Inputs are
+synthetic with the shapes and value distributions of that configuration; no dataset is read.
+
+Prints one JSON line (see README/DESIGN for the keys).  `--impl reference` instead times the
+reference's own CPU path (its torch-native scoring and torch index-op optimizer, restated in
+oracle/native_torch.py) on the host cores, on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FREEBASE_ENTITIES = 86054151
+FREEBASE_RELATIONS = 14824
+
+# query structures (smore/common/config.py:21-43), in the reference's nested-tuple notation
+E1 = ("e", ("r",))
+STRUCTURES = {
+    "1p": E1,
+    "2p": ("e", ("r", "r")),
+    "3p": ("e", ("r", "r", "r")),
+    "2i": (E1, E1),
+    "3i": (E1, E1, E1),
+    "ip": ((E1, E1), ("r",)),
+    "pi": (("e", ("r", "r")), E1),
+    "2u": (E1, E1, ("u",)),
+    "up": ((E1, E1, ("u",)), ("r",)),
+}
+
+
+def structure_columns(qs):
+    """Column kinds ('e', 'r', 'u') of the flattened query matrix, in embed order."""
+    if all(isinstance(x, str) for x in qs[-1]) and all(x in ("r", "n") for x in qs[-1]):
+        head = ["e"] if qs[0] == "e" else structure_columns(qs[0])
+        return head + list(qs[-1])
+    cols = []
+    is_union = qs[-1][0] == "u"
+    for branch in (qs[:-1] if is_union else qs):
+        cols += structure_columns(branch)
+    return cols + (["u"] if is_union else [])
+
+
+WORKLOADS = {
+    # name: geo, rows per GPU (None = FREEBASE/8), relations, dim, B, K, shared negatives, gamma, structures,
+    #       adversarial temperature, lr, row-wise second moment
+    "freebase_q2b": dict(geo="box", rows=None, relations=FREEBASE_RELATIONS, dim=400, B=1024, K=1024, shared=False,
+                         gamma=2.0, cen=0.02, structures=["1p", "2p", "3p", "2i", "3i", "ip", "pi", "2u", "up"],
+                         adv=0.5, lr=5e-5, squeeze=True),
+    "rotate_wikikg": dict(geo="rotate", rows=2500604, relations=535, dim=500, B=1024, K=1024, shared=False,
+                          gamma=24.0, cen=0.0, structures=["1p"], adv=1.0, lr=1e-4, squeeze=False, zipf_anchor=1.1),
+    "q2b_fb15k": dict(geo="box", rows=14951, relations=1345, dim=400, B=1024, K=512, shared=True, gamma=12.0,
+                      cen=0.02, structures=["1p", "2p", "3p", "2i"], adv=None, lr=1e-4, squeeze=False),
+    "gqe_fb15k237": dict(geo="vec", rows=14505, relations=237, dim=64, B=512, K=128, shared=False, gamma=12.0,
+                         cen=0.0, structures=["1p"], adv=None, lr=1e-4, squeeze=False),
+}
+
+
+# ------------------------------------------------------------------------------------------------
+# synthetic index batches (what the online sampler hands to the training step)
+# ------------------------------------------------------------------------------------------------
+
+def _power_law_ids(gen, n, size, s, mult):
+    """Ids in [0, n) whose popularity rank follows ~ rank^-s; rank -> id through a fixed bijection."""
+    u = torch.rand(size, generator=gen, dtype=torch.float64)
+    if abs(s - 1.0) < 1e-9:
+        x = torch.exp(u * math.log(n))
+    else:
+        x = (1.0 + u * (float(n) ** (1.0 - s) - 1.0)) ** (1.0 / (1.0 - s))
+    rank = x.floor().long().clamp_(1, n) - 1
+    return (rank * mult + 12345) % n
+
+
+def _coprime_multiplier(n):
+    m = 2654435761 % n
+    while m < 2 or math.gcd(m, n) != 1:
+        m += 1
+    return m
+
+
+def make_batch(cfg, n_rows, structure, seed):
+    """(positive [B], negative [B, K] or [1, K], queries [B, n_cols]) as int64 CPU tensors."""
+    gen = torch.Generator().manual_seed(seed)
+    B, K = cfg["B"], cfg["K"]
+    cols = structure_columns(STRUCTURES[structure])
+    mult_e, mult_r = _coprime_multiplier(n_rows), _coprime_multiplier(cfg["relations"])
+    q = torch.empty(B, len(cols), dtype=torch.int64)
+    for c, kind in enumerate(cols):
+        if kind == "e":
+            q[:, c] = _power_law_ids(gen, n_rows, (B,), cfg.get("zipf_anchor", 1.2), mult_e)
+        elif kind == "r":
+            q[:, c] = _power_law_ids(gen, cfg["relations"], (B,), 1.0, mult_r)
+        else:
+            q[:, c] = -1
+    pos = torch.randint(0, n_rows, (B,), generator=gen)
+    neg = torch.randint(0, n_rows, (1 if cfg["shared"] else B, K), generator=gen)
+    return pos, neg, q
+
+
+# ------------------------------------------------------------------------------------------------
+# the caller side: query embedding in plain torch (smore/models/{box,vec,rotate}.py), scoring through
+# the library's ops
+# ------------------------------------------------------------------------------------------------
+
+class Intersection(nn.Module):
+    """CenterIntersection (box.py:55-70): attention over the branches."""
+
+    def __init__(self, dim):
+        super().__init__()
+        self.dim = dim
+        self.layers = nn.Parameter(torch.zeros(dim * 2 + 2, dim))
+        nn.init.xavier_uniform_(self.layers[:dim * 2, :])
+
+    def forward(self, embeddings):
+        w1, w2, b1, b2 = torch.split(self.layers, [self.dim, self.dim, 1, 1], dim=0)
+        act = F.relu(F.linear(embeddings, w1, b1.view(-1)))
+        attention = F.softmax(F.linear(act, w2, b2.view(-1)), dim=0)
+        return torch.sum(attention * embeddings, dim=0)
+
+
+class OffsetIntersection(nn.Module):
+    """BoxOffsetIntersection (box.py:38-53)."""
+
+    def __init__(self, dim):
+        super().__init__()
+        self.dim = dim
+        self.layers = nn.Parameter(torch.zeros(dim * 2 + 2, dim))
+        nn.init.xavier_uniform_(self.layers[:dim * 2, :])
+
+    def forward(self, embeddings):
+        w1, w2, b1, b2 = torch.split(self.layers, [self.dim, self.dim, 1, 1], dim=0)
+        act = F.relu(F.linear(embeddings, w1, b1.view(-1)))
+        gate = torch.sigmoid(F.linear(torch.mean(act, dim=0), w2, b2.view(-1)))
+        offset, _ = torch.min(embeddings, dim=0)
+        return offset * gate
+
+
+class QueryModel(nn.Module):
+    """Entity table (sparse, updated by the library's optimizer) + dense relation parameters and
+    intersection nets; embeds one batch of same-structure queries and scores candidates."""
+
+    def __init__(self, cfg, n_rows, device, ops, embedding_mod, lazy=True):
+        super().__init__()
+        self.cfg, self.geo, self.dim = cfg, cfg["geo"], cfg["dim"]
+        self.gamma, self.cen = cfg["gamma"], cfg.get("cen", 0.0)
+        self.ops = ops
+        width = self.dim * (2 if self.geo == "rotate" else 1)
+        self.embedding_range = (self.gamma + 2.0) / self.dim
+        r = self.embedding_range
+        self.entity_embedding = embedding_mod.SparseEmbedding(0, width)
+        table = torch.empty(n_rows, width, device=device)
+        table.uniform_(-r, r)
+        self.entity_embedding.num_rows = n_rows
+        self.entity_embedding.embedding = nn.Parameter(table, requires_grad=False)
+        R = cfg["relations"]
+        self.relation_embedding = nn.Parameter(torch.empty(R, self.dim, device=device).uniform_(-r, r))
+        if self.geo == "box":
+            self.offset_embedding = nn.Parameter(torch.empty(R, self.dim, device=device).uniform_(0, r))
+            self.offset_net = OffsetIntersection(self.dim).to(device)
+        self.center_net = Intersection(width).to(device)
+
+        class _Args(object):
+            optim_mode = ("aggr", "adam", "gpu", bool(cfg["squeeze"]), 0)
+            share_optim_stats = False
+
+        lazy_names = ("negative_entity", "positive_entity") if lazy else ()
+        self.embed_opt = embedding_mod.AdamEmbedOptimizer(_Args(), self.entity_embedding, device.index,
+                                                          lazy_names=lazy_names)
+        dense = [p for n, p in self.named_parameters() if p.requires_grad and "dummy" not in n]
+        self.dense_opt = torch.optim.Adam(dense, lr=cfg["lr"], fused=True)
+
+    # -- query embedding (kg_reasoning.py:217-250 with the per-model hooks) -----------------------
+    def _retrieve(self, ids):
+        e = self.entity_embedding(ids)
+        if self.geo == "rotate":
+            re, im = torch.chunk(e, 2, dim=1)
+            return [re.unsqueeze(1), im.unsqueeze(1)]
+        if self.geo == "box":
+            return [e.unsqueeze(1), torch.zeros_like(e).unsqueeze(1)]
+        return [e.unsqueeze(1)]
+
+    def _project(self, emb, rel_ids):
+        rel = self.relation_embedding[rel_ids].unsqueeze(1)
+        if self.geo == "rotate":
+            phase = rel / (self.embedding_range / math.pi)
+            re_r, im_r = torch.cos(phase), torch.sin(phase)
+            re, im = emb
+            return [re * re_r - im * im_r, re * im_r + im * re_r]
+        if self.geo == "box":
+            return [emb[0] + rel, emb[1] + self.offset_embedding[rel_ids].unsqueeze(1)]
+        return [emb[0] + rel]
+
+    def _intersect(self, branches):
+        if self.geo == "box":
+            centers = torch.stack([b[0] for b in branches])
+            offsets = torch.stack([b[1] for b in branches])
+            return [self.center_net(centers), self.offset_net(offsets)]
+        if self.geo == "rotate":
+            stacked = torch.stack([torch.cat(b, dim=-1) for b in branches])
+            return list(torch.chunk(self.center_net(stacked), 2, dim=-1))
+        return [self.center_net(torch.stack([b[0] for b in branches]))]
+
+    def embed_query(self, queries, qs, col):
+        if all(isinstance(x, str) for x in qs[-1]) and all(x in ("r", "n") for x in qs[-1]):
+            if qs[0] == "e":
+                emb = self._retrieve(queries[:, col])
+                col += 1
+            else:
+                emb, col = self.embed_query(queries, qs[0], col)
+            for _ in qs[-1]:
+                emb = self._project(emb, queries[:, col])
+                col += 1
+            return emb, col
+        is_union = qs[-1][0] == "u"
+        branches = []
+        for b in (qs[:-1] if is_union else qs):
+            emb, col = self.embed_query(queries, b, col)
+            branches.append(emb)
+        if is_union:
+            n = len(branches[0])
+            return [torch.cat([b[i] for b in branches], dim=1) for i in range(n)], col + 1
+        return self._intersect(branches), col
+
+    def cal_logit(self, entity, query):
+        ops = self.ops
+        if self.geo == "box":
+            d1 = ops.box_dist_out(entity, query[0], query[1])
+            d2 = ops.box_dist_in(entity, query[0], query[1])
+            logit = self.gamma - d1 - self.cen * d2
+        elif self.geo == "rotate":
+            logit = self.gamma - ops.rotate_dist(entity, query[0], query[1])
+        else:
+            logit = self.gamma - ops.l1_dist(entity, query[0])
+        return torch.max(logit, dim=1)[0]
+
+    def forward(self, pos, neg, queries, structure):
+        """kg_reasoning.py:270-364 for one structure: (positive_logit [B,1], negative_logit [B,K])."""
+        B = queries.shape[0]
+        pos_rows = self.entity_embedding(pos, "positive_entity")
+        neg_rows = self.entity_embedding(neg.view(-1), "negative_entity")
+        emb, col = self.embed_query(queries, STRUCTURES[structure], 0)
+        assert col == queries.shape[1]
+        query = [e.unsqueeze(-2) for e in emb]
+        pos_logit = self.cal_logit(pos_rows.unsqueeze(1), query)
+        neg_logit = self.cal_logit(neg_rows.view(neg.shape[0], neg.shape[1], -1), query)
+        return pos_logit, neg_logit
+
+
+def sampling_loss(pos_logit, neg_logit, adv, world_size=1):
+    """train_process.py:195-213 with uniform query weights and no regulariser."""
+    if adv is not None:
+        neg_score = (F.softmax(neg_logit * adv, dim=1).detach() * F.logsigmoid(-neg_logit)).sum(dim=1)
+    else:
+        neg_score = F.logsigmoid(-neg_logit).mean(dim=1)
+    pos_score = F.logsigmoid(pos_logit).squeeze(dim=1)
+    return (-pos_score.mean() - neg_score.mean()) / 2 / world_size
+
+
+def train_step(model, pos, neg, queries, structure):
+    """train_process.py:172-227 on device-resident index tensors."""
+    model.dense_opt.zero_grad(set_to_none=True)
+    model.embed_opt.zero_grad()
+    pos_logit, neg_logit = model(pos, neg, queries, structure)
+    loss = sampling_loss(pos_logit, neg_logit, model.cfg["adv"])
+    loss.backward()
+    model.embed_opt.apply_grad(model.cfg["lr"])
+    model.dense_opt.step()
+    return loss
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU every 100 ms through NVML (read-only)."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.stop_flag = index, threading.Event()
+        self.sm, self.reasons, self.sm_max, self.ok = [], set(), None, False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        while self.ok and not self.stop_flag.is_set():
+            try:
+                self.sm.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                mask = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self.stop_flag.wait(0.1)
+
+    def summary(self):
+        self.stop_flag.set()
+        if not self.sm:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": sorted(self.reasons)}
+        s = sorted(self.sm)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.sm_max, "reasons": sorted(self.reasons)}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline: the reference's torch-native path on host cores, bounded sample
+# ------------------------------------------------------------------------------------------------
+
+def cpu_reference_steps(cfg, steps, warmup, sample_queries=64, table_rows=1000000):
+    """Times fwd + bwd + touched-row merge + row-wise Adam of `sample_queries` queries (full K and
+    dim) against a host table of `table_rows` rows.  Returns (queries/s, ms/step, threads, text)."""
+    from oracle import native_torch as nt
+    torch.set_num_threads(os.cpu_count() or 1)
+    geo, D, K = cfg["geo"], cfg["dim"], cfg["K"]
+    width = D * (2 if geo == "rotate" else 1)
+    n_rows = min(table_rows, cfg["rows"] or table_rows)
+    g = torch.Generator().manual_seed(0)
+    r = (cfg["gamma"] + 2.0) / D
+    table = (torch.rand(n_rows, width, generator=g) * 2 - 1) * r
+    m = torch.zeros_like(table)
+    v = torch.zeros(n_rows, 1) if cfg["squeeze"] else torch.zeros_like(table)
+    Bs = min(sample_queries, cfg["B"])
+    times = []
+    for it in range(warmup + steps):
+        pos = torch.randint(0, n_rows, (Bs,), generator=g)
+        neg = torch.randint(0, n_rows, (1 if cfg["shared"] else Bs, K), generator=g)
+        qparts = [((torch.rand(Bs, 1, 1, D, generator=g) * 2 - 1) * r).requires_grad_() for _ in range(2)]
+        t0 = time.perf_counter()
+        pos_rows = table[pos].requires_grad_()
+        neg_rows = table[neg.view(-1)].requires_grad_()
+        ent_pos, ent_neg = pos_rows.unsqueeze(1), neg_rows.view(neg.shape[0], K, width)
+        if geo == "box":
+            q = (qparts[0], qparts[1].abs())
+            pl, nl = nt.box_logit(ent_pos, q, cfg["gamma"], cfg["cen"]), nt.box_logit(ent_neg, q, cfg["gamma"], cfg["cen"])
+        elif geo == "rotate":
+            q = (qparts[0], qparts[1])
+            pl, nl = nt.rotate_logit(ent_pos, q, cfg["gamma"]), nt.rotate_logit(ent_neg, q, cfg["gamma"])
+        else:
+            q = (qparts[0],)
+            pl, nl = nt.vec_logit(ent_pos, q, cfg["gamma"]), nt.vec_logit(ent_neg, q, cfg["gamma"])
+        loss = nt.sampling_loss(pl, nl, cfg["adv"])
+        loss.backward()
+        idx, inv, merged = nt.merge_grads([pos, neg.view(-1)], [pos_rows.grad, neg_rows.grad])
+        nt.adam_rows(table, m, v, idx, merged, cfg["lr"], it + 1, cfg["squeeze"])
+        dt = time.perf_counter() - t0
+        if it >= warmup:
+            times.append(dt)
+    ms = 1e3 * sum(times) / len(times)
+    sample = "%d of %d queries per step, K=%d, dim=%d, host table %d rows, %d timed steps" % (
+        Bs, cfg["B"], K, D, n_rows, len(times))
+    return Bs / (ms / 1e3), ms, torch.get_num_threads(), sample
+
+
+# ------------------------------------------------------------------------------------------------
+# the GPU arm
+# ------------------------------------------------------------------------------------------------
+
+# DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) for the
+# kernels below at the default workload; None until a capture exists (see profiles/).
+NCU_TRAFFIC_BYTES = {"rows_forward": None, "rows_backward": None, "sparse_update_rows": None}
+
+
+def algorithmic_bytes(cfg, n_unique_mean):
+    """Bytes each kernel has to move per launch (per union branch for the two distance kernels)."""
+    B, K, D = cfg["B"], cfg["K"], cfg["dim"]
+    W = D * (2 if cfg["geo"] == "rotate" else 1)
+    nq = 1 if cfg["geo"] == "vec" else 2
+    nout = 2 if cfg["geo"] == "box" else 1
+    pairs = B * K
+    fwd = pairs * (4 * W + 8 + 4 * nout) + B * D * 4 * nq
+    bwd = pairs * (8 * W + 8 + 4 + 4 + 4 * nout) + 2 * B * D * 4 * nq
+    v_bytes = 8 if cfg["squeeze"] else 8 * W
+    upd = n_unique_mean * (4 * W + 8 * W + 8 * W + v_bytes + 8)
+    return {"rows_forward": fwd, "rows_backward": bwd, "sparse_update_rows": upd}
+
+
+def load_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def run_gpu(args):
+    import torch.distributed as dist
+    from smore_b200 import _lib, embedding, ext_ops
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU path for the product arm)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    cfg = dict(WORKLOADS[args.workload])
+    rows_per_gpu = cfg["rows"] or (FREEBASE_ENTITIES + 7) // 8
+    if args.rows:
+        rows_per_gpu = args.rows
+    if world > 1:
+        raise NotImplementedError("multi-GPU sharded run is provided by smore_b200.sharded (not wired yet)")
+    n_rows = rows_per_gpu
+
+    torch.manual_seed(1234 + rank)
+    model = QueryModel(cfg, n_rows, device, ext_ops, embedding, lazy=not args.no_lazy)
+    model.train()
+    structures = cfg["structures"]
+    pool = max(len(structures), args.pool)
+    host_batches = []
+    for i in range(pool):
+        s = structures[i % len(structures)]
+        pos, neg, q = make_batch(cfg, n_rows, s, seed=1000 * rank + i)
+        host_batches.append((s, pos.pin_memory(), neg.pin_memory(), q.pin_memory()))
+    dev_batches = [(s, p.to(device), n.to(device), q.to(device)) for s, p, n, q in host_batches]
+    h2d_bytes = sum(p.numel() + n.numel() + q.numel() for _, p, n, q in host_batches) * 8 / pool
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def run_resident(k0, k):
+        for i in range(k0, k0 + k):
+            s, p, n, q = dev_batches[i % pool]
+            train_step(model, p, n, q, s)
+
+    def run_e2e(k0, k):
+        last = 0.0
+        for i in range(k0, k0 + k):
+            s, p, n, q = host_batches[i % pool]
+            p, n, q = p.to(device, non_blocking=True), n.to(device, non_blocking=True), q.to(device, non_blocking=True)
+            last = train_step(model, p, n, q, s).item()   # device -> host read of the step's loss
+        return last
+
+    L = _lib.lib()
+    # ---- resident-input timing ("value") with per-kernel events ------------------------------------
+    run_resident(0, args.warmup)
+    sync_all()
+    timer = _lib.KernelTimer()
+    _lib.set_timer(timer)
+    clocks = ClockSampler(local_rank)
+    clocks.start()
+    launches0 = L.smore_kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    e0.record()
+    run_resident(args.warmup, args.steps)
+    e1.record()
+    sync_all()
+    launches = L.smore_kernel_launch_count() - launches0
+    _lib.set_timer(None)
+    ms_total = e0.elapsed_time(e1)
+    kernel_ms = timer.elapsed_ms()
+    # ---- end-to-end timing: pinned host index tensors in, loss out, every step ----------------------
+    run_e2e(0, min(3, args.warmup))
+    sync_all()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    last_loss = run_e2e(args.warmup, args.steps)
+    e3.record()
+    sync_all()
+    clock_summary = clocks.summary()
+    ms_e2e = e2.elapsed_time(e3)
+    if world > 1:
+        t = torch.tensor([ms_total, ms_e2e], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total, ms_e2e = t.tolist()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = load_peaks()
+    plan_rows = cfg["B"] * cfg["K"] + cfg["B"] * 3
+    alg = algorithmic_bytes(cfg, n_unique_mean=plan_rows)  # refined below when a count is available
+    kernels = {}
+    for name, ms_list in kernel_ms.items():
+        if not ms_list:
+            continue
+        avg = sum(ms_list) / len(ms_list)
+        entry = {"launches": len(ms_list), "avg_ms": round(avg, 4), "total_ms": round(sum(ms_list), 3)}
+        if name in alg:
+            gbs = alg[name] / (avg * 1e-3) / 1e9
+            entry.update({"algorithmic_bytes": int(alg[name]), "achieved_gbs": round(gbs, 1),
+                          "frac_of_%s_peak" % peak_kind: round(gbs / peak, 4)})
+        kernels[name] = entry
+    dom = max((k for k in kernels if k in alg), key=lambda k: kernels[k]["total_ms"], default=None)
+    roofline = None
+    if dom:
+        roofline = {"kernel": dom, "bound": "hbm", "achieved": kernels[dom]["achieved_gbs"], "peak": peak,
+                    "peak_source": peak_kind, "unit": "GB/s", "frac": round(kernels[dom]["achieved_gbs"] / peak, 4),
+                    "traffic": NCU_TRAFFIC_BYTES.get(dom)}
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        try:
+            qps, ms, threads, sample = cpu_reference_steps(cfg, steps=args.cpu_steps, warmup=2)
+            cpu = {"value": round(qps, 1), "unit": "queries/s", "cores": threads, "kind": "port",
+                   "ms_per_step": round(ms, 2), "sample": sample}
+        except Exception as exc:  # the baseline is a report, not a dependency of the product arm
+            cpu = {"value": None, "unit": "queries/s", "cores": None, "kind": "port", "sample": "failed: %r" % (exc,)}
+
+    total_queries = cfg["B"] * world * args.steps
+    out = {
+        "metric": "queries/sec (fwd+bwd+sparse update)",
+        "value": round(total_queries / (ms_total * 1e-3), 1),
+        "unit": "queries/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_total / args.steps, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "geo": cfg["geo"], "queries_per_gpu": cfg["B"], "negatives": cfg["K"],
+                   "shared_negatives": cfg["shared"], "dim": cfg["dim"], "table_rows_per_gpu": rows_per_gpu,
+                   "table_rows_total": n_rows * world, "structures": structures,
+                   "optimizer": "adam, row-wise v" if cfg["squeeze"] else "adam, full v",
+                   "lazy_rows": not args.no_lazy,
+                   "l2_policy": "inputs larger than L2: every step touches ~%.1f GB of table rows" %
+                                (cfg["B"] * cfg["K"] * cfg["dim"] * 4 / 1e9)},
+        "e2e": {"value": round(total_queries / (ms_e2e * 1e-3), 1), "unit": "queries/s",
+                "ms_per_step": round(ms_e2e / args.steps, 4),
+                "h2d_bytes_per_step": int(h2d_bytes), "d2h_bytes_per_step": 4},
+        "gpu_launches": int(launches),
+        "roofline": roofline,
+        "kernels": kernels,
+        "cpu_baseline": cpu,
+        "clocks": clock_summary,
+        "last_loss": last_loss,
+    }
+    print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = dict(WORKLOADS[args.workload])
+    qps, ms, threads, sample = cpu_reference_steps(cfg, steps=args.steps, warmup=args.warmup)
+    world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    out = {
+        "impl": "reference",
+        "metric": "queries/sec (fwd+bwd+sparse update)", "value": round(qps, 1), "unit": "queries/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "geo": cfg["geo"], "queries_per_gpu": cfg["B"],
+                   "negatives": cfg["K"], "dim": cfg["dim"]},
+        "cpu_baseline": {"value": round(qps, 1), "unit": "queries/s", "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(qps, 1), "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=18)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--workload", default="freebase_q2b", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="smore_b200", choices=["smore_b200", "reference"])
+    ap.add_argument("--rows", type=int, default=0, help="override entity-table rows per GPU")
+    ap.add_argument("--pool", type=int, default=18, help="distinct pre-generated batches to cycle through")
+    ap.add_argument("--no-lazy", action="store_true", help="gather candidate rows instead of reading the table in place")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-steps", type=int, default=6)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

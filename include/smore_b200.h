@@ -1,0 +1,193 @@
+/*
+ * smore_b200 — C ABI of the B200 (sm_100a) distance-op and sparse-row-update library.
+ *
+ * Conventions shared by every entry point
+ *   - plain pointers and sizes only; every pointer is DEVICE memory owned by the caller unless
+ *     a parameter is documented as a host pointer.  The library never allocates or frees device
+ *     memory (scratch is passed in; see smore_unique_rows_workspace_bytes).
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued on it and the call returns
+ *     without synchronising.  The device that is current when the call is made must own the
+ *     pointers.
+ *   - return value: SMORE_OK (0) or a negative SMORE_ERR_* code.  The library never exits the
+ *     process and never prints; smore_last_error() gives a thread-local message for the last
+ *     failing call.  (The reference prints and calls exit(), extlib_cuda.cpp:26-49, or silently
+ *     ignores an unknown distance name, ext_cuda_kernel.cu:48-49; both become error codes here.)
+ *   - all arithmetic is IEEE fp32 unless the name ends in _f64.
+ *
+ * Shapes follow the reference's op contract (extlib_cuda.cpp:172-196): an entity operand
+ * [be, ne, mul*dim], query operands [bc, nc, dim], an output [bsize, num] with
+ * bsize = max(be, bc), num = max(ne, nc); cell (i, j) pairs entity row (i % be, j % ne) with
+ * query row (i % bc, j % nc).  mul is 2 for the distances whose entity rows hold two parts
+ * ([part0 | part1], each `dim` long: rotate, complex) and 1 otherwise.
+ */
+#ifndef SMORE_B200_H_
+#define SMORE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define SMORE_API __attribute__((visibility("default")))
+#else
+#define SMORE_API
+#endif
+
+#define SMORE_OK 0
+#define SMORE_ERR_BAD_DIST (-1)   /* unknown distance / optimizer id */
+#define SMORE_ERR_BAD_SHAPE (-2)  /* sizes violate the broadcast contract or a documented limit */
+#define SMORE_ERR_NULL (-3)       /* a required pointer is NULL */
+#define SMORE_ERR_CUDA (-4)       /* the CUDA runtime reported an error (see smore_last_error) */
+#define SMORE_ERR_WORKSPACE (-5)  /* scratch buffer missing, misaligned or too small */
+#define SMORE_ERR_TOO_LARGE (-6)  /* size beyond what an entry point supports */
+
+/* Distance ids.  Same set and order as the name dispatch of the reference
+ * (ext_cuda_kernel.cu:27-46) without the beta family. */
+enum smore_dist {
+  SMORE_DIST_BOX_OUT = 0,  /* sum relu(|e - c| - o)                 dist_kernel.h:58-79   */
+  SMORE_DIST_BOX_IN = 1,   /* sum |min(|e - c|, o)|                 dist_kernel.h:82-105  */
+  SMORE_DIST_ROTATE = 2,   /* sum sqrt((e0-re)^2 + (e1-im)^2 + eps) dist_kernel.h:108-126 */
+  SMORE_DIST_L1 = 3,       /* sum |e - c|                           dist_kernel.h:129-155 */
+  SMORE_DIST_L2 = 4,       /* sum (e - c)^2  (no root)              dist_kernel.h:158-184 */
+  SMORE_DIST_COMPLEX = 5,  /* sum e0*re + e1*im                     dist_kernel.h:187-204 */
+  SMORE_DIST_DISTMULT = 6, /* sum e*c                               dist_kernel.h:324-349 */
+  SMORE_DIST_COUNT = 7
+};
+
+enum smore_opt {
+  SMORE_OPT_SGD = 0,     /* embed_optimizer.py:166-185 */
+  SMORE_OPT_ADAM = 1,    /* embed_optimizer.py:188-252 */
+  SMORE_OPT_ADAGRAD = 2  /* embed_optimizer.py:312-349 */
+};
+
+SMORE_API const char* smore_last_error(void);
+/* Library build tag, e.g. "smore_b200 sm_100a". */
+SMORE_API const char* smore_version(void);
+/* Number of this library's kernels enqueued by the calling process so far (all threads, all
+ * streams); memsets are not counted.  For accounting in benchmarks. */
+SMORE_API unsigned long long smore_kernel_launch_count(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Distance ops on materialised operands.
+ * Replace DistImpl<float>::forward / ::backward (ext_cuda_kernel.h:24-32, ext_cuda_kernel.cu:25-77)
+ * and the dist_forward / dist_backward bindings above them (extlib_cuda.cpp:172-196, 233-262).
+ * `second` / `g_second` may be NULL for l1, l2, distmult.  Every element of dst, g_ent, g_first
+ * and g_second is written; the caller need not clear them.
+ * ------------------------------------------------------------------------------------------ */
+SMORE_API int smore_dist_forward(int dist_id, const float* ent, const float* first, const float* second,
+                       float* dst, size_t bsize, size_t num, size_t be, size_t ne, size_t bc,
+                       size_t nc, size_t dim, void* stream);
+
+SMORE_API int smore_dist_backward(int dist_id, const float* gout, const float* ent, const float* first,
+                        const float* second, float* g_ent, float* g_first, float* g_second,
+                        size_t bsize, size_t num, size_t be, size_t ne, size_t bc, size_t nc,
+                        size_t dim, void* stream);
+
+/* fp64 instantiation (the reference dispatches over float and double,
+ * extlib_cuda.cpp:187,249; ext_cuda_kernel.cu:79-80). */
+SMORE_API int smore_dist_forward_f64(int dist_id, const double* ent, const double* first,
+                           const double* second, double* dst, size_t bsize, size_t num, size_t be,
+                           size_t ne, size_t bc, size_t nc, size_t dim, void* stream);
+
+SMORE_API int smore_dist_backward_f64(int dist_id, const double* gout, const double* ent,
+                            const double* first, const double* second, double* g_ent,
+                            double* g_first, double* g_second, size_t bsize, size_t num, size_t be,
+                            size_t ne, size_t bc, size_t nc, size_t dim, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Distance ops that read entity rows straight from the table.
+ * The entity operand is (table[n_table_rows, mul*dim], idx[be*ne] int64) instead of the gathered
+ * copy that SparseEmbedding.forward -> EmbeddingRW.read materialises (sparse_embed.py:56-67,
+ * embed_rw.py:74-77) before the op runs; results equal smore_dist_forward on table[idx].
+ *
+ * Backward does not produce a [be, ne, mul*dim] gradient.  It adds each row's gradient into
+ * g_rows[slot[p], :] (p = position in idx), the compact per-step buffer that
+ * merge_grad_indices / merge_grad_list (embed_optimizer.py:39-48) would build afterwards:
+ * `slot` is the inverse map of the step's sorted-unique row list and slot_count[s] the number
+ * of positions of the whole step that map to s (see smore_unique_rows).  A row with
+ * slot_count == 1 is stored, others are accumulated with atomics, so g_rows rows with
+ * slot_count > 1 must be zero beforehand (smore_zero_shared_rows).
+ * g_first / g_second are fully written as in smore_dist_backward.
+ * ------------------------------------------------------------------------------------------ */
+SMORE_API int smore_dist_forward_rows(int dist_id, const float* table, const int64_t* idx,
+                            const float* first, const float* second, float* dst, size_t bsize,
+                            size_t num, size_t be, size_t ne, size_t bc, size_t nc, size_t dim,
+                            void* stream);
+
+SMORE_API int smore_dist_backward_rows(int dist_id, const float* gout, const float* table,
+                             const int64_t* idx, const float* first, const float* second,
+                             const int32_t* slot, const int32_t* slot_count, float* g_rows,
+                             float* g_first, float* g_second, size_t bsize, size_t num, size_t be,
+                             size_t ne, size_t bc, size_t nc, size_t dim, void* stream);
+
+/* Query2box scores both box distances of the same operands (box.py:157-164 calls box_dist_out
+ * and box_dist_in back to back).  These two entry points read every entity row once and return
+ * / consume both: dst_out, dst_in and gout_out, gout_in are [bsize, num].
+ * idx == NULL means `ent` is a materialised [be, ne, dim] operand; then g_ent ([be, ne, dim])
+ * receives the entity gradient and slot / slot_count / g_rows must be NULL.  With idx != NULL
+ * the rules of the _rows entry points apply and g_ent must be NULL. */
+SMORE_API int smore_box_forward(const float* ent, const int64_t* idx, const float* center,
+                      const float* offset, float* dst_out, float* dst_in, size_t bsize, size_t num,
+                      size_t be, size_t ne, size_t bc, size_t nc, size_t dim, void* stream);
+
+SMORE_API int smore_box_backward(const float* gout_out, const float* gout_in, const float* ent,
+                       const int64_t* idx, const float* center, const float* offset, float* g_ent,
+                       const int32_t* slot, const int32_t* slot_count, float* g_rows,
+                       float* g_center, float* g_offset, size_t bsize, size_t num, size_t be,
+                       size_t ne, size_t bc, size_t nc, size_t dim, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Row gather, per-step gradient merge and row-wise optimizers.
+ * ------------------------------------------------------------------------------------------ */
+
+/* out[p, :] = table[idx[p], :]   (embed_rw.py:74-77: self.embed[indices]). */
+SMORE_API int smore_gather_rows(const float* table, const int64_t* idx, float* out, size_t n, size_t width,
+                      void* stream);
+
+/* Sorted-unique of a step's row ids with inverse map — the result of
+ * torch.unique(cat(idx_list), return_inverse=True) in merge_grad_indices
+ * (embed_optimizer.py:39-42), bit for bit: uniq ascending, inverse[p] = rank of idx[p].
+ *   idx[n] int64, every value in [0, n_table_rows)   (values outside are reported, see below)
+ *   uniq[n] int64 (first *n_unique entries valid), inverse[n] int32, counts[n] int32
+ *   n_unique: device int32[2]; [0] = number of distinct ids, [1] = number of out-of-range ids
+ *             (those positions get inverse -1 and are ignored everywhere else)
+ *   workspace: device scratch of at least smore_unique_rows_workspace_bytes(n_table_rows) bytes,
+ *              256-byte aligned; contents are scratch on entry and exit.
+ * Cost is O(n_table_rows / 32 + n): a presence bitmap over the id space and a popcount scan,
+ * not a sort. */
+SMORE_API size_t smore_unique_rows_workspace_bytes(size_t n_table_rows);
+SMORE_API int smore_unique_rows(const int64_t* idx, size_t n, size_t n_table_rows, int64_t* uniq,
+                      int32_t* inverse, int32_t* counts, int32_t* n_unique, void* workspace,
+                      size_t workspace_bytes, void* stream);
+
+/* Zero the rows of g_rows[capacity, width] whose slot_count > 1 (see smore_dist_backward_rows).
+ * n_unique is the device counter written by smore_unique_rows. */
+SMORE_API int smore_zero_shared_rows(float* g_rows, const int32_t* slot_count, const int32_t* n_unique,
+                           size_t capacity, size_t width, void* stream);
+
+/* g_rows[slot[p], :] (+)= grad[p, :] for p < n — merge_grad_list's scatter-sum
+ * (embed_optimizer.py:45-48) for gradients that autograd delivers as a dense [n, width]
+ * block (anchor and positive-entity lookups).  Store when slot_count == 1, atomic add
+ * otherwise; positions with slot < 0 are skipped. */
+SMORE_API int smore_scatter_add_rows(const float* grad, const int32_t* slot, const int32_t* slot_count,
+                           float* g_rows, size_t n, size_t width, void* stream);
+
+/* Row-wise optimizer step on the touched rows: for u < *n_unique, row = uniq[u], g = g_rows[u,:].
+ *   SGD      table[row] += -lr * g
+ *   Adam     m, v moments (v is [N, width], or [N] row-wise mean of g^2 when squeeze != 0),
+ *            beta1, beta2, eps, one optimizer-wide `step` (>= 1) for the bias corrections
+ *            (embed_optimizer.py:208-252)
+ *   Adagrad  v accumulates g^2 (or its row mean)          (embed_optimizer.py:328-349)
+ * m may be NULL for SGD/Adagrad, v NULL for SGD. */
+SMORE_API int smore_sparse_update_rows(int opt_id, float* table, float* m, float* v, const int64_t* uniq,
+                             const float* g_rows, const int32_t* n_unique, size_t capacity,
+                             size_t width, double lr, double beta1, double beta2, double eps,
+                             int64_t step, int squeeze, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SMORE_B200_H_ */

@@ -1,0 +1,676 @@
+// Distance-op kernels for sm_100a and their C entry points.
+//
+// Two kernel families:
+//   * "cell" kernels — any broadcast combination the op contract allows, any dim, fp32 or fp64.
+//     Forward: one warp per output cell.  Backward: one thread per gradient element that walks
+//     the cells using it in a fixed order (deterministic, coalesced over the embedding dim).
+//   * "row-stream" kernels — the training shape in which every query owns its own candidate
+//     rows (entity [B, K, W] or table + idx[B, K]; query [B, 1, dim]).  A CTA keeps one query
+//     in registers and streams a block of that query's candidate rows with 128-bit loads,
+//     several rows in flight per warp; backward produces the row gradients and the query
+//     gradient in the same pass.  This is the HBM-bound hot path.
+//
+// Replaces smore/common/torchext/common_kernel.h:33-145 (the three reference kernels and their
+// launchers) and the dispatch of smore/common/torchext/ext_cuda_kernel.cu:25-77.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "dist_terms.cuh"
+
+namespace smore {
+
+// ----------------------------------------------------------------------------------------
+// cell kernels
+// ----------------------------------------------------------------------------------------
+
+template <typename T>
+struct CellArgs {
+  const T* ent;        // [be*ne, mul*dim] or table when idx != nullptr
+  const int64_t* idx;  // nullable: row ids into `ent`
+  const T* first;      // [bc*nc, dim]
+  const T* second;     // [bc*nc, dim] (== first for single-operand distances)
+  size_t bsize, num, be, ne, bc, nc, dim;
+};
+
+template <typename T, class Term>
+__global__ void __launch_bounds__(256) cell_forward_kernel(CellArgs<T> a, T* __restrict__ dst0,
+                                                           T* __restrict__ dst1) {
+  const int lane = threadIdx.x & 31;
+  const size_t warps_per_grid = (size_t)gridDim.x * (blockDim.x >> 5);
+  const size_t cells = a.bsize * a.num;
+  for (size_t cell = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); cell < cells;
+       cell += warps_per_grid) {
+    const size_t i = cell / a.num, j = cell - i * a.num;
+    size_t row = (i % a.be) * a.ne + (j % a.ne);
+    if (a.idx) row = (size_t)a.idx[row];
+    const T* pe = a.ent + row * a.dim * Term::kMul;
+    const size_t qrow = (i % a.bc) * a.nc + (j % a.nc);
+    const T* p0 = a.first + qrow * a.dim;
+    const T* p1 = a.second + qrow * a.dim;
+    T acc[Term::kNOut];
+#pragma unroll
+    for (int o = 0; o < Term::kNOut; ++o) acc[o] = T(0);
+    for (size_t d = lane; d < a.dim; d += kWarp) {
+      const T e0 = pe[d];
+      const T e1 = Term::kMul == 2 ? pe[d + a.dim] : T(0);
+      Term::fwd(e0, e1, p0[d], p1[d], acc);
+    }
+#pragma unroll
+    for (int o = 0; o < Term::kNOut; ++o) {
+#pragma unroll
+      for (int m = kWarp / 2; m > 0; m >>= 1) acc[o] += __shfl_xor_sync(0xffffffffu, acc[o], m);
+    }
+    if (lane == 0) {
+      dst0[cell] = acc[0];
+      if (Term::kNOut == 2) dst1[cell] = acc[Term::kNOut - 1];
+    }
+  }
+}
+
+// One thread per (entity position, d).  With slot == nullptr the result is stored to
+// g_ent[position]; otherwise it goes to g_rows[slot[position]] (store when that slot has a
+// single contributor in the whole step, atomic otherwise).
+template <typename T, class Term>
+__global__ void __launch_bounds__(256)
+    cell_backward_ent_kernel(CellArgs<T> a, const T* __restrict__ gout0, const T* __restrict__ gout1,
+                             T* __restrict__ g_ent, const int32_t* __restrict__ slot,
+                             const int32_t* __restrict__ slot_count, T* __restrict__ g_rows) {
+  const size_t total = a.be * a.ne * a.dim;
+  const size_t nji = a.bsize / a.be, njj = a.num / a.ne;
+  for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total;
+       t += (size_t)gridDim.x * blockDim.x) {
+    const size_t pos = t / a.dim, d = t - pos * a.dim;
+    const size_t r0 = pos / a.ne, r1 = pos - r0 * a.ne;
+    const size_t row = a.idx ? (size_t)a.idx[pos] : pos;
+    const T* pe = a.ent + row * a.dim * Term::kMul;
+    const T e0 = pe[d];
+    const T e1 = Term::kMul == 2 ? pe[d + a.dim] : T(0);
+    T ge0 = T(0), ge1 = T(0), t0 = T(0), t1 = T(0);
+    for (size_t ji = 0; ji < nji; ++ji) {
+      const size_t i = ji * a.be + r0;
+      for (size_t jj = 0; jj < njj; ++jj) {
+        const size_t j = jj * a.ne + r1;
+        const size_t qrow = (i % a.bc) * a.nc + (j % a.nc);
+        T g[Term::kNOut];
+        g[0] = gout0[i * a.num + j];
+        if (Term::kNOut == 2) g[Term::kNOut - 1] = gout1[i * a.num + j];
+        Term::bwd(g, e0, e1, a.first[qrow * a.dim + d], a.second[qrow * a.dim + d], ge0, ge1, t0, t1);
+      }
+    }
+    if (slot == nullptr) {
+      T* out = g_ent + pos * a.dim * Term::kMul;
+      out[d] = ge0;
+      if (Term::kMul == 2) out[d + a.dim] = ge1;
+    } else {
+      const int32_t s = slot[pos];
+      if (s < 0) continue;
+      T* out = g_rows + (size_t)s * a.dim * Term::kMul;
+      if (slot_count[s] == 1) {
+        out[d] = ge0;
+        if (Term::kMul == 2) out[d + a.dim] = ge1;
+      } else {
+        atomicAdd(out + d, ge0);
+        if (Term::kMul == 2) atomicAdd(out + d + a.dim, ge1);
+      }
+    }
+  }
+}
+
+template <typename T, class Term>
+__global__ void __launch_bounds__(256)
+    cell_backward_query_kernel(CellArgs<T> a, const T* __restrict__ gout0, const T* __restrict__ gout1,
+                               T* __restrict__ g_first, T* __restrict__ g_second) {
+  const size_t total = a.bc * a.nc * a.dim;
+  const size_t nji = a.bsize / a.bc, njj = a.num / a.nc;
+  for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total;
+       t += (size_t)gridDim.x * blockDim.x) {
+    const size_t qrow = t / a.dim, d = t - qrow * a.dim;
+    const size_t r0 = qrow / a.nc, r1 = qrow - r0 * a.nc;
+    const T q0 = a.first[qrow * a.dim + d], q1 = a.second[qrow * a.dim + d];
+    T gq0 = T(0), gq1 = T(0), t0 = T(0), t1 = T(0);
+    for (size_t ji = 0; ji < nji; ++ji) {
+      const size_t i = ji * a.bc + r0;
+      for (size_t jj = 0; jj < njj; ++jj) {
+        const size_t j = jj * a.nc + r1;
+        size_t row = (i % a.be) * a.ne + (j % a.ne);
+        if (a.idx) row = (size_t)a.idx[row];
+        const T* pe = a.ent + row * a.dim * Term::kMul;
+        T g[Term::kNOut];
+        g[0] = gout0[i * a.num + j];
+        if (Term::kNOut == 2) g[Term::kNOut - 1] = gout1[i * a.num + j];
+        Term::bwd(g, pe[d], Term::kMul == 2 ? pe[d + a.dim] : T(0), q0, q1, t0, t1, gq0, gq1);
+      }
+    }
+    g_first[qrow * a.dim + d] = gq0;
+    if (Term::kNQ == 2) g_second[qrow * a.dim + d] = gq1;
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// row-stream kernels (per-query candidate rows)
+// ----------------------------------------------------------------------------------------
+
+constexpr int kRowCtaThreads = 256;
+constexpr int kRowCtaWarps = kRowCtaThreads / kWarp;
+
+struct RowArgs {
+  const float* ent;        // dense [B*K, W] or table [N, W] when idx != nullptr
+  const int64_t* idx;      // nullable [B*K]
+  const float* first;      // [B, dim]
+  const float* second;     // [B, dim]
+  int K;                   // candidate rows per query
+  int dim;                 // multiple of 4
+  int rows_per_cta;        // multiple of kRowCtaWarps * wrows
+  int chunks;              // CTAs per query
+  int wrows;               // rows a warp takes per sweep (<= 32)
+};
+
+__device__ __forceinline__ float4 ld_row4(const float4* p) { return __ldg(p); }
+
+// acc over the 4 components of one 16-byte chunk
+template <class Term>
+__device__ __forceinline__ void fwd4(const float4& e0, const float4& e1, const float4& q0,
+                                     const float4& q1, float* acc) {
+  Term::fwd(e0.x, e1.x, q0.x, q1.x, acc);
+  Term::fwd(e0.y, e1.y, q0.y, q1.y, acc);
+  Term::fwd(e0.z, e1.z, q0.z, q1.z, acc);
+  Term::fwd(e0.w, e1.w, q0.w, q1.w, acc);
+}
+
+template <class Term>
+__device__ __forceinline__ void bwd4(const float* g, const float4& e0, const float4& e1,
+                                     const float4& q0, const float4& q1, float4& ge0, float4& ge1,
+                                     float4& gq0, float4& gq1) {
+  Term::bwd(g, e0.x, e1.x, q0.x, q1.x, ge0.x, ge1.x, gq0.x, gq1.x);
+  Term::bwd(g, e0.y, e1.y, q0.y, q1.y, ge0.y, ge1.y, gq0.y, gq1.y);
+  Term::bwd(g, e0.z, e1.z, q0.z, q1.z, ge0.z, ge1.z, gq0.z, gq1.z);
+  Term::bwd(g, e0.w, e1.w, q0.w, q1.w, ge0.w, ge1.w, gq0.w, gq1.w);
+}
+
+template <class Term, int NCH, int R>
+__global__ void __launch_bounds__(kRowCtaThreads)
+    row_forward_kernel(RowArgs a, float* __restrict__ dst0, float* __restrict__ dst1) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int b = blockIdx.x / a.chunks, c = blockIdx.x - b * a.chunks;
+  const int dim4 = a.dim >> 2;
+  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+
+  float4 q0[NCH], q1[NCH];
+  {
+    const float4* p0 = reinterpret_cast<const float4*>(a.first + (size_t)b * a.dim);
+    const float4* p1 = reinterpret_cast<const float4*>(a.second + (size_t)b * a.dim);
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int d4 = lane + 32 * j;
+      q0[j] = d4 < dim4 ? __ldg(p0 + d4) : z4;
+      q1[j] = (Term::kNQ == 2 && d4 < dim4) ? __ldg(p1 + d4) : z4;
+    }
+  }
+
+  const int r_begin = c * a.rows_per_cta;
+  const int r_end = min(a.K, r_begin + a.rows_per_cta);
+  const size_t w4 = (size_t)dim4 * Term::kMul;
+  const float4* ent4 = reinterpret_cast<const float4*>(a.ent);
+
+  for (int base = r_begin + warp * a.wrows; base < r_end; base += kRowCtaWarps * a.wrows) {
+    const int n = min(a.wrows, r_end - base);
+    const size_t pos = (size_t)b * a.K + base + lane;
+    long long myrow = 0;
+    if (lane < n) myrow = a.idx ? (long long)a.idx[pos] : (long long)pos;
+    float out0 = 0.f, out1 = 0.f;
+    for (int t = 0; t < n; t += R) {
+      float4 e[R][Term::kMul][NCH];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const long long row = __shfl_sync(0xffffffffu, myrow, min(t + r, n - 1));
+        const float4* pe = ent4 + (size_t)row * w4;
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) {
+          const int d4 = lane + 32 * j;
+          if (d4 < dim4) {
+            e[r][0][j] = ld_row4(pe + d4);
+            if (Term::kMul == 2) e[r][Term::kMul - 1][j] = ld_row4(pe + dim4 + d4);
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float acc[Term::kNOut];
+#pragma unroll
+        for (int o = 0; o < Term::kNOut; ++o) acc[o] = 0.f;
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) {
+          if (lane + 32 * j < dim4) fwd4<Term>(e[r][0][j], e[r][Term::kMul - 1][j], q0[j], q1[j], acc);
+        }
+#pragma unroll
+        for (int o = 0; o < Term::kNOut; ++o) acc[o] = warp_sum(acc[o]);
+        if (lane == t + r) {
+          out0 = acc[0];
+          out1 = acc[Term::kNOut - 1];
+        }
+      }
+    }
+    if (lane < n) {
+      dst0[pos] = out0;
+      if (Term::kNOut == 2) dst1[pos] = out1;
+    }
+  }
+}
+
+struct RowGradArgs {
+  const float* gout0;         // [B, K]
+  const float* gout1;         // [B, K] (two-output term only)
+  float* g_ent;               // dense [B*K, W], or nullptr when slot != nullptr
+  const int32_t* slot;        // [B*K] -> row of g_rows, < 0 to skip
+  const int32_t* slot_count;  // contributors per slot over the whole step
+  float* g_rows;              // [capacity, W]
+  float* g_first;             // [B, dim]
+  float* g_second;            // [B, dim]
+  int query_atomic;           // several CTAs share one query: accumulate into zeroed g_first/second
+};
+
+__device__ __forceinline__ void add4(float4& a, const float4& b) {
+  a.x += b.x;
+  a.y += b.y;
+  a.z += b.z;
+  a.w += b.w;
+}
+
+template <class Term, int NCH, int R>
+__global__ void __launch_bounds__(kRowCtaThreads) row_backward_kernel(RowArgs a, RowGradArgs ga) {
+  extern __shared__ float4 red[];  // [kNQ][dim4]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int b = blockIdx.x / a.chunks, c = blockIdx.x - b * a.chunks;
+  const int dim4 = a.dim >> 2;
+  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+
+  float4 q0[NCH], q1[NCH], gq0[NCH], gq1[NCH];
+  {
+    const float4* p0 = reinterpret_cast<const float4*>(a.first + (size_t)b * a.dim);
+    const float4* p1 = reinterpret_cast<const float4*>(a.second + (size_t)b * a.dim);
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int d4 = lane + 32 * j;
+      q0[j] = d4 < dim4 ? __ldg(p0 + d4) : z4;
+      q1[j] = (Term::kNQ == 2 && d4 < dim4) ? __ldg(p1 + d4) : z4;
+      gq0[j] = z4;
+      gq1[j] = z4;
+    }
+  }
+
+  const int r_begin = c * a.rows_per_cta;
+  const int r_end = min(a.K, r_begin + a.rows_per_cta);
+  const size_t w4 = (size_t)dim4 * Term::kMul;
+  const float4* ent4 = reinterpret_cast<const float4*>(a.ent);
+
+  for (int base = r_begin + warp * a.wrows; base < r_end; base += kRowCtaWarps * a.wrows) {
+    const int n = min(a.wrows, r_end - base);
+    const size_t pos = (size_t)b * a.K + base + lane;
+    long long myrow = 0;
+    long long mydst = -1;  // destination row of the gradient, < 0: skip
+    int mysingle = 1;
+    float g0 = 0.f, g1 = 0.f;
+    if (lane < n) {
+      myrow = a.idx ? (long long)a.idx[pos] : (long long)pos;
+      g0 = ga.gout0[pos];
+      if (Term::kNOut == 2) g1 = ga.gout1[pos];
+      if (ga.slot) {
+        const int32_t s = ga.slot[pos];
+        mydst = s;
+        mysingle = s >= 0 ? (ga.slot_count[s] == 1) : 1;
+      } else {
+        mydst = (long long)pos;
+      }
+    }
+    float* gbase = ga.slot ? ga.g_rows : ga.g_ent;
+    for (int t = 0; t < n; t += R) {
+      float4 e[R][Term::kMul][NCH];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const long long row = __shfl_sync(0xffffffffu, myrow, min(t + r, n - 1));
+        const float4* pe = ent4 + (size_t)row * w4;
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) {
+          const int d4 = lane + 32 * j;
+          if (d4 < dim4) {
+            e[r][0][j] = ld_row4(pe + d4);
+            if (Term::kMul == 2) e[r][Term::kMul - 1][j] = ld_row4(pe + dim4 + d4);
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int src = min(t + r, n - 1);
+        float g[Term::kNOut];
+        g[0] = __shfl_sync(0xffffffffu, g0, src);
+        if (Term::kNOut == 2) g[Term::kNOut - 1] = __shfl_sync(0xffffffffu, g1, src);
+        const long long dst = __shfl_sync(0xffffffffu, mydst, src);
+        const int single = __shfl_sync(0xffffffffu, mysingle, src);
+        if (t + r >= n) continue;  // warp-uniform
+        float4* gout_row = reinterpret_cast<float4*>(gbase) + (size_t)(dst < 0 ? 0 : dst) * w4;
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) {
+          const int d4 = lane + 32 * j;
+          if (d4 < dim4) {
+            float4 ge0 = z4, ge1 = z4;
+            bwd4<Term>(g, e[r][0][j], e[r][Term::kMul - 1][j], q0[j], q1[j], ge0, ge1, gq0[j], gq1[j]);
+            if (dst >= 0) {
+              if (single) {
+                gout_row[d4] = ge0;
+                if (Term::kMul == 2) gout_row[dim4 + d4] = ge1;
+              } else {
+                atomicAdd(gout_row + d4, ge0);
+                if (Term::kMul == 2) atomicAdd(gout_row + dim4 + d4, ge1);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // fold the 8 warps' query gradients in warp order (fixed order: deterministic per CTA)
+  for (int w = 0; w < kRowCtaWarps; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const int d4 = lane + 32 * j;
+        if (d4 < dim4) {
+          if (w == 0) {
+            red[d4] = gq0[j];
+            if (Term::kNQ == 2) red[dim4 + d4] = gq1[j];
+          } else {
+            add4(red[d4], gq0[j]);
+            if (Term::kNQ == 2) add4(red[dim4 + d4], gq1[j]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  float4* gf = reinterpret_cast<float4*>(ga.g_first + (size_t)b * a.dim);
+  float4* gs = reinterpret_cast<float4*>(ga.g_second + (size_t)b * a.dim);
+  for (int d4 = threadIdx.x; d4 < dim4; d4 += kRowCtaThreads) {
+    if (ga.query_atomic) {
+      atomicAdd(gf + d4, red[d4]);
+      if (Term::kNQ == 2) atomicAdd(gs + d4, red[dim4 + d4]);
+    } else {
+      gf[d4] = red[d4];
+      if (Term::kNQ == 2) gs[d4] = red[dim4 + d4];
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// host side: validation, shape classification, launches
+// ----------------------------------------------------------------------------------------
+
+struct Shape {
+  size_t bsize, num, be, ne, bc, nc, dim;
+};
+
+static int validate_shape(const Shape& s) {
+  if (!s.bsize || !s.num || !s.be || !s.ne || !s.bc || !s.nc || !s.dim)
+    return fail(SMORE_ERR_BAD_SHAPE, "all sizes must be positive");
+  if (s.bsize != std::max(s.be, s.bc) || s.num != std::max(s.ne, s.nc))
+    return fail(SMORE_ERR_BAD_SHAPE, "output must be [max(be,bc), max(ne,nc)]");
+  if (s.bsize % s.be || s.bsize % s.bc || s.num % s.ne || s.num % s.nc)
+    return fail(SMORE_ERR_BAD_SHAPE, "operand sizes must divide the output sizes");
+  if (s.dim > (size_t)1 << 30 || s.bsize * s.num > (size_t)1 << 40)
+    return fail(SMORE_ERR_TOO_LARGE, "operand too large");
+  return SMORE_OK;
+}
+
+static int grid_for(size_t work_items, int per_block) {
+  size_t blocks = (work_items + per_block - 1) / per_block;
+  const size_t cap = (size_t)kNumSM * 32;
+  return (int)std::max<size_t>(1, std::min(blocks, cap));
+}
+
+// row-stream launch plan; chunks == 0 means "not eligible"
+struct RowPlan {
+  int nch, wrows, rows_per_cta, chunks;
+};
+
+static RowPlan plan_rows(const Shape& s, bool aligned) {
+  RowPlan p{0, 0, 0, 0};
+  const bool shape_ok = s.be == s.bsize && s.bc == s.bsize && s.ne == s.num && s.nc == 1;
+  if (!shape_ok || !aligned || (s.dim & 3) || s.dim > 1024 || s.num < 4 || s.num > (size_t)1 << 30 ||
+      s.bsize > (size_t)1 << 24)
+    return p;
+  const int dim4 = (int)(s.dim >> 2);
+  p.nch = dim4 <= 32 ? 1 : dim4 <= 64 ? 2 : dim4 <= 128 ? 4 : 8;
+  const size_t K = s.num;
+  int wrows = 32;
+  while (wrows > 4 && (size_t)wrows * kRowCtaWarps / 2 >= K) wrows >>= 1;
+  p.wrows = wrows;
+  const size_t sweep = (size_t)wrows * kRowCtaWarps;
+  size_t sweeps_per_cta = 1;
+  const size_t sweeps_total = (K + sweep - 1) / sweep;
+  // keep the grid within a few dozen waves; larger blocks of rows amortise the query load
+  const size_t max_ctas = (size_t)kNumSM * 32;
+  while (s.bsize * ((sweeps_total + sweeps_per_cta - 1) / sweeps_per_cta) > max_ctas &&
+         sweeps_per_cta < sweeps_total)
+    sweeps_per_cta *= 2;
+  p.rows_per_cta = (int)std::min<size_t>(sweep * sweeps_per_cta, (size_t)1 << 30);
+  p.chunks = (int)((K + p.rows_per_cta - 1) / p.rows_per_cta);
+  return p;
+}
+
+template <class Term>
+static int launch_forward(const Shape& s, const float* ent, const int64_t* idx, const float* first,
+                          const float* second, float* dst0, float* dst1, cudaStream_t st) {
+  if (Term::kNQ == 1) second = first;
+  const bool aligned = aligned16(ent) && aligned16(first) && aligned16(second);
+  const RowPlan p = plan_rows(s, aligned);
+  if (p.chunks > 0) {
+    RowArgs a{ent, idx, first, second, (int)s.num, (int)s.dim, p.rows_per_cta, p.chunks, p.wrows};
+    const unsigned grid = (unsigned)(s.bsize * p.chunks);
+    constexpr int R = Term::kMul == 2 ? 2 : 2;
+    switch (p.nch) {
+      case 1: row_forward_kernel<Term, 1, 4><<<grid, kRowCtaThreads, 0, st>>>(a, dst0, dst1); break;
+      case 2: row_forward_kernel<Term, 2, 4><<<grid, kRowCtaThreads, 0, st>>>(a, dst0, dst1); break;
+      case 4: row_forward_kernel<Term, 4, R><<<grid, kRowCtaThreads, 0, st>>>(a, dst0, dst1); break;
+      default: row_forward_kernel<Term, 8, 1><<<grid, kRowCtaThreads, 0, st>>>(a, dst0, dst1); break;
+    }
+    return check_launch("row_forward_kernel");
+  }
+  CellArgs<float> a{ent, idx, first, second, s.bsize, s.num, s.be, s.ne, s.bc, s.nc, s.dim};
+  cell_forward_kernel<float, Term><<<grid_for(s.bsize * s.num, 8), 256, 0, st>>>(a, dst0, dst1);
+  return check_launch("cell_forward_kernel");
+}
+
+template <class Term>
+static int launch_backward(const Shape& s, const float* gout0, const float* gout1, const float* ent,
+                           const int64_t* idx, const float* first, const float* second, float* g_ent,
+                           const int32_t* slot, const int32_t* slot_count, float* g_rows,
+                           float* g_first, float* g_second, cudaStream_t st) {
+  if (Term::kNQ == 1) {
+    second = first;
+    g_second = g_first;
+  }
+  float* gdst = slot ? g_rows : g_ent;
+  const bool aligned = aligned16(ent) && aligned16(first) && aligned16(second) && aligned16(gdst) &&
+                       aligned16(g_first) && aligned16(g_second);
+  const RowPlan p = plan_rows(s, aligned);
+  if (p.chunks > 0) {
+    RowArgs a{ent, idx, first, second, (int)s.num, (int)s.dim, p.rows_per_cta, p.chunks, p.wrows};
+    RowGradArgs ga{gout0, gout1, g_ent, slot, slot_count, g_rows, g_first, g_second, p.chunks > 1};
+    if (p.chunks > 1) {
+      cudaMemsetAsync(g_first, 0, s.bsize * s.dim * sizeof(float), st);
+      if (Term::kNQ == 2) cudaMemsetAsync(g_second, 0, s.bsize * s.dim * sizeof(float), st);
+    }
+    const unsigned grid = (unsigned)(s.bsize * p.chunks);
+    const size_t smem = (size_t)Term::kNQ * s.dim * sizeof(float);
+    switch (p.nch) {
+      case 1: row_backward_kernel<Term, 1, 4><<<grid, kRowCtaThreads, smem, st>>>(a, ga); break;
+      case 2: row_backward_kernel<Term, 2, 2><<<grid, kRowCtaThreads, smem, st>>>(a, ga); break;
+      case 4: row_backward_kernel<Term, 4, 2><<<grid, kRowCtaThreads, smem, st>>>(a, ga); break;
+      default: row_backward_kernel<Term, 8, 1><<<grid, kRowCtaThreads, smem, st>>>(a, ga); break;
+    }
+    return check_launch("row_backward_kernel");
+  }
+  CellArgs<float> a{ent, idx, first, second, s.bsize, s.num, s.be, s.ne, s.bc, s.nc, s.dim};
+  cell_backward_ent_kernel<float, Term><<<grid_for(s.be * s.ne * s.dim, 256), 256, 0, st>>>(
+      a, gout0, gout1, g_ent, slot, slot_count, g_rows);
+  cell_backward_query_kernel<float, Term><<<grid_for(s.bc * s.nc * s.dim, 256), 256, 0, st>>>(
+      a, gout0, gout1, g_first, g_second);
+  return check_launch("cell_backward kernels", 2);
+}
+
+template <class Term>
+static int launch_forward_f64(const Shape& s, const double* ent, const double* first,
+                              const double* second, double* dst, cudaStream_t st) {
+  if (Term::kNQ == 1) second = first;
+  CellArgs<double> a{ent, nullptr, first, second, s.bsize, s.num, s.be, s.ne, s.bc, s.nc, s.dim};
+  cell_forward_kernel<double, Term><<<grid_for(s.bsize * s.num, 8), 256, 0, st>>>(a, dst, dst);
+  return check_launch("cell_forward_kernel<double>");
+}
+
+template <class Term>
+static int launch_backward_f64(const Shape& s, const double* gout, const double* ent,
+                               const double* first, const double* second, double* g_ent,
+                               double* g_first, double* g_second, cudaStream_t st) {
+  if (Term::kNQ == 1) {
+    second = first;
+    g_second = g_first;
+  }
+  CellArgs<double> a{ent, nullptr, first, second, s.bsize, s.num, s.be, s.ne, s.bc, s.nc, s.dim};
+  cell_backward_ent_kernel<double, Term><<<grid_for(s.be * s.ne * s.dim, 256), 256, 0, st>>>(
+      a, gout, gout, g_ent, nullptr, nullptr, nullptr);
+  cell_backward_query_kernel<double, Term><<<grid_for(s.bc * s.nc * s.dim, 256), 256, 0, st>>>(
+      a, gout, gout, g_first, g_second);
+  return check_launch("cell_backward kernels<double>", 2);
+}
+
+static bool needs_second(int id) {
+  return id == SMORE_DIST_BOX_OUT || id == SMORE_DIST_BOX_IN || id == SMORE_DIST_ROTATE ||
+         id == SMORE_DIST_COMPLEX;
+}
+
+#define SMORE_DISPATCH(id, CALL)                                        \
+  switch (id) {                                                         \
+    case SMORE_DIST_BOX_OUT: { using Term = TermBoxOut; return CALL; }  \
+    case SMORE_DIST_BOX_IN: { using Term = TermBoxIn; return CALL; }    \
+    case SMORE_DIST_ROTATE: { using Term = TermRotate; return CALL; }   \
+    case SMORE_DIST_L1: { using Term = TermL1; return CALL; }           \
+    case SMORE_DIST_L2: { using Term = TermL2; return CALL; }           \
+    case SMORE_DIST_COMPLEX: { using Term = TermComplex; return CALL; } \
+    case SMORE_DIST_DISTMULT: { using Term = TermDistmult; return CALL; } \
+    default: return fail(SMORE_ERR_BAD_DIST, "unknown distance id %d", id); \
+  }
+
+static int forward_common(int id, const float* ent, const int64_t* idx, const float* first,
+                          const float* second, float* dst, const Shape& s, void* stream) {
+  if (id < 0 || id >= SMORE_DIST_COUNT) return fail(SMORE_ERR_BAD_DIST, "unknown distance id %d", id);
+  if (!ent || !first || !dst || (needs_second(id) && !second))
+    return fail(SMORE_ERR_NULL, "forward: required pointer is NULL");
+  if (int rc = validate_shape(s)) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  SMORE_DISPATCH(id, launch_forward<Term>(s, ent, idx, first, second, dst, dst, st));
+}
+
+static int backward_common(int id, const float* gout, const float* ent, const int64_t* idx,
+                           const float* first, const float* second, float* g_ent, const int32_t* slot,
+                           const int32_t* slot_count, float* g_rows, float* g_first, float* g_second,
+                           const Shape& s, void* stream) {
+  if (id < 0 || id >= SMORE_DIST_COUNT) return fail(SMORE_ERR_BAD_DIST, "unknown distance id %d", id);
+  if (!gout || !ent || !first || !g_first || (needs_second(id) && (!second || !g_second)))
+    return fail(SMORE_ERR_NULL, "backward: required pointer is NULL");
+  if (slot ? (!slot_count || !g_rows) : !g_ent)
+    return fail(SMORE_ERR_NULL, "backward: entity gradient destination is NULL");
+  if (int rc = validate_shape(s)) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  SMORE_DISPATCH(id, launch_backward<Term>(s, gout, gout, ent, idx, first, second, g_ent, slot, slot_count,
+                                           g_rows, g_first, g_second, st));
+}
+
+}  // namespace smore
+
+using namespace smore;
+
+extern "C" {
+
+int smore_dist_forward(int dist_id, const float* ent, const float* first, const float* second, float* dst,
+                       size_t bsize, size_t num, size_t be, size_t ne, size_t bc, size_t nc, size_t dim,
+                       void* stream) {
+  return forward_common(dist_id, ent, nullptr, first, second, dst, Shape{bsize, num, be, ne, bc, nc, dim},
+                        stream);
+}
+
+int smore_dist_backward(int dist_id, const float* gout, const float* ent, const float* first,
+                        const float* second, float* g_ent, float* g_first, float* g_second, size_t bsize,
+                        size_t num, size_t be, size_t ne, size_t bc, size_t nc, size_t dim, void* stream) {
+  return backward_common(dist_id, gout, ent, nullptr, first, second, g_ent, nullptr, nullptr, nullptr,
+                         g_first, g_second, Shape{bsize, num, be, ne, bc, nc, dim}, stream);
+}
+
+int smore_dist_forward_rows(int dist_id, const float* table, const int64_t* idx, const float* first,
+                            const float* second, float* dst, size_t bsize, size_t num, size_t be, size_t ne,
+                            size_t bc, size_t nc, size_t dim, void* stream) {
+  if (!idx) return fail(SMORE_ERR_NULL, "forward_rows: idx is NULL");
+  return forward_common(dist_id, table, idx, first, second, dst, Shape{bsize, num, be, ne, bc, nc, dim},
+                        stream);
+}
+
+int smore_dist_backward_rows(int dist_id, const float* gout, const float* table, const int64_t* idx,
+                             const float* first, const float* second, const int32_t* slot,
+                             const int32_t* slot_count, float* g_rows, float* g_first, float* g_second,
+                             size_t bsize, size_t num, size_t be, size_t ne, size_t bc, size_t nc,
+                             size_t dim, void* stream) {
+  if (!idx || !slot) return fail(SMORE_ERR_NULL, "backward_rows: idx or slot is NULL");
+  return backward_common(dist_id, gout, table, idx, first, second, nullptr, slot, slot_count, g_rows,
+                         g_first, g_second, Shape{bsize, num, be, ne, bc, nc, dim}, stream);
+}
+
+int smore_box_forward(const float* ent, const int64_t* idx, const float* center, const float* offset,
+                      float* dst_out, float* dst_in, size_t bsize, size_t num, size_t be, size_t ne,
+                      size_t bc, size_t nc, size_t dim, void* stream) {
+  if (!ent || !center || !offset || !dst_out || !dst_in)
+    return fail(SMORE_ERR_NULL, "box_forward: required pointer is NULL");
+  const Shape s{bsize, num, be, ne, bc, nc, dim};
+  if (int rc = validate_shape(s)) return rc;
+  return launch_forward<TermBoxBoth>(s, ent, idx, center, offset, dst_out, dst_in, (cudaStream_t)stream);
+}
+
+int smore_box_backward(const float* gout_out, const float* gout_in, const float* ent, const int64_t* idx,
+                       const float* center, const float* offset, float* g_ent, const int32_t* slot,
+                       const int32_t* slot_count, float* g_rows, float* g_center, float* g_offset,
+                       size_t bsize, size_t num, size_t be, size_t ne, size_t bc, size_t nc, size_t dim,
+                       void* stream) {
+  if (!gout_out || !gout_in || !ent || !center || !offset || !g_center || !g_offset)
+    return fail(SMORE_ERR_NULL, "box_backward: required pointer is NULL");
+  if (idx ? (!slot || !slot_count || !g_rows || g_ent) : (!g_ent || slot || g_rows))
+    return fail(SMORE_ERR_NULL, "box_backward: pass g_ent (materialised) or slot/slot_count/g_rows (indexed)");
+  const Shape s{bsize, num, be, ne, bc, nc, dim};
+  if (int rc = validate_shape(s)) return rc;
+  return launch_backward<TermBoxBoth>(s, gout_out, gout_in, ent, idx, center, offset, g_ent, slot, slot_count,
+                                      g_rows, g_center, g_offset, (cudaStream_t)stream);
+}
+
+int smore_dist_forward_f64(int dist_id, const double* ent, const double* first, const double* second,
+                           double* dst, size_t bsize, size_t num, size_t be, size_t ne, size_t bc, size_t nc,
+                           size_t dim, void* stream) {
+  if (!ent || !first || !dst || (needs_second(dist_id) && !second))
+    return fail(SMORE_ERR_NULL, "forward_f64: required pointer is NULL");
+  const Shape s{bsize, num, be, ne, bc, nc, dim};
+  if (int rc = validate_shape(s)) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  SMORE_DISPATCH(dist_id, launch_forward_f64<Term>(s, ent, first, second, dst, st));
+}
+
+int smore_dist_backward_f64(int dist_id, const double* gout, const double* ent, const double* first,
+                            const double* second, double* g_ent, double* g_first, double* g_second,
+                            size_t bsize, size_t num, size_t be, size_t ne, size_t bc, size_t nc, size_t dim,
+                            void* stream) {
+  if (!gout || !ent || !first || !g_ent || !g_first || (needs_second(dist_id) && (!second || !g_second)))
+    return fail(SMORE_ERR_NULL, "backward_f64: required pointer is NULL");
+  const Shape s{bsize, num, be, ne, bc, nc, dim};
+  if (int rc = validate_shape(s)) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  SMORE_DISPATCH(dist_id, launch_backward_f64<Term>(s, gout, ent, first, second, g_ent, g_first, g_second, st));
+}
+
+}  // extern "C"

@@ -1,0 +1,536 @@
+// Row gather, per-step gradient merge (sorted unique + inverse map, scatter-sum) and the
+// row-wise optimizers for sm_100a, with their C entry points.
+//
+// Replaces, for a table that lives in GPU memory:
+//   smore/common/embedding/embed_rw.py:74-77,102-111       (embed[indices], index_add_)
+//   smore/common/embedding/embed_optimizer.py:39-48        (torch.unique + torch_scatter sum)
+//   smore/common/embedding/embed_optimizer.py:166-185      (SGD rows)
+//   smore/common/embedding/embed_optimizer.py:208-252      (Adam rows, ~15 torch kernels)
+//   smore/common/embedding/embed_optimizer.py:328-349      (Adagrad rows)
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+
+#include "common.cuh"
+
+namespace smore {
+
+// ----------------------------------------------------------------------------------------
+// gather
+// ----------------------------------------------------------------------------------------
+
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+    gather_rows_kernel(const float* __restrict__ table, const int64_t* __restrict__ idx,
+                       float* __restrict__ out, size_t n, size_t width) {
+  const int lane = threadIdx.x & 31;
+  const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+  for (size_t p = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); p < n; p += warps) {
+    const size_t row = (size_t)idx[p];
+    if (VEC) {
+      const float4* src = reinterpret_cast<const float4*>(table + row * width);
+      float4* dst = reinterpret_cast<float4*>(out + p * width);
+      for (size_t d = lane; d < width / 4; d += kWarp) dst[d] = __ldg(src + d);
+    } else {
+      const float* src = table + row * width;
+      float* dst = out + p * width;
+      for (size_t d = lane; d < width; d += kWarp) dst[d] = __ldg(src + d);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// sorted unique over a bounded id space: presence bitmap + popcount scan
+// ----------------------------------------------------------------------------------------
+
+constexpr int kScanThreads = 256;
+constexpr int kWordsPerThread = 4;
+constexpr int kWordsPerBlock = kScanThreads * kWordsPerThread;  // 1024 words = 32768 ids
+
+struct UniqueWorkspace {
+  uint32_t* bitmap;      // [nwords]   bit v set <=> id v occurs
+  uint32_t* wordprefix;  // [nwords]   distinct ids below word w
+  uint32_t* blocksum;    // [nblocks]  distinct ids per 1024-word block, then their exclusive scan
+  size_t nwords, nblocks, bytes;
+};
+
+static size_t round256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+static UniqueWorkspace carve_unique_workspace(void* base, size_t n_table_rows) {
+  UniqueWorkspace w;
+  w.nwords = (n_table_rows + 31) / 32;
+  w.nblocks = (w.nwords + kWordsPerBlock - 1) / kWordsPerBlock;
+  const size_t b0 = round256(w.nwords * sizeof(uint32_t));
+  const size_t b2 = round256(w.nblocks * sizeof(uint32_t));
+  char* p = static_cast<char*>(base);
+  w.bitmap = reinterpret_cast<uint32_t*>(p);
+  w.wordprefix = reinterpret_cast<uint32_t*>(p + b0);
+  w.blocksum = reinterpret_cast<uint32_t*>(p + 2 * b0);
+  w.bytes = 2 * b0 + b2;
+  return w;
+}
+
+__global__ void __launch_bounds__(256)
+    unique_mark_kernel(const int64_t* __restrict__ idx, size_t n, size_t n_table_rows,
+                       uint32_t* __restrict__ bitmap, int32_t* __restrict__ n_unique) {
+  for (size_t p = (size_t)blockIdx.x * blockDim.x + threadIdx.x; p < n;
+       p += (size_t)gridDim.x * blockDim.x) {
+    const int64_t v = idx[p];
+    if (v >= 0 && (size_t)v < n_table_rows) {
+      const uint32_t bit = 1u << (v & 31);
+      uint32_t* w = bitmap + (v >> 5);
+      if (!(*w & bit)) atomicOr(w, bit);
+    } else {
+      atomicAdd(n_unique + 1, 1);
+    }
+  }
+}
+
+__device__ __forceinline__ uint32_t block_sum_256(uint32_t v, uint32_t* sh) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  uint32_t t = 0;
+#pragma unroll
+  for (int w = 0; w < kScanThreads / 32; ++w) t += sh[w];
+  __syncthreads();
+  return t;
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+    unique_blocksum_kernel(const uint32_t* __restrict__ bitmap, size_t nwords,
+                           uint32_t* __restrict__ blocksum) {
+  __shared__ uint32_t sh[kScanThreads / 32];
+  const size_t w0 = (size_t)blockIdx.x * kWordsPerBlock + (size_t)threadIdx.x * kWordsPerThread;
+  uint32_t c = 0;
+#pragma unroll
+  for (int k = 0; k < kWordsPerThread; ++k)
+    if (w0 + k < nwords) c += __popc(bitmap[w0 + k]);
+  const uint32_t t = block_sum_256(c, sh);
+  if (threadIdx.x == 0) blocksum[blockIdx.x] = t;
+}
+
+// exclusive scan of blocksum in place by one CTA; total -> n_unique[0]
+__global__ void __launch_bounds__(1024)
+    unique_scan_blocks_kernel(uint32_t* __restrict__ blocksum, size_t nblocks,
+                              int32_t* __restrict__ n_unique) {
+  __shared__ uint32_t warp_tot[32];
+  __shared__ uint32_t carry_sh;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) carry_sh = 0;
+  __syncthreads();
+  for (size_t base = 0; base < nblocks; base += 1024) {
+    const size_t i = base + threadIdx.x;
+    const uint32_t v = i < nblocks ? blocksum[i] : 0;
+    uint32_t inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += t;
+    }
+    if (lane == 31) warp_tot[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+      uint32_t w = warp_tot[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += t;
+      }
+      warp_tot[lane] = w;  // inclusive over warps
+    }
+    __syncthreads();
+    const uint32_t carry = carry_sh;
+    const uint32_t before_warp = warp ? warp_tot[warp - 1] : 0;
+    if (i < nblocks) blocksum[i] = carry + before_warp + inc - v;
+    __syncthreads();
+    if (threadIdx.x == 0) carry_sh = carry + warp_tot[31];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) n_unique[0] = (int32_t)carry_sh;
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+    unique_wordprefix_kernel(const uint32_t* __restrict__ bitmap, size_t nwords,
+                             const uint32_t* __restrict__ blockoff, uint32_t* __restrict__ wordprefix) {
+  __shared__ uint32_t warp_tot[kScanThreads / 32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t w0 = (size_t)blockIdx.x * kWordsPerBlock + (size_t)threadIdx.x * kWordsPerThread;
+  uint32_t c[kWordsPerThread];
+  uint32_t mine = 0;
+#pragma unroll
+  for (int k = 0; k < kWordsPerThread; ++k) {
+    c[k] = (w0 + k < nwords) ? __popc(bitmap[w0 + k]) : 0;
+    mine += c[k];
+  }
+  uint32_t inc = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (lane == 31) warp_tot[warp] = inc;
+  __syncthreads();
+  uint32_t before = blockoff[blockIdx.x];
+  for (int w = 0; w < warp; ++w) before += warp_tot[w];
+  uint32_t run = before + inc - mine;
+#pragma unroll
+  for (int k = 0; k < kWordsPerThread; ++k) {
+    if (w0 + k < nwords) wordprefix[w0 + k] = run;
+    run += c[k];
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    unique_assign_kernel(const int64_t* __restrict__ idx, size_t n, size_t n_table_rows,
+                         const uint32_t* __restrict__ bitmap, const uint32_t* __restrict__ wordprefix,
+                         int64_t* __restrict__ uniq, int32_t* __restrict__ inverse,
+                         int32_t* __restrict__ counts) {
+  for (size_t p = (size_t)blockIdx.x * blockDim.x + threadIdx.x; p < n;
+       p += (size_t)gridDim.x * blockDim.x) {
+    const int64_t v = idx[p];
+    if (v < 0 || (size_t)v >= n_table_rows) {
+      inverse[p] = -1;
+      continue;
+    }
+    const uint32_t word = bitmap[v >> 5];
+    const uint32_t below = word & ((1u << (v & 31)) - 1u);
+    const int32_t s = (int32_t)(wordprefix[v >> 5] + __popc(below));
+    inverse[p] = s;
+    if (atomicAdd(counts + s, 1) == 0) uniq[s] = v;
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// compact gradient buffer helpers
+// ----------------------------------------------------------------------------------------
+
+__global__ void __launch_bounds__(256)
+    zero_shared_rows_kernel(float* __restrict__ g_rows, const int32_t* __restrict__ slot_count,
+                            const int32_t* __restrict__ n_unique, size_t width) {
+  const int lane = threadIdx.x & 31;
+  const size_t nu = (size_t)max(n_unique[0], 0);
+  const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+  for (size_t u = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); u < nu; u += warps) {
+    if (slot_count[u] > 1) {
+      float* r = g_rows + u * width;
+      for (size_t d = lane; d < width; d += kWarp) r[d] = 0.f;
+    }
+  }
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+    scatter_add_rows_kernel(const float* __restrict__ grad, const int32_t* __restrict__ slot,
+                            const int32_t* __restrict__ slot_count, float* __restrict__ g_rows, size_t n,
+                            size_t width) {
+  const int lane = threadIdx.x & 31;
+  const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+  for (size_t p = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); p < n; p += warps) {
+    const int32_t s = slot[p];
+    if (s < 0) continue;
+    const bool single = slot_count[s] == 1;
+    if (VEC) {
+      const float4* src = reinterpret_cast<const float4*>(grad + p * width);
+      float4* dst = reinterpret_cast<float4*>(g_rows + (size_t)s * width);
+      for (size_t d = lane; d < width / 4; d += kWarp) {
+        const float4 v = __ldg(src + d);
+        if (single) dst[d] = v; else atomicAdd(dst + d, v);
+      }
+    } else {
+      const float* src = grad + p * width;
+      float* dst = g_rows + (size_t)s * width;
+      for (size_t d = lane; d < width; d += kWarp) {
+        if (single) dst[d] = src[d]; else atomicAdd(dst + d, src[d]);
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// row-wise optimizers: one warp per touched row, one pass over (g, p, m, v)
+// ----------------------------------------------------------------------------------------
+
+struct UpdateArgs {
+  float* table;
+  float* m;
+  float* v;
+  const int64_t* uniq;
+  const float* g_rows;
+  const int32_t* n_unique;
+  size_t width;
+  float lr, beta1, beta2, omb1, omb2, eps, step_size, sqrt_bc2;
+  int squeeze;
+};
+
+__device__ __forceinline__ void adam_elem(float g, float& p, float& m, float& v, const UpdateArgs& a) {
+  const float v_new = v * a.beta2 + g * g * a.omb2;
+  const float m_new = m * a.beta1 + g * a.omb1;
+  const float denom = sqrtf(v_new) / a.sqrt_bc2 + a.eps;
+  p += a.step_size * m_new / denom;
+  m = m + (m_new - m);  // the reference stores state as old + (new - old), embed_optimizer.py:251-252
+  v = v + (v_new - v);
+}
+
+__device__ __forceinline__ void adam_elem_rowwise(float g, float& p, float& m, float denom,
+                                                  const UpdateArgs& a) {
+  const float m_new = m * a.beta1 + g * a.omb1;
+  p += a.step_size * m_new / denom;
+  m = m + (m_new - m);
+}
+
+template <int OPT, bool VEC>
+__global__ void __launch_bounds__(256) sparse_update_rows_kernel(UpdateArgs a) {
+  const int lane = threadIdx.x & 31;
+  const size_t nu = (size_t)max(a.n_unique[0], 0);
+  const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+  const size_t W = a.width;
+  for (size_t u = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); u < nu; u += warps) {
+    const size_t row = (size_t)a.uniq[u];
+    const float* g = a.g_rows + u * W;
+    float* p = a.table + row * W;
+
+    float g2mean = 0.f;
+    if (OPT != SMORE_OPT_SGD && a.squeeze) {
+      float s = 0.f;
+      if (VEC) {
+        const float4* g4 = reinterpret_cast<const float4*>(g);
+        for (size_t d = lane; d < W / 4; d += kWarp) {
+          const float4 x = g4[d];
+          s += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+        }
+      } else {
+        for (size_t d = lane; d < W; d += kWarp) s += g[d] * g[d];
+      }
+      g2mean = warp_sum(s) / (float)W;
+    }
+
+    if (OPT == SMORE_OPT_SGD) {
+      if (VEC) {
+        const float4* g4 = reinterpret_cast<const float4*>(g);
+        float4* p4 = reinterpret_cast<float4*>(p);
+        for (size_t d = lane; d < W / 4; d += kWarp) {
+          const float4 x = g4[d];
+          float4 y = p4[d];
+          y.x += -a.lr * x.x; y.y += -a.lr * x.y; y.z += -a.lr * x.z; y.w += -a.lr * x.w;
+          p4[d] = y;
+        }
+      } else {
+        for (size_t d = lane; d < W; d += kWarp) p[d] += -a.lr * g[d];
+      }
+    } else if (OPT == SMORE_OPT_ADAGRAD) {
+      if (a.squeeze) {
+        const float s_old = a.v[row];
+        const float avg = sqrtf(s_old + g2mean) + a.eps;
+        if (VEC) {
+          const float4* g4 = reinterpret_cast<const float4*>(g);
+          float4* p4 = reinterpret_cast<float4*>(p);
+          for (size_t d = lane; d < W / 4; d += kWarp) {
+            const float4 x = g4[d];
+            float4 y = p4[d];
+            y.x += -a.lr * x.x / avg; y.y += -a.lr * x.y / avg;
+            y.z += -a.lr * x.z / avg; y.w += -a.lr * x.w / avg;
+            p4[d] = y;
+          }
+        } else {
+          for (size_t d = lane; d < W; d += kWarp) p[d] += -a.lr * g[d] / avg;
+        }
+        __syncwarp();
+        if (lane == 0) a.v[row] = s_old + g2mean;
+      } else {
+        float* sv = a.v + row * W;
+        for (size_t d = lane; d < W; d += kWarp) {
+          const float gs = g[d] * g[d];
+          const float s_old = sv[d];
+          p[d] += -a.lr * g[d] / (sqrtf(s_old + gs) + a.eps);
+          sv[d] = s_old + gs;
+        }
+      }
+    } else {  // Adam
+      float* m = a.m + row * W;
+      if (a.squeeze) {
+        const float v_old = a.v[row];
+        const float v_new = v_old * a.beta2 + g2mean * a.omb2;
+        const float denom = sqrtf(v_new) / a.sqrt_bc2 + a.eps;
+        if (VEC) {
+          const float4* g4 = reinterpret_cast<const float4*>(g);
+          float4* p4 = reinterpret_cast<float4*>(p);
+          float4* m4 = reinterpret_cast<float4*>(m);
+          for (size_t d = lane; d < W / 4; d += kWarp) {
+            const float4 x = g4[d];
+            float4 y = p4[d], mm = m4[d];
+            adam_elem_rowwise(x.x, y.x, mm.x, denom, a);
+            adam_elem_rowwise(x.y, y.y, mm.y, denom, a);
+            adam_elem_rowwise(x.z, y.z, mm.z, denom, a);
+            adam_elem_rowwise(x.w, y.w, mm.w, denom, a);
+            p4[d] = y;
+            m4[d] = mm;
+          }
+        } else {
+          for (size_t d = lane; d < W; d += kWarp) {
+            float y = p[d], mm = m[d];
+            adam_elem_rowwise(g[d], y, mm, denom, a);
+            p[d] = y;
+            m[d] = mm;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) a.v[row] = v_old + (v_new - v_old);
+      } else {
+        float* v = a.v + row * W;
+        if (VEC) {
+          const float4* g4 = reinterpret_cast<const float4*>(g);
+          float4* p4 = reinterpret_cast<float4*>(p);
+          float4* m4 = reinterpret_cast<float4*>(m);
+          float4* v4 = reinterpret_cast<float4*>(v);
+          for (size_t d = lane; d < W / 4; d += kWarp) {
+            const float4 x = g4[d];
+            float4 y = p4[d], mm = m4[d], vv = v4[d];
+            adam_elem(x.x, y.x, mm.x, vv.x, a);
+            adam_elem(x.y, y.y, mm.y, vv.y, a);
+            adam_elem(x.z, y.z, mm.z, vv.z, a);
+            adam_elem(x.w, y.w, mm.w, vv.w, a);
+            p4[d] = y;
+            m4[d] = mm;
+            v4[d] = vv;
+          }
+        } else {
+          for (size_t d = lane; d < W; d += kWarp) {
+            float y = p[d], mm = m[d], vv = v[d];
+            adam_elem(g[d], y, mm, vv, a);
+            p[d] = y;
+            m[d] = mm;
+            v[d] = vv;
+          }
+        }
+      }
+    }
+  }
+}
+
+static int warp_grid(size_t items) {
+  const size_t blocks = (items + 7) / 8;
+  return (int)std::max<size_t>(1, std::min<size_t>(blocks, (size_t)kNumSM * 16));
+}
+
+static int thread_grid(size_t items) {
+  const size_t blocks = (items + 255) / 256;
+  return (int)std::max<size_t>(1, std::min<size_t>(blocks, (size_t)kNumSM * 16));
+}
+
+}  // namespace smore
+
+using namespace smore;
+
+extern "C" {
+
+int smore_gather_rows(const float* table, const int64_t* idx, float* out, size_t n, size_t width,
+                      void* stream) {
+  if (!table || !idx || !out) return fail(SMORE_ERR_NULL, "gather_rows: NULL pointer");
+  if (!width) return fail(SMORE_ERR_BAD_SHAPE, "gather_rows: width is 0");
+  if (n == 0) return SMORE_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool vec = (width % 4 == 0) && aligned16(table) && aligned16(out);
+  if (vec)
+    gather_rows_kernel<true><<<warp_grid(n), 256, 0, st>>>(table, idx, out, n, width);
+  else
+    gather_rows_kernel<false><<<warp_grid(n), 256, 0, st>>>(table, idx, out, n, width);
+  return check_launch("gather_rows_kernel");
+}
+
+size_t smore_unique_rows_workspace_bytes(size_t n_table_rows) {
+  return carve_unique_workspace(nullptr, n_table_rows).bytes;
+}
+
+int smore_unique_rows(const int64_t* idx, size_t n, size_t n_table_rows, int64_t* uniq, int32_t* inverse,
+                      int32_t* counts, int32_t* n_unique, void* workspace, size_t workspace_bytes,
+                      void* stream) {
+  if (!n_unique) return fail(SMORE_ERR_NULL, "unique_rows: n_unique is NULL");
+  if (n && (!idx || !uniq || !inverse || !counts)) return fail(SMORE_ERR_NULL, "unique_rows: NULL pointer");
+  if (n_table_rows == 0 || n_table_rows > ((size_t)1 << 36))
+    return fail(SMORE_ERR_BAD_SHAPE, "unique_rows: n_table_rows out of range");
+  if (n > ((size_t)1 << 31) - 1) return fail(SMORE_ERR_TOO_LARGE, "unique_rows: more than 2^31-1 ids");
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+    return fail(SMORE_ERR_WORKSPACE, "unique_rows: workspace missing or not 256-byte aligned");
+  const UniqueWorkspace w = carve_unique_workspace(workspace, n_table_rows);
+  if (workspace_bytes < w.bytes)
+    return fail(SMORE_ERR_WORKSPACE, "unique_rows: workspace has %zu bytes, %zu needed", workspace_bytes,
+                w.bytes);
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaMemsetAsync(n_unique, 0, 2 * sizeof(int32_t), st);
+  if (n == 0) return check_launch("unique_rows memset", 0);
+  cudaMemsetAsync(w.bitmap, 0, w.nwords * sizeof(uint32_t), st);
+  cudaMemsetAsync(counts, 0, n * sizeof(int32_t), st);
+  unique_mark_kernel<<<thread_grid(n), 256, 0, st>>>(idx, n, n_table_rows, w.bitmap, n_unique);
+  unique_blocksum_kernel<<<(unsigned)w.nblocks, kScanThreads, 0, st>>>(w.bitmap, w.nwords, w.blocksum);
+  unique_scan_blocks_kernel<<<1, 1024, 0, st>>>(w.blocksum, w.nblocks, n_unique);
+  unique_wordprefix_kernel<<<(unsigned)w.nblocks, kScanThreads, 0, st>>>(w.bitmap, w.nwords, w.blocksum,
+                                                                         w.wordprefix);
+  unique_assign_kernel<<<thread_grid(n), 256, 0, st>>>(idx, n, n_table_rows, w.bitmap, w.wordprefix, uniq,
+                                                        inverse, counts);
+  return check_launch("unique_rows kernels", 5);
+}
+
+int smore_zero_shared_rows(float* g_rows, const int32_t* slot_count, const int32_t* n_unique, size_t capacity,
+                           size_t width, void* stream) {
+  if (!g_rows || !slot_count || !n_unique) return fail(SMORE_ERR_NULL, "zero_shared_rows: NULL pointer");
+  if (capacity == 0) return SMORE_OK;
+  zero_shared_rows_kernel<<<warp_grid(capacity), 256, 0, (cudaStream_t)stream>>>(g_rows, slot_count, n_unique,
+                                                                                  width);
+  return check_launch("zero_shared_rows_kernel");
+}
+
+int smore_scatter_add_rows(const float* grad, const int32_t* slot, const int32_t* slot_count, float* g_rows,
+                           size_t n, size_t width, void* stream) {
+  if (n == 0) return SMORE_OK;
+  if (!grad || !slot || !slot_count || !g_rows) return fail(SMORE_ERR_NULL, "scatter_add_rows: NULL pointer");
+  if (!width) return fail(SMORE_ERR_BAD_SHAPE, "scatter_add_rows: width is 0");
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool vec = (width % 4 == 0) && aligned16(grad) && aligned16(g_rows);
+  if (vec)
+    scatter_add_rows_kernel<true><<<warp_grid(n), 256, 0, st>>>(grad, slot, slot_count, g_rows, n, width);
+  else
+    scatter_add_rows_kernel<false><<<warp_grid(n), 256, 0, st>>>(grad, slot, slot_count, g_rows, n, width);
+  return check_launch("scatter_add_rows_kernel");
+}
+
+int smore_sparse_update_rows(int opt_id, float* table, float* m, float* v, const int64_t* uniq,
+                             const float* g_rows, const int32_t* n_unique, size_t capacity, size_t width,
+                             double lr, double beta1, double beta2, double eps, int64_t step, int squeeze,
+                             void* stream) {
+  if (opt_id < SMORE_OPT_SGD || opt_id > SMORE_OPT_ADAGRAD)
+    return fail(SMORE_ERR_BAD_DIST, "unknown optimizer id %d", opt_id);
+  if (capacity == 0) return SMORE_OK;
+  if (!table || !uniq || !g_rows || !n_unique) return fail(SMORE_ERR_NULL, "sparse_update_rows: NULL pointer");
+  if (opt_id == SMORE_OPT_ADAM && (!m || !v)) return fail(SMORE_ERR_NULL, "adam needs m and v");
+  if (opt_id == SMORE_OPT_ADAGRAD && !v) return fail(SMORE_ERR_NULL, "adagrad needs v");
+  if (!width) return fail(SMORE_ERR_BAD_SHAPE, "sparse_update_rows: width is 0");
+  if (opt_id == SMORE_OPT_ADAM && step < 1) return fail(SMORE_ERR_BAD_SHAPE, "adam step must be >= 1");
+  UpdateArgs a;
+  a.table = table; a.m = m; a.v = v; a.uniq = uniq; a.g_rows = g_rows; a.n_unique = n_unique;
+  a.width = width;
+  // hyper-parameters arrive as doubles (Python floats in the reference) and are narrowed once
+  const double bc1 = 1.0 - std::pow(beta1, (double)step);
+  const double bc2 = 1.0 - std::pow(beta2, (double)step);
+  a.lr = (float)lr; a.beta1 = (float)beta1; a.beta2 = (float)beta2;
+  a.omb1 = (float)(1.0 - beta1); a.omb2 = (float)(1.0 - beta2); a.eps = (float)eps;
+  a.step_size = (float)(-lr / bc1); a.sqrt_bc2 = (float)std::sqrt(bc2);
+  a.squeeze = squeeze != 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool vec = (width % 4 == 0) && aligned16(table) && aligned16(g_rows) && (!m || aligned16(m)) &&
+                   (!v || squeeze || aligned16(v));
+  const int grid = warp_grid(capacity);
+#define LAUNCH(OPT)                                                                  \
+  if (vec) sparse_update_rows_kernel<OPT, true><<<grid, 256, 0, st>>>(a);            \
+  else sparse_update_rows_kernel<OPT, false><<<grid, 256, 0, st>>>(a)
+  if (opt_id == SMORE_OPT_SGD) { LAUNCH(SMORE_OPT_SGD); }
+  else if (opt_id == SMORE_OPT_ADAM) { LAUNCH(SMORE_OPT_ADAM); }
+  else { LAUNCH(SMORE_OPT_ADAGRAD); }
+#undef LAUNCH
+  return check_launch("sparse_update_rows_kernel");
+}
+
+}  // extern "C"

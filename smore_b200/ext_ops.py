@@ -1,0 +1,271 @@
+"""The custom distance ops, with the names, tensor contracts and autograd behaviour of
+smore/common/torchext/ext_ops.py:15-22 and the dist_func/*.py modules behind it.
+
+    l1_dist, l2_dist, box_dist_in, box_dist_out, rotate_dist, complex_sim, distmult_sim
+    (+ box_dist_both, which returns the two box distances from a single pass)
+
+Operand rule (e.g. box_dist.py:50-70): the entity operand is 3-D [be, ne, rows]; the query
+operands are 3-D [bc, nc, dim], or 4-D [B, U, 1, dim] with U union branches, in which case the
+op runs once per branch and the results are stacked to [B, U, num].  l2_dist takes the root
+outside the kernel, as l2_dist.py:59,62 does.
+
+The entity operand may also be a smore_b200.embedding.LazyRows handle (rows of the table named
+by index).  Then nothing is gathered: the kernels read the table rows in place and the
+backward pass adds the row gradients into the owning optimizer's per-step buffer.
+"""
+import torch
+
+from . import _lib
+from . import extlib_cuda as extlib
+from .embedding import LazyRows
+
+__all__ = ["l1_dist", "l2_dist", "box_dist_in", "box_dist_out", "box_dist_both", "rotate_dist", "complex_sim",
+           "distmult_sim"]
+
+
+def _out_shape(entity_shape, query_shape):
+    return max(entity_shape[0], query_shape[0]), max(entity_shape[1], query_shape[1])
+
+
+def _check_broadcast(entity_shape, query_shape):
+    for a, b in ((entity_shape[0], query_shape[0]), (entity_shape[1], query_shape[1])):
+        if a % b != 0 and b % a != 0:
+            raise ValueError("entity %s and query %s do not broadcast" % (tuple(entity_shape), tuple(query_shape)))
+
+
+class _DistFunc(torch.autograd.Function):
+    """One distance on materialised operands (the pattern of l1_dist.py:21-46 / box_dist.py:21-47)."""
+
+    @staticmethod
+    def forward(ctx, name, entity, first, second):
+        _check_broadcast(entity.shape, first.shape)
+        entity, first = entity.contiguous(), first.contiguous()
+        second = None if second is None else second.contiguous()
+        dst = torch.empty(_out_shape(entity.shape, first.shape), dtype=entity.dtype, device=entity.device)
+        extlib.dist_forward(name, entity, first, second, dst)
+        ctx.name = name
+        ctx.two = second is not None
+        if ctx.two:
+            ctx.save_for_backward(entity, first, second)
+        else:
+            ctx.save_for_backward(entity, first)
+        return dst
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        if ctx.two:
+            entity, first, second = ctx.saved_tensors
+        else:
+            entity, first = ctx.saved_tensors
+            second = None
+        grad_out = grad_out.contiguous()
+        # the kernels write every element, so the buffers need not be cleared first
+        g_entity = torch.empty_like(entity)
+        g_first = torch.empty_like(first)
+        g_second = torch.empty_like(second) if ctx.two else None
+        extlib.dist_backward(ctx.name, grad_out, entity, first, second, g_entity, g_first, g_second)
+        return None, g_entity, g_first, g_second
+
+
+class _BoxBothFunc(torch.autograd.Function):
+    """Both box distances of materialised operands in one pass over the entity rows."""
+
+    @staticmethod
+    def forward(ctx, entity, center, offset):
+        _check_broadcast(entity.shape, center.shape)
+        entity, center, offset = entity.contiguous(), center.contiguous(), offset.contiguous()
+        bsize, num = _out_shape(entity.shape, center.shape)
+        d_out = torch.empty(bsize, num, dtype=entity.dtype, device=entity.device)
+        d_in = torch.empty_like(d_out)
+        L = _lib.lib()
+        with torch.cuda.device(entity.device):
+            _lib.check(L.smore_box_forward(entity.data_ptr(), None, center.data_ptr(), offset.data_ptr(),
+                                           d_out.data_ptr(), d_in.data_ptr(), bsize, num, entity.shape[0],
+                                           entity.shape[1], center.shape[0], center.shape[1], center.shape[2],
+                                           torch.cuda.current_stream(entity.device).cuda_stream),
+                       "smore_box_forward")
+        ctx.save_for_backward(entity, center, offset)
+        return d_out, d_in
+
+    @staticmethod
+    def backward(ctx, g_out, g_in):
+        entity, center, offset = ctx.saved_tensors
+        g_out, g_in = g_out.contiguous(), g_in.contiguous()
+        g_entity, g_center, g_offset = torch.empty_like(entity), torch.empty_like(center), torch.empty_like(offset)
+        bsize, num = g_out.shape
+        L = _lib.lib()
+        with torch.cuda.device(entity.device):
+            _lib.check(L.smore_box_backward(g_out.data_ptr(), g_in.data_ptr(), entity.data_ptr(), None,
+                                            center.data_ptr(), offset.data_ptr(), g_entity.data_ptr(), None, None,
+                                            None, g_center.data_ptr(), g_offset.data_ptr(), bsize, num,
+                                            entity.shape[0], entity.shape[1], center.shape[0], center.shape[1],
+                                            center.shape[2],
+                                            torch.cuda.current_stream(entity.device).cuda_stream),
+                       "smore_box_backward")
+        return g_entity, g_center, g_offset
+
+
+def _check_rows_operands(name, rows, first, second):
+    table = rows.owner.table
+    if first.dim() != 3:
+        raise ValueError("%s: query operands must be 3-D" % name)
+    if not first.is_cuda or first.device != table.device or first.dtype != torch.float32:
+        raise TypeError("%s: query operands must be float32 on the table's device" % name)
+    if second is not None and second.shape != first.shape:
+        raise ValueError("%s: the two query operands must have the same shape" % name)
+    be, ne, width = rows.as_3d()
+    parts = 1 if name == "box_both" else _lib.ROW_PARTS[name]
+    if width != parts * first.shape[2]:
+        raise ValueError("%s: table rows must be %d x the query dim" % (name, parts))
+    _check_broadcast((be, ne), first.shape)
+    return be, ne
+
+
+class _RowsDistFunc(torch.autograd.Function):
+    """A distance whose entity operand is table rows named by index.  `dummy` is the owning
+    optimizer's one-element parameter: it makes autograd call backward even when no query
+    operand needs a gradient (the same device the reference uses, embed_optimizer.py:128,153)."""
+
+    @staticmethod
+    def forward(ctx, name, rows, dummy, first, second):
+        first = first.contiguous()
+        second = None if second is None else second.contiguous()
+        be, ne = _check_rows_operands(name, rows, first, second)
+        owner, lookup = rows.owner, rows.lookup
+        table = owner.table
+        bc, nc, dim = first.shape
+        bsize, num = max(be, bc), max(ne, nc)
+        L = _lib.lib()
+        st = torch.cuda.current_stream(table.device).cuda_stream
+        sizes = (bsize, num, be, ne, bc, nc, dim)
+        with torch.cuda.device(table.device), _lib.timed("rows_forward"):
+            if name == "box_both":
+                d0 = torch.empty(bsize, num, dtype=table.dtype, device=table.device)
+                d1 = torch.empty_like(d0)
+                _lib.check(L.smore_box_forward(table.data_ptr(), lookup.idx.data_ptr(), first.data_ptr(),
+                                               second.data_ptr(), d0.data_ptr(), d1.data_ptr(), *sizes, st),
+                           "smore_box_forward")
+                outs = (d0, d1)
+            else:
+                d0 = torch.empty(bsize, num, dtype=table.dtype, device=table.device)
+                _lib.check(L.smore_dist_forward_rows(_lib.DIST_IDS[name], table.data_ptr(), lookup.idx.data_ptr(),
+                                                     first.data_ptr(), None if second is None else second.data_ptr(),
+                                                     d0.data_ptr(), *sizes, st), "smore_dist_forward_rows")
+                outs = (d0,)
+        ctx.name, ctx.rows, ctx.sizes = name, rows, sizes
+        ctx.two = second is not None
+        if ctx.two:
+            ctx.save_for_backward(first, second)
+        else:
+            ctx.save_for_backward(first)
+        return outs if name == "box_both" else outs[0]
+
+    @staticmethod
+    def backward(ctx, *gouts):
+        if ctx.two:
+            first, second = ctx.saved_tensors
+        else:
+            (first,) = ctx.saved_tensors
+            second = None
+        owner, lookup = ctx.rows.owner, ctx.rows.lookup
+        table = owner.table
+        plan = owner.plan_for(lookup)
+        lookup.received = True
+        slot = plan.slot_of(lookup)
+        g_first = torch.empty_like(first)
+        g_second = torch.empty_like(second) if ctx.two else None
+        gouts = [g.contiguous() for g in gouts]
+        L = _lib.lib()
+        st = torch.cuda.current_stream(table.device).cuda_stream
+        with torch.cuda.device(table.device), _lib.timed("rows_backward"):
+            if ctx.name == "box_both":
+                _lib.check(L.smore_box_backward(gouts[0].data_ptr(), gouts[1].data_ptr(), table.data_ptr(),
+                                                lookup.idx.data_ptr(), first.data_ptr(), second.data_ptr(), None,
+                                                slot.data_ptr(), plan.counts.data_ptr(), plan.g_rows.data_ptr(),
+                                                g_first.data_ptr(), g_second.data_ptr(), *ctx.sizes, st),
+                           "smore_box_backward")
+            else:
+                _lib.check(L.smore_dist_backward_rows(_lib.DIST_IDS[ctx.name], gouts[0].data_ptr(), table.data_ptr(),
+                                                      lookup.idx.data_ptr(), first.data_ptr(),
+                                                      None if second is None else second.data_ptr(),
+                                                      slot.data_ptr(), plan.counts.data_ptr(), plan.g_rows.data_ptr(),
+                                                      g_first.data_ptr(),
+                                                      None if g_second is None else g_second.data_ptr(),
+                                                      *ctx.sizes, st), "smore_dist_backward_rows")
+        return None, None, None, g_first, g_second
+
+
+def _apply(name, entity, first, second):
+    if isinstance(entity, LazyRows):
+        return _RowsDistFunc.apply(name, entity, entity.owner.dummy_tensor, first, second)
+    if name == "box_both":
+        return _BoxBothFunc.apply(entity, first, second)
+    return _DistFunc.apply(name, entity, first, second)
+
+
+def _dist(name, entity, first, second=None):
+    """Front-end shared by all ops: 3-D operands, or a per-branch loop for 4-D query operands."""
+    if entity.dim() != first.dim():
+        if first.dim() != 4 or entity.dim() != 3:
+            raise ValueError("expected a 3-D entity operand with 3-D or 4-D query operands")
+        outs = []
+        for i in range(first.shape[1]):
+            f = first[:, i, :, :].contiguous()
+            s = None if second is None else second[:, i, :, :].contiguous()
+            outs.append(_apply(name, entity, f, s))
+        if name == "box_both":
+            return torch.stack([o[0] for o in outs], dim=1), torch.stack([o[1] for o in outs], dim=1)
+        return torch.stack(outs, dim=1)
+    if entity.dim() != 3:
+        raise ValueError("operands must be 3-D")
+    return _apply(name, entity, first, second)
+
+
+def l1_dist(entity_embed, center_embed):
+    return _dist("l1", entity_embed, center_embed)
+
+
+def l2_dist(entity_embed, center_embed):
+    return torch.sqrt(_dist("l2", entity_embed, center_embed))
+
+
+def rotate_dist(entity_embed, re_embed, im_embed):
+    return _dist("rotate", entity_embed, re_embed, im_embed)
+
+
+def complex_sim(entity_embed, re_embed, im_embed):
+    return _dist("complex", entity_embed, re_embed, im_embed)
+
+
+def distmult_sim(entity_embed, center_embed):
+    return _dist("distmult", entity_embed, center_embed)
+
+
+def box_dist_both(entity_embed, center_embed, offset_embed):
+    """(dist_out, dist_in) of the same operands from one pass over the entity rows."""
+    return _dist("box_both", entity_embed, center_embed, offset_embed)
+
+
+def _box_one(which, entity_embed, center_embed, offset_embed):
+    if not isinstance(entity_embed, LazyRows):
+        return _dist("box_" + which, entity_embed, center_embed, offset_embed)
+    # Query2box asks for "out" and then "in" of the same operands (box.py:160-161).  For table rows
+    # the first request computes both in one pass and parks the other result on the handle.
+    cache = entity_embed._box_cache
+    if cache is not None and cache[0] is center_embed and cache[1] is offset_embed and cache[2] != which:
+        entity_embed._box_cache = None
+        return cache[3]
+    d_out, d_in = _dist("box_both", entity_embed, center_embed, offset_embed)
+    if which == "out":
+        entity_embed._box_cache = (center_embed, offset_embed, "out", d_in)
+        return d_out
+    entity_embed._box_cache = (center_embed, offset_embed, "in", d_out)
+    return d_in
+
+
+def box_dist_out(entity_embed, center_embed, offset_embed):
+    return _box_one("out", entity_embed, center_embed, offset_embed)
+
+
+def box_dist_in(entity_embed, center_embed, offset_embed):
+    return _box_one("in", entity_embed, center_embed, offset_embed)

@@ -1,0 +1,201 @@
+"""Whole training steps of the hot path on the GPU (needs a B200).
+
+Small cases: the library path (table-resident rows, fused box distances, de-duplicated scatter,
+fused Adam) against an independent torch-native restatement of the reference's CPU-capable path
+(oracle/native_torch.py) driven through the same query model.
+Full-size cases: size-independent properties at the benchmark shapes."""
+import numpy as np
+import pytest
+import torch
+
+import bench
+from tests.util import RTOL, RTOL_ATOMIC, close
+
+pytestmark = pytest.mark.gpu
+
+
+class _NativeOps(object):
+    """The pure-torch twins of the ops (dist_func/*.py naive_*), accepting 4-D query operands."""
+
+    @staticmethod
+    def _delta(e, c):
+        return (e.unsqueeze(1) - c).abs()
+
+    def box_dist_out(self, e, c, o):
+        return torch.relu(self._delta(e, c) - o).sum(-1)
+
+    def box_dist_in(self, e, c, o):
+        return torch.min(self._delta(e, c), o).sum(-1)
+
+    def l1_dist(self, e, c):
+        return self._delta(e, c).sum(-1)
+
+    def rotate_dist(self, e, re, im):
+        e_re, e_im = torch.chunk(e.unsqueeze(1), 2, dim=-1)
+        return torch.stack([e_re - re, e_im - im], dim=0).norm(dim=0).sum(-1)
+
+
+class _NativeEmbeddingModule(object):
+    """Stand-in for smore_b200.embedding that follows the reference literally: gathered copies,
+    torch.unique, index_add_ and the ~15-kernel Adam of embed_optimizer.py:208-252."""
+
+    class SparseEmbedding(torch.nn.Module):
+        def __init__(self, num_rows, num_cols):
+            super().__init__()
+            self.num_rows = num_rows
+            self.embedding = torch.nn.Parameter(torch.zeros(num_rows, num_cols))
+            self.records = []
+
+        def forward(self, indices, name=None):
+            rows = self.embedding.data[indices.reshape(-1)].clone().requires_grad_()
+            self.records.append((indices.reshape(-1), rows))
+            return rows
+
+    class AdamEmbedOptimizer(object):
+        def __init__(self, args, emb, gpu_id, lazy_names=()):
+            self.emb, self.step, self.squeeze = emb, 0, bool(args.optim_mode[3])
+            t = emb.embedding.data
+            self.m = torch.zeros_like(t)
+            self.v = torch.zeros(t.shape[0], 1, device=t.device) if self.squeeze else torch.zeros_like(t)
+
+        def zero_grad(self):
+            self.emb.records = []
+
+        def apply_grad(self, lr):
+            from oracle import native_torch as nt
+            self.step += 1
+            recs = [(i, r.grad) for i, r in self.emb.records if r.grad is not None]
+            idx, inv, merged = nt.merge_grads([i for i, _ in recs], [g for _, g in recs])
+            nt.adam_rows(self.emb.embedding.data, self.m, self.v, idx, merged, lr, self.step, self.squeeze)
+
+
+def _pair(cfg, n_rows, lazy=True):
+    from smore_b200 import embedding, ext_ops
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(5)
+    a = bench.QueryModel(cfg, n_rows, dev, ext_ops, embedding, lazy=lazy)
+    torch.manual_seed(5)
+    b = bench.QueryModel(cfg, n_rows, dev, _NativeOps(), _NativeEmbeddingModule)
+    b.load_state_dict(a.state_dict())
+    a.train(), b.train()
+    return a, b
+
+
+SMALL = {
+    "box": dict(geo="box", relations=11, dim=48, B=6, K=40, shared=False, gamma=2.0, cen=0.02, adv=0.5, lr=1e-2,
+                squeeze=True, structures=list(bench.STRUCTURES)),
+    "box_full_v": dict(geo="box", relations=7, dim=400, B=4, K=70, shared=False, gamma=12.0, cen=0.02, adv=None,
+                       lr=1e-2, squeeze=False, structures=["1p", "2i", "2u"]),
+    "box_shared": dict(geo="box", relations=9, dim=36, B=8, K=24, shared=True, gamma=12.0, cen=0.02, adv=None,
+                       lr=1e-2, squeeze=False, structures=["1p", "2p", "3p", "2i"]),
+    "rotate": dict(geo="rotate", relations=5, dim=500, B=4, K=64, shared=False, gamma=24.0, cen=0.0, adv=1.0,
+                   lr=1e-2, squeeze=False, structures=["1p", "2p", "2i"]),
+    "vec": dict(geo="vec", relations=13, dim=64, B=16, K=128, shared=False, gamma=12.0, cen=0.0, adv=None, lr=1e-2,
+                squeeze=False, structures=["1p", "3i", "up"]),
+}
+
+
+@pytest.mark.parametrize("name", sorted(SMALL))
+@pytest.mark.parametrize("lazy", [True, False], ids=["table_rows", "gathered_rows"])
+def test_training_steps_match_native_path(name, lazy):
+    cfg = SMALL[name]
+    n_rows = 300           # far fewer rows than lookups: heavy duplication within a step
+    a, b = _pair(cfg, n_rows, lazy)
+    for step, s in enumerate(cfg["structures"]):
+        pos, neg, q = (t.cuda() for t in bench.make_batch(cfg, n_rows, s, seed=step))
+        la = bench.train_step(a, pos, neg, q, s)
+        lb = bench.train_step(b, pos, neg, q, s)
+        close(la.item(), lb.item(), RTOL, what="loss %s" % s)
+        ta, tb = a.entity_embedding.embedding.data, b.entity_embedding.embedding.data
+        # rows the step did not touch stay bit-identical; touched rows agree to tolerance
+        touched = torch.zeros(n_rows, dtype=torch.bool, device="cuda")
+        for t in (pos, neg.reshape(-1)):
+            touched[t] = True
+        for c, kind in enumerate(bench.structure_columns(bench.STRUCTURES[s])):
+            if kind == "e":
+                touched[q[:, c]] = True
+        assert torch.equal(ta[~touched], tb[~touched])
+        close(ta.cpu().numpy(), tb.cpu().numpy(), RTOL_ATOMIC, what="table after %s" % s)
+        close(a.embed_opt.state("state_sum_fo").cpu().numpy(), b.embed_opt.m.cpu().numpy(), RTOL_ATOMIC, what="m")
+        close(a.embed_opt.state("state_sum_sq").cpu().numpy(), b.embed_opt.v.cpu().numpy(), RTOL_ATOMIC, what="v")
+        for (n1, p1), (n2, p2) in zip(a.named_parameters(), b.named_parameters()):
+            if p1.requires_grad:
+                # dense Adam turns a gradient of rounding-noise size into a full-size update, so a
+                # handful of elements may differ by a step; the bulk must agree tightly
+                diff = (p1.detach() - p2.detach()).abs()
+                assert diff.mean().item() < 1e-5 and diff.max().item() < 2.5 * cfg["lr"] * (step + 1), n1
+
+
+def test_full_size_properties():
+    """Benchmark shapes (B=1024, K=1024, dim 400) on a 2M-row table: index sets are exact,
+    logits equal a torch-native evaluation, the gradient buffer is linear in the output gradient
+    and sums to the dense gradient's checksum, untouched rows are bit-identical after the update."""
+    from smore_b200 import _lib, embedding, ext_ops
+    L = _lib.lib()
+    dev = torch.device("cuda", 0)
+    N, D, B, K = 2000000, 400, 1024, 1024
+    g = torch.Generator(device="cuda").manual_seed(0)
+    emb = embedding.SparseEmbedding(0, D)
+    emb.num_rows = N
+    emb.embedding = torch.nn.Parameter((torch.rand(N, D, device=dev, generator=g) - 0.5) * 0.02, requires_grad=False)
+    emb.train()
+
+    class Args(object):
+        optim_mode = ("aggr", "adam", "gpu", True, 0)
+        share_optim_stats = False
+
+    opt = embedding.AdamEmbedOptimizer(Args(), emb, 0, lazy_names=("negative_entity",))
+    neg = torch.randint(0, N, (B, K), device=dev, generator=g)
+    center = ((torch.rand(B, 1, D, device=dev, generator=g) - 0.5) * 0.02).requires_grad_()
+    offset = (torch.rand(B, 1, D, device=dev, generator=g) * 0.01).requires_grad_()
+    table_before = emb.embedding.data.clone()
+
+    opt.zero_grad()
+    rows = emb(neg.view(-1), "negative_entity").view(B, K, -1)
+    d_out, d_in = ext_ops.box_dist_both(rows, center, offset)
+    # torch-native evaluation of the same distances, in slabs
+    for b0 in range(0, B, 128):
+        e = table_before[neg[b0:b0 + 128]]
+        delta = (e - center[b0:b0 + 128].detach()).abs()
+        o = offset[b0:b0 + 128].detach()
+        close(d_out[b0:b0 + 128].detach().cpu().numpy(), torch.relu(delta - o).sum(-1).cpu().numpy(), RTOL)
+        close(d_in[b0:b0 + 128].detach().cpu().numpy(), torch.min(delta, o).sum(-1).cpu().numpy(), RTOL)
+    w_out = torch.randn(B, K, device=dev, generator=g)
+    w_in = torch.randn(B, K, device=dev, generator=g)
+    ((d_out * w_out).sum() + (d_in * w_in).sum()).backward()
+    plan = opt._plans[0]
+    # index sets: exactly torch.unique's
+    t_u, t_i = torch.unique(neg.view(-1), return_inverse=True)
+    nu = int(plan.n_unique[0])
+    assert nu == t_u.numel() and torch.equal(plan.uniq[:nu], t_u) and torch.equal(plan.slot.long(), t_i)
+    g1 = plan.g_rows[:nu].clone()
+    # checksum of checksums against the dense gradient computed by autograd on gathered rows
+    e = table_before[neg[:64]].requires_grad_()
+    delta = (e - center[:64].detach()).abs()
+    ((torch.relu(delta - offset[:64].detach()).sum(-1) * w_out[:64]).sum()
+     + (torch.min(delta, offset[:64].detach()).sum(-1) * w_in[:64]).sum()).backward()
+    dense = torch.zeros(nu, D, device=dev)
+    dense.index_add_(0, t_i.view(B, K)[:64].reshape(-1), e.grad.view(-1, D))
+    only_first = torch.ones(nu, dtype=torch.bool, device=dev)
+    only_first[t_i.view(B, K)[64:].reshape(-1)] = False       # rows referenced by the first 64 queries only
+    close(g1[only_first].cpu().numpy(), dense[only_first].cpu().numpy(), RTOL_ATOMIC, what="g_rows slab")
+    # linearity: doubling the output gradients doubles every accumulated row gradient exactly
+    opt.zero_grad()
+    rows = emb(neg.view(-1), "negative_entity").view(B, K, -1)
+    d_out2, d_in2 = ext_ops.box_dist_both(rows, center, offset)
+    assert torch.equal(d_out2, d_out) and torch.equal(d_in2, d_in)        # idempotent forward
+    ((d_out2 * (2 * w_out)).sum() + (d_in2 * (2 * w_in)).sum()).backward()
+    plan2 = opt._plans[0]
+    singles = plan2.counts[:nu] == 1
+    assert torch.equal(plan2.g_rows[:nu][singles], 2 * g1[singles])
+    close(plan2.g_rows[:nu].cpu().numpy(), (2 * g1).cpu().numpy(), RTOL_ATOMIC)
+    opt.apply_grad(1e-3)
+    torch.cuda.synchronize()
+    after = emb.embedding.data
+    touched = torch.zeros(N, dtype=torch.bool, device=dev)
+    touched[t_u] = True
+    assert torch.equal(after[~touched], table_before[~touched])
+    moved = (after[t_u] != table_before[t_u]).any(dim=1)
+    assert moved.float().mean().item() > 0.999
+    # Adam's first step moves every touched element by lr * sign-like amounts bounded by lr / (1 - beta1) ...
+    assert (after[t_u] - table_before[t_u]).abs().max().item() <= 1e-3 * 10.0 + 1e-6
