@@ -77,6 +77,7 @@ class KernelTimer(object):
 
     def __init__(self):
         self.records = {}
+        self.notes = {}
 
     def range(self, name):
         return _TimedRange(self, name)
@@ -120,3 +121,10 @@ def set_timer(timer):
 
 def timed(name):
     return _NO_RANGE if _timer is None else _timer.range(name)
+
+
+def note(name, device_scalar):
+    """Keep a copy of a device-side scalar (e.g. the number of distinct rows of a step) for the
+    installed timer; no host synchronisation happens here."""
+    if _timer is not None:
+        _timer.notes.setdefault(name, []).append(device_scalar.clone())

@@ -278,92 +278,86 @@ __device__ __forceinline__ void add4(float4& a, const float4& b) {
   a.w += b.w;
 }
 
-template <class Term, int NCH, int R>
-__global__ void __launch_bounds__(kRowCtaThreads) row_backward_kernel(RowArgs a, RowGradArgs ga) {
-  extern __shared__ float4 red[];  // [kNQ][dim4]
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// Backward of the row-stream shape.  The gradient of a row element needs no reduction over the
+// embedding dim, so the CTA is laid out by columns: `tpr` consecutive threads (a multiple of 32)
+// own the 16-byte columns of a row and `groups` such thread groups take alternate rows of the
+// CTA's block.  A thread keeps only its column of the query and of the query gradient in
+// registers (a handful of registers: high occupancy), has U row loads in flight, and writes its
+// column of each row gradient.  Per-row scalars (row id, output gradients, destination slot) are
+// fetched 32 rows at a time by the lanes of each warp and handed out by shuffles.
+template <class Term, int U>
+__global__ void __launch_bounds__(kRowCtaThreads)
+    col_backward_kernel(RowArgs a, RowGradArgs ga, int tpr, int groups) {
+  extern __shared__ float4 red[];  // [groups][kNQ][dim4]
+  const int lane = threadIdx.x & 31;
+  const int grp = threadIdx.x / tpr, col = threadIdx.x - grp * tpr;
   const int b = blockIdx.x / a.chunks, c = blockIdx.x - b * a.chunks;
   const int dim4 = a.dim >> 2;
+  const bool active = grp < groups && col < dim4;
   const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  const size_t w4 = (size_t)dim4 * Term::kMul;
+  const float4* ent4 = reinterpret_cast<const float4*>(a.ent);
+  float4* gbase = reinterpret_cast<float4*>(ga.slot ? ga.g_rows : ga.g_ent);
 
-  float4 q0[NCH], q1[NCH], gq0[NCH], gq1[NCH];
-  {
-    const float4* p0 = reinterpret_cast<const float4*>(a.first + (size_t)b * a.dim);
-    const float4* p1 = reinterpret_cast<const float4*>(a.second + (size_t)b * a.dim);
-#pragma unroll
-    for (int j = 0; j < NCH; ++j) {
-      const int d4 = lane + 32 * j;
-      q0[j] = d4 < dim4 ? __ldg(p0 + d4) : z4;
-      q1[j] = (Term::kNQ == 2 && d4 < dim4) ? __ldg(p1 + d4) : z4;
-      gq0[j] = z4;
-      gq1[j] = z4;
-    }
+  float4 q0 = z4, q1 = z4, gq0 = z4, gq1 = z4;
+  if (active) {
+    q0 = __ldg(reinterpret_cast<const float4*>(a.first + (size_t)b * a.dim) + col);
+    if (Term::kNQ == 2) q1 = __ldg(reinterpret_cast<const float4*>(a.second + (size_t)b * a.dim) + col);
   }
 
   const int r_begin = c * a.rows_per_cta;
   const int r_end = min(a.K, r_begin + a.rows_per_cta);
-  const size_t w4 = (size_t)dim4 * Term::kMul;
-  const float4* ent4 = reinterpret_cast<const float4*>(a.ent);
-
-  for (int base = r_begin + warp * a.wrows; base < r_end; base += kRowCtaWarps * a.wrows) {
-    const int n = min(a.wrows, r_end - base);
-    const size_t pos = (size_t)b * a.K + base + lane;
-    long long myrow = 0;
-    long long mydst = -1;  // destination row of the gradient, < 0: skip
-    int mysingle = 1;
-    float g0 = 0.f, g1 = 0.f;
-    if (lane < n) {
-      myrow = a.idx ? (long long)a.idx[pos] : (long long)pos;
-      g0 = ga.gout0[pos];
-      if (Term::kNOut == 2) g1 = ga.gout1[pos];
-      if (ga.slot) {
-        const int32_t s = ga.slot[pos];
-        mydst = s;
-        mysingle = s >= 0 ? (ga.slot_count[s] == 1) : 1;
-      } else {
-        mydst = (long long)pos;
-      }
-    }
-    float* gbase = ga.slot ? ga.g_rows : ga.g_ent;
-    for (int t = 0; t < n; t += R) {
-      float4 e[R][Term::kMul][NCH];
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        const long long row = __shfl_sync(0xffffffffu, myrow, min(t + r, n - 1));
-        const float4* pe = ent4 + (size_t)row * w4;
-#pragma unroll
-        for (int j = 0; j < NCH; ++j) {
-          const int d4 = lane + 32 * j;
-          if (d4 < dim4) {
-            e[r][0][j] = ld_row4(pe + d4);
-            if (Term::kMul == 2) e[r][Term::kMul - 1][j] = ld_row4(pe + dim4 + d4);
-          }
+  if (grp < groups) {
+    // this group's rows: r_begin + grp + groups * t, t = 0, 1, ...
+    const int n_mine = (r_end - r_begin - grp + groups - 1) / groups;
+    for (int t0 = 0; t0 < n_mine; t0 += 32) {
+      const int n = min(32, n_mine - t0);
+      long long myrow = 0, mydst = -1;
+      int mysingle = 1;
+      float g0 = 0.f, g1 = 0.f;
+      if (lane < n) {
+        const size_t pos = (size_t)b * a.K + r_begin + grp + (size_t)groups * (t0 + lane);
+        myrow = a.idx ? (long long)a.idx[pos] : (long long)pos;
+        g0 = ga.gout0[pos];
+        if (Term::kNOut == 2) g1 = ga.gout1[pos];
+        if (ga.slot) {
+          const int32_t s = ga.slot[pos];
+          mydst = s;
+          mysingle = s >= 0 ? (ga.slot_count[s] == 1) : 1;
+        } else {
+          mydst = (long long)pos;
         }
       }
+      for (int t = 0; t < n; t += U) {
+        float4 e0[U], e1[U];
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        const int src = min(t + r, n - 1);
-        float g[Term::kNOut];
-        g[0] = __shfl_sync(0xffffffffu, g0, src);
-        if (Term::kNOut == 2) g[Term::kNOut - 1] = __shfl_sync(0xffffffffu, g1, src);
-        const long long dst = __shfl_sync(0xffffffffu, mydst, src);
-        const int single = __shfl_sync(0xffffffffu, mysingle, src);
-        if (t + r >= n) continue;  // warp-uniform
-        float4* gout_row = reinterpret_cast<float4*>(gbase) + (size_t)(dst < 0 ? 0 : dst) * w4;
+        for (int u = 0; u < U; ++u) {
+          const long long row = __shfl_sync(0xffffffffu, myrow, min(t + u, n - 1));
+          if (active) {
+            const float4* pe = ent4 + (size_t)row * w4 + col;
+            e0[u] = ld_row4(pe);
+            if (Term::kMul == 2) e1[u] = ld_row4(pe + dim4);
+          }
+        }
 #pragma unroll
-        for (int j = 0; j < NCH; ++j) {
-          const int d4 = lane + 32 * j;
-          if (d4 < dim4) {
-            float4 ge0 = z4, ge1 = z4;
-            bwd4<Term>(g, e[r][0][j], e[r][Term::kMul - 1][j], q0[j], q1[j], ge0, ge1, gq0[j], gq1[j]);
-            if (dst >= 0) {
-              if (single) {
-                gout_row[d4] = ge0;
-                if (Term::kMul == 2) gout_row[dim4 + d4] = ge1;
-              } else {
-                atomicAdd(gout_row + d4, ge0);
-                if (Term::kMul == 2) atomicAdd(gout_row + dim4 + d4, ge1);
-              }
+        for (int u = 0; u < U; ++u) {
+          const int src = min(t + u, n - 1);
+          float g[Term::kNOut];
+          g[0] = __shfl_sync(0xffffffffu, g0, src);
+          if (Term::kNOut == 2) g[Term::kNOut - 1] = __shfl_sync(0xffffffffu, g1, src);
+          const long long dst = __shfl_sync(0xffffffffu, mydst, src);
+          const int single = __shfl_sync(0xffffffffu, mysingle, src);
+          if (t + u >= n || !active) continue;
+          float4 ge0 = z4, ge1 = z4;
+          bwd4<Term>(g, e0[u], Term::kMul == 2 ? e1[u] : e0[u], q0, q1, ge0, ge1, gq0, gq1);
+          if (dst >= 0) {
+            float4* out = gbase + (size_t)dst * w4 + col;
+            if (single) {
+              out[0] = ge0;
+              if (Term::kMul == 2) out[dim4] = ge1;
+            } else {
+              atomicAdd(out, ge0);
+              if (Term::kMul == 2) atomicAdd(out + dim4, ge1);
             }
           }
         }
@@ -371,34 +365,25 @@ __global__ void __launch_bounds__(kRowCtaThreads) row_backward_kernel(RowArgs a,
     }
   }
 
-  // fold the 8 warps' query gradients in warp order (fixed order: deterministic per CTA)
-  for (int w = 0; w < kRowCtaWarps; ++w) {
-    if (warp == w) {
-#pragma unroll
-      for (int j = 0; j < NCH; ++j) {
-        const int d4 = lane + 32 * j;
-        if (d4 < dim4) {
-          if (w == 0) {
-            red[d4] = gq0[j];
-            if (Term::kNQ == 2) red[dim4 + d4] = gq1[j];
-          } else {
-            add4(red[d4], gq0[j]);
-            if (Term::kNQ == 2) add4(red[dim4 + d4], gq1[j]);
-          }
-        }
-      }
-    }
-    __syncthreads();
+  // fold the groups' query gradients in group order (fixed order: deterministic per CTA)
+  if (active) {
+    red[(size_t)grp * Term::kNQ * dim4 + col] = gq0;
+    if (Term::kNQ == 2) red[(size_t)grp * Term::kNQ * dim4 + dim4 + col] = gq1;
   }
-  float4* gf = reinterpret_cast<float4*>(ga.g_first + (size_t)b * a.dim);
-  float4* gs = reinterpret_cast<float4*>(ga.g_second + (size_t)b * a.dim);
-  for (int d4 = threadIdx.x; d4 < dim4; d4 += kRowCtaThreads) {
+  __syncthreads();
+  if (grp == 0 && active) {
+    for (int gi = 1; gi < groups; ++gi) {
+      add4(gq0, red[(size_t)gi * Term::kNQ * dim4 + col]);
+      if (Term::kNQ == 2) add4(gq1, red[(size_t)gi * Term::kNQ * dim4 + dim4 + col]);
+    }
+    float4* gf = reinterpret_cast<float4*>(ga.g_first + (size_t)b * a.dim) + col;
+    float4* gs = reinterpret_cast<float4*>(ga.g_second + (size_t)b * a.dim) + col;
     if (ga.query_atomic) {
-      atomicAdd(gf + d4, red[d4]);
-      if (Term::kNQ == 2) atomicAdd(gs + d4, red[dim4 + d4]);
+      atomicAdd(gf, gq0);
+      if (Term::kNQ == 2) atomicAdd(gs, gq1);
     } else {
-      gf[d4] = red[d4];
-      if (Term::kNQ == 2) gs[d4] = red[dim4 + d4];
+      *gf = gq0;
+      if (Term::kNQ == 2) *gs = gq1;
     }
   }
 }
@@ -468,7 +453,7 @@ static int launch_forward(const Shape& s, const float* ent, const int64_t* idx, 
   if (p.chunks > 0) {
     RowArgs a{ent, idx, first, second, (int)s.num, (int)s.dim, p.rows_per_cta, p.chunks, p.wrows};
     const unsigned grid = (unsigned)(s.bsize * p.chunks);
-    constexpr int R = Term::kMul == 2 ? 2 : 2;
+    constexpr int R = 2;  // rows in flight per warp at 4 chunks per lane
     switch (p.nch) {
       case 1: row_forward_kernel<Term, 1, 4><<<grid, kRowCtaThreads, 0, st>>>(a, dst0, dst1); break;
       case 2: row_forward_kernel<Term, 2, 4><<<grid, kRowCtaThreads, 0, st>>>(a, dst0, dst1); break;
@@ -503,14 +488,15 @@ static int launch_backward(const Shape& s, const float* gout0, const float* gout
       if (Term::kNQ == 2) cudaMemsetAsync(g_second, 0, s.bsize * s.dim * sizeof(float), st);
     }
     const unsigned grid = (unsigned)(s.bsize * p.chunks);
-    const size_t smem = (size_t)Term::kNQ * s.dim * sizeof(float);
-    switch (p.nch) {
-      case 1: row_backward_kernel<Term, 1, 4><<<grid, kRowCtaThreads, smem, st>>>(a, ga); break;
-      case 2: row_backward_kernel<Term, 2, 2><<<grid, kRowCtaThreads, smem, st>>>(a, ga); break;
-      case 4: row_backward_kernel<Term, 4, 2><<<grid, kRowCtaThreads, smem, st>>>(a, ga); break;
-      default: row_backward_kernel<Term, 8, 1><<<grid, kRowCtaThreads, smem, st>>>(a, ga); break;
-    }
-    return check_launch("row_backward_kernel");
+    const int dim4 = (int)(s.dim >> 2);
+    const int tpr = ((dim4 + 31) / 32) * 32;          // threads that own the columns of one row
+    const int groups = kRowCtaThreads / tpr;          // row groups per CTA (dim <= 1024 -> >= 1)
+    const size_t smem = (size_t)groups * Term::kNQ * s.dim * sizeof(float);
+    if (Term::kMul == 2)
+      col_backward_kernel<Term, 4><<<grid, kRowCtaThreads, smem, st>>>(a, ga, tpr, groups);
+    else
+      col_backward_kernel<Term, 8><<<grid, kRowCtaThreads, smem, st>>>(a, ga, tpr, groups);
+    return check_launch("col_backward_kernel");
   }
   CellArgs<float> a{ent, idx, first, second, s.bsize, s.num, s.be, s.ne, s.bc, s.nc, s.dim};
   cell_backward_ent_kernel<float, Term><<<grid_for(s.be * s.ne * s.dim, 256), 256, 0, st>>>(

@@ -282,6 +282,71 @@ __device__ __forceinline__ void adam_elem_rowwise(float g, float& p, float& m, f
   m = m + (m_new - m);
 }
 
+// Adam for rows of at most 32 * NCH 16-byte chunks: every load of a row (gradient, parameters,
+// first moment and, with a full second moment, that too) is issued before anything is computed,
+// so each warp keeps 3-4 x NCH 512-byte requests in flight; the gradient is read once even when
+// the row-wise mean of its square is needed first.
+template <int NCH, bool ROWWISE>
+__global__ void __launch_bounds__(256) adam_rows_reg_kernel(UpdateArgs a) {
+  const int lane = threadIdx.x & 31;
+  const size_t nu = (size_t)max(a.n_unique[0], 0);
+  const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+  const int w4 = (int)(a.width >> 2);
+  size_t u = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  long long row = u < nu ? a.uniq[u] : 0;
+  for (; u < nu; u += warps) {
+    const long long next_row = (u + warps < nu) ? a.uniq[u + warps] : 0;
+    const float4* g4 = reinterpret_cast<const float4*>(a.g_rows + u * a.width);
+    float4* p4 = reinterpret_cast<float4*>(a.table + (size_t)row * a.width);
+    float4* m4 = reinterpret_cast<float4*>(a.m + (size_t)row * a.width);
+    float4* v4 = ROWWISE ? nullptr : reinterpret_cast<float4*>(a.v + (size_t)row * a.width);
+    float4 g[NCH], p[NCH], m[NCH], v[NCH];
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int d = lane + 32 * j;
+      if (d < w4) {
+        g[j] = __ldcs(g4 + d);
+        p[j] = p4[d];
+        m[j] = m4[d];
+        if (!ROWWISE) v[j] = v4[d];
+      }
+    }
+    float denom = 0.f, v_old = 0.f, v_new = 0.f;
+    if (ROWWISE) {
+      v_old = a.v[row];
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < NCH; ++j)
+        if (lane + 32 * j < w4) s += g[j].x * g[j].x + g[j].y * g[j].y + g[j].z * g[j].z + g[j].w * g[j].w;
+      const float g2mean = warp_sum(s) / (float)a.width;
+      v_new = v_old * a.beta2 + g2mean * a.omb2;
+      denom = sqrtf(v_new) / a.sqrt_bc2 + a.eps;
+    }
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int d = lane + 32 * j;
+      if (d < w4) {
+        if (ROWWISE) {
+          adam_elem_rowwise(g[j].x, p[j].x, m[j].x, denom, a);
+          adam_elem_rowwise(g[j].y, p[j].y, m[j].y, denom, a);
+          adam_elem_rowwise(g[j].z, p[j].z, m[j].z, denom, a);
+          adam_elem_rowwise(g[j].w, p[j].w, m[j].w, denom, a);
+        } else {
+          adam_elem(g[j].x, p[j].x, m[j].x, v[j].x, a);
+          adam_elem(g[j].y, p[j].y, m[j].y, v[j].y, a);
+          adam_elem(g[j].z, p[j].z, m[j].z, v[j].z, a);
+          adam_elem(g[j].w, p[j].w, m[j].w, v[j].w, a);
+          v4[d] = v[j];
+        }
+        p4[d] = p[j];
+        m4[d] = m[j];
+      }
+    }
+    if (ROWWISE && lane == 0) a.v[row] = v_old + (v_new - v_old);
+    row = next_row;
+  }
+}
+
 template <int OPT, bool VEC>
 __global__ void __launch_bounds__(256) sparse_update_rows_kernel(UpdateArgs a) {
   const int lane = threadIdx.x & 31;
@@ -523,6 +588,19 @@ int smore_sparse_update_rows(int opt_id, float* table, float* m, float* v, const
   const bool vec = (width % 4 == 0) && aligned16(table) && aligned16(g_rows) && (!m || aligned16(m)) &&
                    (!v || squeeze || aligned16(v));
   const int grid = warp_grid(capacity);
+  const size_t w4 = width >> 2;
+  if (opt_id == SMORE_OPT_ADAM && vec && w4 <= 256) {
+    // rows of up to 1024 floats: the register-resident kernel
+#define ADAM_REG(NCH)                                                         \
+  if (a.squeeze) adam_rows_reg_kernel<NCH, true><<<grid, 256, 0, st>>>(a);    \
+  else adam_rows_reg_kernel<NCH, false><<<grid, 256, 0, st>>>(a)
+    if (w4 <= 32) { ADAM_REG(1); }
+    else if (w4 <= 64) { ADAM_REG(2); }
+    else if (w4 <= 128) { ADAM_REG(4); }
+    else { ADAM_REG(8); }
+#undef ADAM_REG
+    return check_launch("adam_rows_reg_kernel");
+  }
 #define LAUNCH(OPT)                                                                  \
   if (vec) sparse_update_rows_kernel<OPT, true><<<grid, 256, 0, st>>>(a);            \
   else sparse_update_rows_kernel<OPT, false><<<grid, 256, 0, st>>>(a)

@@ -489,6 +489,7 @@ class EmbeddingOptimizer(object):
             n_unique = torch.tensor([sel.numel(), 0], dtype=torch.int32, device=uniq.device)
             self._launch_update(uniq, g_rows, n_unique, sel.numel(), lr)
         else:
+            _lib.note("n_unique", plan.n_unique[0])
             self._launch_update(uniq, plan.g_rows, plan.n_unique, plan.n, lr)
         self._plans = []
         self._pending = []

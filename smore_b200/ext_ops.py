@@ -138,7 +138,7 @@ class _RowsDistFunc(torch.autograd.Function):
         L = _lib.lib()
         st = torch.cuda.current_stream(table.device).cuda_stream
         sizes = (bsize, num, be, ne, bc, nc, dim)
-        with torch.cuda.device(table.device), _lib.timed("rows_forward"):
+        with torch.cuda.device(table.device), _lib.timed("rows_forward" if num >= 16 else "rows_forward_few"):
             if name == "box_both":
                 d0 = torch.empty(bsize, num, dtype=table.dtype, device=table.device)
                 d1 = torch.empty_like(d0)
@@ -177,7 +177,7 @@ class _RowsDistFunc(torch.autograd.Function):
         gouts = [g.contiguous() for g in gouts]
         L = _lib.lib()
         st = torch.cuda.current_stream(table.device).cuda_stream
-        with torch.cuda.device(table.device), _lib.timed("rows_backward"):
+        with torch.cuda.device(table.device), _lib.timed("rows_backward" if ctx.sizes[1] >= 16 else "rows_backward_few"):
             if ctx.name == "box_both":
                 _lib.check(L.smore_box_backward(gouts[0].data_ptr(), gouts[1].data_ptr(), table.data_ptr(),
                                                 lookup.idx.data_ptr(), first.data_ptr(), second.data_ptr(), None,

@@ -25,7 +25,7 @@ class _NativeOps(object):
         return torch.relu(self._delta(e, c) - o).sum(-1)
 
     def box_dist_in(self, e, c, o):
-        return torch.min(self._delta(e, c), o).sum(-1)
+        return torch.norm(torch.min(self._delta(e, c), o), p=1, dim=-1)   # |.|: offsets may turn negative
 
     def l1_dist(self, e, c):
         return self._delta(e, c).sum(-1)
@@ -69,6 +69,20 @@ class _NativeEmbeddingModule(object):
             nt.adam_rows(self.emb.embedding.data, self.m, self.v, idx, merged, lr, self.step, self.squeeze)
 
 
+def close_mostly(got, want, rtol, outlier_atol, what, frac=2e-5):
+    """Element-wise agreement to `rtol` of the largest magnitude, except that a fraction `frac` of
+    the elements may be off by up to `outlier_atol`.  Needed after an Adam update: an element whose
+    gradient is of rounding-noise size, or sits exactly on a tie of the distance (where the torch
+    twins and the reference functors pick different sub-gradients), receives a full-size update of
+    either sign."""
+    got, want = got.float(), want.float()
+    diff = (got - want).abs()
+    tol = rtol * want.abs().max().clamp_min(1e-30) + rtol * want.abs()
+    bad = diff > tol
+    assert bad.float().mean().item() <= frac, "%s: %d of %d elements differ" % (what, int(bad.sum()), bad.numel())
+    assert diff.max().item() <= outlier_atol + tol.max().item(), "%s: max difference %g" % (what, diff.max().item())
+
+
 def _pair(cfg, n_rows, lazy=True):
     from smore_b200 import embedding, ext_ops
     dev = torch.device("cuda", 0)
@@ -102,28 +116,35 @@ def test_training_steps_match_native_path(name, lazy):
     n_rows = 300           # far fewer rows than lookups: heavy duplication within a step
     a, b = _pair(cfg, n_rows, lazy)
     for step, s in enumerate(cfg["structures"]):
+        # every step starts from identical states, so that one step's rounding differences are
+        # not amplified by the next (Adam turns noise-sized gradients into full-size updates)
+        b.load_state_dict(a.state_dict())
+        b.embed_opt.m.copy_(a.embed_opt.state("state_sum_fo"))
+        b.embed_opt.v.copy_(a.embed_opt.state("state_sum_sq"))
+        b.embed_opt.step = a.embed_opt.step
+        before = a.entity_embedding.embedding.data.clone()
         pos, neg, q = (t.cuda() for t in bench.make_batch(cfg, n_rows, s, seed=step))
         la = bench.train_step(a, pos, neg, q, s)
         lb = bench.train_step(b, pos, neg, q, s)
         close(la.item(), lb.item(), RTOL, what="loss %s" % s)
         ta, tb = a.entity_embedding.embedding.data, b.entity_embedding.embedding.data
-        # rows the step did not touch stay bit-identical; touched rows agree to tolerance
+        # rows the step did not look up stay bit-identical; the others agree to tolerance
         touched = torch.zeros(n_rows, dtype=torch.bool, device="cuda")
         for t in (pos, neg.reshape(-1)):
             touched[t] = True
         for c, kind in enumerate(bench.structure_columns(bench.STRUCTURES[s])):
             if kind == "e":
                 touched[q[:, c]] = True
-        assert torch.equal(ta[~touched], tb[~touched])
-        close(ta.cpu().numpy(), tb.cpu().numpy(), RTOL_ATOMIC, what="table after %s" % s)
-        close(a.embed_opt.state("state_sum_fo").cpu().numpy(), b.embed_opt.m.cpu().numpy(), RTOL_ATOMIC, what="m")
-        close(a.embed_opt.state("state_sum_sq").cpu().numpy(), b.embed_opt.v.cpu().numpy(), RTOL_ATOMIC, what="v")
+        assert torch.equal(ta[~touched], before[~touched]) and torch.equal(tb[~touched], before[~touched])
+        lr = cfg["lr"]
+        close_mostly(ta, tb, RTOL_ATOMIC, 4 * lr, "table after %s" % s)
+        close_mostly(a.embed_opt.state("state_sum_fo"), b.embed_opt.m, RTOL_ATOMIC, 1e-3, "m after %s" % s)
+        close_mostly(a.embed_opt.state("state_sum_sq"), b.embed_opt.v, RTOL_ATOMIC, 1e-3, "v after %s" % s)
         for (n1, p1), (n2, p2) in zip(a.named_parameters(), b.named_parameters()):
-            if p1.requires_grad:
-                # dense Adam turns a gradient of rounding-noise size into a full-size update, so a
-                # handful of elements may differ by a step; the bulk must agree tightly
-                diff = (p1.detach() - p2.detach()).abs()
-                assert diff.mean().item() < 1e-5 and diff.max().item() < 2.5 * cfg["lr"] * (step + 1), n1
+            if p1.requires_grad and p1.grad is not None:
+                # the dense parameters' gradients (what the op's query gradients feed); the values
+                # after torch's Adam are not compared: it turns noise-sized gradients into full steps
+                close(p1.grad.cpu().numpy(), p2.grad.cpu().numpy(), RTOL_ATOMIC, what="grad of " + n1)
 
 
 def test_full_size_properties():
@@ -178,7 +199,14 @@ def test_full_size_properties():
     dense.index_add_(0, t_i.view(B, K)[:64].reshape(-1), e.grad.view(-1, D))
     only_first = torch.ones(nu, dtype=torch.bool, device=dev)
     only_first[t_i.view(B, K)[64:].reshape(-1)] = False       # rows referenced by the first 64 queries only
-    close(g1[only_first].cpu().numpy(), dense[only_first].cpu().numpy(), RTOL_ATOMIC, what="g_rows slab")
+    # an exact tie |e - c| == o takes the reference functors' branch in the kernels and a split
+    # sub-gradient in torch's min/relu: leave rows holding such an element out of the comparison
+    tie_rows = torch.zeros(nu, dtype=torch.bool, device=dev)
+    ties = (delta == offset[:64].detach()) | (delta == 0)        # |e - c| == o, or e == c (sign(0) is -1 there)
+    tie_rows[t_i.view(B, K)[:64][ties.any(-1)]] = True
+    keep = only_first & ~tie_rows
+    assert keep.sum().item() > 30000 and tie_rows.sum().item() < 100
+    close(g1[keep].cpu().numpy(), dense[keep].cpu().numpy(), RTOL_ATOMIC, what="g_rows slab")
     # linearity: doubling the output gradients doubles every accumulated row gradient exactly
     opt.zero_grad()
     rows = emb(neg.view(-1), "negative_entity").view(B, K, -1)
