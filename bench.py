@@ -431,6 +431,8 @@ def run_gpu(args):
     rows_per_gpu = cfg["rows"] or (FREEBASE_ENTITIES + 7) // 8
     if args.rows:
         rows_per_gpu = args.rows
+    if args.structures:
+        cfg["structures"] = args.structures.split(",")
     if world > 1:
         raise NotImplementedError("multi-GPU sharded run is provided by smore_b200.sharded (not wired yet)")
     n_rows = rows_per_gpu
@@ -600,6 +602,7 @@ def main():
     ap.add_argument("--workload", default="freebase_q2b", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="smore_b200", choices=["smore_b200", "reference"])
     ap.add_argument("--rows", type=int, default=0, help="override entity-table rows per GPU")
+    ap.add_argument("--structures", default="", help="comma-separated subset of query structures (profiling runs)")
     ap.add_argument("--pool", type=int, default=18, help="distinct pre-generated batches to cycle through")
     ap.add_argument("--no-lazy", action="store_true", help="gather candidate rows instead of reading the table in place")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -110,6 +110,10 @@ SMORE_API int smore_dist_backward_f64(int dist_id, const double* gout, const dou
  * of positions of the whole step that map to s (see smore_unique_rows).  A row with
  * slot_count == 1 is stored, others are accumulated with atomics, so g_rows rows with
  * slot_count > 1 must be zero beforehand (smore_zero_shared_rows).
+ * slot_count == NULL means "accumulate everywhere": every row gradient is added atomically.
+ * Use it for the second and later backward calls over the same positions in one step (a union
+ * query scores the same candidate rows once per branch): the first call may store, the others
+ * must add.
  * g_first / g_second are fully written as in smore_dist_backward.
  * ------------------------------------------------------------------------------------------ */
 SMORE_API int smore_dist_forward_rows(int dist_id, const float* table, const int64_t* idx,
@@ -171,7 +175,7 @@ SMORE_API int smore_zero_shared_rows(float* g_rows, const int32_t* slot_count, c
 /* g_rows[slot[p], :] (+)= grad[p, :] for p < n — merge_grad_list's scatter-sum
  * (embed_optimizer.py:45-48) for gradients that autograd delivers as a dense [n, width]
  * block (anchor and positive-entity lookups).  Store when slot_count == 1, atomic add
- * otherwise; positions with slot < 0 are skipped. */
+ * otherwise (always, when slot_count is NULL); positions with slot < 0 are skipped. */
 SMORE_API int smore_scatter_add_rows(const float* grad, const int32_t* slot, const int32_t* slot_count,
                            float* g_rows, size_t n, size_t width, void* stream);
 

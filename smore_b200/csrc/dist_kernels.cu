@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(256)
       const int32_t s = slot[pos];
       if (s < 0) continue;
       T* out = g_rows + (size_t)s * a.dim * Term::kMul;
-      if (slot_count[s] == 1) {
+      if (slot_count != nullptr && slot_count[s] == 1) {
         out[d] = ge0;
         if (Term::kMul == 2) out[d + a.dim] = ge1;
       } else {
@@ -323,7 +323,7 @@ __global__ void __launch_bounds__(kRowCtaThreads)
         if (ga.slot) {
           const int32_t s = ga.slot[pos];
           mydst = s;
-          mysingle = s >= 0 ? (ga.slot_count[s] == 1) : 1;
+          mysingle = (s >= 0 && ga.slot_count != nullptr) ? (ga.slot_count[s] == 1) : 0;
         } else {
           mydst = (long long)pos;
         }
@@ -565,7 +565,7 @@ static int backward_common(int id, const float* gout, const float* ent, const in
   if (id < 0 || id >= SMORE_DIST_COUNT) return fail(SMORE_ERR_BAD_DIST, "unknown distance id %d", id);
   if (!gout || !ent || !first || !g_first || (needs_second(id) && (!second || !g_second)))
     return fail(SMORE_ERR_NULL, "backward: required pointer is NULL");
-  if (slot ? (!slot_count || !g_rows) : !g_ent)
+  if (slot ? !g_rows : !g_ent)
     return fail(SMORE_ERR_NULL, "backward: entity gradient destination is NULL");
   if (int rc = validate_shape(s)) return rc;
   cudaStream_t st = (cudaStream_t)stream;
@@ -628,8 +628,8 @@ int smore_box_backward(const float* gout_out, const float* gout_in, const float*
                        void* stream) {
   if (!gout_out || !gout_in || !ent || !center || !offset || !g_center || !g_offset)
     return fail(SMORE_ERR_NULL, "box_backward: required pointer is NULL");
-  if (idx ? (!slot || !slot_count || !g_rows || g_ent) : (!g_ent || slot || g_rows))
-    return fail(SMORE_ERR_NULL, "box_backward: pass g_ent (materialised) or slot/slot_count/g_rows (indexed)");
+  if (idx ? (!slot || !g_rows || g_ent) : (!g_ent || slot || g_rows))
+    return fail(SMORE_ERR_NULL, "box_backward: pass g_ent (materialised) or slot/g_rows (indexed)");
   const Shape s{bsize, num, be, ne, bc, nc, dim};
   if (int rc = validate_shape(s)) return rc;
   return launch_backward<TermBoxBoth>(s, gout_out, gout_in, ent, idx, center, offset, g_ent, slot, slot_count,

@@ -232,7 +232,7 @@ __global__ void __launch_bounds__(256)
   for (size_t p = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); p < n; p += warps) {
     const int32_t s = slot[p];
     if (s < 0) continue;
-    const bool single = slot_count[s] == 1;
+    const bool single = slot_count != nullptr && slot_count[s] == 1;
     if (VEC) {
       const float4* src = reinterpret_cast<const float4*>(grad + p * width);
       float4* dst = reinterpret_cast<float4*>(g_rows + (size_t)s * width);
@@ -551,7 +551,7 @@ int smore_zero_shared_rows(float* g_rows, const int32_t* slot_count, const int32
 int smore_scatter_add_rows(const float* grad, const int32_t* slot, const int32_t* slot_count, float* g_rows,
                            size_t n, size_t width, void* stream) {
   if (n == 0) return SMORE_OK;
-  if (!grad || !slot || !slot_count || !g_rows) return fail(SMORE_ERR_NULL, "scatter_add_rows: NULL pointer");
+  if (!grad || !slot || !g_rows) return fail(SMORE_ERR_NULL, "scatter_add_rows: NULL pointer");
   if (!width) return fail(SMORE_ERR_BAD_SHAPE, "scatter_add_rows: width is 0");
   cudaStream_t st = (cudaStream_t)stream;
   const bool vec = (width % 4 == 0) && aligned16(grad) && aligned16(g_rows);

@@ -410,11 +410,13 @@ class EmbeddingOptimizer(object):
     def accumulate_grad(self, lookup, grad_submat, fwd_idx=None):
         """Add a dense [n, width] gradient block of one lookup (embed_optimizer.py:146-148)."""
         plan = self.plan_for(lookup)
+        # a second producer for the same positions must add to what the first one stored
+        counts_ptr = None if lookup.received else plan.counts.data_ptr()
         lookup.received = True
         self.has_grad_list.append(lookup.order)
         with torch.cuda.device(self.table.device):
             _lib.check(_lib.lib().smore_scatter_add_rows(grad_submat.data_ptr(), plan.slot_of(lookup).data_ptr(),
-                                                         plan.counts.data_ptr(), plan.g_rows.data_ptr(), lookup.n,
+                                                         counts_ptr, plan.g_rows.data_ptr(), lookup.n,
                                                          self.table.shape[1], _stream_ptr(self.table.device)),
                        "smore_scatter_add_rows")
 

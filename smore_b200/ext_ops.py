@@ -170,6 +170,9 @@ class _RowsDistFunc(torch.autograd.Function):
         owner, lookup = ctx.rows.owner, ctx.rows.lookup
         table = owner.table
         plan = owner.plan_for(lookup)
+        # the first gradient producer of a lookup may store rows that nothing else touches; any
+        # later one over the same positions (another union branch) has to add to what is there
+        counts_ptr = None if lookup.received else plan.counts.data_ptr()
         lookup.received = True
         slot = plan.slot_of(lookup)
         g_first = torch.empty_like(first)
@@ -181,14 +184,14 @@ class _RowsDistFunc(torch.autograd.Function):
             if ctx.name == "box_both":
                 _lib.check(L.smore_box_backward(gouts[0].data_ptr(), gouts[1].data_ptr(), table.data_ptr(),
                                                 lookup.idx.data_ptr(), first.data_ptr(), second.data_ptr(), None,
-                                                slot.data_ptr(), plan.counts.data_ptr(), plan.g_rows.data_ptr(),
+                                                slot.data_ptr(), counts_ptr, plan.g_rows.data_ptr(),
                                                 g_first.data_ptr(), g_second.data_ptr(), *ctx.sizes, st),
                            "smore_box_backward")
             else:
                 _lib.check(L.smore_dist_backward_rows(_lib.DIST_IDS[ctx.name], gouts[0].data_ptr(), table.data_ptr(),
                                                       lookup.idx.data_ptr(), first.data_ptr(),
                                                       None if second is None else second.data_ptr(),
-                                                      slot.data_ptr(), plan.counts.data_ptr(), plan.g_rows.data_ptr(),
+                                                      slot.data_ptr(), counts_ptr, plan.g_rows.data_ptr(),
                                                       g_first.data_ptr(),
                                                       None if g_second is None else g_second.data_ptr(),
                                                       *ctx.sizes, st), "smore_dist_backward_rows")
