@@ -167,6 +167,28 @@ SMORE_API int smore_unique_rows(const int64_t* idx, size_t n, size_t n_table_row
                       int32_t* inverse, int32_t* counts, int32_t* n_unique, void* workspace,
                       size_t workspace_bytes, void* stream);
 
+/* smore_unique_rows for callers that cannot provide scratch memory.  (No counterpart in the
+ * reference: it exists for hosts that cannot allocate when they call — a server whose memory
+ * manager reserved the whole GPU at start-up, so that a later cudaMalloc fails, or a steady-state
+ * training loop that must avoid cudaMalloc because it synchronises the device.)
+ * Same arguments and results as smore_unique_rows minus the workspace: the scratch is a fixed
+ * array inside the library, about 4 MiB per GPU that loads the library, held until the process
+ * exits.  Limits and rules:
+ *   - n_table_rows <= SMORE_UNIQUE_STATIC_MAX_ROWS, otherwise SMORE_ERR_TOO_LARGE (use
+ *     smore_unique_rows with your own workspace for larger tables);
+ *   - neither this call nor anything it uses calls cudaMalloc / cudaFree;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress,
+ *     with the calling thread's current device); make that first call outside any stream
+ *     capture;
+ *   - all calls on a device share the one array, which still holds the previous call's bitmap:
+ *     the entry point clears what has to start at zero, but two calls whose kernels overlap on
+ *     the GPU (different streams, no ordering between them) race on it and give wrong results.
+ *     Order such calls, or use smore_unique_rows with separate workspaces. */
+#define SMORE_UNIQUE_STATIC_MAX_ROWS ((size_t)1 << 24)
+SMORE_API int smore_unique_rows_static(const int64_t* idx, size_t n, size_t n_table_rows, int64_t* uniq,
+                                       int32_t* inverse, int32_t* counts, int32_t* n_unique,
+                                       void* stream);
+
 /* Zero the rows of g_rows[capacity, width] whose slot_count > 1 (see smore_dist_backward_rows).
  * n_unique is the device counter written by smore_unique_rows. */
 SMORE_API int smore_zero_shared_rows(float* g_rows, const int32_t* slot_count, const int32_t* n_unique,

@@ -35,6 +35,7 @@ SIGNATURES = {
     "smore_gather_rows": (_int, [_p, _p, _p, _sz, _sz, _p]),
     "smore_unique_rows_workspace_bytes": (_sz, [_sz]),
     "smore_unique_rows": (_int, [_p, _sz, _sz, _p, _p, _p, _p, _p, _sz, _p]),
+    "smore_unique_rows_static": (_int, [_p, _sz, _sz, _p, _p, _p, _p, _p]),
     "smore_zero_shared_rows": (_int, [_p, _p, _p, _sz, _sz, _p]),
     "smore_scatter_add_rows": (_int, [_p, _p, _p, _p, _sz, _sz, _p]),
     "smore_sparse_update_rows": (_int, [_int, _p, _p, _p, _p, _p, _p, _sz, _sz, _dbl, _dbl, _dbl, _dbl,

@@ -11,6 +11,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -612,3 +613,81 @@ int smore_sparse_update_rows(int opt_id, float* table, float* m, float* v, const
 }
 
 }  // extern "C"
+
+// ----------------------------------------------------------------------------------------
+// smore_unique_rows_static: the same de-duplication with its scratch inside the library
+// ----------------------------------------------------------------------------------------
+//
+// Some hosts cannot hand this library a scratch buffer because they cannot allocate one at the
+// moment of the call: an embedding server whose memory manager claimed the whole GPU at start-up
+// (a later cudaMalloc simply fails), or a training loop that must not call cudaMalloc in steady
+// state because the call synchronises the device and stalls every stream.  For them the scratch
+// lives in this file as a fixed device array.  Every GPU that loads the library carries the
+// array (about 4 MiB) until the process exits, which is why its size is capped.
+
+namespace smore {
+
+// presence bitmap + per-word prefix for 2^24 ids, plus the per-block sums
+constexpr size_t kStaticUniqueMaxRows = SMORE_UNIQUE_STATIC_MAX_ROWS;
+constexpr size_t kStaticUniqueWords = kStaticUniqueMaxRows / 32;
+constexpr size_t kStaticUniqueBytes =
+    2 * kStaticUniqueWords * sizeof(uint32_t) + ((kStaticUniqueWords / kWordsPerBlock) * sizeof(uint32_t) + 255) / 256 * 256;
+
+static __device__ __align__(256) unsigned char g_unique_scratch[kStaticUniqueBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_unique_scratch_addr[kMaxDevices] = {nullptr};
+static std::mutex g_unique_scratch_mutex;
+
+// Device address of g_unique_scratch on the current device.  In host code the array's name is
+// only a handle for the runtime, not a pointer a kernel could use: the address has to be asked
+// for, once per device, while that device is current.
+static int static_unique_scratch(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(SMORE_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(SMORE_ERR_TOO_LARGE, "device ordinal %d not supported", dev);
+  std::lock_guard<std::mutex> lock(g_unique_scratch_mutex);
+  if (g_unique_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_unique_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(SMORE_ERR_CUDA, "cudaGetSymbolAddress(unique scratch): %s", cudaGetErrorString(e));
+    g_unique_scratch_addr[dev] = p;
+  }
+  *out = g_unique_scratch_addr[dev];
+  return SMORE_OK;
+}
+
+}  // namespace smore
+
+extern "C" int smore_unique_rows_static(const int64_t* idx, size_t n, size_t n_table_rows, int64_t* uniq,
+                                        int32_t* inverse, int32_t* counts, int32_t* n_unique, void* stream) {
+  if (!n_unique) return fail(SMORE_ERR_NULL, "unique_rows_static: n_unique is NULL");
+  if (n && (!idx || !uniq || !inverse || !counts)) return fail(SMORE_ERR_NULL, "unique_rows_static: NULL pointer");
+  if (n_table_rows == 0) return fail(SMORE_ERR_BAD_SHAPE, "unique_rows_static: n_table_rows is 0");
+  if (n_table_rows > kStaticUniqueMaxRows)
+    return fail(SMORE_ERR_TOO_LARGE,
+                "unique_rows_static: table has %zu rows, the built-in scratch covers at most %zu; use "
+                "smore_unique_rows with a caller-provided workspace",
+                n_table_rows, (size_t)kStaticUniqueMaxRows);
+  if (n > ((size_t)1 << 31) - 1) return fail(SMORE_ERR_TOO_LARGE, "unique_rows_static: more than 2^31-1 ids");
+  void* scratch = nullptr;
+  if (int rc = static_unique_scratch(&scratch)) return rc;
+  const UniqueWorkspace w = carve_unique_workspace(scratch, n_table_rows);
+  if (w.bytes > kStaticUniqueBytes) return fail(SMORE_ERR_WORKSPACE, "unique_rows_static: scratch layout overflow");
+  cudaStream_t st = (cudaStream_t)stream;
+  // the array still holds the previous call's bitmap: everything that must start at zero is cleared here
+  cudaMemsetAsync(n_unique, 0, 2 * sizeof(int32_t), st);
+  if (n == 0) return check_launch("unique_rows_static memset", 0);
+  cudaMemsetAsync(w.bitmap, 0, w.nwords * sizeof(uint32_t), st);
+  cudaMemsetAsync(counts, 0, n * sizeof(int32_t), st);
+  unique_mark_kernel<<<thread_grid(n), 256, 0, st>>>(idx, n, n_table_rows, w.bitmap, n_unique);
+  unique_blocksum_kernel<<<(unsigned)w.nblocks, kScanThreads, 0, st>>>(w.bitmap, w.nwords, w.blocksum);
+  unique_scan_blocks_kernel<<<1, 1024, 0, st>>>(w.blocksum, w.nblocks, n_unique);
+  unique_wordprefix_kernel<<<(unsigned)w.nblocks, kScanThreads, 0, st>>>(w.bitmap, w.nwords, w.blocksum,
+                                                                         w.wordprefix);
+  unique_assign_kernel<<<thread_grid(n), 256, 0, st>>>(idx, n, n_table_rows, w.bitmap, w.wordprefix, uniq,
+                                                        inverse, counts);
+  return check_launch("unique_rows_static kernels", 5);
+}
