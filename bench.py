@@ -163,19 +163,22 @@ class QueryModel(nn.Module):
     """Entity table (sparse, updated by the library's optimizer) + dense relation parameters and
     intersection nets; embeds one batch of same-structure queries and scores candidates."""
 
-    def __init__(self, cfg, n_rows, device, ops, embedding_mod, lazy=True):
+    def __init__(self, cfg, n_rows, device, ops, embedding_mod, lazy=True, shard=None, barrier=None, world=1):
         super().__init__()
         self.cfg, self.geo, self.dim = cfg, cfg["geo"], cfg["dim"]
         self.gamma, self.cen = cfg["gamma"], cfg.get("cen", 0.0)
         self.ops = ops
+        self.world = world
         width = self.dim * (2 if self.geo == "rotate" else 1)
         self.embedding_range = (self.gamma + 2.0) / self.dim
         r = self.embedding_range
         self.entity_embedding = embedding_mod.SparseEmbedding(0, width)
-        table = torch.empty(n_rows, width, device=device)
-        table.uniform_(-r, r)
         self.entity_embedding.num_rows = n_rows
-        self.entity_embedding.embedding = nn.Parameter(table, requires_grad=False)
+        lazy_names = ("negative_entity", "positive_entity") if lazy else ()
+        if shard is None:
+            table = torch.empty(n_rows, width, device=device)
+            table.uniform_(-r, r)
+            self.entity_embedding.embedding = nn.Parameter(table, requires_grad=False)
         R = cfg["relations"]
         self.relation_embedding = nn.Parameter(torch.empty(R, self.dim, device=device).uniform_(-r, r))
         if self.geo == "box":
@@ -187,9 +190,14 @@ class QueryModel(nn.Module):
             optim_mode = ("aggr", "adam", "gpu", bool(cfg["squeeze"]), 0)
             share_optim_stats = False
 
-        lazy_names = ("negative_entity", "positive_entity") if lazy else ()
-        self.embed_opt = embedding_mod.AdamEmbedOptimizer(_Args(), self.entity_embedding, device.index,
-                                                          lazy_names=lazy_names)
+        if shard is None:
+            self.embed_opt = embedding_mod.AdamEmbedOptimizer(_Args(), self.entity_embedding, device.index,
+                                                              lazy_names=lazy_names)
+        else:
+            # the table is a row shard per GPU: lookups and the update go through the sharded optimizer
+            from smore_b200 import sharded
+            self.embed_opt = sharded.ShardedAdamOptimizer(shard, lazy_names=lazy_names, barrier=barrier)
+            self.entity_embedding.fwd_delegate = self.embed_opt.forward
         dense = [p for n, p in self.named_parameters() if p.requires_grad and "dummy" not in n]
         self.dense_opt = torch.optim.Adam(dense, lr=cfg["lr"], fused=True)
 
@@ -280,14 +288,19 @@ def sampling_loss(pos_logit, neg_logit, adv, world_size=1):
     return (-pos_score.mean() - neg_score.mean()) / 2 / world_size
 
 
-def train_step(model, pos, neg, queries, structure):
-    """train_process.py:172-227 on device-resident index tensors."""
+def train_step(model, pos, neg, queries, structure, reduce_dense=None):
+    """train_process.py:172-227 on device-resident index tensors.  `reduce_dense(tensor)` sums a
+    dense parameter's gradient over the ranks (train_process.py:221-225) when there are several."""
     model.dense_opt.zero_grad(set_to_none=True)
     model.embed_opt.zero_grad()
     pos_logit, neg_logit = model(pos, neg, queries, structure)
-    loss = sampling_loss(pos_logit, neg_logit, model.cfg["adv"])
+    loss = sampling_loss(pos_logit, neg_logit, model.cfg["adv"], model.world)
     loss.backward()
     model.embed_opt.apply_grad(model.cfg["lr"])
+    if reduce_dense is not None:
+        for p in model.parameters():
+            if p.requires_grad and p.grad is not None:
+                reduce_dense(p.grad)
     model.dense_opt.step()
     return loss
 
@@ -404,7 +417,10 @@ def algorithmic_bytes(cfg, n_unique_mean):
     bwd = pairs * (8 * W + 8 + 4 + 4 + 4 * nout) + 2 * B * D * 4 * nq
     v_bytes = 8 if cfg["squeeze"] else 8 * W
     upd = n_unique_mean * (4 * W + 8 * W + 8 * W + v_bytes + 8)
-    return {"rows_forward": fwd, "rows_backward": bwd, "sparse_update_rows": upd}
+    # sharded run: the owner-side kernel moves the same bytes as the update (the gradient read is a
+    # peer read); the fetch copies every distinct row once (read + write)
+    return {"rows_forward": fwd, "rows_backward": bwd, "sparse_update_rows": upd, "shard_reduce_update": upd,
+            "fetch_rows": n_unique_mean * 8 * W}
 
 
 def load_peaks():
@@ -433,12 +449,25 @@ def run_gpu(args):
         rows_per_gpu = args.rows
     if args.structures:
         cfg["structures"] = args.structures.split(",")
-    if world > 1:
-        raise NotImplementedError("multi-GPU sharded run is provided by smore_b200.sharded (not wired yet)")
-    n_rows = rows_per_gpu
+    n_rows = rows_per_gpu * world     # weak scaling: the table grows with the number of GPUs
 
-    torch.manual_seed(1234 + rank)
-    model = QueryModel(cfg, n_rows, device, ext_ops, embedding, lazy=not args.no_lazy)
+    torch.manual_seed(1234)           # dense parameters start identical on every rank
+    reduce_dense = None
+    if world > 1:
+        # table + Adam state row-sharded over the ranks; rows and row gradients move over NVLink
+        from smore_b200 import sharded
+        B, K = cfg["B"], cfg["K"]
+        width = cfg["dim"] * (2 if cfg["geo"] == "rotate" else 1)
+        caps = ((K if cfg["shared"] else B * K) + 2 * B, B, B)
+        shard = sharded.ShardGroup.from_process_group(n_rows, width, caps, squeeze=cfg["squeeze"], device=device)
+        r = (cfg["gamma"] + 2.0) / cfg["dim"]
+        shard.init_uniform(-r, r, seed=1234)
+        model = QueryModel(cfg, n_rows, device, ext_ops, embedding, lazy=True, shard=shard, world=world)
+
+        def reduce_dense(t):
+            dist.all_reduce(t)
+    else:
+        model = QueryModel(cfg, n_rows, device, ext_ops, embedding, lazy=not args.no_lazy)
     model.train()
     structures = cfg["structures"]
     pool = max(len(structures), args.pool)
@@ -459,14 +488,14 @@ def run_gpu(args):
     def run_resident(k0, k):
         for i in range(k0, k0 + k):
             s, p, n, q = dev_batches[i % pool]
-            train_step(model, p, n, q, s)
+            train_step(model, p, n, q, s, reduce_dense)
 
     def run_e2e(k0, k):
         last = 0.0
         for i in range(k0, k0 + k):
             s, p, n, q = host_batches[i % pool]
             p, n, q = p.to(device, non_blocking=True), n.to(device, non_blocking=True), q.to(device, non_blocking=True)
-            last = train_step(model, p, n, q, s).item()   # device -> host read of the step's loss
+            last = train_step(model, p, n, q, s, reduce_dense).item()   # device -> host read of the step's loss
         return last
 
     L = _lib.lib()
@@ -511,7 +540,7 @@ def run_gpu(args):
         return
 
     peak, peak_kind = load_peaks()
-    nus = [int(t.item()) for t in timer.notes.get("n_unique", [])]
+    nus = [int(t.item()) for t in timer.notes.get("n_unique", []) + timer.notes.get("n_unique_owner", [])]
     n_unique_mean = sum(nus) / len(nus) if nus else cfg["B"] * cfg["K"]
     alg = algorithmic_bytes(cfg, n_unique_mean=n_unique_mean)
     kernels = {}
@@ -552,7 +581,9 @@ def run_gpu(args):
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "geo": cfg["geo"], "queries_per_gpu": cfg["B"], "negatives": cfg["K"],
                    "shared_negatives": cfg["shared"], "dim": cfg["dim"], "table_rows_per_gpu": rows_per_gpu,
-                   "table_rows_total": n_rows * world, "structures": structures,
+                   "table_rows_total": n_rows, "structures": structures,
+                   "parallelism": "1 GPU, table resident" if world == 1 else
+                                  "table and Adam state row-sharded over %d GPUs, rows and row gradients over NVLink" % world,
                    "optimizer": "adam, row-wise v" if cfg["squeeze"] else "adam, full v",
                    "lazy_rows": not args.no_lazy,
                    "l2_policy": "inputs larger than L2: every step touches ~%.1f GB of table rows" %

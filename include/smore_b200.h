@@ -213,6 +213,58 @@ SMORE_API int smore_sparse_update_rows(int opt_id, float* table, float* m, float
                              size_t width, double lr, double beta1, double beta2, double eps,
                              int64_t step, int squeeze, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Row-sharded table over the GPUs of one box (one process per GPU).
+ * Replaces the reference's sharing of the table through CPU shared memory with pinned PCIe
+ * staging (embed_rw.py:53-134, extlib_cuda.cpp:82-144, kg_reasoning.py:144-147): rows
+ * [g*S, (g+1)*S) of the table and of its Adam state live in the memory of GPU g; requesters and
+ * owners read each other's memory with plain loads over NVLink.  None of these calls waits on
+ * another rank; the caller orders the phases of a step (stream-ordered collectives).
+ * ------------------------------------------------------------------------------------------ */
+
+/* Device memory that other processes may map.  The only entry points of the library that
+ * allocate or free.  export/import move a 64-byte handle between processes (any transport);
+ * release unmaps an imported pointer. */
+SMORE_API int smore_peer_alloc(size_t bytes, void** ptr);
+SMORE_API int smore_peer_free(void* ptr);
+SMORE_API int smore_peer_export(const void* ptr, unsigned char* handle64);
+SMORE_API int smore_peer_import(const unsigned char* handle64, void** ptr);
+SMORE_API int smore_peer_release(void* ptr);
+
+/* staging[u, :] = shard_ptrs[id / rows_per_shard][id % rows_per_shard, :] for id = uniq[u],
+ * u < *n_unique: each distinct row of the step crosses NVLink once and lands in local memory,
+ * where the distance kernels then read it (by slot).  shard_ptrs: device array of the ranks'
+ * shard base pointers (peer-mapped). */
+SMORE_API int smore_fetch_rows(const float* const* shard_ptrs, size_t rows_per_shard, const int64_t* uniq,
+                     const int32_t* n_unique, size_t capacity, size_t width, float* staging,
+                     void* stream);
+
+/* Owner side of the gradient return.  Every rank publishes up to n_plans (<= 4) sorted lists of
+ * distinct global row ids per step with a gradient row per id; list (g, p) has room for
+ * plan_caps[p] ids (host array, same on all ranks), its current length is the int32 that
+ * nuniq_ptrs[g*n_plans+p] points to (0 = unused this step).
+ * collect_ids writes ids[g][prefix(p) + j] = id - base if the j-th id of list (g, p) lies in
+ * [base, base + shard_rows), else -1, and list_bounds[l] = [first, last+1) of the kept entries.
+ * Run smore_unique_rows over `ids` (n = n_ranks * sum(plan_caps), n_table_rows = shard_rows) to
+ * get the owner's distinct local rows, then record_sources, then reduce_update. */
+SMORE_API int smore_shard_collect_ids(const int64_t* const* uniq_ptrs, const int32_t* const* nuniq_ptrs,
+                            size_t n_ranks, size_t n_plans, const int32_t* plan_caps, int64_t base,
+                            size_t shard_rows, int64_t* ids, int32_t* list_bounds, void* stream);
+
+/* src[slot[i]] = i for every position with slot >= 0 (one contributing position per distinct
+ * row; rows with several contributors are resolved by search in reduce_update). */
+SMORE_API int smore_shard_record_sources(const int32_t* slot, size_t n, int32_t* src, void* stream);
+
+/* For each distinct local row u < *n_unique: pull its gradient rows from the lists that contain
+ * it (grad_ptrs[l] + j*width, peer memory), add them in list order, and apply the Adam update of
+ * smore_sparse_update_rows to table / m / v of this shard — one kernel, one pass. */
+SMORE_API int smore_shard_reduce_update_rows(float* table, float* m, float* v, const int64_t* uniq,
+                                   const int32_t* counts, const int32_t* src, const int32_t* n_unique,
+                                   size_t capacity, const float* const* grad_ptrs, const int64_t* ids,
+                                   const int32_t* list_bounds, size_t n_ranks, size_t n_plans,
+                                   const int32_t* plan_caps, size_t width, double lr, double beta1,
+                                   double beta2, double eps, int64_t step, int squeeze, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,358 @@
+// Row-sharded entity table over the GPUs of one NVLink / NVSwitch box: peer-memory plumbing and
+// the kernels that move rows and row gradients between owners and requesters.
+//
+// The reference shares its table between GPU processes through CPU shared memory and PCIe staging
+// (smore/common/embedding/embed_rw.py:53-134, smore/common/torchext/extlib_cuda.cpp:82-144,
+// smore/models/kg_reasoning.py:144-147).  Here rows [g*S, (g+1)*S) of the table and of its Adam
+// state live in the HBM of GPU g, and every exchange is a kernel of this file doing plain 128-bit
+// loads from peer-mapped memory:
+//   fetch_rows_kernel          requester pulls each distinct row of its step once into a local
+//                              staging block (forward and backward then run on local memory)
+//   shard_collect_ids_kernel   owner reads every rank's list of distinct row ids and keeps those in
+//                              its range (as local ids; everything else becomes -1)
+//   shard_reduce_update_kernel owner pulls the gradient rows of each of its touched rows from the
+//                              ranks that produced them, sums them in a fixed order and applies
+//                              Adam to its shard — transfer, reduction and update in one pass
+// No kernel here waits on another rank: ordering between the phases of a step is the caller's
+// (stream-ordered collectives).  No TMA, no multicast: peer data is read with ordinary loads.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <climits>
+#include <cstring>
+
+#include "common.cuh"
+#include "update_math.cuh"
+
+namespace smore {
+
+constexpr int kMaxPlans = 4;    // id lists a rank may publish per step
+constexpr int kMaxLists = 32;   // ranks x plans; one lane per list in the search below
+
+struct PlanCaps {
+  int n_plans;
+  int cap[kMaxPlans];
+  int prefix[kMaxPlans + 1];  // prefix[p] = first position of plan p inside one rank's span
+};
+
+static int make_caps(const int32_t* plan_caps, size_t n_plans, PlanCaps* out) {
+  if (n_plans == 0 || n_plans > (size_t)kMaxPlans || !plan_caps)
+    return fail(SMORE_ERR_BAD_SHAPE, "n_plans must be 1..%d", kMaxPlans);
+  out->n_plans = (int)n_plans;
+  out->prefix[0] = 0;
+  for (int p = 0; p < kMaxPlans; ++p) {
+    out->cap[p] = p < (int)n_plans ? plan_caps[p] : 0;
+    if (out->cap[p] < 0) return fail(SMORE_ERR_BAD_SHAPE, "negative plan capacity");
+    if ((long long)out->prefix[p] + out->cap[p] > INT_MAX) return fail(SMORE_ERR_TOO_LARGE, "plan capacities");
+    out->prefix[p + 1] = out->prefix[p] + out->cap[p];
+  }
+  return SMORE_OK;
+}
+
+__device__ __forceinline__ void decode_position(const PlanCaps& c, int64_t i, int& list, int& j) {
+  const int span = c.prefix[kMaxPlans];
+  const int g = (int)(i / span);
+  const int rem = (int)(i - (int64_t)g * span);
+  int p = 0;
+#pragma unroll
+  for (int q = 1; q < kMaxPlans; ++q)
+    if (q < c.n_plans && rem >= c.prefix[q]) p = q;
+  list = g * c.n_plans + p;
+  j = rem - c.prefix[p];
+}
+
+// staging[u, :] = shard[owner(uniq[u])][local(uniq[u]), :]
+__global__ void __launch_bounds__(256)
+    fetch_rows_kernel(const float* const* __restrict__ shard_ptrs, size_t rows_per_shard,
+                      const int64_t* __restrict__ uniq, const int32_t* __restrict__ n_unique, size_t w4,
+                      float4* __restrict__ staging) {
+  const int lane = threadIdx.x & 31;
+  const size_t nu = (size_t)max(n_unique[0], 0);
+  const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+  for (size_t u = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); u < nu; u += warps) {
+    const size_t id = (size_t)uniq[u];
+    const size_t owner = id / rows_per_shard, local = id - owner * rows_per_shard;
+    const float4* src = reinterpret_cast<const float4*>(shard_ptrs[owner]) + local * w4;
+    float4* dst = staging + u * w4;
+    for (size_t d = lane; d < w4; d += kWarp) dst[d] = src[d];
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    shard_collect_ids_kernel(const int64_t* const* __restrict__ uniq_ptrs,
+                             const int32_t* const* __restrict__ nuniq_ptrs, PlanCaps c, int n_ranks,
+                             int64_t base, int64_t shard_rows, int64_t* __restrict__ out_ids,
+                             int32_t* __restrict__ bounds) {
+  __shared__ int counts_sh[kMaxLists];  // each list's length is read from its owner once per CTA
+  if (threadIdx.x < n_ranks * c.n_plans) counts_sh[threadIdx.x] = nuniq_ptrs[threadIdx.x][0];
+  __syncthreads();
+  const int64_t total = (int64_t)n_ranks * c.prefix[kMaxPlans];
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int list, j;
+    decode_position(c, i, list, j);
+    int64_t local = -1;
+    const int count = counts_sh[list];
+    if (j < count) {
+      const int64_t id = uniq_ptrs[list][j] - base;
+      if (id >= 0 && id < shard_rows) {
+        local = id;
+        atomicMin(bounds + 2 * list, j);
+        atomicMax(bounds + 2 * list + 1, j + 1);
+      }
+    }
+    out_ids[i] = local;
+  }
+}
+
+__global__ void __launch_bounds__(256) shard_init_bounds_kernel(int32_t* bounds, int n_lists) {
+  const int l = blockIdx.x * blockDim.x + threadIdx.x;
+  if (l < n_lists) {
+    bounds[2 * l] = INT_MAX;
+    bounds[2 * l + 1] = 0;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    shard_record_sources_kernel(const int32_t* __restrict__ slot, size_t n, int32_t* __restrict__ src) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const int32_t s = slot[i];
+    if (s >= 0) src[s] = (int32_t)i;  // any contributor will do; rows with several are searched for
+  }
+}
+
+struct ReduceArgs {
+  const int32_t* counts;            // contributors per distinct row
+  const int32_t* src;               // one contributing position per distinct row
+  const float* const* grad_ptrs;    // [lists] gradient blocks (peer memory)
+  const int64_t* ids;               // collected local ids, [ranks][span]
+  const int32_t* bounds;            // [lists][2] valid range of each list inside its span
+  PlanCaps caps;
+  int n_lists;
+};
+
+template <int NCH>
+__device__ __forceinline__ void add_row(float4 (&g)[NCH], const float4* row, int lane, int w4) {
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int d = lane + 32 * j;
+    if (d < w4) {
+      const float4 x = row[d];
+      g[j].x += x.x;
+      g[j].y += x.y;
+      g[j].z += x.z;
+      g[j].w += x.w;
+    }
+  }
+}
+
+template <int NCH, bool ROWWISE>
+__global__ void __launch_bounds__(256) shard_reduce_update_kernel(UpdateArgs a, ReduceArgs r) {
+  const int lane = threadIdx.x & 31;
+  const size_t nu = (size_t)max(a.n_unique[0], 0);
+  const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+  const int w4 = (int)(a.width >> 2);
+  const int span = r.caps.prefix[kMaxPlans];
+  for (size_t u = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); u < nu; u += warps) {
+    const int64_t row = a.uniq[u];
+    float4* p4 = reinterpret_cast<float4*>(a.table + (size_t)row * a.width);
+    float4* m4 = reinterpret_cast<float4*>(a.m + (size_t)row * a.width);
+    float4* v4 = ROWWISE ? nullptr : reinterpret_cast<float4*>(a.v + (size_t)row * a.width);
+    float4 g[NCH], p[NCH], m[NCH], v[NCH];
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int d = lane + 32 * j;
+      g[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (d < w4) {
+        p[j] = p4[d];
+        m[j] = m4[d];
+        if (!ROWWISE) v[j] = v4[d];
+      }
+    }
+    // ---- pull and sum this row's gradient contributions ----------------------------------------
+    if (r.counts[u] == 1) {
+      int list, j;
+      decode_position(r.caps, (int64_t)r.src[u], list, j);
+      add_row<NCH>(g, reinterpret_cast<const float4*>(r.grad_ptrs[list]) + (size_t)j * w4, lane, w4);
+    } else {
+      // lane l searches list l (ids ascending inside [lo, hi)); contributions are then added in
+      // list order, so the sum does not depend on timing
+      int found = -1;
+      if (lane < r.n_lists) {
+        const int g_rank = lane / r.caps.n_plans, pl = lane - g_rank * r.caps.n_plans;
+        const int64_t* ids = r.ids + (size_t)g_rank * span + r.caps.prefix[pl];
+        int lo = r.bounds[2 * lane], hi = r.bounds[2 * lane + 1];
+        while (lo < hi) {
+          const int mid = (lo + hi) >> 1;
+          const int64_t x = ids[mid];
+          if (x < row) lo = mid + 1; else hi = mid;
+        }
+        if (lo < r.bounds[2 * lane + 1] && ids[lo] == row) found = lo;
+      }
+      unsigned hits = __ballot_sync(0xffffffffu, found >= 0);
+      while (hits) {
+        const int l = __ffs(hits) - 1;
+        hits &= hits - 1;
+        const int j = __shfl_sync(0xffffffffu, found, l);
+        add_row<NCH>(g, reinterpret_cast<const float4*>(r.grad_ptrs[l]) + (size_t)j * w4, lane, w4);
+      }
+    }
+    // ---- Adam on the local row -----------------------------------------------------------------
+    float denom = 0.f, v_old = 0.f, v_new = 0.f;
+    if (ROWWISE) {
+      v_old = a.v[row];
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < NCH; ++j)
+        if (lane + 32 * j < w4) s += g[j].x * g[j].x + g[j].y * g[j].y + g[j].z * g[j].z + g[j].w * g[j].w;
+      const float g2mean = warp_sum(s) / (float)a.width;
+      v_new = v_old * a.beta2 + g2mean * a.omb2;
+      denom = sqrtf(v_new) / a.sqrt_bc2 + a.eps;
+    }
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int d = lane + 32 * j;
+      if (d < w4) {
+        if (ROWWISE) {
+          adam_elem_rowwise(g[j].x, p[j].x, m[j].x, denom, a);
+          adam_elem_rowwise(g[j].y, p[j].y, m[j].y, denom, a);
+          adam_elem_rowwise(g[j].z, p[j].z, m[j].z, denom, a);
+          adam_elem_rowwise(g[j].w, p[j].w, m[j].w, denom, a);
+        } else {
+          adam_elem(g[j].x, p[j].x, m[j].x, v[j].x, a);
+          adam_elem(g[j].y, p[j].y, m[j].y, v[j].y, a);
+          adam_elem(g[j].z, p[j].z, m[j].z, v[j].z, a);
+          adam_elem(g[j].w, p[j].w, m[j].w, v[j].w, a);
+          v4[d] = v[j];
+        }
+        p4[d] = p[j];
+        m4[d] = m[j];
+      }
+    }
+    if (ROWWISE && lane == 0) a.v[row] = v_old + (v_new - v_old);
+  }
+}
+
+static int grid_warps(size_t items) {
+  return (int)std::max<size_t>(1, std::min<size_t>((items + 7) / 8, (size_t)kNumSM * 16));
+}
+static int grid_threads(size_t items) {
+  return (int)std::max<size_t>(1, std::min<size_t>((items + 255) / 256, (size_t)kNumSM * 16));
+}
+
+}  // namespace smore
+
+using namespace smore;
+
+extern "C" {
+
+int smore_peer_alloc(size_t bytes, void** ptr) {
+  if (!ptr || bytes == 0) return fail(SMORE_ERR_NULL, "peer_alloc: bad arguments");
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e != cudaSuccess) return fail(SMORE_ERR_CUDA, "cudaMalloc(%zu): %s", bytes, cudaGetErrorString(e));
+  return SMORE_OK;
+}
+
+int smore_peer_free(void* ptr) {
+  cudaError_t e = cudaFree(ptr);
+  if (e != cudaSuccess) return fail(SMORE_ERR_CUDA, "cudaFree: %s", cudaGetErrorString(e));
+  return SMORE_OK;
+}
+
+int smore_peer_export(const void* ptr, unsigned char* handle64) {
+  if (!ptr || !handle64) return fail(SMORE_ERR_NULL, "peer_export: NULL pointer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, const_cast<void*>(ptr));
+  if (e != cudaSuccess) return fail(SMORE_ERR_CUDA, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+  memcpy(handle64, &h, 64);
+  return SMORE_OK;
+}
+
+int smore_peer_import(const unsigned char* handle64, void** ptr) {
+  if (!ptr || !handle64) return fail(SMORE_ERR_NULL, "peer_import: NULL pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return fail(SMORE_ERR_CUDA, "cudaIpcOpenMemHandle: %s", cudaGetErrorString(e));
+  return SMORE_OK;
+}
+
+int smore_peer_release(void* ptr) {
+  cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  if (e != cudaSuccess) return fail(SMORE_ERR_CUDA, "cudaIpcCloseMemHandle: %s", cudaGetErrorString(e));
+  return SMORE_OK;
+}
+
+int smore_fetch_rows(const float* const* shard_ptrs, size_t rows_per_shard, const int64_t* uniq,
+                     const int32_t* n_unique, size_t capacity, size_t width, float* staging, void* stream) {
+  if (capacity == 0) return SMORE_OK;
+  if (!shard_ptrs || !uniq || !n_unique || !staging) return fail(SMORE_ERR_NULL, "fetch_rows: NULL pointer");
+  if (rows_per_shard == 0 || width == 0 || (width & 3) || !aligned16(staging))
+    return fail(SMORE_ERR_BAD_SHAPE, "fetch_rows: width must be a positive multiple of 4 floats, staging 16-byte aligned");
+  fetch_rows_kernel<<<grid_warps(capacity), 256, 0, (cudaStream_t)stream>>>(
+      shard_ptrs, rows_per_shard, uniq, n_unique, width >> 2, reinterpret_cast<float4*>(staging));
+  return check_launch("fetch_rows_kernel");
+}
+
+int smore_shard_collect_ids(const int64_t* const* uniq_ptrs, const int32_t* const* nuniq_ptrs, size_t n_ranks,
+                            size_t n_plans, const int32_t* plan_caps, int64_t base, size_t shard_rows,
+                            int64_t* out_ids, int32_t* list_bounds, void* stream) {
+  if (!uniq_ptrs || !nuniq_ptrs || !out_ids || !list_bounds) return fail(SMORE_ERR_NULL, "shard_collect_ids: NULL pointer");
+  PlanCaps c;
+  if (int rc = make_caps(plan_caps, n_plans, &c)) return rc;
+  if (n_ranks == 0 || n_ranks * n_plans > (size_t)kMaxLists)
+    return fail(SMORE_ERR_BAD_SHAPE, "ranks x plans must be 1..%d", kMaxLists);
+  const size_t total = n_ranks * (size_t)c.prefix[kMaxPlans];
+  if (total > (size_t)INT_MAX) return fail(SMORE_ERR_TOO_LARGE, "shard_collect_ids: more than 2^31-1 positions");
+  cudaStream_t st = (cudaStream_t)stream;
+  shard_init_bounds_kernel<<<1, 256, 0, st>>>(list_bounds, (int)(n_ranks * n_plans));
+  if (total)
+    shard_collect_ids_kernel<<<grid_threads(total), 256, 0, st>>>(uniq_ptrs, nuniq_ptrs, c, (int)n_ranks, base,
+                                                                  (int64_t)shard_rows, out_ids, list_bounds);
+  return check_launch("shard_collect_ids kernels", 2);
+}
+
+int smore_shard_record_sources(const int32_t* slot, size_t n, int32_t* src, void* stream) {
+  if (n == 0) return SMORE_OK;
+  if (!slot || !src) return fail(SMORE_ERR_NULL, "shard_record_sources: NULL pointer");
+  shard_record_sources_kernel<<<grid_threads(n), 256, 0, (cudaStream_t)stream>>>(slot, n, src);
+  return check_launch("shard_record_sources_kernel");
+}
+
+int smore_shard_reduce_update_rows(float* table, float* m, float* v, const int64_t* uniq, const int32_t* counts,
+                                   const int32_t* src, const int32_t* n_unique, size_t capacity,
+                                   const float* const* grad_ptrs, const int64_t* ids, const int32_t* list_bounds,
+                                   size_t n_ranks, size_t n_plans, const int32_t* plan_caps, size_t width,
+                                   double lr, double beta1, double beta2, double eps, int64_t step, int squeeze,
+                                   void* stream) {
+  if (capacity == 0) return SMORE_OK;
+  if (!table || !m || !v || !uniq || !counts || !src || !n_unique || !grad_ptrs || !ids || !list_bounds)
+    return fail(SMORE_ERR_NULL, "shard_reduce_update_rows: NULL pointer");
+  if (step < 1) return fail(SMORE_ERR_BAD_SHAPE, "adam step must be >= 1");
+  if (width == 0 || (width & 3) || width > 1024 || !aligned16(table) || !aligned16(m) || (!squeeze && !aligned16(v)))
+    return fail(SMORE_ERR_BAD_SHAPE, "shard_reduce_update_rows: width must be a multiple of 4 floats, at most 1024");
+  ReduceArgs r;
+  if (int rc = make_caps(plan_caps, n_plans, &r.caps)) return rc;
+  if (n_ranks == 0 || n_ranks * n_plans > (size_t)kMaxLists)
+    return fail(SMORE_ERR_BAD_SHAPE, "ranks x plans must be 1..%d", kMaxLists);
+  r.counts = counts; r.src = src; r.grad_ptrs = grad_ptrs; r.ids = ids; r.bounds = list_bounds;
+  r.n_lists = (int)(n_ranks * n_plans);
+  UpdateArgs a;
+  a.table = table; a.m = m; a.v = v; a.uniq = uniq; a.g_rows = nullptr; a.n_unique = n_unique; a.width = width;
+  set_hyper(a, lr, beta1, beta2, eps, step, squeeze);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int grid = grid_warps(capacity);
+  const size_t w4 = width >> 2;
+#define REDUCE(NCH)                                                                \
+  if (a.squeeze) shard_reduce_update_kernel<NCH, true><<<grid, 256, 0, st>>>(a, r); \
+  else shard_reduce_update_kernel<NCH, false><<<grid, 256, 0, st>>>(a, r)
+  if (w4 <= 32) { REDUCE(1); }
+  else if (w4 <= 64) { REDUCE(2); }
+  else if (w4 <= 128) { REDUCE(4); }
+  else { REDUCE(8); }
+#undef REDUCE
+  return check_launch("shard_reduce_update_kernel");
+}
+
+}  // extern "C"

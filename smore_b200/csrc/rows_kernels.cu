@@ -14,6 +14,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "update_math.cuh"
 
 namespace smore {
 
@@ -255,33 +256,7 @@ __global__ void __launch_bounds__(256)
 // row-wise optimizers: one warp per touched row, one pass over (g, p, m, v)
 // ----------------------------------------------------------------------------------------
 
-struct UpdateArgs {
-  float* table;
-  float* m;
-  float* v;
-  const int64_t* uniq;
-  const float* g_rows;
-  const int32_t* n_unique;
-  size_t width;
-  float lr, beta1, beta2, omb1, omb2, eps, step_size, sqrt_bc2;
-  int squeeze;
-};
-
-__device__ __forceinline__ void adam_elem(float g, float& p, float& m, float& v, const UpdateArgs& a) {
-  const float v_new = v * a.beta2 + g * g * a.omb2;
-  const float m_new = m * a.beta1 + g * a.omb1;
-  const float denom = sqrtf(v_new) / a.sqrt_bc2 + a.eps;
-  p += a.step_size * m_new / denom;
-  m = m + (m_new - m);  // the reference stores state as old + (new - old), embed_optimizer.py:251-252
-  v = v + (v_new - v);
-}
-
-__device__ __forceinline__ void adam_elem_rowwise(float g, float& p, float& m, float denom,
-                                                  const UpdateArgs& a) {
-  const float m_new = m * a.beta1 + g * a.omb1;
-  p += a.step_size * m_new / denom;
-  m = m + (m_new - m);
-}
+// UpdateArgs, adam_elem, adam_elem_rowwise: update_math.cuh
 
 // Adam for rows of at most 32 * NCH 16-byte chunks: every load of a row (gradient, parameters,
 // first moment and, with a full second moment, that too) is issued before anything is computed,
@@ -578,13 +553,7 @@ int smore_sparse_update_rows(int opt_id, float* table, float* m, float* v, const
   UpdateArgs a;
   a.table = table; a.m = m; a.v = v; a.uniq = uniq; a.g_rows = g_rows; a.n_unique = n_unique;
   a.width = width;
-  // hyper-parameters arrive as doubles (Python floats in the reference) and are narrowed once
-  const double bc1 = 1.0 - std::pow(beta1, (double)step);
-  const double bc2 = 1.0 - std::pow(beta2, (double)step);
-  a.lr = (float)lr; a.beta1 = (float)beta1; a.beta2 = (float)beta2;
-  a.omb1 = (float)(1.0 - beta1); a.omb2 = (float)(1.0 - beta2); a.eps = (float)eps;
-  a.step_size = (float)(-lr / bc1); a.sqrt_bc2 = (float)std::sqrt(bc2);
-  a.squeeze = squeeze != 0;
+  set_hyper(a, lr, beta1, beta2, eps, step, squeeze);
   cudaStream_t st = (cudaStream_t)stream;
   const bool vec = (width % 4 == 0) && aligned16(table) && aligned16(g_rows) && (!m || aligned16(m)) &&
                    (!v || squeeze || aligned16(v));

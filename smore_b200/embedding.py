@@ -260,7 +260,7 @@ class _EmbedLookupFunc(torch.autograd.Function):
     def forward(ctx, opt, dummy, lookup):
         ctx.opt = opt
         ctx.lookup = lookup
-        return opt._gather(lookup.idx)
+        return opt._gather_lookup(lookup)
 
     @staticmethod
     def backward(ctx, grad_output):
@@ -399,6 +399,13 @@ class EmbeddingOptimizer(object):
 
     def _materialize(self, lookup):
         return _EmbedLookupFunc.apply(self, self.dummy_tensor, lookup)
+
+    def _gather_lookup(self, lookup):
+        return self._gather(lookup.idx)
+
+    def rows_operands(self, lookup):
+        """(rows tensor, int64 row ids into it) that the distance kernels read for `lookup`."""
+        return self.table, lookup.idx
 
     def plan_for(self, lookup):
         """The step plan that covers `lookup`, built on first use from every lookup made so far."""

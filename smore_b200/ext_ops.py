@@ -132,7 +132,7 @@ class _RowsDistFunc(torch.autograd.Function):
         second = None if second is None else second.contiguous()
         be, ne = _check_rows_operands(name, rows, first, second)
         owner, lookup = rows.owner, rows.lookup
-        table = owner.table
+        table, row_ids = owner.rows_operands(lookup)
         bc, nc, dim = first.shape
         bsize, num = max(be, bc), max(ne, nc)
         L = _lib.lib()
@@ -142,13 +142,13 @@ class _RowsDistFunc(torch.autograd.Function):
             if name == "box_both":
                 d0 = torch.empty(bsize, num, dtype=table.dtype, device=table.device)
                 d1 = torch.empty_like(d0)
-                _lib.check(L.smore_box_forward(table.data_ptr(), lookup.idx.data_ptr(), first.data_ptr(),
+                _lib.check(L.smore_box_forward(table.data_ptr(), row_ids.data_ptr(), first.data_ptr(),
                                                second.data_ptr(), d0.data_ptr(), d1.data_ptr(), *sizes, st),
                            "smore_box_forward")
                 outs = (d0, d1)
             else:
                 d0 = torch.empty(bsize, num, dtype=table.dtype, device=table.device)
-                _lib.check(L.smore_dist_forward_rows(_lib.DIST_IDS[name], table.data_ptr(), lookup.idx.data_ptr(),
+                _lib.check(L.smore_dist_forward_rows(_lib.DIST_IDS[name], table.data_ptr(), row_ids.data_ptr(),
                                                      first.data_ptr(), None if second is None else second.data_ptr(),
                                                      d0.data_ptr(), *sizes, st), "smore_dist_forward_rows")
                 outs = (d0,)
@@ -168,7 +168,7 @@ class _RowsDistFunc(torch.autograd.Function):
             (first,) = ctx.saved_tensors
             second = None
         owner, lookup = ctx.rows.owner, ctx.rows.lookup
-        table = owner.table
+        table, row_ids = owner.rows_operands(lookup)
         plan = owner.plan_for(lookup)
         # the first gradient producer of a lookup may store rows that nothing else touches; any
         # later one over the same positions (another union branch) has to add to what is there
@@ -183,13 +183,13 @@ class _RowsDistFunc(torch.autograd.Function):
         with torch.cuda.device(table.device), _lib.timed("rows_backward" if ctx.sizes[1] >= 16 else "rows_backward_few"):
             if ctx.name == "box_both":
                 _lib.check(L.smore_box_backward(gouts[0].data_ptr(), gouts[1].data_ptr(), table.data_ptr(),
-                                                lookup.idx.data_ptr(), first.data_ptr(), second.data_ptr(), None,
+                                                row_ids.data_ptr(), first.data_ptr(), second.data_ptr(), None,
                                                 slot.data_ptr(), counts_ptr, plan.g_rows.data_ptr(),
                                                 g_first.data_ptr(), g_second.data_ptr(), *ctx.sizes, st),
                            "smore_box_backward")
             else:
                 _lib.check(L.smore_dist_backward_rows(_lib.DIST_IDS[ctx.name], gouts[0].data_ptr(), table.data_ptr(),
-                                                      lookup.idx.data_ptr(), first.data_ptr(),
+                                                      row_ids.data_ptr(), first.data_ptr(),
                                                       None if second is None else second.data_ptr(),
                                                       slot.data_ptr(), counts_ptr, plan.g_rows.data_ptr(),
                                                       g_first.data_ptr(),
