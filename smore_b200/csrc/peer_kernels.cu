@@ -62,19 +62,42 @@ __device__ __forceinline__ void decode_position(const PlanCaps& c, int64_t i, in
 }
 
 // staging[u, :] = shard[owner(uniq[u])][local(uniq[u]), :]
+// A warp copies ROWS rows per iteration and issues every 16-byte load of all of them before the
+// first store, so that ROWS x NCH 512-byte requests per warp are in flight over NVLink.
+template <int NCH, int ROWS>
 __global__ void __launch_bounds__(256)
     fetch_rows_kernel(const float* const* __restrict__ shard_ptrs, size_t rows_per_shard,
-                      const int64_t* __restrict__ uniq, const int32_t* __restrict__ n_unique, size_t w4,
+                      const int64_t* __restrict__ uniq, const int32_t* __restrict__ n_unique, int w4,
                       float4* __restrict__ staging) {
   const int lane = threadIdx.x & 31;
   const size_t nu = (size_t)max(n_unique[0], 0);
   const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
-  for (size_t u = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); u < nu; u += warps) {
-    const size_t id = (size_t)uniq[u];
-    const size_t owner = id / rows_per_shard, local = id - owner * rows_per_shard;
-    const float4* src = reinterpret_cast<const float4*>(shard_ptrs[owner]) + local * w4;
-    float4* dst = staging + u * w4;
-    for (size_t d = lane; d < w4; d += kWarp) dst[d] = src[d];
+  for (size_t u0 = ((size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * ROWS; u0 < nu;
+       u0 += warps * ROWS) {
+    float4 x[ROWS][NCH];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const size_t u = min(u0 + r, nu - 1);
+      const size_t id = (size_t)uniq[u];
+      const size_t owner = id / rows_per_shard, local = id - owner * rows_per_shard;
+      const float4* src = reinterpret_cast<const float4*>(shard_ptrs[owner]) + local * (size_t)w4;
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const int d = lane + 32 * j;
+        if (d < w4) x[r][j] = src[d];
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      if (u0 + r < nu) {
+        float4* dst = staging + (u0 + r) * (size_t)w4;
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) {
+          const int d = lane + 32 * j;
+          if (d < w4) dst[d] = x[r][j];
+        }
+      }
+    }
   }
 }
 
@@ -94,11 +117,13 @@ __global__ void __launch_bounds__(256)
     int64_t local = -1;
     const int count = counts_sh[list];
     if (j < count) {
-      const int64_t id = uniq_ptrs[list][j] - base;
+      const int64_t* ids = uniq_ptrs[list];
+      const int64_t id = ids[j] - base;
       if (id >= 0 && id < shard_rows) {
         local = id;
-        atomicMin(bounds + 2 * list, j);
-        atomicMax(bounds + 2 * list + 1, j + 1);
+        // ids ascend, so the kept entries of a list are one run: only its two ends write the bounds
+        if (j == 0 || ids[j - 1] < base) bounds[2 * list] = j;
+        if (j + 1 == count || ids[j + 1] - base >= shard_rows) bounds[2 * list + 1] = j + 1;
       }
     }
     out_ids[i] = local;
@@ -288,10 +313,20 @@ int smore_fetch_rows(const float* const* shard_ptrs, size_t rows_per_shard, cons
                      const int32_t* n_unique, size_t capacity, size_t width, float* staging, void* stream) {
   if (capacity == 0) return SMORE_OK;
   if (!shard_ptrs || !uniq || !n_unique || !staging) return fail(SMORE_ERR_NULL, "fetch_rows: NULL pointer");
-  if (rows_per_shard == 0 || width == 0 || (width & 3) || !aligned16(staging))
-    return fail(SMORE_ERR_BAD_SHAPE, "fetch_rows: width must be a positive multiple of 4 floats, staging 16-byte aligned");
-  fetch_rows_kernel<<<grid_warps(capacity), 256, 0, (cudaStream_t)stream>>>(
-      shard_ptrs, rows_per_shard, uniq, n_unique, width >> 2, reinterpret_cast<float4*>(staging));
+  if (rows_per_shard == 0 || width == 0 || (width & 3) || width > 1024 || !aligned16(staging))
+    return fail(SMORE_ERR_BAD_SHAPE,
+                "fetch_rows: width must be a multiple of 4 floats, at most 1024; staging 16-byte aligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int w4 = (int)(width >> 2);
+  float4* out = reinterpret_cast<float4*>(staging);
+  if (w4 <= 32)
+    fetch_rows_kernel<1, 8><<<grid_warps((capacity + 7) / 8), 256, 0, st>>>(shard_ptrs, rows_per_shard, uniq, n_unique, w4, out);
+  else if (w4 <= 64)
+    fetch_rows_kernel<2, 4><<<grid_warps((capacity + 3) / 4), 256, 0, st>>>(shard_ptrs, rows_per_shard, uniq, n_unique, w4, out);
+  else if (w4 <= 128)
+    fetch_rows_kernel<4, 4><<<grid_warps((capacity + 3) / 4), 256, 0, st>>>(shard_ptrs, rows_per_shard, uniq, n_unique, w4, out);
+  else
+    fetch_rows_kernel<8, 2><<<grid_warps((capacity + 1) / 2), 256, 0, st>>>(shard_ptrs, rows_per_shard, uniq, n_unique, w4, out);
   return check_launch("fetch_rows_kernel");
 }
 
