@@ -599,6 +599,8 @@ def run_gpu(args):
         "clocks": clock_summary,
         "last_loss": last_loss,
     }
+    if args.dump_kernel_times:
+        out["kernel_ms_raw"] = {k: [round(x, 3) for x in v] for k, v in kernel_ms.items()}
     print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -638,6 +640,7 @@ def main():
     ap.add_argument("--no-lazy", action="store_true", help="gather candidate rows instead of reading the table in place")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-steps", type=int, default=6)
+    ap.add_argument("--dump-kernel-times", action="store_true", help="add every timed launch's duration to the JSON")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

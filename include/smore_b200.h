@@ -222,14 +222,9 @@ SMORE_API int smore_sparse_update_rows(int opt_id, float* table, float* m, float
  * another rank; the caller orders the phases of a step (stream-ordered collectives).
  * ------------------------------------------------------------------------------------------ */
 
-/* Device memory that other processes may map.  The only entry points of the library that
- * allocate or free.  export/import move a 64-byte handle between processes (any transport);
- * release unmaps an imported pointer. */
-SMORE_API int smore_peer_alloc(size_t bytes, void** ptr);
-SMORE_API int smore_peer_free(void* ptr);
-SMORE_API int smore_peer_export(const void* ptr, unsigned char* handle64);
-SMORE_API int smore_peer_import(const unsigned char* handle64, void** ptr);
-SMORE_API int smore_peer_release(void* ptr);
+/* Peer-visible memory is the caller's business: the pointers given to these entry points must
+ * be dereferenceable from the calling GPU (same-process peer access, or blocks mapped into every
+ * process by a symmetric-memory allocator; a CUDA IPC mapping works but is slow for random rows). */
 
 /* staging[u, :] = shard_ptrs[id / rows_per_shard][id % rows_per_shard, :] for id = uniq[u],
  * u < *n_unique: each distinct row of the step crosses NVLink once and lands in local memory,

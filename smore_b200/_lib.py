@@ -40,11 +40,6 @@ SIGNATURES = {
     "smore_scatter_add_rows": (_int, [_p, _p, _p, _p, _sz, _sz, _p]),
     "smore_sparse_update_rows": (_int, [_int, _p, _p, _p, _p, _p, _p, _sz, _sz, _dbl, _dbl, _dbl, _dbl,
                                         ctypes.c_int64, _int, _p]),
-    "smore_peer_alloc": (_int, [_sz, ctypes.POINTER(ctypes.c_void_p)]),
-    "smore_peer_free": (_int, [_p]),
-    "smore_peer_export": (_int, [_p, ctypes.c_char_p]),
-    "smore_peer_import": (_int, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),
-    "smore_peer_release": (_int, [_p]),
     "smore_fetch_rows": (_int, [_p, _sz, _p, _p, _sz, _sz, _p, _p]),
     "smore_shard_collect_ids": (_int, [_p, _p, _sz, _sz, ctypes.POINTER(ctypes.c_int32), ctypes.c_int64, _sz, _p, _p,
                                        _p]),

@@ -271,44 +271,6 @@ using namespace smore;
 
 extern "C" {
 
-int smore_peer_alloc(size_t bytes, void** ptr) {
-  if (!ptr || bytes == 0) return fail(SMORE_ERR_NULL, "peer_alloc: bad arguments");
-  cudaError_t e = cudaMalloc(ptr, bytes);
-  if (e != cudaSuccess) return fail(SMORE_ERR_CUDA, "cudaMalloc(%zu): %s", bytes, cudaGetErrorString(e));
-  return SMORE_OK;
-}
-
-int smore_peer_free(void* ptr) {
-  cudaError_t e = cudaFree(ptr);
-  if (e != cudaSuccess) return fail(SMORE_ERR_CUDA, "cudaFree: %s", cudaGetErrorString(e));
-  return SMORE_OK;
-}
-
-int smore_peer_export(const void* ptr, unsigned char* handle64) {
-  if (!ptr || !handle64) return fail(SMORE_ERR_NULL, "peer_export: NULL pointer");
-  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
-  cudaIpcMemHandle_t h;
-  cudaError_t e = cudaIpcGetMemHandle(&h, const_cast<void*>(ptr));
-  if (e != cudaSuccess) return fail(SMORE_ERR_CUDA, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
-  memcpy(handle64, &h, 64);
-  return SMORE_OK;
-}
-
-int smore_peer_import(const unsigned char* handle64, void** ptr) {
-  if (!ptr || !handle64) return fail(SMORE_ERR_NULL, "peer_import: NULL pointer");
-  cudaIpcMemHandle_t h;
-  memcpy(&h, handle64, 64);
-  cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
-  if (e != cudaSuccess) return fail(SMORE_ERR_CUDA, "cudaIpcOpenMemHandle: %s", cudaGetErrorString(e));
-  return SMORE_OK;
-}
-
-int smore_peer_release(void* ptr) {
-  cudaError_t e = cudaIpcCloseMemHandle(ptr);
-  if (e != cudaSuccess) return fail(SMORE_ERR_CUDA, "cudaIpcCloseMemHandle: %s", cudaGetErrorString(e));
-  return SMORE_OK;
-}
-
 int smore_fetch_rows(const float* const* shard_ptrs, size_t rows_per_shard, const int64_t* uniq,
                      const int32_t* n_unique, size_t capacity, size_t width, float* staging, void* stream) {
   if (capacity == 0) return SMORE_OK;

@@ -24,6 +24,7 @@ batches (all gradients of a row are summed before its one Adam update).
 "peer" pointers local, barriers replaced by call order) for tests.
 """
 import ctypes
+import os
 
 import torch
 
@@ -35,20 +36,23 @@ MAX_PLANS = 4
 
 
 class _DeviceBlock(object):
-    """A raw device allocation exposed through __cuda_array_interface__ so torch can view it."""
+    """A byte block of device memory (a uint8 tensor) that typed views are cut from.
 
-    def __init__(self, ptr, nbytes, owner=None):
-        self.ptr, self.nbytes, self.owner = ptr, nbytes, owner
-        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3,
-                                         "strides": None}
+    Peer-visible blocks come from torch's symmetric-memory allocator, which maps every rank's
+    block into every process with large pages.  (Mapping a peer's cudaMalloc block through a CUDA
+    IPC handle also works, but random 1.6 KB row reads through such a mapping ran at ~80 GB/s on
+    B200 against ~700 GB/s through a symmetric-memory mapping, so that route is not offered.)"""
+
+    def __init__(self, tensor):
+        self.tensor = tensor
+        self.ptr, self.nbytes = tensor.data_ptr(), tensor.numel()
 
     def view(self, device, offset, shape, dtype):
-        base = torch.as_tensor(self, device=device)
         n = 1
         for s in shape:
             n *= s
         nbytes = n * torch.empty((), dtype=dtype).element_size()
-        return base[offset:offset + nbytes].view(dtype).view(shape)
+        return self.tensor[offset:offset + nbytes].view(dtype).view(shape)
 
 
 def _round(x, a=256):
@@ -103,7 +107,8 @@ def pointer_tables(layout, arena_ptrs):
 
 
 def exchange_handles(my_handles, group=None):
-    """All ranks' handle lists, indexed by rank (object all-gather over the process group)."""
+    """All ranks' handle lists, indexed by rank (object all-gather over the process group); for
+    transports that pass their own handles between processes."""
     import torch.distributed as dist
     world = dist.get_world_size(group)
     out = [None] * world
@@ -114,7 +119,7 @@ def exchange_handles(my_handles, group=None):
 class ShardedTable(object):
     """The local shard (table + Adam state), the peer-visible arena, and the pointer tables."""
 
-    def __init__(self, n_rows_total, width, rank, world, device, plan_caps, squeeze=True):
+    def __init__(self, n_rows_total, width, rank, world, device, plan_caps, squeeze=True, symmetric=False):
         self.n_rows_total, self.width, self.rank, self.world = int(n_rows_total), int(width), rank, world
         self.device = torch.device(device)
         self.squeeze = bool(squeeze)
@@ -122,10 +127,9 @@ class ShardedTable(object):
         self.base = rank * self.S
         self.local_rows = max(0, min(self.S, n_rows_total - self.base))
         self.layout = ArenaLayout(plan_caps, width)
-        L = _lib.lib()
-        with torch.cuda.device(self.device):
-            self._table_block = self._alloc(L, max(self.S, 1) * width * 4)
-            self._arena_block = self._alloc(L, self.layout.nbytes)
+        self.symmetric = symmetric
+        self._table_block = self._alloc(max(self.S, 1) * width * 4)
+        self._arena_block = self._alloc(self.layout.nbytes)
         self.table = self._table_block.view(self.device, 0, (self.S, width), torch.float32)
         self.m = torch.zeros(self.S, width, device=self.device)
         self.v = torch.zeros(self.S, 1, device=self.device) if squeeze else torch.zeros(self.S, width, device=self.device)
@@ -140,22 +144,19 @@ class ShardedTable(object):
                       for p in range(len(lay.plan_caps))]
         self.peer_table_ptrs = None   # filled by connect()
         self.peer_arena_ptrs = None
-        self._imported = []
+        self._handles = []
 
-    def _alloc(self, L, nbytes):
-        p = ctypes.c_void_p()
-        _lib.check(L.smore_peer_alloc(nbytes, ctypes.byref(p)), "smore_peer_alloc")
-        return _DeviceBlock(p.value, nbytes)
-
-    def export_handles(self):
-        L = _lib.lib()
-        out = []
-        with torch.cuda.device(self.device):
-            for blk in (self._table_block, self._arena_block):
-                buf = ctypes.create_string_buffer(64)
-                _lib.check(L.smore_peer_export(blk.ptr, buf), "smore_peer_export")
-                out.append(bytes(buf.raw))
-        return out
+    def _alloc(self, nbytes):
+        nbytes = _round(nbytes, 16)
+        if self.symmetric:
+            # this library reads peers with plain loads only; keep the blocks off NVLink multicast
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm_mem
+            with torch.cuda.device(self.device):
+                t = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        else:
+            t = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        return _DeviceBlock(t)
 
     def connect(self, table_ptrs, arena_ptrs):
         """Install the base pointers of every rank's shard and arena (this rank's own included)."""
@@ -168,31 +169,23 @@ class ShardedTable(object):
         self.d_grad_ptrs = torch.tensor(tabs["grads"], dtype=torch.int64, device=dev)
 
     def connect_processes(self, group=None):
-        """Exchange IPC handles with the other ranks of `group` and map their memory."""
+        """Map the other ranks' shard and arena blocks (symmetric-memory rendezvous over `group`)."""
         import torch.distributed as dist
-        L = _lib.lib()
-        handles = exchange_handles(self.export_handles(), group)
-        table_ptrs, arena_ptrs = [], []
+        import torch.distributed._symmetric_memory as symm_mem
+        if not self.symmetric:
+            raise _lib.SmoreError("connect_processes needs blocks from the symmetric-memory allocator")
+        group = group if group is not None else dist.group.WORLD
         with torch.cuda.device(self.device):
-            for g, (ht, ha) in enumerate(handles):
-                if g == self.rank:
-                    table_ptrs.append(self._table_block.ptr)
-                    arena_ptrs.append(self._arena_block.ptr)
-                    continue
-                pt, pa = ctypes.c_void_p(), ctypes.c_void_p()
-                _lib.check(L.smore_peer_import(ht, ctypes.byref(pt)), "smore_peer_import(table)")
-                _lib.check(L.smore_peer_import(ha, ctypes.byref(pa)), "smore_peer_import(arena)")
-                self._imported += [pt.value, pa.value]
-                table_ptrs.append(pt.value)
-                arena_ptrs.append(pa.value)
+            ht = symm_mem.rendezvous(self._table_block.tensor, group)
+            ha = symm_mem.rendezvous(self._arena_block.tensor, group)
+        self._handles = [ht, ha]
+        table_ptrs, arena_ptrs = [int(p) for p in ht.buffer_ptrs], [int(p) for p in ha.buffer_ptrs]
+        if table_ptrs[self.rank] != self._table_block.ptr or arena_ptrs[self.rank] != self._arena_block.ptr:
+            raise _lib.SmoreError("symmetric-memory rendezvous returned a different address for the local block")
         self.connect(table_ptrs, arena_ptrs)
 
     def close(self):
-        L = _lib.lib()
-        with torch.cuda.device(self.device):
-            for p in self._imported:
-                L.smore_peer_release(p)
-            self._imported = []
+        self._handles = []
 
     def init_uniform(self, lo, hi, seed):
         """Fill the shard as rows [base, base+S) of a table drawn uniform(lo, hi); the values depend
@@ -420,7 +413,7 @@ class ShardGroup(object):
         import torch.distributed as dist
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
-        shard = ShardedTable(n_rows_total, width, rank, world, device, plan_caps, squeeze)
+        shard = ShardedTable(n_rows_total, width, rank, world, device, plan_caps, squeeze, symmetric=True)
         shard.connect_processes(group)
         return shard
 
