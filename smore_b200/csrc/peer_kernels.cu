@@ -64,6 +64,12 @@ __device__ __forceinline__ void decode_position(const PlanCaps& c, int64_t i, in
 // staging[u, :] = shard[owner(uniq[u])][local(uniq[u]), :]
 // A warp copies ROWS rows per iteration and issues every 16-byte load of all of them before the
 // first store, so that ROWS x NCH 512-byte requests per warp are in flight over NVLink.
+// uniq is sorted, i.e. grouped by owner.  Walking it front to back would make every rank pull
+// from the same owner at the same time (one NVLink port serving all); instead consecutive
+// iterations take rows from kFetchSegments evenly spaced segments of the list, so the requests in
+// flight are spread over all owners at all times.
+constexpr int kFetchSegments = 16;
+
 template <int NCH, int ROWS>
 __global__ void __launch_bounds__(256)
     fetch_rows_kernel(const float* const* __restrict__ shard_ptrs, size_t rows_per_shard,
@@ -71,26 +77,31 @@ __global__ void __launch_bounds__(256)
                       float4* __restrict__ staging) {
   const int lane = threadIdx.x & 31;
   const size_t nu = (size_t)max(n_unique[0], 0);
+  const size_t seglen = (nu + kFetchSegments - 1) / kFetchSegments;
+  const size_t total = seglen * kFetchSegments;
   const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
-  for (size_t u0 = ((size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * ROWS; u0 < nu;
-       u0 += warps * ROWS) {
+  for (size_t t0 = ((size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * ROWS; t0 < total;
+       t0 += warps * ROWS) {
     float4 x[ROWS][NCH];
+    size_t urow[ROWS];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
-      const size_t u = min(u0 + r, nu - 1);
-      const size_t id = (size_t)uniq[u];
+      const size_t t = t0 + r;
+      urow[r] = (t % kFetchSegments) * seglen + t / kFetchSegments;
+      if (t >= total || urow[r] >= nu) urow[r] = nu;  // nothing to copy for this slot
+      const size_t id = (size_t)uniq[urow[r] < nu ? urow[r] : 0];
       const size_t owner = id / rows_per_shard, local = id - owner * rows_per_shard;
       const float4* src = reinterpret_cast<const float4*>(shard_ptrs[owner]) + local * (size_t)w4;
 #pragma unroll
       for (int j = 0; j < NCH; ++j) {
         const int d = lane + 32 * j;
-        if (d < w4) x[r][j] = src[d];
+        if (d < w4 && urow[r] < nu) x[r][j] = src[d];
       }
     }
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
-      if (u0 + r < nu) {
-        float4* dst = staging + (u0 + r) * (size_t)w4;
+      if (urow[r] < nu) {
+        float4* dst = staging + urow[r] * (size_t)w4;
 #pragma unroll
         for (int j = 0; j < NCH; ++j) {
           const int d = lane + 32 * j;
