@@ -18,6 +18,7 @@
 
 #include "common.cuh"
 #include "dist_terms.cuh"
+#include "shared_kernels.cuh"
 
 namespace smore {
 
@@ -444,6 +445,14 @@ static RowPlan plan_rows(const Shape& s, bool aligned) {
   return p;
 }
 
+// one candidate set scored against every query (shared negatives, full-table evaluation)
+static bool shared_shape(const Shape& s, bool aligned) {
+  return aligned && s.be == 1 && s.bc == s.bsize && s.ne == s.num && s.nc == 1 && (s.dim & 3) == 0 &&
+         s.bsize >= 8 && s.num >= 8 && s.bsize < ((size_t)1 << 24) && s.num < ((size_t)1 << 30) &&
+         s.dim < ((size_t)1 << 20) && (s.bsize + kTileB - 1) / kTileB <= 65535 &&
+         ((s.dim >> 2) + kGradCols - 1) / kGradCols <= 65535;
+}
+
 template <class Term>
 static int launch_forward(const Shape& s, const float* ent, const int64_t* idx, const float* first,
                           const float* second, float* dst0, float* dst1, cudaStream_t st) {
@@ -461,6 +470,12 @@ static int launch_forward(const Shape& s, const float* ent, const int64_t* idx, 
       default: row_forward_kernel<Term, 8, 1><<<grid, kRowCtaThreads, 0, st>>>(a, dst0, dst1); break;
     }
     return check_launch("row_forward_kernel");
+  }
+  if (shared_shape(s, aligned)) {
+    SharedArgs a{ent, idx, first, second, (int)s.bsize, (int)s.num, (int)s.dim};
+    dim3 grid((unsigned)((s.num + kTileK - 1) / kTileK), (unsigned)((s.bsize + kTileB - 1) / kTileB));
+    shared_forward_kernel<Term><<<grid, 256, 0, st>>>(a, dst0, dst1);
+    return check_launch("shared_forward_kernel");
   }
   CellArgs<float> a{ent, idx, first, second, s.bsize, s.num, s.be, s.ne, s.bc, s.nc, s.dim};
   cell_forward_kernel<float, Term><<<grid_for(s.bsize * s.num, 8), 256, 0, st>>>(a, dst0, dst1);
@@ -497,6 +512,16 @@ static int launch_backward(const Shape& s, const float* gout0, const float* gout
     else
       col_backward_kernel<Term, 8><<<grid, kRowCtaThreads, smem, st>>>(a, ga, tpr, groups);
     return check_launch("col_backward_kernel");
+  }
+  if (shared_shape(s, aligned)) {
+    SharedArgs a{ent, idx, first, second, (int)s.bsize, (int)s.num, (int)s.dim};
+    SharedGradArgs ga{gout0, gout1, g_ent, slot, slot_count, g_rows, g_first, g_second};
+    const unsigned cols = (unsigned)(((s.dim >> 2) + kGradCols - 1) / kGradCols);
+    dim3 grid_e((unsigned)((s.num + kGradRows - 1) / kGradRows), cols);
+    dim3 grid_q((unsigned)((s.bsize + kGradRows - 1) / kGradRows), cols);
+    shared_backward_ent_kernel<Term><<<grid_e, kGradRows * kGradCols, 0, st>>>(a, ga);
+    shared_backward_query_kernel<Term><<<grid_q, kGradRows * kGradCols, 0, st>>>(a, ga);
+    return check_launch("shared_backward kernels", 2);
   }
   CellArgs<float> a{ent, idx, first, second, s.bsize, s.num, s.be, s.ne, s.bc, s.nc, s.dim};
   cell_backward_ent_kernel<float, Term><<<grid_for(s.be * s.ne * s.dim, 256), 256, 0, st>>>(

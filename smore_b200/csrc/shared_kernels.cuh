@@ -1,0 +1,224 @@
+// Kernels for the shared-candidate shape: one set of K candidate rows scored against every one of
+// B queries (entity [1, K, W] or table + idx[K]; query [B, 1, dim]) — the reference's
+// `--share_negative` training shape and its full-table evaluation shape.
+//
+// Every (query, candidate) pair re-uses rows that other pairs also use, so this shape is bound by
+// fp32 ALU throughput and on-chip bandwidth, not by HBM: B*K*dim term evaluations against only
+// (B + K)*dim*4 bytes.  The forward kernel is tiled like a SIMT matrix product (a 64 x 64 tile of
+// cells per CTA, operands staged through shared memory, 4 x 4 cells per thread); the two backward
+// kernels give each thread one 16-byte column of one gradient row and walk the other operand's
+// rows, which come from L2.  All three are deterministic (no atomics except into rows that occur
+// several times in a step's compact gradient buffer).
+//
+// The reference runs this shape through the same three kernels as every other shape
+// (smore/common/torchext/common_kernel.h:33-123): one warp per cell re-reading both rows from L2
+// in the forward pass, and column-strided walks (one 32-byte sector per 4 useful bytes) in the
+// backward pass.
+#pragma once
+#include <cuda_runtime.h>
+
+#include "common.cuh"
+#include "dist_terms.cuh"
+
+namespace smore {
+
+constexpr int kTileB = 64;     // queries per CTA tile
+constexpr int kTileK = 64;     // candidate rows per CTA tile
+constexpr int kTileD = 16;     // embedding dims staged per step
+constexpr int kTilePad = 4;    // keeps rows of the transposed tiles 16-byte aligned, off the same bank
+
+struct SharedArgs {
+  const float* ent;        // [K, W] or table when idx != nullptr
+  const int64_t* idx;      // nullable [K]
+  const float* first;      // [B, dim]
+  const float* second;     // [B, dim]
+  int B, K, dim;           // dim % 4 == 0
+};
+
+template <class Term>
+__global__ void __launch_bounds__(256)
+    shared_forward_kernel(SharedArgs a, float* __restrict__ dst0, float* __restrict__ dst1) {
+  __shared__ __align__(16) float q0s[kTileD][kTileB + kTilePad];
+  __shared__ __align__(16) float q1s[kTileD][kTileB + kTilePad];
+  __shared__ __align__(16) float e0s[kTileD][kTileK + kTilePad];
+  __shared__ __align__(16) float e1s[Term::kMul == 2 ? kTileD : 1][kTileK + kTilePad];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int b0 = blockIdx.y * kTileB, k0 = blockIdx.x * kTileK;
+  const int dim4 = a.dim >> 2;
+  const size_t w4 = (size_t)dim4 * Term::kMul;
+  // staging role: one 16-byte piece of one row per operand per step
+  const int lrow = threadIdx.x >> 2, lq = threadIdx.x & 3;
+  const bool qrow_ok = b0 + lrow < a.B, erow_ok = k0 + lrow < a.K;
+  const float4* q0p = reinterpret_cast<const float4*>(a.first) + (size_t)(qrow_ok ? b0 + lrow : 0) * dim4;
+  const float4* q1p = reinterpret_cast<const float4*>(a.second) + (size_t)(qrow_ok ? b0 + lrow : 0) * dim4;
+  size_t erow = 0;
+  if (erow_ok) erow = a.idx ? (size_t)a.idx[k0 + lrow] : (size_t)(k0 + lrow);
+  const float4* e0p = reinterpret_cast<const float4*>(a.ent) + erow * w4;
+
+  float acc[4][4][Term::kNOut];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int o = 0; o < Term::kNOut; ++o) acc[i][j][o] = 0.f;
+
+  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int d0 = 0; d0 < a.dim; d0 += kTileD) {
+    const int d4 = (d0 >> 2) + lq;
+    const bool d_ok = d4 < dim4;
+    const float4 vq0 = (qrow_ok && d_ok) ? __ldg(q0p + d4) : z4;
+    const float4 vq1 = (Term::kNQ == 2 && qrow_ok && d_ok) ? __ldg(q1p + d4) : z4;
+    const float4 ve0 = (erow_ok && d_ok) ? __ldg(e0p + d4) : z4;
+    const float4 ve1 = (Term::kMul == 2 && erow_ok && d_ok) ? __ldg(e0p + dim4 + d4) : z4;
+    __syncthreads();  // the previous step's tiles are no longer being read
+    q0s[lq * 4 + 0][lrow] = vq0.x; q0s[lq * 4 + 1][lrow] = vq0.y; q0s[lq * 4 + 2][lrow] = vq0.z; q0s[lq * 4 + 3][lrow] = vq0.w;
+    if (Term::kNQ == 2) {
+      q1s[lq * 4 + 0][lrow] = vq1.x; q1s[lq * 4 + 1][lrow] = vq1.y; q1s[lq * 4 + 2][lrow] = vq1.z; q1s[lq * 4 + 3][lrow] = vq1.w;
+    }
+    e0s[lq * 4 + 0][lrow] = ve0.x; e0s[lq * 4 + 1][lrow] = ve0.y; e0s[lq * 4 + 2][lrow] = ve0.z; e0s[lq * 4 + 3][lrow] = ve0.w;
+    if (Term::kMul == 2) {
+      e1s[lq * 4 + 0][lrow] = ve1.x; e1s[lq * 4 + 1][lrow] = ve1.y; e1s[lq * 4 + 2][lrow] = ve1.z; e1s[lq * 4 + 3][lrow] = ve1.w;
+    }
+    __syncthreads();
+    const int dcount = min(kTileD, a.dim - d0);
+#pragma unroll 4
+    for (int dd = 0; dd < dcount; ++dd) {
+      const float4 q0 = *reinterpret_cast<const float4*>(&q0s[dd][ty * 4]);
+      const float4 q1 = Term::kNQ == 2 ? *reinterpret_cast<const float4*>(&q1s[dd][ty * 4]) : q0;
+      const float4 e0 = *reinterpret_cast<const float4*>(&e0s[dd][tx * 4]);
+      const float4 e1 = Term::kMul == 2 ? *reinterpret_cast<const float4*>(&e1s[dd][tx * 4]) : e0;
+      const float qa[4] = {q0.x, q0.y, q0.z, q0.w}, qb[4] = {q1.x, q1.y, q1.z, q1.w};
+      const float ea[4] = {e0.x, e0.y, e0.z, e0.w}, eb[4] = {e1.x, e1.y, e1.z, e1.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) Term::fwd(ea[j], eb[j], qa[i], qb[i], acc[i][j]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int b = b0 + ty * 4 + i;
+    if (b >= a.B) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int k = k0 + tx * 4 + j;
+      if (k < a.K) {
+        dst0[(size_t)b * a.K + k] = acc[i][j][0];
+        if (Term::kNOut == 2) dst1[(size_t)b * a.K + k] = acc[i][j][Term::kNOut - 1];
+      }
+    }
+  }
+}
+
+struct SharedGradArgs {
+  const float* gout0;         // [B, K]
+  const float* gout1;         // [B, K] (two-output term only)
+  float* g_ent;               // dense [K, W], or nullptr when slot != nullptr
+  const int32_t* slot;        // [K] -> row of g_rows (< 0: skip)
+  const int32_t* slot_count;  // nullable: nullptr = accumulate everywhere
+  float* g_rows;
+  float* g_first;             // [B, dim]
+  float* g_second;            // [B, dim]
+};
+
+template <class Term>
+__device__ __forceinline__ void bwd_vec4(const float* g, const float4& e0, const float4& e1, const float4& q0,
+                                         const float4& q1, float4& ge0, float4& ge1, float4& gq0, float4& gq1) {
+  Term::bwd(g, e0.x, e1.x, q0.x, q1.x, ge0.x, ge1.x, gq0.x, gq1.x);
+  Term::bwd(g, e0.y, e1.y, q0.y, q1.y, ge0.y, ge1.y, gq0.y, gq1.y);
+  Term::bwd(g, e0.z, e1.z, q0.z, q1.z, ge0.z, ge1.z, gq0.z, gq1.z);
+  Term::bwd(g, e0.w, e1.w, q0.w, q1.w, ge0.w, ge1.w, gq0.w, gq1.w);
+}
+
+constexpr int kGradRows = 8;    // gradient rows per CTA
+constexpr int kGradCols = 16;   // 16-byte columns per CTA
+
+// g_ent[k, :] = sum over queries b: thread = (row k, one 16-byte column), queries walked in order.
+template <class Term>
+__global__ void __launch_bounds__(kGradRows* kGradCols)
+    shared_backward_ent_kernel(SharedArgs a, SharedGradArgs ga) {
+  const int tx = threadIdx.x % kGradCols, ty = threadIdx.x / kGradCols;
+  const int k = blockIdx.x * kGradRows + ty, c4 = blockIdx.y * kGradCols + tx;
+  const int dim4 = a.dim >> 2;
+  if (k >= a.K || c4 >= dim4) return;
+  const size_t w4 = (size_t)dim4 * Term::kMul;
+  const size_t row = a.idx ? (size_t)a.idx[k] : (size_t)k;
+  const float4* pe = reinterpret_cast<const float4*>(a.ent) + row * w4 + c4;
+  const float4 e0 = __ldg(pe);
+  const float4 e1 = Term::kMul == 2 ? __ldg(pe + dim4) : e0;
+  const float4* q0p = reinterpret_cast<const float4*>(a.first) + c4;
+  const float4* q1p = reinterpret_cast<const float4*>(a.second) + c4;
+  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 ge0 = z4, ge1 = z4, t0 = z4, t1 = z4;
+#pragma unroll 4
+  for (int b = 0; b < a.B; ++b) {
+    float g[Term::kNOut];
+    g[0] = __ldg(ga.gout0 + (size_t)b * a.K + k);
+    if (Term::kNOut == 2) g[Term::kNOut - 1] = __ldg(ga.gout1 + (size_t)b * a.K + k);
+    const float4 q0 = __ldg(q0p + (size_t)b * dim4);
+    const float4 q1 = Term::kNQ == 2 ? __ldg(q1p + (size_t)b * dim4) : q0;
+    bwd_vec4<Term>(g, e0, e1, q0, q1, ge0, ge1, t0, t1);
+  }
+  if (ga.slot == nullptr) {
+    float4* out = reinterpret_cast<float4*>(ga.g_ent) + (size_t)k * w4 + c4;
+    out[0] = ge0;
+    if (Term::kMul == 2) out[dim4] = ge1;
+  } else {
+    const int32_t s = ga.slot[k];
+    if (s < 0) return;
+    float4* out = reinterpret_cast<float4*>(ga.g_rows) + (size_t)s * w4 + c4;
+    if (ga.slot_count != nullptr && ga.slot_count[s] == 1) {
+      out[0] = ge0;
+      if (Term::kMul == 2) out[dim4] = ge1;
+    } else {
+      atomicAdd(out, ge0);
+      if (Term::kMul == 2) atomicAdd(out + dim4, ge1);
+    }
+  }
+}
+
+// g_first / g_second[b, :] = sum over candidates k: thread = (query b, one 16-byte column).
+template <class Term>
+__global__ void __launch_bounds__(kGradRows* kGradCols)
+    shared_backward_query_kernel(SharedArgs a, SharedGradArgs ga) {
+  __shared__ long long rows_sh[kGradRows * kGradCols];
+  const int tx = threadIdx.x % kGradCols, ty = threadIdx.x / kGradCols;
+  const int b = blockIdx.x * kGradRows + ty, c4 = blockIdx.y * kGradCols + tx;
+  const int dim4 = a.dim >> 2;
+  const bool active = b < a.B && c4 < dim4;
+  const size_t w4 = (size_t)dim4 * Term::kMul;
+  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 q0 = z4, q1 = z4;
+  if (active) {
+    q0 = __ldg(reinterpret_cast<const float4*>(a.first) + (size_t)b * dim4 + c4);
+    if (Term::kNQ == 2) q1 = __ldg(reinterpret_cast<const float4*>(a.second) + (size_t)b * dim4 + c4);
+  }
+  const float4* ent4 = reinterpret_cast<const float4*>(a.ent);
+  float4 gq0 = z4, gq1 = z4, t0 = z4, t1 = z4;
+  for (int k0 = 0; k0 < a.K; k0 += kGradRows * kGradCols) {
+    // the CTA's threads fetch the next 128 row ids once
+    __syncthreads();
+    const int kk = k0 + threadIdx.x;
+    rows_sh[threadIdx.x] = kk < a.K ? (a.idx ? (long long)a.idx[kk] : (long long)kk) : 0;
+    __syncthreads();
+    if (!active) continue;
+    const int n = min(kGradRows * kGradCols, a.K - k0);
+#pragma unroll 4
+    for (int j = 0; j < n; ++j) {
+      const float4* pe = ent4 + (size_t)rows_sh[j] * w4 + c4;
+      const float4 e0 = __ldg(pe);
+      const float4 e1 = Term::kMul == 2 ? __ldg(pe + dim4) : e0;
+      float g[Term::kNOut];
+      g[0] = __ldg(ga.gout0 + (size_t)b * a.K + k0 + j);
+      if (Term::kNOut == 2) g[Term::kNOut - 1] = __ldg(ga.gout1 + (size_t)b * a.K + k0 + j);
+      bwd_vec4<Term>(g, e0, e1, q0, q1, t0, t1, gq0, gq1);
+    }
+  }
+  if (active) {
+    reinterpret_cast<float4*>(ga.g_first)[(size_t)b * dim4 + c4] = gq0;
+    if (Term::kNQ == 2) reinterpret_cast<float4*>(ga.g_second)[(size_t)b * dim4 + c4] = gq1;
+  }
+}
+
+}  // namespace smore

@@ -27,6 +27,10 @@ SHAPES = [
     (2, 19, 2, 1, 1028),     # wider than that: falls back to the cell kernels
     (3, 12, 3, 1, 30),       # dim not a multiple of 4: cell kernels
     (1, 5000, 1, 1, 128),    # one query against many rows (evaluation orientation), several CTAs per query
+    (1, 100, 40, 1, 64),     # shared candidates: the tiled kernels, ragged tiles
+    (1, 512, 70, 1, 400),    # shared candidates at the Query2box row shape
+    (1, 33, 9, 1, 500),      # shared candidates, two-part rows of 1000 floats, dim not a multiple of 16
+    (1, 64, 64, 1, 16),      # exactly one tile
 ]
 
 

@@ -166,7 +166,8 @@ def test_lookup_merge_update_through_optimizer_api(golden, oracle, opt, squeeze)
 
 
 @pytest.mark.parametrize("op", ["l1", "l2", "box_out", "box_in", "rotate", "complex", "distmult"])
-@pytest.mark.parametrize("shape", [(6, 50, 6, 1, 64), (4, 9, 4, 1, 30), (1, 40, 5, 1, 36), (5, 1, 5, 1, 400)],
+@pytest.mark.parametrize("shape", [(6, 50, 6, 1, 64), (4, 9, 4, 1, 30), (1, 40, 5, 1, 36), (5, 1, 5, 1, 400),
+                                   (1, 70, 16, 1, 48)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_table_resident_rows_equal_gathered_rows(oracle, op, shape):
     """forward_rows(table, idx) == forward(table[idx]); backward_rows accumulates what
