@@ -502,6 +502,11 @@ def run_gpu(args):
     # untimed set-up: one step of every query structure, so that the caching allocator already owns
     # a block for each buffer size before the W warm-up steps and the K timed steps
     run_resident(0, len(structures))
+    # keep Python's cycle collector from scanning the long-lived model objects inside a timed region
+    # (a full collection costs ~100 ms here, more than a dozen steps)
+    import gc
+    gc.collect()
+    gc.freeze()
     # ---- resident-input timing ("value") with per-kernel events ------------------------------------
     run_resident(0, args.warmup)
     sync_all()

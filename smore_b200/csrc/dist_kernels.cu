@@ -284,12 +284,18 @@ __device__ __forceinline__ void add4(float4& a, const float4& b) {
 // own the 16-byte columns of a row and `groups` such thread groups take alternate rows of the
 // CTA's block.  A thread keeps only its column of the query and of the query gradient in
 // registers (a handful of registers: high occupancy), has U row loads in flight, and writes its
-// column of each row gradient.  Per-row scalars (row id, output gradients, destination slot) are
-// fetched 32 rows at a time by the lanes of each warp and handed out by shuffles.
+// column of each row gradient.  Per-row scalars (row offset, output gradients, destination) are
+// fetched 32 rows at a time by the lanes of each warp into a warp-private shared-memory table, so
+// the inner loop is one broadcast read, one add and one 16-byte access per operand: the kernel
+// has to stay well under the SM's issue rate to be bound by HBM instead.
 template <class Term, int U>
 __global__ void __launch_bounds__(kRowCtaThreads)
     col_backward_kernel(RowArgs a, RowGradArgs ga, int tpr, int groups) {
   extern __shared__ float4 red[];  // [groups][kNQ][dim4]
+  __shared__ size_t meta_src[kRowCtaWarps][32];
+  __shared__ long long meta_dst[kRowCtaWarps][32];
+  __shared__ float2 meta_g[kRowCtaWarps][32];
+  __shared__ int meta_single[kRowCtaWarps][32];
   const int lane = threadIdx.x & 31;
   const int grp = threadIdx.x / tpr, col = threadIdx.x - grp * tpr;
   const int b = blockIdx.x / a.chunks, c = blockIdx.x - b * a.chunks;
@@ -311,54 +317,59 @@ __global__ void __launch_bounds__(kRowCtaThreads)
   if (grp < groups) {
     // this group's rows: r_begin + grp + groups * t, t = 0, 1, ...
     const int n_mine = (r_end - r_begin - grp + groups - 1) / groups;
+    const int warp = threadIdx.x >> 5;
     for (int t0 = 0; t0 < n_mine; t0 += 32) {
       const int n = min(32, n_mine - t0);
-      long long myrow = 0, mydst = -1;
-      int mysingle = 1;
-      float g0 = 0.f, g1 = 0.f;
-      if (lane < n) {
-        const size_t pos = (size_t)b * a.K + r_begin + grp + (size_t)groups * (t0 + lane);
-        myrow = a.idx ? (long long)a.idx[pos] : (long long)pos;
-        g0 = ga.gout0[pos];
-        if (Term::kNOut == 2) g1 = ga.gout1[pos];
+      // Each warp keeps its own copy of the next 32 rows' scalars in shared memory: where the row
+      // starts, where its gradient goes (in 16-byte units, so the inner loop only adds its column),
+      // the output gradients, and whether the destination is stored or accumulated.
+      __syncwarp();
+      {
+        const int l = lane < n ? lane : 0;   // surplus lanes repeat the tile's first row: harmless loads
+        const size_t pos = (size_t)b * a.K + r_begin + grp + (size_t)groups * (t0 + l);
+        const size_t row = a.idx ? (size_t)a.idx[pos] : pos;
+        long long dst = (long long)pos;
+        int single = 1;
         if (ga.slot) {
           const int32_t s = ga.slot[pos];
-          mydst = s;
-          mysingle = (s >= 0 && ga.slot_count != nullptr) ? (ga.slot_count[s] == 1) : 0;
-        } else {
-          mydst = (long long)pos;
+          dst = s;
+          single = (s >= 0 && ga.slot_count != nullptr) ? (ga.slot_count[s] == 1) : 0;
         }
+        meta_src[warp][lane] = row * w4;
+        meta_dst[warp][lane] = dst < 0 ? -1 : dst * (long long)w4;
+        meta_g[warp][lane] = make_float2(ga.gout0[pos], Term::kNOut == 2 ? ga.gout1[pos] : 0.f);
+        meta_single[warp][lane] = single;
       }
+      __syncwarp();
       for (int t = 0; t < n; t += U) {
         float4 e0[U], e1[U];
+        if (active) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const long long row = __shfl_sync(0xffffffffu, myrow, min(t + u, n - 1));
-          if (active) {
-            const float4* pe = ent4 + (size_t)row * w4 + col;
+          for (int u = 0; u < U; ++u) {
+            const float4* pe = ent4 + meta_src[warp][t + u] + col;
             e0[u] = ld_row4(pe);
             if (Term::kMul == 2) e1[u] = ld_row4(pe + dim4);
           }
-        }
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int src = min(t + u, n - 1);
-          float g[Term::kNOut];
-          g[0] = __shfl_sync(0xffffffffu, g0, src);
-          if (Term::kNOut == 2) g[Term::kNOut - 1] = __shfl_sync(0xffffffffu, g1, src);
-          const long long dst = __shfl_sync(0xffffffffu, mydst, src);
-          const int single = __shfl_sync(0xffffffffu, mysingle, src);
-          if (t + u >= n || !active) continue;
-          float4 ge0 = z4, ge1 = z4;
-          bwd4<Term>(g, e0[u], Term::kMul == 2 ? e1[u] : e0[u], q0, q1, ge0, ge1, gq0, gq1);
-          if (dst >= 0) {
-            float4* out = gbase + (size_t)dst * w4 + col;
-            if (single) {
-              out[0] = ge0;
-              if (Term::kMul == 2) out[dim4] = ge1;
-            } else {
-              atomicAdd(out, ge0);
-              if (Term::kMul == 2) atomicAdd(out + dim4, ge1);
+          for (int u = 0; u < U; ++u) {
+            if (t + u < n) {
+              const float2 g2 = meta_g[warp][t + u];
+              const long long dst = meta_dst[warp][t + u];
+              float g[Term::kNOut];
+              g[0] = g2.x;
+              if (Term::kNOut == 2) g[Term::kNOut - 1] = g2.y;
+              float4 ge0 = z4, ge1 = z4;
+              bwd4<Term>(g, e0[u], Term::kMul == 2 ? e1[u] : e0[u], q0, q1, ge0, ge1, gq0, gq1);
+              if (dst >= 0) {
+                float4* out = gbase + dst + col;
+                if (meta_single[warp][t + u]) {
+                  out[0] = ge0;
+                  if (Term::kMul == 2) out[dim4] = ge1;
+                } else {
+                  atomicAdd(out, ge0);
+                  if (Term::kMul == 2) atomicAdd(out + dim4, ge1);
+                }
+              }
             }
           }
         }

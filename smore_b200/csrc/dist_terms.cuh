@@ -80,19 +80,16 @@ struct TermBoxBoth {
   }
   template <typename T>
   __device__ __forceinline__ static void bwd(const T* g, T e0, T, T c, T o, T& ge0, T&, T& gc, T& go) {
-    T a = t_abs(e0 - c);
-    T sgn = t_sign(e0 - c);
-    T de = T(0), dofs = T(0);
-    if (a - o >= T(0)) {
-      dofs -= g[0];
-      de += sgn * g[0];
-    }
-    T outer = t_sign(t_min(a, o)) * g[1];
-    if (a < o) {
-      de += sgn * outer;
-    } else {
-      dofs += outer;
-    }
+    // The two rules folded together.  For finite operands exactly one of "a < o" (the entity
+    // gradient comes from the in-box term) and "a - o >= 0" (it comes from the out-of-box term,
+    // and the in-box term feeds the offset) holds, so selects replace the branches.
+    const T diff = e0 - c;
+    const T a = t_abs(diff);
+    const T outer = t_min(a, o) > T(0) ? g[1] : -g[1];
+    const bool in_side = a < o;
+    const T w = in_side ? outer : g[0];
+    const T de = diff > T(0) ? w : -w;
+    const T dofs = in_side ? T(0) : outer - g[0];
     ge0 += de;
     gc -= de;
     go += dofs;

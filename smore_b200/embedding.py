@@ -353,10 +353,20 @@ class EmbeddingOptimizer(object):
         return self._ws
 
     # ---- per-step bookkeeping ----------------------------------------------------------------------
+    def _drop_plans(self):
+        """Forget the step's plans.  A plan and its lookups refer to each other; cutting the links
+        here lets the step's large buffers be released at once instead of at the next cycle
+        collection."""
+        for plan in getattr(self, "_plans", []):
+            for lk in plan.lookups:
+                lk.plan = None
+            plan.lookups = []
+        self._plans = []       # plans built in this step (normally one)
+
     def zero_grad(self):
         self.n_fwd = 0
         self._pending = []     # lookups registered since the last plan was built
-        self._plans = []       # plans built in this step (normally one)
+        self._drop_plans()
         self.grad_list = []    # kept for interface parity; gradients never queue up here
         self.has_grad_list = []
 
@@ -500,7 +510,7 @@ class EmbeddingOptimizer(object):
         else:
             _lib.note("n_unique", plan.n_unique[0])
             self._launch_update(uniq, plan.g_rows, plan.n_unique, plan.n, lr)
-        self._plans = []
+        self._drop_plans()
         self._pending = []
 
     def update_step(self, indices, inverse_indices, grad, lr):

@@ -294,7 +294,7 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
     def zero_grad(self):
         self.n_fwd = 0
         self._pending = []
-        self._plans = []
+        self._drop_plans()
         self.grad_list = []
         self.has_grad_list = []
         # no list of this rank is in use until a plan of this step fills it (owners read these
@@ -368,7 +368,7 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         self.barrier()              # every rank's id lists and gradient rows are complete
         self.owner_update(lr)
         self.barrier()              # every shard is updated; arenas may be overwritten
-        self._plans = []
+        self._drop_plans()
 
     def owner_update(self, lr):
         sh = self.shard
