@@ -213,6 +213,19 @@ SMORE_API int smore_sparse_update_rows(int opt_id, float* table, float* m, float
                              size_t width, double lr, double beta1, double beta2, double eps,
                              int64_t step, int squeeze, void* stream);
 
+/* The same update with the optimizer's step counter on the device, for hosts that replay a
+ * captured CUDA graph step after step (kernel arguments are frozen in a graph, the step is not).
+ * smore_adam_step_scalars increments *step (device int64) and writes the two step-dependent
+ * scalars {-lr / (1 - beta1^step), sqrt(1 - beta2^step)} to step_scalars (device float[2]);
+ * smore_sparse_update_rows_dev reads them instead of taking `step`.  Enqueue both on one stream,
+ * scalars first. */
+SMORE_API int smore_adam_step_scalars(int64_t* step, double lr, double beta1, double beta2, float* step_scalars,
+                            void* stream);
+SMORE_API int smore_sparse_update_rows_dev(int opt_id, float* table, float* m, float* v, const int64_t* uniq,
+                                 const float* g_rows, const int32_t* n_unique, size_t capacity,
+                                 size_t width, double lr, double beta1, double beta2, double eps,
+                                 const float* step_scalars, int squeeze, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Row-sharded table over the GPUs of one box (one process per GPU).
  * Replaces the reference's sharing of the table through CPU shared memory with pinned PCIe

@@ -184,6 +184,7 @@ __device__ __forceinline__ void add_row(float4 (&g)[NCH], const float4* row, int
 
 template <int NCH, bool ROWWISE>
 __global__ void __launch_bounds__(256) shard_reduce_update_kernel(UpdateArgs a, ReduceArgs r) {
+  load_dyn(a);
   const int lane = threadIdx.x & 31;
   const size_t nu = (size_t)max(a.n_unique[0], 0);
   const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);

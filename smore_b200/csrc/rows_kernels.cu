@@ -264,6 +264,7 @@ __global__ void __launch_bounds__(256)
 // the row-wise mean of its square is needed first.
 template <int NCH, bool ROWWISE>
 __global__ void __launch_bounds__(256) adam_rows_reg_kernel(UpdateArgs a) {
+  load_dyn(a);
   const int lane = threadIdx.x & 31;
   const size_t nu = (size_t)max(a.n_unique[0], 0);
   const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
@@ -325,6 +326,7 @@ __global__ void __launch_bounds__(256) adam_rows_reg_kernel(UpdateArgs a) {
 
 template <int OPT, bool VEC>
 __global__ void __launch_bounds__(256) sparse_update_rows_kernel(UpdateArgs a) {
+  load_dyn(a);
   const int lane = threadIdx.x & 31;
   const size_t nu = (size_t)max(a.n_unique[0], 0);
   const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
@@ -538,10 +540,57 @@ int smore_scatter_add_rows(const float* grad, const int32_t* slot, const int32_t
   return check_launch("scatter_add_rows_kernel");
 }
 
+}  // extern "C"
+
+namespace smore {
+// *step += 1; out = {-lr / (1 - beta1^step), sqrt(1 - beta2^step)} in double, narrowed once
+__global__ void adam_step_scalars_kernel(long long* step, double lr, double beta1, double beta2, float* out) {
+  const long long t = *step + 1;
+  *step = t;
+  out[0] = (float)(-lr / (1.0 - pow(beta1, (double)t)));
+  out[1] = (float)sqrt(1.0 - pow(beta2, (double)t));
+}
+}  // namespace smore
+
+static int update_rows_impl(int opt_id, float* table, float* m, float* v, const int64_t* uniq,
+                            const float* g_rows, const int32_t* n_unique, size_t capacity, size_t width,
+                            double lr, double beta1, double beta2, double eps, int64_t step,
+                            const float* step_scalars, int squeeze, void* stream);
+
+extern "C" {
+
+int smore_adam_step_scalars(int64_t* step, double lr, double beta1, double beta2, float* step_scalars,
+                            void* stream) {
+  if (!step || !step_scalars) return fail(SMORE_ERR_NULL, "adam_step_scalars: NULL pointer");
+  adam_step_scalars_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(reinterpret_cast<long long*>(step), lr, beta1, beta2,
+                                                               step_scalars);
+  return check_launch("adam_step_scalars_kernel");
+}
+
 int smore_sparse_update_rows(int opt_id, float* table, float* m, float* v, const int64_t* uniq,
                              const float* g_rows, const int32_t* n_unique, size_t capacity, size_t width,
                              double lr, double beta1, double beta2, double eps, int64_t step, int squeeze,
                              void* stream) {
+  if (opt_id == SMORE_OPT_ADAM && step < 1) return fail(SMORE_ERR_BAD_SHAPE, "adam step must be >= 1");
+  return update_rows_impl(opt_id, table, m, v, uniq, g_rows, n_unique, capacity, width, lr, beta1, beta2, eps,
+                          step < 1 ? 1 : step, nullptr, squeeze, stream);
+}
+
+int smore_sparse_update_rows_dev(int opt_id, float* table, float* m, float* v, const int64_t* uniq,
+                                 const float* g_rows, const int32_t* n_unique, size_t capacity, size_t width,
+                                 double lr, double beta1, double beta2, double eps, const float* step_scalars,
+                                 int squeeze, void* stream) {
+  if (!step_scalars) return fail(SMORE_ERR_NULL, "sparse_update_rows_dev: step_scalars is NULL");
+  return update_rows_impl(opt_id, table, m, v, uniq, g_rows, n_unique, capacity, width, lr, beta1, beta2, eps, 1,
+                          step_scalars, squeeze, stream);
+}
+
+}  // extern "C"
+
+static int update_rows_impl(int opt_id, float* table, float* m, float* v, const int64_t* uniq,
+                            const float* g_rows, const int32_t* n_unique, size_t capacity, size_t width,
+                            double lr, double beta1, double beta2, double eps, int64_t step,
+                            const float* step_scalars, int squeeze, void* stream) {
   if (opt_id < SMORE_OPT_SGD || opt_id > SMORE_OPT_ADAGRAD)
     return fail(SMORE_ERR_BAD_DIST, "unknown optimizer id %d", opt_id);
   if (capacity == 0) return SMORE_OK;
@@ -549,11 +598,11 @@ int smore_sparse_update_rows(int opt_id, float* table, float* m, float* v, const
   if (opt_id == SMORE_OPT_ADAM && (!m || !v)) return fail(SMORE_ERR_NULL, "adam needs m and v");
   if (opt_id == SMORE_OPT_ADAGRAD && !v) return fail(SMORE_ERR_NULL, "adagrad needs v");
   if (!width) return fail(SMORE_ERR_BAD_SHAPE, "sparse_update_rows: width is 0");
-  if (opt_id == SMORE_OPT_ADAM && step < 1) return fail(SMORE_ERR_BAD_SHAPE, "adam step must be >= 1");
   UpdateArgs a;
   a.table = table; a.m = m; a.v = v; a.uniq = uniq; a.g_rows = g_rows; a.n_unique = n_unique;
   a.width = width;
   set_hyper(a, lr, beta1, beta2, eps, step, squeeze);
+  a.dyn = step_scalars;
   cudaStream_t st = (cudaStream_t)stream;
   const bool vec = (width % 4 == 0) && aligned16(table) && aligned16(g_rows) && (!m || aligned16(m)) &&
                    (!v || squeeze || aligned16(v));
@@ -580,8 +629,6 @@ int smore_sparse_update_rows(int opt_id, float* table, float* m, float* v, const
 #undef LAUNCH
   return check_launch("sparse_update_rows_kernel");
 }
-
-}  // extern "C"
 
 // ----------------------------------------------------------------------------------------
 // smore_unique_rows_static: the same de-duplication with its scratch inside the library

@@ -20,6 +20,7 @@ struct UpdateArgs {
   size_t width;
   float lr, beta1, beta2, omb1, omb2, eps, step_size, sqrt_bc2;
   int squeeze;
+  const float* dyn;  // nullable: device [2] = {step_size, sqrt_bc2}, overrides the two fields above
 };
 
 // Hyper-parameters arrive as doubles (Python floats in the reference) and are narrowed once,
@@ -37,6 +38,17 @@ inline void set_hyper(UpdateArgs& a, double lr, double beta1, double beta2, doub
   a.step_size = (float)(-lr / bc1);
   a.sqrt_bc2 = (float)std::sqrt(bc2);
   a.squeeze = squeeze != 0;
+  a.dyn = nullptr;
+}
+
+// The two scalars that depend on the optimizer's step count may come from device memory (written
+// by adam_step_scalars_kernel from a step counter that lives on the device), so that a captured
+// CUDA graph can be replayed step after step.
+__device__ __forceinline__ void load_dyn(UpdateArgs& a) {
+  if (a.dyn != nullptr) {
+    a.step_size = a.dyn[0];
+    a.sqrt_bc2 = a.dyn[1];
+  }
 }
 
 __device__ __forceinline__ void adam_elem(float g, float& p, float& m, float& v, const UpdateArgs& a) {

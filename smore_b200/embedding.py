@@ -441,8 +441,32 @@ class EmbeddingOptimizer(object):
     def _launch_update(self, uniq, g_rows, n_unique, capacity, lr):
         raise NotImplementedError
 
+    def use_device_step(self):
+        """Keep the optimizer's step counter on the device from now on (it starts from the current
+        host-side value).  Needed when training steps are captured in a CUDA graph and replayed:
+        Python does not run during a replay, so the bias corrections must come from device memory."""
+        dev = self.table.device
+        self._step_dev = torch.tensor([int(self.step)], dtype=torch.int64, device=dev)
+        self._step_scalars = torch.zeros(2, dtype=torch.float32, device=dev)
+
+    def _advance_device_step(self, lr):
+        dev = self.table.device
+        with torch.cuda.device(dev):
+            _lib.check(_lib.lib().smore_adam_step_scalars(self._step_dev.data_ptr(), float(lr), 0.9, 0.999,
+                                                          self._step_scalars.data_ptr(), _stream_ptr(dev)),
+                       "smore_adam_step_scalars")
+
     def _run_update(self, opt_name, m, v, uniq, g_rows, n_unique, capacity, lr):
         dev = self.table.device
+        if getattr(self, "_step_dev", None) is not None:
+            self._advance_device_step(lr)
+            with torch.cuda.device(dev), _lib.timed("sparse_update_rows"):
+                _lib.check(_lib.lib().smore_sparse_update_rows_dev(
+                    _lib.OPT_IDS[opt_name], self.table.data_ptr(), None if m is None else m.data_ptr(),
+                    None if v is None else v.data_ptr(), uniq.data_ptr(), g_rows.data_ptr(), n_unique.data_ptr(),
+                    capacity, self.table.shape[1], float(lr), 0.9, 0.999, eps, self._step_scalars.data_ptr(),
+                    int(self.squeeze), _stream_ptr(dev)), "smore_sparse_update_rows_dev")
+            return
         with torch.cuda.device(dev), _lib.timed("sparse_update_rows"):
             _lib.check(_lib.lib().smore_sparse_update_rows(
                 _lib.OPT_IDS[opt_name], self.table.data_ptr(), None if m is None else m.data_ptr(),
@@ -494,6 +518,8 @@ class EmbeddingOptimizer(object):
         self.step += 1
         if not self._plans:
             self._pending = []
+            if getattr(self, "_step_dev", None) is not None:
+                self._advance_device_step(lr)
             return
         plan = self._plans[0] if len(self._plans) == 1 else self._merge_plans()
         uniq = plan.uniq

@@ -130,6 +130,32 @@ def test_row_optimizers_vs_reference_golden(golden, opt, squeeze):
             close(o.state("state_sum").cpu().numpy(), z[tag + "v_after%d" % step], RTOL, what="state")
 
 
+@pytest.mark.parametrize("squeeze", [False, True])
+def test_device_side_step_counter_matches_host_side(golden, squeeze):
+    """Adam with its step counter kept on the device (what a replayed CUDA graph needs) follows
+    the reference-generated tables exactly like the host-side counter does."""
+    from smore_b200 import embedding
+    z = golden["optimizer"]
+    tag = "opt/adam_%s/" % ("rowwise" if squeeze else "full")
+    emb = embedding.SparseEmbedding(*z["opt/table0"].shape)
+    emb.embedding.data.copy_(torch.from_numpy(z["opt/table0"]))
+    emb = emb.cuda()
+
+    class Args(object):
+        optim_mode = ("aggr", "adam", "gpu", squeeze, 0)
+        share_optim_stats = False
+
+    o = embedding.AdamEmbedOptimizer(Args(), emb, 0)
+    o.use_device_step()
+    lr = float(z["opt/lr"])
+    for step in range(3):
+        o.update_step(torch.from_numpy(z["opt/step%d/uniq" % step]), None,
+                      torch.from_numpy(z["opt/step%d/merged_grad" % step]), lr)
+        close(emb.embedding.data.cpu().numpy(), z[tag + "table_after%d" % step], RTOL, what="table")
+        close(o.state("state_sum_fo").cpu().numpy(), z[tag + "m_after%d" % step], RTOL, what="m")
+    assert int(o._step_dev.item()) == 3
+
+
 @pytest.mark.parametrize("opt,squeeze", [("adam", False), ("adam", True), ("adagrad", True)])
 def test_lookup_merge_update_through_optimizer_api(golden, oracle, opt, squeeze):
     """zero_grad -> three lookups -> backward -> apply_grad, as train_step_mp drives it
