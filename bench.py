@@ -75,6 +75,11 @@ WORKLOADS = {
                           gamma=24.0, cen=0.0, structures=["1p"], adv=1.0, lr=1e-4, squeeze=False, zipf_anchor=1.1),
     "q2b_fb15k": dict(geo="box", rows=14951, relations=1345, dim=400, B=1024, K=512, shared=True, gamma=12.0,
                       cen=0.02, structures=["1p", "2p", "3p", "2i"], adv=None, lr=1e-4, squeeze=False),
+    # dot-product scoring against shared negatives: the op and its gradients are GEMMs (tensor cores)
+    "distmult_wikikg": dict(geo="distmult", rows=2500604, relations=535, dim=1000, B=4096, K=8192, shared=True,
+                            gamma=0.0, cen=0.0, structures=["1p"], adv=None, lr=1e-4, squeeze=False, init_std=0.05),
+    "complex_wikikg": dict(geo="complex", rows=2500604, relations=535, dim=500, B=4096, K=8192, shared=True,
+                           gamma=0.0, cen=0.0, structures=["1p"], adv=None, lr=1e-4, squeeze=False, init_std=0.05),
     "gqe_fb15k237": dict(geo="vec", rows=14505, relations=237, dim=64, B=512, K=128, shared=False, gamma=12.0,
                          cen=0.0, structures=["1p"], adv=None, lr=1e-4, squeeze=False),
 }
@@ -170,7 +175,8 @@ class QueryModel(nn.Module):
         self.gamma, self.cen = cfg["gamma"], cfg.get("cen", 0.0)
         self.ops = ops
         self.world = world
-        width = self.dim * (2 if self.geo == "rotate" else 1)
+        two_part = self.geo in ("rotate", "complex")      # rows laid out [part0 | part1]
+        width = self.dim * (2 if two_part else 1)
         self.embedding_range = (self.gamma + 2.0) / self.dim
         r = self.embedding_range
         self.entity_embedding = embedding_mod.SparseEmbedding(0, width)
@@ -178,10 +184,16 @@ class QueryModel(nn.Module):
         lazy_names = ("negative_entity", "positive_entity") if lazy else ()
         if shard is None:
             table = torch.empty(n_rows, width, device=device)
-            table.uniform_(-r, r)
+            if cfg.get("init_std"):
+                table.normal_(0.0, cfg["init_std"])
+            else:
+                table.uniform_(-r, r)
             self.entity_embedding.embedding = nn.Parameter(table, requires_grad=False)
         R = cfg["relations"]
-        self.relation_embedding = nn.Parameter(torch.empty(R, self.dim, device=device).uniform_(-r, r))
+        rel_width = self.dim * (2 if self.geo == "complex" else 1)
+        rel = torch.empty(R, rel_width, device=device)
+        rel = rel.normal_(0.0, cfg["init_std"]) if cfg.get("init_std") else rel.uniform_(-r, r)
+        self.relation_embedding = nn.Parameter(rel)
         if self.geo == "box":
             self.offset_embedding = nn.Parameter(torch.empty(R, self.dim, device=device).uniform_(0, r))
             self.offset_net = OffsetIntersection(self.dim).to(device)
@@ -205,7 +217,7 @@ class QueryModel(nn.Module):
     # -- query embedding (kg_reasoning.py:217-250 with the per-model hooks) -----------------------
     def _retrieve(self, ids):
         e = self.entity_embedding(ids)
-        if self.geo == "rotate":
+        if self.geo in ("rotate", "complex"):
             re, im = torch.chunk(e, 2, dim=1)
             return [re.unsqueeze(1), im.unsqueeze(1)]
         if self.geo == "box":
@@ -221,6 +233,12 @@ class QueryModel(nn.Module):
             return [re * re_r - im * im_r, re * im_r + im * re_r]
         if self.geo == "box":
             return [emb[0] + rel, emb[1] + self.offset_embedding[rel_ids].unsqueeze(1)]
+        if self.geo == "complex":      # complex.py:108-117: multiply by the relation as a complex number
+            re_r, im_r = torch.chunk(rel, 2, dim=-1)
+            re, im = emb
+            return [re * re_r - im * im_r, re * im_r + im * re_r]
+        if self.geo == "distmult":     # distmult.py:106-111
+            return [emb[0] * rel]
         return [emb[0] + rel]
 
     def _intersect(self, branches):
@@ -228,7 +246,7 @@ class QueryModel(nn.Module):
             centers = torch.stack([b[0] for b in branches])
             offsets = torch.stack([b[1] for b in branches])
             return [self.center_net(centers), self.offset_net(offsets)]
-        if self.geo == "rotate":
+        if self.geo in ("rotate", "complex"):
             stacked = torch.stack([torch.cat(b, dim=-1) for b in branches])
             return list(torch.chunk(self.center_net(stacked), 2, dim=-1))
         return [self.center_net(torch.stack([b[0] for b in branches]))]
@@ -262,6 +280,10 @@ class QueryModel(nn.Module):
             logit = self.gamma - d1 - self.cen * d2
         elif self.geo == "rotate":
             logit = self.gamma - ops.rotate_dist(entity, query[0], query[1])
+        elif self.geo == "complex":
+            logit = ops.complex_sim(entity, query[0], query[1])
+        elif self.geo == "distmult":
+            logit = ops.distmult_sim(entity, query[0])
         else:
             logit = self.gamma - ops.l1_dist(entity, query[0])
         return torch.max(logit, dim=1)[0]
@@ -359,7 +381,7 @@ def cpu_reference_steps(cfg, steps, warmup, sample_queries=64, table_rows=100000
     from oracle import native_torch as nt
     torch.set_num_threads(os.cpu_count() or 1)
     geo, D, K = cfg["geo"], cfg["dim"], cfg["K"]
-    width = D * (2 if geo == "rotate" else 1)
+    width = D * (2 if geo in ("rotate", "complex") else 1)
     n_rows = min(table_rows, cfg["rows"] or table_rows)
     g = torch.Generator().manual_seed(0)
     r = (cfg["gamma"] + 2.0) / D
@@ -382,6 +404,12 @@ def cpu_reference_steps(cfg, steps, warmup, sample_queries=64, table_rows=100000
         elif geo == "rotate":
             q = (qparts[0], qparts[1])
             pl, nl = nt.rotate_logit(ent_pos, q, cfg["gamma"]), nt.rotate_logit(ent_neg, q, cfg["gamma"])
+        elif geo == "complex":
+            q = (qparts[0], qparts[1])
+            pl, nl = nt.complex_logit(ent_pos, q), nt.complex_logit(ent_neg, q)
+        elif geo == "distmult":
+            q = (qparts[0],)
+            pl, nl = nt.distmult_logit(ent_pos, q), nt.distmult_logit(ent_neg, q)
         else:
             q = (qparts[0],)
             pl, nl = nt.vec_logit(ent_pos, q, cfg["gamma"]), nt.vec_logit(ent_neg, q, cfg["gamma"])
@@ -410,7 +438,7 @@ NCU_TRAFFIC_BYTES = {"rows_forward": None, "rows_backward": None, "sparse_update
 def algorithmic_bytes(cfg, n_unique_mean):
     """Bytes each kernel has to move per launch (per union branch for the two distance kernels)."""
     B, K, D = cfg["B"], cfg["K"], cfg["dim"]
-    W = D * (2 if cfg["geo"] == "rotate" else 1)
+    W = D * (2 if cfg["geo"] in ("rotate", "complex") else 1)
     nq = 1 if cfg["geo"] == "vec" else 2
     nout = 2 if cfg["geo"] == "box" else 1
     pairs = B * K
@@ -422,6 +450,13 @@ def algorithmic_bytes(cfg, n_unique_mean):
     # peer read); the fetch copies every distinct row once (read + write)
     return {"rows_forward": fwd, "rows_backward": bwd, "sparse_update_rows": upd, "shard_reduce_update": upd,
             "fetch_rows": n_unique_mean * 8 * W}
+
+
+def algorithmic_flops(cfg):
+    """Useful floating-point operations per launch of the shared-candidate GEMM kernels."""
+    B, K, D = cfg["B"], cfg["K"], cfg["dim"]
+    W = D * (2 if cfg["geo"] in ("rotate", "complex") else 1)
+    return {"dot_forward": 2.0 * B * K * W, "dot_backward": 4.0 * B * K * W}
 
 
 def load_peaks():
@@ -458,7 +493,7 @@ def run_gpu(args):
         # table + Adam state row-sharded over the ranks; rows and row gradients move over NVLink
         from smore_b200 import sharded
         B, K = cfg["B"], cfg["K"]
-        width = cfg["dim"] * (2 if cfg["geo"] == "rotate" else 1)
+        width = cfg["dim"] * (2 if cfg["geo"] in ("rotate", "complex") else 1)
         caps = ((K if cfg["shared"] else B * K) + 2 * B, B, B)
         shard = sharded.ShardGroup.from_process_group(n_rows, width, caps, squeeze=cfg["squeeze"], device=device)
         r = (cfg["gamma"] + 2.0) / cfg["dim"]
@@ -597,6 +632,7 @@ def run_gpu(args):
     nus = [int(t.item()) for t in timer.notes.get("n_unique", []) + timer.notes.get("n_unique_owner", [])]
     n_unique_mean = sum(nus) / len(nus) if nus else cfg["B"] * cfg["K"]
     alg = algorithmic_bytes(cfg, n_unique_mean=n_unique_mean)
+    flops = algorithmic_flops(cfg)
     kernels = {}
     for name, ms_list in kernel_ms.items():
         if not ms_list:
@@ -607,6 +643,8 @@ def run_gpu(args):
             gbs = alg[name] / (avg * 1e-3) / 1e9
             entry.update({"algorithmic_bytes": int(alg[name]), "achieved_gbs": round(gbs, 1),
                           "frac_of_%s_peak" % peak_kind: round(gbs / peak, 4)})
+        if name in flops:
+            entry.update({"algorithmic_flops": flops[name], "achieved_tflops": round(flops[name] / (avg * 1e-3) / 1e12, 1)})
         kernels[name] = entry
     dom = max((k for k in kernels if k in alg), key=lambda k: kernels[k]["total_ms"], default=None)
     roofline = None

@@ -227,6 +227,34 @@ SMORE_API int smore_sparse_update_rows_dev(int opt_id, float* table, float* m, f
                                  const float* step_scalars, int squeeze, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Dot-product scoring of B queries against ONE shared set of K candidate rows on the tensor
+ * cores (tcgen05 / TMEM through CUTLASS sm100 templates).  DistMult and ComplEx scores are inner
+ * products (dist_kernel.h:187-204, 324-349); with shared candidates the op and both gradients are
+ * dense GEMMs — what complex.py:186 does with torch.mm:
+ *     dst[B, K]     = query[B, W] . cand[K, W]^T
+ *     g_query[B, W] = gout[B, K]  . cand[K, W]
+ *     g_cand[K, W]  = gout[B, K]^T . query[B, W]
+ * W = dim for DistMult; 2*dim for ComplEx with the query given as [re | im], like the rows.
+ * B, K and W must be multiples of 4 (16-byte TMA strides), else SMORE_ERR_BAD_SHAPE and the
+ * caller falls back to smore_dist_forward / _backward (SIMT, exact fp32 order).
+ * precision: SMORE_DOT_TF32 — products of 10-bit-mantissa inputs, fp32 accumulation (error about
+ * 1e-3 of sum |terms|); SMORE_DOT_FP32 — each operand split into three bf16 terms, nine MMAs per
+ * product, fp32-level accuracy at a third of the rate.
+ * workspace: device scratch of smore_dot_workspace_bytes(...) bytes.  smore_dot_available() is 0
+ * when the library was built without a CUTLASS header tree.
+ * ------------------------------------------------------------------------------------------ */
+#define SMORE_DOT_TF32 0
+#define SMORE_DOT_FP32 1
+SMORE_API int smore_dot_available(void);
+SMORE_API size_t smore_dot_workspace_bytes(size_t B, size_t K, size_t W, int precision);
+SMORE_API int smore_dot_forward_shared(const float* cand, const float* query, float* dst, size_t B, size_t K,
+                             size_t W, int precision, void* workspace, size_t workspace_bytes,
+                             void* stream);
+SMORE_API int smore_dot_backward_shared(const float* gout, const float* cand, const float* query, float* g_cand,
+                              float* g_query, size_t B, size_t K, size_t W, int precision,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Row-sharded table over the GPUs of one box (one process per GPU).
  * Replaces the reference's sharing of the table through CPU shared memory with pinned PCIe
  * staging (embed_rw.py:53-134, extlib_cuda.cpp:82-144, kg_reasoning.py:144-147): rows

@@ -24,35 +24,81 @@ def sources():
     return sorted(glob.glob(os.path.join(HERE, "*.cu")))
 
 
-def _stale():
-    if not os.path.exists(LIB_PATH):
+def cutlass_include_dirs():
+    """Include directories of a CUTLASS 3.x/4.x header tree with sm100 support, or None.  Looked
+    for in $CUTLASS_HOME and in the header trees that ship inside installed Python packages."""
+    import sysconfig
+    roots = []
+    if os.environ.get("CUTLASS_HOME"):
+        roots.append(os.environ["CUTLASS_HOME"])
+    for key in ("purelib", "platlib"):
+        site = sysconfig.get_paths().get(key)
+        if site:
+            roots.append(os.path.join(site, "flashinfer", "data", "cutlass"))
+    for r in roots:
+        if os.path.isfile(os.path.join(r, "include", "cute", "arch", "mma_sm100_umma.hpp")):
+            dirs = [os.path.join(r, "include")]
+            util = os.path.join(r, "tools", "util", "include")
+            if os.path.isdir(util):
+                dirs.append(util)
+            return dirs
+    return None
+
+
+def _local_deps(src):
+    """The source plus the local headers it includes (one level is enough here)."""
+    deps = [src]
+    for line in open(src):
+        line = line.strip()
+        if line.startswith('#include "'):
+            name = line.split('"')[1]
+            for d in (HERE, os.path.join(ROOT, "include")):
+                if os.path.exists(os.path.join(d, name)):
+                    deps.append(os.path.join(d, name))
+    for h in list(deps[1:]):
+        if h.endswith(".cuh"):
+            for line in open(h):
+                if line.strip().startswith('#include "'):
+                    name = line.split('"')[1]
+                    if os.path.exists(os.path.join(HERE, name)):
+                        deps.append(os.path.join(HERE, name))
+    return deps
+
+
+def _newer(target, deps):
+    if not os.path.exists(target):
         return True
-    t = os.path.getmtime(LIB_PATH)
-    deps = sources() + glob.glob(os.path.join(HERE, "*.cuh")) + glob.glob(os.path.join(ROOT, "include", "*.h"))
+    t = os.path.getmtime(target)
     return any(os.path.getmtime(d) > t for d in deps)
 
 
 def build(force=False, verbose=False):
-    if not force and not _stale():
-        return LIB_PATH
     nvcc = os.path.join(CUDA_HOME, "bin", "nvcc")
     obj_dir = os.path.join(HERE, "_obj")
     os.makedirs(obj_dir, exist_ok=True)
-    procs = []
-    objs = []
+    cutlass = cutlass_include_dirs()
+    procs, objs = [], []
     for src in sources():
         obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
-        cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + \
+        if not force and not _newer(obj, _local_deps(src) + [os.path.abspath(__file__)]):
+            continue
+        extra = []
+        if os.path.basename(src) == "gemm_sm100.cu" and cutlass:
+            extra = ["-DSMORE_HAVE_CUTLASS", "--expt-extended-lambda"]
+            for d in cutlass:
+                extra += ["-I", d]
+        cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + \
               ["-I", os.path.join(ROOT, "include"), "-I", HERE, "-c", src, "-o", obj]
         print("+", " ".join(cmd), flush=True)
         procs.append((src, subprocess.Popen(cmd)))
     for src, p in procs:
         if p.wait() != 0:
             raise RuntimeError("nvcc failed on " + src)
-    cmd = [nvcc, "-shared", "-o", LIB_PATH] + objs
-    print("+", " ".join(cmd), flush=True)
-    subprocess.check_call(cmd)
+    if procs or force or _newer(LIB_PATH, objs):
+        cmd = [nvcc, "-shared", "-o", LIB_PATH] + objs
+        print("+", " ".join(cmd), flush=True)
+        subprocess.check_call(cmd)
     return LIB_PATH
 
 

@@ -198,7 +198,81 @@ class _RowsDistFunc(torch.autograd.Function):
         return None, None, None, g_first, g_second
 
 
+_DOT_PRECISIONS = {"tf32": 0, "fp32": 1}
+
+
+def dot_precision():
+    """How shared-candidate inner products are computed: 'fp32' (tensor cores, every fp32 operand
+    split into three bf16 terms: fp32-level accuracy, the default), 'tf32' (tensor cores, 10-bit
+    mantissa products) or 'off' (SIMT kernels in exact fp32).  Environment: SMORE_B200_DOT."""
+    import os
+    mode = os.environ.get("SMORE_B200_DOT", "fp32").lower()
+    if mode not in ("fp32", "tf32", "off"):
+        raise ValueError("SMORE_B200_DOT must be fp32, tf32 or off")
+    return mode
+
+
+class _DotSharedFunc(torch.autograd.Function):
+    """score[B, K] = query[B, W] . cand[K, W]^T and its two gradients as tensor-core GEMMs."""
+
+    @staticmethod
+    def forward(ctx, cand, query, precision):
+        cand, query = cand.contiguous(), query.contiguous()
+        K, W = cand.shape[-2], cand.shape[-1]
+        B = query.shape[0]
+        L = _lib.lib()
+        dst = torch.empty(B, K, dtype=torch.float32, device=cand.device)
+        ws = torch.empty(L.smore_dot_workspace_bytes(B, K, W, precision), dtype=torch.uint8, device=cand.device)
+        with torch.cuda.device(cand.device), _lib.timed("dot_forward"):
+            _lib.check(L.smore_dot_forward_shared(cand.data_ptr(), query.data_ptr(), dst.data_ptr(), B, K, W, precision,
+                                                  ws.data_ptr(), ws.numel(),
+                                                  torch.cuda.current_stream(cand.device).cuda_stream),
+                       "smore_dot_forward_shared")
+        ctx.save_for_backward(cand, query)
+        ctx.precision = precision
+        return dst
+
+    @staticmethod
+    def backward(ctx, gout):
+        cand, query = ctx.saved_tensors
+        gout = gout.contiguous()
+        K, W = cand.shape[-2], cand.shape[-1]
+        B = query.shape[0]
+        L = _lib.lib()
+        g_cand, g_query = torch.empty_like(cand), torch.empty_like(query)
+        ws = torch.empty(L.smore_dot_workspace_bytes(B, K, W, ctx.precision), dtype=torch.uint8, device=cand.device)
+        with torch.cuda.device(cand.device), _lib.timed("dot_backward"):
+            _lib.check(L.smore_dot_backward_shared(gout.data_ptr(), cand.data_ptr(), query.data_ptr(), g_cand.data_ptr(),
+                                                   g_query.data_ptr(), B, K, W, ctx.precision, ws.data_ptr(), ws.numel(),
+                                                   torch.cuda.current_stream(cand.device).cuda_stream),
+                       "smore_dot_backward_shared")
+        return g_cand, g_query, None
+
+
+def _dot_shared(name, entity, first, second):
+    """The GEMM route for DistMult / ComplEx against shared candidates, or None if it does not apply."""
+    if name not in ("distmult", "complex") or first.dim() != 3:
+        return None
+    mode = dot_precision()
+    if mode == "off" or not _lib.lib().smore_dot_available():
+        return None
+    eshape = entity.as_3d() if isinstance(entity, LazyRows) else tuple(entity.shape)
+    B, nc, dim = first.shape
+    K, W = eshape[1], eshape[2]
+    if eshape[0] != 1 or nc != 1 or B < 128 or K < 128 or (B | K | W) & 3 or first.dtype != torch.float32:
+        return None
+    if W != _lib.ROW_PARTS[name] * dim or not first.is_cuda:
+        return None
+    if isinstance(entity, LazyRows):
+        entity = entity.materialize()          # K rows only: the gathered copy is small here
+    query = first if second is None else torch.cat([first, second], dim=-1)
+    return _DotSharedFunc.apply(entity.reshape(K, W), query.reshape(B, W), _DOT_PRECISIONS[mode])
+
+
 def _apply(name, entity, first, second):
+    routed = _dot_shared(name, entity, first, second)
+    if routed is not None:
+        return routed
     if isinstance(entity, LazyRows):
         return _RowsDistFunc.apply(name, entity, entity.owner.dummy_tensor, first, second)
     if name == "box_both":
