@@ -430,9 +430,20 @@ def cpu_reference_steps(cfg, steps, warmup, sample_queries=64, table_rows=100000
 # the GPU arm
 # ------------------------------------------------------------------------------------------------
 
-# DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) for the
-# kernels below at the default workload; None until a capture exists (see profiles/).
-NCU_TRAFFIC_BYTES = {"rows_forward": None, "rows_backward": None, "sparse_update_rows": None}
+# DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the
+# 2M-row capture of the Query2box workload (profiles/q2b_box_step_2M_rows_ncu.md), scaled to a
+# full-size launch by the units processed: the two distance kernels process B*K rows per launch at
+# every table size; the update kernel moves 8070 bytes per distinct row.  Other workloads: None.
+NCU_TRAFFIC_BYTES = {"rows_forward": 1.722e9, "rows_backward": 4.094e9}
+NCU_UPDATE_BYTES_PER_ROW = 8070.0
+
+
+def ncu_traffic(workload, kernel, n_unique_mean):
+    if workload != "freebase_q2b":
+        return None
+    if kernel in ("sparse_update_rows", "shard_reduce_update"):
+        return round(NCU_UPDATE_BYTES_PER_ROW * n_unique_mean)
+    return NCU_TRAFFIC_BYTES.get(kernel)
 
 
 def algorithmic_bytes(cfg, n_unique_mean):
@@ -671,7 +682,7 @@ def run_gpu(args):
     elif dom:
         roofline = {"kernel": dom, "bound": "hbm", "achieved": kernels[dom]["achieved_gbs"], "peak": peak,
                     "peak_source": peak_kind, "unit": "GB/s", "frac": round(kernels[dom]["achieved_gbs"] / peak, 4),
-                    "traffic": NCU_TRAFFIC_BYTES.get(dom), "timing": timing_note}
+                    "traffic": ncu_traffic(args.workload, dom, n_unique_mean), "timing": timing_note}
 
     cpu = None
     if not args.no_cpu_baseline:
