@@ -580,13 +580,30 @@ def run_gpu(args):
         for i in range(k0, k0 + k):
             step(*dev_batches[i % pool])
 
+    copy_stream = torch.cuda.Stream(device)
+
+    def upload(i):
+        """Start the host -> device copy of batch i's index tensors (pinned memory) on the copy
+        stream; the previous step's compute overlaps it, as the sampler's prefetch thread would."""
+        s, p, n, q = host_batches[i % pool]
+        with torch.cuda.stream(copy_stream):
+            dev = [t.to(device, non_blocking=True) for t in (p, n, q)]
+            done = torch.cuda.Event()
+            done.record(copy_stream)
+        return s, dev, done
+
     def run_e2e(k0, k):
         last = 0.0
+        main = torch.cuda.current_stream(device)
+        nxt = upload(k0)
         for i in range(k0, k0 + k):
-            s, p, n, q = host_batches[i % pool]
-            if not use_graphs:
-                p, n, q = (t.to(device, non_blocking=True) for t in (p, n, q))
-            last = step(s, p, n, q).item()   # pinned host -> device copies in, the step's loss out
+            s, dev, done = nxt
+            if i + 1 < k0 + k:
+                nxt = upload(i + 1)
+            main.wait_event(done)
+            for t in dev:
+                t.record_stream(main)
+            last = step(s, *dev).item()   # the step's loss is read back by the host every step
         return last
 
     # keep Python's cycle collector from scanning the long-lived model objects inside a timed region
