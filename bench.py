@@ -311,11 +311,20 @@ def sampling_loss(pos_logit, neg_logit, adv, world_size=1):
     return (-pos_score.mean() - neg_score.mean()) / 2 / world_size
 
 
-def train_step(model, pos, neg, queries, structure, reduce_dense=None):
+def first_lookup_group(pos, neg, queries):
+    """The id tensors a step looks up before it first needs rows: positives, negatives, first anchors."""
+    return [pos, neg.view(-1), queries[:, 0]]
+
+
+def train_step(model, pos, neg, queries, structure, reduce_dense=None, upcoming=None):
     """train_process.py:172-227 on device-resident index tensors.  `reduce_dense(tensor)` sums a
-    dense parameter's gradient over the ranks (train_process.py:221-225) when there are several."""
+    dense parameter's gradient over the ranks (train_process.py:221-225) when there are several.
+    `upcoming` = (pos, neg, queries, event or None) of the NEXT step, whose rows a sharded table
+    starts pulling now (the role of the reference's asynchronous embedding read, embedding.py:98-121)."""
     model.dense_opt.zero_grad(set_to_none=True)
     model.embed_opt.zero_grad()
+    if upcoming is not None:
+        model.embed_opt.prefetch(first_lookup_group(*upcoming[:3]), after=upcoming[3])
     pos_logit, neg_logit = model(pos, neg, queries, structure)
     loss = sampling_loss(pos_logit, neg_logit, model.cfg["adv"], model.world)
     loss.backward()
@@ -542,8 +551,10 @@ def run_gpu(args):
 
     L = _lib.lib()
 
-    def eager_step(s, p, n, q):
-        return train_step(model, p, n, q, s, reduce_dense)
+    prefetching = world > 1 and not args.no_prefetch
+
+    def eager_step(s, p, n, q, upcoming=None):
+        return train_step(model, p, n, q, s, reduce_dense, upcoming if prefetching else None)
 
     # untimed set-up: one eager step of every query structure (allocator blocks, optimizer state)
     for i in range(len(structures)):
@@ -566,9 +577,9 @@ def run_gpu(args):
             graphs[s] = (g, static, loss)
         sync_all()
 
-    def step(s, p, n, q):
+    def step(s, p, n, q, upcoming=None):
         if not use_graphs:
-            return eager_step(s, p, n, q)
+            return eager_step(s, p, n, q, upcoming)
         g, static, loss = graphs[s]
         static[0].copy_(p, non_blocking=True)
         static[1].copy_(n, non_blocking=True)
@@ -578,7 +589,7 @@ def run_gpu(args):
 
     def run_resident(k0, k):
         for i in range(k0, k0 + k):
-            step(*dev_batches[i % pool])
+            step(*dev_batches[i % pool], upcoming=dev_batches[(i + 1) % pool][1:] + (None,))
 
     copy_stream = torch.cuda.Stream(device)
 
@@ -598,12 +609,14 @@ def run_gpu(args):
         nxt = upload(k0)
         for i in range(k0, k0 + k):
             s, dev, done = nxt
+            upcoming = None
             if i + 1 < k0 + k:
                 nxt = upload(i + 1)
+                upcoming = tuple(nxt[1]) + (nxt[2],)
             main.wait_event(done)
             for t in dev:
                 t.record_stream(main)
-            last = step(s, *dev).item()   # the step's loss is read back by the host every step
+            last = step(s, *dev, upcoming=upcoming).item()   # the loss is read back by the host every step
         return last
 
     # keep Python's cycle collector from scanning the long-lived model objects inside a timed region
@@ -649,7 +662,7 @@ def run_gpu(args):
     e4, e5 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e4.record()
     for i in range(args.warmup, args.warmup + args.steps):
-        eager_step(*dev_batches[i % pool])
+        eager_step(*dev_batches[i % pool], upcoming=dev_batches[(i + 1) % pool][1:] + (None,))
     e5.record()
     sync_all()
     _lib.set_timer(None)
@@ -787,6 +800,8 @@ def main():
     ap.add_argument("--no-lazy", action="store_true", help="gather candidate rows instead of reading the table in place")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graphs", action="store_true", help="launch every step eagerly instead of replaying CUDA graphs")
+    ap.add_argument("--no-prefetch", action="store_true",
+                    help="several GPUs: pull every step's rows after the previous update instead of during it")
     ap.add_argument("--cpu-steps", type=int, default=6)
     ap.add_argument("--dump-kernel-times", action="store_true", help="add every timed launch's duration to the JSON")
     args = ap.parse_args()

@@ -275,6 +275,19 @@ SMORE_API int smore_fetch_rows(const float* const* shard_ptrs, size_t rows_per_s
                      const int32_t* n_unique, size_t capacity, size_t width, float* staging,
                      void* stream);
 
+/* Prefetching: rows may be pulled for the NEXT step while the current step is still running
+ * (other stream), which hides the NVLink transfer behind the distance kernels.  Rows whose owner
+ * updates them afterwards would be stale, so owners publish the rows they updated in a step as a
+ * bitmap over their shard (smore_shard_mark_dirty: clears the bitmap, then sets one bit per row of
+ * uniq[0 .. *n_unique)), and the requester re-pulls exactly the marked rows after the step's last
+ * barrier (smore_refresh_rows; dirty_ptrs = device array of the ranks' bitmaps, peer-mapped).
+ * The result equals fetching everything after the barrier. */
+SMORE_API int smore_refresh_rows(const float* const* shard_ptrs, const uint32_t* const* dirty_ptrs,
+                       size_t rows_per_shard, const int64_t* uniq, const int32_t* n_unique,
+                       size_t capacity, size_t width, float* staging, void* stream);
+SMORE_API int smore_shard_mark_dirty(const int64_t* uniq, const int32_t* n_unique, size_t capacity,
+                           size_t shard_rows, uint32_t* dirty, void* stream);
+
 /* Owner side of the gradient return.  Every rank publishes up to n_plans (<= 4) sorted lists of
  * distinct global row ids per step with a gradient row per id; list (g, p) has room for
  * plan_caps[p] ids (host array, same on all ranks), its current length is the int32 that

@@ -112,6 +112,49 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// Rows that were pulled into `staging` BEFORE their owners finished the previous step's update may
+// be stale (or torn).  Owners publish the set of rows they updated as a bitmap over their shard;
+// this kernel re-pulls exactly those rows.  One warp per distinct row: a 4-byte peer read of the
+// bitmap word, then, for the ~10 % that are marked, the row copy.
+__global__ void __launch_bounds__(256)
+    refresh_rows_kernel(const float* const* __restrict__ shard_ptrs, const uint32_t* const* __restrict__ dirty_ptrs,
+                        size_t rows_per_shard, const int64_t* __restrict__ uniq,
+                        const int32_t* __restrict__ n_unique, int w4, float4* __restrict__ staging) {
+  const int lane = threadIdx.x & 31;
+  const size_t nu = (size_t)max(n_unique[0], 0);
+  const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
+  for (size_t u0 = ((size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 32; u0 < nu; u0 += warps * 32) {
+    // each lane tests one row of a 32-row batch, then the warp copies the marked ones together
+    bool marked = false;
+    size_t owner = 0, local = 0;
+    if (u0 + lane < nu) {
+      const size_t id = (size_t)uniq[u0 + lane];
+      owner = id / rows_per_shard;
+      local = id - owner * rows_per_shard;
+      marked = (dirty_ptrs[owner][local >> 5] >> (local & 31)) & 1u;
+    }
+    unsigned todo = __ballot_sync(0xffffffffu, marked);
+    while (todo) {
+      const int l = __ffs(todo) - 1;
+      todo &= todo - 1;
+      const size_t o = __shfl_sync(0xffffffffu, owner, l), r = __shfl_sync(0xffffffffu, local, l);
+      const float4* src = reinterpret_cast<const float4*>(shard_ptrs[o]) + r * (size_t)w4;
+      float4* dst = staging + (u0 + l) * (size_t)w4;
+      for (int d = lane; d < w4; d += kWarp) dst[d] = src[d];
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    shard_mark_dirty_kernel(const int64_t* __restrict__ uniq, const int32_t* __restrict__ n_unique,
+                            uint32_t* __restrict__ dirty) {
+  const size_t nu = (size_t)max(n_unique[0], 0);
+  for (size_t u = (size_t)blockIdx.x * blockDim.x + threadIdx.x; u < nu; u += (size_t)gridDim.x * blockDim.x) {
+    const int64_t row = uniq[u];
+    atomicOr(dirty + (row >> 5), 1u << (row & 31));
+  }
+}
+
 __global__ void __launch_bounds__(256)
     shard_collect_ids_kernel(const int64_t* const* __restrict__ uniq_ptrs,
                              const int32_t* const* __restrict__ nuniq_ptrs, PlanCaps c, int n_ranks,
@@ -302,6 +345,29 @@ int smore_fetch_rows(const float* const* shard_ptrs, size_t rows_per_shard, cons
   else
     fetch_rows_kernel<8, 2><<<grid_warps((capacity + 1) / 2), 256, 0, st>>>(shard_ptrs, rows_per_shard, uniq, n_unique, w4, out);
   return check_launch("fetch_rows_kernel");
+}
+
+int smore_refresh_rows(const float* const* shard_ptrs, const uint32_t* const* dirty_ptrs, size_t rows_per_shard,
+                       const int64_t* uniq, const int32_t* n_unique, size_t capacity, size_t width, float* staging,
+                       void* stream) {
+  if (capacity == 0) return SMORE_OK;
+  if (!shard_ptrs || !dirty_ptrs || !uniq || !n_unique || !staging)
+    return fail(SMORE_ERR_NULL, "refresh_rows: NULL pointer");
+  if (rows_per_shard == 0 || width == 0 || (width & 3) || !aligned16(staging))
+    return fail(SMORE_ERR_BAD_SHAPE, "refresh_rows: width must be a multiple of 4 floats; staging 16-byte aligned");
+  refresh_rows_kernel<<<grid_warps(capacity), 256, 0, (cudaStream_t)stream>>>(
+      shard_ptrs, dirty_ptrs, rows_per_shard, uniq, n_unique, (int)(width >> 2), reinterpret_cast<float4*>(staging));
+  return check_launch("refresh_rows_kernel");
+}
+
+int smore_shard_mark_dirty(const int64_t* uniq, const int32_t* n_unique, size_t capacity, size_t shard_rows,
+                           uint32_t* dirty, void* stream) {
+  if (!uniq || !n_unique || !dirty) return fail(SMORE_ERR_NULL, "shard_mark_dirty: NULL pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaMemsetAsync(dirty, 0, ((shard_rows + 31) / 32) * sizeof(uint32_t), st);
+  if (capacity)
+    shard_mark_dirty_kernel<<<grid_threads(capacity), 256, 0, st>>>(uniq, n_unique, dirty);
+  return check_launch("shard_mark_dirty_kernel", capacity ? 1 : 0);
 }
 
 int smore_shard_collect_ids(const int64_t* const* uniq_ptrs, const int32_t* const* nuniq_ptrs, size_t n_ranks,

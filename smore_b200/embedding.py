@@ -206,7 +206,7 @@ class LazyRows(object):
 
 
 class _Lookup(object):
-    __slots__ = ("idx", "n", "name", "order", "offset", "plan", "received")
+    __slots__ = ("idx", "n", "name", "order", "offset", "plan", "received", "key")
 
     def __init__(self, idx, name, order):
         self.idx = idx          # int64 [n] on the table's device
@@ -216,6 +216,7 @@ class _Lookup(object):
         self.offset = None      # position of this lookup in its plan's concatenated id list
         self.plan = None
         self.received = False   # a gradient producer has run for this lookup
+        self.key = None         # identity of the caller's id tensor (sharded tables with prefetch)
 
 
 class _StepPlan(object):

@@ -16,6 +16,10 @@ happens here over NVLink with plain peer loads, synchronously per step:
             ranks' lists, de-duplicates them, and one kernel pulls the matching gradient rows,
             sums them in a fixed order and applies Adam to the shard
             (smore_shard_reduce_update_rows); a second barrier ends the step.
+  prefetch  (optional) the rows of the NEXT step's first lookup group are pulled on a side stream
+            while the current step computes; after the step's last barrier only the rows their
+            owners updated meanwhile (published as a bitmap) are pulled again, so the result is
+            the same as fetching everything after the barrier.
 
 A step therefore equals one optimizer step of a single process on the union of all ranks'
 batches (all gradients of a row are summed before its one Adam update).
@@ -117,7 +121,9 @@ def exchange_handles(my_handles, group=None):
 
 
 class ShardedTable(object):
-    """The local shard (table + Adam state), the peer-visible arena, and the pointer tables."""
+    """The local shard (table + Adam state), two peer-visible per-step arenas (steps alternate
+    between them, so the next step's id list can be prepared while owners still read the current
+    one), the bitmap of rows updated in the last step, and the pointer tables."""
 
     def __init__(self, n_rows_total, width, rank, world, device, plan_caps, squeeze=True, symmetric=False):
         self.n_rows_total, self.width, self.rank, self.world = int(n_rows_total), int(width), rank, world
@@ -129,21 +135,25 @@ class ShardedTable(object):
         self.layout = ArenaLayout(plan_caps, width)
         self.symmetric = symmetric
         self._table_block = self._alloc(max(self.S, 1) * width * 4)
-        self._arena_block = self._alloc(self.layout.nbytes)
+        self._arena_blocks = [self._alloc(self.layout.nbytes) for _ in range(2)]
+        self._dirty_block = self._alloc(((max(self.S, 1) + 31) // 32) * 4)
         self.table = self._table_block.view(self.device, 0, (self.S, width), torch.float32)
+        self.dirty = self._dirty_block.view(self.device, 0, ((max(self.S, 1) + 31) // 32,), torch.int32)
+        self.dirty.zero_()
         self.m = torch.zeros(self.S, width, device=self.device)
         self.v = torch.zeros(self.S, 1, device=self.device) if squeeze else torch.zeros(self.S, width, device=self.device)
         lay = self.layout
-        self.nuniq = [self._arena_block.view(self.device, lay.nuniq_offset(p), (2,), torch.int32)
-                      for p in range(len(lay.plan_caps))]
-        self.nuniq_all = self._arena_block.view(self.device, 0, (MAX_PLANS * 2,), torch.int32)
-        self.nuniq_all.zero_()
-        self.ids = [self._arena_block.view(self.device, lay.ids_offset(p), (lay.plan_caps[p],), torch.int64)
-                    for p in range(len(lay.plan_caps))]
-        self.grads = [self._arena_block.view(self.device, lay.grads_offset(p), (lay.plan_caps[p], width), torch.float32)
-                      for p in range(len(lay.plan_caps))]
+        P = len(lay.plan_caps)
+        self.nuniq = [[blk.view(self.device, lay.nuniq_offset(p), (2,), torch.int32) for p in range(P)]
+                      for blk in self._arena_blocks]
+        self.nuniq_all = [blk.view(self.device, 0, (MAX_PLANS * 2,), torch.int32) for blk in self._arena_blocks]
+        for t in self.nuniq_all:
+            t.zero_()
+        self.ids = [[blk.view(self.device, lay.ids_offset(p), (lay.plan_caps[p],), torch.int64) for p in range(P)]
+                    for blk in self._arena_blocks]
+        self.grads = [[blk.view(self.device, lay.grads_offset(p), (lay.plan_caps[p], width), torch.float32)
+                       for p in range(P)] for blk in self._arena_blocks]
         self.peer_table_ptrs = None   # filled by connect()
-        self.peer_arena_ptrs = None
         self._handles = []
 
     def _alloc(self, nbytes):
@@ -158,31 +168,38 @@ class ShardedTable(object):
             t = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
         return _DeviceBlock(t)
 
-    def connect(self, table_ptrs, arena_ptrs):
-        """Install the base pointers of every rank's shard and arena (this rank's own included)."""
-        self.peer_table_ptrs, self.peer_arena_ptrs = list(table_ptrs), list(arena_ptrs)
-        tabs = pointer_tables(self.layout, self.peer_arena_ptrs)
+    def connect(self, table_ptrs, arena_ptrs, dirty_ptrs):
+        """Install the base pointers of every rank's shard, arenas (`arena_ptrs[parity][rank]`) and
+        updated-rows bitmap (this rank's own included)."""
+        self.peer_table_ptrs = list(table_ptrs)
         dev = self.device
         self.d_shard_ptrs = torch.tensor(self.peer_table_ptrs, dtype=torch.int64, device=dev)
-        self.d_uniq_ptrs = torch.tensor(tabs["ids"], dtype=torch.int64, device=dev)
-        self.d_nuniq_ptrs = torch.tensor(tabs["nuniq"], dtype=torch.int64, device=dev)
-        self.d_grad_ptrs = torch.tensor(tabs["grads"], dtype=torch.int64, device=dev)
+        self.d_dirty_ptrs = torch.tensor(list(dirty_ptrs), dtype=torch.int64, device=dev)
+        self.d_uniq_ptrs, self.d_nuniq_ptrs, self.d_grad_ptrs = [], [], []
+        for parity in range(2):
+            tabs = pointer_tables(self.layout, list(arena_ptrs[parity]))
+            self.d_uniq_ptrs.append(torch.tensor(tabs["ids"], dtype=torch.int64, device=dev))
+            self.d_nuniq_ptrs.append(torch.tensor(tabs["nuniq"], dtype=torch.int64, device=dev))
+            self.d_grad_ptrs.append(torch.tensor(tabs["grads"], dtype=torch.int64, device=dev))
 
     def connect_processes(self, group=None):
-        """Map the other ranks' shard and arena blocks (symmetric-memory rendezvous over `group`)."""
+        """Map the other ranks' blocks (symmetric-memory rendezvous over `group`)."""
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
         if not self.symmetric:
             raise _lib.SmoreError("connect_processes needs blocks from the symmetric-memory allocator")
         group = group if group is not None else dist.group.WORLD
+        blocks = [self._table_block] + self._arena_blocks + [self._dirty_block]
+        ptrs = []
         with torch.cuda.device(self.device):
-            ht = symm_mem.rendezvous(self._table_block.tensor, group)
-            ha = symm_mem.rendezvous(self._arena_block.tensor, group)
-        self._handles = [ht, ha]
-        table_ptrs, arena_ptrs = [int(p) for p in ht.buffer_ptrs], [int(p) for p in ha.buffer_ptrs]
-        if table_ptrs[self.rank] != self._table_block.ptr or arena_ptrs[self.rank] != self._arena_block.ptr:
-            raise _lib.SmoreError("symmetric-memory rendezvous returned a different address for the local block")
-        self.connect(table_ptrs, arena_ptrs)
+            for blk in blocks:
+                h = symm_mem.rendezvous(blk.tensor, group)
+                self._handles.append(h)
+                p = [int(x) for x in h.buffer_ptrs]
+                if p[self.rank] != blk.ptr:
+                    raise _lib.SmoreError("symmetric-memory rendezvous returned a different address for a local block")
+                ptrs.append(p)
+        self.connect(ptrs[0], [ptrs[1], ptrs[2]], ptrs[3])
 
     def close(self):
         self._handles = []
@@ -194,36 +211,60 @@ class ShardedTable(object):
         self.table.uniform_(lo, hi, generator=g)
 
 
+class _PlanBuffers(object):
+    """Persistent storage of one prefetched plan (ids, slots, counts, staged rows) at full capacity."""
+
+    def __init__(self, capacity, width, device):
+        self.idx = torch.empty(capacity, dtype=torch.int64, device=device)
+        self.slot = torch.empty(capacity, dtype=torch.int32, device=device)
+        self.counts = torch.empty(capacity, dtype=torch.int32, device=device)
+        self.slot64 = torch.empty(capacity, dtype=torch.int64, device=device)
+        self.staging = torch.empty(capacity, width, dtype=torch.float32, device=device)
+
+
+def _id_key(t):
+    """Identity of an id tensor as the caller holds it: address, element count, innermost stride."""
+    return (t.device, t.data_ptr(), t.numel(), t.stride()[-1] if t.dim() else 1, t.dtype)
+
+
 class _ShardedPlan(object):
     """One de-duplicated group of lookups of a rank: ids and gradients in the arena, rows staged."""
 
-    def __init__(self, opt, lookups, index):
+    def __init__(self, opt, id_tensors, index, parity, workspace, buffers=None):
+        """Runs on the current stream: unique over the ids, pull of the distinct rows.  `buffers`
+        (a _PlanBuffers) replaces the per-step allocations by persistent storage."""
         shard = opt.shard
         dev = shard.device
-        self.lookups, self.index = lookups, index
-        off = 0
-        for lk in lookups:
-            lk.offset, lk.plan = off, self
-            off += lk.n
-        self.n = off
+        self.index, self.parity = index, parity
+        self.lookups = []
+        self.n = sum(t.numel() for t in id_tensors)
         cap = shard.layout.plan_caps[index]
         if self.n > cap:
             raise _lib.SmoreError("plan %d holds %d looked-up ids, its capacity is %d (plan_caps)" % (index, self.n, cap))
-        self.idx_all = lookups[0].idx if len(lookups) == 1 else torch.cat([lk.idx for lk in lookups])
-        self.uniq = shard.ids[index]
-        self.n_unique = shard.nuniq[index]
-        self.g_rows = shard.grads[index]
-        self.slot = torch.empty(self.n, dtype=torch.int32, device=dev)
-        self.counts = torch.empty(self.n, dtype=torch.int32, device=dev)
-        self.staging = torch.empty(self.n, shard.width, dtype=torch.float32, device=dev)
+        self.uniq = shard.ids[parity][index]
+        self.n_unique = shard.nuniq[parity][index]
+        self.g_rows = shard.grads[parity][index]
+        if buffers is None:
+            self.idx_all = id_tensors[0] if len(id_tensors) == 1 else torch.cat(list(id_tensors))
+            self.slot = torch.empty(self.n, dtype=torch.int32, device=dev)
+            self.counts = torch.empty(self.n, dtype=torch.int32, device=dev)
+            self.staging = torch.empty(self.n, shard.width, dtype=torch.float32, device=dev)
+            self.slot64 = None
+        else:
+            self.idx_all = buffers.idx[:self.n]
+            off = 0
+            for t in id_tensors:
+                self.idx_all[off:off + t.numel()].copy_(t.reshape(-1))
+                off += t.numel()
+            self.slot, self.counts = buffers.slot[:self.n], buffers.counts[:self.n]
+            self.staging, self.slot64 = buffers.staging[:self.n], buffers.slot64[:self.n]
         L = _lib.lib()
-        ws = opt._unique_workspace()
         st = _stream_ptr(dev)
         with torch.cuda.device(dev):
             with _lib.timed("unique_rows"):
                 _lib.check(L.smore_unique_rows(self.idx_all.data_ptr(), self.n, shard.n_rows_total,
                                                self.uniq.data_ptr(), self.slot.data_ptr(), self.counts.data_ptr(),
-                                               self.n_unique.data_ptr(), ws.data_ptr(), ws.numel(), st),
+                                               self.n_unique.data_ptr(), workspace.data_ptr(), workspace.numel(), st),
                            "smore_unique_rows")
             with _lib.timed("fetch_rows"):
                 _lib.check(L.smore_fetch_rows(shard.d_shard_ptrs.data_ptr(), shard.S, self.uniq.data_ptr(),
@@ -232,7 +273,26 @@ class _ShardedPlan(object):
             _lib.check(L.smore_zero_shared_rows(self.g_rows.data_ptr(), self.counts.data_ptr(),
                                                 self.n_unique.data_ptr(), self.n, shard.width, st),
                        "smore_zero_shared_rows")
-        self.slot64 = self.slot.long()
+        if self.slot64 is None:
+            self.slot64 = self.slot.long()
+        else:
+            self.slot64.copy_(self.slot)
+
+    def adopt(self, lookups):
+        off = 0
+        for lk in lookups:
+            lk.offset, lk.plan = off, self
+            off += lk.n
+        self.lookups = list(lookups)
+
+    def refresh(self, opt):
+        """Pull again the rows whose owners updated them after (or while) they were fetched."""
+        shard = opt.shard
+        with torch.cuda.device(shard.device), _lib.timed("refresh_rows"):
+            _lib.check(_lib.lib().smore_refresh_rows(shard.d_shard_ptrs.data_ptr(), shard.d_dirty_ptrs.data_ptr(),
+                                                     shard.S, self.uniq.data_ptr(), self.n_unique.data_ptr(), self.n,
+                                                     shard.width, self.staging.data_ptr(),
+                                                     _stream_ptr(shard.device)), "smore_refresh_rows")
 
     def slot_of(self, lookup):
         return self.slot[lookup.offset:lookup.offset + lookup.n]
@@ -261,9 +321,16 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         self.training = True
         self.dummy_tensor = torch.nn.Parameter(torch.zeros(1, 1, device=shard.device))
         self.step = 0
+        self.parity = 0                   # arena of the step in progress
         self._ws = None
+        self._prefetch_ws = None
         self._owner_ws = None
+        self._prefetched = None           # (plan, done_event, id tensors) being prepared for the next step
+        self._ready = None                # the same, prepared during the previous step for this one
+        self._prefetch_stream = None
+        self._prefetch_buffers = [None, None]   # per arena; a buffer is reused two steps later
         self._group = group
+        self._plans = []
         if barrier is None:
             import torch.distributed as dist
             flag = torch.zeros(1, device=shard.device)
@@ -282,30 +349,74 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         self._o_counts = torch.empty(n_in, dtype=torch.int32, device=dev)
         self._o_src = torch.empty(n_in, dtype=torch.int32, device=dev)
         self._o_nuniq = torch.zeros(2, dtype=torch.int32, device=dev)
+        self._started = False
         self.zero_grad()
 
     # ---- lookups ----------------------------------------------------------------------------------
-    def _unique_workspace(self):
-        if self._ws is None:
+    def _workspace(self, which):
+        if getattr(self, which) is None:
             nbytes = _lib.lib().smore_unique_rows_workspace_bytes(self.shard.n_rows_total)
-            self._ws = torch.empty(nbytes, dtype=torch.uint8, device=self.shard.device)
-        return self._ws
+            setattr(self, which, torch.empty(nbytes, dtype=torch.uint8, device=self.shard.device))
+        return getattr(self, which)
 
     def zero_grad(self):
+        """Begins a step: the step uses the other arena than the previous one."""
         self.n_fwd = 0
         self._pending = []
         self._drop_plans()
         self.grad_list = []
         self.has_grad_list = []
-        # no list of this rank is in use until a plan of this step fills it (owners read these
-        # counters only after the step's first barrier)
-        self.shard.nuniq_all.zero_()
+        if self._started:
+            self.parity ^= 1
+        self._started = True
+        nu = self.shard.nuniq_all[self.parity]
+        self._ready, self._prefetched = self._prefetched, None
+        if self._ready is not None and self._ready[0].parity == self.parity:
+            # list 0 of this arena was already filled by the prefetch; the others start unused
+            torch.cuda.current_stream(self.shard.device).wait_event(self._ready[1])
+            nu[2:].zero_()
+        else:
+            # no list of this rank is in use until a plan of this step fills it (owners read these
+            # counters only after the step's first barrier)
+            self._ready = None
+            nu.zero_()
+
+    def prefetch(self, id_tensors, after=None):
+        """Prepare the NEXT step's first lookup group now, on a side stream: `id_tensors` are the
+        device id tensors that step will look up, in order, up to and including the first lookup
+        whose rows are needed (e.g. positives, negatives, first anchors).  Call it after this step's
+        zero_grad() and pass the same tensors, unchanged, to the lookups of the next step; a step
+        that looks up anything else simply ignores what was prepared.  `after` is an event that
+        marks the id tensors as written, if another stream than the current one produces them."""
+        dev = self.shard.device
+        if any(t.device != dev or t.dtype != torch.int64 for t in id_tensors):
+            raise _lib.SmoreError("prefetch takes int64 id tensors that already live on the shard's device")
+        if self._prefetch_stream is None:
+            self._prefetch_stream = torch.cuda.Stream(dev)
+        main = torch.cuda.current_stream(dev)
+        ready = torch.cuda.Event()
+        ready.record(main)                       # everything before this step (the last update) is done
+        side = self._prefetch_stream
+        side.wait_event(ready)
+        if after is not None:
+            side.wait_event(after)
+        target = self.parity ^ 1
+        if self._prefetch_buffers[target] is None:
+            self._prefetch_buffers[target] = _PlanBuffers(self.shard.layout.plan_caps[0], self.shard.width, dev)
+        with torch.cuda.stream(side):
+            plan = _ShardedPlan(self, id_tensors, 0, target, self._workspace("_prefetch_ws"),
+                                self._prefetch_buffers[target])
+            done = torch.cuda.Event()
+            done.record(side)
+        # the raw tensors stay referenced so that their addresses cannot be reused before the match
+        self._prefetched = (plan, done, [_id_key(t) for t in id_tensors], list(id_tensors))
 
     def forward(self, indices, name=None):
         if indices is None:
             raise _lib.SmoreError("a sharded table cannot be returned whole; rank it shard by shard")
         idx = self._device_indices(indices)
         lookup = _Lookup(idx, name, self.n_fwd)
+        lookup.key = _id_key(indices)
         self.n_fwd += 1
         self._pending.append(lookup)
         if name is not None and name in self.lazy_names:
@@ -325,12 +436,28 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
             idx = idx.to(self.shard.device, non_blocking=True)
         return idx.contiguous()
 
+    def _matches_prefetch(self, lookups):
+        if self._ready is None:
+            return False
+        keys = self._ready[2]
+        return len(keys) == len(lookups) and all(k == lk.key for k, lk in zip(keys, lookups))
+
     def plan_for(self, lookup):
         if lookup.plan is None:
             index = len(self._plans)
             if index >= len(self.shard.layout.plan_caps):
                 raise _lib.SmoreError("more than %d lookup groups in one step" % len(self.shard.layout.plan_caps))
-            self._plans.append(_ShardedPlan(self, self._pending, index))
+            if index == 0 and self._matches_prefetch(self._pending):
+                plan = self._ready[0]
+                plan.refresh(self)          # rows their owners updated since the prefetch began
+            else:
+                # (a step that does not look up what was prefetched rebuilds list 0 here)
+                plan = _ShardedPlan(self, [lk.idx for lk in self._pending], index, self.parity,
+                                    self._workspace("_ws"))
+            if index == 0:
+                self._ready = None
+            plan.adopt(self._pending)
+            self._plans.append(plan)
             self._pending = []
         return lookup.plan
 
@@ -367,7 +494,7 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         self._neutralise_unused_lookups()
         self.barrier()              # every rank's id lists and gradient rows are complete
         self.owner_update(lr)
-        self.barrier()              # every shard is updated; arenas may be overwritten
+        self.barrier()              # every shard is updated; this step's arena may be overwritten
         self._drop_plans()
 
     def owner_update(self, lr):
@@ -378,13 +505,14 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         st = _stream_ptr(dev)
         G, P = sh.world, len(lay.plan_caps)
         n_in = G * lay.span
+        par = self.parity
         if self._owner_ws is None:
             nbytes = L.smore_unique_rows_workspace_bytes(max(sh.S, 1))
             self._owner_ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         with torch.cuda.device(dev):
             with _lib.timed("shard_collect"):
-                _lib.check(L.smore_shard_collect_ids(sh.d_uniq_ptrs.data_ptr(), sh.d_nuniq_ptrs.data_ptr(), G, P,
-                                                     self._caps, sh.base, sh.S, self._in_ids.data_ptr(),
+                _lib.check(L.smore_shard_collect_ids(sh.d_uniq_ptrs[par].data_ptr(), sh.d_nuniq_ptrs[par].data_ptr(),
+                                                     G, P, self._caps, sh.base, sh.S, self._in_ids.data_ptr(),
                                                      self._in_bounds.data_ptr(), st), "smore_shard_collect_ids")
                 _lib.check(L.smore_unique_rows(self._in_ids.data_ptr(), n_in, max(sh.S, 1), self._o_uniq.data_ptr(),
                                                self._o_slot.data_ptr(), self._o_counts.data_ptr(),
@@ -392,13 +520,16 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
                                                self._owner_ws.numel(), st), "smore_unique_rows(owner)")
                 _lib.check(L.smore_shard_record_sources(self._o_slot.data_ptr(), n_in, self._o_src.data_ptr(), st),
                            "smore_shard_record_sources")
+                # publish which rows this step updates (readers: the next step's refresh on every rank)
+                _lib.check(L.smore_shard_mark_dirty(self._o_uniq.data_ptr(), self._o_nuniq.data_ptr(), n_in,
+                                                    max(sh.S, 1), sh.dirty.data_ptr(), st), "smore_shard_mark_dirty")
             _lib.note("n_unique_owner", self._o_nuniq[0])
             with _lib.timed("shard_reduce_update"):
                 _lib.check(L.smore_shard_reduce_update_rows(
                     sh.table.data_ptr(), sh.m.data_ptr(), sh.v.data_ptr(), self._o_uniq.data_ptr(),
                     self._o_counts.data_ptr(), self._o_src.data_ptr(), self._o_nuniq.data_ptr(), n_in,
-                    sh.d_grad_ptrs.data_ptr(), self._in_ids.data_ptr(), self._in_bounds.data_ptr(), G, P, self._caps,
-                    sh.width, float(lr), 0.9, 0.999, eps, int(self.step), int(self.squeeze), st),
+                    sh.d_grad_ptrs[par].data_ptr(), self._in_ids.data_ptr(), self._in_bounds.data_ptr(), G, P,
+                    self._caps, sh.width, float(lr), 0.9, 0.999, eps, int(self.step), int(self.squeeze), st),
                     "smore_shard_reduce_update_rows")
 
     def update_step(self, indices, inverse_indices, grad, lr):
@@ -422,7 +553,8 @@ class ShardGroup(object):
         """`world` shards in this process on one GPU, wired to each other by raw pointers."""
         shards = [ShardedTable(n_rows_total, width, r, world, device, plan_caps, squeeze) for r in range(world)]
         tables = [s._table_block.ptr for s in shards]
-        arenas = [s._arena_block.ptr for s in shards]
+        arenas = [[s._arena_blocks[par].ptr for s in shards] for par in range(2)]
+        dirty = [s._dirty_block.ptr for s in shards]
         for s in shards:
-            s.connect(tables, arenas)
+            s.connect(tables, arenas, dirty)
         return shards

@@ -190,3 +190,55 @@ def test_two_processes_over_nvlink_match_emulation(tmp_path):
             o_.apply_grad(1e-2)
     emu = torch.cat([s.table[:s.local_rows] for s in shards]).cpu()
     close(real.numpy(), emu.numpy(), RTOL_ATOMIC, what="two-process table")
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_prefetch_with_refresh_equals_fetch_after_the_update(world):
+    """Rows pulled for step s+1 while step s still runs, then repaired from the owners' updated-rows
+    bitmaps, give bit-identical tables, state and losses to pulling everything after the update."""
+    from smore_b200 import sharded
+    n_total, D, B, K = 1003, 64, 6, 50
+    caps = (B * K + 2 * B, B, B)
+    torch.manual_seed(0)
+    full = (torch.rand(n_total, D) - 0.5) * 0.2
+    steps = 5
+    batches = [[tuple(t.cuda() for t in _rank_batch(r, s, n_total, B, K, D)) for r in range(world)]
+               for s in range(steps)]
+
+    def first_group(batch):
+        neg, pos, anchors = batch[0], batch[1], batch[2]
+        return [pos, neg.view(-1), anchors[0]]
+
+    results = []
+    for use_prefetch in (False, True):
+        shards = sharded.ShardGroup.emulated(world, n_total, D, caps, squeeze=True)
+        for s in shards:
+            s.table.zero_()
+            s.table[:s.local_rows] = full[s.base:s.base + s.local_rows].cuda()
+        opts = [sharded.ShardedAdamOptimizer(s, barrier=lambda: None) for s in shards]
+        losses = []
+        for step in range(steps):
+            for r, o_ in enumerate(opts):
+                o_.zero_grad()
+                # step 3 deliberately looks up something else than what was prepared for it
+                if use_prefetch and step + 1 < steps:
+                    nxt = batches[step + 1][r] if step != 2 else batches[0][r]
+                    o_.prefetch(first_group(nxt))
+            if use_prefetch and step > 0 and step != 3:
+                assert all(o_._ready is not None for o_ in opts)
+            losses.append([_rank_forward_backward(opts[r].forward, batches[step][r], world)[0]
+                           for r in range(world)])
+            if use_prefetch:
+                assert all(o_._ready is None for o_ in opts)       # consumed or dropped
+            for o_ in opts:
+                o_.apply_grad(1e-2)
+        torch.cuda.synchronize()
+        results.append((losses, torch.cat([s.table[:s.local_rows] for s in shards]).cpu(),
+                        torch.cat([s.m[:s.local_rows] for s in shards]).cpu(),
+                        torch.cat([s.v[:s.local_rows] for s in shards]).cpu()))
+    (l0, t0, m0, v0), (l1, t1, m1, v1) = results
+    # the only non-deterministic part of a step is the order of atomic adds into shared rows
+    close(np.array(l1), np.array(l0), 1e-6, what="loss")
+    close(t1.numpy(), t0.numpy(), RTOL_ATOMIC, what="table")
+    close(m1.numpy(), m0.numpy(), RTOL_ATOMIC, what="m")
+    close(v1.numpy(), v0.numpy(), RTOL_ATOMIC, what="v")
