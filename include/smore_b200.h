@@ -54,7 +54,8 @@ enum smore_dist {
   SMORE_DIST_L2 = 4,       /* sum (e - c)^2  (no root)              dist_kernel.h:158-184 */
   SMORE_DIST_COMPLEX = 5,  /* sum e0*re + e1*im                     dist_kernel.h:187-204 */
   SMORE_DIST_DISTMULT = 6, /* sum e*c                               dist_kernel.h:324-349 */
-  SMORE_DIST_COUNT = 7
+  SMORE_DIST_COUNT = 7,
+  SMORE_DIST_BOX_BOTH = 7  /* box_out and box_in of the same operands; smore_union_* entry points only */
 };
 
 enum smore_opt {
@@ -142,6 +143,29 @@ SMORE_API int smore_box_backward(const float* gout_out, const float* gout_in, co
                        const int32_t* slot, const int32_t* slot_count, float* g_rows,
                        float* g_center, float* g_offset, size_t bsize, size_t num, size_t be,
                        size_t ne, size_t bc, size_t nc, size_t dim, void* stream);
+
+/* Union queries (query operand [B, U, 1, dim]): the reference front-ends loop over the U branches
+ * in Python, call the op once per branch on the same entity operand and stack the results to
+ * [B, U, num] (box_dist.py:60-68, l1_dist.py:52-60, rotate_dist.py:54-63).  These entry points score
+ * all branches of a query in one pass over the table rows and, in backward, add the sum of the
+ * branches' row gradients to g_rows once (slot / slot_count / g_rows as for the _rows entry points).
+ *   first, second      [bsize, branches, dim]           g_first, g_second the same
+ *   dst0 (dst1)        [bsize, branches, num]           gout0 (gout1) the same
+ * Shape: every query has its own `num` candidate rows (idx is [bsize, num]).
+ * dist_id: a SMORE_DIST_* id (dst1 / gout1 unused), or SMORE_DIST_BOX_BOTH: dst0 / gout0 belong to
+ * box_out, dst1 / gout1 to box_in.  Results equal the per-branch calls.
+ * `branches` must be 2 (the union structures of the reference, 2u and up, have two branches);
+ * callers run other counts branch by branch.  SMORE_ERR_BAD_SHAPE if dim is not a multiple of 4,
+ * exceeds 1024, an operand is not 16-byte aligned or num < 4. */
+SMORE_API int smore_union_forward_rows(int dist_id, const float* table, const int64_t* idx,
+                             const float* first, const float* second, float* dst0, float* dst1,
+                             size_t branches, size_t bsize, size_t num, size_t dim, void* stream);
+
+SMORE_API int smore_union_backward_rows(int dist_id, const float* gout0, const float* gout1,
+                              const float* table, const int64_t* idx, const float* first,
+                              const float* second, const int32_t* slot, const int32_t* slot_count,
+                              float* g_rows, float* g_first, float* g_second, size_t branches,
+                              size_t bsize, size_t num, size_t dim, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Row gather, per-step gradient merge and row-wise optimizers.

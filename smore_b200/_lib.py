@@ -10,6 +10,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "csrc", "libsmore_b200.so")
 
 DIST_IDS = {"box_out": 0, "box_in": 1, "rotate": 2, "l1": 3, "l2": 4, "complex": 5, "distmult": 6}
+BOX_BOTH_ID = 7     # smore_union_* entry points only
 OPT_IDS = {"sgd": 0, "adam": 1, "adagrad": 2}
 ROW_PARTS = {"box_out": 1, "box_in": 1, "rotate": 2, "l1": 1, "l2": 1, "complex": 2, "distmult": 1}
 QUERY_PARTS = {"box_out": 2, "box_in": 2, "rotate": 2, "l1": 1, "l2": 1, "complex": 2, "distmult": 1}
@@ -32,6 +33,8 @@ SIGNATURES = {
     "smore_dist_backward_rows": (_int, [_int] + [_p] * 10 + [_sz] * 7 + [_p]),
     "smore_box_forward": (_int, [_p] * 6 + [_sz] * 7 + [_p]),
     "smore_box_backward": (_int, [_p] * 12 + [_sz] * 7 + [_p]),
+    "smore_union_forward_rows": (_int, [_int] + [_p] * 6 + [_sz] * 4 + [_p]),
+    "smore_union_backward_rows": (_int, [_int] + [_p] * 11 + [_sz] * 4 + [_p]),
     "smore_gather_rows": (_int, [_p, _p, _p, _sz, _sz, _p]),
     "smore_unique_rows_workspace_bytes": (_sz, [_sz]),
     "smore_unique_rows": (_int, [_p, _sz, _sz, _p, _p, _p, _p, _p, _sz, _p]),

@@ -401,6 +401,225 @@ __global__ void __launch_bounds__(kRowCtaThreads)
 }
 
 // ----------------------------------------------------------------------------------------
+// Union queries: NB branches of every query scored against the same candidate rows.
+// The reference runs the op once per branch and stacks the results (a Python loop over the
+// branch axis of a 4-D query operand); here one pass over the rows serves all branches, and the
+// backward pass writes the sum of the branches' row gradients once.
+// Operands: first / second [B, NB, dim]; outputs and output gradients [B, NB, K].
+// ----------------------------------------------------------------------------------------
+
+template <class Term, int NB, int NCH, int R>
+__global__ void __launch_bounds__(kRowCtaThreads)
+    row_forward_union_kernel(RowArgs a, float* __restrict__ dst0, float* __restrict__ dst1) {
+  extern __shared__ float4 sq[];  // [2][NB][dim4]: the query's branches, first then second operand
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int b = blockIdx.x / a.chunks, c = blockIdx.x - b * a.chunks;
+  const int dim4 = a.dim >> 2;
+  {
+    const float4* p0 = reinterpret_cast<const float4*>(a.first + (size_t)b * NB * a.dim);
+    const float4* p1 = reinterpret_cast<const float4*>(a.second + (size_t)b * NB * a.dim);
+    for (int i = threadIdx.x; i < NB * dim4; i += kRowCtaThreads) {
+      sq[i] = __ldg(p0 + i);
+      if (Term::kNQ == 2) sq[NB * dim4 + i] = __ldg(p1 + i);
+    }
+  }
+  __syncthreads();
+  const float4* sq0 = sq;
+  const float4* sq1 = Term::kNQ == 2 ? sq + NB * dim4 : sq;
+
+  const int r_begin = c * a.rows_per_cta;
+  const int r_end = min(a.K, r_begin + a.rows_per_cta);
+  const size_t w4 = (size_t)dim4 * Term::kMul;
+  const float4* ent4 = reinterpret_cast<const float4*>(a.ent);
+
+  for (int base = r_begin + warp * a.wrows; base < r_end; base += kRowCtaWarps * a.wrows) {
+    const int n = min(a.wrows, r_end - base);
+    const size_t pos = (size_t)b * a.K + base + lane;
+    long long myrow = 0;
+    if (lane < n) myrow = a.idx ? (long long)a.idx[pos] : (long long)pos;
+    float out0[NB], out1[NB];
+#pragma unroll
+    for (int u = 0; u < NB; ++u) out0[u] = out1[u] = 0.f;
+    for (int t = 0; t < n; t += R) {
+      float4 e[R][Term::kMul][NCH];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const long long row = __shfl_sync(0xffffffffu, myrow, min(t + r, n - 1));
+        const float4* pe = ent4 + (size_t)row * w4;
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) {
+          const int d4 = lane + 32 * j;
+          if (d4 < dim4) {
+            e[r][0][j] = ld_row4(pe + d4);
+            if (Term::kMul == 2) e[r][Term::kMul - 1][j] = ld_row4(pe + dim4 + d4);
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+#pragma unroll
+        for (int u = 0; u < NB; ++u) {
+          float acc[Term::kNOut];
+#pragma unroll
+          for (int o = 0; o < Term::kNOut; ++o) acc[o] = 0.f;
+#pragma unroll
+          for (int j = 0; j < NCH; ++j) {
+            const int d4 = lane + 32 * j;
+            if (d4 < dim4)
+              fwd4<Term>(e[r][0][j], e[r][Term::kMul - 1][j], sq0[u * dim4 + d4], sq1[u * dim4 + d4], acc);
+          }
+#pragma unroll
+          for (int o = 0; o < Term::kNOut; ++o) acc[o] = warp_sum(acc[o]);
+          if (lane == t + r) {
+            out0[u] = acc[0];
+            out1[u] = acc[Term::kNOut - 1];
+          }
+        }
+      }
+    }
+    if (lane < n) {
+#pragma unroll
+      for (int u = 0; u < NB; ++u) {
+        const size_t o = ((size_t)b * NB + u) * a.K + base + lane;
+        dst0[o] = out0[u];
+        if (Term::kNOut == 2) dst1[o] = out1[u];
+      }
+    }
+  }
+}
+
+template <int N>
+struct alignas(4 * N) GoutVec {
+  float v[N];
+};
+
+template <class Term, int NB, int U>
+__global__ void __launch_bounds__(kRowCtaThreads)
+    col_backward_union_kernel(RowArgs a, RowGradArgs ga, int tpr, int groups) {
+  constexpr int NG = NB * Term::kNOut;   // output gradients per row: 2 or 4
+  extern __shared__ float4 red[];        // [groups][NB][kNQ][dim4]
+  __shared__ size_t meta_src[kRowCtaWarps][32];
+  __shared__ long long meta_dst[kRowCtaWarps][32];
+  __shared__ GoutVec<NG> meta_g[kRowCtaWarps][32];
+  __shared__ int meta_single[kRowCtaWarps][32];
+  const int lane = threadIdx.x & 31;
+  const int grp = threadIdx.x / tpr, col = threadIdx.x - grp * tpr;
+  const int b = blockIdx.x / a.chunks, c = blockIdx.x - b * a.chunks;
+  const int dim4 = a.dim >> 2;
+  const bool active = grp < groups && col < dim4;
+  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  const size_t w4 = (size_t)dim4 * Term::kMul;
+  const float4* ent4 = reinterpret_cast<const float4*>(a.ent);
+  float4* gbase = reinterpret_cast<float4*>(ga.g_rows);
+
+  float4 q0[NB], q1[NB], gq0[NB], gq1[NB];
+#pragma unroll
+  for (int u = 0; u < NB; ++u) {
+    q0[u] = q1[u] = gq0[u] = gq1[u] = z4;
+    if (active) {
+      q0[u] = __ldg(reinterpret_cast<const float4*>(a.first + ((size_t)b * NB + u) * a.dim) + col);
+      if (Term::kNQ == 2)
+        q1[u] = __ldg(reinterpret_cast<const float4*>(a.second + ((size_t)b * NB + u) * a.dim) + col);
+    }
+  }
+
+  const int r_begin = c * a.rows_per_cta;
+  const int r_end = min(a.K, r_begin + a.rows_per_cta);
+  if (grp < groups) {
+    const int n_mine = (r_end - r_begin - grp + groups - 1) / groups;
+    const int warp = threadIdx.x >> 5;
+    for (int t0 = 0; t0 < n_mine; t0 += 32) {
+      const int n = min(32, n_mine - t0);
+      __syncwarp();
+      {
+        const int l = lane < n ? lane : 0;
+        const int k = r_begin + grp + groups * (t0 + l);
+        const size_t pos = (size_t)b * a.K + k;
+        const size_t row = (size_t)a.idx[pos];
+        const int32_t s = ga.slot[pos];
+        meta_src[warp][lane] = row * w4;
+        meta_dst[warp][lane] = s < 0 ? -1 : s * (long long)w4;
+        GoutVec<NG> g;
+#pragma unroll
+        for (int u = 0; u < NB; ++u) {
+          const size_t o = ((size_t)b * NB + u) * a.K + k;
+          g.v[u * Term::kNOut] = ga.gout0[o];
+          if (Term::kNOut == 2) g.v[u * Term::kNOut + Term::kNOut - 1] = ga.gout1[o];
+        }
+        meta_g[warp][lane] = g;
+        meta_single[warp][lane] = (s >= 0 && ga.slot_count != nullptr) ? (ga.slot_count[s] == 1) : 0;
+      }
+      __syncwarp();
+      for (int t = 0; t < n; t += U) {
+        float4 e0[U], e1[U];
+        if (active) {
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const float4* pe = ent4 + meta_src[warp][t + u] + col;
+            e0[u] = ld_row4(pe);
+            if (Term::kMul == 2) e1[u] = ld_row4(pe + dim4);
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            if (t + u < n) {
+              const GoutVec<NG> gv = meta_g[warp][t + u];
+              const long long dst = meta_dst[warp][t + u];
+              float4 ge0 = z4, ge1 = z4;
+#pragma unroll
+              for (int br = 0; br < NB; ++br) {
+                float g[Term::kNOut];
+                g[0] = gv.v[br * Term::kNOut];
+                if (Term::kNOut == 2) g[Term::kNOut - 1] = gv.v[br * Term::kNOut + Term::kNOut - 1];
+                bwd4<Term>(g, e0[u], Term::kMul == 2 ? e1[u] : e0[u], q0[br], q1[br], ge0, ge1, gq0[br], gq1[br]);
+              }
+              if (dst >= 0) {
+                float4* out = gbase + dst + col;
+                if (meta_single[warp][t + u]) {
+                  out[0] = ge0;
+                  if (Term::kMul == 2) out[dim4] = ge1;
+                } else {
+                  atomicAdd(out, ge0);
+                  if (Term::kMul == 2) atomicAdd(out + dim4, ge1);
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // fold the groups' query gradients in group order
+  const size_t per_group = (size_t)NB * Term::kNQ * dim4;
+  if (active) {
+#pragma unroll
+    for (int u = 0; u < NB; ++u) {
+      red[grp * per_group + (size_t)u * Term::kNQ * dim4 + col] = gq0[u];
+      if (Term::kNQ == 2) red[grp * per_group + (size_t)u * Term::kNQ * dim4 + dim4 + col] = gq1[u];
+    }
+  }
+  __syncthreads();
+  if (grp == 0 && active) {
+#pragma unroll
+    for (int u = 0; u < NB; ++u) {
+      for (int gi = 1; gi < groups; ++gi) {
+        add4(gq0[u], red[gi * per_group + (size_t)u * Term::kNQ * dim4 + col]);
+        if (Term::kNQ == 2) add4(gq1[u], red[gi * per_group + (size_t)u * Term::kNQ * dim4 + dim4 + col]);
+      }
+      float4* gf = reinterpret_cast<float4*>(ga.g_first + ((size_t)b * NB + u) * a.dim) + col;
+      float4* gs = reinterpret_cast<float4*>(ga.g_second + ((size_t)b * NB + u) * a.dim) + col;
+      if (ga.query_atomic) {
+        atomicAdd(gf, gq0[u]);
+        if (Term::kNQ == 2) atomicAdd(gs, gq1[u]);
+      } else {
+        *gf = gq0[u];
+        if (Term::kNQ == 2) *gs = gq1[u];
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------
 // host side: validation, shape classification, launches
 // ----------------------------------------------------------------------------------------
 
@@ -542,6 +761,76 @@ static int launch_backward(const Shape& s, const float* gout0, const float* gout
   return check_launch("cell_backward kernels", 2);
 }
 
+constexpr int kUnionBranches = 2;
+
+static int check_union(const char* what, size_t branches, const Shape& s, bool aligned, RowPlan* p) {
+  if (branches != kUnionBranches)
+    return fail(SMORE_ERR_BAD_SHAPE, "%s: %d branches per query are supported (run other counts branch by branch)",
+                what, kUnionBranches);
+  if (int rc = validate_shape(s)) return rc;
+  *p = plan_rows(s, aligned);
+  if (p->chunks == 0)
+    return fail(SMORE_ERR_BAD_SHAPE,
+                "%s: needs 16-byte aligned operands, dim a multiple of 4 and <= 1024, at least 4 rows per query", what);
+  return SMORE_OK;
+}
+
+template <class Term>
+static int launch_forward_union(size_t branches, const Shape& s, const float* table, const int64_t* idx,
+                                const float* first, const float* second, float* dst0, float* dst1,
+                                cudaStream_t st) {
+  if (Term::kNQ == 1) second = first;
+  RowPlan p;
+  if (int rc = check_union("union_forward_rows", branches, s, aligned16(table) && aligned16(first) && aligned16(second),
+                           &p))
+    return rc;
+  RowArgs a{table, idx, first, second, (int)s.num, (int)s.dim, p.rows_per_cta, p.chunks, p.wrows};
+  const unsigned grid = (unsigned)(s.bsize * p.chunks);
+  const size_t smem = (size_t)kUnionBranches * Term::kNQ * s.dim * sizeof(float);
+  constexpr int NB = kUnionBranches;
+  switch (p.nch) {
+    case 1: row_forward_union_kernel<Term, NB, 1, 4><<<grid, kRowCtaThreads, smem, st>>>(a, dst0, dst1); break;
+    case 2: row_forward_union_kernel<Term, NB, 2, 4><<<grid, kRowCtaThreads, smem, st>>>(a, dst0, dst1); break;
+    case 4: row_forward_union_kernel<Term, NB, 4, 2><<<grid, kRowCtaThreads, smem, st>>>(a, dst0, dst1); break;
+    default: row_forward_union_kernel<Term, NB, 8, 1><<<grid, kRowCtaThreads, smem, st>>>(a, dst0, dst1); break;
+  }
+  return check_launch("row_forward_union_kernel");
+}
+
+template <class Term>
+static int launch_backward_union(size_t branches, const Shape& s, const float* gout0, const float* gout1,
+                                 const float* table, const int64_t* idx, const float* first, const float* second,
+                                 const int32_t* slot, const int32_t* slot_count, float* g_rows, float* g_first,
+                                 float* g_second, cudaStream_t st) {
+  if (Term::kNQ == 1) {
+    second = first;
+    g_second = g_first;
+  }
+  RowPlan p;
+  const bool aligned = aligned16(table) && aligned16(first) && aligned16(second) && aligned16(g_rows) &&
+                       aligned16(g_first) && aligned16(g_second);
+  if (int rc = check_union("union_backward_rows", branches, s, aligned, &p)) return rc;
+  constexpr int NB = kUnionBranches;
+  RowArgs a{table, idx, first, second, (int)s.num, (int)s.dim, p.rows_per_cta, p.chunks, p.wrows};
+  RowGradArgs ga{gout0, gout1, nullptr, slot, slot_count, g_rows, g_first, g_second, p.chunks > 1};
+  if (p.chunks > 1) {
+    const size_t bytes = s.bsize * NB * s.dim * sizeof(float);
+    if (cudaMemsetAsync(g_first, 0, bytes, st) != cudaSuccess ||
+        (Term::kNQ == 2 && cudaMemsetAsync(g_second, 0, bytes, st) != cudaSuccess))
+      return fail(SMORE_ERR_CUDA, "union_backward_rows: cudaMemsetAsync failed");
+  }
+  const unsigned grid = (unsigned)(s.bsize * p.chunks);
+  const int dim4 = (int)(s.dim >> 2);
+  const int tpr = ((dim4 + 31) / 32) * 32;
+  const int groups = kRowCtaThreads / tpr;
+  const size_t smem = (size_t)groups * NB * Term::kNQ * s.dim * sizeof(float);
+  if (Term::kMul == 2)
+    col_backward_union_kernel<Term, NB, 4><<<grid, kRowCtaThreads, smem, st>>>(a, ga, tpr, groups);
+  else
+    col_backward_union_kernel<Term, NB, 8><<<grid, kRowCtaThreads, smem, st>>>(a, ga, tpr, groups);
+  return check_launch("col_backward_union_kernel");
+}
+
 template <class Term>
 static int launch_forward_f64(const Shape& s, const double* ent, const double* first,
                               const double* second, double* dst, cudaStream_t st) {
@@ -670,6 +959,40 @@ int smore_box_backward(const float* gout_out, const float* gout_in, const float*
   if (int rc = validate_shape(s)) return rc;
   return launch_backward<TermBoxBoth>(s, gout_out, gout_in, ent, idx, center, offset, g_ent, slot, slot_count,
                                       g_rows, g_center, g_offset, (cudaStream_t)stream);
+}
+
+int smore_union_forward_rows(int dist_id, const float* table, const int64_t* idx, const float* first,
+                             const float* second, float* dst0, float* dst1, size_t branches, size_t bsize,
+                             size_t num, size_t dim, void* stream) {
+  const bool both = dist_id == SMORE_DIST_BOX_BOTH;
+  if (!both && (dist_id < 0 || dist_id >= SMORE_DIST_COUNT))
+    return fail(SMORE_ERR_BAD_DIST, "unknown distance id %d", dist_id);
+  if (!table || !idx || !first || !dst0 || (both && !dst1) || ((both || needs_second(dist_id)) && !second))
+    return fail(SMORE_ERR_NULL, "union_forward_rows: required pointer is NULL");
+  const Shape s{bsize, num, bsize, num, bsize, 1, dim};
+  cudaStream_t st = (cudaStream_t)stream;
+  if (both) return launch_forward_union<TermBoxBoth>(branches, s, table, idx, first, second, dst0, dst1, st);
+  SMORE_DISPATCH(dist_id, launch_forward_union<Term>(branches, s, table, idx, first, second, dst0, dst0, st));
+}
+
+int smore_union_backward_rows(int dist_id, const float* gout0, const float* gout1, const float* table,
+                              const int64_t* idx, const float* first, const float* second, const int32_t* slot,
+                              const int32_t* slot_count, float* g_rows, float* g_first, float* g_second,
+                              size_t branches, size_t bsize, size_t num, size_t dim, void* stream) {
+  const bool both = dist_id == SMORE_DIST_BOX_BOTH;
+  if (!both && (dist_id < 0 || dist_id >= SMORE_DIST_COUNT))
+    return fail(SMORE_ERR_BAD_DIST, "unknown distance id %d", dist_id);
+  const bool two = both || needs_second(dist_id);
+  if (!gout0 || (both && !gout1) || !table || !idx || !first || !slot || !g_rows || !g_first ||
+      (two && (!second || !g_second)))
+    return fail(SMORE_ERR_NULL, "union_backward_rows: required pointer is NULL");
+  const Shape s{bsize, num, bsize, num, bsize, 1, dim};
+  cudaStream_t st = (cudaStream_t)stream;
+  if (both)
+    return launch_backward_union<TermBoxBoth>(branches, s, gout0, gout1, table, idx, first, second, slot, slot_count,
+                                              g_rows, g_first, g_second, st);
+  SMORE_DISPATCH(dist_id, launch_backward_union<Term>(branches, s, gout0, gout0, table, idx, first, second, slot,
+                                                      slot_count, g_rows, g_first, g_second, st));
 }
 
 int smore_dist_forward_f64(int dist_id, const double* ent, const double* first, const double* second,

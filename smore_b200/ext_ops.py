@@ -198,6 +198,75 @@ class _RowsDistFunc(torch.autograd.Function):
         return None, None, None, g_first, g_second
 
 
+class _RowsUnionFunc(torch.autograd.Function):
+    """All branches of a union query ([B, U, 1, dim] operands) against table rows in one pass:
+    results [B, U, num], the same values as the per-branch loop of the reference front-ends
+    (box_dist.py:60-68); backward adds the sum of the branches' row gradients once."""
+
+    @staticmethod
+    def forward(ctx, name, rows, dummy, first, second):
+        first = first.contiguous()
+        second = None if second is None else second.contiguous()
+        owner, lookup = rows.owner, rows.lookup
+        table, row_ids = owner.rows_operands(lookup)
+        B, U, _, dim = first.shape
+        num = rows.as_3d()[1]
+        both = name == "box_both"
+        dist_id = _lib.BOX_BOTH_ID if both else _lib.DIST_IDS[name]
+        d0 = torch.empty(B, U, num, dtype=table.dtype, device=table.device)
+        d1 = torch.empty_like(d0) if both else None
+        with torch.cuda.device(table.device), _lib.timed("rows_forward_union"):
+            _lib.check(_lib.lib().smore_union_forward_rows(
+                dist_id, table.data_ptr(), row_ids.data_ptr(), first.data_ptr(),
+                None if second is None else second.data_ptr(), d0.data_ptr(), None if d1 is None else d1.data_ptr(),
+                U, B, num, dim, torch.cuda.current_stream(table.device).cuda_stream), "smore_union_forward_rows")
+        ctx.name, ctx.rows, ctx.sizes, ctx.dist_id = name, rows, (U, B, num, dim), dist_id
+        ctx.two = second is not None
+        if ctx.two:
+            ctx.save_for_backward(first, second)
+        else:
+            ctx.save_for_backward(first)
+        return (d0, d1) if both else d0
+
+    @staticmethod
+    def backward(ctx, *gouts):
+        if ctx.two:
+            first, second = ctx.saved_tensors
+        else:
+            (first,) = ctx.saved_tensors
+            second = None
+        owner, lookup = ctx.rows.owner, ctx.rows.lookup
+        table, row_ids = owner.rows_operands(lookup)
+        plan = owner.plan_for(lookup)
+        counts_ptr = None if lookup.received else plan.counts.data_ptr()
+        lookup.received = True
+        slot = plan.slot_of(lookup)
+        g_first = torch.empty_like(first)
+        g_second = torch.empty_like(second) if ctx.two else None
+        gouts = [g.contiguous() for g in gouts]
+        with torch.cuda.device(table.device), _lib.timed("rows_backward_union"):
+            _lib.check(_lib.lib().smore_union_backward_rows(
+                ctx.dist_id, gouts[0].data_ptr(), gouts[1].data_ptr() if len(gouts) > 1 else None, table.data_ptr(),
+                row_ids.data_ptr(), first.data_ptr(), None if second is None else second.data_ptr(), slot.data_ptr(),
+                counts_ptr, plan.g_rows.data_ptr(), g_first.data_ptr(),
+                None if g_second is None else g_second.data_ptr(), *ctx.sizes,
+                torch.cuda.current_stream(table.device).cuda_stream), "smore_union_backward_rows")
+        return None, None, None, g_first, g_second
+
+
+def _union_in_one_pass(name, entity, first, second):
+    """Whether the fused union kernels cover this call: table rows, two branches, one candidate
+    list per query, row width within the row-stream kernels' limits."""
+    if not isinstance(entity, LazyRows) or first.shape[1] != 2 or first.shape[2] != 1:
+        return False
+    if not first.is_cuda or first.dtype != torch.float32 or (second is not None and second.shape != first.shape):
+        return False
+    be, ne, width = entity.as_3d()
+    dim = first.shape[3]
+    parts = 1 if name == "box_both" else _lib.ROW_PARTS[name]
+    return be == first.shape[0] and ne >= 4 and width == parts * dim and dim % 4 == 0 and dim <= 1024
+
+
 _DOT_PRECISIONS = {"tf32": 0, "fp32": 1}
 
 
@@ -285,6 +354,8 @@ def _dist(name, entity, first, second=None):
     if entity.dim() != first.dim():
         if first.dim() != 4 or entity.dim() != 3:
             raise ValueError("expected a 3-D entity operand with 3-D or 4-D query operands")
+        if _union_in_one_pass(name, entity, first, second):
+            return _RowsUnionFunc.apply(name, entity, entity.owner.dummy_tensor, first, second)
         outs = []
         for i in range(first.shape[1]):
             f = first[:, i, :, :].contiguous()

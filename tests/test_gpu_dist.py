@@ -213,3 +213,71 @@ def test_reference_cuda_kernels_agree(oracle):
         close(g[1].cpu().numpy(), r[1].cpu().numpy(), RTOL_ATOMIC, what=op + " g_first")
         if q1 is not None:
             close(g[2].cpu().numpy(), r[2].cpu().numpy(), RTOL_ATOMIC, what=op + " g_second")
+
+
+@pytest.mark.parametrize("op,shared", [("box_out", False), ("box_in", False), ("rotate", False), ("l1", False),
+                                       ("box_out", True), ("distmult", True)])
+def test_speed_against_reference_kernels(op, shared, capsys):
+    """The reference's kernels recompiled for sm_100a are the kernels to beat: same operands
+    (materialised candidate rows, B = K = 1024), CUDA-event times of forward and backward, results
+    compared; prints one line per case (run with -s to see it)."""
+    import ctypes
+    from oracle.oracle import DIST_IDS, reference_cuda_path
+    from smore_b200 import extlib_cuda as ext
+    path = reference_cuda_path()
+    if path is None:
+        pytest.skip("reference CUDA library not built")
+    ref = ctypes.CDLL(path)
+    vp, sz = ctypes.c_void_p, ctypes.c_size_t
+    ref.ref_cuda_dist_forward.argtypes = [ctypes.c_int, vp, vp, vp, vp] + [sz] * 7 + [vp]
+    ref.ref_cuda_dist_backward.argtypes = [ctypes.c_int] + [vp] * 7 + [sz] * 7 + [vp]
+    B, K = 1024, 1024
+    dim = 500 if op == "rotate" else 400
+    mul = 2 if op == "rotate" else 1
+    two = op in ("box_out", "box_in", "rotate")
+    be = 1 if shared else B
+    g = torch.Generator(device="cuda").manual_seed(11)
+    ent = (torch.rand(be, K, mul * dim, device="cuda", generator=g) - 0.5) * 0.1
+    q0 = (torch.rand(B, 1, dim, device="cuda", generator=g) - 0.5) * 0.1
+    q1 = torch.rand(B, 1, dim, device="cuda", generator=g) * 0.05 if two else None
+    gout = torch.randn(B, K, device="cuda", generator=g)
+    st = torch.cuda.current_stream().cuda_stream
+    p = lambda t: None if t is None else t.data_ptr()
+    mine, theirs = torch.empty(B, K, device="cuda"), torch.empty(B, K, device="cuda")
+    gm = [torch.empty_like(ent), torch.empty_like(q0), None if q1 is None else torch.empty_like(q1)]
+    gr = [torch.zeros_like(ent), torch.zeros_like(q0), None if q1 is None else torch.zeros_like(q1)]
+
+    def ours_fwd():
+        ext.dist_forward(op, ent, q0, q1, mine)
+
+    def ours_bwd():
+        ext.dist_backward(op, gout, ent, q0, q1, gm[0], gm[1], gm[2])
+
+    def ref_fwd():
+        assert ref.ref_cuda_dist_forward(DIST_IDS[op], p(ent), p(q0), p(q1), p(theirs), B, K, be, K, B, 1, dim, st) == 0
+
+    def ref_bwd():
+        assert ref.ref_cuda_dist_backward(DIST_IDS[op], p(gout), p(ent), p(q0), p(q1), p(gr[0]), p(gr[1]), p(gr[2]),
+                                          B, K, be, K, B, 1, dim, st) == 0
+
+    def time_ms(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    t = {"ours_fwd": time_ms(ours_fwd, 5), "ref_fwd": time_ms(ref_fwd, 3),
+         "ours_bwd": time_ms(ours_bwd, 5), "ref_bwd": time_ms(ref_bwd, 2)}
+    close(mine.cpu().numpy(), theirs.cpu().numpy(), 1e-4, what=op + " forward")
+    close(gm[1].cpu().numpy(), gr[1].cpu().numpy(), 1e-3, what=op + " g_first")
+    with capsys.disabled():
+        print("\nreference-kernel comparison %s %s B=K=1024 dim=%d: forward %.3f ms vs %.3f ms (x%.1f), "
+              "backward %.3f ms vs %.3f ms (x%.1f)" % (op, "shared" if shared else "per-query", dim, t["ours_fwd"],
+                                                       t["ref_fwd"], t["ref_fwd"] / t["ours_fwd"], t["ours_bwd"],
+                                                       t["ref_bwd"], t["ref_bwd"] / t["ours_bwd"]))
+    assert t["ours_fwd"] < t["ref_fwd"] * 1.1 and t["ours_bwd"] < t["ref_bwd"]

@@ -238,3 +238,121 @@ def test_table_resident_rows_equal_gathered_rows(oracle, op, shape):
     close(g_q0.cpu().numpy(), w_q0, 2 * RTOL, what="g_first")
     if q1 is not None:
         close(g_q1.cpu().numpy(), w_q1, 2 * RTOL, what="g_second")
+
+
+@pytest.mark.parametrize("op", ["l1", "l2", "box_out", "box_in", "box_both", "rotate", "complex", "distmult"])
+@pytest.mark.parametrize("shape", [(6, 50, 64), (3, 9, 36), (5, 700, 400), (2, 33, 1000)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_union_branches_in_one_pass(oracle, op, shape):
+    """smore_union_*_rows == the per-branch oracle calls stacked on the branch axis, with the row
+    gradients of both branches summed into the step's compact gradient rows."""
+    from smore_b200 import _lib
+    L = _lib.lib()
+    B, K, dim = shape
+    U, N = 2, 97
+    base = "box_out" if op == "box_both" else op
+    mul = 2 if op in ("rotate", "complex") else 1
+    tab, q0, q1 = make_operands(base, N, 1, B * U, 1, dim, seed=sum(shape))
+    table = tab.reshape(N, dim * mul)
+    q0 = q0.reshape(B, U, dim)
+    q1 = None if q1 is None else q1.reshape(B, U, dim)
+    rng = np.random.default_rng(2)
+    idx = rng.integers(0, N, B * K)
+    ent = table[idx].reshape(B, K, dim * mul)
+    names = ["box_out", "box_in"] if op == "box_both" else [op]
+    gouts = [rng.standard_normal((B, U, K)).astype(np.float32) for _ in names]
+    want = [np.zeros((B, U, K), np.float32) for _ in names]
+    w_ent = np.zeros_like(ent)
+    w_q0, w_q1 = np.zeros_like(q0), None if q1 is None else np.zeros_like(q1)
+    for u in range(U):
+        f = np.ascontiguousarray(q0[:, u:u + 1])
+        s = None if q1 is None else np.ascontiguousarray(q1[:, u:u + 1])
+        for k, nm in enumerate(names):
+            want[k][:, u] = oracle.dist_forward(nm, ent, f, s)
+            ge, g0, g1 = oracle.dist_backward(nm, np.ascontiguousarray(gouts[k][:, u]), ent, f, s)
+            w_ent += ge
+            w_q0[:, u:u + 1] += g0
+            if q1 is not None:
+                w_q1[:, u:u + 1] += g1
+    w_uniq, w_inv, _ = oracle.unique_rows(idx)
+    w_rows = oracle.scatter_sum_rows(w_ent.reshape(B * K, -1), w_inv, len(w_uniq))
+
+    dev = lambda a: None if a is None else torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    ptr = lambda t_: None if t_ is None else t_.data_ptr()
+    t, i, d_q0, d_q1 = dev(table), dev(idx), dev(q0), dev(q1)
+    dist_id = _lib.BOX_BOTH_ID if op == "box_both" else _lib.DIST_IDS[op]
+    dst = [torch.full((B, U, K), float("nan"), device="cuda") for _ in names]
+    _lib.check(L.smore_union_forward_rows(dist_id, t.data_ptr(), i.data_ptr(), ptr(d_q0), ptr(d_q1), dst[0].data_ptr(),
+                                          dst[1].data_ptr() if len(dst) > 1 else None, U, B, K, dim, _st()), "fwd")
+    for k, nm in enumerate(names):
+        scale = forward_scale(oracle, nm, ent, np.ascontiguousarray(q0[:, :1]),
+                              None if q1 is None else np.ascontiguousarray(q1[:, :1]))
+        close(dst[k].cpu().numpy(), want[k], RTOL, scale, what=nm)
+
+    uniq, inverse, counts, n_unique = _unique(idx, N)
+    g_rows = torch.full((B * K, dim * mul), float("nan"), device="cuda")
+    _lib.check(L.smore_zero_shared_rows(g_rows.data_ptr(), counts.data_ptr(), n_unique.data_ptr(), B * K, dim * mul,
+                                        _st()), "zero")
+    g_q0 = torch.full_like(d_q0, float("nan"))
+    g_q1 = None if q1 is None else torch.full_like(d_q1, float("nan"))
+    d_g = [dev(g) for g in gouts]
+    _lib.check(L.smore_union_backward_rows(dist_id, d_g[0].data_ptr(), d_g[1].data_ptr() if len(d_g) > 1 else None,
+                                           t.data_ptr(), i.data_ptr(), ptr(d_q0), ptr(d_q1), inverse.data_ptr(),
+                                           counts.data_ptr(), g_rows.data_ptr(), g_q0.data_ptr(), ptr(g_q1), U, B, K,
+                                           dim, _st()), "bwd")
+    close(g_rows[:len(w_uniq)].cpu().numpy(), w_rows, RTOL_ATOMIC, what="g_rows")
+    close(g_q0.cpu().numpy(), w_q0, 4 * RTOL, what="g_first")
+    if q1 is not None:
+        close(g_q1.cpu().numpy(), w_q1, 4 * RTOL, what="g_second")
+    # other branch counts are the caller's loop
+    assert L.smore_union_forward_rows(dist_id, t.data_ptr(), i.data_ptr(), ptr(d_q0), ptr(d_q1), dst[0].data_ptr(),
+                                      dst[-1].data_ptr(), 3, B, K, dim, _st()) == -2
+
+
+@pytest.mark.parametrize("op", ["l1", "box", "rotate"])
+def test_union_front_end_equals_branch_loop(op, monkeypatch):
+    """ext_ops with a [B, 2, 1, dim] query on table rows: the one-pass route and the per-branch loop
+    of the reference front-end give the same scores, query gradients and table update."""
+    from smore_b200 import embedding, ext_ops
+    B, K, dim, N = 8, 64, 64, 300
+    mul = 2 if op == "rotate" else 1
+    torch.manual_seed(3)
+    init = (torch.rand(N, dim * mul) - 0.5) * 0.3
+    idx = torch.randint(0, N, (B, K)).cuda()
+    q = [((torch.rand(B, 2, 1, dim) - 0.5) * 0.3).cuda() for _ in range(2)]
+    q[1] = q[1].abs()
+
+    class Args(object):
+        optim_mode = ("aggr", "adam", "gpu", True, 0)
+        share_optim_stats = False
+
+    results = []
+    for fused in (True, False):
+        if not fused:
+            monkeypatch.setattr(ext_ops, "_union_in_one_pass", lambda *a: False)
+        emb = embedding.SparseEmbedding(N, dim * mul)
+        emb.embedding.data.copy_(init)
+        emb = emb.cuda()
+        emb.train()
+        opt = embedding.AdamEmbedOptimizer(Args(), emb, 0, lazy_names=("negative_entity",))
+        opt.zero_grad()
+        rows = emb(idx.view(-1), "negative_entity").view(B, K, -1)
+        a, b = q[0].clone().requires_grad_(), q[1].clone().requires_grad_()
+        if op == "l1":
+            score = ext_ops.l1_dist(rows, a)
+        elif op == "rotate":
+            score = ext_ops.rotate_dist(rows, a, b)
+        else:
+            score = ext_ops.box_dist_out(rows, a, b) + 0.02 * ext_ops.box_dist_in(rows, a, b)
+        assert score.shape == (B, 2, K)
+        (torch.max(score, dim=1)[0] ** 2).sum().backward()
+        opt.apply_grad(1e-2)
+        torch.cuda.synchronize()
+        results.append((score.detach().cpu(), a.grad.cpu(), None if b.grad is None else b.grad.cpu(),
+                        emb.embedding.data.cpu()))
+    (s1, a1, b1, t1), (s0, a0, b0, t0) = results
+    assert torch.equal(s1, s0)
+    close(a1.numpy(), a0.numpy(), RTOL, what="g_first")
+    if b0 is not None:
+        close(b1.numpy(), b0.numpy(), RTOL, what="g_second")
+    close(t1.numpy(), t0.numpy(), RTOL_ATOMIC, what="table")
