@@ -650,6 +650,8 @@ def run_gpu(args):
     e3.record()
     sync_all()
     ms_e2e = e2.elapsed_time(e3)
+    if _lib.async_status() != 0:
+        raise RuntimeError("a bulk-copy wait gave up inside a kernel: the timed results are invalid")
     # ---- the same K steps once more, eagerly, with CUDA events around each library call -------------
     # (kernels inside a replayed graph cannot be bracketed by events; the kernels are the same)
     if use_graphs:

@@ -144,6 +144,13 @@ SMORE_API int smore_box_backward(const float* gout_out, const float* gout_in, co
                        float* g_center, float* g_offset, size_t bsize, size_t num, size_t be,
                        size_t ne, size_t bc, size_t nc, size_t dim, void* stream);
 
+/* Kernels that stage table rows through shared memory with bulk asynchronous copies wait for each
+ * copy with a time limit (about a second).  A wait that runs out sets bit 0 of a device-side status
+ * word, the kernel stops early and its results are invalid; nothing else reports it.  This call
+ * synchronises the current device and returns the status word of that device (0 = every wait so far
+ * completed).  No counterpart in the reference. */
+SMORE_API int smore_async_status(int* status);
+
 /* Union queries (query operand [B, U, 1, dim]): the reference front-ends loop over the U branches
  * in Python, call the op once per branch on the same entity operand and stack the results to
  * [B, U, num] (box_dist.py:60-68, l1_dist.py:52-60, rotate_dist.py:54-63).  These entry points score

@@ -33,6 +33,7 @@ SIGNATURES = {
     "smore_dist_backward_rows": (_int, [_int] + [_p] * 10 + [_sz] * 7 + [_p]),
     "smore_box_forward": (_int, [_p] * 6 + [_sz] * 7 + [_p]),
     "smore_box_backward": (_int, [_p] * 12 + [_sz] * 7 + [_p]),
+    "smore_async_status": (_int, [ctypes.POINTER(ctypes.c_int)]),
     "smore_union_forward_rows": (_int, [_int] + [_p] * 6 + [_sz] * 4 + [_p]),
     "smore_union_backward_rows": (_int, [_int] + [_p] * 11 + [_sz] * 4 + [_p]),
     "smore_gather_rows": (_int, [_p, _p, _p, _sz, _sz, _p]),
@@ -86,6 +87,13 @@ def check(rc, what):
     if rc != 0:
         msg = lib().smore_last_error()
         raise SmoreError("%s failed (%d): %s" % (what, rc, msg.decode() if msg else ""))
+
+
+def async_status():
+    """Status word of the current device's bulk-copy kernels (synchronises); 0 means no wait gave up."""
+    v = ctypes.c_int(0)
+    check(lib().smore_async_status(ctypes.byref(v)), "smore_async_status")
+    return v.value
 
 
 # ---- optional per-kernel timing (benchmarks only) ----------------------------------------------

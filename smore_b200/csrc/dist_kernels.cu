@@ -15,8 +15,12 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "common.cuh"
+#include "bulk_copy.cuh"
 #include "dist_terms.cuh"
 #include "shared_kernels.cuh"
 
@@ -401,6 +405,133 @@ __global__ void __launch_bounds__(kRowCtaThreads)
 }
 
 // ----------------------------------------------------------------------------------------
+// Row-stream forward with the rows staged through shared memory by bulk asynchronous copies.
+// Each warp owns a ring of `stages` row slots and one mbarrier per slot; lane 0 keeps `stages`
+// row copies (one instruction per row) in flight ahead of the row the warp is reducing, so the
+// bytes in flight per SM no longer depend on registers or on how many warps are resident.
+// Work split: the CTA's block of rows is cut into one contiguous run per warp.
+// ----------------------------------------------------------------------------------------
+
+__device__ int g_async_status = 0;  // bit 0: a wait for a bulk copy gave up (results invalid)
+
+__host__ __device__ inline size_t bulk_ring_offset(int stages) {
+  return ((size_t)kRowCtaWarps * stages * sizeof(uint64_t) + 127) & ~(size_t)127;
+}
+
+template <class Term, int NCH>
+__global__ void __launch_bounds__(kRowCtaThreads)
+    row_forward_bulk_kernel(RowArgs a, float* __restrict__ dst0, float* __restrict__ dst1, int stages) {
+  extern __shared__ __align__(128) unsigned char bulk_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int b = blockIdx.x / a.chunks, c = blockIdx.x - b * a.chunks;
+  const int dim4 = a.dim >> 2;
+  const unsigned row_bytes = (unsigned)dim4 * Term::kMul * 16u;
+  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(bulk_smem) + warp * stages;
+  unsigned char* ring = bulk_smem + bulk_ring_offset(stages) + (size_t)warp * stages * row_bytes;
+  if (lane == 0) {
+    for (int s = 0; s < stages; ++s) bulk::barrier_init(bars + s, 1);
+    bulk::fence_barrier_init();
+  }
+  __syncthreads();
+
+  float4 q0[NCH], q1[NCH];
+  {
+    const float4* p0 = reinterpret_cast<const float4*>(a.first + (size_t)b * a.dim);
+    const float4* p1 = reinterpret_cast<const float4*>(a.second + (size_t)b * a.dim);
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int d4 = lane + 32 * j;
+      q0[j] = d4 < dim4 ? __ldg(p0 + d4) : z4;
+      q1[j] = (Term::kNQ == 2 && d4 < dim4) ? __ldg(p1 + d4) : z4;
+    }
+  }
+
+  const int r_begin = c * a.rows_per_cta;
+  const int r_end = min(a.K, r_begin + a.rows_per_cta);
+  const int per_warp = (r_end - r_begin + kRowCtaWarps - 1) / kRowCtaWarps;
+  const int w_begin = r_begin + warp * per_warp;
+  const int n = max(0, min(r_end, w_begin + per_warp) - w_begin);
+  const size_t pos0 = (size_t)b * a.K + w_begin;
+  const unsigned char* ent = reinterpret_cast<const unsigned char*>(a.ent);
+
+  auto batch_ids = [&](int first_t) -> long long {
+    const int t = first_t + lane;
+    if (t >= n) return 0;
+    return a.idx ? (long long)a.idx[pos0 + t] : (long long)(pos0 + t);
+  };
+  long long cur = batch_ids(0), nxt = 0;
+  // prologue: fill the ring
+  const int ahead = min(stages, n);
+  for (int t = 0; t < ahead; ++t) {
+    const long long row = __shfl_sync(0xffffffffu, cur, t);
+    if (lane == 0) {
+      bulk::barrier_expect(bars + t, row_bytes);
+      bulk::load(ring + (size_t)t * row_bytes, ent + (size_t)row * row_bytes, row_bytes, bars + t);
+    }
+  }
+  int slot = 0;
+  unsigned parity = 0;
+  float out0 = 0.f, out1 = 0.f;
+  for (int t = 0; t < n; ++t) {
+    const int tl = t & 31;
+    if (tl == 0) nxt = batch_ids(t + 32);
+    bool ok = bulk::barrier_wait(bars + slot, parity);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) {
+      // give up: let the copies still in flight land (bounded), flag the failure, stop
+      if (lane == 0) atomicOr(&g_async_status, 1);
+      for (int k = 1; k < stages && t + k < n; ++k) {
+        const int s2 = (slot + k) % stages;
+        bulk::barrier_wait(bars + s2, s2 > slot ? parity : parity ^ 1u);
+      }
+      break;
+    }
+    const float4* row4 = reinterpret_cast<const float4*>(ring + (size_t)slot * row_bytes);
+    float acc[Term::kNOut];
+#pragma unroll
+    for (int o = 0; o < Term::kNOut; ++o) acc[o] = 0.f;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int d4 = lane + 32 * j;
+      if (d4 < dim4) {
+        const float4 e0 = row4[d4];
+        const float4 e1 = Term::kMul == 2 ? row4[dim4 + d4] : e0;
+        fwd4<Term>(e0, e1, q0[j], q1[j], acc);
+      }
+    }
+#pragma unroll
+    for (int o = 0; o < Term::kNOut; ++o) acc[o] = warp_sum(acc[o]);
+    // the sums above consumed every lane's reads of the slot: it may be refilled
+    __syncwarp();
+    const int tn = t + stages;
+    if (tn < n) {
+      const long long row = __shfl_sync(0xffffffffu, (tn >> 5) == (t >> 5) ? cur : nxt, tn & 31);
+      if (lane == 0) {
+        bulk::barrier_expect(bars + slot, row_bytes);
+        bulk::load(ring + (size_t)slot * row_bytes, ent + (size_t)row * row_bytes, row_bytes, bars + slot);
+      }
+    }
+    if (lane == tl) {
+      out0 = acc[0];
+      out1 = acc[Term::kNOut - 1];
+    }
+    if (tl == 31 || t == n - 1) {
+      if (lane <= tl) {
+        const size_t o = pos0 + (t - tl) + lane;
+        dst0[o] = out0;
+        if (Term::kNOut == 2) dst1[o] = out1;
+      }
+      cur = nxt;
+    }
+    if (++slot == stages) {
+      slot = 0;
+      parity ^= 1u;
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------
 // Union queries: NB branches of every query scored against the same candidate rows.
 // The reference runs the op once per branch and stacks the results (a Python loop over the
 // branch axis of a 4-D query operand); here one pass over the rows serves all branches, and the
@@ -645,6 +776,26 @@ static int grid_for(size_t work_items, int per_block) {
   return (int)std::max<size_t>(1, std::min(blocks, cap));
 }
 
+// Opt a kernel in to more than 48 KB of dynamic shared memory and the largest shared-memory
+// carve-out, once per kernel and device.
+template <class Kernel>
+static int allow_large_smem(Kernel kern, int bytes) {
+  static std::mutex lock;
+  static std::map<std::pair<const void*, int>, bool> done;   // (kernel, device ordinal)
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return fail(SMORE_ERR_CUDA, "cudaGetDevice failed");
+  const std::pair<const void*, int> key(reinterpret_cast<const void*>(kern), dev);
+  std::lock_guard<std::mutex> guard(lock);
+  if (done.count(key)) return SMORE_OK;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess ||
+      cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) !=
+          cudaSuccess)
+    return fail(SMORE_ERR_CUDA, "cannot raise the shared-memory limit of a kernel: %s",
+                cudaGetErrorString(cudaGetLastError()));
+  done[key] = true;
+  return SMORE_OK;
+}
+
 // row-stream launch plan; chunks == 0 means "not eligible"
 struct RowPlan {
   int nch, wrows, rows_per_cta, chunks;
@@ -693,6 +844,21 @@ static int launch_forward(const Shape& s, const float* ent, const int64_t* idx, 
     RowArgs a{ent, idx, first, second, (int)s.num, (int)s.dim, p.rows_per_cta, p.chunks, p.wrows};
     const unsigned grid = (unsigned)(s.bsize * p.chunks);
     constexpr int R = 2;  // rows in flight per warp at 4 chunks per lane
+    // Rows of 1 KB and more go through the bulk-copy kernel: 2..8 slots per warp (about 96 KB of
+    // row copies in flight per SM at 32 resident warps; more in flight measured slower), CTAs of
+    // 512 rows.  It needs at least two CTAs per SM to cover the reduction latency.
+    const size_t row_bytes = s.dim * Term::kMul * sizeof(float);
+    const int stages = (int)std::min<size_t>(8, std::max<size_t>(2, (96 * 1024 / 32 + row_bytes - 1) / row_bytes));
+    const size_t bulk_smem = bulk_ring_offset(stages) + (size_t)kRowCtaWarps * stages * row_bytes;
+    if ((p.nch == 4 || p.nch == 8) && bulk_smem <= 110 * 1024) {
+      RowArgs ab = a;
+      ab.rows_per_cta = (int)std::min<size_t>(s.num, 512);
+      ab.chunks = (int)((s.num + ab.rows_per_cta - 1) / ab.rows_per_cta);
+      auto kern = p.nch == 4 ? row_forward_bulk_kernel<Term, 4> : row_forward_bulk_kernel<Term, 8>;
+      if (int rc = allow_large_smem(kern, 110 * 1024)) return rc;
+      kern<<<(unsigned)(s.bsize * ab.chunks), kRowCtaThreads, bulk_smem, st>>>(ab, dst0, dst1, stages);
+      return check_launch("row_forward_bulk_kernel");
+    }
     switch (p.nch) {
       case 1: row_forward_kernel<Term, 1, 4><<<grid, kRowCtaThreads, 0, st>>>(a, dst0, dst1); break;
       case 2: row_forward_kernel<Term, 2, 4><<<grid, kRowCtaThreads, 0, st>>>(a, dst0, dst1); break;
@@ -993,6 +1159,15 @@ int smore_union_backward_rows(int dist_id, const float* gout0, const float* gout
                                               g_rows, g_first, g_second, st);
   SMORE_DISPATCH(dist_id, launch_backward_union<Term>(branches, s, gout0, gout0, table, idx, first, second, slot,
                                                       slot_count, g_rows, g_first, g_second, st));
+}
+
+int smore_async_status(int* status) {
+  if (!status) return fail(SMORE_ERR_NULL, "async_status: NULL pointer");
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_async_status, sizeof(int));
+  if (e != cudaSuccess) return fail(SMORE_ERR_CUDA, "async_status: %s", cudaGetErrorString(e));
+  *status = v;
+  return SMORE_OK;
 }
 
 int smore_dist_forward_f64(int dist_id, const double* ent, const double* first, const double* second,

@@ -26,3 +26,14 @@ def golden():
     import numpy as np
     gdir = os.path.join(ROOT, "tests", "golden")
     return {name: np.load(os.path.join(gdir, "reference_%s.npz" % name)) for name in ("ops", "logits", "optimizer")}
+
+
+@pytest.fixture(autouse=True)
+def _no_abandoned_copy_waits(request):
+    """After every GPU test: no kernel of the library gave up waiting for a bulk copy."""
+    yield
+    if request.node.get_closest_marker("gpu") is not None:
+        import torch
+        if torch.cuda.is_available():
+            from smore_b200 import _lib
+            assert _lib.async_status() == 0, "a bulk-copy wait ran out inside a kernel"
