@@ -317,7 +317,7 @@ def first_lookup_group(pos, neg, queries):
 
 
 def train_step(model, pos, neg, queries, structure, reduce_dense=None, upcoming=None):
-    """train_process.py:172-227 on device-resident index tensors.  `reduce_dense(tensor)` sums a
+    """train_process.py:172-227 on device-resident index tensors.  `reduce_dense(list of gradients)` sums the
     dense parameter's gradient over the ranks (train_process.py:221-225) when there are several.
     `upcoming` = (pos, neg, queries, event or None) of the NEXT step, whose rows a sharded table
     starts pulling now (the role of the reference's asynchronous embedding read, embedding.py:98-121)."""
@@ -330,9 +330,7 @@ def train_step(model, pos, neg, queries, structure, reduce_dense=None, upcoming=
     loss.backward()
     model.embed_opt.apply_grad(model.cfg["lr"])
     if reduce_dense is not None:
-        for p in model.parameters():
-            if p.requires_grad and p.grad is not None:
-                reduce_dense(p.grad)
+        reduce_dense([p.grad for p in model.parameters() if p.requires_grad and p.grad is not None])
     model.dense_opt.step()
     return loss
 
@@ -522,15 +520,21 @@ def run_gpu(args):
         shard = sharded.ShardGroup.from_process_group(n_rows, width, caps, squeeze=cfg["squeeze"], device=device)
         r = (cfg["gamma"] + 2.0) / cfg["dim"]
         shard.init_uniform(-r, r, seed=1234)
-        model = QueryModel(cfg, n_rows, device, ext_ops, embedding, lazy=True, shard=shard, world=world)
+        model = QueryModel(cfg, n_rows, device, ext_ops, embedding, lazy=True, shard=shard, world=world,
+                           capturable=not args.no_graphs)
 
-        def reduce_dense(t):
-            dist.all_reduce(t)
+        def reduce_dense(grads):
+            # one all-reduce over all dense gradients instead of one per parameter
+            flat = torch.cat([g.reshape(-1) for g in grads])
+            dist.all_reduce(flat)
+            torch._foreach_copy_(grads, [f.view_as(g) for f, g in zip(flat.split([g.numel() for g in grads]), grads)])
     else:
         model = QueryModel(cfg, n_rows, device, ext_ops, embedding, lazy=not args.no_lazy,
                            capturable=not args.no_graphs)
+    prefetching = world > 1 and not args.no_prefetch
     use_graphs = world == 1 and not args.no_graphs
-    if use_graphs:
+    chained_graphs = world > 1 and prefetching and not args.no_graphs
+    if use_graphs or chained_graphs:
         model.embed_opt.use_device_step()      # the Adam step counter must advance inside replayed graphs
     model.train()
     structures = cfg["structures"]
@@ -550,8 +554,6 @@ def run_gpu(args):
             torch.cuda.synchronize()
 
     L = _lib.lib()
-
-    prefetching = world > 1 and not args.no_prefetch
 
     def eager_step(s, p, n, q, upcoming=None):
         return train_step(model, p, n, q, s, reduce_dense, upcoming if prefetching else None)
@@ -577,17 +579,74 @@ def run_gpu(args):
             graphs[s] = (g, static, loss)
         sync_all()
 
+    # Several GPUs: the same, except that a step's graph also holds the side-stream branch that pulls
+    # the NEXT step's rows (forked at the start of the step, joined at its end), and that steps
+    # alternate between two arenas of peer-visible id lists / gradient rows.  So there is one graph
+    # per (structure, arena); the index tensors of step i live in static buffer i % 2 and those of
+    # step i + 1 are copied into the other buffer before the graph of step i is launched.
+    static, chain = [], {}
+    if chained_graphs:
+        max_cols = max(b[3].shape[1] for b in host_batches)
+        for par in range(2):
+            _, p0, n0, q0 = dev_batches[0]
+            static.append((torch.zeros_like(p0), torch.zeros_like(n0),
+                           torch.zeros(q0.shape[0], max_cols, dtype=q0.dtype, device=device)))
+
+        def load_static(par, batch):
+            pos, neg, q = static[par]
+            pos.copy_(batch[1], non_blocking=True)
+            neg.copy_(batch[2], non_blocking=True)
+            q[:, :batch[3].shape[1]].copy_(batch[3], non_blocking=True)
+
+        def start_chain(i, first_batch):
+            """Make step i replayable: its index tensors in static buffer i % 2, their rows pulled by
+            the prefetch branch of one eager step on the other arena."""
+            par = i % 2
+            load_static(par, first_batch)
+            model.embed_opt.reset_prefetch(next_parity=par ^ 1)
+            prev = dev_batches[(i - 1) % pool]
+            train_step(model, prev[1], prev[2], prev[3], prev[0], reduce_dense, static[par] + (None,))
+
+        n_cols = {b[0]: b[3].shape[1] for b in host_batches}
+        start_chain(0, dev_batches[0])
+        pool_handle = torch.cuda.graph_pool_handle()
+        for s in structures:
+            for par in range(2):            # captures alternate between the arenas like the steps do
+                pos, neg, q = static[par]
+                before = L.smore_kernel_launch_count()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, pool=pool_handle):
+                    loss = train_step(model, pos, neg, q[:, :n_cols[s]], s, reduce_dense, static[par ^ 1] + (None,))
+                launches_per_step[s] = L.smore_kernel_launch_count() - before
+                graphs[(s, par)] = (g, loss)
+        sync_all()
+        chain["next"] = 0                   # static buffer 0 holds batch 0 and its rows are staged
+
     def step(s, p, n, q, upcoming=None):
         if not use_graphs:
             return eager_step(s, p, n, q, upcoming)
-        g, static, loss = graphs[s]
-        static[0].copy_(p, non_blocking=True)
-        static[1].copy_(n, non_blocking=True)
-        static[2].copy_(q, non_blocking=True)
+        g, static_in, loss = graphs[s]
+        static_in[0].copy_(p, non_blocking=True)
+        static_in[1].copy_(n, non_blocking=True)
+        static_in[2].copy_(q, non_blocking=True)
         g.replay()
         return loss
 
+    def replay_chained(i, this_structure, next_batch):
+        par = i % 2
+        load_static(par ^ 1, next_batch)
+        g, loss = graphs[(this_structure, par)]
+        g.replay()
+        chain["next"] = i + 1
+        return loss
+
     def run_resident(k0, k):
+        if chained_graphs:
+            if chain.get("next") != k0:
+                start_chain(k0, dev_batches[k0 % pool])
+            for i in range(k0, k0 + k):
+                replay_chained(i, dev_batches[i % pool][0], dev_batches[(i + 1) % pool])
+            return
         for i in range(k0, k0 + k):
             step(*dev_batches[i % pool], upcoming=dev_batches[(i + 1) % pool][1:] + (None,))
 
@@ -603,9 +662,28 @@ def run_gpu(args):
             done.record(copy_stream)
         return s, dev, done
 
+    def prepare_e2e(k0):
+        """Untimed: with chained graphs, stage step k0 (its indices come from the host like all others)."""
+        if chained_graphs:
+            s, dev, done = upload(k0)
+            torch.cuda.current_stream(device).wait_event(done)
+            start_chain(k0, (s,) + tuple(dev))
+
     def run_e2e(k0, k):
         last = 0.0
         main = torch.cuda.current_stream(device)
+        if chained_graphs:
+            # the indices of step i + 1 are uploaded while step i - 1 runs and copied into the free
+            # static buffer just before step i is launched
+            ahead = [upload(k0 + 1), upload(k0 + 2)]
+            for i in range(k0, k0 + k):
+                s_next, dev, done = ahead.pop(0)
+                ahead.append(upload(i + 3))
+                main.wait_event(done)
+                for t in dev:
+                    t.record_stream(main)
+                last = replay_chained(i, host_batches[i % pool][0], (s_next,) + tuple(dev)).item()
+            return last
         nxt = upload(k0)
         for i in range(k0, k0 + k):
             s, dev, done = nxt
@@ -633,16 +711,21 @@ def run_gpu(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync_all()
     e0.record()
+    t_issue = time.perf_counter()
     run_resident(args.warmup, args.steps)
+    t_issue = time.perf_counter() - t_issue     # host time to enqueue the steps (no synchronisation inside)
     e1.record()
     sync_all()
-    if use_graphs:
+    if use_graphs or chained_graphs:
         launches = sum(launches_per_step[dev_batches[i % pool][0]] for i in range(args.warmup, args.warmup + args.steps))
     else:
         launches = L.smore_kernel_launch_count() - launches0
     ms_total = e0.elapsed_time(e1)
     # ---- end-to-end timing: pinned host index tensors in, loss out, every step ----------------------
+    prepare_e2e(0)
     run_e2e(0, min(3, args.warmup))
+    sync_all()
+    prepare_e2e(args.warmup)
     sync_all()
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2.record()
@@ -654,7 +737,9 @@ def run_gpu(args):
         raise RuntimeError("a bulk-copy wait gave up inside a kernel: the timed results are invalid")
     # ---- the same K steps once more, eagerly, with CUDA events around each library call -------------
     # (kernels inside a replayed graph cannot be bracketed by events; the kernels are the same)
-    if use_graphs:
+    if chained_graphs:
+        model.embed_opt.reset_prefetch()
+    if use_graphs or chained_graphs:
         # graph capture emptied the allocator's cache: give eager mode its blocks back first
         for i in range(len(structures)):
             eager_step(*dev_batches[i])
@@ -675,9 +760,19 @@ def run_gpu(args):
         t = torch.tensor([ms_total, ms_e2e], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total, ms_e2e = t.tolist()
-    if rank != 0:
+    def shutdown():
+        torch.cuda.synchronize()
+        if chained_graphs:
+            # CUDA graphs that captured NCCL collectives keep the communicator busy, and destroying the
+            # process group under them blocks; every rank is done communicating here, so leave at once
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
         if world > 1:
             dist.destroy_process_group()
+
+    if rank != 0:
+        shutdown()
         return
 
     peak, peak_kind = load_peaks()
@@ -737,7 +832,9 @@ def run_gpu(args):
         "unit": "queries/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_total / args.steps, 4),
-        "execution": "one captured CUDA graph per query structure, replayed" if use_graphs else "eager launches",
+        "execution": ("one captured CUDA graph per query structure, replayed" if use_graphs else
+                      "one captured CUDA graph per (query structure, arena), replayed; next step's rows prefetched "
+                      "inside the graph" if chained_graphs else "eager launches"),
         "eager_ms_per_step": round(ms_eager / args.steps, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
@@ -759,13 +856,13 @@ def run_gpu(args):
         "kernels": kernels,
         "cpu_baseline": cpu,
         "clocks": clock_summary,
+        "host_issue_ms_per_step": round(1e3 * t_issue / args.steps, 4),
         "last_loss": last_loss,
     }
     if args.dump_kernel_times:
         out["kernel_ms_raw"] = {k: [round(x, 3) for x in v] for k, v in kernel_ms.items()}
     print(json.dumps(out), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    shutdown()
 
 
 def run_reference(args):

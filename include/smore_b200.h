@@ -311,11 +311,20 @@ SMORE_API int smore_fetch_rows(const float* const* shard_ptrs, size_t rows_per_s
  * updates them afterwards would be stale, so owners publish the rows they updated in a step as a
  * bitmap over their shard (smore_shard_mark_dirty: clears the bitmap, then sets one bit per row of
  * uniq[0 .. *n_unique)), and the requester re-pulls exactly the marked rows after the step's last
- * barrier (smore_refresh_rows; dirty_ptrs = device array of the ranks' bitmaps, peer-mapped).
- * The result equals fetching everything after the barrier. */
+ * barrier (smore_refresh_rows; dirty_ptrs = device array of the n_ranks bitmaps, peer-mapped;
+ * bitmap_scratch = n_ranks * ceil(rows_per_shard / 32) words of local memory that receive a copy
+ * of all bitmaps first).  The result equals fetching everything after the barrier.
+ * smore_fetch_rows_background is smore_fetch_rows on at most max_ctas thread blocks, so that the
+ * kernels of the current step, launched afterwards on another stream, find room on every SM
+ * instead of queueing behind the copy (one block per SM keeps NVLink busy). */
+SMORE_API int smore_fetch_rows_background(const float* const* shard_ptrs, size_t rows_per_shard,
+                                const int64_t* uniq, const int32_t* n_unique, size_t capacity,
+                                size_t width, float* staging, size_t max_ctas, void* stream);
+
 SMORE_API int smore_refresh_rows(const float* const* shard_ptrs, const uint32_t* const* dirty_ptrs,
-                       size_t rows_per_shard, const int64_t* uniq, const int32_t* n_unique,
-                       size_t capacity, size_t width, float* staging, void* stream);
+                       size_t n_ranks, size_t rows_per_shard, const int64_t* uniq,
+                       const int32_t* n_unique, size_t capacity, size_t width, float* staging,
+                       uint32_t* bitmap_scratch, void* stream);
 SMORE_API int smore_shard_mark_dirty(const int64_t* uniq, const int32_t* n_unique, size_t capacity,
                            size_t shard_rows, uint32_t* dirty, void* stream);
 
@@ -344,6 +353,16 @@ SMORE_API int smore_shard_reduce_update_rows(float* table, float* m, float* v, c
                                    const int32_t* list_bounds, size_t n_ranks, size_t n_plans,
                                    const int32_t* plan_caps, size_t width, double lr, double beta1,
                                    double beta2, double eps, int64_t step, int squeeze, void* stream);
+
+/* The same with the step-dependent scalars read from device memory (see smore_adam_step_scalars),
+ * for hosts that replay a captured CUDA graph step after step. */
+SMORE_API int smore_shard_reduce_update_rows_dev(float* table, float* m, float* v, const int64_t* uniq,
+                                       const int32_t* counts, const int32_t* src, const int32_t* n_unique,
+                                       size_t capacity, const float* const* grad_ptrs, const int64_t* ids,
+                                       const int32_t* list_bounds, size_t n_ranks, size_t n_plans,
+                                       const int32_t* plan_caps, size_t width, double lr, double beta1,
+                                       double beta2, double eps, const float* step_scalars, int squeeze,
+                                       void* stream);
 
 #ifdef __cplusplus
 }

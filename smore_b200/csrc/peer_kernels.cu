@@ -113,12 +113,23 @@ __global__ void __launch_bounds__(256)
 }
 
 // Rows that were pulled into `staging` BEFORE their owners finished the previous step's update may
-// be stale (or torn).  Owners publish the set of rows they updated as a bitmap over their shard;
-// this kernel re-pulls exactly those rows.  One warp per distinct row: a 4-byte peer read of the
-// bitmap word, then, for the ~10 % that are marked, the row copy.
+// be stale (or torn).  Owners publish the set of rows they updated as a bitmap over their shard.
+// pull_bitmaps_kernel copies every rank's bitmap into local memory (a few MB in all, one bulk
+// transfer instead of one 4-byte peer read per row); refresh_rows_kernel then tests each distinct
+// row of the step against the local copy and re-pulls exactly the marked rows.
 __global__ void __launch_bounds__(256)
-    refresh_rows_kernel(const float* const* __restrict__ shard_ptrs, const uint32_t* const* __restrict__ dirty_ptrs,
-                        size_t rows_per_shard, const int64_t* __restrict__ uniq,
+    pull_bitmaps_kernel(const uint32_t* const* __restrict__ dirty_ptrs, int n_ranks, size_t words,
+                        uint32_t* __restrict__ local) {
+  const size_t total = (size_t)n_ranks * words;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t g = i / words;
+    local[i] = dirty_ptrs[g][i - g * words];
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    refresh_rows_kernel(const float* const* __restrict__ shard_ptrs, const uint32_t* __restrict__ dirty_local,
+                        size_t words, size_t rows_per_shard, const int64_t* __restrict__ uniq,
                         const int32_t* __restrict__ n_unique, int w4, float4* __restrict__ staging) {
   const int lane = threadIdx.x & 31;
   const size_t nu = (size_t)max(n_unique[0], 0);
@@ -131,7 +142,7 @@ __global__ void __launch_bounds__(256)
       const size_t id = (size_t)uniq[u0 + lane];
       owner = id / rows_per_shard;
       local = id - owner * rows_per_shard;
-      marked = (dirty_ptrs[owner][local >> 5] >> (local & 31)) & 1u;
+      marked = (dirty_local[owner * words + (local >> 5)] >> (local & 31)) & 1u;
     }
     unsigned todo = __ballot_sync(0xffffffffu, marked);
     while (todo) {
@@ -326,8 +337,9 @@ using namespace smore;
 
 extern "C" {
 
-int smore_fetch_rows(const float* const* shard_ptrs, size_t rows_per_shard, const int64_t* uniq,
-                     const int32_t* n_unique, size_t capacity, size_t width, float* staging, void* stream) {
+static int fetch_rows_impl(const float* const* shard_ptrs, size_t rows_per_shard, const int64_t* uniq,
+                           const int32_t* n_unique, size_t capacity, size_t width, float* staging, size_t max_ctas,
+                           void* stream) {
   if (capacity == 0) return SMORE_OK;
   if (!shard_ptrs || !uniq || !n_unique || !staging) return fail(SMORE_ERR_NULL, "fetch_rows: NULL pointer");
   if (rows_per_shard == 0 || width == 0 || (width & 3) || width > 1024 || !aligned16(staging))
@@ -336,28 +348,48 @@ int smore_fetch_rows(const float* const* shard_ptrs, size_t rows_per_shard, cons
   cudaStream_t st = (cudaStream_t)stream;
   const int w4 = (int)(width >> 2);
   float4* out = reinterpret_cast<float4*>(staging);
+  const auto grid = [&](size_t warp_items) {
+    const int g = grid_warps(warp_items);
+    return max_ctas ? (int)std::min<size_t>((size_t)g, max_ctas) : g;
+  };
   if (w4 <= 32)
-    fetch_rows_kernel<1, 8><<<grid_warps((capacity + 7) / 8), 256, 0, st>>>(shard_ptrs, rows_per_shard, uniq, n_unique, w4, out);
+    fetch_rows_kernel<1, 8><<<grid((capacity + 7) / 8), 256, 0, st>>>(shard_ptrs, rows_per_shard, uniq, n_unique, w4, out);
   else if (w4 <= 64)
-    fetch_rows_kernel<2, 4><<<grid_warps((capacity + 3) / 4), 256, 0, st>>>(shard_ptrs, rows_per_shard, uniq, n_unique, w4, out);
+    fetch_rows_kernel<2, 4><<<grid((capacity + 3) / 4), 256, 0, st>>>(shard_ptrs, rows_per_shard, uniq, n_unique, w4, out);
   else if (w4 <= 128)
-    fetch_rows_kernel<4, 4><<<grid_warps((capacity + 3) / 4), 256, 0, st>>>(shard_ptrs, rows_per_shard, uniq, n_unique, w4, out);
+    fetch_rows_kernel<4, 4><<<grid((capacity + 3) / 4), 256, 0, st>>>(shard_ptrs, rows_per_shard, uniq, n_unique, w4, out);
   else
-    fetch_rows_kernel<8, 2><<<grid_warps((capacity + 1) / 2), 256, 0, st>>>(shard_ptrs, rows_per_shard, uniq, n_unique, w4, out);
+    fetch_rows_kernel<8, 2><<<grid((capacity + 1) / 2), 256, 0, st>>>(shard_ptrs, rows_per_shard, uniq, n_unique, w4, out);
   return check_launch("fetch_rows_kernel");
 }
 
-int smore_refresh_rows(const float* const* shard_ptrs, const uint32_t* const* dirty_ptrs, size_t rows_per_shard,
-                       const int64_t* uniq, const int32_t* n_unique, size_t capacity, size_t width, float* staging,
-                       void* stream) {
+int smore_fetch_rows(const float* const* shard_ptrs, size_t rows_per_shard, const int64_t* uniq,
+                     const int32_t* n_unique, size_t capacity, size_t width, float* staging, void* stream) {
+  return fetch_rows_impl(shard_ptrs, rows_per_shard, uniq, n_unique, capacity, width, staging, 0, stream);
+}
+
+int smore_fetch_rows_background(const float* const* shard_ptrs, size_t rows_per_shard, const int64_t* uniq,
+                                const int32_t* n_unique, size_t capacity, size_t width, float* staging,
+                                size_t max_ctas, void* stream) {
+  if (max_ctas == 0) return fail(SMORE_ERR_BAD_SHAPE, "fetch_rows_background: max_ctas must be positive");
+  return fetch_rows_impl(shard_ptrs, rows_per_shard, uniq, n_unique, capacity, width, staging, max_ctas, stream);
+}
+
+int smore_refresh_rows(const float* const* shard_ptrs, const uint32_t* const* dirty_ptrs, size_t n_ranks,
+                       size_t rows_per_shard, const int64_t* uniq, const int32_t* n_unique, size_t capacity,
+                       size_t width, float* staging, uint32_t* bitmap_scratch, void* stream) {
   if (capacity == 0) return SMORE_OK;
-  if (!shard_ptrs || !dirty_ptrs || !uniq || !n_unique || !staging)
+  if (!shard_ptrs || !dirty_ptrs || !uniq || !n_unique || !staging || !bitmap_scratch)
     return fail(SMORE_ERR_NULL, "refresh_rows: NULL pointer");
-  if (rows_per_shard == 0 || width == 0 || (width & 3) || !aligned16(staging))
+  if (n_ranks == 0 || rows_per_shard == 0 || width == 0 || (width & 3) || !aligned16(staging))
     return fail(SMORE_ERR_BAD_SHAPE, "refresh_rows: width must be a multiple of 4 floats; staging 16-byte aligned");
-  refresh_rows_kernel<<<grid_warps(capacity), 256, 0, (cudaStream_t)stream>>>(
-      shard_ptrs, dirty_ptrs, rows_per_shard, uniq, n_unique, (int)(width >> 2), reinterpret_cast<float4*>(staging));
-  return check_launch("refresh_rows_kernel");
+  const size_t words = (rows_per_shard + 31) / 32;
+  cudaStream_t st = (cudaStream_t)stream;
+  pull_bitmaps_kernel<<<grid_threads(n_ranks * words), 256, 0, st>>>(dirty_ptrs, (int)n_ranks, words, bitmap_scratch);
+  refresh_rows_kernel<<<grid_warps(capacity), 256, 0, st>>>(shard_ptrs, bitmap_scratch, words, rows_per_shard, uniq,
+                                                            n_unique, (int)(width >> 2),
+                                                            reinterpret_cast<float4*>(staging));
+  return check_launch("refresh_rows kernels", 2);
 }
 
 int smore_shard_mark_dirty(const int64_t* uniq, const int32_t* n_unique, size_t capacity, size_t shard_rows,
@@ -395,16 +427,16 @@ int smore_shard_record_sources(const int32_t* slot, size_t n, int32_t* src, void
   return check_launch("shard_record_sources_kernel");
 }
 
-int smore_shard_reduce_update_rows(float* table, float* m, float* v, const int64_t* uniq, const int32_t* counts,
+static int shard_reduce_update_impl(float* table, float* m, float* v, const int64_t* uniq, const int32_t* counts,
                                    const int32_t* src, const int32_t* n_unique, size_t capacity,
                                    const float* const* grad_ptrs, const int64_t* ids, const int32_t* list_bounds,
                                    size_t n_ranks, size_t n_plans, const int32_t* plan_caps, size_t width,
-                                   double lr, double beta1, double beta2, double eps, int64_t step, int squeeze,
-                                   void* stream) {
+                                   double lr, double beta1, double beta2, double eps, int64_t step,
+                                   const float* step_scalars, int squeeze, void* stream) {
   if (capacity == 0) return SMORE_OK;
   if (!table || !m || !v || !uniq || !counts || !src || !n_unique || !grad_ptrs || !ids || !list_bounds)
     return fail(SMORE_ERR_NULL, "shard_reduce_update_rows: NULL pointer");
-  if (step < 1) return fail(SMORE_ERR_BAD_SHAPE, "adam step must be >= 1");
+  if (!step_scalars && step < 1) return fail(SMORE_ERR_BAD_SHAPE, "adam step must be >= 1");
   if (width == 0 || (width & 3) || width > 1024 || !aligned16(table) || !aligned16(m) || (!squeeze && !aligned16(v)))
     return fail(SMORE_ERR_BAD_SHAPE, "shard_reduce_update_rows: width must be a multiple of 4 floats, at most 1024");
   ReduceArgs r;
@@ -415,7 +447,8 @@ int smore_shard_reduce_update_rows(float* table, float* m, float* v, const int64
   r.n_lists = (int)(n_ranks * n_plans);
   UpdateArgs a;
   a.table = table; a.m = m; a.v = v; a.uniq = uniq; a.g_rows = nullptr; a.n_unique = n_unique; a.width = width;
-  set_hyper(a, lr, beta1, beta2, eps, step, squeeze);
+  set_hyper(a, lr, beta1, beta2, eps, step_scalars ? 1 : step, squeeze);
+  a.dyn = step_scalars;
   cudaStream_t st = (cudaStream_t)stream;
   const int grid = grid_warps(capacity);
   const size_t w4 = width >> 2;
@@ -428,6 +461,29 @@ int smore_shard_reduce_update_rows(float* table, float* m, float* v, const int64
   else { REDUCE(8); }
 #undef REDUCE
   return check_launch("shard_reduce_update_kernel");
+}
+
+int smore_shard_reduce_update_rows(float* table, float* m, float* v, const int64_t* uniq, const int32_t* counts,
+                                   const int32_t* src, const int32_t* n_unique, size_t capacity,
+                                   const float* const* grad_ptrs, const int64_t* ids, const int32_t* list_bounds,
+                                   size_t n_ranks, size_t n_plans, const int32_t* plan_caps, size_t width,
+                                   double lr, double beta1, double beta2, double eps, int64_t step, int squeeze,
+                                   void* stream) {
+  return shard_reduce_update_impl(table, m, v, uniq, counts, src, n_unique, capacity, grad_ptrs, ids, list_bounds,
+                                  n_ranks, n_plans, plan_caps, width, lr, beta1, beta2, eps, step, nullptr, squeeze,
+                                  stream);
+}
+
+int smore_shard_reduce_update_rows_dev(float* table, float* m, float* v, const int64_t* uniq, const int32_t* counts,
+                                       const int32_t* src, const int32_t* n_unique, size_t capacity,
+                                       const float* const* grad_ptrs, const int64_t* ids,
+                                       const int32_t* list_bounds, size_t n_ranks, size_t n_plans,
+                                       const int32_t* plan_caps, size_t width, double lr, double beta1, double beta2,
+                                       double eps, const float* step_scalars, int squeeze, void* stream) {
+  if (!step_scalars) return fail(SMORE_ERR_NULL, "shard_reduce_update_rows_dev: step_scalars is NULL");
+  return shard_reduce_update_impl(table, m, v, uniq, counts, src, n_unique, capacity, grad_ptrs, ids, list_bounds,
+                                  n_ranks, n_plans, plan_caps, width, lr, beta1, beta2, eps, 1, step_scalars, squeeze,
+                                  stream);
 }
 
 }  // extern "C"

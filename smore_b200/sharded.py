@@ -120,6 +120,9 @@ def exchange_handles(my_handles, group=None):
     return out
 
 
+BACKGROUND_CTAS = 148     # thread blocks of a prefetch copy: one per SM
+
+
 class ShardedTable(object):
     """The local shard (table + Adam state), two peer-visible per-step arenas (steps alternate
     between them, so the next step's id list can be prepared while owners still read the current
@@ -140,6 +143,7 @@ class ShardedTable(object):
         self.table = self._table_block.view(self.device, 0, (self.S, width), torch.float32)
         self.dirty = self._dirty_block.view(self.device, 0, ((max(self.S, 1) + 31) // 32,), torch.int32)
         self.dirty.zero_()
+        self.bitmap_scratch = torch.empty(world * self.dirty.numel(), dtype=torch.int32, device=self.device)
         self.m = torch.zeros(self.S, width, device=self.device)
         self.v = torch.zeros(self.S, 1, device=self.device) if squeeze else torch.zeros(self.S, width, device=self.device)
         lay = self.layout
@@ -267,9 +271,16 @@ class _ShardedPlan(object):
                                                self.n_unique.data_ptr(), workspace.data_ptr(), workspace.numel(), st),
                            "smore_unique_rows")
             with _lib.timed("fetch_rows"):
-                _lib.check(L.smore_fetch_rows(shard.d_shard_ptrs.data_ptr(), shard.S, self.uniq.data_ptr(),
-                                              self.n_unique.data_ptr(), self.n, shard.width, self.staging.data_ptr(),
-                                              st), "smore_fetch_rows")
+                if buffers is None:
+                    _lib.check(L.smore_fetch_rows(shard.d_shard_ptrs.data_ptr(), shard.S, self.uniq.data_ptr(),
+                                                  self.n_unique.data_ptr(), self.n, shard.width,
+                                                  self.staging.data_ptr(), st), "smore_fetch_rows")
+                else:
+                    # a prefetch shares the GPU with the step in progress: one thread block per SM
+                    _lib.check(L.smore_fetch_rows_background(shard.d_shard_ptrs.data_ptr(), shard.S,
+                                                             self.uniq.data_ptr(), self.n_unique.data_ptr(), self.n,
+                                                             shard.width, self.staging.data_ptr(), BACKGROUND_CTAS,
+                                                             st), "smore_fetch_rows_background")
             _lib.check(L.smore_zero_shared_rows(self.g_rows.data_ptr(), self.counts.data_ptr(),
                                                 self.n_unique.data_ptr(), self.n, shard.width, st),
                        "smore_zero_shared_rows")
@@ -290,8 +301,9 @@ class _ShardedPlan(object):
         shard = opt.shard
         with torch.cuda.device(shard.device), _lib.timed("refresh_rows"):
             _lib.check(_lib.lib().smore_refresh_rows(shard.d_shard_ptrs.data_ptr(), shard.d_dirty_ptrs.data_ptr(),
-                                                     shard.S, self.uniq.data_ptr(), self.n_unique.data_ptr(), self.n,
-                                                     shard.width, self.staging.data_ptr(),
+                                                     shard.world, shard.S, self.uniq.data_ptr(),
+                                                     self.n_unique.data_ptr(), self.n, shard.width,
+                                                     self.staging.data_ptr(), shard.bitmap_scratch.data_ptr(),
                                                      _stream_ptr(shard.device)), "smore_refresh_rows")
 
     def slot_of(self, lookup):
@@ -372,14 +384,21 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         nu = self.shard.nuniq_all[self.parity]
         self._ready, self._prefetched = self._prefetched, None
         if self._ready is not None and self._ready[0].parity == self.parity:
-            # list 0 of this arena was already filled by the prefetch; the others start unused
-            torch.cuda.current_stream(self.shard.device).wait_event(self._ready[1])
+            # list 0 of this arena was already filled by the prefetch (apply_grad waited for it);
+            # the others start unused
             nu[2:].zero_()
         else:
             # no list of this rank is in use until a plan of this step fills it (owners read these
             # counters only after the step's first barrier)
             self._ready = None
             nu.zero_()
+
+    def reset_prefetch(self, next_parity=None):
+        """Forget anything prepared for coming steps.  `next_parity` (0 or 1) chooses the arena the
+        next step will use, for hosts that replay per-arena CUDA graphs and must line them up."""
+        self._prefetched = self._ready = None
+        if next_parity is not None:
+            self.parity = int(next_parity) ^ 1     # zero_grad flips it
 
     def prefetch(self, id_tensors, after=None):
         """Prepare the NEXT step's first lookup group now, on a side stream: `id_tensors` are the
@@ -495,6 +514,10 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         self.barrier()              # every rank's id lists and gradient rows are complete
         self.owner_update(lr)
         self.barrier()              # every shard is updated; this step's arena may be overwritten
+        if self._prefetched is not None:
+            # the copy prepared for the next step joins the step's stream here (inside a CUDA graph
+            # capture a forked stream has to re-join before the capture ends)
+            torch.cuda.current_stream(self.shard.device).wait_event(self._prefetched[1])
         self._drop_plans()
 
     def owner_update(self, lr):
@@ -524,7 +547,18 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
                 _lib.check(L.smore_shard_mark_dirty(self._o_uniq.data_ptr(), self._o_nuniq.data_ptr(), n_in,
                                                     max(sh.S, 1), sh.dirty.data_ptr(), st), "smore_shard_mark_dirty")
             _lib.note("n_unique_owner", self._o_nuniq[0])
+            dev_step = getattr(self, "_step_dev", None) is not None
+            if dev_step:
+                self._advance_device_step(lr)
             with _lib.timed("shard_reduce_update"):
+                if dev_step:
+                    _lib.check(L.smore_shard_reduce_update_rows_dev(
+                        sh.table.data_ptr(), sh.m.data_ptr(), sh.v.data_ptr(), self._o_uniq.data_ptr(),
+                        self._o_counts.data_ptr(), self._o_src.data_ptr(), self._o_nuniq.data_ptr(), n_in,
+                        sh.d_grad_ptrs[par].data_ptr(), self._in_ids.data_ptr(), self._in_bounds.data_ptr(), G, P,
+                        self._caps, sh.width, float(lr), 0.9, 0.999, eps, self._step_scalars.data_ptr(),
+                        int(self.squeeze), st), "smore_shard_reduce_update_rows_dev")
+                    return
                 _lib.check(L.smore_shard_reduce_update_rows(
                     sh.table.data_ptr(), sh.m.data_ptr(), sh.v.data_ptr(), self._o_uniq.data_ptr(),
                     self._o_counts.data_ptr(), self._o_src.data_ptr(), self._o_nuniq.data_ptr(), n_in,
