@@ -532,6 +532,195 @@ __global__ void __launch_bounds__(kRowCtaThreads)
 }
 
 // ----------------------------------------------------------------------------------------
+// Row-stream backward on the same bulk-copy ring.  A warp takes a contiguous run of rows; each
+// row is copied into a ring slot, its gradient is computed IN PLACE over the row (every lane
+// overwrites exactly the 16-byte pieces it read), and lane 0 sends the slot to the gradient
+// buffer with one bulk store - or one bulk floating-point add where several positions of the
+// step share the destination row.  The slot is refilled once that transfer has read it.
+// NB query branches (union queries) are applied to every row; their row gradients are summed in
+// registers before the slot is written.  The query gradients stay in registers over the warp's
+// run and are folded over the CTA's warps through the ring at the end, in warp order.
+// ----------------------------------------------------------------------------------------
+
+template <class Term, int NB, int NCH>
+__global__ void __launch_bounds__(kRowCtaThreads, 2)
+    row_backward_bulk_kernel(RowArgs a, RowGradArgs ga, int stages) {
+  constexpr int NG = NB * Term::kNOut;
+  extern __shared__ __align__(128) unsigned char bulk_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int b = blockIdx.x / a.chunks, c = blockIdx.x - b * a.chunks;
+  const int dim4 = a.dim >> 2;
+  const unsigned row_bytes = (unsigned)dim4 * Term::kMul * 16u;
+  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(bulk_smem) + warp * stages;
+  float4* sq = reinterpret_cast<float4*>(bulk_smem + bulk_ring_offset(stages));   // [kNQ][NB][dim4]
+  unsigned char* ring_all = reinterpret_cast<unsigned char*>(sq + (size_t)Term::kNQ * NB * dim4);
+  unsigned char* ring = ring_all + (size_t)warp * stages * row_bytes;
+  if (lane == 0) {
+    for (int s = 0; s < stages; ++s) bulk::barrier_init(bars + s, 1);
+    bulk::fence_barrier_init();
+  }
+  {
+    const float4* p0 = reinterpret_cast<const float4*>(a.first + (size_t)b * NB * a.dim);
+    const float4* p1 = reinterpret_cast<const float4*>(a.second + (size_t)b * NB * a.dim);
+    for (int i = threadIdx.x; i < NB * dim4; i += kRowCtaThreads) {
+      sq[i] = __ldg(p0 + i);
+      if (Term::kNQ == 2) sq[NB * dim4 + i] = __ldg(p1 + i);
+    }
+  }
+  __syncthreads();
+  const float4* sq0 = sq;
+  const float4* sq1 = Term::kNQ == 2 ? sq + NB * dim4 : sq;
+
+  float4 gq0[NB][NCH], gq1[NB][NCH];
+#pragma unroll
+  for (int u = 0; u < NB; ++u)
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) gq0[u][j] = gq1[u][j] = z4;
+
+  const int r_begin = c * a.rows_per_cta;
+  const int r_end = min(a.K, r_begin + a.rows_per_cta);
+  const int per_warp = (r_end - r_begin + kRowCtaWarps - 1) / kRowCtaWarps;
+  const int w_begin = r_begin + warp * per_warp;
+  const int n = max(0, min(r_end, w_begin + per_warp) - w_begin);
+  const size_t pos0 = (size_t)b * a.K + w_begin;
+  const unsigned char* ent = reinterpret_cast<const unsigned char*>(a.ent);
+  unsigned char* gbase = reinterpret_cast<unsigned char*>(ga.slot ? ga.g_rows : ga.g_ent);
+
+  // per-lane scalars of one batch of 32 rows: source row, destination row (-1: none), whether the
+  // destination is written by this position alone, output gradients of every branch
+  struct Meta {
+    long long src, dst;
+    int single;
+    float g[NG];
+  };
+  auto load_meta = [&](int first_t) {
+    Meta m;
+    m.src = 0;
+    m.dst = -1;
+    m.single = 1;
+#pragma unroll
+    for (int i = 0; i < NG; ++i) m.g[i] = 0.f;
+    const int t = first_t + lane;
+    if (t < n) {
+      const size_t pos = pos0 + t;
+      m.src = a.idx ? (long long)a.idx[pos] : (long long)pos;
+      m.dst = (long long)pos;
+      if (ga.slot) {
+        const int32_t sl = ga.slot[pos];
+        m.dst = sl;
+        m.single = (sl >= 0 && ga.slot_count != nullptr) ? (ga.slot_count[sl] == 1) : 0;
+      }
+#pragma unroll
+      for (int u = 0; u < NB; ++u) {
+        const size_t o = ((size_t)b * NB + u) * a.K + (w_begin + t);
+        m.g[u * Term::kNOut] = ga.gout0[o];
+        if (Term::kNOut == 2) m.g[u * Term::kNOut + Term::kNOut - 1] = ga.gout1[o];
+      }
+    }
+    return m;
+  };
+  Meta cur = load_meta(0), nxt = cur;
+
+  const int ahead = min(stages - 1, n);   // one slot always belongs to the store in flight
+  for (int t = 0; t < ahead; ++t) {
+    const long long row = __shfl_sync(0xffffffffu, cur.src, t);
+    if (lane == 0) {
+      bulk::barrier_expect(bars + t, row_bytes);
+      bulk::load(ring + (size_t)t * row_bytes, ent + (size_t)row * row_bytes, row_bytes, bars + t);
+    }
+  }
+  int slot = 0;
+  unsigned parity = 0;
+  for (int t = 0; t < n; ++t) {
+    const int tl = t & 31;
+    if (tl == 0) nxt = load_meta(t + 32);
+    bool ok = bulk::barrier_wait(bars + slot, parity);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) {
+      if (lane == 0) atomicOr(&g_async_status, 1);
+      for (int k = 1; k < stages - 1 && t + k < n; ++k) {
+        const int s2 = (slot + k) % stages;
+        bulk::barrier_wait(bars + s2, s2 > slot ? parity : parity ^ 1u);
+      }
+      break;
+    }
+    float g[NG];
+#pragma unroll
+    for (int i = 0; i < NG; ++i) g[i] = __shfl_sync(0xffffffffu, cur.g[i], tl);
+    const long long dst = __shfl_sync(0xffffffffu, cur.dst, tl);
+    const int single = __shfl_sync(0xffffffffu, cur.single, tl);
+    float4* row4 = reinterpret_cast<float4*>(ring + (size_t)slot * row_bytes);
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int d4 = lane + 32 * j;
+      if (d4 < dim4) {
+        const float4 e0 = row4[d4];
+        const float4 e1 = Term::kMul == 2 ? row4[dim4 + d4] : e0;
+        float4 ge0 = z4, ge1 = z4;
+#pragma unroll
+        for (int u = 0; u < NB; ++u)
+          bwd4<Term>(g + u * Term::kNOut, e0, e1, sq0[u * dim4 + d4], sq1[u * dim4 + d4], ge0, ge1, gq0[u][j],
+                     gq1[u][j]);
+        row4[d4] = ge0;
+        if (Term::kMul == 2) row4[dim4 + d4] = ge1;
+      }
+    }
+    bulk::fence_async_shared();   // the gradient row is visible to the copy engine
+    __syncwarp();
+    // refill target: the slot of the previous row, whose transfer was committed one row ago
+    const int tn = t + stages - 1;
+    const long long next_row = __shfl_sync(0xffffffffu, (tn >> 5) == (t >> 5) ? cur.src : nxt.src, tn & 31);
+    if (lane == 0) {
+      if (dst >= 0) {
+        unsigned char* out = gbase + (size_t)dst * row_bytes;
+        if (single) bulk::store(out, row4, row_bytes);
+        else bulk::reduce_add_f32(out, row4, row_bytes);
+      }
+      bulk::commit_group();
+      if (tn < n) {
+        bulk::wait_group_read<1>();   // all transfers but the one just committed have read their slots
+        const int s2 = slot == 0 ? stages - 1 : slot - 1;
+        bulk::barrier_expect(bars + s2, row_bytes);
+        bulk::load(ring + (size_t)s2 * row_bytes, ent + (size_t)next_row * row_bytes, row_bytes, bars + s2);
+      }
+    }
+    if (tl == 31) cur = nxt;
+    if (++slot == stages) {
+      slot = 0;
+      parity ^= 1u;
+    }
+  }
+  if (lane == 0) bulk::wait_group<0>();   // every gradient row has left shared memory and landed
+  __syncthreads();
+
+  // fold the warps' query gradients through the (now idle) ring, in warp order
+  float4* red = reinterpret_cast<float4*>(ring_all);
+  const size_t per_warp4 = (size_t)NB * Term::kNQ * dim4;
+#pragma unroll
+  for (int u = 0; u < NB; ++u)
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int d4 = lane + 32 * j;
+      if (d4 < dim4) {
+        red[warp * per_warp4 + (size_t)u * Term::kNQ * dim4 + d4] = gq0[u][j];
+        if (Term::kNQ == 2) red[warp * per_warp4 + (size_t)u * Term::kNQ * dim4 + dim4 + d4] = gq1[u][j];
+      }
+    }
+  __syncthreads();
+  for (size_t i = threadIdx.x; i < per_warp4; i += kRowCtaThreads) {
+    float4 acc = red[i];
+    for (int w = 1; w < kRowCtaWarps; ++w) add4(acc, red[w * per_warp4 + i]);
+    const size_t u = i / ((size_t)Term::kNQ * dim4), rem = i - u * Term::kNQ * dim4;
+    const bool second = rem >= (size_t)dim4;
+    float* base = second ? ga.g_second : ga.g_first;
+    float4* out = reinterpret_cast<float4*>(base + ((size_t)b * NB + u) * a.dim) + (rem - (second ? dim4 : 0));
+    if (ga.query_atomic) atomicAdd(out, acc);
+    else *out = acc;
+  }
+}
+
+// ----------------------------------------------------------------------------------------
 // Union queries: NB branches of every query scored against the same candidate rows.
 // The reference runs the op once per branch and stacks the results (a Python loop over the
 // branch axis of a 4-D query operand); here one pass over the rows serves all branches, and the
@@ -834,6 +1023,36 @@ static bool shared_shape(const Shape& s, bool aligned) {
          ((s.dim >> 2) + kGradCols - 1) / kGradCols <= 65535;
 }
 
+// Launches row_backward_bulk_kernel when the row width suits it.  Returns 1 when launched, 0 when
+// the caller should use another kernel, a negative status on failure.
+template <class Term, int NB>
+static int launch_backward_bulk(const Shape& s, RowArgs a, RowGradArgs ga, int nch, cudaStream_t st) {
+  // Measured on B200: ahead of the column-thread kernel for rows of 2 KB and more (RotatE rows of
+  // 4000 B: 1.59 ms against 1.67 ms per 1M rows); for 1600-byte rows it executes more instructions
+  // per row (waits, per-row scalars) than that kernel and ends level with it, so those stay there.
+  if (nch != 8) return 0;
+  const size_t row_bytes = s.dim * Term::kMul * sizeof(float);
+  const int need = (NB * Term::kNQ + Term::kMul - 1) / Term::kMul;   // ring must hold the final fold
+  const int stages = std::max(3, need);
+  const size_t q_bytes = (size_t)NB * Term::kNQ * s.dim * sizeof(float);
+  const size_t smem = bulk_ring_offset(stages) + q_bytes + (size_t)kRowCtaWarps * stages * row_bytes;
+  if (smem > 110 * 1024) return 0;
+  a.rows_per_cta = (int)std::min<size_t>(s.num, 512);
+  a.chunks = (int)((s.num + a.rows_per_cta - 1) / a.rows_per_cta);
+  ga.query_atomic = a.chunks > 1;
+  if (a.chunks > 1) {
+    const size_t bytes = s.bsize * NB * s.dim * sizeof(float);
+    if (cudaMemsetAsync(ga.g_first, 0, bytes, st) != cudaSuccess ||
+        (Term::kNQ == 2 && cudaMemsetAsync(ga.g_second, 0, bytes, st) != cudaSuccess))
+      return fail(SMORE_ERR_CUDA, "row_backward_bulk_kernel: cudaMemsetAsync failed");
+  }
+  auto kern = row_backward_bulk_kernel<Term, NB, 8>;
+  if (int rc = allow_large_smem(kern, 110 * 1024)) return rc;
+  kern<<<(unsigned)(s.bsize * a.chunks), kRowCtaThreads, smem, st>>>(a, ga, stages);
+  if (int rc = check_launch("row_backward_bulk_kernel")) return rc;
+  return 1;
+}
+
 template <class Term>
 static int launch_forward(const Shape& s, const float* ent, const int64_t* idx, const float* first,
                           const float* second, float* dst0, float* dst1, cudaStream_t st) {
@@ -894,6 +1113,7 @@ static int launch_backward(const Shape& s, const float* gout0, const float* gout
   if (p.chunks > 0) {
     RowArgs a{ent, idx, first, second, (int)s.num, (int)s.dim, p.rows_per_cta, p.chunks, p.wrows};
     RowGradArgs ga{gout0, gout1, g_ent, slot, slot_count, g_rows, g_first, g_second, p.chunks > 1};
+    if (int rc = launch_backward_bulk<Term, 1>(s, a, ga, p.nch, st)) return rc < 0 ? rc : SMORE_OK;
     if (p.chunks > 1) {
       cudaMemsetAsync(g_first, 0, s.bsize * s.dim * sizeof(float), st);
       if (Term::kNQ == 2) cudaMemsetAsync(g_second, 0, s.bsize * s.dim * sizeof(float), st);
