@@ -258,6 +258,28 @@ SMORE_API int smore_sparse_update_rows_dev(int opt_id, float* table, float* m, f
                                  const float* step_scalars, int squeeze, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Evaluation: filtered ranks of the answers of each query among all candidates.
+ * The reference (train_process.py:113-146) argsorts the [1, N] logits of a query, scatters the
+ * permutation into a rank per entity, takes the ranks of the easy and hard answers, sorts them and
+ * subtracts each one's position in that sorted list ("filtered setting").  Only the answers' ranks
+ * are used, so this entry point counts instead of sorting N values:
+ *   ranks[p] = 1 + #{candidates ahead of answer p} - #{answers of the same query ahead of it}
+ * where "ahead" means a higher logit, or an equal logit and a lower candidate id (the order of a
+ * stable descending sort; torch.argsort leaves ties unspecified).
+ *   logits      [n_queries, n_candidates] fp32 (NaN counts as -inf)
+ *   answer_ptr  [n_queries + 1] int64, CSR offsets into answer_ids (device memory)
+ *   answer_ids  [n_answers] candidate ids: per query the easy and the hard answers in any order;
+ *               the caller keeps the ranks of the hard ones
+ *   ranks       [n_answers] int64, in the order of answer_ids
+ *   max_answers the longest answer list (host value, <= 8192; SMORE_ERR_TOO_LARGE beyond)
+ * workspace: smore_filtered_ranks_workspace_bytes(n_answers) bytes, 256-byte aligned. */
+SMORE_API size_t smore_filtered_ranks_workspace_bytes(size_t n_answers);
+SMORE_API int smore_filtered_ranks(const float* logits, size_t n_queries, size_t n_candidates,
+                         const int64_t* answer_ptr, const int64_t* answer_ids, size_t n_answers,
+                         size_t max_answers, int64_t* ranks, void* workspace, size_t workspace_bytes,
+                         void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Dot-product scoring of B queries against ONE shared set of K candidate rows on the tensor
  * cores (tcgen05 / TMEM through CUTLASS sm100 templates).  DistMult and ComplEx scores are inner
  * products (dist_kernel.h:187-204, 324-349); with shared candidates the op and both gradients are

@@ -121,3 +121,32 @@ def adagrad_rows(table, state, indices, grad, lr, squeeze):
 
 def sgd_rows(table, indices, grad, lr):
     table.index_add_(0, indices, -lr * grad)
+
+
+def reference_filtered_ranks(negative_logit, easy_answer, hard_answer):
+    """The ranking block of the reference's test step for one query, as torch ops on the CPU
+    (smore/training/train_process.py:113-141): argsort of the [1, N] logits (descending), ranks by
+    scatter, the answers' ranks sorted, minus their position in that list, plus one; only the hard
+    answers' entries are kept.  `stable=True` fixes the order of tied logits (lower id first), which
+    the reference leaves to the sort implementation.  Returns the float tensor `cur_ranking`."""
+    negative_logit = negative_logit.reshape(1, -1).float().cpu()
+    easy_answer, hard_answer = list(easy_answer), list(hard_answer)
+    argsort = torch.argsort(negative_logit, dim=1, descending=True, stable=True)
+    ranking = argsort.clone().to(torch.float)
+    ranking = ranking.scatter_(1, argsort, torch.arange(negative_logit.shape[1]).to(torch.float).repeat(argsort.shape[0], 1))
+    num_easy, num_hard = len(easy_answer), len(hard_answer)
+    cur_ranking = ranking[0, easy_answer + hard_answer]
+    cur_ranking, indices = torch.sort(cur_ranking)
+    masks = indices >= num_easy
+    answer_list = torch.arange(num_hard + num_easy).to(torch.float)
+    cur_ranking = cur_ranking - answer_list + 1
+    return cur_ranking[masks]
+
+
+def reference_ranking_metrics(cur_ranking):
+    """train_process.py:142-146."""
+    return {"MRR": torch.mean(1. / cur_ranking).item(),
+            "HITS1": torch.mean((cur_ranking <= 1).to(torch.float)).item(),
+            "HITS3": torch.mean((cur_ranking <= 3).to(torch.float)).item(),
+            "HITS10": torch.mean((cur_ranking <= 10).to(torch.float)).item(),
+            "HITS1max": ((cur_ranking[0] == 1).to(torch.float)).item()}

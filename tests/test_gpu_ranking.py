@@ -1,0 +1,75 @@
+"""Filtered ranks by counting (smore_filtered_ranks) against the reference's argsort/scatter
+block restated on the CPU (needs a B200)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _answers(rng, n, n_easy, n_hard):
+    ids = rng.choice(n, size=min(n, n_easy + n_hard), replace=False)
+    return list(map(int, ids[:min(n_easy, len(ids))])), list(map(int, ids[min(n_easy, len(ids)):]))
+
+
+@pytest.mark.parametrize("n,levels", [(1, 0), (17, 0), (5000, 0), (5000, 7), (300000, 0), (300000, 50)])
+def test_filtered_ranks_equal_reference_block(n, levels):
+    """Exact equality, ties included (levels > 0 quantises the logits so that many are equal)."""
+    from oracle.native_torch import reference_filtered_ranks
+    from smore_b200 import ranking
+    rng = np.random.default_rng(n + levels)
+    sizes = [(0, 1), (3, 1), (0, 40), (25, 60), (700, 900), (0, 0)]
+    Q = len(sizes)
+    logits = torch.from_numpy(rng.standard_normal((Q, n)).astype(np.float32))
+    if levels:
+        logits = torch.round(logits * levels) / levels
+    easy, hard = [], []
+    for ne, nh in sizes:
+        e, h = _answers(rng, n, ne, nh)
+        easy.append(e)
+        hard.append(h)
+    got = ranking.filtered_ranks(logits.cuda(), easy, hard)
+    for q in range(Q):
+        want = reference_filtered_ranks(logits[q], easy[q], hard[q]) if hard[q] else torch.empty(0)
+        assert got[q].dtype == torch.int64 and got[q].numel() == len(hard[q])
+        assert torch.equal(got[q].cpu().float(), want), "query %d" % q
+
+
+def test_metrics_and_full_table_scoring_path():
+    """The evaluation path end to end: box logits of 5 queries against every entity through the
+    distance ops (one shared candidate set, be = 1, ne = N), filtered ranks, metrics."""
+    from oracle.native_torch import reference_filtered_ranks, reference_ranking_metrics
+    from smore_b200 import ext_ops, ranking
+    torch.manual_seed(0)
+    N, D, Q = 20000, 64, 5
+    table = ((torch.rand(N, D) - 0.5) * 0.4).cuda()
+    center = ((torch.rand(Q, 1, D) - 0.5) * 0.4).cuda()
+    offset = (torch.rand(Q, 1, D) * 0.1).cuda()
+    all_entities = table.unsqueeze(0)                      # [1, N, D]: every query scores all entities
+    logits = 12.0 - ext_ops.box_dist_out(all_entities, center, offset) \
+        - 0.02 * ext_ops.box_dist_in(all_entities, center, offset)
+    assert logits.shape == (Q, N)
+    rng = np.random.default_rng(5)
+    easy, hard = zip(*[_answers(rng, N, 10 * q, 1 + 30 * q) for q in range(Q)])
+    # make the answers score well, as a trained model would: some of them rank first
+    for q in range(Q):
+        logits[q, hard[q][0]] = logits[q].max() + 1.0
+    ranks = ranking.filtered_ranks(logits, easy, hard)
+    for q in range(Q):
+        want = reference_filtered_ranks(logits[q].cpu(), easy[q], hard[q])
+        assert torch.equal(ranks[q].cpu().float(), want)
+        got_m, want_m = ranking.ranking_metrics(ranks[q]), reference_ranking_metrics(want)
+        for k in want_m:
+            assert abs(got_m[k] - want_m[k]) < 1e-6, k
+        assert got_m["HITS1max"] == 1.0
+
+
+def test_filtered_ranks_rejects_bad_input():
+    from smore_b200 import _lib, ranking
+    logits = torch.zeros(1, 10, device="cuda")
+    with pytest.raises(ValueError):
+        ranking.filtered_ranks(logits, [[]], [[10]])
+    with pytest.raises(TypeError):
+        ranking.filtered_ranks(logits.double(), [[]], [[1]])
+    with pytest.raises(_lib.SmoreError):
+        ranking.filtered_ranks(torch.zeros(1, 9000, device="cuda"), [[]], [list(range(8193))])

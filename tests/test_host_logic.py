@@ -104,3 +104,26 @@ def test_native_torch_baseline_vs_reference_golden(golden):
             assert np.array_equal(u.numpy(), zo["opt/step%d/uniq" % step])
             nt.adam_rows(table, m, v, u, merged, float(zo["opt/lr"]), step + 1, squeeze)
             np.testing.assert_allclose(table.numpy(), zo[tag + "table_after%d" % step], rtol=1e-6, atol=1e-7)
+
+
+def test_reference_ranking_block_matches_the_counting_definition():
+    """The restated argsort/scatter block (the checker of the GPU ranks) against the definition it is
+    replaced by: rank = 1 + candidates ahead - answers ahead, ahead = higher logit or equal logit
+    and lower id."""
+    import numpy as np
+    import torch
+    from oracle.native_torch import reference_filtered_ranks
+    rng = np.random.default_rng(0)
+    for n, levels in [(1, 0), (50, 0), (400, 5)]:
+        x = rng.standard_normal(n).astype(np.float32)
+        if levels:
+            x = np.round(x * levels) / levels
+        ids = rng.choice(n, size=min(n, 30), replace=False)
+        easy, hard = [int(i) for i in ids[:len(ids) // 3]], [int(i) for i in ids[len(ids) // 3:]]
+        answers = set(easy) | set(hard)
+        want = []
+        for a in hard:
+            ahead = [e for e in range(n) if x[e] > x[a] or (x[e] == x[a] and e < a)]
+            want.append(1 + len(ahead) - len([e for e in ahead if e in answers]))
+        got = reference_filtered_ranks(torch.from_numpy(x), easy, hard)
+        assert sorted(want) == [int(v) for v in got.tolist()]
