@@ -886,6 +886,91 @@ def run_reference(args):
     print(json.dumps(out), flush=True)
 
 
+def run_eval(args):
+    """Side benchmark (not the contract line): the evaluation step that follows the hot path in the
+    reference (train_process.py:104-153) - score a batch of queries against EVERY entity with the
+    distance ops (one shared candidate set), then the filtered ranks of their answers - and the same
+    work through the reference's argsort/scatter block on the host cores."""
+    from smore_b200 import _lib, ext_ops, ranking
+    from oracle.native_torch import box_logit, vec_logit, reference_filtered_ranks
+    cfg = dict(WORKLOADS[args.workload])
+    if cfg["geo"] not in ("box", "vec"):
+        raise SystemExit("--eval covers the box and vec workloads")
+    device = torch.device("cuda", 0)
+    N = args.rows or cfg["rows"] or (FREEBASE_ENTITIES + 7) // 8
+    D, Q = cfg["dim"], args.eval_queries
+    r = (cfg["gamma"] + 2.0) / D
+    g = torch.Generator(device=device).manual_seed(7)
+    table = torch.empty(N, D, device=device).uniform_(-r, r, generator=g)
+    center = torch.empty(Q, 1, D, device=device).uniform_(-r, r, generator=g)
+    offset = torch.empty(Q, 1, D, device=device).uniform_(0, r, generator=g)
+    rng = torch.Generator().manual_seed(8)
+    easy = [torch.randint(0, N, (10,), generator=rng).unique().tolist() for _ in range(Q)]
+    hard = [[i for i in torch.randint(0, N, (20,), generator=rng).unique().tolist() if i not in set(e)]
+            for e in easy]
+    everything = table.unsqueeze(0)
+
+    def score():
+        if cfg["geo"] == "box":
+            return cfg["gamma"] - ext_ops.box_dist_out(everything, center, offset) \
+                - cfg["cen"] * ext_ops.box_dist_in(everything, center, offset)
+        return cfg["gamma"] - ext_ops.l1_dist(everything, center)
+
+    def step():
+        with torch.no_grad():
+            logits = score()
+            ranks = ranking.filtered_ranks(logits, easy, hard)
+        return logits, ranks
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    timer = _lib.KernelTimer()
+    _lib.set_timer(timer)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        logits, ranks = step()
+    e1.record()
+    torch.cuda.synchronize()
+    _lib.set_timer(None)
+    ms = e0.elapsed_time(e1) / args.steps
+    rank_ms = timer.elapsed_ms().get("filtered_ranks", [0.0])
+    # host cores: the reference's scoring (torch twins) and ranking block, a few queries of the same batch
+    torch.set_num_threads(os.cpu_count() or 1)
+    n_cpu = min(Q, args.cpu_steps)
+    tab_c, cen_c, off_c = table.cpu(), center.cpu(), offset.cpu()
+    t0 = time.perf_counter()
+    for q in range(n_cpu):
+        pieces = []
+        for lo in range(0, N, 200000):          # the torch twins materialise [N, D] temporaries
+            blk = tab_c[lo:lo + 200000].unsqueeze(0)
+            if cfg["geo"] == "box":
+                pieces.append(box_logit(blk, [cen_c[q:q + 1], off_c[q:q + 1]], cfg["gamma"], cfg["cen"]))
+            else:
+                pieces.append(vec_logit(blk, [cen_c[q:q + 1]], cfg["gamma"]))
+        lg = torch.cat(pieces, dim=1)
+        want = reference_filtered_ranks(lg, easy[q], hard[q])
+        got = ranks[q].cpu().float()
+        if not torch.equal(got, want):      # the host scoring rounds differently: ranks may move by near-ties
+            close = (got - want).abs().max().item() <= max(2.0, 1e-5 * N)
+            if not close:
+                raise RuntimeError("evaluation ranks differ from the reference block: %s vs %s" % (got, want))
+    cpu_s = (time.perf_counter() - t0) / n_cpu
+    out = {
+        "metric": "evaluation queries/sec (score every entity + filtered ranks)", "value": round(Q / (ms * 1e-3), 1),
+        "unit": "queries/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3),
+        "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "eval:" + args.workload, "queries_per_step": Q, "candidates": N, "dim": D,
+                   "answers_per_query": "~10 easy + ~20 hard"},
+        "filtered_ranks_ms": round(sum(rank_ms) / max(1, len(rank_ms)), 4),
+        "logits_bytes": Q * N * 4,
+        "cpu_baseline": {"value": round(1.0 / cpu_s, 2), "unit": "queries/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": "%d queries of the same batch" % n_cpu},
+    }
+    print(json.dumps(out), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -903,8 +988,13 @@ def main():
                     help="several GPUs: pull every step's rows after the previous update instead of during it")
     ap.add_argument("--cpu-steps", type=int, default=6)
     ap.add_argument("--dump-kernel-times", action="store_true", help="add every timed launch's duration to the JSON")
+    ap.add_argument("--eval", action="store_true",
+                    help="side benchmark: score queries against every entity and rank their answers (1 GPU)")
+    ap.add_argument("--eval-queries", type=int, default=32)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.eval:
+        run_eval(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)
