@@ -1171,9 +1171,11 @@ static int launch_forward_union(size_t branches, const Shape& s, const float* ta
                            &p))
     return rc;
   RowArgs a{table, idx, first, second, (int)s.num, (int)s.dim, p.rows_per_cta, p.chunks, p.wrows};
+  constexpr int NB = kUnionBranches;
+  // (staging the rows with bulk copies, as row_forward_bulk_kernel does, measured no faster here:
+  // with two branches per row the kernel is bound by instruction issue, not by memory latency)
   const unsigned grid = (unsigned)(s.bsize * p.chunks);
   const size_t smem = (size_t)kUnionBranches * Term::kNQ * s.dim * sizeof(float);
-  constexpr int NB = kUnionBranches;
   switch (p.nch) {
     case 1: row_forward_union_kernel<Term, NB, 1, 4><<<grid, kRowCtaThreads, smem, st>>>(a, dst0, dst1); break;
     case 2: row_forward_union_kernel<Term, NB, 2, 4><<<grid, kRowCtaThreads, smem, st>>>(a, dst0, dst1); break;

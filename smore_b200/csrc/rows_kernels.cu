@@ -210,16 +210,28 @@ __global__ void __launch_bounds__(256)
 // compact gradient buffer helpers
 // ----------------------------------------------------------------------------------------
 
+// Each lane tests one slot of a 32-slot batch; the warp then clears the marked rows together
+// (16-byte stores when the row allows it).  Only ~5 % of the slots are shared at the benchmark.
+template <bool VEC>
 __global__ void __launch_bounds__(256)
     zero_shared_rows_kernel(float* __restrict__ g_rows, const int32_t* __restrict__ slot_count,
                             const int32_t* __restrict__ n_unique, size_t width) {
   const int lane = threadIdx.x & 31;
   const size_t nu = (size_t)max(n_unique[0], 0);
   const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
-  for (size_t u = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); u < nu; u += warps) {
-    if (slot_count[u] > 1) {
-      float* r = g_rows + u * width;
-      for (size_t d = lane; d < width; d += kWarp) r[d] = 0.f;
+  for (size_t u0 = ((size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 32; u0 < nu; u0 += warps * 32) {
+    const bool shared = u0 + lane < nu && slot_count[u0 + lane] > 1;
+    unsigned todo = __ballot_sync(0xffffffffu, shared);
+    while (todo) {
+      const int l = __ffs(todo) - 1;
+      todo &= todo - 1;
+      float* r = g_rows + (u0 + l) * width;
+      if (VEC) {
+        float4* r4 = reinterpret_cast<float4*>(r);
+        for (size_t d = lane; d < (width >> 2); d += kWarp) r4[d] = make_float4(0.f, 0.f, 0.f, 0.f);
+      } else {
+        for (size_t d = lane; d < width; d += kWarp) r[d] = 0.f;
+      }
     }
   }
 }
@@ -521,8 +533,12 @@ int smore_zero_shared_rows(float* g_rows, const int32_t* slot_count, const int32
                            size_t width, void* stream) {
   if (!g_rows || !slot_count || !n_unique) return fail(SMORE_ERR_NULL, "zero_shared_rows: NULL pointer");
   if (capacity == 0) return SMORE_OK;
-  zero_shared_rows_kernel<<<warp_grid(capacity), 256, 0, (cudaStream_t)stream>>>(g_rows, slot_count, n_unique,
-                                                                                  width);
+  if ((width & 3) == 0 && aligned16(g_rows))
+    zero_shared_rows_kernel<true><<<warp_grid((capacity + 31) / 32), 256, 0, (cudaStream_t)stream>>>(
+        g_rows, slot_count, n_unique, width);
+  else
+    zero_shared_rows_kernel<false><<<warp_grid((capacity + 31) / 32), 256, 0, (cudaStream_t)stream>>>(
+        g_rows, slot_count, n_unique, width);
   return check_launch("zero_shared_rows_kernel");
 }
 
