@@ -117,9 +117,9 @@ __global__ void __launch_bounds__(kRankThreads)
   const float* row = logits + q * n_candidates;
   const size_t c0 = (size_t)blockIdx.x * per_cta;
   const size_t c1 = c0 + per_cta < n_candidates ? c0 + per_cta : n_candidates;
-  for (size_t e = c0 + threadIdx.x; e < c1; e += kRankThreads) {
-    const float x = rank_clean(row[e]);
-    if (!rank_ahead(x, (long long)e, worst, worst_id)) continue;   // ahead of no answer (the usual case)
+  auto place = [&](float x, size_t e) {
+    x = rank_clean(x);
+    if (!rank_ahead(x, (long long)e, worst, worst_id)) return;   // ahead of no answer (the usual case)
     int lo = 0, hi = A - 1;   // first answer this candidate is ahead of
     while (lo < hi) {
       const int mid = (lo + hi) >> 1;
@@ -127,7 +127,17 @@ __global__ void __launch_bounds__(kRankThreads)
       else lo = mid + 1;
     }
     atomicAdd(&local[lo], 1);
+  };
+  // four independent, coalesced loads per thread and iteration
+  size_t e = c0 + threadIdx.x;
+  for (; e + 3 * kRankThreads < c1; e += 4 * kRankThreads) {
+    const float x0 = row[e], x1 = row[e + kRankThreads], x2 = row[e + 2 * kRankThreads], x3 = row[e + 3 * kRankThreads];
+    place(x0, e);
+    place(x1, e + kRankThreads);
+    place(x2, e + 2 * kRankThreads);
+    place(x3, e + 3 * kRankThreads);
   }
+  for (; e < c1; e += kRankThreads) place(row[e], e);
   __syncthreads();
   for (int i = threadIdx.x; i < A; i += kRankThreads)
     if (local[i]) atomicAdd(&hist[begin + i], local[i]);
