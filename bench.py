@@ -169,8 +169,10 @@ class QueryModel(nn.Module):
     intersection nets; embeds one batch of same-structure queries and scores candidates."""
 
     def __init__(self, cfg, n_rows, device, ops, embedding_mod, lazy=True, shard=None, barrier=None, world=1,
-                 capturable=False):
+                 capturable=False, fused_paths=False):
         super().__init__()
+        # relation projections of a path as one library op (box and vec geometries) instead of per-hop torch ops
+        self.fused_paths = bool(fused_paths) and cfg["geo"] in ("box", "vec")
         self.cfg, self.geo, self.dim = cfg, cfg["geo"], cfg["dim"]
         self.gamma, self.cen = cfg["gamma"], cfg.get("cen", 0.0)
         self.ops = ops
@@ -221,8 +223,20 @@ class QueryModel(nn.Module):
             re, im = torch.chunk(e, 2, dim=1)
             return [re.unsqueeze(1), im.unsqueeze(1)]
         if self.geo == "box":
-            return [e.unsqueeze(1), torch.zeros_like(e).unsqueeze(1)]
+            # a fresh anchor is a box of zero size (box.py:138-139); the fused projection takes None for it
+            return [e.unsqueeze(1), None if self.fused_paths else torch.zeros_like(e).unsqueeze(1)]
         return [e.unsqueeze(1)]
+
+    def _project_path(self, emb, rel_ids):
+        """All hops of a path at once (smore_b200.query_ops) for the additive geometries."""
+        from smore_b200 import query_ops
+        start = emb[0].squeeze(1)
+        if self.geo == "box":
+            c, o = query_ops.project_path(start, self.relation_embedding, rel_ids,
+                                          start_offset=None if emb[1] is None else emb[1].squeeze(1),
+                                          off_table=self.offset_embedding)
+            return [c.unsqueeze(1), o.unsqueeze(1)]
+        return [query_ops.project_path(start, self.relation_embedding, rel_ids).unsqueeze(1)]
 
     def _project(self, emb, rel_ids):
         rel = self.relation_embedding[rel_ids].unsqueeze(1)
@@ -258,6 +272,11 @@ class QueryModel(nn.Module):
                 col += 1
             else:
                 emb, col = self.embed_query(queries, qs[0], col)
+            if self.fused_paths and all(x == "r" for x in qs[-1]) and emb[0].shape[1] == 1:   # not after a union
+                emb = self._project_path(emb, queries[:, col:col + len(qs[-1])])
+                return emb, col + len(qs[-1])
+            if emb[-1] is None:
+                emb[-1] = torch.zeros_like(emb[0])
             for _ in qs[-1]:
                 emb = self._project(emb, queries[:, col])
                 col += 1
@@ -521,7 +540,7 @@ def run_gpu(args):
         r = (cfg["gamma"] + 2.0) / cfg["dim"]
         shard.init_uniform(-r, r, seed=1234)
         model = QueryModel(cfg, n_rows, device, ext_ops, embedding, lazy=True, shard=shard, world=world,
-                           capturable=not args.no_graphs)
+                           capturable=not args.no_graphs, fused_paths=not args.no_fused_paths)
 
         def reduce_dense(grads):
             # one all-reduce over all dense gradients instead of one per parameter
@@ -530,7 +549,7 @@ def run_gpu(args):
             torch._foreach_copy_(grads, [f.view_as(g) for f, g in zip(flat.split([g.numel() for g in grads]), grads)])
     else:
         model = QueryModel(cfg, n_rows, device, ext_ops, embedding, lazy=not args.no_lazy,
-                           capturable=not args.no_graphs)
+                           capturable=not args.no_graphs, fused_paths=not args.no_fused_paths)
     prefetching = world > 1 and not args.no_prefetch
     use_graphs = world == 1 and not args.no_graphs
     chained_graphs = world > 1 and prefetching and not args.no_graphs
@@ -986,6 +1005,8 @@ def main():
     ap.add_argument("--no-graphs", action="store_true", help="launch every step eagerly instead of replaying CUDA graphs")
     ap.add_argument("--no-prefetch", action="store_true",
                     help="several GPUs: pull every step's rows after the previous update instead of during it")
+    ap.add_argument("--no-fused-paths", action="store_true",
+                    help="embed path queries hop by hop with torch ops, as the reference models do")
     ap.add_argument("--cpu-steps", type=int, default=6)
     ap.add_argument("--dump-kernel-times", action="store_true", help="add every timed launch's duration to the JSON")
     ap.add_argument("--eval", action="store_true",

@@ -258,6 +258,25 @@ SMORE_API int smore_sparse_update_rows_dev(int opt_id, float* table, float* m, f
                                  const float* step_scalars, int squeeze, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Relation projection of path queries for the additive geometries (GQE, Query2box): all hops of
+ * a batch in one kernel each way, in place of the per-hop lookups and additions of
+ * kg_reasoning.py:229-236 with vec.py:58-60 / box.py:126-129.
+ *   center[b, :] = start_center[b, :] + sum_h rel_table[ids[b, h], :]        (hop order)
+ *   offset[b, :] = start_offset[b, :] + sum_h act(off_table[ids[b, h], :])   (off_table != NULL)
+ * ids[b, h] = rel_ids[b * id_stride + h] (a column block of the reference's query matrix);
+ * start_offset NULL = zeros (box.py:138-139); act = relu if relu_offset else identity (box.py:76-85).
+ * Backward overwrites g_rel_table [n_relations, dim] (and g_off_table) with the dense gradients
+ * of the tables; the gradient of start_center / start_offset is g_center / g_offset unchanged. */
+SMORE_API int smore_path_project_forward(const float* start_center, const float* start_offset,
+                               const float* rel_table, const float* off_table, size_t n_relations,
+                               const int64_t* rel_ids, size_t id_stride, size_t n_queries, size_t hops,
+                               size_t dim, int relu_offset, float* center, float* offset, void* stream);
+SMORE_API int smore_path_project_backward(const float* g_center, const float* g_offset, const float* off_table,
+                                size_t n_relations, const int64_t* rel_ids, size_t id_stride,
+                                size_t n_queries, size_t hops, size_t dim, int relu_offset,
+                                float* g_rel_table, float* g_off_table, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Evaluation: filtered ranks of the answers of each query among all candidates.
  * The reference (train_process.py:113-146) argsorts the [1, N] logits of a query, scatters the
  * permutation into a rank per entity, takes the ranks of the easy and hard answers, sorts them and

@@ -47,6 +47,8 @@ SIGNATURES = {
     "smore_adam_step_scalars": (_int, [_p, _dbl, _dbl, _dbl, _p, _p]),
     "smore_sparse_update_rows_dev": (_int, [_int, _p, _p, _p, _p, _p, _p, _sz, _sz, _dbl, _dbl, _dbl, _dbl, _p, _int,
                                             _p]),
+    "smore_path_project_forward": (_int, [_p, _p, _p, _p, _sz, _p, _sz, _sz, _sz, _sz, _int, _p, _p, _p]),
+    "smore_path_project_backward": (_int, [_p, _p, _p, _sz, _p, _sz, _sz, _sz, _sz, _int, _p, _p, _p]),
     "smore_filtered_ranks_workspace_bytes": (_sz, [_sz]),
     "smore_filtered_ranks": (_int, [_p, _sz, _sz, _p, _p, _sz, _sz, _p, _p, _sz, _p]),
     "smore_dot_available": (_int, []),

@@ -1115,8 +1115,10 @@ static int launch_backward(const Shape& s, const float* gout0, const float* gout
     RowGradArgs ga{gout0, gout1, g_ent, slot, slot_count, g_rows, g_first, g_second, p.chunks > 1};
     if (int rc = launch_backward_bulk<Term, 1>(s, a, ga, p.nch, st)) return rc < 0 ? rc : SMORE_OK;
     if (p.chunks > 1) {
-      cudaMemsetAsync(g_first, 0, s.bsize * s.dim * sizeof(float), st);
-      if (Term::kNQ == 2) cudaMemsetAsync(g_second, 0, s.bsize * s.dim * sizeof(float), st);
+      const size_t bytes = s.bsize * s.dim * sizeof(float);
+      if (cudaMemsetAsync(g_first, 0, bytes, st) != cudaSuccess ||
+          (Term::kNQ == 2 && cudaMemsetAsync(g_second, 0, bytes, st) != cudaSuccess))
+        return fail(SMORE_ERR_CUDA, "dist_backward: cudaMemsetAsync failed");
     }
     const unsigned grid = (unsigned)(s.bsize * p.chunks);
     const int dim4 = (int)(s.dim >> 2);

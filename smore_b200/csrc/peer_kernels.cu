@@ -396,7 +396,8 @@ int smore_shard_mark_dirty(const int64_t* uniq, const int32_t* n_unique, size_t 
                            uint32_t* dirty, void* stream) {
   if (!uniq || !n_unique || !dirty) return fail(SMORE_ERR_NULL, "shard_mark_dirty: NULL pointer");
   cudaStream_t st = (cudaStream_t)stream;
-  cudaMemsetAsync(dirty, 0, ((shard_rows + 31) / 32) * sizeof(uint32_t), st);
+  if (cudaMemsetAsync(dirty, 0, ((shard_rows + 31) / 32) * sizeof(uint32_t), st) != cudaSuccess)
+    return fail(SMORE_ERR_CUDA, "shard_mark_dirty: cudaMemsetAsync failed");
   if (capacity)
     shard_mark_dirty_kernel<<<grid_threads(capacity), 256, 0, st>>>(uniq, n_unique, dirty);
   return check_launch("shard_mark_dirty_kernel", capacity ? 1 : 0);

@@ -515,10 +515,12 @@ int smore_unique_rows(const int64_t* idx, size_t n, size_t n_table_rows, int64_t
     return fail(SMORE_ERR_WORKSPACE, "unique_rows: workspace has %zu bytes, %zu needed", workspace_bytes,
                 w.bytes);
   cudaStream_t st = (cudaStream_t)stream;
-  cudaMemsetAsync(n_unique, 0, 2 * sizeof(int32_t), st);
+  if (cudaMemsetAsync(n_unique, 0, 2 * sizeof(int32_t), st) != cudaSuccess)
+    return fail(SMORE_ERR_CUDA, "unique_rows: cudaMemsetAsync failed");
   if (n == 0) return check_launch("unique_rows memset", 0);
-  cudaMemsetAsync(w.bitmap, 0, w.nwords * sizeof(uint32_t), st);
-  cudaMemsetAsync(counts, 0, n * sizeof(int32_t), st);
+  if (cudaMemsetAsync(w.bitmap, 0, w.nwords * sizeof(uint32_t), st) != cudaSuccess ||
+      cudaMemsetAsync(counts, 0, n * sizeof(int32_t), st) != cudaSuccess)
+    return fail(SMORE_ERR_CUDA, "unique_rows: cudaMemsetAsync failed");
   unique_mark_kernel<<<thread_grid(n), 256, 0, st>>>(idx, n, n_table_rows, w.bitmap, n_unique);
   unique_blocksum_kernel<<<(unsigned)w.nblocks, kScanThreads, 0, st>>>(w.bitmap, w.nwords, w.blocksum);
   unique_scan_blocks_kernel<<<1, 1024, 0, st>>>(w.blocksum, w.nblocks, n_unique);
@@ -710,10 +712,12 @@ extern "C" int smore_unique_rows_static(const int64_t* idx, size_t n, size_t n_t
   if (w.bytes > kStaticUniqueBytes) return fail(SMORE_ERR_WORKSPACE, "unique_rows_static: scratch layout overflow");
   cudaStream_t st = (cudaStream_t)stream;
   // the array still holds the previous call's bitmap: everything that must start at zero is cleared here
-  cudaMemsetAsync(n_unique, 0, 2 * sizeof(int32_t), st);
+  if (cudaMemsetAsync(n_unique, 0, 2 * sizeof(int32_t), st) != cudaSuccess)
+    return fail(SMORE_ERR_CUDA, "unique_rows_static: cudaMemsetAsync failed");
   if (n == 0) return check_launch("unique_rows_static memset", 0);
-  cudaMemsetAsync(w.bitmap, 0, w.nwords * sizeof(uint32_t), st);
-  cudaMemsetAsync(counts, 0, n * sizeof(int32_t), st);
+  if (cudaMemsetAsync(w.bitmap, 0, w.nwords * sizeof(uint32_t), st) != cudaSuccess ||
+      cudaMemsetAsync(counts, 0, n * sizeof(int32_t), st) != cudaSuccess)
+    return fail(SMORE_ERR_CUDA, "unique_rows_static: cudaMemsetAsync failed");
   unique_mark_kernel<<<thread_grid(n), 256, 0, st>>>(idx, n, n_table_rows, w.bitmap, n_unique);
   unique_blocksum_kernel<<<(unsigned)w.nblocks, kScanThreads, 0, st>>>(w.bitmap, w.nwords, w.blocksum);
   unique_scan_blocks_kernel<<<1, 1024, 0, st>>>(w.blocksum, w.nblocks, n_unique);
