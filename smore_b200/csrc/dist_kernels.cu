@@ -1068,7 +1068,11 @@ static int launch_forward(const Shape& s, const float* ent, const int64_t* idx, 
     // 512 rows.  It needs at least two CTAs per SM to cover the reduction latency.
     const size_t row_bytes = s.dim * Term::kMul * sizeof(float);
     const int stages = (int)std::min<size_t>(8, std::max<size_t>(2, (96 * 1024 / 32 + row_bytes - 1) / row_bytes));
-    const size_t bulk_smem = bulk_ring_offset(stages) + (size_t)kRowCtaWarps * stages * row_bytes;
+    // at least 46 KB per CTA keeps the residency at four CTAs per SM whatever the register count:
+    // five and more (terms with few registers) put more row copies in flight than the memory
+    // system likes and measured up to 1.8x slower
+    const size_t bulk_smem = std::max<size_t>(bulk_ring_offset(stages) + (size_t)kRowCtaWarps * stages * row_bytes,
+                                              46 * 1024);
     if ((p.nch == 4 || p.nch == 8) && bulk_smem <= 110 * 1024) {
       RowArgs ab = a;
       ab.rows_per_cta = (int)std::min<size_t>(s.num, 512);
