@@ -931,8 +931,8 @@ def run_eval(args):
 
     def score():
         if cfg["geo"] == "box":
-            return cfg["gamma"] - ext_ops.box_dist_out(everything, center, offset) \
-                - cfg["cen"] * ext_ops.box_dist_in(everything, center, offset)
+            d_out, d_in = ext_ops.box_dist_both(everything, center, offset)     # one pass over the table
+            return cfg["gamma"] - d_out - cfg["cen"] * d_in
         return cfg["gamma"] - ext_ops.l1_dist(everything, center)
 
     def step():

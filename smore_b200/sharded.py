@@ -39,6 +39,34 @@ from .embedding import (EmbeddingOptimizer, LazyRows, _DUMMY_JOB, _EmbedLookupFu
 MAX_PLANS = 4
 
 
+def rows_of_rank(full, rank, world):
+    """The rows of a full [N, ...] tensor that rank `rank` of `world` owns."""
+    S = shard_rows(full.shape[0], world)
+    return full[rank * S:min(full.shape[0], (rank + 1) * S)]
+
+
+def merge_shard_states(states, prefix="entity_embedding."):
+    """Rebuild the reference's checkpoint entries of a sparse embedding from the ranks' shard states
+    (ShardedTable.shard_state()), in any order: `<prefix>embedding`, `<prefix>state_sum_fo`,
+    `<prefix>state_sum_sq` - the keys `model.state_dict()` holds for a SparseEmbedding whose optimizer
+    registered its state on it (sparse_embed.py:50-53, embed_optimizer.py:192-197), as saved by
+    train_process.py:250-260."""
+    states = sorted(states, key=lambda st: st["rank"])
+    world = states[0]["world"]
+    if [st["rank"] for st in states] != list(range(world)):
+        raise ValueError("need the state of every rank 0..%d exactly once" % (world - 1))
+    for st in states:
+        for k in ("world", "n_rows_total", "width", "squeeze"):
+            if st[k] != states[0][k]:
+                raise ValueError("shard states disagree on %s" % k)
+    out = {}
+    for key in ("embedding", "state_sum_fo", "state_sum_sq"):
+        out[prefix + key] = torch.cat([st[key] for st in states], dim=0)
+        if out[prefix + key].shape[0] != states[0]["n_rows_total"]:
+            raise ValueError("shard states do not add up to %d rows" % states[0]["n_rows_total"])
+    return out
+
+
 class _DeviceBlock(object):
     """A byte block of device memory (a uint8 tensor) that typed views are cut from.
 
@@ -207,6 +235,40 @@ class ShardedTable(object):
 
     def close(self):
         self._handles = []
+
+    def shard_state(self):
+        """This rank's rows of the table and of the Adam state as CPU tensors (one file per rank when
+        saved); merge_shard_states() turns all ranks' states into the reference's checkpoint keys."""
+        n = self.local_rows
+        return {"rank": self.rank, "world": self.world, "n_rows_total": self.n_rows_total, "width": self.width,
+                "squeeze": self.squeeze, "embedding": self.table[:n].detach().cpu(),
+                "state_sum_fo": self.m[:n].detach().cpu(), "state_sum_sq": self.v[:n].detach().cpu()}
+
+    def load_shard_state(self, state):
+        for k in ("rank", "world", "n_rows_total", "width", "squeeze"):
+            if state[k] != getattr(self, k):
+                raise _lib.SmoreError("shard state was saved with %s = %r, this shard has %r" % (k, state[k], getattr(self, k)))
+        n = self.local_rows
+        self.table[:n].copy_(state["embedding"])
+        self.m[:n].copy_(state["state_sum_fo"])
+        self.v[:n].copy_(state["state_sum_sq"])
+
+    def load_full(self, embedding, state_sum_fo=None, state_sum_sq=None):
+        """Take this rank's rows from full [N, ...] tensors, e.g. the entries of a reference checkpoint
+        (`checkpoint['model_state_dict']['entity_embedding.embedding']`, main_train.py:191-194).
+        Optimizer state that is not given starts at zero, as a fresh optimizer's would."""
+        if embedding.shape != (self.n_rows_total, self.width):
+            raise _lib.SmoreError("embedding must be [%d, %d]" % (self.n_rows_total, self.width))
+        n = self.local_rows
+        self.table[:n].copy_(rows_of_rank(embedding, self.rank, self.world))
+        for dst, src, shape in ((self.m, state_sum_fo, (self.n_rows_total, self.width)),
+                                (self.v, state_sum_sq, (self.n_rows_total, 1 if self.squeeze else self.width))):
+            if src is None:
+                dst.zero_()
+            else:
+                if tuple(src.shape) != shape:
+                    raise _lib.SmoreError("optimizer state must be %s, got %s" % (shape, tuple(src.shape)))
+                dst[:n].copy_(rows_of_rank(src, self.rank, self.world))
 
     def init_uniform(self, lo, hi, seed):
         """Fill the shard as rows [base, base+S) of a table drawn uniform(lo, hi); the values depend

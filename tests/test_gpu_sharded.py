@@ -242,3 +242,43 @@ def test_prefetch_with_refresh_equals_fetch_after_the_update(world):
     close(t1.numpy(), t0.numpy(), RTOL_ATOMIC, what="table")
     close(m1.numpy(), m0.numpy(), RTOL_ATOMIC, what="m")
     close(v1.numpy(), v0.numpy(), RTOL_ATOMIC, what="v")
+
+
+def test_shard_states_round_trip_through_reference_checkpoint_keys():
+    """load_full (reference checkpoint entries) -> steps -> shard_state -> merge == concatenated shards;
+    a second group of shards loaded from the merged entries continues bit-identically."""
+    from smore_b200 import sharded
+    world, n_total, D, B, K = 3, 1003, 64, 6, 50
+    caps = (B * K + 2 * B, B, B)
+    torch.manual_seed(1)
+    full = (torch.rand(n_total, D) - 0.5) * 0.2
+
+    def make(entries):
+        shards = sharded.ShardGroup.emulated(world, n_total, D, caps, squeeze=True)
+        for s in shards:
+            s.load_full(entries["entity_embedding.embedding"], entries.get("entity_embedding.state_sum_fo"),
+                        entries.get("entity_embedding.state_sum_sq"))
+        return shards, [sharded.ShardedAdamOptimizer(s, barrier=lambda: None) for s in shards]
+
+    def run(shards, opts, steps):
+        for step in steps:
+            for o_ in opts:
+                o_.zero_grad()
+            for r in range(world):
+                _rank_forward_backward(opts[r].forward, _rank_batch(r, step, n_total, B, K, D), world)
+            for o_ in opts:
+                o_.apply_grad(1e-2)
+        torch.cuda.synchronize()
+        return sharded.merge_shard_states([s.shard_state() for s in shards])
+
+    shards, opts = make({"entity_embedding.embedding": full})
+    first = run(shards, opts, [0, 1])
+    assert torch.equal(first["entity_embedding.embedding"], torch.cat([s.table[:s.local_rows] for s in shards]).cpu())
+    assert first["entity_embedding.state_sum_sq"].shape == (n_total, 1)
+    want = run(shards, opts, [2])
+    shards2, opts2 = make(first)
+    for o_ in opts2:
+        o_.step = 2                              # the optimizer's step count is part of a checkpoint
+    got = run(shards2, opts2, [2])
+    for k in want:
+        close(got[k].numpy(), want[k].numpy(), RTOL_ATOMIC, what=k)

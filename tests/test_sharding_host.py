@@ -1,6 +1,8 @@
 """Host-side logic of the row-sharded table, on CPU: arena layout, ownership, pointer tables, and
 the handle exchange / barrier pattern over a two-process gloo group."""
 import os
+
+import pytest
 import socket
 
 import torch
@@ -77,3 +79,27 @@ def test_handle_exchange_and_barrier_over_gloo(tmp_path):
     assert views[0]["handles"] == views[1]["handles"] == [[b"table-0", b"arena-0"], [b"table-1", b"arena-1"]]
     assert views[0]["tabs"] == views[1]["tabs"]          # every rank indexes the lists identically
     assert views[0]["store"].tolist() == views[1]["store"].tolist() == [1.0, 2.0]
+
+
+def test_shard_states_merge_to_reference_checkpoint_keys():
+    """Per-rank shard states -> the keys a reference checkpoint holds for the entity table, and back."""
+    import torch
+    from smore_b200 import sharded
+    n, w, world = 1003, 8, 4
+    full = {"embedding": torch.randn(n, w), "state_sum_fo": torch.randn(n, w), "state_sum_sq": torch.rand(n, 1)}
+    states = []
+    for r in reversed(range(world)):          # any order
+        st = {"rank": r, "world": world, "n_rows_total": n, "width": w, "squeeze": True}
+        st.update({k: sharded.rows_of_rank(v, r, world).clone() for k, v in full.items()})
+        states.append(st)
+    assert sum(st["embedding"].shape[0] for st in states) == n
+    merged = sharded.merge_shard_states(states)
+    assert sorted(merged) == ["entity_embedding.embedding", "entity_embedding.state_sum_fo",
+                              "entity_embedding.state_sum_sq"]
+    for k, v in full.items():
+        assert torch.equal(merged["entity_embedding." + k], v)
+    with pytest.raises(ValueError):
+        sharded.merge_shard_states(states[:-1])
+    states[0]["width"] = 9
+    with pytest.raises(ValueError):
+        sharded.merge_shard_states(states)
