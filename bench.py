@@ -670,6 +670,8 @@ def run_gpu(args):
             step(*dev_batches[i % pool], upcoming=dev_batches[(i + 1) % pool][1:] + (None,))
 
     copy_stream = torch.cuda.Stream(device)
+    from smore_b200.feed import BatchFeeder
+    feeder = BatchFeeder(device, depth=2)
 
     def upload(i):
         """Start the host -> device copy of batch i's index tensors (pinned memory) on the copy
@@ -703,17 +705,21 @@ def run_gpu(args):
                     t.record_stream(main)
                 last = replay_chained(i, host_batches[i % pool][0], (s_next,) + tuple(dev)).item()
             return last
-        nxt = upload(k0)
+        # host batches go through the library's BatchFeeder (pinned staging, copy stream): batch i + 1
+        # is on its way when step i is launched, batch i + 2 is staged while step i runs on the GPU -
+        # the role of the sampler's prefetch thread
+        for j in range(k0, min(k0 + 2, k0 + k)):
+            feeder.submit(host_batches[j % pool][0], *host_batches[j % pool][1:])
         for i in range(k0, k0 + k):
-            s, dev, done = nxt
+            batch = feeder.get()
             upcoming = None
-            if i + 1 < k0 + k:
-                nxt = upload(i + 1)
-                upcoming = tuple(nxt[1]) + (nxt[2],)
-            main.wait_event(done)
-            for t in dev:
-                t.record_stream(main)
-            last = step(s, *dev, upcoming=upcoming).item()   # the loss is read back by the host every step
+            if prefetching and len(feeder):
+                nxt = feeder.peek()
+                upcoming = tuple(nxt.tensors) + (nxt.event,)
+            loss = step(batch.tag, *batch.tensors, upcoming=upcoming)
+            if i + 2 < k0 + k:
+                feeder.submit(host_batches[(i + 2) % pool][0], *host_batches[(i + 2) % pool][1:])
+            last = loss.item()        # the step's loss is read back by the host every step
         return last
 
     # keep Python's cycle collector from scanning the long-lived model objects inside a timed region
