@@ -145,8 +145,9 @@ SMORE_API int smore_box_backward(const float* gout_out, const float* gout_in, co
                        size_t ne, size_t bc, size_t nc, size_t dim, void* stream);
 
 /* Kernels that stage table rows through shared memory with bulk asynchronous copies wait for each
- * copy with a time limit (about a second).  A wait that runs out sets bit 0 of a device-side status
- * word, the kernel stops early and its results are invalid; nothing else reports it.  This call
+ * copy with a time limit (about a second).  A wait that runs out sets a bit of a device-side status
+ * word (bit 0: distance kernels, bit 1: background row pull), the kernel stops early and its
+ * results are invalid; nothing else reports it.  This call
  * synchronises the current device and returns the status word of that device (0 = every wait so far
  * completed).  No counterpart in the reference. */
 SMORE_API int smore_async_status(int* status);
@@ -357,7 +358,10 @@ SMORE_API int smore_fetch_rows(const float* const* shard_ptrs, size_t rows_per_s
  * of all bitmaps first).  The result equals fetching everything after the barrier.
  * smore_fetch_rows_background is smore_fetch_rows on at most max_ctas thread blocks, so that the
  * kernels of the current step, launched afterwards on another stream, find room on every SM
- * instead of queueing behind the copy (one block per SM keeps NVLink busy). */
+ * instead of queueing behind the copy (one block per SM keeps NVLink busy).  For rows of up to
+ * 20 KB it moves every row with two bulk asynchronous copies (peer memory -> shared memory ->
+ * local staging block; untiled, no multicast) issued by 64-thread blocks, so that the copy takes
+ * next to no registers, issue slots or load/store bandwidth from those kernels. */
 SMORE_API int smore_fetch_rows_background(const float* const* shard_ptrs, size_t rows_per_shard,
                                 const int64_t* uniq, const int32_t* n_unique, size_t capacity,
                                 size_t width, float* staging, size_t max_ctas, void* stream);

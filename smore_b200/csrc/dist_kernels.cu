@@ -1389,12 +1389,15 @@ int smore_union_backward_rows(int dist_id, const float* gout0, const float* gout
                                                       slot_count, g_rows, g_first, g_second, st));
 }
 
+extern "C" int smore_peer_async_status(int* status);   // peer_kernels.cu (not part of the public header)
+
 int smore_async_status(int* status) {
   if (!status) return fail(SMORE_ERR_NULL, "async_status: NULL pointer");
-  int v = 0;
+  int v = 0, peer = 0;
   cudaError_t e = cudaMemcpyFromSymbol(&v, g_async_status, sizeof(int));
   if (e != cudaSuccess) return fail(SMORE_ERR_CUDA, "async_status: %s", cudaGetErrorString(e));
-  *status = v;
+  if (int rc = smore_peer_async_status(&peer)) return rc;   // the row-pull kernels keep their own word
+  *status = v | (peer << 1);
   return SMORE_OK;
 }
 

@@ -21,6 +21,7 @@
 #include <climits>
 #include <cstring>
 
+#include "bulk_copy.cuh"
 #include "common.cuh"
 #include "update_math.cuh"
 
@@ -110,6 +111,62 @@ __global__ void __launch_bounds__(256)
       }
     }
   }
+}
+
+// The background form of the row pull: no registers or load/store slots to speak of.  A CTA is two
+// warps; every active lane owns one row slot in shared memory and moves one row at a time with
+// two bulk asynchronous copies, peer (or local) global memory -> slot -> local staging block,
+// tracked by the lane's mbarrier and bulk group.  The copy engine does the work; the SM's
+// registers, issue slots and load/store units stay with the kernels of the step in progress.
+// No multicast, no tensor maps: plain untiled bulk copies, which may read a peer's memory.
+__device__ int g_peer_async_status = 0;   // bit 0: a bounded wait for a bulk copy gave up
+
+constexpr int kBulkFetchWarps = 2;
+
+__global__ void __launch_bounds__(kBulkFetchWarps * 32)
+    fetch_rows_bulk_kernel(const float* const* __restrict__ shard_ptrs, size_t rows_per_shard,
+                           const int64_t* __restrict__ uniq, const int32_t* __restrict__ n_unique,
+                           unsigned row_bytes, int slots_per_warp, unsigned char* __restrict__ staging) {
+  extern __shared__ __align__(128) unsigned char fetch_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(fetch_smem);                       // [warps][32]
+  unsigned char* slots = fetch_smem + kBulkFetchWarps * 32 * sizeof(uint64_t);    // [warps][slots_per_warp][row_bytes]
+  uint64_t* bar = bars + warp * 32 + lane;
+  unsigned char* slot = slots + ((size_t)warp * slots_per_warp + lane) * row_bytes;
+  const bool owns_slot = lane < slots_per_warp;
+  if (owns_slot) bulk::barrier_init(bar, 1);
+  bulk::fence_barrier_init();
+  __syncthreads();
+  const size_t nu = (size_t)max(n_unique[0], 0);
+  const size_t seglen = (nu + kFetchSegments - 1) / kFetchSegments;
+  const size_t total = seglen * kFetchSegments;
+  const size_t per_sweep = (size_t)gridDim.x * kBulkFetchWarps * slots_per_warp;
+  unsigned parity = 0;
+  for (size_t t0 = ((size_t)blockIdx.x * kBulkFetchWarps + warp) * slots_per_warp; t0 < total; t0 += per_sweep) {
+    const size_t t = t0 + lane;
+    // the same interleaving of the sorted id list as fetch_rows_kernel: neighbours hit different owners
+    size_t u = (t % kFetchSegments) * seglen + t / kFetchSegments;
+    const bool work = owns_slot && t < total && u < nu;
+    if (work) {
+      const size_t id = (size_t)uniq[u];
+      const size_t owner = id / rows_per_shard, local = id - owner * rows_per_shard;
+      const unsigned char* src = reinterpret_cast<const unsigned char*>(shard_ptrs[owner]) + local * (size_t)row_bytes;
+      bulk::barrier_expect(bar, row_bytes);
+      bulk::load(slot, src, row_bytes, bar);
+    }
+    bool ok = !work || bulk::barrier_wait(bar, parity);
+    if (!__all_sync(0xffffffffu, ok)) {
+      if (lane == 0) atomicOr(&g_peer_async_status, 1);
+      break;   // copies that did arrive stay in shared memory; nothing else is in flight for this warp
+    }
+    if (work) {
+      bulk::store(staging + u * (size_t)row_bytes, slot, row_bytes);
+      bulk::commit_group();
+      bulk::wait_group_read<0>();   // the slot may be overwritten by the next sweep's load
+    }
+    parity ^= 1u;
+  }
+  bulk::wait_group<0>();
 }
 
 // Rows that were pulled into `staging` BEFORE their owners finished the previous step's update may
@@ -368,10 +425,38 @@ int smore_fetch_rows(const float* const* shard_ptrs, size_t rows_per_shard, cons
   return fetch_rows_impl(shard_ptrs, rows_per_shard, uniq, n_unique, capacity, width, staging, 0, stream);
 }
 
+int smore_peer_async_status(int* status) {
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_peer_async_status, sizeof(int));
+  if (e != cudaSuccess) return fail(SMORE_ERR_CUDA, "async_status: %s", cudaGetErrorString(e));
+  *status = v;
+  return SMORE_OK;
+}
+
 int smore_fetch_rows_background(const float* const* shard_ptrs, size_t rows_per_shard, const int64_t* uniq,
                                 const int32_t* n_unique, size_t capacity, size_t width, float* staging,
                                 size_t max_ctas, void* stream) {
   if (max_ctas == 0) return fail(SMORE_ERR_BAD_SHAPE, "fetch_rows_background: max_ctas must be positive");
+  const size_t row_bytes = width * sizeof(float);
+  if (capacity && shard_ptrs && uniq && n_unique && staging && rows_per_shard && width && (width & 3) == 0 &&
+      aligned16(staging) && row_bytes <= 20 * 1024) {
+    // rows of up to 20 KB: the copy-engine kernel (about 20 KB of slots per warp, two warps per CTA)
+    const int slots = (int)std::min<size_t>(32, std::max<size_t>(1, 20 * 1024 / row_bytes));
+    const size_t smem = kBulkFetchWarps * 32 * sizeof(uint64_t) + (size_t)kBulkFetchWarps * slots * row_bytes;
+    static bool raised = false;
+    if (!raised) {
+      if (cudaFuncSetAttribute(fetch_rows_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024) !=
+          cudaSuccess)
+        return fail(SMORE_ERR_CUDA, "fetch_rows_background: cannot set the shared-memory limit");
+      raised = true;
+    }
+    const size_t want = (capacity + (size_t)kBulkFetchWarps * slots - 1) / ((size_t)kBulkFetchWarps * slots);
+    const unsigned grid = (unsigned)std::max<size_t>(1, std::min(want, max_ctas));
+    fetch_rows_bulk_kernel<<<grid, kBulkFetchWarps * 32, smem, (cudaStream_t)stream>>>(
+        shard_ptrs, rows_per_shard, uniq, n_unique, (unsigned)row_bytes, slots,
+        reinterpret_cast<unsigned char*>(staging));
+    return check_launch("fetch_rows_bulk_kernel");
+  }
   return fetch_rows_impl(shard_ptrs, rows_per_shard, uniq, n_unique, capacity, width, staging, max_ctas, stream);
 }
 
