@@ -286,7 +286,7 @@ SMORE_API int smore_path_project_backward(const float* g_center, const float* g_
  *   ranks[p] = 1 + #{candidates ahead of answer p} - #{answers of the same query ahead of it}
  * where "ahead" means a higher logit, or an equal logit and a lower candidate id (the order of a
  * stable descending sort; torch.argsort leaves ties unspecified).
- *   logits      [n_queries, n_candidates] fp32 (NaN counts as -inf)
+ *   logits      [n_queries, n_candidates] fp32 (ordered as torch.sort does: NaN largest, -0 == +0)
  *   answer_ptr  [n_queries + 1] int64, CSR offsets into answer_ids (device memory)
  *   answer_ids  [n_answers] candidate ids: per query the easy and the hard answers in any order;
  *               the caller keeps the ranks of the hard ones

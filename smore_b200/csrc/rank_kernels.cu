@@ -30,31 +30,37 @@ namespace smore {
 constexpr int kRankThreads = 256;
 constexpr size_t kRankMaxAnswers = 8192;   // per query: sorted in shared memory
 
-__device__ __forceinline__ bool rank_ahead(float x, long long e, float t, long long id) {
-  return x > t || (x == t && e < id);
+// Logits are compared through an order-preserving integer key: the order of torch.sort, in which
+// NaN is the largest value, -0 equals +0, and everything else is the usual float order.
+__device__ __forceinline__ uint32_t rank_key(float x) {
+  if (x != x) return 0xFFFFFFFFu;
+  const uint32_t b = __float_as_uint(x + 0.f);   // -0 + 0 = +0
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
-__device__ __forceinline__ float rank_clean(float x) { return x == x ? x : -INFINITY; }  // NaN sorts last
+__device__ __forceinline__ bool rank_ahead(uint32_t x, long long e, uint32_t t, long long id) {
+  return x > t || (x == t && e < id);
+}
 
 // one CTA per query; P = power of two >= the longest answer list
 __global__ void __launch_bounds__(kRankThreads)
     rank_sort_answers_kernel(const float* __restrict__ logits, size_t n_candidates,
                              const int64_t* __restrict__ answer_ptr, const int64_t* __restrict__ answer_ids,
-                             int P, float* __restrict__ sorted_logit, int64_t* __restrict__ sorted_id,
+                             int P, uint32_t* __restrict__ sorted_logit, int64_t* __restrict__ sorted_id,
                              int32_t* __restrict__ perm) {
   extern __shared__ unsigned char rank_smem[];
-  float* key = reinterpret_cast<float*>(rank_smem);          // [P]
+  uint32_t* key = reinterpret_cast<uint32_t*>(rank_smem);    // [P]
   int32_t* pos = reinterpret_cast<int32_t*>(key + P);        // [P] index into the query's answer list
   const size_t q = blockIdx.x;
   const int64_t begin = answer_ptr[q];
   const int A = (int)(answer_ptr[q + 1] - begin);
   const float* row = logits + q * n_candidates;
   for (int i = threadIdx.x; i < P; i += kRankThreads) {
-    float k = -INFINITY;
+    uint32_t k = 0;
     int32_t p = INT_MAX;
     if (i < A) {
       const int64_t id = answer_ids[begin + i];
-      k = (id >= 0 && (size_t)id < n_candidates) ? rank_clean(row[id]) : -INFINITY;
+      k = (id >= 0 && (size_t)id < n_candidates) ? rank_key(row[id]) : 0u;
       p = i;
     }
     key[i] = k;
@@ -62,7 +68,7 @@ __global__ void __launch_bounds__(kRankThreads)
   }
   __syncthreads();
   // a sorts before b: higher logit, then lower entity id; padding (pos == INT_MAX) last
-  auto before = [&](float ka, int32_t pa, float kb, int32_t pb) -> bool {
+  auto before = [&](uint32_t ka, int32_t pa, uint32_t kb, int32_t pb) -> bool {
     if (pa == INT_MAX || pb == INT_MAX) return pb == INT_MAX && pa != INT_MAX;
     if (ka != kb) return ka > kb;
     const int64_t ia = answer_ids[begin + pa], ib = answer_ids[begin + pb];
@@ -74,7 +80,7 @@ __global__ void __launch_bounds__(kRankThreads)
         const int j = i ^ stride;
         if (j > i) {
           const bool up = (i & size) == 0;     // this pair sorts into "best first" order
-          const float ki = key[i], kj = key[j];
+          const uint32_t ki = key[i], kj = key[j];
           const int32_t pi = pos[i], pj = pos[j];
           const bool swap = up ? before(kj, pj, ki, pi) : before(ki, pi, kj, pj);
           if (swap) {
@@ -96,7 +102,7 @@ __global__ void __launch_bounds__(kRankThreads)
 // grid (chunks over the candidates, queries)
 __global__ void __launch_bounds__(kRankThreads)
     rank_count_kernel(const float* __restrict__ logits, size_t n_candidates, const int64_t* __restrict__ answer_ptr,
-                      const float* __restrict__ sorted_logit, const int64_t* __restrict__ sorted_id,
+                      const uint32_t* __restrict__ sorted_logit, const int64_t* __restrict__ sorted_id,
                       size_t per_cta, int32_t* __restrict__ hist) {
   extern __shared__ unsigned char rank_smem[];
   const size_t q = blockIdx.y;
@@ -104,7 +110,7 @@ __global__ void __launch_bounds__(kRankThreads)
   const int A = (int)(answer_ptr[q + 1] - begin);
   if (A == 0) return;
   int64_t* ids = reinterpret_cast<int64_t*>(rank_smem);      // [A]
-  float* thr = reinterpret_cast<float*>(ids + A);            // [A]
+  uint32_t* thr = reinterpret_cast<uint32_t*>(ids + A);      // [A]
   int32_t* local = reinterpret_cast<int32_t*>(thr + A);      // [A]
   for (int i = threadIdx.x; i < A; i += kRankThreads) {
     ids[i] = sorted_id[begin + i];
@@ -112,13 +118,13 @@ __global__ void __launch_bounds__(kRankThreads)
     local[i] = 0;
   }
   __syncthreads();
-  const float worst = thr[A - 1];
+  const uint32_t worst = thr[A - 1];
   const long long worst_id = ids[A - 1];
   const float* row = logits + q * n_candidates;
   const size_t c0 = (size_t)blockIdx.x * per_cta;
   const size_t c1 = c0 + per_cta < n_candidates ? c0 + per_cta : n_candidates;
-  auto place = [&](float x, size_t e) {
-    x = rank_clean(x);
+  auto place = [&](float logit, size_t e) {
+    const uint32_t x = rank_key(logit);
     if (!rank_ahead(x, (long long)e, worst, worst_id)) return;   // ahead of no answer (the usual case)
     int lo = 0, hi = A - 1;   // first answer this candidate is ahead of
     while (lo < hi) {
@@ -202,7 +208,7 @@ int smore_filtered_ranks(const float* logits, size_t n_queries, size_t n_candida
   unsigned char* w = static_cast<unsigned char*>(workspace);
   int64_t* sorted_id = reinterpret_cast<int64_t*>(w);
   w += align_up(n_answers * sizeof(int64_t), 256);
-  float* sorted_logit = reinterpret_cast<float*>(w);
+  uint32_t* sorted_logit = reinterpret_cast<uint32_t*>(w);
   w += align_up(n_answers * sizeof(int32_t), 256);
   int32_t* perm = reinterpret_cast<int32_t*>(w);
   w += align_up(n_answers * sizeof(int32_t), 256);

@@ -73,3 +73,14 @@ def test_filtered_ranks_rejects_bad_input():
         ranking.filtered_ranks(logits.double(), [[]], [[1]])
     with pytest.raises(_lib.SmoreError):
         ranking.filtered_ranks(torch.zeros(1, 9000, device="cuda"), [[]], [list(range(8193))])
+
+
+def test_filtered_ranks_special_values_follow_torch_sort_order():
+    """NaN ranks first (torch.sort treats it as the largest value), then +inf; -0 ties with +0."""
+    from oracle.native_torch import reference_filtered_ranks
+    from smore_b200 import ranking
+    x = torch.tensor([[0.5, float("nan"), -0.0, 0.0, float("inf"), -float("inf"), 0.5, float("nan"), 1.0, -2.0]])
+    easy, hard = [[2]], [[0, 1, 3, 5, 6, 8]]
+    got = ranking.filtered_ranks(x.cuda(), easy, hard)[0]
+    want = reference_filtered_ranks(x[0], easy[0], hard[0])
+    assert torch.equal(got.cpu().float(), want)
