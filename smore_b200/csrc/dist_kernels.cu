@@ -1030,8 +1030,8 @@ static int launch_backward_bulk(const Shape& s, RowArgs a, RowGradArgs ga, int n
   // Measured on B200: ahead of the column-thread kernel for rows of 2 KB and more (RotatE rows of
   // 4000 B: 1.59 ms against 1.67 ms per 1M rows); for 1600-byte rows it executes more instructions
   // per row (waits, per-row scalars) than that kernel and ends level with it, so those stay there.
-  if (nch != 8) return 0;
   const size_t row_bytes = s.dim * Term::kMul * sizeof(float);
+  if ((nch != 4 && nch != 8) || row_bytes < 2048) return 0;
   const int need = (NB * Term::kNQ + Term::kMul - 1) / Term::kMul;   // ring must hold the final fold
   const int stages = std::max(3, need);
   const size_t q_bytes = (size_t)NB * Term::kNQ * s.dim * sizeof(float);
@@ -1046,7 +1046,7 @@ static int launch_backward_bulk(const Shape& s, RowArgs a, RowGradArgs ga, int n
         (Term::kNQ == 2 && cudaMemsetAsync(ga.g_second, 0, bytes, st) != cudaSuccess))
       return fail(SMORE_ERR_CUDA, "row_backward_bulk_kernel: cudaMemsetAsync failed");
   }
-  auto kern = row_backward_bulk_kernel<Term, NB, 8>;
+  auto kern = nch == 4 ? row_backward_bulk_kernel<Term, NB, 4> : row_backward_bulk_kernel<Term, NB, 8>;
   if (int rc = allow_large_smem(kern, 110 * 1024)) return rc;
   kern<<<(unsigned)(s.bsize * a.chunks), kRowCtaThreads, smem, st>>>(a, ga, stages);
   if (int rc = check_launch("row_backward_bulk_kernel")) return rc;
