@@ -394,8 +394,33 @@ def box_dist_both(entity_embed, center_embed, offset_embed):
     return _dist("box_both", entity_embed, center_embed, offset_embed)
 
 
+_eval_box_cache = None      # (entity, center, offset, versions, which, other result) of the last no-grad call
+
+
+def _box_one_eval(which, entity_embed, center_embed, offset_embed):
+    """Without autograd (evaluation: every entity scored against a batch of queries) the pair of
+    calls box_dist_out / box_dist_in on the same tensors (box.py:160-161) is served by one pass:
+    the first computes both distances and parks the other one until the second call asks for it."""
+    global _eval_box_cache
+    versions = (entity_embed._version, center_embed._version, offset_embed._version)
+    c = _eval_box_cache
+    _eval_box_cache = None
+    if (c is not None and c[0] is entity_embed and c[1] is center_embed and c[2] is offset_embed and
+            c[3] == versions and c[4] != which):
+        return c[5]
+    d_out, d_in = _dist("box_both", entity_embed, center_embed, offset_embed)
+    if which == "out":
+        _eval_box_cache = (entity_embed, center_embed, offset_embed, versions, "out", d_in)
+        return d_out
+    _eval_box_cache = (entity_embed, center_embed, offset_embed, versions, "in", d_out)
+    return d_in
+
+
 def _box_one(which, entity_embed, center_embed, offset_embed):
     if not isinstance(entity_embed, LazyRows):
+        if (not torch.is_grad_enabled() and entity_embed.dim() == 3 and center_embed.dim() == 3
+                and entity_embed.is_cuda):
+            return _box_one_eval(which, entity_embed, center_embed, offset_embed)
         return _dist("box_" + which, entity_embed, center_embed, offset_embed)
     # Query2box asks for "out" and then "in" of the same operands (box.py:160-161).  For table rows
     # the first request computes both in one pass and parks the other result on the handle.

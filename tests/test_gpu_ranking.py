@@ -84,3 +84,28 @@ def test_filtered_ranks_special_values_follow_torch_sort_order():
     got = ranking.filtered_ranks(x.cuda(), easy, hard)[0]
     want = reference_filtered_ranks(x[0], easy[0], hard[0])
     assert torch.equal(got.cpu().float(), want)
+
+
+def test_evaluation_pair_of_box_calls_is_one_pass_and_exact():
+    """Under no_grad, box_dist_out then box_dist_in on the same tensors return what the separate ops
+    return; changed operands are not served from the parked result."""
+    from smore_b200 import _lib, ext_ops
+    torch.manual_seed(1)
+    ent = torch.rand(1, 3000, 64, device="cuda") - 0.5
+    c = torch.rand(5, 1, 64, device="cuda") - 0.5
+    o = torch.rand(5, 1, 64, device="cuda") * 0.2
+    ref_out = ext_ops._dist("box_out", ent, c, o)
+    ref_in = ext_ops._dist("box_in", ent, c, o)
+    L = _lib.lib()
+    with torch.no_grad():
+        n0 = L.smore_kernel_launch_count()
+        d_out = ext_ops.box_dist_out(ent, c, o)
+        d_in = ext_ops.box_dist_in(ent, c, o)
+        assert L.smore_kernel_launch_count() - n0 == 1          # one pass served both
+        assert torch.equal(d_out, ref_out) and torch.equal(d_in, ref_in)
+        d_out2 = ext_ops.box_dist_out(ent, c, o)
+        c.add_(0.1)                                             # operand changed in place: no reuse
+        d_in2 = ext_ops.box_dist_in(ent, c, o)
+        assert torch.equal(d_out2, ref_out)
+        assert torch.equal(d_in2, ext_ops._dist("box_in", ent, c, o))
+        assert not torch.equal(d_in2, ref_in)
