@@ -842,7 +842,7 @@ def run_gpu(args):
                     "traffic": ncu_traffic(args.workload, dom, n_unique_mean), "timing": timing_note}
 
     cpu = None
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:      # reported at N=1 only
         try:
             qps, ms, threads, sample = cpu_reference_steps(cfg, steps=args.cpu_steps, warmup=2)
             cpu = {"value": round(qps, 1), "unit": "queries/s", "cores": threads, "kind": "port",
