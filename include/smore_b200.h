@@ -116,41 +116,55 @@ SMORE_API int smore_dist_backward_f64(int dist_id, const double* gout, const dou
  * query scores the same candidate rows once per branch): the first call may store, the others
  * must add.
  * g_first / g_second are fully written as in smore_dist_backward.
+ *
+ * Row ids are the caller's data and are checked against n_table_rows in every entry point that
+ * takes (table, idx): an id outside [0, n_table_rows) is never dereferenced.  The forward result of
+ * a pair with such an id is NaN, the backward pass takes no gradient from it and writes none for
+ * it, a gathered row is NaN, and bit 2 (value 4) of the status word of smore_async_status is set.
+ * (The reference indexes with torch, which raises a device-side assertion instead,
+ * embed_rw.py:74-77.)  n_table_rows == 0 switches the check off.
  * ------------------------------------------------------------------------------------------ */
 SMORE_API int smore_dist_forward_rows(int dist_id, const float* table, const int64_t* idx,
-                            const float* first, const float* second, float* dst, size_t bsize,
-                            size_t num, size_t be, size_t ne, size_t bc, size_t nc, size_t dim,
-                            void* stream);
+                            size_t n_table_rows, const float* first, const float* second, float* dst,
+                            size_t bsize, size_t num, size_t be, size_t ne, size_t bc, size_t nc,
+                            size_t dim, void* stream);
 
 SMORE_API int smore_dist_backward_rows(int dist_id, const float* gout, const float* table,
-                             const int64_t* idx, const float* first, const float* second,
-                             const int32_t* slot, const int32_t* slot_count, float* g_rows,
-                             float* g_first, float* g_second, size_t bsize, size_t num, size_t be,
-                             size_t ne, size_t bc, size_t nc, size_t dim, void* stream);
+                             const int64_t* idx, size_t n_table_rows, const float* first,
+                             const float* second, const int32_t* slot, const int32_t* slot_count,
+                             float* g_rows, float* g_first, float* g_second, size_t bsize, size_t num,
+                             size_t be, size_t ne, size_t bc, size_t nc, size_t dim, void* stream);
 
 /* Query2box scores both box distances of the same operands (box.py:157-164 calls box_dist_out
  * and box_dist_in back to back).  These two entry points read every entity row once and return
  * / consume both: dst_out, dst_in and gout_out, gout_in are [bsize, num].
  * idx == NULL means `ent` is a materialised [be, ne, dim] operand; then g_ent ([be, ne, dim])
  * receives the entity gradient and slot / slot_count / g_rows must be NULL.  With idx != NULL
- * the rules of the _rows entry points apply and g_ent must be NULL. */
-SMORE_API int smore_box_forward(const float* ent, const int64_t* idx, const float* center,
-                      const float* offset, float* dst_out, float* dst_in, size_t bsize, size_t num,
-                      size_t be, size_t ne, size_t bc, size_t nc, size_t dim, void* stream);
+ * the rules of the _rows entry points apply (n_table_rows included) and g_ent must be NULL. */
+SMORE_API int smore_box_forward(const float* ent, const int64_t* idx, size_t n_table_rows,
+                      const float* center, const float* offset, float* dst_out, float* dst_in,
+                      size_t bsize, size_t num, size_t be, size_t ne, size_t bc, size_t nc, size_t dim,
+                      void* stream);
 
 SMORE_API int smore_box_backward(const float* gout_out, const float* gout_in, const float* ent,
-                       const int64_t* idx, const float* center, const float* offset, float* g_ent,
-                       const int32_t* slot, const int32_t* slot_count, float* g_rows,
-                       float* g_center, float* g_offset, size_t bsize, size_t num, size_t be,
-                       size_t ne, size_t bc, size_t nc, size_t dim, void* stream);
+                       const int64_t* idx, size_t n_table_rows, const float* center,
+                       const float* offset, float* g_ent, const int32_t* slot,
+                       const int32_t* slot_count, float* g_rows, float* g_center, float* g_offset,
+                       size_t bsize, size_t num, size_t be, size_t ne, size_t bc, size_t nc, size_t dim,
+                       void* stream);
 
-/* Kernels that stage table rows through shared memory with bulk asynchronous copies wait for each
- * copy with a time limit (about a second).  A wait that runs out sets a bit of a device-side status
- * word (bit 0: distance kernels, bit 1: background row pull), the kernel stops early and its
- * results are invalid; nothing else reports it.  This call
- * synchronises the current device and returns the status word of that device (0 = every wait so far
- * completed).  No counterpart in the reference. */
+/* Device-side status word.  Kernels that stage table rows through shared memory with bulk
+ * asynchronous copies wait for each copy with a time limit (about a second); a wait that runs out
+ * sets bit 0 (distance kernels) or bit 1 (background row pull), the kernel stops early and its
+ * results are invalid.  Bit 2 is set when a kernel met a row id outside its table (see the _rows
+ * entry points).  Nothing else reports either condition: hosts should read the word where they
+ * synchronise anyway (when they read the loss, before a checkpoint).  This call synchronises the
+ * current device and returns that device's word (0 = nothing happened so far); the bits stay set
+ * until smore_async_status_clear.  No counterpart in the reference. */
 SMORE_API int smore_async_status(int* status);
+/* Synchronises the current device and sets its status word back to 0 (a host that has dealt with
+ * what the word reported, e.g. dropped the offending batch). */
+SMORE_API int smore_async_status_clear(void);
 
 /* Union queries (query operand [B, U, 1, dim]): the reference front-ends loop over the U branches
  * in Python, call the op once per branch on the same entity operand and stack the results to
@@ -166,22 +180,24 @@ SMORE_API int smore_async_status(int* status);
  * callers run other counts branch by branch.  SMORE_ERR_BAD_SHAPE if dim is not a multiple of 4,
  * exceeds 1024, an operand is not 16-byte aligned or num < 4. */
 SMORE_API int smore_union_forward_rows(int dist_id, const float* table, const int64_t* idx,
-                             const float* first, const float* second, float* dst0, float* dst1,
-                             size_t branches, size_t bsize, size_t num, size_t dim, void* stream);
+                             size_t n_table_rows, const float* first, const float* second, float* dst0,
+                             float* dst1, size_t branches, size_t bsize, size_t num, size_t dim,
+                             void* stream);
 
 SMORE_API int smore_union_backward_rows(int dist_id, const float* gout0, const float* gout1,
-                              const float* table, const int64_t* idx, const float* first,
-                              const float* second, const int32_t* slot, const int32_t* slot_count,
-                              float* g_rows, float* g_first, float* g_second, size_t branches,
-                              size_t bsize, size_t num, size_t dim, void* stream);
+                              const float* table, const int64_t* idx, size_t n_table_rows,
+                              const float* first, const float* second, const int32_t* slot,
+                              const int32_t* slot_count, float* g_rows, float* g_first, float* g_second,
+                              size_t branches, size_t bsize, size_t num, size_t dim, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Row gather, per-step gradient merge and row-wise optimizers.
  * ------------------------------------------------------------------------------------------ */
 
-/* out[p, :] = table[idx[p], :]   (embed_rw.py:74-77: self.embed[indices]). */
-SMORE_API int smore_gather_rows(const float* table, const int64_t* idx, float* out, size_t n, size_t width,
-                      void* stream);
+/* out[p, :] = table[idx[p], :]   (embed_rw.py:74-77: self.embed[indices]); ids are checked against
+ * n_table_rows as described for the _rows entry points (a bad id gives a NaN row). */
+SMORE_API int smore_gather_rows(const float* table, const int64_t* idx, size_t n_table_rows, float* out,
+                      size_t n, size_t width, void* stream);
 
 /* Sorted-unique of a step's row ids with inverse map — the result of
  * torch.unique(cat(idx_list), return_inverse=True) in merge_grad_indices

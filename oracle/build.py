@@ -6,7 +6,12 @@ TEST INFRASTRUCTURE.  Outputs:
                                        behind ref_host_driver.cpp        (needs the reference tree)
   oracle/_ref/libsmore_ref_cuda.so     the reference's CUDA kernels compiled for sm_100a behind
                                        ref_cuda_wrapper.cu               (needs the reference tree)
-Reference sources are compiled where they lie; nothing is copied into this repository.
+  oracle/_ref/pyref/smore/             the reference's Python package (*.py only) placed next to the
+                                       two libraries, so that its own op front-ends, models and
+                                       training step can be imported where the reference tree is
+                                       not mounted (oracle/ref_harness.py)
+Reference sources are compiled where they lie; oracle/_ref/ is a build output that version control
+ignores, so nothing of the reference enters this repository's history.
 
 Usage: python oracle/build.py [--reference DIR] [--force]
 """
@@ -16,7 +21,18 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-DEFAULT_REFERENCE = os.environ.get("SMORE_REFERENCE_DIR", "/root/reference")
+
+
+def default_reference():
+    """$SMORE_REFERENCE_DIR, else a checkout named `reference` beside this repository, else ''."""
+    env = os.environ.get("SMORE_REFERENCE_DIR", "")
+    if env:
+        return env
+    beside = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return beside if os.path.isdir(os.path.join(beside, "smore")) else ""
+
+
+DEFAULT_REFERENCE = default_reference()
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 
@@ -43,7 +59,33 @@ def build_oracle(force=False):
     return out
 
 
+def build_pyref(reference_dir, force=False):
+    """Place the reference's Python package under oracle/_ref/pyref (files are taken as they are)."""
+    import shutil
+    src_root = os.path.join(reference_dir, "smore")
+    if not os.path.isfile(os.path.join(src_root, "common", "torchext", "ext_ops.py")):
+        return []
+    dst_root = os.path.join(HERE, "_ref", "pyref", "smore")
+    n = 0
+    for dirpath, dirnames, filenames in os.walk(src_root):
+        dirnames[:] = [d for d in dirnames if d not in ("build", "__pycache__")]
+        for name in filenames:
+            if not name.endswith(".py"):
+                continue
+            src = os.path.join(dirpath, name)
+            dst = os.path.join(dst_root, os.path.relpath(src, src_root))
+            if force or _newer(dst, [src]):
+                os.makedirs(os.path.dirname(dst), exist_ok=True)
+                shutil.copyfile(src, dst)
+                n += 1
+    if n:
+        print("placed %d reference .py files under %s" % (n, os.path.relpath(dst_root, HERE)), flush=True)
+    return [dst_root]
+
+
 def build_reference(reference_dir, force=False):
+    if not reference_dir:
+        return []
     ext_dir = os.path.join(reference_dir, "smore", "common", "torchext")
     if not os.path.isfile(os.path.join(ext_dir, "dist_kernel.h")):
         return []
@@ -67,12 +109,15 @@ def build_reference(reference_dir, force=False):
               "-shared", "-Xcompiler", "-fPIC", "-I", ext_dir,
               "-o", cuda_out, cuda_src, ref_cu])
     built.append(cuda_out)
+    built += build_pyref(reference_dir, force)
     return built
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=DEFAULT_REFERENCE)
+    ap.add_argument("--reference", default=DEFAULT_REFERENCE,
+                    help="checkout of the reference (default: $SMORE_REFERENCE_DIR, else ../reference); without it only "
+                         "the C oracle is built")
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
     outs = [build_oracle(a.force)]

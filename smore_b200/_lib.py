@@ -29,14 +29,15 @@ SIGNATURES = {
     "smore_dist_backward": (_int, [_int] + [_p] * 7 + [_sz] * 7 + [_p]),
     "smore_dist_forward_f64": (_int, [_int, _p, _p, _p, _p] + [_sz] * 7 + [_p]),
     "smore_dist_backward_f64": (_int, [_int] + [_p] * 7 + [_sz] * 7 + [_p]),
-    "smore_dist_forward_rows": (_int, [_int, _p, _p, _p, _p, _p] + [_sz] * 7 + [_p]),
-    "smore_dist_backward_rows": (_int, [_int] + [_p] * 10 + [_sz] * 7 + [_p]),
-    "smore_box_forward": (_int, [_p] * 6 + [_sz] * 7 + [_p]),
-    "smore_box_backward": (_int, [_p] * 12 + [_sz] * 7 + [_p]),
+    "smore_dist_forward_rows": (_int, [_int, _p, _p, _sz, _p, _p, _p] + [_sz] * 7 + [_p]),
+    "smore_dist_backward_rows": (_int, [_int, _p, _p, _p, _sz] + [_p] * 7 + [_sz] * 7 + [_p]),
+    "smore_box_forward": (_int, [_p, _p, _sz] + [_p] * 4 + [_sz] * 7 + [_p]),
+    "smore_box_backward": (_int, [_p] * 4 + [_sz] + [_p] * 8 + [_sz] * 7 + [_p]),
     "smore_async_status": (_int, [ctypes.POINTER(ctypes.c_int)]),
-    "smore_union_forward_rows": (_int, [_int] + [_p] * 6 + [_sz] * 4 + [_p]),
-    "smore_union_backward_rows": (_int, [_int] + [_p] * 11 + [_sz] * 4 + [_p]),
-    "smore_gather_rows": (_int, [_p, _p, _p, _sz, _sz, _p]),
+    "smore_async_status_clear": (_int, []),
+    "smore_union_forward_rows": (_int, [_int, _p, _p, _sz] + [_p] * 4 + [_sz] * 4 + [_p]),
+    "smore_union_backward_rows": (_int, [_int] + [_p] * 4 + [_sz] + [_p] * 7 + [_sz] * 4 + [_p]),
+    "smore_gather_rows": (_int, [_p, _p, _sz, _p, _sz, _sz, _p]),
     "smore_unique_rows_workspace_bytes": (_sz, [_sz]),
     "smore_unique_rows": (_int, [_p, _sz, _sz, _p, _p, _p, _p, _p, _sz, _p]),
     "smore_unique_rows_static": (_int, [_p, _sz, _sz, _p, _p, _p, _p, _p]),
@@ -101,6 +102,13 @@ def async_status():
     v = ctypes.c_int(0)
     check(lib().smore_async_status(ctypes.byref(v)), "smore_async_status")
     return v.value
+
+
+def async_status_clear():
+    check(lib().smore_async_status_clear(), "smore_async_status_clear")
+
+
+STATUS_COPY_WAIT, STATUS_PEER_WAIT, STATUS_BAD_ROW_ID = 1, 2, 4
 
 
 # ---- optional per-kernel timing (benchmarks only) ----------------------------------------------

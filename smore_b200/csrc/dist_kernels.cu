@@ -37,6 +37,7 @@ struct CellArgs {
   const T* first;      // [bc*nc, dim]
   const T* second;     // [bc*nc, dim] (== first for single-operand distances)
   size_t bsize, num, be, ne, bc, nc, dim;
+  long long n_rows;    // rows of `ent` when idx != nullptr (0: ids are not checked)
 };
 
 template <typename T, class Term>
@@ -49,7 +50,12 @@ __global__ void __launch_bounds__(256) cell_forward_kernel(CellArgs<T> a, T* __r
        cell += warps_per_grid) {
     const size_t i = cell / a.num, j = cell - i * a.num;
     size_t row = (i % a.be) * a.ne + (j % a.ne);
-    if (a.idx) row = (size_t)a.idx[row];
+    bool bad = false;
+    if (a.idx) {
+      const long long r = checked_row_id(a.idx, row, a.n_rows, &g_async_status);
+      bad = r < 0;
+      row = bad ? 0 : (size_t)r;
+    }
     const T* pe = a.ent + row * a.dim * Term::kMul;
     const size_t qrow = (i % a.bc) * a.nc + (j % a.nc);
     const T* p0 = a.first + qrow * a.dim;
@@ -68,8 +74,8 @@ __global__ void __launch_bounds__(256) cell_forward_kernel(CellArgs<T> a, T* __r
       for (int m = kWarp / 2; m > 0; m >>= 1) acc[o] += __shfl_xor_sync(0xffffffffu, acc[o], m);
     }
     if (lane == 0) {
-      dst0[cell] = acc[0];
-      if (Term::kNOut == 2) dst1[cell] = acc[Term::kNOut - 1];
+      dst0[cell] = bad ? T(NAN) : acc[0];
+      if (Term::kNOut == 2) dst1[cell] = bad ? T(NAN) : acc[Term::kNOut - 1];
     }
   }
 }
@@ -88,7 +94,12 @@ __global__ void __launch_bounds__(256)
        t += (size_t)gridDim.x * blockDim.x) {
     const size_t pos = t / a.dim, d = t - pos * a.dim;
     const size_t r0 = pos / a.ne, r1 = pos - r0 * a.ne;
-    const size_t row = a.idx ? (size_t)a.idx[pos] : pos;
+    size_t row = pos;
+    if (a.idx) {
+      const long long r = checked_row_id(a.idx, pos, a.n_rows, &g_async_status);
+      if (r < 0) continue;   // no gradient from (or for) a row that does not exist
+      row = (size_t)r;
+    }
     const T* pe = a.ent + row * a.dim * Term::kMul;
     const T e0 = pe[d];
     const T e1 = Term::kMul == 2 ? pe[d + a.dim] : T(0);
@@ -140,7 +151,11 @@ __global__ void __launch_bounds__(256)
       for (size_t jj = 0; jj < njj; ++jj) {
         const size_t j = jj * a.nc + r1;
         size_t row = (i % a.be) * a.ne + (j % a.ne);
-        if (a.idx) row = (size_t)a.idx[row];
+        if (a.idx) {
+          const long long r = checked_row_id(a.idx, row, a.n_rows, &g_async_status);
+          if (r < 0) continue;
+          row = (size_t)r;
+        }
         const T* pe = a.ent + row * a.dim * Term::kMul;
         T g[Term::kNOut];
         g[0] = gout0[i * a.num + j];
@@ -170,6 +185,7 @@ struct RowArgs {
   int rows_per_cta;        // multiple of kRowCtaWarps * wrows
   int chunks;              // CTAs per query
   int wrows;               // rows a warp takes per sweep (<= 32)
+  long long n_rows;        // rows of `ent` when idx != nullptr (0: ids are not checked)
 };
 
 __device__ __forceinline__ float4 ld_row4(const float4* p) { return __ldg(p); }
@@ -222,14 +238,14 @@ __global__ void __launch_bounds__(kRowCtaThreads)
   for (int base = r_begin + warp * a.wrows; base < r_end; base += kRowCtaWarps * a.wrows) {
     const int n = min(a.wrows, r_end - base);
     const size_t pos = (size_t)b * a.K + base + lane;
-    long long myrow = 0;
-    if (lane < n) myrow = a.idx ? (long long)a.idx[pos] : (long long)pos;
+    long long myrow = 0;   // -1: an id outside the table (row 0 is read instead, the result is NaN)
+    if (lane < n) myrow = a.idx ? checked_row_id(a.idx, pos, a.n_rows, &g_async_status) : (long long)pos;
     float out0 = 0.f, out1 = 0.f;
     for (int t = 0; t < n; t += R) {
       float4 e[R][Term::kMul][NCH];
 #pragma unroll
       for (int r = 0; r < R; ++r) {
-        const long long row = __shfl_sync(0xffffffffu, myrow, min(t + r, n - 1));
+        const long long row = max(__shfl_sync(0xffffffffu, myrow, min(t + r, n - 1)), 0LL);
         const float4* pe = ent4 + (size_t)row * w4;
 #pragma unroll
         for (int j = 0; j < NCH; ++j) {
@@ -258,8 +274,8 @@ __global__ void __launch_bounds__(kRowCtaThreads)
       }
     }
     if (lane < n) {
-      dst0[pos] = out0;
-      if (Term::kNOut == 2) dst1[pos] = out1;
+      dst0[pos] = myrow < 0 ? NAN : out0;
+      if (Term::kNOut == 2) dst1[pos] = myrow < 0 ? NAN : out1;
     }
   }
 }
@@ -331,7 +347,7 @@ __global__ void __launch_bounds__(kRowCtaThreads)
       {
         const int l = lane < n ? lane : 0;   // surplus lanes repeat the tile's first row: harmless loads
         const size_t pos = (size_t)b * a.K + r_begin + grp + (size_t)groups * (t0 + l);
-        const size_t row = a.idx ? (size_t)a.idx[pos] : pos;
+        const long long row = a.idx ? checked_row_id(a.idx, pos, a.n_rows, &g_async_status) : (long long)pos;
         long long dst = (long long)pos;
         int single = 1;
         if (ga.slot) {
@@ -339,9 +355,13 @@ __global__ void __launch_bounds__(kRowCtaThreads)
           dst = s;
           single = (s >= 0 && ga.slot_count != nullptr) ? (ga.slot_count[s] == 1) : 0;
         }
-        meta_src[warp][lane] = row * w4;
-        meta_dst[warp][lane] = dst < 0 ? -1 : dst * (long long)w4;
-        meta_g[warp][lane] = make_float2(ga.gout0[pos], Term::kNOut == 2 ? ga.gout1[pos] : 0.f);
+        // an id outside the table: row 0 is read, no gradient is written and, with the output
+        // gradients zeroed, nothing reaches the query gradient either
+        const bool bad = row < 0;
+        meta_src[warp][lane] = bad ? 0 : (size_t)row * w4;
+        meta_dst[warp][lane] = (dst < 0 || bad) ? -1 : dst * (long long)w4;
+        meta_g[warp][lane] = bad ? make_float2(0.f, 0.f)
+                                 : make_float2(ga.gout0[pos], Term::kNOut == 2 ? ga.gout1[pos] : 0.f);
         meta_single[warp][lane] = single;
       }
       __syncwarp();
@@ -412,8 +432,6 @@ __global__ void __launch_bounds__(kRowCtaThreads)
 // Work split: the CTA's block of rows is cut into one contiguous run per warp.
 // ----------------------------------------------------------------------------------------
 
-__device__ int g_async_status = 0;  // bit 0: a wait for a bulk copy gave up (results invalid)
-
 __host__ __device__ inline size_t bulk_ring_offset(int stages) {
   return ((size_t)kRowCtaWarps * stages * sizeof(uint64_t) + 127) & ~(size_t)127;
 }
@@ -455,16 +473,18 @@ __global__ void __launch_bounds__(kRowCtaThreads)
   const size_t pos0 = (size_t)b * a.K + w_begin;
   const unsigned char* ent = reinterpret_cast<const unsigned char*>(a.ent);
 
+  // row ids of a batch of 32 rows, one per lane; -1 marks an id outside the table (row 0 is copied
+  // in its place and the result written for it is NaN)
   auto batch_ids = [&](int first_t) -> long long {
     const int t = first_t + lane;
     if (t >= n) return 0;
-    return a.idx ? (long long)a.idx[pos0 + t] : (long long)(pos0 + t);
+    return a.idx ? checked_row_id(a.idx, pos0 + t, a.n_rows, &g_async_status) : (long long)(pos0 + t);
   };
   long long cur = batch_ids(0), nxt = 0;
   // prologue: fill the ring
   const int ahead = min(stages, n);
   for (int t = 0; t < ahead; ++t) {
-    const long long row = __shfl_sync(0xffffffffu, cur, t);
+    const long long row = max(__shfl_sync(0xffffffffu, cur, t), 0LL);
     if (lane == 0) {
       bulk::barrier_expect(bars + t, row_bytes);
       bulk::load(ring + (size_t)t * row_bytes, ent + (size_t)row * row_bytes, row_bytes, bars + t);
@@ -480,7 +500,7 @@ __global__ void __launch_bounds__(kRowCtaThreads)
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) {
       // give up: let the copies still in flight land (bounded), flag the failure, stop
-      if (lane == 0) atomicOr(&g_async_status, 1);
+      if (lane == 0) atomicOr(&g_async_status, kStatusCopyWait);
       for (int k = 1; k < stages && t + k < n; ++k) {
         const int s2 = (slot + k) % stages;
         bulk::barrier_wait(bars + s2, s2 > slot ? parity : parity ^ 1u);
@@ -506,7 +526,7 @@ __global__ void __launch_bounds__(kRowCtaThreads)
     __syncwarp();
     const int tn = t + stages;
     if (tn < n) {
-      const long long row = __shfl_sync(0xffffffffu, (tn >> 5) == (t >> 5) ? cur : nxt, tn & 31);
+      const long long row = max(__shfl_sync(0xffffffffu, (tn >> 5) == (t >> 5) ? cur : nxt, tn & 31), 0LL);
       if (lane == 0) {
         bulk::barrier_expect(bars + slot, row_bytes);
         bulk::load(ring + (size_t)slot * row_bytes, ent + (size_t)row * row_bytes, row_bytes, bars + slot);
@@ -519,8 +539,8 @@ __global__ void __launch_bounds__(kRowCtaThreads)
     if (tl == 31 || t == n - 1) {
       if (lane <= tl) {
         const size_t o = pos0 + (t - tl) + lane;
-        dst0[o] = out0;
-        if (Term::kNOut == 2) dst1[o] = out1;
+        dst0[o] = cur < 0 ? NAN : out0;
+        if (Term::kNOut == 2) dst1[o] = cur < 0 ? NAN : out1;
       }
       cur = nxt;
     }
@@ -604,18 +624,25 @@ __global__ void __launch_bounds__(kRowCtaThreads, 2)
     const int t = first_t + lane;
     if (t < n) {
       const size_t pos = pos0 + t;
-      m.src = a.idx ? (long long)a.idx[pos] : (long long)pos;
+      m.src = a.idx ? checked_row_id(a.idx, pos, a.n_rows, &g_async_status) : (long long)pos;
       m.dst = (long long)pos;
       if (ga.slot) {
         const int32_t sl = ga.slot[pos];
         m.dst = sl;
         m.single = (sl >= 0 && ga.slot_count != nullptr) ? (ga.slot_count[sl] == 1) : 0;
       }
+      if (m.src < 0) {
+        // an id outside the table: row 0 is copied, nothing is written for it and its output
+        // gradients stay zero, so the query gradients see nothing of it either
+        m.src = 0;
+        m.dst = -1;
+      } else {
 #pragma unroll
-      for (int u = 0; u < NB; ++u) {
-        const size_t o = ((size_t)b * NB + u) * a.K + (w_begin + t);
-        m.g[u * Term::kNOut] = ga.gout0[o];
-        if (Term::kNOut == 2) m.g[u * Term::kNOut + Term::kNOut - 1] = ga.gout1[o];
+        for (int u = 0; u < NB; ++u) {
+          const size_t o = ((size_t)b * NB + u) * a.K + (w_begin + t);
+          m.g[u * Term::kNOut] = ga.gout0[o];
+          if (Term::kNOut == 2) m.g[u * Term::kNOut + Term::kNOut - 1] = ga.gout1[o];
+        }
       }
     }
     return m;
@@ -638,7 +665,7 @@ __global__ void __launch_bounds__(kRowCtaThreads, 2)
     bool ok = bulk::barrier_wait(bars + slot, parity);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) {
-      if (lane == 0) atomicOr(&g_async_status, 1);
+      if (lane == 0) atomicOr(&g_async_status, kStatusCopyWait);
       for (int k = 1; k < stages - 1 && t + k < n; ++k) {
         const int s2 = (slot + k) % stages;
         bulk::barrier_wait(bars + s2, s2 > slot ? parity : parity ^ 1u);
@@ -755,8 +782,8 @@ __global__ void __launch_bounds__(kRowCtaThreads)
   for (int base = r_begin + warp * a.wrows; base < r_end; base += kRowCtaWarps * a.wrows) {
     const int n = min(a.wrows, r_end - base);
     const size_t pos = (size_t)b * a.K + base + lane;
-    long long myrow = 0;
-    if (lane < n) myrow = a.idx ? (long long)a.idx[pos] : (long long)pos;
+    long long myrow = 0;   // -1: an id outside the table (row 0 is read instead, the result is NaN)
+    if (lane < n) myrow = a.idx ? checked_row_id(a.idx, pos, a.n_rows, &g_async_status) : (long long)pos;
     float out0[NB], out1[NB];
 #pragma unroll
     for (int u = 0; u < NB; ++u) out0[u] = out1[u] = 0.f;
@@ -764,7 +791,7 @@ __global__ void __launch_bounds__(kRowCtaThreads)
       float4 e[R][Term::kMul][NCH];
 #pragma unroll
       for (int r = 0; r < R; ++r) {
-        const long long row = __shfl_sync(0xffffffffu, myrow, min(t + r, n - 1));
+        const long long row = max(__shfl_sync(0xffffffffu, myrow, min(t + r, n - 1)), 0LL);
         const float4* pe = ent4 + (size_t)row * w4;
 #pragma unroll
         for (int j = 0; j < NCH; ++j) {
@@ -801,8 +828,8 @@ __global__ void __launch_bounds__(kRowCtaThreads)
 #pragma unroll
       for (int u = 0; u < NB; ++u) {
         const size_t o = ((size_t)b * NB + u) * a.K + base + lane;
-        dst0[o] = out0[u];
-        if (Term::kNOut == 2) dst1[o] = out1[u];
+        dst0[o] = myrow < 0 ? NAN : out0[u];
+        if (Term::kNOut == 2) dst1[o] = myrow < 0 ? NAN : out1[u];
       }
     }
   }
@@ -855,16 +882,17 @@ __global__ void __launch_bounds__(kRowCtaThreads)
         const int l = lane < n ? lane : 0;
         const int k = r_begin + grp + groups * (t0 + l);
         const size_t pos = (size_t)b * a.K + k;
-        const size_t row = (size_t)a.idx[pos];
+        const long long row = checked_row_id(a.idx, pos, a.n_rows, &g_async_status);
+        const bool bad = row < 0;   // as in col_backward_kernel: read row 0, write and contribute nothing
         const int32_t s = ga.slot[pos];
-        meta_src[warp][lane] = row * w4;
-        meta_dst[warp][lane] = s < 0 ? -1 : s * (long long)w4;
+        meta_src[warp][lane] = bad ? 0 : (size_t)row * w4;
+        meta_dst[warp][lane] = (s < 0 || bad) ? -1 : s * (long long)w4;
         GoutVec<NG> g;
 #pragma unroll
         for (int u = 0; u < NB; ++u) {
           const size_t o = ((size_t)b * NB + u) * a.K + k;
-          g.v[u * Term::kNOut] = ga.gout0[o];
-          if (Term::kNOut == 2) g.v[u * Term::kNOut + Term::kNOut - 1] = ga.gout1[o];
+          g.v[u * Term::kNOut] = bad ? 0.f : ga.gout0[o];
+          if (Term::kNOut == 2) g.v[u * Term::kNOut + Term::kNOut - 1] = bad ? 0.f : ga.gout1[o];
         }
         meta_g[warp][lane] = g;
         meta_single[warp][lane] = (s >= 0 && ga.slot_count != nullptr) ? (ga.slot_count[s] == 1) : 0;
@@ -945,6 +973,7 @@ __global__ void __launch_bounds__(kRowCtaThreads)
 
 struct Shape {
   size_t bsize, num, be, ne, bc, nc, dim;
+  size_t n_rows = 0;   // rows of the table when the entity operand is (table, idx); 0: ids unchecked
 };
 
 static int validate_shape(const Shape& s) {
@@ -961,28 +990,8 @@ static int validate_shape(const Shape& s) {
 
 static int grid_for(size_t work_items, int per_block) {
   size_t blocks = (work_items + per_block - 1) / per_block;
-  const size_t cap = (size_t)kNumSM * 32;
+  const size_t cap = (size_t)sm_count() * 32;
   return (int)std::max<size_t>(1, std::min(blocks, cap));
-}
-
-// Opt a kernel in to more than 48 KB of dynamic shared memory and the largest shared-memory
-// carve-out, once per kernel and device.
-template <class Kernel>
-static int allow_large_smem(Kernel kern, int bytes) {
-  static std::mutex lock;
-  static std::map<std::pair<const void*, int>, bool> done;   // (kernel, device ordinal)
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return fail(SMORE_ERR_CUDA, "cudaGetDevice failed");
-  const std::pair<const void*, int> key(reinterpret_cast<const void*>(kern), dev);
-  std::lock_guard<std::mutex> guard(lock);
-  if (done.count(key)) return SMORE_OK;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess ||
-      cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) !=
-          cudaSuccess)
-    return fail(SMORE_ERR_CUDA, "cannot raise the shared-memory limit of a kernel: %s",
-                cudaGetErrorString(cudaGetLastError()));
-  done[key] = true;
-  return SMORE_OK;
 }
 
 // row-stream launch plan; chunks == 0 means "not eligible"
@@ -1006,7 +1015,7 @@ static RowPlan plan_rows(const Shape& s, bool aligned) {
   size_t sweeps_per_cta = 1;
   const size_t sweeps_total = (K + sweep - 1) / sweep;
   // keep the grid within a few dozen waves; larger blocks of rows amortise the query load
-  const size_t max_ctas = (size_t)kNumSM * 32;
+  const size_t max_ctas = (size_t)sm_count() * 32;
   while (s.bsize * ((sweeps_total + sweeps_per_cta - 1) / sweeps_per_cta) > max_ctas &&
          sweeps_per_cta < sweeps_total)
     sweeps_per_cta *= 2;
@@ -1060,7 +1069,7 @@ static int launch_forward(const Shape& s, const float* ent, const int64_t* idx, 
   const bool aligned = aligned16(ent) && aligned16(first) && aligned16(second);
   const RowPlan p = plan_rows(s, aligned);
   if (p.chunks > 0) {
-    RowArgs a{ent, idx, first, second, (int)s.num, (int)s.dim, p.rows_per_cta, p.chunks, p.wrows};
+    RowArgs a{ent, idx, first, second, (int)s.num, (int)s.dim, p.rows_per_cta, p.chunks, p.wrows, (long long)s.n_rows};
     const unsigned grid = (unsigned)(s.bsize * p.chunks);
     constexpr int R = 2;  // rows in flight per warp at 4 chunks per lane
     // Rows of 1 KB and more go through the bulk-copy kernel: 2..8 slots per warp (about 96 KB of
@@ -1091,12 +1100,12 @@ static int launch_forward(const Shape& s, const float* ent, const int64_t* idx, 
     return check_launch("row_forward_kernel");
   }
   if (shared_shape(s, aligned)) {
-    SharedArgs a{ent, idx, first, second, (int)s.bsize, (int)s.num, (int)s.dim};
+    SharedArgs a{ent, idx, first, second, (int)s.bsize, (int)s.num, (int)s.dim, (long long)s.n_rows};
     dim3 grid((unsigned)((s.num + kTileK - 1) / kTileK), (unsigned)((s.bsize + kTileB - 1) / kTileB));
     shared_forward_kernel<Term><<<grid, 256, 0, st>>>(a, dst0, dst1);
     return check_launch("shared_forward_kernel");
   }
-  CellArgs<float> a{ent, idx, first, second, s.bsize, s.num, s.be, s.ne, s.bc, s.nc, s.dim};
+  CellArgs<float> a{ent, idx, first, second, s.bsize, s.num, s.be, s.ne, s.bc, s.nc, s.dim, (long long)s.n_rows};
   cell_forward_kernel<float, Term><<<grid_for(s.bsize * s.num, 8), 256, 0, st>>>(a, dst0, dst1);
   return check_launch("cell_forward_kernel");
 }
@@ -1115,7 +1124,7 @@ static int launch_backward(const Shape& s, const float* gout0, const float* gout
                        aligned16(g_first) && aligned16(g_second);
   const RowPlan p = plan_rows(s, aligned);
   if (p.chunks > 0) {
-    RowArgs a{ent, idx, first, second, (int)s.num, (int)s.dim, p.rows_per_cta, p.chunks, p.wrows};
+    RowArgs a{ent, idx, first, second, (int)s.num, (int)s.dim, p.rows_per_cta, p.chunks, p.wrows, (long long)s.n_rows};
     RowGradArgs ga{gout0, gout1, g_ent, slot, slot_count, g_rows, g_first, g_second, p.chunks > 1};
     if (int rc = launch_backward_bulk<Term, 1>(s, a, ga, p.nch, st)) return rc < 0 ? rc : SMORE_OK;
     if (p.chunks > 1) {
@@ -1136,7 +1145,7 @@ static int launch_backward(const Shape& s, const float* gout0, const float* gout
     return check_launch("col_backward_kernel");
   }
   if (shared_shape(s, aligned)) {
-    SharedArgs a{ent, idx, first, second, (int)s.bsize, (int)s.num, (int)s.dim};
+    SharedArgs a{ent, idx, first, second, (int)s.bsize, (int)s.num, (int)s.dim, (long long)s.n_rows};
     SharedGradArgs ga{gout0, gout1, g_ent, slot, slot_count, g_rows, g_first, g_second};
     const unsigned cols = (unsigned)(((s.dim >> 2) + kGradCols - 1) / kGradCols);
     dim3 grid_e((unsigned)((s.num + kGradRows - 1) / kGradRows), cols);
@@ -1145,7 +1154,7 @@ static int launch_backward(const Shape& s, const float* gout0, const float* gout
     shared_backward_query_kernel<Term><<<grid_q, kGradRows * kGradCols, 0, st>>>(a, ga);
     return check_launch("shared_backward kernels", 2);
   }
-  CellArgs<float> a{ent, idx, first, second, s.bsize, s.num, s.be, s.ne, s.bc, s.nc, s.dim};
+  CellArgs<float> a{ent, idx, first, second, s.bsize, s.num, s.be, s.ne, s.bc, s.nc, s.dim, (long long)s.n_rows};
   cell_backward_ent_kernel<float, Term><<<grid_for(s.be * s.ne * s.dim, 256), 256, 0, st>>>(
       a, gout0, gout1, g_ent, slot, slot_count, g_rows);
   cell_backward_query_kernel<float, Term><<<grid_for(s.bc * s.nc * s.dim, 256), 256, 0, st>>>(
@@ -1176,7 +1185,7 @@ static int launch_forward_union(size_t branches, const Shape& s, const float* ta
   if (int rc = check_union("union_forward_rows", branches, s, aligned16(table) && aligned16(first) && aligned16(second),
                            &p))
     return rc;
-  RowArgs a{table, idx, first, second, (int)s.num, (int)s.dim, p.rows_per_cta, p.chunks, p.wrows};
+  RowArgs a{table, idx, first, second, (int)s.num, (int)s.dim, p.rows_per_cta, p.chunks, p.wrows, (long long)s.n_rows};
   constexpr int NB = kUnionBranches;
   // (staging the rows with bulk copies, as row_forward_bulk_kernel does, measured no faster here:
   // with two branches per row the kernel is bound by instruction issue, not by memory latency)
@@ -1205,7 +1214,7 @@ static int launch_backward_union(size_t branches, const Shape& s, const float* g
                        aligned16(g_first) && aligned16(g_second);
   if (int rc = check_union("union_backward_rows", branches, s, aligned, &p)) return rc;
   constexpr int NB = kUnionBranches;
-  RowArgs a{table, idx, first, second, (int)s.num, (int)s.dim, p.rows_per_cta, p.chunks, p.wrows};
+  RowArgs a{table, idx, first, second, (int)s.num, (int)s.dim, p.rows_per_cta, p.chunks, p.wrows, (long long)s.n_rows};
   RowGradArgs ga{gout0, gout1, nullptr, slot, slot_count, g_rows, g_first, g_second, p.chunks > 1};
   if (p.chunks > 1) {
     const size_t bytes = s.bsize * NB * s.dim * sizeof(float);
@@ -1229,7 +1238,7 @@ template <class Term>
 static int launch_forward_f64(const Shape& s, const double* ent, const double* first,
                               const double* second, double* dst, cudaStream_t st) {
   if (Term::kNQ == 1) second = first;
-  CellArgs<double> a{ent, nullptr, first, second, s.bsize, s.num, s.be, s.ne, s.bc, s.nc, s.dim};
+  CellArgs<double> a{ent, nullptr, first, second, s.bsize, s.num, s.be, s.ne, s.bc, s.nc, s.dim, (long long)s.n_rows};
   cell_forward_kernel<double, Term><<<grid_for(s.bsize * s.num, 8), 256, 0, st>>>(a, dst, dst);
   return check_launch("cell_forward_kernel<double>");
 }
@@ -1242,7 +1251,7 @@ static int launch_backward_f64(const Shape& s, const double* gout, const double*
     second = first;
     g_second = g_first;
   }
-  CellArgs<double> a{ent, nullptr, first, second, s.bsize, s.num, s.be, s.ne, s.bc, s.nc, s.dim};
+  CellArgs<double> a{ent, nullptr, first, second, s.bsize, s.num, s.be, s.ne, s.bc, s.nc, s.dim, (long long)s.n_rows};
   cell_backward_ent_kernel<double, Term><<<grid_for(s.be * s.ne * s.dim, 256), 256, 0, st>>>(
       a, gout, gout, g_ent, nullptr, nullptr, nullptr);
   cell_backward_query_kernel<double, Term><<<grid_for(s.bc * s.nc * s.dim, 256), 256, 0, st>>>(
@@ -1312,36 +1321,37 @@ int smore_dist_backward(int dist_id, const float* gout, const float* ent, const 
                          g_first, g_second, Shape{bsize, num, be, ne, bc, nc, dim}, stream);
 }
 
-int smore_dist_forward_rows(int dist_id, const float* table, const int64_t* idx, const float* first,
-                            const float* second, float* dst, size_t bsize, size_t num, size_t be, size_t ne,
-                            size_t bc, size_t nc, size_t dim, void* stream) {
+int smore_dist_forward_rows(int dist_id, const float* table, const int64_t* idx, size_t n_table_rows,
+                            const float* first, const float* second, float* dst, size_t bsize, size_t num,
+                            size_t be, size_t ne, size_t bc, size_t nc, size_t dim, void* stream) {
   if (!idx) return fail(SMORE_ERR_NULL, "forward_rows: idx is NULL");
-  return forward_common(dist_id, table, idx, first, second, dst, Shape{bsize, num, be, ne, bc, nc, dim},
-                        stream);
+  return forward_common(dist_id, table, idx, first, second, dst,
+                        Shape{bsize, num, be, ne, bc, nc, dim, n_table_rows}, stream);
 }
 
 int smore_dist_backward_rows(int dist_id, const float* gout, const float* table, const int64_t* idx,
-                             const float* first, const float* second, const int32_t* slot,
+                             size_t n_table_rows, const float* first, const float* second, const int32_t* slot,
                              const int32_t* slot_count, float* g_rows, float* g_first, float* g_second,
                              size_t bsize, size_t num, size_t be, size_t ne, size_t bc, size_t nc,
                              size_t dim, void* stream) {
   if (!idx || !slot) return fail(SMORE_ERR_NULL, "backward_rows: idx or slot is NULL");
   return backward_common(dist_id, gout, table, idx, first, second, nullptr, slot, slot_count, g_rows,
-                         g_first, g_second, Shape{bsize, num, be, ne, bc, nc, dim}, stream);
+                         g_first, g_second, Shape{bsize, num, be, ne, bc, nc, dim, n_table_rows}, stream);
 }
 
-int smore_box_forward(const float* ent, const int64_t* idx, const float* center, const float* offset,
-                      float* dst_out, float* dst_in, size_t bsize, size_t num, size_t be, size_t ne,
-                      size_t bc, size_t nc, size_t dim, void* stream) {
+int smore_box_forward(const float* ent, const int64_t* idx, size_t n_table_rows, const float* center,
+                      const float* offset, float* dst_out, float* dst_in, size_t bsize, size_t num, size_t be,
+                      size_t ne, size_t bc, size_t nc, size_t dim, void* stream) {
   if (!ent || !center || !offset || !dst_out || !dst_in)
     return fail(SMORE_ERR_NULL, "box_forward: required pointer is NULL");
-  const Shape s{bsize, num, be, ne, bc, nc, dim};
+  const Shape s{bsize, num, be, ne, bc, nc, dim, idx ? n_table_rows : 0};
   if (int rc = validate_shape(s)) return rc;
   return launch_forward<TermBoxBoth>(s, ent, idx, center, offset, dst_out, dst_in, (cudaStream_t)stream);
 }
 
 int smore_box_backward(const float* gout_out, const float* gout_in, const float* ent, const int64_t* idx,
-                       const float* center, const float* offset, float* g_ent, const int32_t* slot,
+                       size_t n_table_rows, const float* center, const float* offset, float* g_ent,
+                       const int32_t* slot,
                        const int32_t* slot_count, float* g_rows, float* g_center, float* g_offset,
                        size_t bsize, size_t num, size_t be, size_t ne, size_t bc, size_t nc, size_t dim,
                        void* stream) {
@@ -1349,28 +1359,29 @@ int smore_box_backward(const float* gout_out, const float* gout_in, const float*
     return fail(SMORE_ERR_NULL, "box_backward: required pointer is NULL");
   if (idx ? (!slot || !g_rows || g_ent) : (!g_ent || slot || g_rows))
     return fail(SMORE_ERR_NULL, "box_backward: pass g_ent (materialised) or slot/g_rows (indexed)");
-  const Shape s{bsize, num, be, ne, bc, nc, dim};
+  const Shape s{bsize, num, be, ne, bc, nc, dim, idx ? n_table_rows : 0};
   if (int rc = validate_shape(s)) return rc;
   return launch_backward<TermBoxBoth>(s, gout_out, gout_in, ent, idx, center, offset, g_ent, slot, slot_count,
                                       g_rows, g_center, g_offset, (cudaStream_t)stream);
 }
 
-int smore_union_forward_rows(int dist_id, const float* table, const int64_t* idx, const float* first,
-                             const float* second, float* dst0, float* dst1, size_t branches, size_t bsize,
-                             size_t num, size_t dim, void* stream) {
+int smore_union_forward_rows(int dist_id, const float* table, const int64_t* idx, size_t n_table_rows,
+                             const float* first, const float* second, float* dst0, float* dst1, size_t branches,
+                             size_t bsize, size_t num, size_t dim, void* stream) {
   const bool both = dist_id == SMORE_DIST_BOX_BOTH;
   if (!both && (dist_id < 0 || dist_id >= SMORE_DIST_COUNT))
     return fail(SMORE_ERR_BAD_DIST, "unknown distance id %d", dist_id);
   if (!table || !idx || !first || !dst0 || (both && !dst1) || ((both || needs_second(dist_id)) && !second))
     return fail(SMORE_ERR_NULL, "union_forward_rows: required pointer is NULL");
-  const Shape s{bsize, num, bsize, num, bsize, 1, dim};
+  const Shape s{bsize, num, bsize, num, bsize, 1, dim, n_table_rows};
   cudaStream_t st = (cudaStream_t)stream;
   if (both) return launch_forward_union<TermBoxBoth>(branches, s, table, idx, first, second, dst0, dst1, st);
   SMORE_DISPATCH(dist_id, launch_forward_union<Term>(branches, s, table, idx, first, second, dst0, dst0, st));
 }
 
 int smore_union_backward_rows(int dist_id, const float* gout0, const float* gout1, const float* table,
-                              const int64_t* idx, const float* first, const float* second, const int32_t* slot,
+                              const int64_t* idx, size_t n_table_rows, const float* first, const float* second,
+                              const int32_t* slot,
                               const int32_t* slot_count, float* g_rows, float* g_first, float* g_second,
                               size_t branches, size_t bsize, size_t num, size_t dim, void* stream) {
   const bool both = dist_id == SMORE_DIST_BOX_BOTH;
@@ -1380,7 +1391,7 @@ int smore_union_backward_rows(int dist_id, const float* gout0, const float* gout
   if (!gout0 || (both && !gout1) || !table || !idx || !first || !slot || !g_rows || !g_first ||
       (two && (!second || !g_second)))
     return fail(SMORE_ERR_NULL, "union_backward_rows: required pointer is NULL");
-  const Shape s{bsize, num, bsize, num, bsize, 1, dim};
+  const Shape s{bsize, num, bsize, num, bsize, 1, dim, n_table_rows};
   cudaStream_t st = (cudaStream_t)stream;
   if (both)
     return launch_backward_union<TermBoxBoth>(branches, s, gout0, gout1, table, idx, first, second, slot, slot_count,
@@ -1390,15 +1401,28 @@ int smore_union_backward_rows(int dist_id, const float* gout0, const float* gout
 }
 
 extern "C" int smore_peer_async_status(int* status);   // peer_kernels.cu (not part of the public header)
+extern "C" int smore_rows_status(int* status);         // rows_kernels.cu (likewise)
+extern "C" int smore_peer_status_clear(void);
+extern "C" int smore_rows_status_clear(void);
 
 int smore_async_status(int* status) {
   if (!status) return fail(SMORE_ERR_NULL, "async_status: NULL pointer");
-  int v = 0, peer = 0;
+  int v = 0, peer = 0, rows = 0;
   cudaError_t e = cudaMemcpyFromSymbol(&v, g_async_status, sizeof(int));
   if (e != cudaSuccess) return fail(SMORE_ERR_CUDA, "async_status: %s", cudaGetErrorString(e));
-  if (int rc = smore_peer_async_status(&peer)) return rc;   // the row-pull kernels keep their own word
-  *status = v | (peer << 1);
+  if (int rc = smore_peer_async_status(&peer)) return rc;   // the other files' kernels keep their own words
+  if (int rc = smore_rows_status(&rows)) return rc;
+  *status = v | (peer ? kStatusPeerWait : 0) | rows;
   return SMORE_OK;
+}
+
+int smore_async_status_clear(void) {
+  if (cudaDeviceSynchronize() != cudaSuccess) return fail(SMORE_ERR_CUDA, "async_status_clear: device error");
+  const int zero = 0;
+  if (cudaMemcpyToSymbol(g_async_status, &zero, sizeof(int)) != cudaSuccess)
+    return fail(SMORE_ERR_CUDA, "async_status_clear: cannot write the status word");
+  if (int rc = smore_peer_status_clear()) return rc;
+  return smore_rows_status_clear();
 }
 
 int smore_dist_forward_f64(int dist_id, const double* ent, const double* first, const double* second,

@@ -1,5 +1,8 @@
 // Library-wide state: the thread-local error text and the version tag.
 #include <atomic>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "common.cuh"
 
@@ -12,6 +15,37 @@ char* last_error_buffer() {
 static std::atomic<unsigned long long> g_launches{0};
 void count_launches(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 unsigned long long launches() { return g_launches.load(std::memory_order_relaxed); }
+
+int sm_count() {
+  constexpr int kMaxDevices = 64;
+  static std::atomic<int> cached[kMaxDevices];   // zero-initialised: 0 = not queried yet
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return kNumSMFull;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = kNumSMFull;
+    cached[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
+int allow_large_smem_impl(const void* kernel, int bytes, bool max_carveout) {
+  static std::mutex lock;
+  static std::map<std::pair<const void*, int>, int> done;   // (kernel, device ordinal) -> bytes granted
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return fail(SMORE_ERR_CUDA, "cudaGetDevice failed");
+  const std::pair<const void*, int> key(kernel, dev);
+  std::lock_guard<std::mutex> guard(lock);
+  auto it = done.find(key);
+  if (it != done.end() && it->second >= bytes) return SMORE_OK;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess ||
+      (max_carveout && cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                            cudaSharedmemCarveoutMaxShared) != cudaSuccess))
+    return fail(SMORE_ERR_CUDA, "cannot raise the shared-memory limit of a kernel: %s",
+                cudaGetErrorString(cudaGetLastError()));
+  done[key] = bytes;
+  return SMORE_OK;
+}
 }  // namespace smore
 
 extern "C" {

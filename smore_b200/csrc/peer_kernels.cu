@@ -14,7 +14,8 @@
 //                              ranks that produced them, sums them in a fixed order and applies
 //                              Adam to its shard — transfer, reduction and update in one pass
 // No kernel here waits on another rank: ordering between the phases of a step is the caller's
-// (stream-ordered collectives).  No TMA, no multicast: peer data is read with ordinary loads.
+// (stream-ordered collectives).  Peer data is read with ordinary loads or, in the background row
+// pull, with untiled bulk asynchronous copies (no tensor maps, no multicast).
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -156,8 +157,12 @@ __global__ void __launch_bounds__(kBulkFetchWarps * 32)
     }
     bool ok = !work || bulk::barrier_wait(bar, parity);
     if (!__all_sync(0xffffffffu, ok)) {
+      // give up: flag it, let the copies that are still on their way land (one more bounded wait by
+      // the lanes that own them, so that nothing writes into this CTA's shared memory after it has
+      // left), and stop.  The rows not copied keep whatever the staging block held.
       if (lane == 0) atomicOr(&g_peer_async_status, 1);
-      break;   // copies that did arrive stay in shared memory; nothing else is in flight for this warp
+      if (!ok) bulk::barrier_wait(bar, parity);
+      break;
     }
     if (work) {
       bulk::store(staging + u * (size_t)row_bytes, slot, row_bytes);
@@ -382,10 +387,10 @@ __global__ void __launch_bounds__(256) shard_reduce_update_kernel(UpdateArgs a, 
 }
 
 static int grid_warps(size_t items) {
-  return (int)std::max<size_t>(1, std::min<size_t>((items + 7) / 8, (size_t)kNumSM * 16));
+  return (int)std::max<size_t>(1, std::min<size_t>((items + 7) / 8, (size_t)sm_count() * 16));
 }
 static int grid_threads(size_t items) {
-  return (int)std::max<size_t>(1, std::min<size_t>((items + 255) / 256, (size_t)kNumSM * 16));
+  return (int)std::max<size_t>(1, std::min<size_t>((items + 255) / 256, (size_t)sm_count() * 16));
 }
 
 }  // namespace smore
@@ -433,6 +438,13 @@ int smore_peer_async_status(int* status) {
   return SMORE_OK;
 }
 
+int smore_peer_status_clear(void) {
+  const int zero = 0;
+  if (cudaMemcpyToSymbol(g_peer_async_status, &zero, sizeof(int)) != cudaSuccess)
+    return fail(SMORE_ERR_CUDA, "async_status_clear: cannot write the status word");
+  return SMORE_OK;
+}
+
 int smore_fetch_rows_background(const float* const* shard_ptrs, size_t rows_per_shard, const int64_t* uniq,
                                 const int32_t* n_unique, size_t capacity, size_t width, float* staging,
                                 size_t max_ctas, void* stream) {
@@ -443,13 +455,7 @@ int smore_fetch_rows_background(const float* const* shard_ptrs, size_t rows_per_
     // rows of up to 20 KB: the copy-engine kernel (about 20 KB of slots per warp, two warps per CTA)
     const int slots = (int)std::min<size_t>(32, std::max<size_t>(1, 20 * 1024 / row_bytes));
     const size_t smem = kBulkFetchWarps * 32 * sizeof(uint64_t) + (size_t)kBulkFetchWarps * slots * row_bytes;
-    static bool raised = false;
-    if (!raised) {
-      if (cudaFuncSetAttribute(fetch_rows_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 48 * 1024) !=
-          cudaSuccess)
-        return fail(SMORE_ERR_CUDA, "fetch_rows_background: cannot set the shared-memory limit");
-      raised = true;
-    }
+    if (int rc = allow_large_smem(fetch_rows_bulk_kernel, 48 * 1024, false)) return rc;
     const size_t want = (capacity + (size_t)kBulkFetchWarps * slots - 1) / ((size_t)kBulkFetchWarps * slots);
     const unsigned grid = (unsigned)std::max<size_t>(1, std::min(want, max_ctas));
     fetch_rows_bulk_kernel<<<grid, kBulkFetchWarps * 32, smem, (cudaStream_t)stream>>>(

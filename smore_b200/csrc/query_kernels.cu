@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(256)
 }
 
 static int path_grid(size_t warps_needed) {
-  return (int)std::max<size_t>(1, std::min<size_t>((warps_needed + 7) / 8, (size_t)kNumSM * 16));
+  return (int)std::max<size_t>(1, std::min<size_t>((warps_needed + 7) / 8, (size_t)sm_count() * 16));
 }
 
 }  // namespace smore

@@ -219,19 +219,12 @@ int smore_filtered_ranks(const float* logits, size_t n_queries, size_t n_candida
   int P = 1;
   while ((size_t)P < max_answers) P <<= 1;
   const size_t sort_smem = (size_t)P * 8, count_smem = max_answers * 16;
-  static bool raised = false;
-  if (!raised) {
-    if (cudaFuncSetAttribute(rank_sort_answers_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)(kRankMaxAnswers * 8)) != cudaSuccess ||
-        cudaFuncSetAttribute(rank_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)(kRankMaxAnswers * 16)) != cudaSuccess)
-      return fail(SMORE_ERR_CUDA, "filtered_ranks: cannot raise the shared-memory limit");
-    raised = true;
-  }
+  if (int rc = allow_large_smem(rank_sort_answers_kernel, (int)(kRankMaxAnswers * 8), false)) return rc;
+  if (int rc = allow_large_smem(rank_count_kernel, (int)(kRankMaxAnswers * 16), false)) return rc;
   rank_sort_answers_kernel<<<(unsigned)n_queries, kRankThreads, sort_smem, st>>>(
       logits, n_candidates, answer_ptr, answer_ids, P, sorted_logit, sorted_id, perm);
   // enough CTAs per query to fill the GPU a few times over, at least 4096 candidates each
-  size_t chunks = std::max<size_t>(1, (size_t)kNumSM * 8 / n_queries);
+  size_t chunks = std::max<size_t>(1, (size_t)sm_count() * 8 / n_queries);
   size_t per_cta = std::max<size_t>(4096, (n_candidates + chunks - 1) / chunks);
   chunks = (n_candidates + per_cta - 1) / per_cta;
   dim3 grid((unsigned)chunks, (unsigned)n_queries);

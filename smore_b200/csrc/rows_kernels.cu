@@ -22,14 +22,23 @@ namespace smore {
 // gather
 // ----------------------------------------------------------------------------------------
 
+__device__ int g_rows_status = 0;   // kStatusBadRowId: a gathered id lay outside the table
+
 template <bool VEC>
 __global__ void __launch_bounds__(256)
-    gather_rows_kernel(const float* __restrict__ table, const int64_t* __restrict__ idx,
+    gather_rows_kernel(const float* __restrict__ table, const int64_t* __restrict__ idx, long long n_rows,
                        float* __restrict__ out, size_t n, size_t width) {
   const int lane = threadIdx.x & 31;
   const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
   for (size_t p = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); p < n; p += warps) {
-    const size_t row = (size_t)idx[p];
+    long long rid = 0;
+    if (lane == 0) rid = checked_row_id(idx, p, n_rows, &g_rows_status);
+    rid = __shfl_sync(0xffffffffu, rid, 0);
+    if (rid < 0) {   // an id outside the table: the gathered row is NaN, nothing is read
+      for (size_t d = lane; d < width; d += kWarp) out[p * width + d] = NAN;
+      continue;
+    }
+    const size_t row = (size_t)rid;
     if (VEC) {
       const float4* src = reinterpret_cast<const float4*>(table + row * width);
       float4* dst = reinterpret_cast<float4*>(out + p * width);
@@ -468,12 +477,12 @@ __global__ void __launch_bounds__(256) sparse_update_rows_kernel(UpdateArgs a) {
 
 static int warp_grid(size_t items) {
   const size_t blocks = (items + 7) / 8;
-  return (int)std::max<size_t>(1, std::min<size_t>(blocks, (size_t)kNumSM * 16));
+  return (int)std::max<size_t>(1, std::min<size_t>(blocks, (size_t)sm_count() * 16));
 }
 
 static int thread_grid(size_t items) {
   const size_t blocks = (items + 255) / 256;
-  return (int)std::max<size_t>(1, std::min<size_t>(blocks, (size_t)kNumSM * 16));
+  return (int)std::max<size_t>(1, std::min<size_t>(blocks, (size_t)sm_count() * 16));
 }
 
 }  // namespace smore
@@ -482,17 +491,32 @@ using namespace smore;
 
 extern "C" {
 
-int smore_gather_rows(const float* table, const int64_t* idx, float* out, size_t n, size_t width,
-                      void* stream) {
+int smore_rows_status(int* status) {   // not part of the public header; smore_async_status adds it in
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_rows_status, sizeof(int));
+  if (e != cudaSuccess) return fail(SMORE_ERR_CUDA, "async_status: %s", cudaGetErrorString(e));
+  *status = v;
+  return SMORE_OK;
+}
+
+int smore_rows_status_clear(void) {
+  const int zero = 0;
+  if (cudaMemcpyToSymbol(g_rows_status, &zero, sizeof(int)) != cudaSuccess)
+    return fail(SMORE_ERR_CUDA, "async_status_clear: cannot write the status word");
+  return SMORE_OK;
+}
+
+int smore_gather_rows(const float* table, const int64_t* idx, size_t n_table_rows, float* out, size_t n,
+                      size_t width, void* stream) {
   if (!table || !idx || !out) return fail(SMORE_ERR_NULL, "gather_rows: NULL pointer");
   if (!width) return fail(SMORE_ERR_BAD_SHAPE, "gather_rows: width is 0");
   if (n == 0) return SMORE_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const bool vec = (width % 4 == 0) && aligned16(table) && aligned16(out);
   if (vec)
-    gather_rows_kernel<true><<<warp_grid(n), 256, 0, st>>>(table, idx, out, n, width);
+    gather_rows_kernel<true><<<warp_grid(n), 256, 0, st>>>(table, idx, (long long)n_table_rows, out, n, width);
   else
-    gather_rows_kernel<false><<<warp_grid(n), 256, 0, st>>>(table, idx, out, n, width);
+    gather_rows_kernel<false><<<warp_grid(n), 256, 0, st>>>(table, idx, (long long)n_table_rows, out, n, width);
   return check_launch("gather_rows_kernel");
 }
 

@@ -33,7 +33,13 @@ struct SharedArgs {
   const float* first;      // [B, dim]
   const float* second;     // [B, dim]
   int B, K, dim;           // dim % 4 == 0
+  long long n_rows;        // rows of `ent` when idx != nullptr (0: ids are not checked)
 };
+
+// Device status word of the distance kernels (kStatus* bits): a bulk-copy wait that gave up, a row
+// id outside the table.  Either makes the results of the launch invalid; smore_async_status reads
+// it.  (Defined here because this header is part of exactly one translation unit, dist_kernels.cu.)
+__device__ int g_async_status = 0;
 
 template <class Term>
 __global__ void __launch_bounds__(256)
@@ -42,6 +48,7 @@ __global__ void __launch_bounds__(256)
   __shared__ __align__(16) float q1s[kTileD][kTileB + kTilePad];
   __shared__ __align__(16) float e0s[kTileD][kTileK + kTilePad];
   __shared__ __align__(16) float e1s[Term::kMul == 2 ? kTileD : 1][kTileK + kTilePad];
+  __shared__ unsigned char ebad[kTileK];   // candidate rows of the tile whose id lay outside the table
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int b0 = blockIdx.y * kTileB, k0 = blockIdx.x * kTileK;
   const int dim4 = a.dim >> 2;
@@ -52,7 +59,13 @@ __global__ void __launch_bounds__(256)
   const float4* q0p = reinterpret_cast<const float4*>(a.first) + (size_t)(qrow_ok ? b0 + lrow : 0) * dim4;
   const float4* q1p = reinterpret_cast<const float4*>(a.second) + (size_t)(qrow_ok ? b0 + lrow : 0) * dim4;
   size_t erow = 0;
-  if (erow_ok) erow = a.idx ? (size_t)a.idx[k0 + lrow] : (size_t)(k0 + lrow);
+  if (erow_ok) {
+    const long long r = a.idx ? checked_row_id(a.idx, k0 + lrow, a.n_rows, &g_async_status) : (long long)(k0 + lrow);
+    erow = r < 0 ? 0 : (size_t)r;
+    if (lq == 0) ebad[lrow] = r < 0;
+  } else if (lq == 0) {
+    ebad[lrow] = 0;
+  }
   const float4* e0p = reinterpret_cast<const float4*>(a.ent) + erow * w4;
 
   float acc[4][4][Term::kNOut];
@@ -104,8 +117,9 @@ __global__ void __launch_bounds__(256)
     for (int j = 0; j < 4; ++j) {
       const int k = k0 + tx * 4 + j;
       if (k < a.K) {
-        dst0[(size_t)b * a.K + k] = acc[i][j][0];
-        if (Term::kNOut == 2) dst1[(size_t)b * a.K + k] = acc[i][j][Term::kNOut - 1];
+        const bool bad = ebad[tx * 4 + j];   // written before the first barrier of the loop above
+        dst0[(size_t)b * a.K + k] = bad ? NAN : acc[i][j][0];
+        if (Term::kNOut == 2) dst1[(size_t)b * a.K + k] = bad ? NAN : acc[i][j][Term::kNOut - 1];
       }
     }
   }
@@ -143,7 +157,9 @@ __global__ void __launch_bounds__(kGradRows* kGradCols)
   const int dim4 = a.dim >> 2;
   if (k >= a.K || c4 >= dim4) return;
   const size_t w4 = (size_t)dim4 * Term::kMul;
-  const size_t row = a.idx ? (size_t)a.idx[k] : (size_t)k;
+  const long long rid = a.idx ? checked_row_id(a.idx, k, a.n_rows, &g_async_status) : (long long)k;
+  if (rid < 0) return;   // no gradient for a row that does not exist
+  const size_t row = (size_t)rid;
   const float4* pe = reinterpret_cast<const float4*>(a.ent) + row * w4 + c4;
   const float4 e0 = __ldg(pe);
   const float4 e1 = Term::kMul == 2 ? __ldg(pe + dim4) : e0;
@@ -200,12 +216,14 @@ __global__ void __launch_bounds__(kGradRows* kGradCols)
     // the CTA's threads fetch the next 128 row ids once
     __syncthreads();
     const int kk = k0 + threadIdx.x;
-    rows_sh[threadIdx.x] = kk < a.K ? (a.idx ? (long long)a.idx[kk] : (long long)kk) : 0;
+    rows_sh[threadIdx.x] =
+        kk < a.K ? (a.idx ? checked_row_id(a.idx, kk, a.n_rows, &g_async_status) : (long long)kk) : 0;
     __syncthreads();
     if (!active) continue;
     const int n = min(kGradRows * kGradCols, a.K - k0);
 #pragma unroll 4
     for (int j = 0; j < n; ++j) {
+      if (rows_sh[j] < 0) continue;   // an id outside the table contributes nothing
       const float4* pe = ent4 + (size_t)rows_sh[j] * w4 + c4;
       const float4 e0 = __ldg(pe);
       const float4 e1 = Term::kMul == 2 ? __ldg(pe + dim4) : e0;

@@ -382,8 +382,8 @@ class EmbeddingOptimizer(object):
     def _gather(self, idx):
         out = torch.empty(idx.numel(), self.table.shape[1], dtype=self.table.dtype, device=self.table.device)
         with torch.cuda.device(self.table.device):
-            _lib.check(_lib.lib().smore_gather_rows(self.table.data_ptr(), idx.data_ptr(), out.data_ptr(),
-                                                    idx.numel(), self.table.shape[1],
+            _lib.check(_lib.lib().smore_gather_rows(self.table.data_ptr(), idx.data_ptr(), self.table.shape[0],
+                                                    out.data_ptr(), idx.numel(), self.table.shape[1],
                                                     _stream_ptr(self.table.device)), "smore_gather_rows")
         return out
 

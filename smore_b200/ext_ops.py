@@ -79,7 +79,7 @@ class _BoxBothFunc(torch.autograd.Function):
         d_in = torch.empty_like(d_out)
         L = _lib.lib()
         with torch.cuda.device(entity.device):
-            _lib.check(L.smore_box_forward(entity.data_ptr(), None, center.data_ptr(), offset.data_ptr(),
+            _lib.check(L.smore_box_forward(entity.data_ptr(), None, 0, center.data_ptr(), offset.data_ptr(),
                                            d_out.data_ptr(), d_in.data_ptr(), bsize, num, entity.shape[0],
                                            entity.shape[1], center.shape[0], center.shape[1], center.shape[2],
                                            torch.cuda.current_stream(entity.device).cuda_stream),
@@ -95,7 +95,7 @@ class _BoxBothFunc(torch.autograd.Function):
         bsize, num = g_out.shape
         L = _lib.lib()
         with torch.cuda.device(entity.device):
-            _lib.check(L.smore_box_backward(g_out.data_ptr(), g_in.data_ptr(), entity.data_ptr(), None,
+            _lib.check(L.smore_box_backward(g_out.data_ptr(), g_in.data_ptr(), entity.data_ptr(), None, 0,
                                             center.data_ptr(), offset.data_ptr(), g_entity.data_ptr(), None, None,
                                             None, g_center.data_ptr(), g_offset.data_ptr(), bsize, num,
                                             entity.shape[0], entity.shape[1], center.shape[0], center.shape[1],
@@ -142,14 +142,14 @@ class _RowsDistFunc(torch.autograd.Function):
             if name == "box_both":
                 d0 = torch.empty(bsize, num, dtype=table.dtype, device=table.device)
                 d1 = torch.empty_like(d0)
-                _lib.check(L.smore_box_forward(table.data_ptr(), row_ids.data_ptr(), first.data_ptr(),
-                                               second.data_ptr(), d0.data_ptr(), d1.data_ptr(), *sizes, st),
+                _lib.check(L.smore_box_forward(table.data_ptr(), row_ids.data_ptr(), table.shape[0],
+                                               first.data_ptr(), second.data_ptr(), d0.data_ptr(), d1.data_ptr(), *sizes, st),
                            "smore_box_forward")
                 outs = (d0, d1)
             else:
                 d0 = torch.empty(bsize, num, dtype=table.dtype, device=table.device)
                 _lib.check(L.smore_dist_forward_rows(_lib.DIST_IDS[name], table.data_ptr(), row_ids.data_ptr(),
-                                                     first.data_ptr(), None if second is None else second.data_ptr(),
+                                                     table.shape[0], first.data_ptr(), None if second is None else second.data_ptr(),
                                                      d0.data_ptr(), *sizes, st), "smore_dist_forward_rows")
                 outs = (d0,)
         ctx.name, ctx.rows, ctx.sizes = name, rows, sizes
@@ -183,13 +183,13 @@ class _RowsDistFunc(torch.autograd.Function):
         with torch.cuda.device(table.device), _lib.timed("rows_backward" if ctx.sizes[1] >= 16 else "rows_backward_few"):
             if ctx.name == "box_both":
                 _lib.check(L.smore_box_backward(gouts[0].data_ptr(), gouts[1].data_ptr(), table.data_ptr(),
-                                                row_ids.data_ptr(), first.data_ptr(), second.data_ptr(), None,
+                                                row_ids.data_ptr(), table.shape[0], first.data_ptr(), second.data_ptr(), None,
                                                 slot.data_ptr(), counts_ptr, plan.g_rows.data_ptr(),
                                                 g_first.data_ptr(), g_second.data_ptr(), *ctx.sizes, st),
                            "smore_box_backward")
             else:
                 _lib.check(L.smore_dist_backward_rows(_lib.DIST_IDS[ctx.name], gouts[0].data_ptr(), table.data_ptr(),
-                                                      row_ids.data_ptr(), first.data_ptr(),
+                                                      row_ids.data_ptr(), table.shape[0], first.data_ptr(),
                                                       None if second is None else second.data_ptr(),
                                                       slot.data_ptr(), counts_ptr, plan.g_rows.data_ptr(),
                                                       g_first.data_ptr(),
@@ -217,7 +217,7 @@ class _RowsUnionFunc(torch.autograd.Function):
         d1 = torch.empty_like(d0) if both else None
         with torch.cuda.device(table.device), _lib.timed("rows_forward_union"):
             _lib.check(_lib.lib().smore_union_forward_rows(
-                dist_id, table.data_ptr(), row_ids.data_ptr(), first.data_ptr(),
+                dist_id, table.data_ptr(), row_ids.data_ptr(), table.shape[0], first.data_ptr(),
                 None if second is None else second.data_ptr(), d0.data_ptr(), None if d1 is None else d1.data_ptr(),
                 U, B, num, dim, torch.cuda.current_stream(table.device).cuda_stream), "smore_union_forward_rows")
         ctx.name, ctx.rows, ctx.sizes, ctx.dist_id = name, rows, (U, B, num, dim), dist_id
@@ -247,7 +247,8 @@ class _RowsUnionFunc(torch.autograd.Function):
         with torch.cuda.device(table.device), _lib.timed("rows_backward_union"):
             _lib.check(_lib.lib().smore_union_backward_rows(
                 ctx.dist_id, gouts[0].data_ptr(), gouts[1].data_ptr() if len(gouts) > 1 else None, table.data_ptr(),
-                row_ids.data_ptr(), first.data_ptr(), None if second is None else second.data_ptr(), slot.data_ptr(),
+                row_ids.data_ptr(), table.shape[0], first.data_ptr(), None if second is None else second.data_ptr(),
+                slot.data_ptr(),
                 counts_ptr, plan.g_rows.data_ptr(), g_first.data_ptr(),
                 None if g_second is None else g_second.data_ptr(), *ctx.sizes,
                 torch.cuda.current_stream(table.device).cuda_stream), "smore_union_backward_rows")
@@ -281,6 +282,20 @@ def dot_precision():
     return mode
 
 
+_dot_workspaces = {}     # (device, stream) -> uint8 scratch tensor, grown on demand
+
+
+def _dot_workspace(device, nbytes):
+    """Scratch for the GEMM route, kept per (device, stream): calls on one stream are ordered, so
+    they can share it, and nothing is allocated in the steady state."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    ws = _dot_workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+        _dot_workspaces[key] = ws
+    return ws
+
+
 class _DotSharedFunc(torch.autograd.Function):
     """score[B, K] = query[B, W] . cand[K, W]^T and its two gradients as tensor-core GEMMs."""
 
@@ -291,7 +306,7 @@ class _DotSharedFunc(torch.autograd.Function):
         B = query.shape[0]
         L = _lib.lib()
         dst = torch.empty(B, K, dtype=torch.float32, device=cand.device)
-        ws = torch.empty(L.smore_dot_workspace_bytes(B, K, W, precision), dtype=torch.uint8, device=cand.device)
+        ws = _dot_workspace(cand.device, L.smore_dot_workspace_bytes(B, K, W, precision))
         with torch.cuda.device(cand.device), _lib.timed("dot_forward"):
             _lib.check(L.smore_dot_forward_shared(cand.data_ptr(), query.data_ptr(), dst.data_ptr(), B, K, W, precision,
                                                   ws.data_ptr(), ws.numel(),
@@ -309,7 +324,7 @@ class _DotSharedFunc(torch.autograd.Function):
         B = query.shape[0]
         L = _lib.lib()
         g_cand, g_query = torch.empty_like(cand), torch.empty_like(query)
-        ws = torch.empty(L.smore_dot_workspace_bytes(B, K, W, ctx.precision), dtype=torch.uint8, device=cand.device)
+        ws = _dot_workspace(cand.device, L.smore_dot_workspace_bytes(B, K, W, ctx.precision))
         with torch.cuda.device(cand.device), _lib.timed("dot_backward"):
             _lib.check(L.smore_dot_backward_shared(gout.data_ptr(), cand.data_ptr(), query.data_ptr(), g_cand.data_ptr(),
                                                    g_query.data_ptr(), B, K, W, ctx.precision, ws.data_ptr(), ws.numel(),

@@ -26,18 +26,22 @@ def _stream_ptr(device):
     return torch.cuda.current_stream(device).cuda_stream
 
 
-def _check_operands(name, entity, first, second, others):
+def _check_operands(name, entity, first, second, inputs, outputs):
+    """Inputs may arrive with any strides (autograd hands the backward of a `torch.stack` over
+    union branches, box_dist.py:60-68, a strided grad_out); the kernels write the output buffers
+    in place, so those must be contiguous as given."""
     if not entity.is_cuda:
         raise _lib.SmoreError("%s: operands must be CUDA tensors (there is no CPU path)" % name)
     if entity.dtype not in (torch.float32, torch.float64):
         raise TypeError("%s: float32 or float64 expected, got %s" % (name, entity.dtype))
-    for t in (entity, first, second) + tuple(others):
+    for t in (entity, first, second) + tuple(inputs) + tuple(outputs):
         if t is None:
             continue
         if t.device != entity.device or t.dtype != entity.dtype:
             raise TypeError("%s: all operands must share device and dtype" % name)
-        if not t.is_contiguous():
-            raise ValueError("%s: operands must be contiguous" % name)
+    for t in outputs:
+        if t is not None and not t.is_contiguous():
+            raise ValueError("%s: output buffers must be contiguous" % name)
     if entity.dim() != 3 or first.dim() != 3:
         raise ValueError("%s: entity and query operands must be 3-D" % name)
     if second is not None and second.shape != first.shape:
@@ -64,8 +68,10 @@ def dist_forward(name, entity, first, second, dst):
     extlib_cuda.cpp:172-196 for the reference binding this replaces."""
     if _lib.QUERY_PARTS[name] == 1:
         second = None
-    _check_operands(name, entity, first, second, (dst,))
+    _check_operands(name, entity, first, second, (), (dst,))
     sizes = _sizes(entity, first, dst)
+    entity, first = entity.contiguous(), first.contiguous()
+    second = None if second is None else second.contiguous()
     L = _lib.lib()
     fn = L.smore_dist_forward if entity.dtype == torch.float32 else L.smore_dist_forward_f64
     with torch.cuda.device(entity.device):
@@ -78,10 +84,12 @@ def dist_backward(name, grad_out, entity, first, second, g_entity, g_first, g_se
     """Fills g_entity, g_first (and g_second) completely; see extlib_cuda.cpp:233-262."""
     if _lib.QUERY_PARTS[name] == 1:
         second = g_second = None
-    _check_operands(name, entity, first, second, (grad_out, g_entity, g_first, g_second))
+    _check_operands(name, entity, first, second, (grad_out,), (g_entity, g_first, g_second))
     if g_entity.shape != entity.shape or g_first.shape != first.shape:
         raise ValueError("gradient buffers must have the shapes of their operands")
     sizes = _sizes(entity, first, grad_out)
+    grad_out, entity, first = grad_out.contiguous(), entity.contiguous(), first.contiguous()
+    second = None if second is None else second.contiguous()
     L = _lib.lib()
     fn = L.smore_dist_backward if entity.dtype == torch.float32 else L.smore_dist_backward_f64
     with torch.cuda.device(entity.device):

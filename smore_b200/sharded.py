@@ -551,7 +551,8 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         out = torch.empty(lookup.n, self.shard.width, dtype=torch.float32, device=self.shard.device)
         with torch.cuda.device(self.shard.device):
             _lib.check(_lib.lib().smore_gather_rows(plan.staging.data_ptr(), plan.slot64_of(lookup).data_ptr(),
-                                                    out.data_ptr(), lookup.n, self.shard.width,
+                                                    plan.staging.shape[0], out.data_ptr(), lookup.n,
+                                                    self.shard.width,
                                                     _stream_ptr(self.shard.device)), "smore_gather_rows")
         return out
 

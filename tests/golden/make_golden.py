@@ -181,8 +181,11 @@ def optimizer_cases(out):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("SMORE_REFERENCE_DIR", ""),
+                    help="checkout of the reference (default: $SMORE_REFERENCE_DIR)")
     a = ap.parse_args()
+    if not os.path.isdir(os.path.join(a.reference, "smore")):
+        raise SystemExit("give the reference checkout with --reference or $SMORE_REFERENCE_DIR")
     sys.path.insert(0, a.reference)
     _install_stubs()
     torch.manual_seed(1)

@@ -78,7 +78,7 @@ def test_gather_rows(oracle):
         idx = rng.integers(0, N, n)
         t, i = torch.from_numpy(table).cuda(), torch.from_numpy(idx).cuda()
         out = torch.empty(n, W, device="cuda")
-        _lib.check(L.smore_gather_rows(t.data_ptr(), i.data_ptr(), out.data_ptr(), n, W, _st()), "gather")
+        _lib.check(L.smore_gather_rows(t.data_ptr(), i.data_ptr(), N, out.data_ptr(), n, W, _st()), "gather")
         assert np.array_equal(out.cpu().numpy(), oracle.gather_rows(table, idx))
 
 
@@ -220,7 +220,7 @@ def test_table_resident_rows_equal_gathered_rows(oracle, op, shape):
     d_q1 = None if q1 is None else torch.from_numpy(q1).cuda()
     dst = torch.empty(bsize, num, device="cuda")
     sizes = (bsize, num, be, ne, bc, nc, dim)
-    _lib.check(L.smore_dist_forward_rows(_lib.DIST_IDS[op], t.data_ptr(), i.data_ptr(), d_q0.data_ptr(),
+    _lib.check(L.smore_dist_forward_rows(_lib.DIST_IDS[op], t.data_ptr(), i.data_ptr(), N, d_q0.data_ptr(),
                                          None if q1 is None else d_q1.data_ptr(), dst.data_ptr(), *sizes, _st()), "fwd")
     close(dst.cpu().numpy(), want, RTOL, forward_scale(oracle, op, ent, q0, q1))
 
@@ -231,7 +231,7 @@ def test_table_resident_rows_equal_gathered_rows(oracle, op, shape):
     g_q0 = torch.full_like(d_q0, float("nan"))
     g_q1 = None if q1 is None else torch.full_like(d_q1, float("nan"))
     _lib.check(L.smore_dist_backward_rows(_lib.DIST_IDS[op], torch.from_numpy(gout).cuda().data_ptr(), t.data_ptr(),
-                                          i.data_ptr(), d_q0.data_ptr(), None if q1 is None else d_q1.data_ptr(),
+                                          i.data_ptr(), N, d_q0.data_ptr(), None if q1 is None else d_q1.data_ptr(),
                                           inverse.data_ptr(), counts.data_ptr(), g_rows.data_ptr(), g_q0.data_ptr(),
                                           None if q1 is None else g_q1.data_ptr(), *sizes, _st()), "bwd")
     close(g_rows[:len(w_uniq)].cpu().numpy(), w_rows, RTOL_ATOMIC, what="g_rows")
@@ -282,7 +282,7 @@ def test_union_branches_in_one_pass(oracle, op, shape):
     t, i, d_q0, d_q1 = dev(table), dev(idx), dev(q0), dev(q1)
     dist_id = _lib.BOX_BOTH_ID if op == "box_both" else _lib.DIST_IDS[op]
     dst = [torch.full((B, U, K), float("nan"), device="cuda") for _ in names]
-    _lib.check(L.smore_union_forward_rows(dist_id, t.data_ptr(), i.data_ptr(), ptr(d_q0), ptr(d_q1), dst[0].data_ptr(),
+    _lib.check(L.smore_union_forward_rows(dist_id, t.data_ptr(), i.data_ptr(), N, ptr(d_q0), ptr(d_q1), dst[0].data_ptr(),
                                           dst[1].data_ptr() if len(dst) > 1 else None, U, B, K, dim, _st()), "fwd")
     for k, nm in enumerate(names):
         scale = forward_scale(oracle, nm, ent, np.ascontiguousarray(q0[:, :1]),
@@ -297,7 +297,7 @@ def test_union_branches_in_one_pass(oracle, op, shape):
     g_q1 = None if q1 is None else torch.full_like(d_q1, float("nan"))
     d_g = [dev(g) for g in gouts]
     _lib.check(L.smore_union_backward_rows(dist_id, d_g[0].data_ptr(), d_g[1].data_ptr() if len(d_g) > 1 else None,
-                                           t.data_ptr(), i.data_ptr(), ptr(d_q0), ptr(d_q1), inverse.data_ptr(),
+                                           t.data_ptr(), i.data_ptr(), N, ptr(d_q0), ptr(d_q1), inverse.data_ptr(),
                                            counts.data_ptr(), g_rows.data_ptr(), g_q0.data_ptr(), ptr(g_q1), U, B, K,
                                            dim, _st()), "bwd")
     close(g_rows[:len(w_uniq)].cpu().numpy(), w_rows, RTOL_ATOMIC, what="g_rows")
@@ -305,7 +305,7 @@ def test_union_branches_in_one_pass(oracle, op, shape):
     if q1 is not None:
         close(g_q1.cpu().numpy(), w_q1, 4 * RTOL, what="g_second")
     # other branch counts are the caller's loop
-    assert L.smore_union_forward_rows(dist_id, t.data_ptr(), i.data_ptr(), ptr(d_q0), ptr(d_q1), dst[0].data_ptr(),
+    assert L.smore_union_forward_rows(dist_id, t.data_ptr(), i.data_ptr(), N, ptr(d_q0), ptr(d_q1), dst[0].data_ptr(),
                                       dst[-1].data_ptr(), 3, B, K, dim, _st()) == -2
 
 

@@ -68,6 +68,32 @@ def test_static_scratch_variant_matches_workspace_variant_twice_in_a_row():
         assert torch.equal(got[0][:nu], t_u) and torch.equal(got[1].long(), t_i)
 
 
+def test_static_scratch_variant_leaves_device_memory_in_use_unchanged():
+    """"Allocates nothing", measured: the driver's count of free device memory is the same before and
+    after a series of calls (the first call on the device, which may load the library's code and
+    looks up the scratch array's address, is made beforehand)."""
+    from smore_b200 import _lib
+    L = _lib.lib()
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda").manual_seed(12)
+    idx = torch.randint(0, 5000011, (200000,), device="cuda", generator=g)
+    outs = _buffers(idx.numel())
+    st = torch.cuda.current_stream().cuda_stream
+
+    def call(n_rows):
+        _lib.check(L.smore_unique_rows_static(idx.data_ptr(), idx.numel(), n_rows, outs[0].data_ptr(),
+                                              outs[1].data_ptr(), outs[2].data_ptr(), outs[3].data_ptr(), st),
+                   "smore_unique_rows_static")
+
+    call(5000011)
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    for n_rows in (5000011, 1 << 24, 6000000):
+        call(n_rows)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+
+
 def test_static_scratch_variant_rejects_tables_beyond_its_limit():
     from smore_b200 import _lib
     L = _lib.lib()
