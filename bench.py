@@ -15,9 +15,19 @@ rotation) with the entity table sized at 1/8 of 86,054,151 rows per GPU, so that
 is the same at every N ("weak" scaling; at N=8 the table is the full 86M rows).  Inputs are
 synthetic with the shapes and value distributions of that configuration; no dataset is read.
 
-Prints one JSON line (see README/DESIGN for the keys).  `--impl reference` instead times the
-reference's own CPU path (its torch-native scoring and torch index-op optimizer, restated in
-oracle/native_torch.py) on the host cores, on a bounded sample of the same workload.
+Prints one JSON line.  Its contract keys: metric, value (whole-job queries/s with the index tensors
+resident on the device: the median of `--repeats` timed regions of exactly `--steps` steps), unit,
+n_gpus, steps, warmup, ms_per_step, higher_is_better, scaling, vs_baseline, dtype, data, config,
+e2e (the same metric with every step's index tensors copied from pinned host memory and the loss
+read back), gpu_launches (this library's kernels per timed region), clocks, roofline (the kernel
+with the largest share: algorithmic bytes / CUDA-event time against the measured copy bandwidth),
+kernels (every library call of an eager pass over the same steps), cpu_baseline.  At one GPU the
+other configurations (RotatE, shared-negative Query2box, GQE, DistMult on the tensor cores in both
+precisions) run afterwards in the same process and are reported under `workloads`; at several GPUs
+a parity check of the prefetching graph mode against the plain mode runs first (`parity_check`).
+`--impl reference` instead times the reference's own CPU implementation of the path (its Python,
+imported by oracle/ref_harness.py, else the torch restatement in oracle/native_torch.py) on the host
+cores, on a bounded sample of the same workload.
 """
 import argparse
 import json
@@ -398,14 +408,65 @@ class ClockSampler(threading.Thread):
 
 
 # ------------------------------------------------------------------------------------------------
-# CPU baseline: the reference's torch-native path on host cores, bounded sample
+# The reference arm: the reference's own CPU implementation of the path on the host cores
 # ------------------------------------------------------------------------------------------------
 
 def cpu_reference_steps(cfg, steps, warmup, sample_queries=64, table_rows=1000000):
-    """Times fwd + bwd + touched-row merge + row-wise Adam of `sample_queries` queries (full K and
-    dim) against a host table of `table_rows` rows.  Returns (queries/s, ms/step, threads, text)."""
-    from oracle import native_torch as nt
+    """Times whole training steps of `sample_queries` queries (full K and dim, the workload's query
+    structures in rotation) on the host cores.  Returns a dict with value (queries/s), ms_per_step,
+    cores, kind and a description of the sample.
+
+    kind "reference": the reference's own Python - its model class with native_cal_logit, its
+    train_step_mp and its AdamEmbedOptimizer - imported from a reference checkout or from the copy
+    the oracle build places beside its compiled sources (oracle/ref_harness.py), for the geometries
+    whose model that harness builds.  kind "port": the torch restatement of the same expressions
+    (oracle/native_torch.py) where the reference package is not available or for DistMult / ComplEx
+    (whose torch-native scoring needs a [B, 1, K, dim] temporary per step: 134 GB at this size)."""
     torch.set_num_threads(os.cpu_count() or 1)
+    from oracle import ref_harness as rh
+    geo = cfg["geo"]
+    if rh.locate() is not None and geo in ("box", "rotate", "vec"):
+        return _cpu_reference_python(rh, cfg, steps, warmup, sample_queries, table_rows)
+    return _cpu_reference_port(cfg, steps, warmup, sample_queries, table_rows)
+
+
+def _cpu_reference_python(rh, cfg, steps, warmup, sample_queries, table_rows):
+    rh.install()
+    rh.ensure_group()
+    from smore.training.train_process import train_step_mp
+    geo, D, K = cfg["geo"], cfg["dim"], cfg["K"]
+    n_rows = min(table_rows, cfg["rows"] or table_rows)
+    Bs = min(sample_queries, cfg["B"])
+    small = dict(cfg, B=Bs)
+    rargs = rh.train_args(adv=cfg["adv"], optim_mode="(aggr,adam,gpu,%s,0)" % bool(cfg["squeeze"]))
+    model = rh.build_model(geo, n_rows, cfg["relations"], D, cfg["gamma"], Bs, "native", cen=cfg.get("cen", 0.02))
+    opts = rh.reference_embedding_optimizers(model, rargs, -1)
+    dense = rh.dense_optimizer(model, cfg["lr"])
+    structures = cfg["structures"]
+    batches = []
+    for i in range(warmup + steps):
+        s = structures[i % len(structures)]
+        pos, neg, q = make_batch(small, n_rows, s, seed=77 + i)
+        batches.append((s, pos, neg, q))
+    it = rh.batch_iterator(batches)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        train_step_mp(model, [dense], opts, it, rargs, i, cfg["lr"], "cpu", 1)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    ms = 1e3 * sum(times) / len(times)
+    sample = ("the reference's train_step_mp (native_cal_logit, its AdamEmbedOptimizer, dense Adam) on %d of %d "
+              "queries per step, K=%d, dim=%d, structures %s, host table %d rows, %d timed steps"
+              % (Bs, cfg["B"], K, D, "/".join(structures), n_rows, len(times)))
+    return {"value": Bs / (ms / 1e3), "ms_per_step": ms, "cores": torch.get_num_threads(), "kind": "reference",
+            "sample": sample}
+
+
+def _cpu_reference_port(cfg, steps, warmup, sample_queries, table_rows):
+    """fwd + bwd + touched-row merge + row-wise Adam through the torch restatement, random query operands."""
+    from oracle import native_torch as nt
     geo, D, K = cfg["geo"], cfg["dim"], cfg["K"]
     width = D * (2 if geo in ("rotate", "complex") else 1)
     n_rows = min(table_rows, cfg["rows"] or table_rows)
@@ -431,11 +492,15 @@ def cpu_reference_steps(cfg, steps, warmup, sample_queries=64, table_rows=100000
             q = (qparts[0], qparts[1])
             pl, nl = nt.rotate_logit(ent_pos, q, cfg["gamma"]), nt.rotate_logit(ent_neg, q, cfg["gamma"])
         elif geo == "complex":
+            # shared candidates: the reference's torch.mm branch (complex.py:176-186)
             q = (qparts[0], qparts[1])
-            pl, nl = nt.complex_logit(ent_pos, q), nt.complex_logit(ent_neg, q)
+            pl = nt.complex_logit(ent_pos, q)
+            e_re, e_im = torch.chunk(ent_neg[0], 2, dim=-1)
+            nl = torch.mm(q[0].view(Bs, D), e_re.t()) + torch.mm(q[1].view(Bs, D), e_im.t())
         elif geo == "distmult":
             q = (qparts[0],)
-            pl, nl = nt.distmult_logit(ent_pos, q), nt.distmult_logit(ent_neg, q)
+            pl = nt.distmult_logit(ent_pos, q)
+            nl = torch.mm(q[0].view(Bs, D), ent_neg[0].t())
         else:
             q = (qparts[0],)
             pl, nl = nt.vec_logit(ent_pos, q, cfg["gamma"]), nt.vec_logit(ent_neg, q, cfg["gamma"])
@@ -447,21 +512,27 @@ def cpu_reference_steps(cfg, steps, warmup, sample_queries=64, table_rows=100000
         if it >= warmup:
             times.append(dt)
     ms = 1e3 * sum(times) / len(times)
-    sample = "%d of %d queries per step, K=%d, dim=%d, host table %d rows, %d timed steps" % (
-        Bs, cfg["B"], K, D, n_rows, len(times))
-    return Bs / (ms / 1e3), ms, torch.get_num_threads(), sample
+    sample = ("torch restatement of the reference's native path (scoring, loss, merge, Adam rows; random query "
+              "operands) on %d of %d queries per step, K=%d, dim=%d, host table %d rows, %d timed steps"
+              % (Bs, cfg["B"], K, D, n_rows, len(times)))
+    return {"value": Bs / (ms / 1e3), "ms_per_step": ms, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": sample}
 
 
 # ------------------------------------------------------------------------------------------------
 # the GPU arm
 # ------------------------------------------------------------------------------------------------
 
-# DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the
-# 2M-row capture of the Query2box workload (profiles/q2b_box_step_2M_rows_ncu.md), scaled to a
-# full-size launch by the units processed: the two distance kernels process B*K rows per launch at
-# every table size; the update kernel moves 8070 bytes per distinct row.  Other workloads: None.
+# DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on a
+# 2M-row capture of the Query2box workload, scaled to a full-size launch by the units processed:
+# the two distance kernels process B*K rows per launch at every table size; the update kernel moves
+# 8070 bytes per distinct row.  Other workloads: None.
 NCU_TRAFFIC_BYTES = {"rows_forward": 1.722e9, "rows_backward": 4.094e9}
 NCU_UPDATE_BYTES_PER_ROW = 8070.0
+
+# fp32 ALU instructions per (pair, dim) term evaluation in the inner loop of the shared-candidate
+# kernels, counted in their source (csrc/dist_terms.cuh): box both = |e-c|, -o, max, +acc, min, |.|+acc
+ALU_OPS_PER_TERM = {"box": {"fwd": 6, "bwd": 14}, "vec": {"fwd": 2, "bwd": 5}}
 
 
 def ncu_traffic(workload, kernel, n_unique_mean):
@@ -487,8 +558,7 @@ def algorithmic_bytes(cfg, n_unique_mean):
     # peer read); the fetch copies every distinct row once (read + write)
     out = {"sparse_update_rows": upd, "shard_reduce_update": upd, "fetch_rows": n_unique_mean * 8 * W}
     if not cfg["shared"]:
-        # with shared candidates the distance kernels are bound by fp32 ALU throughput, not by HBM:
-        # no bandwidth fraction is quoted for them
+        # with shared candidates the distance kernels are bound by fp32 ALU throughput, not by HBM
         out.update({"rows_forward": fwd, "rows_backward": bwd})
     return out
 
@@ -508,300 +578,355 @@ def load_peaks():
         return 6650.0, "fallback"
 
 
-def run_gpu(args):
-    import torch.distributed as dist
-    from smore_b200 import _lib, embedding, ext_ops
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise RuntimeError("bench.py needs a CUDA device (there is no CPU path for the product arm)")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    cfg = dict(WORKLOADS[args.workload])
-    rows_per_gpu = cfg["rows"] or (FREEBASE_ENTITIES + 7) // 8
-    if args.rows:
-        rows_per_gpu = args.rows
-    if args.structures:
-        cfg["structures"] = args.structures.split(",")
-    n_rows = rows_per_gpu * world     # weak scaling: the table grows with the number of GPUs
-
-    torch.manual_seed(1234)           # dense parameters start identical on every rank
-    reduce_dense = None
-    if world > 1:
-        # table + Adam state row-sharded over the ranks; rows and row gradients move over NVLink
-        from smore_b200 import sharded
-        B, K = cfg["B"], cfg["K"]
-        width = cfg["dim"] * (2 if cfg["geo"] in ("rotate", "complex") else 1)
-        caps = ((K if cfg["shared"] else B * K) + 2 * B, B, B)
-        shard = sharded.ShardGroup.from_process_group(n_rows, width, caps, squeeze=cfg["squeeze"], device=device)
-        r = (cfg["gamma"] + 2.0) / cfg["dim"]
-        shard.init_uniform(-r, r, seed=1234)
-        model = QueryModel(cfg, n_rows, device, ext_ops, embedding, lazy=True, shard=shard, world=world,
-                           capturable=not args.no_graphs, fused_paths=not args.no_fused_paths)
-
-        def reduce_dense(grads):
-            # one all-reduce over all dense gradients instead of one per parameter
-            flat = torch.cat([g.reshape(-1) for g in grads])
-            dist.all_reduce(flat)
-            torch._foreach_copy_(grads, [f.view_as(g) for f, g in zip(flat.split([g.numel() for g in grads]), grads)])
-    else:
-        model = QueryModel(cfg, n_rows, device, ext_ops, embedding, lazy=not args.no_lazy,
-                           capturable=not args.no_graphs, fused_paths=not args.no_fused_paths)
-    prefetching = world > 1 and not args.no_prefetch
-    use_graphs = world == 1 and not args.no_graphs
-    chained_graphs = world > 1 and prefetching and not args.no_graphs
-    if use_graphs or chained_graphs:
-        model.embed_opt.use_device_step()      # the Adam step counter must advance inside replayed graphs
-    model.train()
-    structures = cfg["structures"]
-    pool = max(len(structures), args.pool)
-    host_batches = []
-    for i in range(pool):
-        s = structures[i % len(structures)]
-        pos, neg, q = make_batch(cfg, n_rows, s, seed=1000 * rank + i)
-        host_batches.append((s, pos.pin_memory(), neg.pin_memory(), q.pin_memory()))
-    dev_batches = [(s, p.to(device), n.to(device), q.to(device)) for s, p, n, q in host_batches]
-    h2d_bytes = sum(p.numel() + n.numel() + q.numel() for _, p, n, q in host_batches) * 8 / pool
-
-    def sync_all():
+def measure_fma_rate(device):
+    """fp32 fused multiply-adds per second of this GPU, measured with the library's probe kernel
+    (every thread runs eight independent chains of dependent FMAs; grid of 8 blocks per SM), best of
+    three launches timed with CUDA events."""
+    import ctypes
+    from smore_b200 import _lib
+    L = _lib.lib()
+    out = torch.zeros(1, device=device)
+    count = ctypes.c_double(0.0)
+    st = torch.cuda.current_stream(device).cuda_stream
+    best = None
+    for _ in range(4):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        _lib.check(L.smore_alu_probe(out.data_ptr(), 20000, ctypes.byref(count), st), "smore_alu_probe")
+        b.record()
         torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        best = ms if best is None else min(best, ms)
+    return count.value / (best * 1e-3)
+
+
+class StepRunner(object):
+    """One workload on this rank's GPU: model, optimizer, pre-generated batches, and the ways of
+    running steps (eager, replayed CUDA graphs, with host batches)."""
+
+    def __init__(self, cfg, rows_per_gpu, device, world=1, rank=0, graphs=True, prefetch=True, lazy=True,
+                 fused_paths=True, pool=18, resettable=False):
+        from smore_b200 import _lib, embedding, ext_ops
+        import torch.distributed as dist
+        self.cfg, self.device, self.world, self.rank = cfg, device, world, rank
+        self.rows_per_gpu = rows_per_gpu
+        self.n_rows = n_rows = rows_per_gpu * world     # weak scaling: the table grows with the number of GPUs
+        self.L = _lib.lib()
+        torch.manual_seed(1234)           # dense parameters start identical on every rank
+        self.reduce_dense = None
+        self.shard = None
+        self.prefetching = world > 1 and prefetch
+        self.use_graphs = world == 1 and graphs
+        self.chained_graphs = world > 1 and self.prefetching and graphs
+        capturable = self.use_graphs or self.chained_graphs
         if world > 1:
+            # table + Adam state row-sharded over the ranks; rows and row gradients move over NVLink
+            from smore_b200 import sharded
+            B, K = cfg["B"], cfg["K"]
+            width = cfg["dim"] * (2 if cfg["geo"] in ("rotate", "complex") else 1)
+            caps = ((K if cfg["shared"] else B * K) + 2 * B, B, B)
+            self.shard = sharded.ShardGroup.from_process_group(n_rows, width, caps, squeeze=cfg["squeeze"], device=device)
+            self._init_range = (cfg["gamma"] + 2.0) / cfg["dim"]
+            self.shard.init_uniform(-self._init_range, self._init_range, seed=1234)
+            self.model = QueryModel(cfg, n_rows, device, ext_ops, embedding, lazy=True, shard=self.shard, world=world,
+                                    capturable=capturable, fused_paths=fused_paths)
+
+            def reduce_dense(grads):
+                # one all-reduce over all dense gradients instead of one per parameter
+                flat = torch.cat([g.reshape(-1) for g in grads])
+                dist.all_reduce(flat)
+                torch._foreach_copy_(grads, [f.view_as(g) for f, g in zip(flat.split([g.numel() for g in grads]), grads)])
+            self.reduce_dense = reduce_dense
+        else:
+            self.model = QueryModel(cfg, n_rows, device, ext_ops, embedding, lazy=lazy, capturable=capturable,
+                                    fused_paths=fused_paths)
+        model = self.model
+        # (a copy of the initial state, table included at one GPU: only for runs that start over)
+        self._initial = {k: v.detach().clone() for k, v in model.state_dict().items()} if resettable else None
+        if capturable:
+            model.embed_opt.use_device_step()      # the Adam step counter must advance inside replayed graphs
+        model.train()
+        self.structures = structures = cfg["structures"]
+        self.pool = pool = max(len(structures), pool)
+        self.host_batches = []
+        for i in range(pool):
+            s = structures[i % len(structures)]
+            pos, neg, q = make_batch(cfg, n_rows, s, seed=1000 * rank + i)
+            self.host_batches.append((s, pos.pin_memory(), neg.pin_memory(), q.pin_memory()))
+        self.dev_batches = [(s, p.to(device), n.to(device), q.to(device)) for s, p, n, q in self.host_batches]
+        self.h2d_bytes = sum(p.numel() + n.numel() + q.numel() for _, p, n, q in self.host_batches) * 8 / pool
+        # untimed set-up: one eager step of every query structure (allocator blocks, optimizer state)
+        for i in range(len(structures)):
+            self.eager_step(*self.dev_batches[i])
+        self.sync_all()
+        self.graphs, self.launches_per_step = {}, {}
+        self.static, self.chain = [], {}
+        if self.use_graphs:
+            self._capture_single()
+        if self.chained_graphs:
+            self._capture_chained()
+        self.copy_stream = torch.cuda.Stream(device)
+        from smore_b200.feed import BatchFeeder
+        self.feeder = BatchFeeder(device, depth=2)
+
+    # ---- plumbing -----------------------------------------------------------------------------------
+    def sync_all(self):
+        torch.cuda.synchronize()
+        if self.world > 1:
+            import torch.distributed as dist
             dist.barrier()
             torch.cuda.synchronize()
 
-    L = _lib.lib()
+    def eager_step(self, s, p, n, q, upcoming=None):
+        return train_step(self.model, p, n, q, s, self.reduce_dense, upcoming if self.prefetching else None)
 
-    def eager_step(s, p, n, q, upcoming=None):
-        return train_step(model, p, n, q, s, reduce_dense, upcoming if prefetching else None)
-
-    # untimed set-up: one eager step of every query structure (allocator blocks, optimizer state)
-    for i in range(len(structures)):
-        eager_step(*dev_batches[i])
-    sync_all()
-
-    # One CUDA graph per query structure: the whole step (lookups, query embedding, scoring, loss,
-    # backward, de-duplication, row-wise Adam, dense Adam) is captured once and replayed on new index
-    # tensors copied into its static input buffers.  Python and launch latency leave the step.
-    graphs, launches_per_step = {}, {}
-    if use_graphs:
-        for s in structures:
-            ex = next(b for b in dev_batches if b[0] == s)
+    def _capture_single(self):
+        """One CUDA graph per query structure: the whole step (lookups, query embedding, scoring, loss,
+        backward, de-duplication, row-wise Adam, dense Adam) is captured once and replayed on new index
+        tensors copied into its static input buffers.  Python and launch latency leave the step."""
+        L = self.L
+        for s in self.structures:
+            ex = next(b for b in self.dev_batches if b[0] == s)
             static = [t.clone() for t in ex[1:]]
             before = L.smore_kernel_launch_count()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
-                loss = train_step(model, static[0], static[1], static[2], s)
-            launches_per_step[s] = L.smore_kernel_launch_count() - before
-            graphs[s] = (g, static, loss)
-        sync_all()
+                loss = train_step(self.model, static[0], static[1], static[2], s)
+            self.launches_per_step[s] = L.smore_kernel_launch_count() - before
+            self.graphs[s] = (g, static, loss)
+        self.sync_all()
 
-    # Several GPUs: the same, except that a step's graph also holds the side-stream branch that pulls
-    # the NEXT step's rows (forked at the start of the step, joined at its end), and that steps
-    # alternate between two arenas of peer-visible id lists / gradient rows.  So there is one graph
-    # per (structure, arena); the index tensors of step i live in static buffer i % 2 and those of
-    # step i + 1 are copied into the other buffer before the graph of step i is launched.
-    static, chain = [], {}
-    if chained_graphs:
-        max_cols = max(b[3].shape[1] for b in host_batches)
+    def _load_static(self, par, batch):
+        pos, neg, q = self.static[par]
+        pos.copy_(batch[1], non_blocking=True)
+        neg.copy_(batch[2], non_blocking=True)
+        q[:, :batch[3].shape[1]].copy_(batch[3], non_blocking=True)
+
+    def start_chain(self, i, first_batch):
+        """Make step i replayable: its index tensors in static buffer i % 2, their rows pulled by the
+        prefetch branch of one eager step (on batch i - 1) on the other arena."""
+        par = i % 2
+        self._load_static(par, first_batch)
+        self.model.embed_opt.reset_prefetch(next_parity=par ^ 1)
+        prev = self.dev_batches[(i - 1) % self.pool]
+        train_step(self.model, prev[1], prev[2], prev[3], prev[0], self.reduce_dense, self.static[par] + (None,))
+
+    def _capture_chained(self):
+        """Several GPUs: a step's graph also holds the side-stream branch that pulls the NEXT step's rows
+        (forked at the start of the step, joined at its end), and steps alternate between two arenas of
+        peer-visible id lists / gradient rows.  So there is one graph per (structure, arena); the index
+        tensors of step i live in static buffer i % 2 and those of step i + 1 are copied into the other
+        buffer before the graph of step i is launched."""
+        L, device = self.L, self.device
+        max_cols = max(b[3].shape[1] for b in self.host_batches)
         for par in range(2):
-            _, p0, n0, q0 = dev_batches[0]
-            static.append((torch.zeros_like(p0), torch.zeros_like(n0),
-                           torch.zeros(q0.shape[0], max_cols, dtype=q0.dtype, device=device)))
-
-        def load_static(par, batch):
-            pos, neg, q = static[par]
-            pos.copy_(batch[1], non_blocking=True)
-            neg.copy_(batch[2], non_blocking=True)
-            q[:, :batch[3].shape[1]].copy_(batch[3], non_blocking=True)
-
-        def start_chain(i, first_batch):
-            """Make step i replayable: its index tensors in static buffer i % 2, their rows pulled by
-            the prefetch branch of one eager step on the other arena."""
-            par = i % 2
-            load_static(par, first_batch)
-            model.embed_opt.reset_prefetch(next_parity=par ^ 1)
-            prev = dev_batches[(i - 1) % pool]
-            train_step(model, prev[1], prev[2], prev[3], prev[0], reduce_dense, static[par] + (None,))
-
-        n_cols = {b[0]: b[3].shape[1] for b in host_batches}
-        start_chain(0, dev_batches[0])
+            _, p0, n0, q0 = self.dev_batches[0]
+            self.static.append((torch.zeros_like(p0), torch.zeros_like(n0),
+                                torch.zeros(q0.shape[0], max_cols, dtype=q0.dtype, device=device)))
+        n_cols = {b[0]: b[3].shape[1] for b in self.host_batches}
+        self.start_chain(0, self.dev_batches[0])
         pool_handle = torch.cuda.graph_pool_handle()
-        for s in structures:
+        for s in self.structures:
             for par in range(2):            # captures alternate between the arenas like the steps do
-                pos, neg, q = static[par]
+                pos, neg, q = self.static[par]
                 before = L.smore_kernel_launch_count()
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g, pool=pool_handle):
-                    loss = train_step(model, pos, neg, q[:, :n_cols[s]], s, reduce_dense, static[par ^ 1] + (None,))
-                launches_per_step[s] = L.smore_kernel_launch_count() - before
-                graphs[(s, par)] = (g, loss)
-        sync_all()
-        chain["next"] = 0                   # static buffer 0 holds batch 0 and its rows are staged
+                    loss = train_step(self.model, pos, neg, q[:, :n_cols[s]], s, self.reduce_dense,
+                                      self.static[par ^ 1] + (None,))
+                self.launches_per_step[s] = L.smore_kernel_launch_count() - before
+                self.graphs[(s, par)] = (g, loss)
+        self.sync_all()
+        self.chain["next"] = 0                   # static buffer 0 holds batch 0 and its rows are staged
 
-    def step(s, p, n, q, upcoming=None):
-        if not use_graphs:
-            return eager_step(s, p, n, q, upcoming)
-        g, static_in, loss = graphs[s]
+    def step(self, s, p, n, q, upcoming=None):
+        if not self.use_graphs:
+            return self.eager_step(s, p, n, q, upcoming)
+        g, static_in, loss = self.graphs[s]
         static_in[0].copy_(p, non_blocking=True)
         static_in[1].copy_(n, non_blocking=True)
         static_in[2].copy_(q, non_blocking=True)
         g.replay()
         return loss
 
-    def replay_chained(i, this_structure, next_batch):
+    def _replay_chained(self, i, this_structure, next_batch):
         par = i % 2
-        load_static(par ^ 1, next_batch)
-        g, loss = graphs[(this_structure, par)]
+        self._load_static(par ^ 1, next_batch)
+        g, loss = self.graphs[(this_structure, par)]
         g.replay()
-        chain["next"] = i + 1
+        self.chain["next"] = i + 1
         return loss
 
-    def run_resident(k0, k):
-        if chained_graphs:
-            if chain.get("next") != k0:
-                start_chain(k0, dev_batches[k0 % pool])
+    # ---- ways of running steps ------------------------------------------------------------------------
+    def run_resident(self, k0, k):
+        """Steps k0 .. k0+k-1 on the device-resident batches (batch i % pool)."""
+        pool, dev_batches = self.pool, self.dev_batches
+        if self.chained_graphs:
+            if self.chain.get("next") != k0:
+                self.start_chain(k0, dev_batches[k0 % pool])
             for i in range(k0, k0 + k):
-                replay_chained(i, dev_batches[i % pool][0], dev_batches[(i + 1) % pool])
+                self._replay_chained(i, dev_batches[i % pool][0], dev_batches[(i + 1) % pool])
             return
         for i in range(k0, k0 + k):
-            step(*dev_batches[i % pool], upcoming=dev_batches[(i + 1) % pool][1:] + (None,))
+            self.step(*dev_batches[i % pool], upcoming=dev_batches[(i + 1) % pool][1:] + (None,))
 
-    copy_stream = torch.cuda.Stream(device)
-    from smore_b200.feed import BatchFeeder
-    feeder = BatchFeeder(device, depth=2)
+    def launches_in(self, k0, k, counted_eagerly):
+        if self.use_graphs or self.chained_graphs:
+            return sum(self.launches_per_step[self.dev_batches[i % self.pool][0]] for i in range(k0, k0 + k))
+        return counted_eagerly
 
-    def upload(i):
-        """Start the host -> device copy of batch i's index tensors (pinned memory) on the copy
-        stream; the previous step's compute overlaps it, as the sampler's prefetch thread would."""
-        s, p, n, q = host_batches[i % pool]
-        with torch.cuda.stream(copy_stream):
-            dev = [t.to(device, non_blocking=True) for t in (p, n, q)]
+    def _upload(self, i):
+        """Start the host -> device copy of batch i's index tensors (pinned memory) on the copy stream;
+        the previous step's compute overlaps it, as the sampler's prefetch thread would."""
+        s, p, n, q = self.host_batches[i % self.pool]
+        with torch.cuda.stream(self.copy_stream):
+            dev = [t.to(self.device, non_blocking=True) for t in (p, n, q)]
             done = torch.cuda.Event()
-            done.record(copy_stream)
+            done.record(self.copy_stream)
         return s, dev, done
 
-    def prepare_e2e(k0):
+    def prepare_e2e(self, k0):
         """Untimed: with chained graphs, stage step k0 (its indices come from the host like all others)."""
-        if chained_graphs:
-            s, dev, done = upload(k0)
-            torch.cuda.current_stream(device).wait_event(done)
-            start_chain(k0, (s,) + tuple(dev))
+        if self.chained_graphs:
+            s, dev, done = self._upload(k0)
+            torch.cuda.current_stream(self.device).wait_event(done)
+            self.start_chain(k0, (s,) + tuple(dev))
 
-    def run_e2e(k0, k):
+    def run_e2e(self, k0, k):
+        """The same steps fed from pinned host memory, the loss read back by the host every step."""
         last = 0.0
-        main = torch.cuda.current_stream(device)
-        if chained_graphs:
+        pool, host_batches = self.pool, self.host_batches
+        main = torch.cuda.current_stream(self.device)
+        if self.chained_graphs:
             # the indices of step i + 1 are uploaded while step i - 1 runs and copied into the free
             # static buffer just before step i is launched
-            ahead = [upload(k0 + 1), upload(k0 + 2)]
+            ahead = [self._upload(k0 + 1), self._upload(k0 + 2)]
             for i in range(k0, k0 + k):
                 s_next, dev, done = ahead.pop(0)
-                ahead.append(upload(i + 3))
+                ahead.append(self._upload(i + 3))
                 main.wait_event(done)
                 for t in dev:
                     t.record_stream(main)
-                last = replay_chained(i, host_batches[i % pool][0], (s_next,) + tuple(dev)).item()
+                last = self._replay_chained(i, host_batches[i % pool][0], (s_next,) + tuple(dev)).item()
             return last
-        # host batches go through the library's BatchFeeder (pinned staging, copy stream): batch i + 1
-        # is on its way when step i is launched, batch i + 2 is staged while step i runs on the GPU -
-        # the role of the sampler's prefetch thread
+        # host batches go through the library's BatchFeeder (pinned staging, copy stream): batch i + 1 is
+        # on its way when step i is launched, batch i + 2 is staged while step i runs on the GPU - the
+        # role of the sampler's prefetch thread
+        feeder = self.feeder
         for j in range(k0, min(k0 + 2, k0 + k)):
             feeder.submit(host_batches[j % pool][0], *host_batches[j % pool][1:])
         for i in range(k0, k0 + k):
             batch = feeder.get()
             upcoming = None
-            if prefetching and len(feeder):
+            if self.prefetching and len(feeder):
                 nxt = feeder.peek()
                 upcoming = tuple(nxt.tensors) + (nxt.event,)
-            loss = step(batch.tag, *batch.tensors, upcoming=upcoming)
+            loss = self.step(batch.tag, *batch.tensors, upcoming=upcoming)
             if i + 2 < k0 + k:
                 feeder.submit(host_batches[(i + 2) % pool][0], *host_batches[(i + 2) % pool][1:])
             last = loss.item()        # the step's loss is read back by the host every step
         return last
 
-    # keep Python's cycle collector from scanning the long-lived model objects inside a timed region
-    # (a full collection costs ~100 ms here, more than a dozen steps)
-    import gc
-    gc.collect()
-    gc.freeze()
-    # ---- resident-input timing ("value") -----------------------------------------------------------
-    run_resident(0, args.warmup)
-    sync_all()
-    clocks = ClockSampler(local_rank)
-    clocks.start()
-    launches0 = L.smore_kernel_launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sync_all()
-    e0.record()
-    t_issue = time.perf_counter()
-    run_resident(args.warmup, args.steps)
-    t_issue = time.perf_counter() - t_issue     # host time to enqueue the steps (no synchronisation inside)
-    e1.record()
-    sync_all()
-    if use_graphs or chained_graphs:
-        launches = sum(launches_per_step[dev_batches[i % pool][0]] for i in range(args.warmup, args.warmup + args.steps))
-    else:
-        launches = L.smore_kernel_launch_count() - launches0
-    ms_total = e0.elapsed_time(e1)
-    # ---- end-to-end timing: pinned host index tensors in, loss out, every step ----------------------
-    prepare_e2e(0)
-    run_e2e(0, min(3, args.warmup))
-    sync_all()
-    prepare_e2e(args.warmup)
-    sync_all()
-    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record()
-    last_loss = run_e2e(args.warmup, args.steps)
-    e3.record()
-    sync_all()
-    ms_e2e = e2.elapsed_time(e3)
-    if _lib.async_status() != 0:
-        raise RuntimeError("a bulk-copy wait gave up inside a kernel: the timed results are invalid")
-    # ---- the same K steps once more, eagerly, with CUDA events around each library call -------------
-    # (kernels inside a replayed graph cannot be bracketed by events; the kernels are the same)
-    if chained_graphs:
-        model.embed_opt.reset_prefetch()
-    if use_graphs or chained_graphs:
-        # graph capture emptied the allocator's cache: give eager mode its blocks back first
-        for i in range(len(structures)):
-            eager_step(*dev_batches[i])
-        sync_all()
-    timer = _lib.KernelTimer()
-    _lib.set_timer(timer)
-    e4, e5 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e4.record()
-    for i in range(args.warmup, args.warmup + args.steps):
-        eager_step(*dev_batches[i % pool], upcoming=dev_batches[(i + 1) % pool][1:] + (None,))
-    e5.record()
-    sync_all()
-    _lib.set_timer(None)
-    clock_summary = clocks.summary()
-    ms_eager = e4.elapsed_time(e5)
-    kernel_ms = timer.elapsed_ms()
-    if world > 1:
-        t = torch.tensor([ms_total, ms_e2e], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total, ms_e2e = t.tolist()
-    def shutdown():
+    def eager_timed_pass(self, k0, k):
+        """The same k steps once more, eagerly, with CUDA events around each library call (kernels inside
+        a replayed graph cannot be bracketed by events; the kernels are the same).  Returns (ms for the
+        k steps, {kernel: [ms]}, notes)."""
+        from smore_b200 import _lib
+        if self.chained_graphs:
+            self.model.embed_opt.reset_prefetch()
+        if self.use_graphs or self.chained_graphs:
+            # graph capture emptied the allocator's cache: give eager mode its blocks back first
+            for i in range(len(self.structures)):
+                self.eager_step(*self.dev_batches[i])
+            self.sync_all()
+        timer = _lib.KernelTimer()
+        _lib.set_timer(timer)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(k0, k0 + k):
+            self.eager_step(*self.dev_batches[i % self.pool], upcoming=self.dev_batches[(i + 1) % self.pool][1:] + (None,))
+        b.record()
+        self.sync_all()
+        _lib.set_timer(None)
+        self.chain["next"] = None
+        return a.elapsed_time(b), timer.elapsed_ms(), timer.notes
+
+    # ---- state (parity checks) ---------------------------------------------------------------------------
+    def reset_state(self):
+        """Back to the state right after construction: table, optimizer state, dense parameters, step
+        counters; nothing prepared for coming steps."""
+        model = self.model
+        if self._initial is None:
+            raise RuntimeError("StepRunner(resettable=True) is needed to start over")
+        with torch.no_grad():
+            model.load_state_dict(self._initial)
+            if self.shard is not None:
+                self.shard.init_uniform(-self._init_range, self._init_range, seed=1234)
+                self.shard.m.zero_()
+                self.shard.v.zero_()
+                self.shard.dirty.zero_()
+            else:
+                for name in model.embed_opt.state_names:
+                    model.embed_opt.state(name).zero_()
+            for st in model.dense_opt.state.values():
+                for t in st.values():
+                    if torch.is_tensor(t):
+                        t.zero_()
+        opt = model.embed_opt
+        opt.step = 0
+        if getattr(opt, "_step_dev", None) is not None:
+            opt._step_dev.zero_()
+        if hasattr(opt, "reset_prefetch"):
+            opt.reset_prefetch()
+        self.chain["next"] = None
+        self.sync_all()
+
+    def state_tensors(self):
+        model = self.model
+        out = {}
+        if self.shard is not None:
+            n = self.shard.local_rows
+            out.update(table=self.shard.table[:n], m=self.shard.m[:n], v=self.shard.v[:n])
+        else:
+            out["table"] = model.entity_embedding.embedding.data
+            for name in model.embed_opt.state_names:
+                out[name] = model.embed_opt.state(name)
+        for name, p in model.named_parameters():
+            if p.requires_grad and "dummy" not in name:
+                out["dense/" + name] = p.data
+        return out
+
+    def close(self):
+        """Drop graphs, model and table so that the next workload finds the memory free."""
+        import gc
         torch.cuda.synchronize()
-        if chained_graphs:
-            # CUDA graphs that captured NCCL collectives keep the communicator busy, and destroying the
-            # process group under them blocks; every rank is done communicating here, so leave at once
-            sys.stdout.flush()
-            sys.stderr.flush()
-            os._exit(0)
-        if world > 1:
-            dist.destroy_process_group()
+        self.graphs, self.static = {}, []
+        self.model = self.shard = self.feeder = None
+        self.dev_batches = self.host_batches = []
+        self._initial = None
+        gc.collect()
+        torch.cuda.empty_cache()
 
-    if rank != 0:
-        shutdown()
-        return
 
-    peak, peak_kind = load_peaks()
-    nus = [int(t.item()) for t in timer.notes.get("n_unique", []) + timer.notes.get("n_unique_owner", [])]
+def timed_steps(runner, k0, k, e2e=False):
+    """ms for steps k0..k0+k-1, bracketed by barrier + synchronize on both sides, CUDA events on the
+    launching stream; with e2e the steps are fed from host memory and the loss is read back."""
+    if e2e:
+        runner.prepare_e2e(k0)
+    runner.sync_all()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    t0 = time.perf_counter()
+    last = runner.run_e2e(k0, k) if e2e else runner.run_resident(k0, k)
+    host = time.perf_counter() - t0
+    b.record()
+    runner.sync_all()
+    return a.elapsed_time(b), host, last
+
+
+def kernel_table(cfg, workload, kernel_ms, notes, peak, peak_kind, fma_rate=None):
+    """Per-kernel averages of the eager pass with the roofline of the kernel that took longest."""
+    nus = [int(t.item()) for t in notes.get("n_unique", []) + notes.get("n_unique_owner", [])]
     n_unique_mean = sum(nus) / len(nus) if nus else cfg["B"] * cfg["K"]
     alg = algorithmic_bytes(cfg, n_unique_mean=n_unique_mean)
     flops = algorithmic_flops(cfg)
@@ -818,9 +943,30 @@ def run_gpu(args):
         if name in flops:
             entry.update({"algorithmic_flops": flops[name], "achieved_tflops": round(flops[name] / (avg * 1e-3) / 1e12, 1)})
         kernels[name] = entry
-    dom = max((k for k in kernels if k in alg or k in flops), key=lambda k: kernels[k]["total_ms"], default=None)
-    roofline = None
     timing_note = "CUDA events around each launch, eager pass over the same K steps"
+    roofline = None
+    if cfg["shared"] and cfg["geo"] in ALU_OPS_PER_TERM and fma_rate:
+        # shared candidates: every pair re-uses rows that other pairs use, so these kernels are bound by
+        # fp32 ALU throughput.  Work unit = one (pair, dim) term evaluation; the bound is the measured
+        # fp32 instruction rate divided by the instructions one term costs in the kernel's inner loop.
+        terms = float(cfg["B"]) * cfg["K"] * cfg["dim"]
+        ops = ALU_OPS_PER_TERM[cfg["geo"]]
+        for name, key in (("rows_forward", "fwd"), ("rows_backward", "bwd")):
+            if name in kernels:
+                rate = terms / (kernels[name]["avg_ms"] * 1e-3)
+                kernels[name].update({"term_evals_per_s": rate, "alu_ops_per_term": ops[key],
+                                      "frac_of_fp32_alu": round(rate * ops[key] / fma_rate, 4)})
+        cands = [k for k in ("rows_forward", "rows_backward") if k in kernels]
+        if cands:
+            dom = max(cands, key=lambda k: kernels[k]["total_ms"])
+            key = "fwd" if dom == "rows_forward" else "bwd"
+            roofline = {"kernel": dom, "bound": "fp32_alu", "achieved": round(kernels[dom]["term_evals_per_s"] / 1e12, 3),
+                        "peak": round(fma_rate / ops[key] / 1e12, 3), "unit": "T term-evaluations/s",
+                        "peak_source": "fp32 FMA rate of the library's probe kernel, measured in this run "
+                                       "(%.1f T instr/s) / %d ALU instructions per term" % (fma_rate / 1e12, ops[key]),
+                        "frac": kernels[dom]["frac_of_fp32_alu"], "traffic": None, "timing": timing_note}
+        return kernels, roofline, n_unique_mean
+    dom = max((k for k in kernels if k in alg or k in flops), key=lambda k: kernels[k]["total_ms"], default=None)
     if dom in flops:
         # tensor-core GEMM: useful flops against the measured dense bf16 rate scaled to the mode in use
         # (TF32 issues at half the bf16 rate; the fp32 mode spends nine bf16 MMAs per product)
@@ -839,53 +985,283 @@ def run_gpu(args):
     elif dom:
         roofline = {"kernel": dom, "bound": "hbm", "achieved": kernels[dom]["achieved_gbs"], "peak": peak,
                     "peak_source": peak_kind, "unit": "GB/s", "frac": round(kernels[dom]["achieved_gbs"] / peak, 4),
-                    "traffic": ncu_traffic(args.workload, dom, n_unique_mean), "timing": timing_note}
+                    "traffic": ncu_traffic(workload, dom, n_unique_mean), "timing": timing_note}
+    return kernels, roofline, n_unique_mean
+
+
+def cublas_comparison(cfg, device):
+    """torch.mm (cuBLAS) on the operands of the shared-candidate inner products - the reference's own
+    call for this shape (complex.py:186) - in TF32 and in fp32: ms for the forward product and for the
+    two gradient products."""
+    B, K = cfg["B"], cfg["K"]
+    W = cfg["dim"] * (2 if cfg["geo"] == "complex" else 1)
+    q = torch.randn(B, W, device=device) * 0.05
+    e = torch.randn(K, W, device=device) * 0.05
+    g = torch.randn(B, K, device=device)
+    out = {}
+    prev = torch.backends.cuda.matmul.allow_tf32
+    for name, tf32 in (("tf32", True), ("fp32", False)):
+        torch.backends.cuda.matmul.allow_tf32 = tf32
+        for what, fn in (("forward", lambda: torch.mm(q, e.t())),
+                         ("backward", lambda: (torch.mm(g, e), torch.mm(g.t(), q)))):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(10):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            out["%s_%s_ms" % (name, what)] = round(a.elapsed_time(b) / 10, 4)
+    torch.backends.cuda.matmul.allow_tf32 = prev
+    return out
+
+
+def parity_check(args, device, world, rank):
+    """Several GPUs, before anything is timed: the production mode of the sharded step (replayed CUDA
+    graphs, the next step's rows prefetched by bulk copies from peer memory, stale rows repaired from
+    the owners' bitmaps) and the plain mode (eager launches, every step's rows pulled after the
+    previous update) run the same five steps (2i, up structures) from identical state on a small
+    table; every rank compares its shard of the table and of the Adam state and all dense parameters.
+    The two modes run the same kernels on the same values; the only freedom is the order of atomic
+    additions into gradient rows that several positions of a rank share, so the comparison allows
+    the atomic-accumulation tolerance and also reports whether the results were bit-identical."""
+    import torch.distributed as dist
+    cfg = dict(WORKLOADS["freebase_q2b"], B=128, K=256, structures=["2i", "up"])
+    rows = 200000
+    results = []
+    for graphs, prefetch in ((True, True), (False, False)):
+        r = StepRunner(cfg, rows, device, world, rank, graphs=graphs, prefetch=prefetch, pool=4, resettable=True)
+        r.reset_state()
+        if r.chained_graphs:
+            r.run_resident(0, 4)           # start_chain runs batch -1 eagerly, then four replays
+        else:
+            r.run_resident(-1, 5)
+        r.sync_all()
+        results.append({k: v.detach().clone() for k, v in r.state_tensors().items()})
+        r.close()
+    tol = 1e-4
+    worst, identical = 0.0, 1.0
+    for k in results[0]:
+        a, b = results[0][k].float(), results[1][k].float()
+        scale = float(b.abs().max().clamp_min(1e-30))
+        diff = (a - b).abs() / scale
+        if k.startswith("dense/"):
+            # torch's Adam divides every element by its own |gradient|: an element whose gradient is of
+            # rounding-noise size may step another way.  Up to 1e-5 of a tensor's elements may do so.
+            n_out = int((diff > tol).sum())
+            if n_out <= 1e-5 * diff.numel():
+                diff = diff.clamp_max(tol) if n_out else diff
+        worst = max(worst, float(diff.max()))
+        identical = min(identical, float(torch.equal(a, b)))
+    t = torch.tensor([worst, -identical], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    worst, identical = float(t[0]), bool(-float(t[1]) > 0.5)
+    verdict = {"prefetch_vs_sync": "bit-identical" if identical else "within tolerance" if worst <= tol else "MISMATCH",
+               "steps": 5, "max_rel_diff": worst, "tolerance": tol, "rows_per_gpu": rows, "structures": cfg["structures"],
+               "compared": "per-rank table shard, Adam state, dense parameters"}
+    if worst > tol:
+        if rank == 0:
+            print(json.dumps({"parity_check": verdict}), flush=True)
+        raise SystemExit("parity check failed: prefetch/graph mode and plain mode differ by %g" % worst)
+    return verdict
+
+
+def run_workload(name, cfg, args, device, world, rank, steps, warmup, repeats, peak, peak_kind, fma_rate, clocks=None):
+    """Build one workload, time it (device-resident inputs, then end to end), take the per-kernel
+    times, free it.  Returns the dict that describes it."""
+    import torch.distributed as dist
+    from smore_b200 import _lib
+    rows_per_gpu = args.rows or cfg["rows"] or (FREEBASE_ENTITIES + 7) // 8
+    runner = StepRunner(cfg, rows_per_gpu, device, world, rank, graphs=not args.no_graphs, prefetch=not args.no_prefetch,
+                        lazy=not args.no_lazy, fused_paths=not args.no_fused_paths, pool=args.pool)
+    import gc
+    gc.collect()
+    gc.freeze()        # keep the cycle collector from scanning the long-lived model objects inside a timed region
+    runner.run_resident(0, warmup)
+    runner.sync_all()
+    if clocks is not None:
+        clocks.start()
+    L = runner.L
+    # ---- resident-input timing ("value"): `repeats` timed regions of exactly `steps` steps each -------
+    samples = []
+    k0 = warmup
+    for _ in range(repeats):
+        launches0 = L.smore_kernel_launch_count()
+        ms, host, _ = timed_steps(runner, k0, steps)
+        launches = runner.launches_in(k0, steps, L.smore_kernel_launch_count() - launches0)
+        samples.append((ms, host, launches))
+        k0 += steps
+    # ---- end-to-end timing: pinned host index tensors in, loss out, every step --------------------------
+    runner.prepare_e2e(0)
+    runner.run_e2e(0, min(3, warmup))
+    runner.sync_all()
+    e2e_samples, last_loss = [], 0.0
+    for rep in range(repeats):
+        ms, _, last_loss = timed_steps(runner, warmup + rep * steps, steps, e2e=True)
+        e2e_samples.append(ms)
+    if _lib.async_status() != 0:
+        raise RuntimeError("device status word %d (a bulk-copy wait gave up, or a row id lay outside the table): "
+                           "the timed results are invalid" % _lib.async_status())
+    ms_eager, kernel_ms, notes = runner.eager_timed_pass(warmup, steps)
+    gc.unfreeze()
+    launch_counts = [s[2] for s in samples]
+    host_issue = sorted(s[1] for s in samples)[len(samples) // 2]   # host time to enqueue a region's steps
+    samples = torch.tensor([[s[0] for s in samples], e2e_samples], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(samples, op=dist.ReduceOp.MAX)      # per timed region: the slowest rank
+    res_ms = sorted(samples[0].tolist())
+    e2e_ms = sorted(samples[1].tolist())
+    med, med_e2e = res_ms[len(res_ms) // 2], e2e_ms[len(e2e_ms) // 2]
+    structures = runner.structures
+    out = None
+    if rank == 0:
+        kernels, roofline, n_unique_mean = kernel_table(cfg, name, kernel_ms, notes, peak, peak_kind, fma_rate)
+        total_queries = cfg["B"] * world * steps
+        out = {
+            "value": round(total_queries / (med * 1e-3), 1), "unit": "queries/s",
+            "ms_per_step": round(med / steps, 4),
+            "repeats": {"n": repeats, "steps_each": steps, "statistic": "median",
+                        "ms_per_step_min": round(res_ms[0] / steps, 4), "ms_per_step_max": round(res_ms[-1] / steps, 4)},
+            "execution": ("one captured CUDA graph per query structure, replayed" if runner.use_graphs else
+                          "one captured CUDA graph per (query structure, arena), replayed; next step's rows prefetched "
+                          "inside the graph" if runner.chained_graphs else "eager launches"),
+            "eager_ms_per_step": round(ms_eager / steps, 4),
+            "config": {"workload": name, "geo": cfg["geo"], "queries_per_gpu": cfg["B"], "negatives": cfg["K"],
+                       "shared_negatives": cfg["shared"], "dim": cfg["dim"], "table_rows_per_gpu": rows_per_gpu,
+                       "table_rows_total": runner.n_rows, "structures": structures,
+                       "parallelism": "1 GPU, table resident" if world == 1 else
+                                      "table and Adam state row-sharded over %d GPUs, rows and row gradients over NVLink" % world,
+                       "optimizer": "adam, row-wise v" if cfg["squeeze"] else "adam, full v",
+                       "lazy_rows": not args.no_lazy,
+                       "l2_policy": ("inputs larger than L2: every step touches ~%.1f GB of table rows" %
+                                     (cfg["B"] * cfg["K"] * cfg["dim"] * 4 / 1e9)) if not cfg["shared"] else
+                                    "working set smaller than L2 by construction (shared candidates): the kernels "
+                                    "are bound by arithmetic, not by memory"},
+            "e2e": {"value": round(total_queries / (med_e2e * 1e-3), 1), "unit": "queries/s",
+                    "ms_per_step": round(med_e2e / steps, 4),
+                    "h2d_bytes_per_step": int(runner.h2d_bytes), "d2h_bytes_per_step": 4},
+            "gpu_launches": int(launch_counts[0]),
+            "distinct_rows_per_step": round(n_unique_mean, 1),
+            "roofline": roofline,
+            "kernels": kernels,
+            "host_issue_ms_per_step": round(1e3 * host_issue / steps, 4),
+            "last_loss": last_loss,
+        }
+        if args.dump_kernel_times:
+            out["kernel_ms_raw"] = {k: [round(x, 3) for x in v] for k, v in kernel_ms.items()}
+    runner.close()
+    return out
+
+
+def run_gpu(args):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU path for the product arm)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    peak, peak_kind = load_peaks()
+    fma_rate = measure_fma_rate(device)
+    parity = parity_check(args, device, world, rank) if world > 1 and not args.no_parity_check else None
+
+    cfg = dict(WORKLOADS[args.workload])
+    if args.structures:
+        cfg["structures"] = args.structures.split(",")
+    clocks = ClockSampler(local_rank)
+    head = run_workload(args.workload, cfg, args, device, world, rank, args.steps, args.warmup, args.repeats, peak,
+                        peak_kind, fma_rate, clocks)
+    clock_summary = clocks.summary()
+
+    # the other configurations, one after the other in the same process (1 GPU, default workload only)
+    others = {}
+    if world == 1 and args.workload == "freebase_q2b" and not args.headline_only and not args.structures:
+        extra = [("rotate_wikikg", None), ("q2b_fb15k", None), ("gqe_fb15k237", None),
+                 ("distmult_wikikg", "fp32"), ("distmult_wikikg", "tf32")]
+        for name, dot_mode in extra:
+            wcfg = dict(WORKLOADS[name])
+            prev = os.environ.get("SMORE_B200_DOT")
+            if dot_mode:
+                os.environ["SMORE_B200_DOT"] = dot_mode
+            try:
+                res = run_workload(name, wcfg, args, device, 1, 0, args.steps, max(3, args.warmup), 3, peak, peak_kind,
+                                   fma_rate)
+                if dot_mode:
+                    res["dot_precision"] = dot_mode
+                    cb = cublas_comparison(wcfg, device)
+                    res["cublas"] = cb
+                    for kname, what in (("dot_forward", "forward"), ("dot_backward", "backward")):
+                        if kname in res["kernels"]:
+                            res["kernels"][kname]["vs_cublas"] = round(
+                                cb["%s_%s_ms" % (dot_mode, what)] / res["kernels"][kname]["avg_ms"], 3)
+                slim = {k: res[k] for k in ("value", "unit", "ms_per_step", "repeats", "eager_ms_per_step", "e2e", "roofline",
+                                            "kernels", "gpu_launches", "distinct_rows_per_step") if k in res}
+                slim["config"] = {k: res["config"][k] for k in ("geo", "queries_per_gpu", "negatives", "shared_negatives",
+                                                                "dim", "table_rows_per_gpu", "structures", "optimizer")}
+                for k in ("dot_precision", "cublas"):
+                    if k in res:
+                        slim[k] = res[k]
+                others[name if not dot_mode else "%s[%s]" % (name, dot_mode)] = slim
+            except Exception as exc:      # a side workload must not take the headline line down with it
+                others[name if not dot_mode else "%s[%s]" % (name, dot_mode)] = {"failed": repr(exc)}
+            finally:
+                if dot_mode:
+                    if prev is None:
+                        os.environ.pop("SMORE_B200_DOT", None)
+                    else:
+                        os.environ["SMORE_B200_DOT"] = prev
+
+    def shutdown():
+        torch.cuda.synchronize()
+        if world > 1:
+            # every graph that captured a collective is gone (StepRunner.close); should the communicator
+            # still be busy, do not let the process hang on it after the line has been printed
+            sys.stdout.flush()
+            sys.stderr.flush()
+            watchdog = threading.Timer(20.0, lambda: os._exit(0))
+            watchdog.daemon = True
+            watchdog.start()
+            dist.destroy_process_group()
+            watchdog.cancel()
+
+    if rank != 0:
+        shutdown()
+        return
 
     cpu = None
     if not args.no_cpu_baseline and world == 1:      # reported at N=1 only
         try:
-            qps, ms, threads, sample = cpu_reference_steps(cfg, steps=args.cpu_steps, warmup=2)
-            cpu = {"value": round(qps, 1), "unit": "queries/s", "cores": threads, "kind": "port",
-                   "ms_per_step": round(ms, 2), "sample": sample}
+            r = cpu_reference_steps(cfg, steps=args.cpu_steps, warmup=2)
+            cpu = {"value": round(r["value"], 1), "unit": "queries/s", "cores": r["cores"], "kind": r["kind"],
+                   "ms_per_step": round(r["ms_per_step"], 2), "sample": r["sample"]}
         except Exception as exc:  # the baseline is a report, not a dependency of the product arm
             cpu = {"value": None, "unit": "queries/s", "cores": None, "kind": "port", "sample": "failed: %r" % (exc,)}
 
-    total_queries = cfg["B"] * world * args.steps
     out = {
         "metric": "queries/sec (fwd+bwd+sparse update)",
-        "value": round(total_queries / (ms_total * 1e-3), 1),
-        "unit": "queries/s",
+        "value": head["value"], "unit": "queries/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms_total / args.steps, 4),
-        "execution": ("one captured CUDA graph per query structure, replayed" if use_graphs else
-                      "one captured CUDA graph per (query structure, arena), replayed; next step's rows prefetched "
-                      "inside the graph" if chained_graphs else "eager launches"),
-        "eager_ms_per_step": round(ms_eager / args.steps, 4),
+        "ms_per_step": head["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "geo": cfg["geo"], "queries_per_gpu": cfg["B"], "negatives": cfg["K"],
-                   "shared_negatives": cfg["shared"], "dim": cfg["dim"], "table_rows_per_gpu": rows_per_gpu,
-                   "table_rows_total": n_rows, "structures": structures,
-                   "parallelism": "1 GPU, table resident" if world == 1 else
-                                  "table and Adam state row-sharded over %d GPUs, rows and row gradients over NVLink" % world,
-                   "optimizer": "adam, row-wise v" if cfg["squeeze"] else "adam, full v",
-                   "lazy_rows": not args.no_lazy,
-                   "l2_policy": "inputs larger than L2: every step touches ~%.1f GB of table rows" %
-                                (cfg["B"] * cfg["K"] * cfg["dim"] * 4 / 1e9)},
-        "e2e": {"value": round(total_queries / (ms_e2e * 1e-3), 1), "unit": "queries/s",
-                "ms_per_step": round(ms_e2e / args.steps, 4),
-                "h2d_bytes_per_step": int(h2d_bytes), "d2h_bytes_per_step": 4},
-        "gpu_launches": int(launches),
-        "distinct_rows_per_step": round(n_unique_mean, 1),
-        "roofline": roofline,
-        "kernels": kernels,
-        "cpu_baseline": cpu,
-        "clocks": clock_summary,
-        "host_issue_ms_per_step": round(1e3 * t_issue / args.steps, 4),
-        "last_loss": last_loss,
     }
-    if args.dump_kernel_times:
-        out["kernel_ms_raw"] = {k: [round(x, 3) for x in v] for k, v in kernel_ms.items()}
+    for k in ("repeats", "execution", "eager_ms_per_step", "config", "e2e", "gpu_launches", "distinct_rows_per_step",
+              "roofline", "kernels", "last_loss"):
+        out[k] = head[k]
+    if "kernel_ms_raw" in head:
+        out["kernel_ms_raw"] = head["kernel_ms_raw"]
+    out["cpu_baseline"] = cpu
+    out["clocks"] = clock_summary
+    out["fp32_fma_per_s"] = fma_rate
+    if parity is not None:
+        out["parity_check"] = parity
+    if others:
+        out["workloads"] = others
     print(json.dumps(out), flush=True)
     shutdown()
 
@@ -895,7 +1271,8 @@ def run_reference(args):
     if rank != 0:
         return
     cfg = dict(WORKLOADS[args.workload])
-    qps, ms, threads, sample = cpu_reference_steps(cfg, steps=args.steps, warmup=args.warmup)
+    r = cpu_reference_steps(cfg, steps=args.steps, warmup=args.warmup)
+    qps, ms = r["value"], r["ms_per_step"]
     world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
     out = {
         "impl": "reference",
@@ -903,9 +1280,9 @@ def run_reference(args):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "geo": cfg["geo"], "queries_per_gpu": cfg["B"],
-                   "negatives": cfg["K"], "dim": cfg["dim"]},
-        "cpu_baseline": {"value": round(qps, 1), "unit": "queries/s", "cores": threads, "kind": "port",
-                         "sample": sample},
+                   "negatives": cfg["K"], "dim": cfg["dim"], "structures": cfg["structures"]},
+        "cpu_baseline": {"value": round(qps, 1), "unit": "queries/s", "cores": r["cores"], "kind": r["kind"],
+                         "sample": r["sample"]},
         "e2e": {"value": round(qps, 1), "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(out), flush=True)
@@ -1001,6 +1378,10 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=18)
     ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps; the median is reported")
+    ap.add_argument("--headline-only", action="store_true", help="1 GPU: skip the other configurations")
+    ap.add_argument("--no-parity-check", action="store_true",
+                    help="several GPUs: skip the comparison of the graph + prefetch mode with the plain mode")
     ap.add_argument("--workload", default="freebase_q2b", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="smore_b200", choices=["smore_b200", "reference"])
     ap.add_argument("--rows", type=int, default=0, help="override entity-table rows per GPU")

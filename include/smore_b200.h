@@ -71,6 +71,14 @@ SMORE_API const char* smore_version(void);
  * streams); memsets are not counted.  For accounting in benchmarks. */
 SMORE_API unsigned long long smore_kernel_launch_count(void);
 
+/* Measurement aid (no counterpart in the reference): enqueues one kernel in which every thread of a
+ * grid that fills the GPU runs eight independent chains of `iters` dependent fp32 fused
+ * multiply-adds, and returns in *fma_count (host) how many FMAs that is in all.  Timed with CUDA
+ * events it gives the non-tensor fp32 instruction rate of the device, the bound of the kernels that
+ * are limited by arithmetic rather than by memory (shared-candidate scoring).  `out` is one device
+ * float that is never written in practice. */
+SMORE_API int smore_alu_probe(float* out, size_t iters, double* fma_count, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Distance ops on materialised operands.
  * Replace DistImpl<float>::forward / ::backward (ext_cuda_kernel.h:24-32, ext_cuda_kernel.cu:25-77)

@@ -163,12 +163,22 @@ class MemoryRW(object):
 
 def reference_embedding_optimizers(model, args, gpu_id):
     """The reference's own row-wise optimizers for the model's sparse embeddings
-    (train_process.py:290-293).  gpu_id == -1: tables in host memory through MemoryRW."""
+    (train_process.py:290-293).
+    gpu_id == -1: tables and state in host memory through MemoryRW.
+    gpu_id >= 0:  the reference keeps optimizer state on the GPU only when it is shared through the
+                  embedding module (--share_optim_stats: main_train.py:165-166 registers the state as
+                  buffers, which then move to the device with the module); that route is taken here."""
     from smore.common.embedding import embed_optimizer as eo
+    cls = eo.get_optim_class(args)
+    embeds = list(model.named_sparse_embeddings())
     if gpu_id == -1:
         eo.EmbeddingRW = MemoryRW
-    cls = eo.get_optim_class(args)
-    return {name: cls(args, embed, gpu_id) for name, embed in model.named_sparse_embeddings()}
+    else:
+        args.share_optim_stats = True
+        cls.prepare_optimizers(args, [e for _, e in embeds])
+        for _, e in embeds:
+            e.cuda(gpu_id)
+    return {name: cls(args, embed, gpu_id) for name, embed in embeds}
 
 
 def dense_optimizer(model, lr):

@@ -25,6 +25,7 @@ SIGNATURES = {
     "smore_last_error": (ctypes.c_char_p, []),
     "smore_version": (ctypes.c_char_p, []),
     "smore_kernel_launch_count": (ctypes.c_ulonglong, []),
+    "smore_alu_probe": (_int, [_p, _sz, ctypes.POINTER(ctypes.c_double), _p]),
     "smore_dist_forward": (_int, [_int, _p, _p, _p, _p] + [_sz] * 7 + [_p]),
     "smore_dist_backward": (_int, [_int] + [_p] * 7 + [_sz] * 7 + [_p]),
     "smore_dist_forward_f64": (_int, [_int, _p, _p, _p, _p] + [_sz] * 7 + [_p]),

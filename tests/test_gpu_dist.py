@@ -156,7 +156,7 @@ def test_shim_rejects_bad_arguments(ext):
     with pytest.raises(ValueError):
         ext.l1_dist_forward(e, c, torch.zeros(3, 3, device="cuda"))          # wrong output shape
     with pytest.raises(ValueError):
-        ext.l1_dist_forward(e.transpose(0, 1), c, torch.zeros(2, 3, device="cuda"))  # not contiguous
+        ext.l1_dist_forward(e, c, torch.zeros(3, 2, device="cuda").t())      # output buffer not contiguous
     with pytest.raises(ValueError):
         ext.rotate_dist_forward(e, c, c, torch.zeros(2, 3, device="cuda"))   # rows must be 2 x dim
     with pytest.raises(ValueError):
@@ -171,6 +171,27 @@ def test_shim_rejects_bad_arguments(ext):
     assert ext.ThreadPool(1).num_threads == 1
     ext.AsyncGPUJob(0).sync()
     ext.CudaEvent(0).record()
+
+
+def test_shim_accepts_strided_inputs(oracle, ext):
+    """Inputs with any strides are accepted (autograd hands the backward of the reference front-ends'
+    torch.stack over union branches, box_dist.py:60-68, a strided grad_out)."""
+    ent, q0, q1 = make_operands("box_out", 5, 7, 5, 1, 24, seed=2)
+    gout = np.random.default_rng(3).standard_normal((5, 7)).astype(np.float32)
+    want = oracle.dist_backward("box_out", gout, ent, q0, q1)
+    d = [_dev(ent), _dev(q0), _dev(q1)]
+    stacked = torch.stack([_dev(gout), _dev(gout) * 2], dim=1)     # [5, 2, 7]
+    strided_gout = stacked[:, 0]                                     # strides (14, 1): not contiguous
+    assert not strided_gout.is_contiguous()
+    strided_ent = torch.stack([d[0], d[0]], dim=2)[:, :, 0]          # [5, 7, 24] view with gaps
+    assert not strided_ent.is_contiguous()
+    g = [torch.empty_like(d[0]), torch.empty_like(d[1]), torch.empty_like(d[2])]
+    ext.box_dist_backward(strided_gout, strided_ent, d[1], d[2], g[0], g[1], g[2], "out")
+    for got, ref in zip(g, want):
+        close(got.cpu().numpy(), ref, 2 * RTOL)
+    dst = torch.empty(5, 7, device="cuda")
+    ext.box_dist_forward(strided_ent, d[1], d[2], dst, "out")
+    close(dst.cpu().numpy(), oracle.dist_forward("box_out", ent, q0, q1), RTOL)
 
 
 def test_reference_cuda_kernels_agree(oracle):
@@ -273,8 +294,18 @@ def test_speed_against_reference_kernels(op, shared, capsys):
 
     t = {"ours_fwd": time_ms(ours_fwd, 5), "ref_fwd": time_ms(ref_fwd, 3),
          "ours_bwd": time_ms(ours_bwd, 5), "ref_bwd": time_ms(ref_bwd, 2)}
-    close(mine.cpu().numpy(), theirs.cpu().numpy(), 1e-4, what=op + " forward")
-    close(gm[1].cpu().numpy(), gr[1].cpu().numpy(), 1e-3, what=op + " g_first")
+    # forward and entity gradient: sums re-associated only; query gradient: the reference's order over
+    # the K candidates differs and its kernel for shared candidates accumulates with atomics
+    fscale = float((ent.abs().reshape(-1, mul * dim)[:64] @ q0.abs().reshape(-1, dim)[:64].t()).max()) \
+        if op == "distmult" else None
+    close(mine.cpu().numpy(), theirs.cpu().numpy(), RTOL, fscale, what=op + " forward")
+    tol = RTOL if not shared else RTOL_ATOMIC      # compared on the device: up to 4 GB per operand
+    bound = tol * float(gr[0].abs().max()) + tol * gr[0].abs()
+    assert bool(((gm[0] - gr[0]).abs() <= bound).all()), op + " g_entity"
+    del bound
+    close(gm[1].cpu().numpy(), gr[1].cpu().numpy(), RTOL_ATOMIC, what=op + " g_first")
+    if q1 is not None:
+        close(gm[2].cpu().numpy(), gr[2].cpu().numpy(), RTOL_ATOMIC, what=op + " g_second")
     with capsys.disabled():
         print("\nreference-kernel comparison %s %s B=K=1024 dim=%d: forward %.3f ms vs %.3f ms (x%.1f), "
               "backward %.3f ms vs %.3f ms (x%.1f)" % (op, "shared" if shared else "per-query", dim, t["ours_fwd"],

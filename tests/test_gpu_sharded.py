@@ -140,7 +140,7 @@ def _free_port():
     return port
 
 
-def _two_process_worker(rank, world, port, n_total, D, B, K, out_dir):
+def _two_process_worker(rank, world, port, n_total, D, B, K, out_dir, prefetch=False, steps=2):
     import torch.distributed as dist
     from smore_b200 import sharded
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -153,11 +153,21 @@ def _two_process_worker(rank, world, port, n_total, D, B, K, out_dir):
     shard.table.zero_()
     shard.table[:shard.local_rows] = full[shard.base:shard.base + shard.local_rows].cuda()
     opt = sharded.ShardedAdamOptimizer(shard)
-    for step in range(2):
+    batches = [tuple(t.cuda() for t in _rank_batch(rank, step, n_total, B, K, D)) for step in range(steps)]
+    for step in range(steps):
         opt.zero_grad()
-        _rank_forward_backward(opt.forward, _rank_batch(rank, step, n_total, B, K, D), world)
+        if prefetch and step + 1 < steps:
+            # the next step's rows are pulled from the peers' memory on a side stream (bulk copies)
+            # while this step runs, and repaired from the owners' updated-rows bitmaps afterwards
+            nxt = batches[step + 1]
+            opt.prefetch([nxt[1], nxt[0].view(-1), nxt[2][0]])
+        if prefetch and step > 0:
+            assert opt._ready is not None
+        _rank_forward_backward(opt.forward, batches[step], world)
         opt.apply_grad(1e-2)
     torch.cuda.synchronize()
+    from smore_b200 import _lib
+    assert _lib.async_status() == 0
     torch.save(shard.table[:shard.local_rows].cpu(), os.path.join(out_dir, "shard%d.pt" % rank))
     dist.barrier()
     shard.close()
@@ -165,13 +175,17 @@ def _two_process_worker(rank, world, port, n_total, D, B, K, out_dir):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_processes_over_nvlink_match_emulation(tmp_path):
-    """The same two steps run by two real processes (NCCL barriers, IPC-mapped peer memory) and by
-    the one-process emulation give the same table."""
+@pytest.mark.parametrize("prefetch", [False, True])
+def test_two_processes_over_nvlink_match_emulation(tmp_path, prefetch):
+    """The same steps run by two real processes (NCCL barriers, peer memory mapped by the
+    symmetric-memory allocator; with `prefetch` the background row pull and the refresh from the
+    owners' bitmaps run on real peer memory) and by the one-process emulation give the same table."""
     import torch.multiprocessing as mp
     from smore_b200 import sharded
     world, n_total, D, B, K = 2, 1003, 64, 6, 50
-    mp.spawn(_two_process_worker, args=(world, _free_port(), n_total, D, B, K, str(tmp_path)), nprocs=world, join=True)
+    steps = 4 if prefetch else 2
+    mp.spawn(_two_process_worker, args=(world, _free_port(), n_total, D, B, K, str(tmp_path), prefetch, steps),
+             nprocs=world, join=True)
     real = torch.cat([torch.load(os.path.join(str(tmp_path), "shard%d.pt" % r)) for r in range(world)])
     caps = (B * K + 2 * B, B, B)
     shards = sharded.ShardGroup.emulated(world, n_total, D, caps, squeeze=True)
@@ -181,7 +195,7 @@ def test_two_processes_over_nvlink_match_emulation(tmp_path):
         s.table.zero_()
         s.table[:s.local_rows] = full[s.base:s.base + s.local_rows].cuda()
     opts = [sharded.ShardedAdamOptimizer(s, barrier=lambda: None) for s in shards]
-    for step in range(2):
+    for step in range(steps):
         for o_ in opts:
             o_.zero_grad()
         for r in range(world):

@@ -147,6 +147,99 @@ def test_training_steps_match_native_path(name, lazy):
                 close(p1.grad.cpu().numpy(), p2.grad.cpu().numpy(), RTOL_ATOMIC, what="grad of " + n1)
 
 
+def test_gqe_fb15k237_exact_shape_step():
+    """The GQE configuration at its exact size (14,505 x 64 table, 237 relations, 512 one-hop queries,
+    128 negatives each, gamma 12): one whole training step against the torch-native path."""
+    cfg = dict(bench.WORKLOADS["gqe_fb15k237"])
+    n_rows = cfg["rows"]
+    a, b = _pair(cfg, n_rows, lazy=True)
+    pos, neg, q = (t.cuda() for t in bench.make_batch(cfg, n_rows, "1p", seed=0))
+    assert neg.shape == (512, 128) and a.entity_embedding.embedding.shape == (14505, 64)
+    before = a.entity_embedding.embedding.data.clone()
+    la = bench.train_step(a, pos, neg, q, "1p")
+    lb = bench.train_step(b, pos, neg, q, "1p")
+    close(la.item(), lb.item(), RTOL, what="loss")
+    ta, tb = a.entity_embedding.embedding.data, b.entity_embedding.embedding.data
+    touched = torch.zeros(n_rows, dtype=torch.bool, device="cuda")
+    for t in (pos, neg.reshape(-1), q[:, 0]):
+        touched[t] = True
+    assert torch.equal(ta[~touched], before[~touched])
+    close_mostly(ta, tb, RTOL_ATOMIC, 4 * cfg["lr"], "table")
+    close_mostly(a.embed_opt.state("state_sum_fo"), b.embed_opt.m, RTOL_ATOMIC, 1e-3, "m")
+    close_mostly(a.embed_opt.state("state_sum_sq"), b.embed_opt.v, RTOL_ATOMIC, 1e-3, "v")
+    close(a.relation_embedding.grad.cpu().numpy(), b.relation_embedding.grad.cpu().numpy(), RTOL_ATOMIC,
+          what="relation gradient")
+
+
+def test_rotate_wikikg_shape_table_rows_against_reference_kernels():
+    """The RotatE configuration's op shape (1024 queries x 1024 negatives each, dim 500, 4000-byte rows)
+    on table-resident rows of a 300,000-row table: forward, the step's merged row gradients and the
+    query gradients against the reference's own CUDA kernels (recompiled for sm_100a) run on the
+    gathered rows, their entity gradient merged with index_add_."""
+    import ctypes
+    from oracle.oracle import DIST_IDS, reference_cuda_path
+    from smore_b200 import _lib
+    path = reference_cuda_path()
+    if path is None:
+        pytest.skip("reference CUDA library not built")
+    ref = ctypes.CDLL(path)
+    vp, sz = ctypes.c_void_p, ctypes.c_size_t
+    ref.ref_cuda_dist_forward.argtypes = [ctypes.c_int, vp, vp, vp, vp] + [sz] * 7 + [vp]
+    ref.ref_cuda_dist_backward.argtypes = [ctypes.c_int] + [vp] * 7 + [sz] * 7 + [vp]
+    L = _lib.lib()
+    N, B, K, dim = 300000, 1024, 1024, 500
+    W = 2 * dim
+    g = torch.Generator(device="cuda").manual_seed(31)
+    table = (torch.rand(N, W, device="cuda", generator=g) - 0.5) * 0.104
+    idx = torch.randint(0, N, (B, K), device="cuda", generator=g)
+    re = (torch.rand(B, 1, dim, device="cuda", generator=g) - 0.5) * 0.104
+    im = (torch.rand(B, 1, dim, device="cuda", generator=g) - 0.5) * 0.104
+    gout = torch.randn(B, K, device="cuda", generator=g)
+    st = torch.cuda.current_stream().cuda_stream
+    sizes = (B, K, B, K, B, 1, dim)
+    # this library: rows read in place, gradients merged into the step's compact buffer
+    n = B * K
+    uniq = torch.empty(n, dtype=torch.int64, device="cuda")
+    slot = torch.empty(n, dtype=torch.int32, device="cuda")
+    counts = torch.empty(n, dtype=torch.int32, device="cuda")
+    n_unique = torch.empty(2, dtype=torch.int32, device="cuda")
+    ws = torch.empty(L.smore_unique_rows_workspace_bytes(N), dtype=torch.uint8, device="cuda")
+    _lib.check(L.smore_unique_rows(idx.data_ptr(), n, N, uniq.data_ptr(), slot.data_ptr(), counts.data_ptr(),
+                                   n_unique.data_ptr(), ws.data_ptr(), ws.numel(), st), "unique")
+    mine = torch.empty(B, K, device="cuda")
+    _lib.check(L.smore_dist_forward_rows(DIST_IDS["rotate"], table.data_ptr(), idx.data_ptr(), N, re.data_ptr(),
+                                         im.data_ptr(), mine.data_ptr(), *sizes, st), "forward_rows")
+    g_rows = torch.empty(n, W, device="cuda")
+    _lib.check(L.smore_zero_shared_rows(g_rows.data_ptr(), counts.data_ptr(), n_unique.data_ptr(), n, W, st), "zero")
+    g_re, g_im = torch.empty_like(re), torch.empty_like(im)
+    _lib.check(L.smore_dist_backward_rows(DIST_IDS["rotate"], gout.data_ptr(), table.data_ptr(), idx.data_ptr(), N,
+                                          re.data_ptr(), im.data_ptr(), slot.data_ptr(), counts.data_ptr(),
+                                          g_rows.data_ptr(), g_re.data_ptr(), g_im.data_ptr(), *sizes, st), "backward_rows")
+    # the reference kernels on the gathered copy
+    ent = table[idx]                                            # [B, K, W], 4.2 GB
+    theirs = torch.empty(B, K, device="cuda")
+    assert ref.ref_cuda_dist_forward(DIST_IDS["rotate"], ent.data_ptr(), re.data_ptr(), im.data_ptr(),
+                                     theirs.data_ptr(), *sizes, st) == 0
+    r_ent, r_re, r_im = torch.zeros_like(ent), torch.zeros_like(re), torch.zeros_like(im)
+    assert ref.ref_cuda_dist_backward(DIST_IDS["rotate"], gout.data_ptr(), ent.data_ptr(), re.data_ptr(), im.data_ptr(),
+                                      r_ent.data_ptr(), r_re.data_ptr(), r_im.data_ptr(), *sizes, st) == 0
+    torch.cuda.synchronize()
+    t_u, t_i = torch.unique(idx.view(-1), return_inverse=True)
+    nu = int(n_unique[0])
+    assert nu == t_u.numel() and torch.equal(uniq[:nu], t_u) and torch.equal(slot.long(), t_i)
+    merged = torch.zeros(nu, W, device="cuda").index_add_(0, t_i, r_ent.view(-1, W))
+    del r_ent, ent
+
+    def agree(a, b, rtol, what):
+        bound = rtol * float(b.abs().max()) + rtol * b.abs()
+        assert bool(((a - b).abs() <= bound).all()), what
+
+    agree(mine, theirs, RTOL, "forward")
+    agree(g_rows[:nu], merged, RTOL_ATOMIC, "merged row gradients")
+    agree(g_re, r_re, RTOL_ATOMIC, "g_re")
+    agree(g_im, r_im, RTOL_ATOMIC, "g_im")
+
+
 def test_full_size_properties():
     """Benchmark shapes (B=1024, K=1024, dim 400) on a 2M-row table: index sets are exact,
     logits equal a torch-native evaluation, the gradient buffer is linear in the output gradient
