@@ -1045,6 +1045,8 @@ def parity_check(args, device, world, rank):
     worst, identical = 0.0, 1.0
     for k in results[0]:
         a, b = results[0][k].float(), results[1][k].float()
+        if a.numel() == 0:
+            continue
         scale = float(b.abs().max().clamp_min(1e-30))
         diff = (a - b).abs() / scale
         if k.startswith("dense/"):

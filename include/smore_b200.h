@@ -400,38 +400,49 @@ SMORE_API int smore_shard_mark_dirty(const int64_t* uniq, const int32_t* n_uniqu
 /* Owner side of the gradient return.  Every rank publishes up to n_plans (<= 4) sorted lists of
  * distinct global row ids per step with a gradient row per id; list (g, p) has room for
  * plan_caps[p] ids (host array, same on all ranks), its current length is the int32 that
- * nuniq_ptrs[g*n_plans+p] points to (0 = unused this step).
- * collect_ids writes ids[g][prefix(p) + j] = id - base if the j-th id of list (g, p) lies in
- * [base, base + shard_rows), else -1, and list_bounds[l] = [first, last+1) of the kept entries.
- * Run smore_unique_rows over `ids` (n = n_ranks * sum(plan_caps), n_table_rows = shard_rows) to
- * get the owner's distinct local rows, then record_sources, then reduce_update. */
-SMORE_API int smore_shard_collect_ids(const int64_t* const* uniq_ptrs, const int32_t* const* nuniq_ptrs,
-                            size_t n_ranks, size_t n_plans, const int32_t* plan_caps, int64_t base,
-                            size_t shard_rows, int64_t* ids, int32_t* list_bounds, void* stream);
-
-/* src[slot[i]] = i for every position with slot >= 0 (one contributing position per distinct
- * row; rows with several contributors are resolved by search in reduce_update). */
-SMORE_API int smore_shard_record_sources(const int32_t* slot, size_t n, int32_t* src, void* stream);
+ * nuniq_ptrs[g*n_plans+p] points to (0 = unused this step).  Lists are numbered l = g*n_plans + p.
+ *
+ * smore_shard_owner_plan prepares an owner's update from them.  The lists are sorted and the owner's
+ * rows are the id range [base, base + shard_rows), so what it needs of each list is one contiguous
+ * run, found by binary search; the runs are copied as local row ids into `ids` (run after run, in
+ * list order: the position of an id there encodes its list and index), then de-duplicated as
+ * smore_unique_rows does: uniq / slot / counts / n_unique over the owner's distinct local rows, and
+ * src[u] = one position in `ids` that holds row uniq[u].  `runs` receives the run table
+ * (SMORE_SHARD_RUNS_INTS int32 of device memory) that smore_shard_reduce_update_rows reads.
+ * `dirty`, if not NULL, is this rank's updated-rows bitmap: cleared, then one bit set per distinct
+ * row (smore_shard_mark_dirty).  capacity: room in ids / uniq / slot / counts / src, at least
+ * n_ranks * sum(plan_caps) (everything could fall into one shard); only the part in use is touched.
+ * workspace: smore_shard_owner_plan_workspace_bytes(shard_rows) bytes, 256-byte aligned. */
+#define SMORE_SHARD_RUNS_INTS 80
+SMORE_API size_t smore_shard_owner_plan_workspace_bytes(size_t shard_rows);
+SMORE_API int smore_shard_owner_plan(const int64_t* const* uniq_ptrs, const int32_t* const* nuniq_ptrs,
+                           size_t n_ranks, size_t n_plans, const int32_t* plan_caps, int64_t base,
+                           size_t shard_rows, size_t capacity, int64_t* ids, int32_t* runs, int64_t* uniq,
+                           int32_t* slot, int32_t* counts, int32_t* src, int32_t* n_unique,
+                           uint32_t* dirty, void* workspace, size_t workspace_bytes, void* stream);
 
 /* For each distinct local row u < *n_unique: pull its gradient rows from the lists that contain
- * it (grad_ptrs[l] + j*width, peer memory), add them in list order, and apply the Adam update of
- * smore_sparse_update_rows to table / m / v of this shard — one kernel, one pass. */
+ * it (grad_ptrs[l] + j*width, peer memory; n_lists = n_ranks * n_plans), add them in list order,
+ * and apply the Adam update of smore_sparse_update_rows to table / m / v of this shard - transfer,
+ * reduction and update in one kernel, one pass.  Rows of 144 bytes to about 12 KB take the ring
+ * form: each warp keeps several bulk asynchronous copies (peer memory -> shared memory; untiled, no
+ * multicast) in flight ahead of the row it is updating; waits are bounded and report through bit 1
+ * of smore_async_status. */
 SMORE_API int smore_shard_reduce_update_rows(float* table, float* m, float* v, const int64_t* uniq,
                                    const int32_t* counts, const int32_t* src, const int32_t* n_unique,
                                    size_t capacity, const float* const* grad_ptrs, const int64_t* ids,
-                                   const int32_t* list_bounds, size_t n_ranks, size_t n_plans,
-                                   const int32_t* plan_caps, size_t width, double lr, double beta1,
-                                   double beta2, double eps, int64_t step, int squeeze, void* stream);
+                                   const int32_t* runs, size_t n_lists, size_t width, double lr,
+                                   double beta1, double beta2, double eps, int64_t step, int squeeze,
+                                   void* stream);
 
 /* The same with the step-dependent scalars read from device memory (see smore_adam_step_scalars),
  * for hosts that replay a captured CUDA graph step after step. */
 SMORE_API int smore_shard_reduce_update_rows_dev(float* table, float* m, float* v, const int64_t* uniq,
                                        const int32_t* counts, const int32_t* src, const int32_t* n_unique,
                                        size_t capacity, const float* const* grad_ptrs, const int64_t* ids,
-                                       const int32_t* list_bounds, size_t n_ranks, size_t n_plans,
-                                       const int32_t* plan_caps, size_t width, double lr, double beta1,
-                                       double beta2, double eps, const float* step_scalars, int squeeze,
-                                       void* stream);
+                                       const int32_t* runs, size_t n_lists, size_t width, double lr,
+                                       double beta1, double beta2, double eps, const float* step_scalars,
+                                       int squeeze, void* stream);
 
 #ifdef __cplusplus
 }

@@ -61,13 +61,13 @@ SIGNATURES = {
     "smore_fetch_rows_background": (_int, [_p, _sz, _p, _p, _sz, _sz, _p, _sz, _p]),
     "smore_refresh_rows": (_int, [_p, _p, _sz, _sz, _p, _p, _sz, _sz, _p, _p, _p]),
     "smore_shard_mark_dirty": (_int, [_p, _p, _sz, _sz, _p, _p]),
-    "smore_shard_collect_ids": (_int, [_p, _p, _sz, _sz, ctypes.POINTER(ctypes.c_int32), ctypes.c_int64, _sz, _p, _p,
-                                       _p]),
-    "smore_shard_record_sources": (_int, [_p, _sz, _p, _p]),
-    "smore_shard_reduce_update_rows": (_int, [_p] * 7 + [_sz, _p, _p, _p, _sz, _sz, ctypes.POINTER(ctypes.c_int32),
-                                              _sz, _dbl, _dbl, _dbl, _dbl, ctypes.c_int64, _int, _p]),
-    "smore_shard_reduce_update_rows_dev": (_int, [_p] * 7 + [_sz, _p, _p, _p, _sz, _sz, ctypes.POINTER(ctypes.c_int32),
-                                                  _sz, _dbl, _dbl, _dbl, _dbl, _p, _int, _p]),
+    "smore_shard_owner_plan_workspace_bytes": (_sz, [_sz]),
+    "smore_shard_owner_plan": (_int, [_p, _p, _sz, _sz, ctypes.POINTER(ctypes.c_int32), ctypes.c_int64, _sz, _sz] +
+                               [_p] * 9 + [_sz, _p]),
+    "smore_shard_reduce_update_rows": (_int, [_p] * 7 + [_sz, _p, _p, _p, _sz, _sz, _dbl, _dbl, _dbl, _dbl,
+                                              ctypes.c_int64, _int, _p]),
+    "smore_shard_reduce_update_rows_dev": (_int, [_p] * 7 + [_sz, _p, _p, _p, _sz, _sz, _dbl, _dbl, _dbl, _dbl, _p, _int,
+                                                  _p]),
 }
 
 _lib = None

@@ -28,6 +28,11 @@
 
 namespace smore {
 
+// rows_kernels.cu: sorted unique + inverse map; with n_dev != nullptr only the first *n_dev ids count
+int unique_rows_impl(const int64_t* idx, size_t n, const int32_t* n_dev, size_t n_table_rows, int64_t* uniq,
+                     int32_t* inverse, int32_t* counts, int32_t* n_unique, void* workspace, size_t workspace_bytes,
+                     cudaStream_t st);
+
 constexpr int kMaxPlans = 4;    // id lists a rank may publish per step
 constexpr int kMaxLists = 32;   // ranks x plans; one lane per list in the search below
 
@@ -49,18 +54,6 @@ static int make_caps(const int32_t* plan_caps, size_t n_plans, PlanCaps* out) {
     out->prefix[p + 1] = out->prefix[p] + out->cap[p];
   }
   return SMORE_OK;
-}
-
-__device__ __forceinline__ void decode_position(const PlanCaps& c, int64_t i, int& list, int& j) {
-  const int span = c.prefix[kMaxPlans];
-  const int g = (int)(i / span);
-  const int rem = (int)(i - (int64_t)g * span);
-  int p = 0;
-#pragma unroll
-  for (int q = 1; q < kMaxPlans; ++q)
-    if (q < c.n_plans && rem >= c.prefix[q]) p = q;
-  list = g * c.n_plans + p;
-  j = rem - c.prefix[p];
 }
 
 // staging[u, :] = shard[owner(uniq[u])][local(uniq[u]), :]
@@ -218,6 +211,70 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// The refresh with bulk copies: a warp tests 32 consecutive rows of the step's list against the local
+// bitmap copy, then its lanes move the marked ones concurrently - lane i owns row slot i in shared
+// memory (as in fetch_rows_bulk_kernel) and takes the i-th marked row of the batch.
+__global__ void __launch_bounds__(kBulkFetchWarps * 32)
+    refresh_rows_bulk_kernel(const float* const* __restrict__ shard_ptrs, const uint32_t* __restrict__ dirty_local,
+                             size_t words, size_t rows_per_shard, const int64_t* __restrict__ uniq,
+                             const int32_t* __restrict__ n_unique, unsigned row_bytes, int slots_per_warp,
+                             unsigned char* __restrict__ staging) {
+  extern __shared__ __align__(128) unsigned char fetch_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(fetch_smem);
+  unsigned char* slots = fetch_smem + kBulkFetchWarps * 32 * sizeof(uint64_t);
+  uint64_t* bar = bars + warp * 32 + lane;
+  unsigned char* slot = slots + ((size_t)warp * slots_per_warp + lane) * row_bytes;
+  const bool owns_slot = lane < slots_per_warp;
+  if (owns_slot) bulk::barrier_init(bar, 1);
+  bulk::fence_barrier_init();
+  __syncthreads();
+  const size_t nu = (size_t)max(n_unique[0], 0);
+  const size_t warps = (size_t)gridDim.x * kBulkFetchWarps;
+  unsigned parity = 0;
+  bool gave_up = false;
+  for (size_t u0 = ((size_t)blockIdx.x * kBulkFetchWarps + warp) * 32; u0 < nu && !gave_up; u0 += warps * 32) {
+    bool marked = false;
+    unsigned long long owner = 0, local = 0;
+    if (u0 + lane < nu) {
+      const size_t id = (size_t)uniq[u0 + lane];
+      owner = id / rows_per_shard;
+      local = id - owner * rows_per_shard;
+      marked = (dirty_local[owner * words + (local >> 5)] >> (local & 31)) & 1u;
+    }
+    unsigned todo = __ballot_sync(0xffffffffu, marked);
+    while (todo) {
+      // lane i takes the i-th marked row still to do (if there is one)
+      const int take = owns_slot ? (int)__fns(todo, 0, lane + 1) : -1;     // 0xffffffff -> -1: none
+      const bool work = owns_slot && take >= 0 && take < 32;
+      const int from = work ? take : 0;
+      const unsigned long long o = __shfl_sync(0xffffffffu, owner, from), r = __shfl_sync(0xffffffffu, local, from);
+      if (work) {
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(shard_ptrs[o]) + r * (size_t)row_bytes;
+        bulk::barrier_expect(bar, row_bytes);
+        bulk::load(slot, src, row_bytes, bar);
+      }
+      const bool ok = !work || bulk::barrier_wait(bar, parity);
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) atomicOr(&g_peer_async_status, 1);
+        if (!ok) bulk::barrier_wait(bar, parity);   // let a copy that is still on its way land
+        gave_up = true;
+        break;
+      }
+      if (work) {
+        bulk::store(staging + (u0 + take) * (size_t)row_bytes, slot, row_bytes);
+        bulk::commit_group();
+        bulk::wait_group_read<0>();
+        parity ^= 1u;
+      }
+      // drop the rows just taken: the lowest min(slots_per_warp, popc) set bits
+      const int taken = min(slots_per_warp, __popc(todo));
+      for (int i = 0; i < taken; ++i) todo &= todo - 1;
+    }
+  }
+  bulk::wait_group<0>();
+}
+
 __global__ void __launch_bounds__(256)
     shard_mark_dirty_kernel(const int64_t* __restrict__ uniq, const int32_t* __restrict__ n_unique,
                             uint32_t* __restrict__ dirty) {
@@ -228,58 +285,98 @@ __global__ void __launch_bounds__(256)
   }
 }
 
-__global__ void __launch_bounds__(256)
-    shard_collect_ids_kernel(const int64_t* const* __restrict__ uniq_ptrs,
-                             const int32_t* const* __restrict__ nuniq_ptrs, PlanCaps c, int n_ranks,
-                             int64_t base, int64_t shard_rows, int64_t* __restrict__ out_ids,
-                             int32_t* __restrict__ bounds) {
-  __shared__ int counts_sh[kMaxLists];  // each list's length is read from its owner once per CTA
-  if (threadIdx.x < n_ranks * c.n_plans) counts_sh[threadIdx.x] = nuniq_ptrs[threadIdx.x][0];
-  __syncthreads();
-  const int64_t total = (int64_t)n_ranks * c.prefix[kMaxPlans];
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    int list, j;
-    decode_position(c, i, list, j);
-    int64_t local = -1;
-    const int count = counts_sh[list];
-    if (j < count) {
-      const int64_t* ids = uniq_ptrs[list];
-      const int64_t id = ids[j] - base;
-      if (id >= 0 && id < shard_rows) {
-        local = id;
-        // ids ascend, so the kept entries of a list are one run: only its two ends write the bounds
-        if (j == 0 || ids[j - 1] < base) bounds[2 * list] = j;
-        if (j + 1 == count || ids[j + 1] - base >= shard_rows) bounds[2 * list + 1] = j + 1;
-      }
-    }
-    out_ids[i] = local;
+// ----------------------------------------------------------------------------------------
+// Owner side of the gradient return.
+//
+// Every rank publishes up to n_plans sorted lists of distinct global row ids with one gradient row
+// per id.  Because the lists are sorted and an owner's rows are one contiguous id range, what an
+// owner needs from a list is one contiguous RUN of it, found with two binary searches.  The runs of
+// all lists are copied, as local row ids, into one compact array (run after run, list order), which
+// is then de-duplicated; the compact position of a contribution encodes its list and its index.
+// ----------------------------------------------------------------------------------------
+
+struct OwnerRuns {          // device-resident, written by shard_find_runs_kernel
+  int lo[kMaxLists];        // first index of the run inside its list
+  int start[kMaxLists + 1]; // first compact position of the run; start[n_lists] = total
+};
+
+__device__ __forceinline__ int lower_bound_ids(const int64_t* ids, int n, int64_t key) {
+  int lo = 0, hi = n;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (ids[mid] < key) lo = mid + 1; else hi = mid;
   }
+  return lo;
 }
 
-__global__ void __launch_bounds__(256) shard_init_bounds_kernel(int32_t* bounds, int n_lists) {
-  const int l = blockIdx.x * blockDim.x + threadIdx.x;
+__global__ void __launch_bounds__(32)
+    shard_find_runs_kernel(const int64_t* const* __restrict__ uniq_ptrs, const int32_t* const* __restrict__ nuniq_ptrs,
+                           PlanCaps c, int n_lists, int64_t base, int64_t shard_rows, OwnerRuns* __restrict__ runs,
+                           int32_t* __restrict__ total_out) {
+  const int l = threadIdx.x;
+  int lo = 0, len = 0;
   if (l < n_lists) {
-    bounds[2 * l] = INT_MAX;
-    bounds[2 * l + 1] = 0;
+    const int cap = c.cap[l % c.n_plans];
+    const int count = min(max(nuniq_ptrs[l][0], 0), cap);
+    const int64_t* ids = uniq_ptrs[l];
+    lo = lower_bound_ids(ids, count, base);
+    len = lower_bound_ids(ids, count, base + shard_rows) - lo;
+  }
+  int inc = len;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (l >= o) inc += t;
+  }
+  if (l < n_lists) {
+    runs->lo[l] = lo;
+    runs->start[l] = inc - len;
+  }
+  const int total = __shfl_sync(0xffffffffu, inc, 31);
+  if (l == 0) {
+    runs->start[n_lists] = total;
+    total_out[0] = total;
+  }
+}
+
+// list that holds compact position p (runs are in list order; start[] ascends)
+__device__ __forceinline__ int list_of_position(const int* start, int n_lists, int p) {
+  int l = 0;
+  for (int q = 1; q < n_lists; ++q)
+    if (start[q] <= p) l = q;
+  return l;
+}
+
+__global__ void __launch_bounds__(256)
+    shard_gather_runs_kernel(const int64_t* const* __restrict__ uniq_ptrs, const OwnerRuns* __restrict__ runs,
+                             int n_lists, int64_t base, int64_t* __restrict__ out_ids) {
+  __shared__ int s_lo[kMaxLists], s_start[kMaxLists + 1];
+  if (threadIdx.x < n_lists) s_lo[threadIdx.x] = runs->lo[threadIdx.x];
+  if (threadIdx.x <= n_lists) s_start[threadIdx.x] = runs->start[threadIdx.x];
+  __syncthreads();
+  const int total = s_start[n_lists];
+  for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < total; p += gridDim.x * blockDim.x) {
+    const int l = list_of_position(s_start, n_lists, p);
+    out_ids[p] = uniq_ptrs[l][s_lo[l] + (p - s_start[l])] - base;
   }
 }
 
 __global__ void __launch_bounds__(256)
-    shard_record_sources_kernel(const int32_t* __restrict__ slot, size_t n, int32_t* __restrict__ src) {
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    shard_record_sources_kernel(const int32_t* __restrict__ slot, const int32_t* __restrict__ total,
+                                int32_t* __restrict__ src) {
+  const int n = total[0];
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
     const int32_t s = slot[i];
-    if (s >= 0) src[s] = (int32_t)i;  // any contributor will do; rows with several are searched for
+    if (s >= 0) src[s] = i;  // any contributor will do; rows with several are searched for
   }
 }
 
 struct ReduceArgs {
   const int32_t* counts;            // contributors per distinct row
-  const int32_t* src;               // one contributing position per distinct row
+  const int32_t* src;               // one contributing compact position per distinct row
   const float* const* grad_ptrs;    // [lists] gradient blocks (peer memory)
-  const int64_t* ids;               // collected local ids, [ranks][span]
-  const int32_t* bounds;            // [lists][2] valid range of each list inside its span
-  PlanCaps caps;
+  const int64_t* ids;               // compact array of local row ids (runs in list order)
+  const OwnerRuns* runs;
   int n_lists;
 };
 
@@ -298,14 +395,81 @@ __device__ __forceinline__ void add_row(float4 (&g)[NCH], const float4* row, int
   }
 }
 
+// A row with several contributors: lane l searches run l of the compact id array (ascending inside
+// a run); the contributions are then added in list order, so the sum does not depend on timing.
+template <int NCH>
+__device__ __forceinline__ void add_contributions(float4 (&g)[NCH], const ReduceArgs& r, const int* s_lo,
+                                                  const int* s_start, int64_t row, int lane, int w4) {
+  int found = -1;
+  if (lane < r.n_lists) {
+    int lo = s_start[lane], hi = s_start[lane + 1];
+    const int end = hi;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (r.ids[mid] < row) lo = mid + 1; else hi = mid;
+    }
+    if (lo < end && r.ids[lo] == row) found = s_lo[lane] + (lo - s_start[lane]);
+  }
+  unsigned hits = __ballot_sync(0xffffffffu, found >= 0);
+  while (hits) {
+    const int l = __ffs(hits) - 1;
+    hits &= hits - 1;
+    const int j = __shfl_sync(0xffffffffu, found, l);
+    add_row<NCH>(g, reinterpret_cast<const float4*>(r.grad_ptrs[l]) + (size_t)j * w4, lane, w4);
+  }
+}
+
+template <int NCH, bool ROWWISE>
+__device__ __forceinline__ void adam_row(float4 (&g)[NCH], float4 (&p)[NCH], float4 (&m)[NCH], float4 (&v)[NCH],
+                                         float4* p4, float4* m4, float4* v4, int64_t row, int lane, int w4,
+                                         const UpdateArgs& a) {
+  float denom = 0.f, v_old = 0.f, v_new = 0.f;
+  if (ROWWISE) {
+    v_old = a.v[row];
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j)
+      if (lane + 32 * j < w4) s += g[j].x * g[j].x + g[j].y * g[j].y + g[j].z * g[j].z + g[j].w * g[j].w;
+    const float g2mean = warp_sum(s) / (float)a.width;
+    v_new = v_old * a.beta2 + g2mean * a.omb2;
+    denom = sqrtf(v_new) / a.sqrt_bc2 + a.eps;
+  }
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int d = lane + 32 * j;
+    if (d < w4) {
+      if (ROWWISE) {
+        adam_elem_rowwise(g[j].x, p[j].x, m[j].x, denom, a);
+        adam_elem_rowwise(g[j].y, p[j].y, m[j].y, denom, a);
+        adam_elem_rowwise(g[j].z, p[j].z, m[j].z, denom, a);
+        adam_elem_rowwise(g[j].w, p[j].w, m[j].w, denom, a);
+      } else {
+        adam_elem(g[j].x, p[j].x, m[j].x, v[j].x, a);
+        adam_elem(g[j].y, p[j].y, m[j].y, v[j].y, a);
+        adam_elem(g[j].z, p[j].z, m[j].z, v[j].z, a);
+        adam_elem(g[j].w, p[j].w, m[j].w, v[j].w, a);
+        v4[d] = v[j];
+      }
+      p4[d] = p[j];
+      m4[d] = m[j];
+    }
+  }
+  if (ROWWISE && lane == 0) a.v[row] = v_old + (v_new - v_old);
+}
+
+// Plain form: one warp per row, the gradient row read with ordinary loads.  Kept for rows the ring
+// kernel below does not take (row sizes that are no multiple of 16 bytes or too large for its ring).
 template <int NCH, bool ROWWISE>
 __global__ void __launch_bounds__(256) shard_reduce_update_kernel(UpdateArgs a, ReduceArgs r) {
+  __shared__ int s_lo[kMaxLists], s_start[kMaxLists + 1];
+  if (threadIdx.x < r.n_lists) s_lo[threadIdx.x] = r.runs->lo[threadIdx.x];
+  if (threadIdx.x <= r.n_lists) s_start[threadIdx.x] = r.runs->start[threadIdx.x];
+  __syncthreads();
   load_dyn(a);
   const int lane = threadIdx.x & 31;
   const size_t nu = (size_t)max(a.n_unique[0], 0);
   const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
   const int w4 = (int)(a.width >> 2);
-  const int span = r.caps.prefix[kMaxPlans];
   for (size_t u = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); u < nu; u += warps) {
     const int64_t row = a.uniq[u];
     float4* p4 = reinterpret_cast<float4*>(a.table + (size_t)row * a.width);
@@ -322,67 +486,151 @@ __global__ void __launch_bounds__(256) shard_reduce_update_kernel(UpdateArgs a, 
         if (!ROWWISE) v[j] = v4[d];
       }
     }
-    // ---- pull and sum this row's gradient contributions ----------------------------------------
     if (r.counts[u] == 1) {
-      int list, j;
-      decode_position(r.caps, (int64_t)r.src[u], list, j);
-      add_row<NCH>(g, reinterpret_cast<const float4*>(r.grad_ptrs[list]) + (size_t)j * w4, lane, w4);
+      const int pos = r.src[u];
+      const int l = list_of_position(s_start, r.n_lists, pos);
+      const int j = s_lo[l] + (pos - s_start[l]);
+      add_row<NCH>(g, reinterpret_cast<const float4*>(r.grad_ptrs[l]) + (size_t)j * w4, lane, w4);
     } else {
-      // lane l searches list l (ids ascending inside [lo, hi)); contributions are then added in
-      // list order, so the sum does not depend on timing
-      int found = -1;
-      if (lane < r.n_lists) {
-        const int g_rank = lane / r.caps.n_plans, pl = lane - g_rank * r.caps.n_plans;
-        const int64_t* ids = r.ids + (size_t)g_rank * span + r.caps.prefix[pl];
-        int lo = r.bounds[2 * lane], hi = r.bounds[2 * lane + 1];
-        while (lo < hi) {
-          const int mid = (lo + hi) >> 1;
-          const int64_t x = ids[mid];
-          if (x < row) lo = mid + 1; else hi = mid;
-        }
-        if (lo < r.bounds[2 * lane + 1] && ids[lo] == row) found = lo;
-      }
-      unsigned hits = __ballot_sync(0xffffffffu, found >= 0);
-      while (hits) {
-        const int l = __ffs(hits) - 1;
-        hits &= hits - 1;
-        const int j = __shfl_sync(0xffffffffu, found, l);
-        add_row<NCH>(g, reinterpret_cast<const float4*>(r.grad_ptrs[l]) + (size_t)j * w4, lane, w4);
+      add_contributions<NCH>(g, r, s_lo, s_start, row, lane, w4);
+    }
+    adam_row<NCH, ROWWISE>(g, p, m, v, p4, m4, v4, row, lane, w4, a);
+  }
+}
+
+// Ring form.  The gradient rows cross NVLink; a warp that asks for one row at a time spends most of
+// its time waiting for it.  Here every warp owns a ring of `stages` row slots in shared memory and
+// one mbarrier per slot; lane 0 keeps `stages` bulk asynchronous copies (peer memory -> slot, one
+// instruction per row, untiled, no multicast) in flight ahead of the row the warp is updating, so
+// the bytes in flight per SM depend neither on registers nor on how many warps are resident, while
+// the local rows (parameters, moments) are read with ordinary loads behind them.  A warp takes rows
+// u = w, w + W, w + 2W, ... (W = warps in the grid): consecutive rows of the sorted list come from
+// unrelated requesters, so the copies in flight are spread over all peers.  Rows with several
+// contributors (a few per cent) are not copied into the ring: they are searched for and read with
+// ordinary loads, in list order.  Every wait is bounded; a wait that runs out sets the status word
+// (kStatusPeerWait) and the warp stops.
+constexpr int kRingWarps = 8;
+
+template <int NCH, bool ROWWISE>
+__global__ void __launch_bounds__(kRingWarps * 32, 2)
+    shard_reduce_update_ring_kernel(UpdateArgs a, ReduceArgs r, int stages) {
+  extern __shared__ __align__(128) unsigned char ring_smem[];
+  __shared__ int s_lo[kMaxLists], s_start[kMaxLists + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x < r.n_lists) s_lo[threadIdx.x] = r.runs->lo[threadIdx.x];
+  if (threadIdx.x <= r.n_lists) s_start[threadIdx.x] = r.runs->start[threadIdx.x];
+  const int w4 = (int)(a.width >> 2);
+  const unsigned row_bytes = (unsigned)w4 * 16u;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring_smem) + warp * stages;
+  const size_t ring_off = ((size_t)kRingWarps * stages * sizeof(uint64_t) + 127) & ~(size_t)127;
+  unsigned char* ring = ring_smem + ring_off + (size_t)warp * stages * row_bytes;
+  if (lane == 0) {
+    for (int s = 0; s < stages; ++s) bulk::barrier_init(bars + s, 1);
+    bulk::fence_barrier_init();
+  }
+  __syncthreads();
+  load_dyn(a);
+  const long long nu = max(a.n_unique[0], 0);
+  const long long W = (long long)gridDim.x * kRingWarps;
+  const long long w = (long long)blockIdx.x * kRingWarps + warp;
+  const int n_k = nu > w ? (int)((nu - w + W - 1) / W) : 0;   // rows of this warp
+
+  // per-lane scalars of a batch of 32 of the warp's rows: local row, where its (single) gradient row
+  // lives, or nullptr when the row has several contributors
+  struct Meta {
+    long long row;
+    const unsigned char* src;
+  };
+  auto load_meta = [&](int first_k) {
+    Meta mt{0, nullptr};
+    const int k = first_k + lane;
+    if (k < n_k) {
+      const long long u = w + (long long)k * W;
+      mt.row = a.uniq[u];
+      if (r.counts[u] == 1) {
+        const int pos = r.src[u];
+        const int l = list_of_position(s_start, r.n_lists, pos);
+        const int j = s_lo[l] + (pos - s_start[l]);
+        mt.src = reinterpret_cast<const unsigned char*>(r.grad_ptrs[l]) + (size_t)j * row_bytes;
       }
     }
-    // ---- Adam on the local row -----------------------------------------------------------------
-    float denom = 0.f, v_old = 0.f, v_new = 0.f;
-    if (ROWWISE) {
-      v_old = a.v[row];
-      float s = 0.f;
-#pragma unroll
-      for (int j = 0; j < NCH; ++j)
-        if (lane + 32 * j < w4) s += g[j].x * g[j].x + g[j].y * g[j].y + g[j].z * g[j].z + g[j].w * g[j].w;
-      const float g2mean = warp_sum(s) / (float)a.width;
-      v_new = v_old * a.beta2 + g2mean * a.omb2;
-      denom = sqrtf(v_new) / a.sqrt_bc2 + a.eps;
+    return mt;
+  };
+  Meta cur = load_meta(0), nxt = cur;
+  unsigned phase_bits = 0;   // parity each slot's barrier will complete next
+  unsigned armed_bits = 0;   // slots with a copy in flight
+  const int ahead = min(stages, n_k);
+  for (int k = 0; k < ahead; ++k) {
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(
+        __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(cur.src), k));
+    if (src != nullptr) {
+      if (lane == 0) {
+        bulk::barrier_expect(bars + k, row_bytes);
+        bulk::load(ring + (size_t)k * row_bytes, src, row_bytes, bars + k);
+      }
+      armed_bits |= 1u << k;
     }
+  }
+  int slot = 0;
+  for (int k = 0; k < n_k; ++k) {
+    const int tl = k & 31;
+    if (tl == 0) nxt = load_meta(k + 32);
+    const long long row = __shfl_sync(0xffffffffu, cur.row, tl);
+    const bool single = (armed_bits >> slot) & 1u;
+    float4* p4 = reinterpret_cast<float4*>(a.table + (size_t)row * a.width);
+    float4* m4 = reinterpret_cast<float4*>(a.m + (size_t)row * a.width);
+    float4* v4 = ROWWISE ? nullptr : reinterpret_cast<float4*>(a.v + (size_t)row * a.width);
+    float4 g[NCH], p[NCH], m[NCH], v[NCH];
 #pragma unroll
     for (int j = 0; j < NCH; ++j) {
       const int d = lane + 32 * j;
+      g[j] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (d < w4) {
-        if (ROWWISE) {
-          adam_elem_rowwise(g[j].x, p[j].x, m[j].x, denom, a);
-          adam_elem_rowwise(g[j].y, p[j].y, m[j].y, denom, a);
-          adam_elem_rowwise(g[j].z, p[j].z, m[j].z, denom, a);
-          adam_elem_rowwise(g[j].w, p[j].w, m[j].w, denom, a);
-        } else {
-          adam_elem(g[j].x, p[j].x, m[j].x, v[j].x, a);
-          adam_elem(g[j].y, p[j].y, m[j].y, v[j].y, a);
-          adam_elem(g[j].z, p[j].z, m[j].z, v[j].z, a);
-          adam_elem(g[j].w, p[j].w, m[j].w, v[j].w, a);
-          v4[d] = v[j];
-        }
-        p4[d] = p[j];
-        m4[d] = m[j];
+        p[j] = p4[d];
+        m[j] = m4[d];
+        if (!ROWWISE) v[j] = v4[d];
       }
     }
-    if (ROWWISE && lane == 0) a.v[row] = v_old + (v_new - v_old);
+    if (single) {
+      bool ok = bulk::barrier_wait(bars + slot, (phase_bits >> slot) & 1u);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        // give up: flag it, let the other copies in flight land (bounded waits), stop
+        if (lane == 0) atomicOr(&g_peer_async_status, 1);
+        armed_bits &= ~(1u << slot);
+        for (int s2 = 0; s2 < stages; ++s2)
+          if ((armed_bits >> s2) & 1u) bulk::barrier_wait(bars + s2, (phase_bits >> s2) & 1u);
+        break;
+      }
+      phase_bits ^= 1u << slot;
+      armed_bits &= ~(1u << slot);
+      const float4* row4 = reinterpret_cast<const float4*>(ring + (size_t)slot * row_bytes);
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const int d = lane + 32 * j;
+        if (d < w4) g[j] = row4[d];
+      }
+    } else {
+      add_contributions<NCH>(g, r, s_lo, s_start, row, lane, w4);
+    }
+    // every lane has taken its pieces of the slot: it may be refilled with the row `stages` ahead
+    __syncwarp();
+    const int kn = k + stages;
+    if (kn < n_k) {
+      const unsigned long long nsrc_bits = __shfl_sync(
+          0xffffffffu, reinterpret_cast<unsigned long long>((kn >> 5) == (k >> 5) ? cur.src : nxt.src), kn & 31);
+      const unsigned char* nsrc = reinterpret_cast<const unsigned char*>(nsrc_bits);
+      if (nsrc != nullptr) {
+        if (lane == 0) {
+          bulk::barrier_expect(bars + slot, row_bytes);
+          bulk::load(ring + (size_t)slot * row_bytes, nsrc, row_bytes, bars + slot);
+        }
+        armed_bits |= 1u << slot;
+      }
+    }
+    adam_row<NCH, ROWWISE>(g, p, m, v, p4, m4, v4, row, lane, w4, a);
+    if (tl == 31) cur = nxt;
+    if (++slot == stages) slot = 0;
   }
 }
 
@@ -477,6 +725,19 @@ int smore_refresh_rows(const float* const* shard_ptrs, const uint32_t* const* di
   const size_t words = (rows_per_shard + 31) / 32;
   cudaStream_t st = (cudaStream_t)stream;
   pull_bitmaps_kernel<<<grid_threads(n_ranks * words), 256, 0, st>>>(dirty_ptrs, (int)n_ranks, words, bitmap_scratch);
+  const size_t row_bytes = width * sizeof(float);
+  if (row_bytes <= 20 * 1024) {
+    // marked rows move with bulk copies, several per warp at a time (about 20 KB of slots per warp)
+    const int slots = (int)std::min<size_t>(32, std::max<size_t>(1, 20 * 1024 / row_bytes));
+    const size_t smem = kBulkFetchWarps * 32 * sizeof(uint64_t) + (size_t)kBulkFetchWarps * slots * row_bytes;
+    if (int rc = allow_large_smem(refresh_rows_bulk_kernel, 48 * 1024, false)) return rc;
+    const size_t want = (capacity + (size_t)kBulkFetchWarps * 32 - 1) / ((size_t)kBulkFetchWarps * 32);
+    const unsigned grid = (unsigned)std::max<size_t>(1, std::min<size_t>(want, (size_t)sm_count() * 8));
+    refresh_rows_bulk_kernel<<<grid, kBulkFetchWarps * 32, smem, st>>>(
+        shard_ptrs, bitmap_scratch, words, rows_per_shard, uniq, n_unique, (unsigned)row_bytes, slots,
+        reinterpret_cast<unsigned char*>(staging));
+    return check_launch("refresh_rows kernels", 2);
+  }
   refresh_rows_kernel<<<grid_warps(capacity), 256, 0, st>>>(shard_ptrs, bitmap_scratch, words, rows_per_shard, uniq,
                                                             n_unique, (int)(width >> 2),
                                                             reinterpret_cast<float4*>(staging));
@@ -494,56 +755,99 @@ int smore_shard_mark_dirty(const int64_t* uniq, const int32_t* n_unique, size_t 
   return check_launch("shard_mark_dirty_kernel", capacity ? 1 : 0);
 }
 
-int smore_shard_collect_ids(const int64_t* const* uniq_ptrs, const int32_t* const* nuniq_ptrs, size_t n_ranks,
-                            size_t n_plans, const int32_t* plan_caps, int64_t base, size_t shard_rows,
-                            int64_t* out_ids, int32_t* list_bounds, void* stream) {
-  if (!uniq_ptrs || !nuniq_ptrs || !out_ids || !list_bounds) return fail(SMORE_ERR_NULL, "shard_collect_ids: NULL pointer");
+size_t smore_shard_owner_plan_workspace_bytes(size_t shard_rows) {
+  return 256 + smore_unique_rows_workspace_bytes(shard_rows ? shard_rows : 1);
+}
+
+int smore_shard_owner_plan(const int64_t* const* uniq_ptrs, const int32_t* const* nuniq_ptrs, size_t n_ranks,
+                           size_t n_plans, const int32_t* plan_caps, int64_t base, size_t shard_rows,
+                           size_t capacity, int64_t* ids, int32_t* runs, int64_t* uniq, int32_t* slot,
+                           int32_t* counts, int32_t* src, int32_t* n_unique, uint32_t* dirty, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+  if (!uniq_ptrs || !nuniq_ptrs || !ids || !runs || !uniq || !slot || !counts || !src || !n_unique || !workspace)
+    return fail(SMORE_ERR_NULL, "shard_owner_plan: NULL pointer");
   PlanCaps c;
   if (int rc = make_caps(plan_caps, n_plans, &c)) return rc;
   if (n_ranks == 0 || n_ranks * n_plans > (size_t)kMaxLists)
     return fail(SMORE_ERR_BAD_SHAPE, "ranks x plans must be 1..%d", kMaxLists);
-  const size_t total = n_ranks * (size_t)c.prefix[kMaxPlans];
-  if (total > (size_t)INT_MAX) return fail(SMORE_ERR_TOO_LARGE, "shard_collect_ids: more than 2^31-1 positions");
+  if (shard_rows == 0) return fail(SMORE_ERR_BAD_SHAPE, "shard_owner_plan: shard_rows is 0");
+  const size_t worst = n_ranks * (size_t)c.prefix[kMaxPlans];
+  if (worst > (size_t)INT_MAX) return fail(SMORE_ERR_TOO_LARGE, "shard_owner_plan: more than 2^31-1 positions");
+  if (capacity < worst)
+    return fail(SMORE_ERR_BAD_SHAPE, "shard_owner_plan: capacity %zu, but the lists can hold %zu ids", capacity, worst);
+  if (workspace_bytes < smore_shard_owner_plan_workspace_bytes(shard_rows) || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+    return fail(SMORE_ERR_WORKSPACE, "shard_owner_plan: workspace too small or not 256-byte aligned");
+  static_assert(sizeof(OwnerRuns) <= SMORE_SHARD_RUNS_INTS * sizeof(int32_t), "runs buffer size");
   cudaStream_t st = (cudaStream_t)stream;
-  shard_init_bounds_kernel<<<1, 256, 0, st>>>(list_bounds, (int)(n_ranks * n_plans));
-  if (total)
-    shard_collect_ids_kernel<<<grid_threads(total), 256, 0, st>>>(uniq_ptrs, nuniq_ptrs, c, (int)n_ranks, base,
-                                                                  (int64_t)shard_rows, out_ids, list_bounds);
-  return check_launch("shard_collect_ids kernels", 2);
-}
-
-int smore_shard_record_sources(const int32_t* slot, size_t n, int32_t* src, void* stream) {
-  if (n == 0) return SMORE_OK;
-  if (!slot || !src) return fail(SMORE_ERR_NULL, "shard_record_sources: NULL pointer");
-  shard_record_sources_kernel<<<grid_threads(n), 256, 0, (cudaStream_t)stream>>>(slot, n, src);
-  return check_launch("shard_record_sources_kernel");
+  const int n_lists = (int)(n_ranks * n_plans);
+  OwnerRuns* r = reinterpret_cast<OwnerRuns*>(runs);
+  int32_t* total = reinterpret_cast<int32_t*>(workspace);            // device count of collected ids
+  void* uws = static_cast<unsigned char*>(workspace) + 256;
+  shard_find_runs_kernel<<<1, 32, 0, st>>>(uniq_ptrs, nuniq_ptrs, c, n_lists, base, (int64_t)shard_rows, r, total);
+  // the collected ids are expected to be about 1 / n_ranks of the worst case; the kernels below loop
+  // over the device-side total, so the grids only have to be large enough to fill the GPU
+  const size_t expect = std::max<size_t>(worst / n_ranks, 1);
+  shard_gather_runs_kernel<<<grid_threads(expect), 256, 0, st>>>(uniq_ptrs, r, n_lists, base, ids);
+  count_launches(2);
+  if (int rc = unique_rows_impl(ids, worst, total, shard_rows, uniq, slot, counts, n_unique, uws,
+                                workspace_bytes - 256, st))
+    return rc;
+  shard_record_sources_kernel<<<grid_threads(expect), 256, 0, st>>>(slot, total, src);
+  count_launches(1);
+  if (dirty != nullptr) {
+    // publish which rows this step updates (readers: the next step's refresh on every rank)
+    if (cudaMemsetAsync(dirty, 0, ((shard_rows + 31) / 32) * sizeof(uint32_t), st) != cudaSuccess)
+      return fail(SMORE_ERR_CUDA, "shard_owner_plan: cudaMemsetAsync failed");
+    shard_mark_dirty_kernel<<<grid_threads(expect), 256, 0, st>>>(uniq, n_unique, dirty);
+    count_launches(1);
+  }
+  return check_launch("shard_owner_plan kernels", 0);
 }
 
 static int shard_reduce_update_impl(float* table, float* m, float* v, const int64_t* uniq, const int32_t* counts,
                                    const int32_t* src, const int32_t* n_unique, size_t capacity,
-                                   const float* const* grad_ptrs, const int64_t* ids, const int32_t* list_bounds,
-                                   size_t n_ranks, size_t n_plans, const int32_t* plan_caps, size_t width,
-                                   double lr, double beta1, double beta2, double eps, int64_t step,
-                                   const float* step_scalars, int squeeze, void* stream) {
+                                   const float* const* grad_ptrs, const int64_t* ids, const int32_t* runs,
+                                   size_t n_lists, size_t width, double lr, double beta1, double beta2, double eps,
+                                   int64_t step, const float* step_scalars, int squeeze, void* stream) {
   if (capacity == 0) return SMORE_OK;
-  if (!table || !m || !v || !uniq || !counts || !src || !n_unique || !grad_ptrs || !ids || !list_bounds)
+  if (!table || !m || !v || !uniq || !counts || !src || !n_unique || !grad_ptrs || !ids || !runs)
     return fail(SMORE_ERR_NULL, "shard_reduce_update_rows: NULL pointer");
   if (!step_scalars && step < 1) return fail(SMORE_ERR_BAD_SHAPE, "adam step must be >= 1");
   if (width == 0 || (width & 3) || width > 1024 || !aligned16(table) || !aligned16(m) || (!squeeze && !aligned16(v)))
     return fail(SMORE_ERR_BAD_SHAPE, "shard_reduce_update_rows: width must be a multiple of 4 floats, at most 1024");
-  ReduceArgs r;
-  if (int rc = make_caps(plan_caps, n_plans, &r.caps)) return rc;
-  if (n_ranks == 0 || n_ranks * n_plans > (size_t)kMaxLists)
+  if (n_lists == 0 || n_lists > (size_t)kMaxLists)
     return fail(SMORE_ERR_BAD_SHAPE, "ranks x plans must be 1..%d", kMaxLists);
-  r.counts = counts; r.src = src; r.grad_ptrs = grad_ptrs; r.ids = ids; r.bounds = list_bounds;
-  r.n_lists = (int)(n_ranks * n_plans);
+  ReduceArgs r;
+  r.counts = counts; r.src = src; r.grad_ptrs = grad_ptrs; r.ids = ids;
+  r.runs = reinterpret_cast<const OwnerRuns*>(runs);
+  r.n_lists = (int)n_lists;
   UpdateArgs a;
   a.table = table; a.m = m; a.v = v; a.uniq = uniq; a.g_rows = nullptr; a.n_unique = n_unique; a.width = width;
   set_hyper(a, lr, beta1, beta2, eps, step_scalars ? 1 : step, squeeze);
   a.dyn = step_scalars;
   cudaStream_t st = (cudaStream_t)stream;
-  const int grid = grid_warps(capacity);
   const size_t w4 = width >> 2;
+  // the ring form: 2..8 row slots per warp, about 6 KB of remote rows in flight per warp
+  const size_t row_bytes = width * sizeof(float);
+  const int stages = (int)std::min<size_t>(8, std::max<size_t>(2, 6400 / row_bytes));
+  const size_t ring_smem = (((size_t)kRingWarps * stages * sizeof(uint64_t) + 127) & ~(size_t)127) +
+                           (size_t)kRingWarps * stages * row_bytes;
+  if (w4 > 32 && ring_smem <= 100 * 1024) {
+    const int grid = (int)std::max<size_t>(1, std::min<size_t>((capacity + kRingWarps - 1) / kRingWarps,
+                                                               (size_t)sm_count() * 2));
+#define RING(NCH)                                                                                            \
+  {                                                                                                          \
+    auto kern = a.squeeze ? shard_reduce_update_ring_kernel<NCH, true> : shard_reduce_update_ring_kernel<NCH, false>; \
+    if (int rc = allow_large_smem(kern, 100 * 1024)) return rc;                                              \
+    kern<<<grid, kRingWarps * 32, ring_smem, st>>>(a, r, stages);                                            \
+  }
+    if (w4 <= 64) RING(2)
+    else if (w4 <= 128) RING(4)
+    else RING(8)
+#undef RING
+    return check_launch("shard_reduce_update_ring_kernel");
+  }
+  const int grid = grid_warps(capacity);
 #define REDUCE(NCH)                                                                \
   if (a.squeeze) shard_reduce_update_kernel<NCH, true><<<grid, 256, 0, st>>>(a, r); \
   else shard_reduce_update_kernel<NCH, false><<<grid, 256, 0, st>>>(a, r)
@@ -557,25 +861,21 @@ static int shard_reduce_update_impl(float* table, float* m, float* v, const int6
 
 int smore_shard_reduce_update_rows(float* table, float* m, float* v, const int64_t* uniq, const int32_t* counts,
                                    const int32_t* src, const int32_t* n_unique, size_t capacity,
-                                   const float* const* grad_ptrs, const int64_t* ids, const int32_t* list_bounds,
-                                   size_t n_ranks, size_t n_plans, const int32_t* plan_caps, size_t width,
-                                   double lr, double beta1, double beta2, double eps, int64_t step, int squeeze,
-                                   void* stream) {
-  return shard_reduce_update_impl(table, m, v, uniq, counts, src, n_unique, capacity, grad_ptrs, ids, list_bounds,
-                                  n_ranks, n_plans, plan_caps, width, lr, beta1, beta2, eps, step, nullptr, squeeze,
-                                  stream);
+                                   const float* const* grad_ptrs, const int64_t* ids, const int32_t* runs,
+                                   size_t n_lists, size_t width, double lr, double beta1, double beta2, double eps,
+                                   int64_t step, int squeeze, void* stream) {
+  return shard_reduce_update_impl(table, m, v, uniq, counts, src, n_unique, capacity, grad_ptrs, ids, runs, n_lists,
+                                  width, lr, beta1, beta2, eps, step, nullptr, squeeze, stream);
 }
 
 int smore_shard_reduce_update_rows_dev(float* table, float* m, float* v, const int64_t* uniq, const int32_t* counts,
                                        const int32_t* src, const int32_t* n_unique, size_t capacity,
-                                       const float* const* grad_ptrs, const int64_t* ids,
-                                       const int32_t* list_bounds, size_t n_ranks, size_t n_plans,
-                                       const int32_t* plan_caps, size_t width, double lr, double beta1, double beta2,
+                                       const float* const* grad_ptrs, const int64_t* ids, const int32_t* runs,
+                                       size_t n_lists, size_t width, double lr, double beta1, double beta2,
                                        double eps, const float* step_scalars, int squeeze, void* stream) {
   if (!step_scalars) return fail(SMORE_ERR_NULL, "shard_reduce_update_rows_dev: step_scalars is NULL");
-  return shard_reduce_update_impl(table, m, v, uniq, counts, src, n_unique, capacity, grad_ptrs, ids, list_bounds,
-                                  n_ranks, n_plans, plan_caps, width, lr, beta1, beta2, eps, 1, step_scalars, squeeze,
-                                  stream);
+  return shard_reduce_update_impl(table, m, v, uniq, counts, src, n_unique, capacity, grad_ptrs, ids, runs, n_lists,
+                                  width, lr, beta1, beta2, eps, 1, step_scalars, squeeze, stream);
 }
 
 }  // extern "C"

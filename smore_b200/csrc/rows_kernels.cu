@@ -83,8 +83,9 @@ static UniqueWorkspace carve_unique_workspace(void* base, size_t n_table_rows) {
 }
 
 __global__ void __launch_bounds__(256)
-    unique_mark_kernel(const int64_t* __restrict__ idx, size_t n, size_t n_table_rows,
-                       uint32_t* __restrict__ bitmap, int32_t* __restrict__ n_unique) {
+    unique_mark_kernel(const int64_t* __restrict__ idx, size_t n, const int32_t* __restrict__ n_dev,
+                       size_t n_table_rows, uint32_t* __restrict__ bitmap, int32_t* __restrict__ n_unique) {
+  if (n_dev != nullptr) n = min(n, (size_t)max(n_dev[0], 0));   // the caller's count lives on the device
   for (size_t p = (size_t)blockIdx.x * blockDim.x + threadIdx.x; p < n;
        p += (size_t)gridDim.x * blockDim.x) {
     const int64_t v = idx[p];
@@ -196,10 +197,11 @@ __global__ void __launch_bounds__(kScanThreads)
 }
 
 __global__ void __launch_bounds__(256)
-    unique_assign_kernel(const int64_t* __restrict__ idx, size_t n, size_t n_table_rows,
-                         const uint32_t* __restrict__ bitmap, const uint32_t* __restrict__ wordprefix,
-                         int64_t* __restrict__ uniq, int32_t* __restrict__ inverse,
-                         int32_t* __restrict__ counts) {
+    unique_assign_kernel(const int64_t* __restrict__ idx, size_t n, const int32_t* __restrict__ n_dev,
+                         size_t n_table_rows, const uint32_t* __restrict__ bitmap,
+                         const uint32_t* __restrict__ wordprefix, int64_t* __restrict__ uniq,
+                         int32_t* __restrict__ inverse, int32_t* __restrict__ counts) {
+  if (n_dev != nullptr) n = min(n, (size_t)max(n_dev[0], 0));
   for (size_t p = (size_t)blockIdx.x * blockDim.x + threadIdx.x; p < n;
        p += (size_t)gridDim.x * blockDim.x) {
     const int64_t v = idx[p];
@@ -212,6 +214,108 @@ __global__ void __launch_bounds__(256)
     const int32_t s = (int32_t)(wordprefix[v >> 5] + __popc(below));
     inverse[p] = s;
     if (atomicAdd(counts + s, 1) == 0) uniq[s] = v;
+  }
+}
+
+
+// ----------------------------------------------------------------------------------------
+// sorted unique of a SHORT id list (a step's anchor lookups: about a thousand ids) over a LARGE id
+// space: the bitmap route costs O(n_table_rows / 32) whatever n is (0.3 ms for 86M rows), a sort of
+// n keys in one CTA's shared memory does not.  Same results: ascending distinct ids, inverse map,
+// multiplicities, counters.
+// ----------------------------------------------------------------------------------------
+
+constexpr int kSmallUniqueMax = 4096;      // ids per call on this route
+constexpr int kSmallUniqueThreads = 1024;
+constexpr int kSmallPosBits = 12;          // position within the call, packed below the id
+constexpr unsigned long long kSmallInvalid = ~0ull;
+
+__global__ void __launch_bounds__(kSmallUniqueThreads)
+    unique_small_kernel(const int64_t* __restrict__ idx, int n, size_t n_table_rows, int P,
+                        int64_t* __restrict__ uniq, int32_t* __restrict__ inverse, int32_t* __restrict__ counts,
+                        int32_t* __restrict__ n_unique) {
+  extern __shared__ unsigned long long keys[];   // [P], P = power of two >= n
+  __shared__ int warp_tot[kSmallUniqueThreads / 32];
+  __shared__ int n_bad_sh;
+  const int tid = threadIdx.x;
+  if (tid == 0) n_bad_sh = 0;
+  __syncthreads();
+  int bad = 0;
+  for (int i = tid; i < P; i += kSmallUniqueThreads) {
+    unsigned long long k = kSmallInvalid;
+    if (i < n) {
+      const int64_t v = idx[i];
+      if (v >= 0 && (size_t)v < n_table_rows) k = ((unsigned long long)v << kSmallPosBits) | (unsigned)i;
+      else ++bad;
+      counts[i] = 0;
+    }
+    keys[i] = k;
+  }
+  if (bad) atomicAdd(&n_bad_sh, bad);
+  // bitonic sort, ascending
+  for (int size = 2; size <= P; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      __syncthreads();
+      for (int t = tid; t < (P >> 1); t += kSmallUniqueThreads) {
+        const int lo = 2 * t - (t & (stride - 1));
+        const int hi = lo + stride;
+        const bool up = (lo & size) == 0;
+        const unsigned long long a = keys[lo], b = keys[hi];
+        if ((a > b) == up) {
+          keys[lo] = b;
+          keys[hi] = a;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // heads of runs of equal ids -> slots: every thread owns P / 1024 consecutive sorted positions
+  const int per = (P + kSmallUniqueThreads - 1) / kSmallUniqueThreads;
+  const int i0 = tid * per;
+  int heads = 0;
+  for (int i = i0; i < min(i0 + per, P); ++i) {
+    const unsigned long long k = keys[i];
+    if (k != kSmallInvalid && (i == 0 || (keys[i - 1] >> kSmallPosBits) != (k >> kSmallPosBits))) ++heads;
+  }
+  int inc = heads;
+  const int lane = tid & 31, warp = tid >> 5;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (lane == 31) warp_tot[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int w = warp_tot[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += t;
+    }
+    warp_tot[lane] = w;
+  }
+  __syncthreads();
+  int slot = (warp ? warp_tot[warp - 1] : 0) + inc - heads - 1;   // slot of the last head before i0
+  for (int i = i0; i < min(i0 + per, P); ++i) {
+    const unsigned long long k = keys[i];
+    if (k == kSmallInvalid) break;                                  // invalid keys sort last
+    const int64_t id = (int64_t)(k >> kSmallPosBits);
+    if (i == 0 || (keys[i - 1] >> kSmallPosBits) != (k >> kSmallPosBits)) {
+      ++slot;
+      uniq[slot] = id;
+    }
+    inverse[(int)(k & ((1u << kSmallPosBits) - 1u))] = slot;
+    atomicAdd(counts + slot, 1);
+  }
+  // positions whose id was out of range
+  for (int i = tid; i < n; i += kSmallUniqueThreads) {
+    const int64_t v = idx[i];
+    if (v < 0 || (size_t)v >= n_table_rows) inverse[i] = -1;
+  }
+  if (tid == 0) {
+    n_unique[0] = warp_tot[31];
+    n_unique[1] = n_bad_sh;
   }
 }
 
@@ -524,9 +628,14 @@ size_t smore_unique_rows_workspace_bytes(size_t n_table_rows) {
   return carve_unique_workspace(nullptr, n_table_rows).bytes;
 }
 
-int smore_unique_rows(const int64_t* idx, size_t n, size_t n_table_rows, int64_t* uniq, int32_t* inverse,
-                      int32_t* counts, int32_t* n_unique, void* workspace, size_t workspace_bytes,
-                      void* stream) {
+}  // extern "C"
+
+namespace smore {
+// Shared by smore_unique_rows and the owner side of the sharded update (peer_kernels.cu), whose number
+// of ids is only known on the device: with n_dev != nullptr the first min(n, *n_dev) ids count.
+int unique_rows_impl(const int64_t* idx, size_t n, const int32_t* n_dev, size_t n_table_rows, int64_t* uniq,
+                     int32_t* inverse, int32_t* counts, int32_t* n_unique, void* workspace, size_t workspace_bytes,
+                     cudaStream_t st) {
   if (!n_unique) return fail(SMORE_ERR_NULL, "unique_rows: n_unique is NULL");
   if (n && (!idx || !uniq || !inverse || !counts)) return fail(SMORE_ERR_NULL, "unique_rows: NULL pointer");
   if (n_table_rows == 0 || n_table_rows > ((size_t)1 << 36))
@@ -538,21 +647,38 @@ int smore_unique_rows(const int64_t* idx, size_t n, size_t n_table_rows, int64_t
   if (workspace_bytes < w.bytes)
     return fail(SMORE_ERR_WORKSPACE, "unique_rows: workspace has %zu bytes, %zu needed", workspace_bytes,
                 w.bytes);
-  cudaStream_t st = (cudaStream_t)stream;
+  if (n_dev == nullptr && n > 0 && n <= (size_t)kSmallUniqueMax && n_table_rows >= ((size_t)1 << 18)) {
+    // few ids over a large id space: sort them in one CTA instead of scanning a bitmap of the space
+    int P = 32;
+    while ((size_t)P < n) P <<= 1;
+    unique_small_kernel<<<1, kSmallUniqueThreads, (size_t)P * sizeof(unsigned long long), st>>>(
+        idx, (int)n, n_table_rows, P, uniq, inverse, counts, n_unique);
+    return check_launch("unique_small_kernel");
+  }
   if (cudaMemsetAsync(n_unique, 0, 2 * sizeof(int32_t), st) != cudaSuccess)
     return fail(SMORE_ERR_CUDA, "unique_rows: cudaMemsetAsync failed");
   if (n == 0) return check_launch("unique_rows memset", 0);
   if (cudaMemsetAsync(w.bitmap, 0, w.nwords * sizeof(uint32_t), st) != cudaSuccess ||
       cudaMemsetAsync(counts, 0, n * sizeof(int32_t), st) != cudaSuccess)
     return fail(SMORE_ERR_CUDA, "unique_rows: cudaMemsetAsync failed");
-  unique_mark_kernel<<<thread_grid(n), 256, 0, st>>>(idx, n, n_table_rows, w.bitmap, n_unique);
+  unique_mark_kernel<<<thread_grid(n), 256, 0, st>>>(idx, n, n_dev, n_table_rows, w.bitmap, n_unique);
   unique_blocksum_kernel<<<(unsigned)w.nblocks, kScanThreads, 0, st>>>(w.bitmap, w.nwords, w.blocksum);
   unique_scan_blocks_kernel<<<1, 1024, 0, st>>>(w.blocksum, w.nblocks, n_unique);
   unique_wordprefix_kernel<<<(unsigned)w.nblocks, kScanThreads, 0, st>>>(w.bitmap, w.nwords, w.blocksum,
                                                                          w.wordprefix);
-  unique_assign_kernel<<<thread_grid(n), 256, 0, st>>>(idx, n, n_table_rows, w.bitmap, w.wordprefix, uniq,
+  unique_assign_kernel<<<thread_grid(n), 256, 0, st>>>(idx, n, n_dev, n_table_rows, w.bitmap, w.wordprefix, uniq,
                                                         inverse, counts);
   return check_launch("unique_rows kernels", 5);
+}
+}  // namespace smore
+
+extern "C" {
+
+int smore_unique_rows(const int64_t* idx, size_t n, size_t n_table_rows, int64_t* uniq, int32_t* inverse,
+                      int32_t* counts, int32_t* n_unique, void* workspace, size_t workspace_bytes,
+                      void* stream) {
+  return unique_rows_impl(idx, n, nullptr, n_table_rows, uniq, inverse, counts, n_unique, workspace, workspace_bytes,
+                          (cudaStream_t)stream);
 }
 
 int smore_zero_shared_rows(float* g_rows, const int32_t* slot_count, const int32_t* n_unique, size_t capacity,
@@ -742,12 +868,12 @@ extern "C" int smore_unique_rows_static(const int64_t* idx, size_t n, size_t n_t
   if (cudaMemsetAsync(w.bitmap, 0, w.nwords * sizeof(uint32_t), st) != cudaSuccess ||
       cudaMemsetAsync(counts, 0, n * sizeof(int32_t), st) != cudaSuccess)
     return fail(SMORE_ERR_CUDA, "unique_rows_static: cudaMemsetAsync failed");
-  unique_mark_kernel<<<thread_grid(n), 256, 0, st>>>(idx, n, n_table_rows, w.bitmap, n_unique);
+  unique_mark_kernel<<<thread_grid(n), 256, 0, st>>>(idx, n, nullptr, n_table_rows, w.bitmap, n_unique);
   unique_blocksum_kernel<<<(unsigned)w.nblocks, kScanThreads, 0, st>>>(w.bitmap, w.nwords, w.blocksum);
   unique_scan_blocks_kernel<<<1, 1024, 0, st>>>(w.blocksum, w.nblocks, n_unique);
   unique_wordprefix_kernel<<<(unsigned)w.nblocks, kScanThreads, 0, st>>>(w.bitmap, w.nwords, w.blocksum,
                                                                          w.wordprefix);
-  unique_assign_kernel<<<thread_grid(n), 256, 0, st>>>(idx, n, n_table_rows, w.bitmap, w.wordprefix, uniq,
+  unique_assign_kernel<<<thread_grid(n), 256, 0, st>>>(idx, n, nullptr, n_table_rows, w.bitmap, w.wordprefix, uniq,
                                                         inverse, counts);
   return check_launch("unique_rows_static kernels", 5);
 }

@@ -13,9 +13,11 @@ happens here over NVLink with plain peer loads, synchronously per step:
   backward  row gradients accumulate in the rank's compact buffer, which lives in peer-visible
             memory together with the sorted id list.
   update    after a stream-ordered barrier every owner collects the ids of its range from all
-            ranks' lists, de-duplicates them, and one kernel pulls the matching gradient rows,
-            sums them in a fixed order and applies Adam to the shard
-            (smore_shard_reduce_update_rows); a second barrier ends the step.
+            ranks' lists (one contiguous run per sorted list), de-duplicates them
+            (smore_shard_owner_plan), and one kernel pulls the matching gradient rows with bulk
+            copies kept in flight ahead of the row being updated, sums them in a fixed order and
+            applies Adam to the shard (smore_shard_reduce_update_rows); a second barrier ends the
+            step.
   prefetch  (optional) the rows of the NEXT step's first lookup group are pulled on a side stream
             while the current step computes; after the step's last barrier only the rows their
             owners updated meanwhile (published as a bitmap) are pulled again, so the result is
@@ -417,7 +419,7 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         n_in = shard.world * lay.span
         dev = shard.device
         self._in_ids = torch.empty(n_in, dtype=torch.int64, device=dev)
-        self._in_bounds = torch.empty(shard.world * len(lay.plan_caps) * 2, dtype=torch.int32, device=dev)
+        self._runs = torch.zeros(80, dtype=torch.int32, device=dev)     # SMORE_SHARD_RUNS_INTS
         self._o_uniq = torch.empty(n_in, dtype=torch.int64, device=dev)
         self._o_slot = torch.empty(n_in, dtype=torch.int32, device=dev)
         self._o_counts = torch.empty(n_in, dtype=torch.int32, device=dev)
@@ -593,22 +595,18 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         n_in = G * lay.span
         par = self.parity
         if self._owner_ws is None:
-            nbytes = L.smore_unique_rows_workspace_bytes(max(sh.S, 1))
+            nbytes = L.smore_shard_owner_plan_workspace_bytes(max(sh.S, 1))
             self._owner_ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         with torch.cuda.device(dev):
             with _lib.timed("shard_collect"):
-                _lib.check(L.smore_shard_collect_ids(sh.d_uniq_ptrs[par].data_ptr(), sh.d_nuniq_ptrs[par].data_ptr(),
-                                                     G, P, self._caps, sh.base, sh.S, self._in_ids.data_ptr(),
-                                                     self._in_bounds.data_ptr(), st), "smore_shard_collect_ids")
-                _lib.check(L.smore_unique_rows(self._in_ids.data_ptr(), n_in, max(sh.S, 1), self._o_uniq.data_ptr(),
-                                               self._o_slot.data_ptr(), self._o_counts.data_ptr(),
-                                               self._o_nuniq.data_ptr(), self._owner_ws.data_ptr(),
-                                               self._owner_ws.numel(), st), "smore_unique_rows(owner)")
-                _lib.check(L.smore_shard_record_sources(self._o_slot.data_ptr(), n_in, self._o_src.data_ptr(), st),
-                           "smore_shard_record_sources")
-                # publish which rows this step updates (readers: the next step's refresh on every rank)
-                _lib.check(L.smore_shard_mark_dirty(self._o_uniq.data_ptr(), self._o_nuniq.data_ptr(), n_in,
-                                                    max(sh.S, 1), sh.dirty.data_ptr(), st), "smore_shard_mark_dirty")
+                # every list's run of ids in this shard's range -> compact local ids -> distinct rows,
+                # one source position per row, the updated-rows bitmap for the next step's refresh
+                _lib.check(L.smore_shard_owner_plan(
+                    sh.d_uniq_ptrs[par].data_ptr(), sh.d_nuniq_ptrs[par].data_ptr(), G, P, self._caps, sh.base,
+                    max(sh.S, 1), n_in, self._in_ids.data_ptr(), self._runs.data_ptr(), self._o_uniq.data_ptr(),
+                    self._o_slot.data_ptr(), self._o_counts.data_ptr(), self._o_src.data_ptr(),
+                    self._o_nuniq.data_ptr(), sh.dirty.data_ptr(), self._owner_ws.data_ptr(),
+                    self._owner_ws.numel(), st), "smore_shard_owner_plan")
             _lib.note("n_unique_owner", self._o_nuniq[0])
             dev_step = getattr(self, "_step_dev", None) is not None
             if dev_step:
@@ -618,15 +616,15 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
                     _lib.check(L.smore_shard_reduce_update_rows_dev(
                         sh.table.data_ptr(), sh.m.data_ptr(), sh.v.data_ptr(), self._o_uniq.data_ptr(),
                         self._o_counts.data_ptr(), self._o_src.data_ptr(), self._o_nuniq.data_ptr(), n_in,
-                        sh.d_grad_ptrs[par].data_ptr(), self._in_ids.data_ptr(), self._in_bounds.data_ptr(), G, P,
-                        self._caps, sh.width, float(lr), 0.9, 0.999, eps, self._step_scalars.data_ptr(),
+                        sh.d_grad_ptrs[par].data_ptr(), self._in_ids.data_ptr(), self._runs.data_ptr(), G * P,
+                        sh.width, float(lr), 0.9, 0.999, eps, self._step_scalars.data_ptr(),
                         int(self.squeeze), st), "smore_shard_reduce_update_rows_dev")
                     return
                 _lib.check(L.smore_shard_reduce_update_rows(
                     sh.table.data_ptr(), sh.m.data_ptr(), sh.v.data_ptr(), self._o_uniq.data_ptr(),
                     self._o_counts.data_ptr(), self._o_src.data_ptr(), self._o_nuniq.data_ptr(), n_in,
-                    sh.d_grad_ptrs[par].data_ptr(), self._in_ids.data_ptr(), self._in_bounds.data_ptr(), G, P,
-                    self._caps, sh.width, float(lr), 0.9, 0.999, eps, int(self.step), int(self.squeeze), st),
+                    sh.d_grad_ptrs[par].data_ptr(), self._in_ids.data_ptr(), self._runs.data_ptr(), G * P,
+                    sh.width, float(lr), 0.9, 0.999, eps, int(self.step), int(self.squeeze), st),
                     "smore_shard_reduce_update_rows")
 
     def update_step(self, indices, inverse_indices, grad, lr):

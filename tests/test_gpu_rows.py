@@ -34,6 +34,9 @@ def _unique(idx_np, n_table_rows):
 @pytest.mark.parametrize("n,n_rows,dist", [
     (1, 1, "uniform"), (5, 40, "uniform"), (1000, 97, "uniform"), (50000, 14505, "uniform"),
     (200000, 2500604, "zipf"), (1050624, 10756769, "uniform"), (4096, 33, "uniform"), (70000, 32768 * 3 + 5, "zipf"),
+    # few ids over a large id space: the one-CTA sort route (a step's anchor lookups on a sharded table)
+    (1024, 86054151, "uniform"), (1024, 86054151, "zipf"), (4096, 10756769, "zipf"), (1, 1 << 20, "uniform"),
+    (37, 300000, "zipf"), (4097, 10756769, "uniform"), (33, 1 << 18, "uniform"),
 ])
 def test_unique_rows_bit_exact(n, n_rows, dist):
     rng = np.random.default_rng(n)
@@ -64,6 +67,19 @@ def test_unique_rows_edge_cases():
     assert uniq[:3].tolist() == [5, 7, 99]
     assert inverse[:7].tolist() == [0, -1, 2, -1, 0, 1, -1]
     assert counts[:3].tolist() == [2, 1, 1]
+    # the same through the short-list route (large id space)
+    big = 5000000
+    idx = np.array([5, -1, big - 1, big, 5, 7, 1 << 40, 7, 7], np.int64)
+    uniq, inverse, counts, n_unique = _unique(idx, big)
+    assert n_unique.tolist() == [3, 3]
+    assert uniq[:3].tolist() == [5, 7, big - 1]
+    assert inverse[:9].tolist() == [0, -1, 2, -1, 0, 1, -1, 1, 1]
+    assert counts[:3].tolist() == [2, 3, 1]
+    uniq, inverse, counts, n_unique = _unique(np.full(3000, big - 1), big)
+    assert n_unique.tolist() == [1, 0] and uniq[0].item() == big - 1 and counts[0].item() == 3000
+    assert inverse[:3000].unique().tolist() == [0]
+    uniq, inverse, counts, n_unique = _unique(np.array([-3, big + 1], np.int64), big)
+    assert n_unique.tolist() == [0, 2] and inverse[:2].tolist() == [-1, -1]
     # every id identical; last id of the table; table size not a multiple of 32
     uniq, inverse, counts, n_unique = _unique(np.full(1000, 32), 33)
     assert n_unique.tolist() == [1, 0] and uniq[0].item() == 32 and counts[0].item() == 1000

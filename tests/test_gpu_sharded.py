@@ -184,8 +184,14 @@ def test_two_processes_over_nvlink_match_emulation(tmp_path, prefetch):
     from smore_b200 import sharded
     world, n_total, D, B, K = 2, 1003, 64, 6, 50
     steps = 4 if prefetch else 2
-    mp.spawn(_two_process_worker, args=(world, _free_port(), n_total, D, B, K, str(tmp_path), prefetch, steps),
-             nprocs=world, join=True)
+    for attempt in range(3):
+        try:
+            mp.spawn(_two_process_worker, args=(world, _free_port(), n_total, D, B, K, str(tmp_path), prefetch, steps),
+                     nprocs=world, join=True)
+            break
+        except Exception as exc:       # the port found free a moment ago may have been taken since
+            if "EADDRINUSE" not in str(exc) or attempt == 2:
+                raise
     real = torch.cat([torch.load(os.path.join(str(tmp_path), "shard%d.pt" % r)) for r in range(world)])
     caps = (B * K + 2 * B, B, B)
     shards = sharded.ShardGroup.emulated(world, n_total, D, caps, squeeze=True)
