@@ -25,7 +25,7 @@ def oracle():
 def golden():
     import numpy as np
     gdir = os.path.join(ROOT, "tests", "golden")
-    return {name: np.load(os.path.join(gdir, "reference_%s.npz" % name)) for name in ("ops", "logits", "optimizer")}
+    return {name: np.load(os.path.join(gdir, "reference_%s.npz" % name)) for name in ("ops", "logits", "optimizer", "ranking")}
 
 
 @pytest.fixture(autouse=True)

@@ -11,6 +11,8 @@ What is executed is the reference's code, imported from its tree, on CPU:
     self-check loss `sum(out ** 2) * 3.14` those files use, differentiated by autograd;
   * the models' native logits (smore/models/{vec,box,rotate}.py: native_cal_logit) on a
     training-shaped batch (per-query negatives and a two-branch union);
+  * the evaluation step test_step_mp (smore/training/train_process.py:94-169) with a stand-in model
+    that returns seeded logits: its logged MRR / HITS per query (reference_ranking.npz);
   * merge_grad_indices / merge_grad_list and AdamEmbedOptimizer / AdaGradEmbedOptimizer /
     SGDEmbedOptimizer.update_step (smore/common/embedding/embed_optimizer.py) for three
     consecutive steps, with full and row-wise second moments.
@@ -47,11 +49,15 @@ def _install_stubs():
 
     ts.scatter = scatter
     sys.modules["torch_scatter"] = ts
-    for name in ("tensorboardX", "pickle5"):
+    for name in ("tensorboardX", "pickle5", "libsampler"):
         if name not in sys.modules:
             m = types.ModuleType(name)
-            m.SummaryWriter = object
+            m.SummaryWriter = m.GlobalSummaryWriter = object
             sys.modules[name] = m
+    if "smore.cpp_sampler.online_sampler" not in sys.modules:
+        m = types.ModuleType("smore.cpp_sampler.online_sampler")
+        m.OnlineSampler = object
+        sys.modules["smore.cpp_sampler.online_sampler"] = m
 
 
 def _np(t):
@@ -179,6 +185,77 @@ def optimizer_cases(out):
                     out[tag + "v_after%d" % step] = _np(me.state_sum_rw.embed)
 
 
+class _StubLoader(list):
+    """What test_step_mp needs of a DataLoader: iteration, len(), .dataset.all_entity_idx."""
+
+    def __init__(self, items, n_entities):
+        super().__init__(items)
+        self.dataset = types.SimpleNamespace(all_entity_idx=torch.arange(n_entities).unsqueeze(0))
+
+
+class _StubModel:
+    """Returns prepared logits for whatever query it is asked to score against all entities."""
+
+    def __init__(self, logits):
+        self.logits = logits
+        self.entity_embedding = lambda idx: torch.zeros(1, 1)
+
+    def eval(self):
+        return self
+
+    def __call__(self, positive, negative_sample, query_structure, query_mat, device=None, all_neg=None):
+        return None, self.logits[int(query_mat[0, 0])].reshape(1, -1).clone(), None
+
+
+def ranking_cases(out):
+    """The reference's evaluation step itself - smore/training/train_process.py:94-169, test_step_mp -
+    run on the CPU for one query at a time with a model that returns seeded logits over N candidates:
+    what it logs per query structure (MRR, HITS1/3/10, HITS1max) is what the library's filtered ranks
+    have to reproduce.  Cases: continuous logits; logits quantised so that many candidates tie with
+    each other (but no answer ties with anything); one answer that ties with other candidates."""
+    import torch.distributed as dist
+    if not dist.is_initialized():
+        import tempfile
+        dist.init_process_group("gloo", init_method="file://" + os.path.join(tempfile.mkdtemp(), "store"),
+                                rank=0, world_size=1)
+    from smore.training.train_process import test_step_mp
+    g = torch.Generator().manual_seed(4242)
+    N = 3000
+    cases = []      # (logits [N], easy ids, hard ids, tag)
+    for tag, n_easy, n_hard, levels in (("plain", 0, 1, 0), ("plain", 5, 3, 0), ("plain", 40, 60, 0),
+                                        ("ties_elsewhere", 7, 9, 6), ("ties_elsewhere", 0, 25, 3),
+                                        ("tie_on_answer", 2, 2, 4)):
+        logits = torch.randn(N, generator=g)
+        ids = torch.randperm(N, generator=g)[:n_easy + n_hard].tolist()
+        easy, hard = ids[:n_easy], ids[n_easy:]
+        if levels:
+            logits = torch.round(logits * levels) / levels
+            if tag == "ties_elsewhere":
+                # give every answer a value no other candidate has
+                for j, a in enumerate(easy + hard):
+                    logits[a] = logits[a] + 0.01 + 0.0001 * j
+        if n_hard:
+            logits[hard[0]] = logits.max() + (1.0 if tag != "tie_on_answer" else 0.0)
+        cases.append((logits, easy, hard, tag))
+    args = types.SimpleNamespace(eval_link_pred=False, eval_batch_size=1, print_on_screen=False, nentity=N,
+                                 test_log_steps=1000000)
+    model = _StubModel([c[0] for c in cases])
+    out["rank/n_cases"] = np.int64(len(cases))
+    for i, (logits, easy, hard, tag) in enumerate(cases):
+        structure = ("e", ("r",))
+        item = (None, [[i, 0]], [(i, (0,))], [structure], [set(easy)], [set(hard)])
+        collected = []
+        buf = types.SimpleNamespace(put=collected.append)
+        test_step_mp(model, args, None, _StubLoader([item], N), buf, 0, "cpu", "test")
+        logs = collected[0][0][structure]
+        out["rank/%d/logits" % i] = _np(logits)
+        out["rank/%d/easy" % i] = np.array(sorted(set(easy)), np.int64)
+        out["rank/%d/hard" % i] = np.array(sorted(set(hard)), np.int64)
+        out["rank/%d/tag" % i] = np.array(tag)
+        out["rank/%d/metrics" % i] = np.array([logs[k] for k in ("MRR", "HITS1", "HITS3", "HITS10", "HITS1max")],
+                                              np.float64)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("SMORE_REFERENCE_DIR", ""),
@@ -190,7 +267,8 @@ def main():
     _install_stubs()
     torch.manual_seed(1)
     torch.set_num_threads(1)
-    for name, fn in (("ops", op_cases), ("logits", logit_cases), ("optimizer", optimizer_cases)):
+    for name, fn in (("ops", op_cases), ("logits", logit_cases), ("optimizer", optimizer_cases),
+                     ("ranking", ranking_cases)):
         out = {}
         fn(out)
         path = os.path.join(HERE, "reference_%s.npz" % name)

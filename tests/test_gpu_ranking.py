@@ -109,3 +109,24 @@ def test_evaluation_pair_of_box_calls_is_one_pass_and_exact():
         assert torch.equal(d_out2, ref_out)
         assert torch.equal(d_in2, ext_ops._dist("box_in", ent, c, o))
         assert not torch.equal(d_in2, ref_in)
+
+
+def test_ranks_reproduce_the_reference_test_step_metrics(golden):
+    """MRR / HITS of the library's filtered ranks against the values the reference's own test_step_mp
+    (train_process.py:94-169) logged for the same logits and answer sets (tests/golden/make_golden.py)."""
+    from smore_b200 import ranking
+    r = golden["ranking"]
+    n = int(r["rank/n_cases"])
+    cases = [(str(r["rank/%d/tag" % i]), r["rank/%d/logits" % i], r["rank/%d/easy" % i].tolist(),
+              r["rank/%d/hard" % i].tolist(), r["rank/%d/metrics" % i]) for i in range(n)]
+    logits = torch.from_numpy(np.stack([c[1] for c in cases])).cuda()
+    ranks = ranking.filtered_ranks(logits, [c[2] for c in cases], [c[3] for c in cases])
+    checked = 0
+    for (tag, lg, easy, hard, want), rk in zip(cases, ranks):
+        got = ranking.ranking_metrics(rk)
+        if tag == "tie_on_answer":
+            continue          # the reference leaves the order of tied logits to the sort implementation
+        for k, w in zip(("MRR", "HITS1", "HITS3", "HITS10", "HITS1max"), want.tolist()):
+            assert abs(got[k] - w) <= 1e-6, (tag, k, got[k], w)
+        checked += 1
+    assert checked >= 5

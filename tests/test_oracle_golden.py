@@ -127,3 +127,33 @@ def test_oracle_equals_reference_functors_bitwise(oracle, op):
         for x, y in zip(oracle.dist_backward(op, gout, ent, q0, q1), ref.dist_backward(op, gout, ent, q0, q1)):
             if x is not None:
                 assert np.array_equal(x, y)
+
+
+def _ranking_cases(golden):
+    r = golden["ranking"]
+    for i in range(int(r["rank/n_cases"])):
+        yield (str(r["rank/%d/tag" % i]), r["rank/%d/logits" % i], r["rank/%d/easy" % i].tolist(),
+               r["rank/%d/hard" % i].tolist(), dict(zip(("MRR", "HITS1", "HITS3", "HITS10", "HITS1max"),
+                                                        r["rank/%d/metrics" % i].tolist())))
+
+
+def test_restated_ranking_block_equals_the_reference_test_step(golden):
+    """oracle/native_torch.reference_filtered_ranks / reference_ranking_metrics (the checker of the GPU
+    ranking kernel) against what the reference's own test_step_mp logged for the same logits and
+    answers.  Where an answer ties with other candidates the reference leaves the order to the sort
+    implementation; the restatement's stable order must then land inside the band the tie allows."""
+    import torch
+    from oracle import native_torch as nt
+    seen = set()
+    for tag, logits, easy, hard, want in _ranking_cases(golden):
+        seen.add(tag)
+        ranks = nt.reference_filtered_ranks(torch.from_numpy(logits), easy, hard)
+        got = nt.reference_ranking_metrics(ranks)
+        if tag != "tie_on_answer":
+            for k in want:
+                assert abs(got[k] - want[k]) <= 1e-6, (tag, k, got[k], want[k])
+        else:
+            tied = max(int((logits == logits[a]).sum()) for a in hard)
+            assert tied > 1
+            assert 1.0 / (1.0 / want["MRR"] + tied) <= got["MRR"] <= 1.0 / max(1.0 / want["MRR"] - tied, 1.0) + 1e-9
+    assert seen == {"plain", "ties_elsewhere", "tie_on_answer"}
