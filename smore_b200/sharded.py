@@ -334,8 +334,12 @@ class _ShardedPlan(object):
                                                self.uniq.data_ptr(), self.slot.data_ptr(), self.counts.data_ptr(),
                                                self.n_unique.data_ptr(), workspace.data_ptr(), workspace.numel(), st),
                            "smore_unique_rows")
+            if opt.exchange == "nccl":
+                self._fetch_by_all_to_all(opt)
             with _lib.timed("fetch_rows"):
-                if buffers is None:
+                if opt.exchange == "nccl":
+                    pass
+                elif buffers is None:
                     _lib.check(L.smore_fetch_rows(shard.d_shard_ptrs.data_ptr(), shard.S, self.uniq.data_ptr(),
                                                   self.n_unique.data_ptr(), self.n, shard.width,
                                                   self.staging.data_ptr(), st), "smore_fetch_rows")
@@ -352,6 +356,33 @@ class _ShardedPlan(object):
             self.slot64 = self.slot.long()
         else:
             self.slot64.copy_(self.slot)
+
+    def _fetch_by_all_to_all(self, opt):
+        """The row pull without peer-mapped memory: the distinct ids go to their owners, the owners'
+        rows come back, both with torch.distributed.all_to_all_single.  The sorted id list is already
+        grouped by owner (owners hold contiguous id ranges), so the send buffers are slices of it.
+        Split sizes have to be known on the host: this route synchronises once per lookup group."""
+        import torch.distributed as dist
+        shard = opt.shard
+        dev, G, W = shard.device, shard.world, shard.width
+        nu = int(self.n_unique[0].item())
+        edges = torch.arange(G + 1, device=dev, dtype=torch.int64) * shard.S
+        cut = torch.searchsorted(self.uniq[:nu].contiguous(), edges)
+        send_counts = (cut[1:] - cut[:-1])
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=opt._group)
+        self.send_counts, self.recv_counts = send_counts.tolist(), recv_counts.tolist()
+        n_recv = sum(self.recv_counts)
+        self.recv_ids = torch.empty(n_recv, dtype=torch.int64, device=dev)
+        dist.all_to_all_single(self.recv_ids, self.uniq[:nu].contiguous(), self.recv_counts, self.send_counts,
+                               group=opt._group)
+        rows = torch.empty(n_recv, W, dtype=torch.float32, device=dev)
+        if n_recv:
+            local = (self.recv_ids - shard.base).contiguous()
+            _lib.check(_lib.lib().smore_gather_rows(shard.table.data_ptr(), local.data_ptr(), shard.S, rows.data_ptr(),
+                                                    n_recv, W, _stream_ptr(dev)), "smore_gather_rows")
+        dist.all_to_all_single(self.staging[:nu], rows, self.send_counts, self.recv_counts, group=opt._group)
+        self.n_sent = nu
 
     def adopt(self, lookups):
         off = 0
@@ -389,7 +420,18 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
     def prepare_embed(cls, args, optim_mode, embed, fn_register):
         pass
 
-    def __init__(self, shard, lazy_names=("negative_entity", "positive_entity"), barrier=None, group=None):
+    def __init__(self, shard, lazy_names=("negative_entity", "positive_entity"), barrier=None, group=None,
+                 exchange="p2p"):
+        """exchange: "p2p" - rows and row gradients are read straight from the peers' memory by this
+        library's kernels (the shard must be connected: ShardGroup.from_process_group / emulated);
+        "nccl" - the fallback for boxes without peer-mapped memory: the same two exchanges as
+        torch.distributed.all_to_all_single calls on owner-bucketed id / row buffers, followed by the
+        same owner-side de-duplication and update kernels reading the received blocks.  The fallback
+        synchronises with the host for its split sizes, does not prefetch, and needs every rank to make
+        the same number of lookup groups per step (each group is a collective)."""
+        if exchange not in ("p2p", "nccl"):
+            raise ValueError("exchange must be 'p2p' or 'nccl'")
+        self.exchange = exchange
         self.shard = shard
         self.table = shard.table          # local shard: device / dtype / width of the rows
         self.squeeze = shard.squeeze
@@ -472,6 +514,8 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         that looks up anything else simply ignores what was prepared.  `after` is an event that
         marks the id tensors as written, if another stream than the current one produces them."""
         dev = self.shard.device
+        if self.exchange == "nccl":
+            return          # the fallback pulls every step's rows when they are first needed
         if any(t.device != dev or t.dtype != torch.int64 for t in id_tensors):
             raise _lib.SmoreError("prefetch takes int64 id tensors that already live on the shard's device")
         if self._prefetch_stream is None:
@@ -573,9 +617,46 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         if self._pending:           # looked up but never used: no plan, nothing published
             self._pending = []
 
+    def _apply_grad_all_to_all(self, lr):
+        """Gradient return of the fallback: every plan's gradient rows go to their owners (the split of
+        the forward exchange, reversed); the received (ids, gradient rows) blocks then serve as the
+        lists the owner-side kernels read - one per (rank, plan), here in local memory."""
+        import torch.distributed as dist
+        sh = self.shard
+        dev, G, W = sh.device, sh.world, sh.width
+        P = len(sh.layout.plan_caps)
+        n_plans = torch.tensor([len(self._plans)], device=dev)
+        hi = n_plans.clone()
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=self._group)
+        if int(hi.item()) != len(self._plans):
+            raise _lib.SmoreError("the all-to-all exchange needs the same number of lookup groups on every rank "
+                                  "in a step (%d here, %d elsewhere)" % (len(self._plans), int(hi.item())))
+        ids_ptr, cnt, grad_ptr, keep = [0] * (G * P), [0] * (G * P), [0] * (G * P), []
+        for plan in self._plans:
+            recv = torch.empty(sum(plan.recv_counts), W, dtype=torch.float32, device=dev)
+            dist.all_to_all_single(recv, plan.g_rows[:plan.n_sent].contiguous(), plan.recv_counts, plan.send_counts,
+                                   group=self._group)
+            keep += [recv, plan.recv_ids]
+            off = 0
+            for g in range(G):
+                l = g * P + plan.index
+                ids_ptr[l] = plan.recv_ids.data_ptr() + off * 8
+                grad_ptr[l] = recv.data_ptr() + off * W * 4
+                cnt[l] = plan.recv_counts[g]
+                off += plan.recv_counts[g]
+        counts = torch.tensor(cnt, dtype=torch.int32, device=dev)
+        tables = {"ids": torch.tensor(ids_ptr, dtype=torch.int64, device=dev),
+                  "nuniq": torch.tensor([counts.data_ptr() + 4 * l for l in range(G * P)], dtype=torch.int64, device=dev),
+                  "grads": torch.tensor(grad_ptr, dtype=torch.int64, device=dev)}
+        self.owner_update(lr, tables)
+        del keep, counts
+        self._drop_plans()
+
     def apply_grad(self, lr):
         self.step += 1
         self._neutralise_unused_lookups()
+        if self.exchange == "nccl":
+            return self._apply_grad_all_to_all(lr)
         self.barrier()              # every rank's id lists and gradient rows are complete
         self.owner_update(lr)
         self.barrier()              # every shard is updated; this step's arena may be overwritten
@@ -585,7 +666,9 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
             torch.cuda.current_stream(self.shard.device).wait_event(self._prefetched[1])
         self._drop_plans()
 
-    def owner_update(self, lr):
+    def owner_update(self, lr, tables=None):
+        """`tables`: device arrays of the lists' id / length / gradient addresses; default: the peers'
+        arenas of the step in progress."""
         sh = self.shard
         lay = sh.layout
         L = _lib.lib()
@@ -594,6 +677,8 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         G, P = sh.world, len(lay.plan_caps)
         n_in = G * lay.span
         par = self.parity
+        if tables is None:
+            tables = {"ids": sh.d_uniq_ptrs[par], "nuniq": sh.d_nuniq_ptrs[par], "grads": sh.d_grad_ptrs[par]}
         if self._owner_ws is None:
             nbytes = L.smore_shard_owner_plan_workspace_bytes(max(sh.S, 1))
             self._owner_ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
@@ -602,7 +687,7 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
                 # every list's run of ids in this shard's range -> compact local ids -> distinct rows,
                 # one source position per row, the updated-rows bitmap for the next step's refresh
                 _lib.check(L.smore_shard_owner_plan(
-                    sh.d_uniq_ptrs[par].data_ptr(), sh.d_nuniq_ptrs[par].data_ptr(), G, P, self._caps, sh.base,
+                    tables["ids"].data_ptr(), tables["nuniq"].data_ptr(), G, P, self._caps, sh.base,
                     max(sh.S, 1), n_in, self._in_ids.data_ptr(), self._runs.data_ptr(), self._o_uniq.data_ptr(),
                     self._o_slot.data_ptr(), self._o_counts.data_ptr(), self._o_src.data_ptr(),
                     self._o_nuniq.data_ptr(), sh.dirty.data_ptr(), self._owner_ws.data_ptr(),
@@ -616,14 +701,14 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
                     _lib.check(L.smore_shard_reduce_update_rows_dev(
                         sh.table.data_ptr(), sh.m.data_ptr(), sh.v.data_ptr(), self._o_uniq.data_ptr(),
                         self._o_counts.data_ptr(), self._o_src.data_ptr(), self._o_nuniq.data_ptr(), n_in,
-                        sh.d_grad_ptrs[par].data_ptr(), self._in_ids.data_ptr(), self._runs.data_ptr(), G * P,
+                        tables["grads"].data_ptr(), self._in_ids.data_ptr(), self._runs.data_ptr(), G * P,
                         sh.width, float(lr), 0.9, 0.999, eps, self._step_scalars.data_ptr(),
                         int(self.squeeze), st), "smore_shard_reduce_update_rows_dev")
                     return
                 _lib.check(L.smore_shard_reduce_update_rows(
                     sh.table.data_ptr(), sh.m.data_ptr(), sh.v.data_ptr(), self._o_uniq.data_ptr(),
                     self._o_counts.data_ptr(), self._o_src.data_ptr(), self._o_nuniq.data_ptr(), n_in,
-                    sh.d_grad_ptrs[par].data_ptr(), self._in_ids.data_ptr(), self._runs.data_ptr(), G * P,
+                    tables["grads"].data_ptr(), self._in_ids.data_ptr(), self._runs.data_ptr(), G * P,
                     sh.width, float(lr), 0.9, 0.999, eps, int(self.step), int(self.squeeze), st),
                     "smore_shard_reduce_update_rows")
 
@@ -635,12 +720,15 @@ class ShardGroup(object):
     """Convenience constructors."""
 
     @staticmethod
-    def from_process_group(n_rows_total, width, plan_caps, squeeze=True, group=None, device=None):
+    def from_process_group(n_rows_total, width, plan_caps, squeeze=True, group=None, device=None, exchange="p2p"):
+        """exchange="p2p": blocks from the symmetric-memory allocator, mapped into every rank;
+        exchange="nccl": plain local blocks (use ShardedAdamOptimizer(shard, exchange="nccl"))."""
         import torch.distributed as dist
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
-        shard = ShardedTable(n_rows_total, width, rank, world, device, plan_caps, squeeze, symmetric=True)
-        shard.connect_processes(group)
+        shard = ShardedTable(n_rows_total, width, rank, world, device, plan_caps, squeeze, symmetric=exchange == "p2p")
+        if exchange == "p2p":
+            shard.connect_processes(group)
         return shard
 
     @staticmethod

@@ -140,19 +140,19 @@ def _free_port():
     return port
 
 
-def _two_process_worker(rank, world, port, n_total, D, B, K, out_dir, prefetch=False, steps=2):
+def _two_process_worker(rank, world, port, n_total, D, B, K, out_dir, prefetch=False, steps=2, exchange="p2p"):
     import torch.distributed as dist
     from smore_b200 import sharded
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     caps = (B * K + 2 * B, B, B)
-    shard = sharded.ShardGroup.from_process_group(n_total, D, caps, squeeze=True)
+    shard = sharded.ShardGroup.from_process_group(n_total, D, caps, squeeze=True, exchange=exchange)
     torch.manual_seed(0)
     full = (torch.rand(n_total, D) - 0.5) * 0.2
     shard.table.zero_()
     shard.table[:shard.local_rows] = full[shard.base:shard.base + shard.local_rows].cuda()
-    opt = sharded.ShardedAdamOptimizer(shard)
+    opt = sharded.ShardedAdamOptimizer(shard, exchange=exchange)
     batches = [tuple(t.cuda() for t in _rank_batch(rank, step, n_total, B, K, D)) for step in range(steps)]
     for step in range(steps):
         opt.zero_grad()
@@ -172,6 +172,49 @@ def _two_process_worker(rank, world, port, n_total, D, B, K, out_dir, prefetch=F
     dist.barrier()
     shard.close()
     dist.destroy_process_group()
+
+
+def _emulated_table(world, n_total, D, B, K, steps):
+    from smore_b200 import sharded
+    caps = (B * K + 2 * B, B, B)
+    shards = sharded.ShardGroup.emulated(world, n_total, D, caps, squeeze=True)
+    torch.manual_seed(0)
+    full = (torch.rand(n_total, D) - 0.5) * 0.2
+    for s in shards:
+        s.table.zero_()
+        s.table[:s.local_rows] = full[s.base:s.base + s.local_rows].cuda()
+    opts = [sharded.ShardedAdamOptimizer(s, barrier=lambda: None) for s in shards]
+    for step in range(steps):
+        for o_ in opts:
+            o_.zero_grad()
+        for r in range(world):
+            _rank_forward_backward(opts[r].forward, _rank_batch(r, step, n_total, B, K, D), world)
+        for o_ in opts:
+            o_.apply_grad(1e-2)
+    return torch.cat([s.table[:s.local_rows] for s in shards]).cpu()
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_all_to_all_exchange_matches_peer_memory_exchange(tmp_path, world):
+    """ShardedAdamOptimizer(exchange="nccl"): rows and row gradients travel through
+    torch.distributed.all_to_all_single instead of peer-mapped memory, the owner-side kernels read the
+    received blocks.  Real processes over NCCL (a one-rank group exercises the same code on a single
+    GPU) against the one-process emulation of the peer-memory path."""
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    n_total, D, B, K, steps = 1003, 64, 6, 50, 3
+    for attempt in range(3):
+        try:
+            mp.spawn(_two_process_worker,
+                     args=(world, _free_port(), n_total, D, B, K, str(tmp_path), False, steps, "nccl"),
+                     nprocs=world, join=True)
+            break
+        except Exception as exc:
+            if "EADDRINUSE" not in str(exc) or attempt == 2:
+                raise
+    real = torch.cat([torch.load(os.path.join(str(tmp_path), "shard%d.pt" % r)) for r in range(world)])
+    close(real.numpy(), _emulated_table(world, n_total, D, B, K, steps).numpy(), RTOL_ATOMIC, what="all-to-all table")
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
