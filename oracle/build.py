@@ -6,6 +6,8 @@ TEST INFRASTRUCTURE.  Outputs:
                                        behind ref_host_driver.cpp        (needs the reference tree)
   oracle/_ref/libsmore_ref_cuda.so     the reference's CUDA kernels compiled for sm_100a behind
                                        ref_cuda_wrapper.cu               (needs the reference tree)
+  oracle/_ref/libsmore_ref_kg.so       the reference's knowledge-graph container (cpp_sampler's
+                                       knowledge_graph.cpp, utils.cpp) behind ref_kg_driver.cpp
   oracle/_ref/pyref/smore/             the reference's Python package (*.py only) placed next to the
                                        two libraries, so that its own op front-ends, models and
                                        training step can be imported where the reference tree is
@@ -109,8 +111,31 @@ def build_reference(reference_dir, force=False):
               "-shared", "-Xcompiler", "-fPIC", "-I", ext_dir,
               "-o", cuda_out, cuda_src, ref_cu])
     built.append(cuda_out)
+    built += build_ref_kg(reference_dir, force)
     built += build_pyref(reference_dir, force)
     return built
+
+
+def build_ref_kg(reference_dir, force=False):
+    """oracle/_ref/libsmore_ref_kg.so: the reference's knowledge-graph container (its own
+    knowledge_graph.cpp and utils.cpp, compiled where they lie) behind ref_kg_driver.cpp."""
+    import sysconfig
+    smp = os.path.join(reference_dir, "smore", "cpp_sampler")
+    srcs = [os.path.join(smp, "src", "lib", "knowledge_graph.cpp"), os.path.join(smp, "src", "lib", "utils.cpp")]
+    if not all(os.path.isfile(s) for s in srcs):
+        return []
+    try:
+        import pybind11
+    except ImportError:
+        return []
+    out = os.path.join(HERE, "_ref", "libsmore_ref_kg.so")
+    driver = os.path.join(HERE, "ref_kg_driver.cpp")
+    if force or _newer(out, srcs + [driver]):
+        # no -DNDEBUG: the reference reads and writes files inside assert()
+        _run(["g++", "-std=c++14", "-O2", "-march=x86-64-v3", "-w", "-shared", "-fPIC",
+              "-I", os.path.join(smp, "include"), "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
+              "-o", out, driver] + srcs)
+    return [out]
 
 
 def main():
