@@ -301,6 +301,37 @@ SMORE_API int smore_path_project_backward(const float* g_center, const float* g_
                                 size_t n_queries, size_t hops, size_t dim, int relu_offset,
                                 float* g_rel_table, float* g_off_table, void* stream);
 
+/* The general form of the two calls above: every geometry, and a path may start from table rows.
+ *   geometry 0  additive (as above; out0 = center, out1 = offset when off_table != NULL)
+ *   geometry 1  rotation: rel_table [n_relations, dim] holds phases; each hop multiplies the complex
+ *               state (re, im) by cos(p) + i sin(p), p = row * phase_scale (rotate.py:101-109, where
+ *               phase_scale = pi / embedding_range); out0 = re, out1 = im
+ *   geometry 2  complex product: rel_table [n_relations, 2*dim] rows [re | im] (complex.py:108-117 with
+ *               the identity normaliser); out0 = re, out1 = im
+ *   geometry 3  product: rel_table [n_relations, dim] (distmult.py:106-111, identity normaliser); out0
+ * start: [n_queries, W] state rows (W = dim, or 2*dim = [re | im] for geometries 1 and 2) - or, with
+ * start_idx != NULL, the entity table [n_start_rows, W] whose rows start_idx[b] the paths start from
+ * (kg_reasoning.py:217-250 looks the anchors up first, box.py:131-139 / rotate.py:111-119): the anchor
+ * rows are then read in place and never gathered.  Ids outside the table: see the _rows entry points.
+ * At most 8 hops per call for geometries 1-3.
+ * Backward overwrites g_rel_table (and g_off_table) with the dense gradients of the relation tables
+ * and delivers the gradient of the start rows either as g_start [n_queries, W] (start given as a
+ * tensor; may be NULL if not wanted) or, for table rows, into g_rows[slot[b], :] under the rules of
+ * smore_dist_backward_rows (store when slot_count == 1, atomic add otherwise, always with slot_count
+ * NULL).  Geometry 0: the start rows' gradient is g_out0 itself. */
+SMORE_API int smore_path_embed_forward(int geometry, const float* start, const int64_t* start_idx,
+                             size_t n_start_rows, const float* start_offset, const float* rel_table,
+                             const float* off_table, size_t n_relations, const int64_t* rel_ids,
+                             size_t id_stride, size_t n_queries, size_t hops, size_t dim, int relu_offset,
+                             double phase_scale, float* out0, float* out1, void* stream);
+SMORE_API int smore_path_embed_backward(int geometry, const float* g_out0, const float* g_out1,
+                              const float* start, const int64_t* start_idx, size_t n_start_rows,
+                              const float* rel_table, const float* off_table, size_t n_relations,
+                              const int64_t* rel_ids, size_t id_stride, size_t n_queries, size_t hops,
+                              size_t dim, int relu_offset, double phase_scale, float* g_rel_table,
+                              float* g_off_table, float* g_start, const int32_t* slot,
+                              const int32_t* slot_count, float* g_rows, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Evaluation: filtered ranks of the answers of each query among all candidates.
  * The reference (train_process.py:113-146) argsorts the [1, N] logits of a query, scatters the

@@ -11,6 +11,7 @@ LIB_PATH = os.path.join(_HERE, "csrc", "libsmore_b200.so")
 
 DIST_IDS = {"box_out": 0, "box_in": 1, "rotate": 2, "l1": 3, "l2": 4, "complex": 5, "distmult": 6}
 BOX_BOTH_ID = 7     # smore_union_* entry points only
+GEOMETRY_IDS = {"add": 0, "rotate": 1, "complex": 2, "distmult": 3}   # smore_path_embed_*
 OPT_IDS = {"sgd": 0, "adam": 1, "adagrad": 2}
 ROW_PARTS = {"box_out": 1, "box_in": 1, "rotate": 2, "l1": 1, "l2": 1, "complex": 2, "distmult": 1}
 QUERY_PARTS = {"box_out": 2, "box_in": 2, "rotate": 2, "l1": 1, "l2": 1, "complex": 2, "distmult": 1}
@@ -51,6 +52,9 @@ SIGNATURES = {
                                             _p]),
     "smore_path_project_forward": (_int, [_p, _p, _p, _p, _sz, _p, _sz, _sz, _sz, _sz, _int, _p, _p, _p]),
     "smore_path_project_backward": (_int, [_p, _p, _p, _sz, _p, _sz, _sz, _sz, _sz, _int, _p, _p, _p]),
+    "smore_path_embed_forward": (_int, [_int, _p, _p, _sz, _p, _p, _p, _sz, _p, _sz, _sz, _sz, _sz, _int, _dbl, _p, _p, _p]),
+    "smore_path_embed_backward": (_int, [_int, _p, _p, _p, _p, _sz, _p, _p, _sz, _p, _sz, _sz, _sz, _sz, _int, _dbl,
+                                         _p, _p, _p, _p, _p, _p, _p]),
     "smore_filtered_ranks_workspace_bytes": (_sz, [_sz]),
     "smore_filtered_ranks": (_int, [_p, _sz, _sz, _p, _p, _sz, _sz, _p, _p, _sz, _p]),
     "smore_dot_available": (_int, []),

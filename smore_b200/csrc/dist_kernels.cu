@@ -1402,8 +1402,10 @@ int smore_union_backward_rows(int dist_id, const float* gout0, const float* gout
 
 extern "C" int smore_peer_async_status(int* status);   // peer_kernels.cu (not part of the public header)
 extern "C" int smore_rows_status(int* status);         // rows_kernels.cu (likewise)
+extern "C" int smore_query_status(int* status);        // query_kernels.cu (likewise)
 extern "C" int smore_peer_status_clear(void);
 extern "C" int smore_rows_status_clear(void);
+extern "C" int smore_query_status_clear(void);
 
 int smore_async_status(int* status) {
   if (!status) return fail(SMORE_ERR_NULL, "async_status: NULL pointer");
@@ -1412,7 +1414,9 @@ int smore_async_status(int* status) {
   if (e != cudaSuccess) return fail(SMORE_ERR_CUDA, "async_status: %s", cudaGetErrorString(e));
   if (int rc = smore_peer_async_status(&peer)) return rc;   // the other files' kernels keep their own words
   if (int rc = smore_rows_status(&rows)) return rc;
-  *status = v | (peer ? kStatusPeerWait : 0) | rows;
+  int query = 0;
+  if (int rc = smore_query_status(&query)) return rc;
+  *status = v | (peer ? kStatusPeerWait : 0) | rows | query;
   return SMORE_OK;
 }
 
@@ -1422,6 +1426,7 @@ int smore_async_status_clear(void) {
   if (cudaMemcpyToSymbol(g_async_status, &zero, sizeof(int)) != cudaSuccess)
     return fail(SMORE_ERR_CUDA, "async_status_clear: cannot write the status word");
   if (int rc = smore_peer_status_clear()) return rc;
+  if (int rc = smore_query_status_clear()) return rc;
   return smore_rows_status_clear();
 }
 
