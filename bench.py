@@ -352,6 +352,9 @@ def train_step(model, pos, neg, queries, structure, reduce_dense=None, upcoming=
     starts pulling now (the role of the reference's asynchronous embedding read, embedding.py:98-121)."""
     model.dense_opt.zero_grad(set_to_none=True)
     model.embed_opt.zero_grad()
+    if getattr(model, "fused_update", False):
+        # rows touched by a single position of the step are updated inside the backward kernel
+        model.embed_opt.announce_lr(model.cfg["lr"])
     if upcoming is not None:
         model.embed_opt.prefetch(first_lookup_group(*upcoming[:3]), after=upcoming[3])
     pos_logit, neg_logit = model(pos, neg, queries, structure)
@@ -535,25 +538,28 @@ NCU_UPDATE_BYTES_PER_ROW = 8070.0
 ALU_OPS_PER_TERM = {"box": {"fwd": 6, "bwd": 14}, "vec": {"fwd": 2, "bwd": 5}}
 
 
-def ncu_traffic(workload, kernel, n_unique_mean):
-    if workload != "freebase_q2b":
-        return None
+def ncu_traffic(workload, kernel, n_unique_mean, fused=False):
+    if workload != "freebase_q2b" or fused:
+        return None         # (no capture of the kernels with the in-backward update yet)
     if kernel in ("sparse_update_rows", "shard_reduce_update"):
         return round(NCU_UPDATE_BYTES_PER_ROW * n_unique_mean)
     return NCU_TRAFFIC_BYTES.get(kernel)
 
 
-def algorithmic_bytes(cfg, n_unique_mean):
-    """Bytes each kernel has to move per launch (per union branch for the two distance kernels)."""
+def algorithmic_bytes(cfg, n_unique_mean, n_single_mean=0.0):
+    """Bytes each kernel has to move per launch (per union branch for the two distance kernels).
+    n_single_mean: rows of a step that the backward kernel updates itself (one contributing position:
+    it reads the row and its first moment and writes both back, 16 W bytes, instead of reading the row
+    and writing the gradient, 8 W); the update kernel then handles the remaining distinct rows only."""
     B, K, D = cfg["B"], cfg["K"], cfg["dim"]
     W = D * (2 if cfg["geo"] in ("rotate", "complex") else 1)
     nq = 1 if cfg["geo"] == "vec" else 2
     nout = 2 if cfg["geo"] == "box" else 1
     pairs = B * K
     fwd = pairs * (4 * W + 8 + 4 * nout) + B * D * 4 * nq
-    bwd = pairs * (8 * W + 8 + 4 + 4 + 4 * nout) + 2 * B * D * 4 * nq
+    bwd = pairs * (8 * W + 8 + 4 + 4 + 4 * nout) + 2 * B * D * 4 * nq + n_single_mean * (8 * W + 8)
     v_bytes = 8 if cfg["squeeze"] else 8 * W
-    upd = n_unique_mean * (4 * W + 8 * W + 8 * W + v_bytes + 8)
+    upd = (n_unique_mean - n_single_mean) * (4 * W + 8 * W + 8 * W + v_bytes + 8) + n_single_mean * 8
     # sharded run: the owner-side kernel moves the same bytes as the update (the gradient read is a
     # peer read); the fetch copies every distinct row once (read + write)
     out = {"sparse_update_rows": upd, "shard_reduce_update": upd, "fetch_rows": n_unique_mean * 8 * W}
@@ -605,7 +611,7 @@ class StepRunner(object):
     running steps (eager, replayed CUDA graphs, with host batches)."""
 
     def __init__(self, cfg, rows_per_gpu, device, world=1, rank=0, graphs=True, prefetch=True, lazy=True,
-                 fused_paths=True, pool=18, resettable=False):
+                 fused_paths=True, pool=18, resettable=False, fused_update=True):
         from smore_b200 import _lib, embedding, ext_ops
         import torch.distributed as dist
         self.cfg, self.device, self.world, self.rank = cfg, device, world, rank
@@ -641,6 +647,7 @@ class StepRunner(object):
             self.model = QueryModel(cfg, n_rows, device, ext_ops, embedding, lazy=lazy, capturable=capturable,
                                     fused_paths=fused_paths)
         model = self.model
+        model.fused_update = bool(fused_update) and world == 1 and lazy
         # (a copy of the initial state, table included at one GPU: only for runs that start over)
         self._initial = {k: v.detach().clone() for k, v in model.state_dict().items()} if resettable else None
         if capturable:
@@ -928,7 +935,9 @@ def kernel_table(cfg, workload, kernel_ms, notes, peak, peak_kind, fma_rate=None
     """Per-kernel averages of the eager pass with the roofline of the kernel that took longest."""
     nus = [int(t.item()) for t in notes.get("n_unique", []) + notes.get("n_unique_owner", [])]
     n_unique_mean = sum(nus) / len(nus) if nus else cfg["B"] * cfg["K"]
-    alg = algorithmic_bytes(cfg, n_unique_mean=n_unique_mean)
+    singles = [int(t.item()) for t in notes.get("n_single", [])]
+    n_single_mean = sum(singles) / max(1, len(nus)) if singles else 0.0
+    alg = algorithmic_bytes(cfg, n_unique_mean=n_unique_mean, n_single_mean=n_single_mean)
     flops = algorithmic_flops(cfg)
     kernels = {}
     for name, ms_list in kernel_ms.items():
@@ -985,7 +994,9 @@ def kernel_table(cfg, workload, kernel_ms, notes, peak, peak_kind, fma_rate=None
     elif dom:
         roofline = {"kernel": dom, "bound": "hbm", "achieved": kernels[dom]["achieved_gbs"], "peak": peak,
                     "peak_source": peak_kind, "unit": "GB/s", "frac": round(kernels[dom]["achieved_gbs"] / peak, 4),
-                    "traffic": ncu_traffic(workload, dom, n_unique_mean), "timing": timing_note}
+                    "traffic": ncu_traffic(workload, dom, n_unique_mean, fused=n_single_mean > 0), "timing": timing_note}
+    if n_single_mean:
+        roofline = dict(roofline or {}, rows_updated_in_backward=round(n_single_mean, 1))
     return kernels, roofline, n_unique_mean
 
 
@@ -1077,7 +1088,8 @@ def run_workload(name, cfg, args, device, world, rank, steps, warmup, repeats, p
     from smore_b200 import _lib
     rows_per_gpu = args.rows or cfg["rows"] or (FREEBASE_ENTITIES + 7) // 8
     runner = StepRunner(cfg, rows_per_gpu, device, world, rank, graphs=not args.no_graphs, prefetch=not args.no_prefetch,
-                        lazy=not args.no_lazy, fused_paths=not args.no_fused_paths, pool=args.pool)
+                        lazy=not args.no_lazy, fused_paths=not args.no_fused_paths, pool=args.pool,
+                        fused_update=not args.no_fused_update)
     import gc
     gc.collect()
     gc.freeze()        # keep the cycle collector from scanning the long-lived model objects inside a timed region
@@ -1396,6 +1408,8 @@ def main():
                     help="several GPUs: pull every step's rows after the previous update instead of during it")
     ap.add_argument("--no-fused-paths", action="store_true",
                     help="embed path queries hop by hop with torch ops, as the reference models do")
+    ap.add_argument("--no-fused-update", action="store_true",
+                    help="1 GPU: write every row gradient out and update all touched rows in the update kernel")
     ap.add_argument("--cpu-steps", type=int, default=6)
     ap.add_argument("--dump-kernel-times", action="store_true", help="add every timed launch's duration to the JSON")
     ap.add_argument("--eval", action="store_true",

@@ -269,6 +269,35 @@ SMORE_API int smore_sparse_update_rows(int opt_id, float* table, float* m, float
                              size_t width, double lr, double beta1, double beta2, double eps,
                              int64_t step, int squeeze, void* stream);
 
+/* Entries of uniq that are negative are skipped (smore_rows_backward_fused_adam marks the rows it
+ * has already updated by complementing their id). */
+
+/* Backward of a distance over table rows (per-query candidates, as smore_dist_backward_rows /
+ * smore_box_backward / smore_union_backward_rows; dist_id may be SMORE_DIST_BOX_BOTH, branches 1 or 2)
+ * WITH the Adam step of every row that has a single contributor in the step folded in (row-wise
+ * second moment only: v is [n_table_rows]).  No counterpart in the reference, where the gradient of
+ * such a row is written to the gathered-gradient tensor, merged, and read back by the optimizer
+ * together with the row (embed_optimizer.py:39-48, 208-252); here the warp that has the row in
+ * shared memory for its gradient also brings in the first-moment row, updates both in place and
+ * writes them back: per such row 1.6 KB less written and 3.2 KB less read (Query2box, dim 400).
+ *   - slot_count is required: a row with slot_count == 1 is updated here and uniq[slot] becomes
+ *     ~row (negative); rows with more contributors get their gradient added into g_rows (zeroed
+ *     beforehand, smore_zero_shared_rows) and are updated by the smore_sparse_update_rows call that
+ *     follows, which skips the negative entries;
+ *   - lr, beta1, beta2, eps, step / step_scalars: those of that update call;
+ *   - use it for a lookup that exactly ONE distance op consumes in the step (a second backward over
+ *     the same positions would add to rows that are already updated) and only after every forward
+ *     read of the step is done;
+ *   - SMORE_ERR_BAD_SHAPE when the shape is not covered (then nothing was enqueued: call the
+ *     ordinary backward). */
+SMORE_API int smore_rows_backward_fused_adam(int dist_id, const float* gout0, const float* gout1, float* table,
+                                   const int64_t* idx, size_t n_table_rows, const float* first,
+                                   const float* second, const int32_t* slot, const int32_t* slot_count,
+                                   float* g_rows, float* g_first, float* g_second, size_t branches,
+                                   size_t bsize, size_t num, size_t dim, float* m, float* v, int64_t* uniq,
+                                   double lr, double beta1, double beta2, double eps, int64_t step,
+                                   const float* step_scalars, void* stream);
+
 /* The same update with the optimizer's step counter on the device, for hosts that replay a
  * captured CUDA graph step after step (kernel arguments are frozen in a graph, the step is not).
  * smore_adam_step_scalars increments *step (device int64) and writes the two step-dependent

@@ -47,6 +47,8 @@ SIGNATURES = {
     "smore_scatter_add_rows": (_int, [_p, _p, _p, _p, _sz, _sz, _p]),
     "smore_sparse_update_rows": (_int, [_int, _p, _p, _p, _p, _p, _p, _sz, _sz, _dbl, _dbl, _dbl, _dbl,
                                         ctypes.c_int64, _int, _p]),
+    "smore_rows_backward_fused_adam": (_int, [_int, _p, _p, _p, _p, _sz] + [_p] * 7 + [_sz] * 4 + [_p, _p, _p, _dbl, _dbl,
+                                              _dbl, _dbl, ctypes.c_int64, _p, _p]),
     "smore_adam_step_scalars": (_int, [_p, _dbl, _dbl, _dbl, _p, _p]),
     "smore_sparse_update_rows_dev": (_int, [_int, _p, _p, _p, _p, _p, _p, _sz, _sz, _dbl, _dbl, _dbl, _dbl, _p, _int,
                                             _p]),

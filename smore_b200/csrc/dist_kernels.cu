@@ -23,6 +23,7 @@
 #include "bulk_copy.cuh"
 #include "dist_terms.cuh"
 #include "shared_kernels.cuh"
+#include "update_math.cuh"
 
 namespace smore {
 
@@ -748,6 +749,261 @@ __global__ void __launch_bounds__(kRowCtaThreads, 2)
 }
 
 // ----------------------------------------------------------------------------------------
+// Row-stream backward with the optimizer step folded in (Adam, row-wise second moment).
+//
+// Most rows a step touches are touched by exactly one (query, candidate) position (about 95 % at
+// the Freebase-scale benchmark).  For such a row the gradient this kernel computes IS the step's
+// merged gradient, so writing it to the gradient buffer only to have the update kernel read it
+// back - together with the parameter row this kernel has just read - is wasted traffic: per row
+// 1.6 KB written and 3.2 KB read again.  Here the warp that owns the row also copies the row of
+// the first moment into the ring (same bulk copy group as the parameter row), applies the update
+// in shared memory and sends both rows back with bulk stores; the row's entry in the step's list
+// of distinct rows is complemented (~row, negative), which the update kernel skips.  Rows with
+// several contributors take the ordinary route (bulk floating-point add into the gradient buffer,
+// updated afterwards by smore_sparse_update_rows).
+// Safe because a row with a single contributor is read by no other position of the backward pass
+// and the forward pass has finished.  The arithmetic is that of adam_rows_reg_kernel.
+// ----------------------------------------------------------------------------------------
+
+template <class Term, int NB, int NCH>
+__global__ void __launch_bounds__(kRowCtaThreads, 2)
+    row_backward_adam_bulk_kernel(RowArgs a, RowGradArgs ga, UpdateArgs ua, int64_t* __restrict__ uniq_rw, int stages) {
+  constexpr int NG = NB * Term::kNOut;
+  extern __shared__ __align__(128) unsigned char bulk_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int b = blockIdx.x / a.chunks, c = blockIdx.x - b * a.chunks;
+  const int dim4 = a.dim >> 2;
+  const unsigned row_bytes = (unsigned)dim4 * Term::kMul * 16u;
+  const unsigned stage_bytes = 2u * row_bytes;          // [parameter row | first-moment row]
+  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(bulk_smem) + warp * stages;
+  float4* sq = reinterpret_cast<float4*>(bulk_smem + bulk_ring_offset(stages));   // [kNQ][NB][dim4]
+  unsigned char* ring_all = reinterpret_cast<unsigned char*>(sq + (size_t)Term::kNQ * NB * dim4);
+  unsigned char* ring = ring_all + (size_t)warp * stages * stage_bytes;
+  if (lane == 0) {
+    for (int s = 0; s < stages; ++s) bulk::barrier_init(bars + s, 1);
+    bulk::fence_barrier_init();
+  }
+  {
+    const float4* p0 = reinterpret_cast<const float4*>(a.first + (size_t)b * NB * a.dim);
+    const float4* p1 = reinterpret_cast<const float4*>(a.second + (size_t)b * NB * a.dim);
+    for (int i = threadIdx.x; i < NB * dim4; i += kRowCtaThreads) {
+      sq[i] = __ldg(p0 + i);
+      if (Term::kNQ == 2) sq[NB * dim4 + i] = __ldg(p1 + i);
+    }
+  }
+  __syncthreads();
+  load_dyn(ua);
+  const float4* sq0 = sq;
+  const float4* sq1 = Term::kNQ == 2 ? sq + NB * dim4 : sq;
+
+  float4 gq0[NB][NCH], gq1[NB][NCH];
+#pragma unroll
+  for (int u = 0; u < NB; ++u)
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) gq0[u][j] = gq1[u][j] = z4;
+
+  const int r_begin = c * a.rows_per_cta;
+  const int r_end = min(a.K, r_begin + a.rows_per_cta);
+  const int per_warp = (r_end - r_begin + kRowCtaWarps - 1) / kRowCtaWarps;
+  const int w_begin = r_begin + warp * per_warp;
+  const int n = max(0, min(r_end, w_begin + per_warp) - w_begin);
+  const size_t pos0 = (size_t)b * a.K + w_begin;
+  const unsigned char* ent = reinterpret_cast<const unsigned char*>(a.ent);
+  const unsigned char* mom = reinterpret_cast<const unsigned char*>(ua.m);
+  unsigned char* gbase = reinterpret_cast<unsigned char*>(ga.g_rows);
+
+  struct Meta {
+    long long src, dst;
+    int single;
+    float v;          // second moment of a row that is updated here
+    float g[NG];
+  };
+  auto load_meta = [&](int first_t) {
+    Meta m;
+    m.src = 0;
+    m.dst = -1;
+    m.single = 0;
+    m.v = 0.f;
+#pragma unroll
+    for (int i = 0; i < NG; ++i) m.g[i] = 0.f;
+    const int t = first_t + lane;
+    if (t < n) {
+      const size_t pos = pos0 + t;
+      m.src = checked_row_id(a.idx, pos, a.n_rows, &g_async_status);
+      const int32_t sl = ga.slot[pos];
+      m.dst = sl;
+      m.single = (sl >= 0 && ga.slot_count != nullptr) ? (ga.slot_count[sl] == 1) : 0;
+      if (m.src < 0) {
+        m.src = 0;
+        m.dst = -1;
+        m.single = 0;
+      } else {
+        if (m.single) m.v = ua.v[m.src];
+#pragma unroll
+        for (int u = 0; u < NB; ++u) {
+          const size_t o = ((size_t)b * NB + u) * a.K + (w_begin + t);
+          m.g[u * Term::kNOut] = ga.gout0[o];
+          if (Term::kNOut == 2) m.g[u * Term::kNOut + Term::kNOut - 1] = ga.gout1[o];
+        }
+      }
+    }
+    return m;
+  };
+  // lane 0: start the copies of one row (and, for a row updated here, of its first-moment row)
+  auto issue = [&](int s, long long row, int single) {
+    unsigned char* dst = ring + (size_t)s * stage_bytes;
+    bulk::barrier_expect(bars + s, single ? stage_bytes : row_bytes);
+    bulk::load(dst, ent + (size_t)row * row_bytes, row_bytes, bars + s);
+    if (single) bulk::load(dst + row_bytes, mom + (size_t)row * row_bytes, row_bytes, bars + s);
+  };
+  Meta cur = load_meta(0), nxt = cur;
+
+  const int ahead = min(stages - 1, n);   // one slot always belongs to the stores in flight
+  for (int t = 0; t < ahead; ++t) {
+    const long long row = __shfl_sync(0xffffffffu, cur.src, t);
+    const int single = __shfl_sync(0xffffffffu, (cur.dst >= 0) ? cur.single : 0, t);
+    if (lane == 0) issue(t, row, single);
+  }
+  int slot = 0;
+  unsigned parity = 0;
+  for (int t = 0; t < n; ++t) {
+    const int tl = t & 31;
+    if (tl == 0) nxt = load_meta(t + 32);
+    bool ok = bulk::barrier_wait(bars + slot, parity);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) {
+      if (lane == 0) atomicOr(&g_async_status, kStatusCopyWait);
+      for (int k = 1; k < stages - 1 && t + k < n; ++k) {
+        const int s2 = (slot + k) % stages;
+        bulk::barrier_wait(bars + s2, s2 > slot ? parity : parity ^ 1u);
+      }
+      break;
+    }
+    float g[NG];
+#pragma unroll
+    for (int i = 0; i < NG; ++i) g[i] = __shfl_sync(0xffffffffu, cur.g[i], tl);
+    const long long dst = __shfl_sync(0xffffffffu, cur.dst, tl);
+    const long long row = __shfl_sync(0xffffffffu, cur.src, tl);
+    const int single = dst >= 0 ? __shfl_sync(0xffffffffu, cur.single, tl) : 0;
+    float4* row4 = reinterpret_cast<float4*>(ring + (size_t)slot * stage_bytes);
+    float4* mom4 = reinterpret_cast<float4*>(ring + (size_t)slot * stage_bytes + row_bytes);
+    float4 ge[Term::kMul][NCH];
+    float sumsq = 0.f;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int d4 = lane + 32 * j;
+      ge[0][j] = z4;
+      if (Term::kMul == 2) ge[Term::kMul - 1][j] = z4;
+      if (d4 < dim4) {
+        const float4 e0 = row4[d4];
+        const float4 e1 = Term::kMul == 2 ? row4[dim4 + d4] : e0;
+        float4 ge0 = z4, ge1 = z4;
+#pragma unroll
+        for (int u = 0; u < NB; ++u)
+          bwd4<Term>(g + u * Term::kNOut, e0, e1, sq0[u * dim4 + d4], sq1[u * dim4 + d4], ge0, ge1, gq0[u][j],
+                     gq1[u][j]);
+        ge[0][j] = ge0;
+        sumsq += ge0.x * ge0.x + ge0.y * ge0.y + ge0.z * ge0.z + ge0.w * ge0.w;
+        if (Term::kMul == 2) {
+          ge[Term::kMul - 1][j] = ge1;
+          sumsq += ge1.x * ge1.x + ge1.y * ge1.y + ge1.z * ge1.z + ge1.w * ge1.w;
+        }
+      }
+    }
+    float v_new = 0.f;
+    const float v_old = __shfl_sync(0xffffffffu, cur.v, tl);
+    if (single) {
+      // the row's Adam step, in place: the slot holds the parameter row and the first-moment row
+      const float g2mean = warp_sum(sumsq) / (float)ua.width;
+      v_new = v_old * ua.beta2 + g2mean * ua.omb2;
+      const float denom = sqrtf(v_new) / ua.sqrt_bc2 + ua.eps;
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const int d4 = lane + 32 * j;
+        if (d4 < dim4) {
+#pragma unroll
+          for (int part = 0; part < Term::kMul; ++part) {
+            float4 p = row4[part * dim4 + d4], m = mom4[part * dim4 + d4];
+            const float4 gg = ge[part][j];
+            adam_elem_rowwise(gg.x, p.x, m.x, denom, ua);
+            adam_elem_rowwise(gg.y, p.y, m.y, denom, ua);
+            adam_elem_rowwise(gg.z, p.z, m.z, denom, ua);
+            adam_elem_rowwise(gg.w, p.w, m.w, denom, ua);
+            row4[part * dim4 + d4] = p;
+            mom4[part * dim4 + d4] = m;
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const int d4 = lane + 32 * j;
+        if (d4 < dim4) {
+          row4[d4] = ge[0][j];
+          if (Term::kMul == 2) row4[dim4 + d4] = ge[Term::kMul - 1][j];
+        }
+      }
+    }
+    bulk::fence_async_shared();   // what the lanes wrote is visible to the copy engine
+    __syncwarp();
+    const int tn = t + stages - 1;
+    const bool same = (tn >> 5) == (t >> 5);
+    const long long next_row = __shfl_sync(0xffffffffu, same ? cur.src : nxt.src, tn & 31);
+    const int next_single = __shfl_sync(0xffffffffu, same ? ((cur.dst >= 0) ? cur.single : 0)
+                                                          : ((nxt.dst >= 0) ? nxt.single : 0), tn & 31);
+    if (lane == 0) {
+      if (single) {
+        bulk::store(const_cast<unsigned char*>(ent) + (size_t)row * row_bytes, row4, row_bytes);
+        bulk::store(const_cast<unsigned char*>(mom) + (size_t)row * row_bytes, mom4, row_bytes);
+        ua.v[row] = v_old + (v_new - v_old);
+        uniq_rw[dst] = ~(int64_t)row;       // this row's update is done: the update kernel skips it
+      } else if (dst >= 0) {
+        bulk::reduce_add_f32(gbase + (size_t)dst * row_bytes, row4, row_bytes);
+      }
+      bulk::commit_group();
+      if (tn < n) {
+        bulk::wait_group_read<1>();   // all transfers but the ones just committed have read their slots
+        const int s2 = slot == 0 ? stages - 1 : slot - 1;
+        issue(s2, next_row, next_single);
+      }
+    }
+    if (tl == 31) cur = nxt;
+    if (++slot == stages) {
+      slot = 0;
+      parity ^= 1u;
+    }
+  }
+  if (lane == 0) bulk::wait_group<0>();
+  __syncthreads();
+
+  // fold the warps' query gradients through the (now idle) ring, in warp order
+  float4* red = reinterpret_cast<float4*>(ring_all);
+  const size_t per_warp4 = (size_t)NB * Term::kNQ * dim4;
+#pragma unroll
+  for (int u = 0; u < NB; ++u)
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int d4 = lane + 32 * j;
+      if (d4 < dim4) {
+        red[warp * per_warp4 + (size_t)u * Term::kNQ * dim4 + d4] = gq0[u][j];
+        if (Term::kNQ == 2) red[warp * per_warp4 + (size_t)u * Term::kNQ * dim4 + dim4 + d4] = gq1[u][j];
+      }
+    }
+  __syncthreads();
+  for (size_t i = threadIdx.x; i < per_warp4; i += kRowCtaThreads) {
+    float4 acc = red[i];
+    for (int w = 1; w < kRowCtaWarps; ++w) add4(acc, red[w * per_warp4 + i]);
+    const size_t u = i / ((size_t)Term::kNQ * dim4), rem = i - u * Term::kNQ * dim4;
+    const bool second = rem >= (size_t)dim4;
+    float* base = second ? ga.g_second : ga.g_first;
+    float4* out = reinterpret_cast<float4*>(base + ((size_t)b * NB + u) * a.dim) + (rem - (second ? dim4 : 0));
+    if (ga.query_atomic) atomicAdd(out, acc);
+    else *out = acc;
+  }
+}
+
+// ----------------------------------------------------------------------------------------
 // Union queries: NB branches of every query scored against the same candidate rows.
 // The reference runs the op once per branch and stacks the results (a Python loop over the
 // branch axis of a 4-D query operand); here one pass over the rows serves all branches, and the
@@ -1062,6 +1318,59 @@ static int launch_backward_bulk(const Shape& s, RowArgs a, RowGradArgs ga, int n
   return 1;
 }
 
+constexpr int kUnionBranches = 2;
+
+// Launches row_backward_adam_bulk_kernel when the shape suits it.  Returns 1 when launched, 0 when the
+// caller should use the ordinary backward + update, a negative status on failure.
+template <class Term, int NB>
+static int launch_backward_adam(const Shape& s, RowArgs a, RowGradArgs ga, const UpdateArgs& ua, int64_t* uniq,
+                                int nch, cudaStream_t st) {
+  const size_t row_bytes = s.dim * Term::kMul * sizeof(float);
+  if ((nch != 4 && nch != 8) || row_bytes < 1024) return 0;
+  const int need = (NB * Term::kNQ + 2 * Term::kMul - 1) / (2 * Term::kMul);   // ring must hold the final fold
+  const size_t q_bytes = (size_t)NB * Term::kNQ * s.dim * sizeof(float);
+  // as many stages (3..5) as fit two CTAs per SM: every stage holds a parameter row and a moment row
+  int stages = 5;
+  while (stages > 3 && bulk_ring_offset(stages) + q_bytes + (size_t)kRowCtaWarps * stages * 2 * row_bytes > 110 * 1024)
+    --stages;
+  stages = std::max(stages, need);
+  const size_t smem = bulk_ring_offset(stages) + q_bytes + (size_t)kRowCtaWarps * stages * 2 * row_bytes;
+  if (smem > 200 * 1024) return 0;      // wide rows (RotatE, 4000 bytes): one CTA per SM
+  a.rows_per_cta = (int)std::min<size_t>(s.num, 512);
+  a.chunks = (int)((s.num + a.rows_per_cta - 1) / a.rows_per_cta);
+  ga.query_atomic = a.chunks > 1;
+  if (a.chunks > 1) {
+    const size_t bytes = s.bsize * NB * s.dim * sizeof(float);
+    if (cudaMemsetAsync(ga.g_first, 0, bytes, st) != cudaSuccess ||
+        (Term::kNQ == 2 && cudaMemsetAsync(ga.g_second, 0, bytes, st) != cudaSuccess))
+      return fail(SMORE_ERR_CUDA, "row_backward_adam_bulk_kernel: cudaMemsetAsync failed");
+  }
+  auto kern = nch == 4 ? row_backward_adam_bulk_kernel<Term, NB, 4> : row_backward_adam_bulk_kernel<Term, NB, 8>;
+  if (int rc = allow_large_smem(kern, 200 * 1024)) return rc;
+  kern<<<(unsigned)(s.bsize * a.chunks), kRowCtaThreads, smem, st>>>(a, ga, ua, uniq, stages);
+  if (int rc = check_launch("row_backward_adam_bulk_kernel")) return rc;
+  return 1;
+}
+
+template <class Term>
+static int backward_adam_common(size_t branches, const Shape& s, const float* gout0, const float* gout1, float* table,
+                                const int64_t* idx, const float* first, const float* second, const int32_t* slot,
+                                const int32_t* slot_count, float* g_rows, float* g_first, float* g_second,
+                                const UpdateArgs& ua, int64_t* uniq, cudaStream_t st) {
+  if (Term::kNQ == 1) {
+    second = first;
+    g_second = g_first;
+  }
+  const bool aligned = aligned16(table) && aligned16(first) && aligned16(second) && aligned16(g_rows) &&
+                       aligned16(g_first) && aligned16(g_second) && aligned16(ua.m);
+  const RowPlan p = plan_rows(s, aligned);
+  if (p.chunks == 0) return 0;
+  RowArgs a{table, idx, first, second, (int)s.num, (int)s.dim, p.rows_per_cta, p.chunks, p.wrows, (long long)s.n_rows};
+  RowGradArgs ga{gout0, gout1, nullptr, slot, slot_count, g_rows, g_first, g_second, 0};
+  if (branches == 1) return launch_backward_adam<Term, 1>(s, a, ga, ua, uniq, p.nch, st);
+  return launch_backward_adam<Term, kUnionBranches>(s, a, ga, ua, uniq, p.nch, st);
+}
+
 template <class Term>
 static int launch_forward(const Shape& s, const float* ent, const int64_t* idx, const float* first,
                           const float* second, float* dst0, float* dst1, cudaStream_t st) {
@@ -1161,8 +1470,6 @@ static int launch_backward(const Shape& s, const float* gout0, const float* gout
       a, gout0, gout1, g_first, g_second);
   return check_launch("cell_backward kernels", 2);
 }
-
-constexpr int kUnionBranches = 2;
 
 static int check_union(const char* what, size_t branches, const Shape& s, bool aligned, RowPlan* p) {
   if (branches != kUnionBranches)
@@ -1398,6 +1705,60 @@ int smore_union_backward_rows(int dist_id, const float* gout0, const float* gout
                                               g_rows, g_first, g_second, st);
   SMORE_DISPATCH(dist_id, launch_backward_union<Term>(branches, s, gout0, gout0, table, idx, first, second, slot,
                                                       slot_count, g_rows, g_first, g_second, st));
+}
+
+int smore_rows_backward_fused_adam(int dist_id, const float* gout0, const float* gout1, float* table,
+                                   const int64_t* idx, size_t n_table_rows, const float* first, const float* second,
+                                   const int32_t* slot, const int32_t* slot_count, float* g_rows, float* g_first,
+                                   float* g_second, size_t branches, size_t bsize, size_t num, size_t dim, float* m,
+                                   float* v, int64_t* uniq, double lr, double beta1, double beta2, double eps,
+                                   int64_t step, const float* step_scalars, void* stream) {
+  const bool both = dist_id == SMORE_DIST_BOX_BOTH;
+  if (!both && (dist_id < 0 || dist_id >= SMORE_DIST_COUNT))
+    return fail(SMORE_ERR_BAD_DIST, "unknown distance id %d", dist_id);
+  const bool two = both || needs_second(dist_id);
+  if (!gout0 || (both && !gout1) || !table || !idx || !first || !slot || !slot_count || !g_rows || !g_first || !m ||
+      !v || !uniq || (two && (!second || !g_second)))
+    return fail(SMORE_ERR_NULL, "rows_backward_fused_adam: required pointer is NULL");
+  if (branches != 1 && branches != (size_t)kUnionBranches)
+    return fail(SMORE_ERR_BAD_SHAPE, "rows_backward_fused_adam: 1 or %d query branches", kUnionBranches);
+  if (!step_scalars && step < 1) return fail(SMORE_ERR_BAD_SHAPE, "adam step must be >= 1");
+  const Shape s{bsize, num, bsize, num, bsize, 1, dim, n_table_rows};
+  if (int rc = validate_shape(s)) return rc;
+  const size_t mul = (dist_id == SMORE_DIST_ROTATE || dist_id == SMORE_DIST_COMPLEX) ? 2 : 1;
+  UpdateArgs ua;
+  ua.table = table; ua.m = m; ua.v = v; ua.uniq = nullptr; ua.g_rows = nullptr; ua.n_unique = nullptr;
+  ua.width = dim * mul;
+  set_hyper(ua, lr, beta1, beta2, eps, step_scalars ? 1 : step, 1);
+  ua.dyn = step_scalars;
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc = 0;
+  if (both) {
+    rc = backward_adam_common<TermBoxBoth>(branches, s, gout0, gout1, table, idx, first, second, slot, slot_count, g_rows,
+                                           g_first, g_second, ua, uniq, st);
+  } else {
+    switch (dist_id) {
+#define FUSED_CASE(ID, TERM)                                                                                        \
+  case ID:                                                                                                          \
+    rc = backward_adam_common<TERM>(branches, s, gout0, gout0, table, idx, first, second, slot, slot_count, g_rows, \
+                                    g_first, g_second, ua, uniq, st);                                               \
+    break;
+      FUSED_CASE(SMORE_DIST_BOX_OUT, TermBoxOut)
+      FUSED_CASE(SMORE_DIST_BOX_IN, TermBoxIn)
+      FUSED_CASE(SMORE_DIST_ROTATE, TermRotate)
+      FUSED_CASE(SMORE_DIST_L1, TermL1)
+      FUSED_CASE(SMORE_DIST_L2, TermL2)
+      FUSED_CASE(SMORE_DIST_COMPLEX, TermComplex)
+      FUSED_CASE(SMORE_DIST_DISTMULT, TermDistmult)
+#undef FUSED_CASE
+    }
+  }
+  if (rc < 0) return rc;
+  if (rc == 0)
+    return fail(SMORE_ERR_BAD_SHAPE,
+                "rows_backward_fused_adam: shape not covered (rows of 1 KB to about 4 KB, dim a multiple of 4, at "
+                "least 4 rows per query, 16-byte aligned operands); use the separate backward and update calls");
+  return SMORE_OK;
 }
 
 extern "C" int smore_peer_async_status(int* status);   // peer_kernels.cu (not part of the public header)

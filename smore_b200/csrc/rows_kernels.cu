@@ -398,6 +398,10 @@ __global__ void __launch_bounds__(256) adam_rows_reg_kernel(UpdateArgs a) {
   long long row = u < nu ? a.uniq[u] : 0;
   for (; u < nu; u += warps) {
     const long long next_row = (u + warps < nu) ? a.uniq[u + warps] : 0;
+    if (row < 0) {     // updated already, inside the backward pass (smore_rows_backward_fused_adam)
+      row = next_row;
+      continue;
+    }
     const float4* g4 = reinterpret_cast<const float4*>(a.g_rows + u * a.width);
     float4* p4 = reinterpret_cast<float4*>(a.table + (size_t)row * a.width);
     float4* m4 = reinterpret_cast<float4*>(a.m + (size_t)row * a.width);
@@ -457,6 +461,7 @@ __global__ void __launch_bounds__(256) sparse_update_rows_kernel(UpdateArgs a) {
   const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
   const size_t W = a.width;
   for (size_t u = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); u < nu; u += warps) {
+    if (a.uniq[u] < 0) continue;   // updated already, inside the backward pass
     const size_t row = (size_t)a.uniq[u];
     const float* g = a.g_rows + u * W;
     float* p = a.table + row * W;

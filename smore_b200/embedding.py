@@ -206,7 +206,7 @@ class LazyRows(object):
 
 
 class _Lookup(object):
-    __slots__ = ("idx", "n", "name", "order", "offset", "plan", "received", "key")
+    __slots__ = ("idx", "n", "name", "order", "offset", "plan", "received", "key", "n_consumers")
 
     def __init__(self, idx, name, order):
         self.idx = idx          # int64 [n] on the table's device
@@ -217,6 +217,7 @@ class _Lookup(object):
         self.plan = None
         self.received = False   # a gradient producer has run for this lookup
         self.key = None         # identity of the caller's id tensor (sharded tables with prefetch)
+        self.n_consumers = 0    # distance ops that took this lookup's rows in the forward pass
 
 
 class _StepPlan(object):
@@ -370,6 +371,35 @@ class EmbeddingOptimizer(object):
         self._drop_plans()
         self.grad_list = []    # kept for interface parity; gradients never queue up here
         self.has_grad_list = []
+        self._fused_lr = None          # set by announce_lr(): rows may be updated inside the backward pass
+        self._step_advanced = False    # the device-side step counter was already advanced for this step
+
+    def announce_lr(self, lr):
+        """Optional, after zero_grad() and before the step's backward pass: tells the optimizer the
+        learning rate apply_grad(lr) will be called with.  Table-resident lookups consumed by exactly
+        one distance op may then have the rows that only ONE position of the step touches updated
+        inside that op's backward kernel (smore_rows_backward_fused_adam) instead of writing their
+        gradient out for apply_grad to read back; the result is the same update.  Only the Adam
+        optimizer with a row-wise second moment does this; others ignore the call.  A step that
+        announced a learning rate must end with apply_grad of the same value (some rows have
+        already moved)."""
+        if self.opt_name != "adam" or not self.squeeze:
+            return
+        self._fused_lr = float(lr)
+        if getattr(self, "_step_dev", None) is not None and not self._step_advanced:
+            self._advance_device_step(lr)
+            self._step_advanced = True
+
+    def fused_update_args(self, lookup, plan):
+        """Arguments of the in-backward update for `lookup`, or None when it does not apply."""
+        if getattr(self, "_fused_lr", None) is None or lookup.n_consumers != 1 or lookup.received:
+            return None
+        if len(self._plans) != 1 or plan is not self._plans[0] or self.share_optim_stats:
+            return None
+        dev_step = getattr(self, "_step_dev", None) is not None
+        return {"m": self.state("state_sum_fo"), "v": self.state("state_sum_sq"), "uniq": plan.uniq,
+                "lr": self._fused_lr, "step": 1 if dev_step else int(self.step) + 1,
+                "step_scalars": self._step_scalars if dev_step else None}
 
     def _device_indices(self, indices):
         idx = indices.reshape(-1)
@@ -460,7 +490,8 @@ class EmbeddingOptimizer(object):
     def _run_update(self, opt_name, m, v, uniq, g_rows, n_unique, capacity, lr):
         dev = self.table.device
         if getattr(self, "_step_dev", None) is not None:
-            self._advance_device_step(lr)
+            if not getattr(self, "_step_advanced", False):
+                self._advance_device_step(lr)
             with torch.cuda.device(dev), _lib.timed("sparse_update_rows"):
                 _lib.check(_lib.lib().smore_sparse_update_rows_dev(
                     _lib.OPT_IDS[opt_name], self.table.data_ptr(), None if m is None else m.data_ptr(),
@@ -517,9 +548,12 @@ class EmbeddingOptimizer(object):
     def apply_grad(self, lr):
         """embed_optimizer.py:155-163: the step counter advances even when nothing was looked up."""
         self.step += 1
+        if getattr(self, "_fused_lr", None) is not None and float(lr) != self._fused_lr:
+            raise _lib.SmoreError("apply_grad(%r) after announce_lr(%r): rows updated inside the backward pass "
+                                  "used the announced value" % (lr, self._fused_lr))
         if not self._plans:
             self._pending = []
-            if getattr(self, "_step_dev", None) is not None:
+            if getattr(self, "_step_dev", None) is not None and not getattr(self, "_step_advanced", False):
                 self._advance_device_step(lr)
             return
         plan = self._plans[0] if len(self._plans) == 1 else self._merge_plans()

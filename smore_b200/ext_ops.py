@@ -121,6 +121,33 @@ def _check_rows_operands(name, rows, first, second):
     return be, ne
 
 
+def _fused_backward(name_or_id, owner, lookup, plan, table, row_ids, first, second, gouts, g_first, g_second, branches,
+                    bsize, num, dim):
+    """Backward with the Adam step of single-contributor rows folded in, when the owning optimizer
+    announced its learning rate for this step and the shape is covered.  True when it ran."""
+    fn = getattr(owner, "fused_update_args", None)
+    fu = fn(lookup, plan) if fn is not None else None
+    if fu is None:
+        return False
+    L = _lib.lib()
+    dist_id = name_or_id if isinstance(name_or_id, int) else (
+        _lib.BOX_BOTH_ID if name_or_id == "box_both" else _lib.DIST_IDS[name_or_id])
+    if _lib._timer is not None:
+        _lib.note("n_single", (plan.counts == 1).sum())
+    rc = L.smore_rows_backward_fused_adam(
+        dist_id, gouts[0].data_ptr(), gouts[1].data_ptr() if len(gouts) > 1 else None, table.data_ptr(),
+        row_ids.data_ptr(), table.shape[0], first.data_ptr(), None if second is None else second.data_ptr(),
+        plan.slot_of(lookup).data_ptr(), plan.counts.data_ptr(), plan.g_rows.data_ptr(), g_first.data_ptr(),
+        None if g_second is None else g_second.data_ptr(), branches, bsize, num, dim, fu["m"].data_ptr(),
+        fu["v"].data_ptr(), fu["uniq"].data_ptr(), fu["lr"], 0.9, 0.999, 1e-8, fu["step"],
+        None if fu["step_scalars"] is None else fu["step_scalars"].data_ptr(),
+        torch.cuda.current_stream(table.device).cuda_stream)
+    if rc == -2:          # SMORE_ERR_BAD_SHAPE: not covered, nothing was enqueued
+        return False
+    _lib.check(rc, "smore_rows_backward_fused_adam")
+    return True
+
+
 class _RowsDistFunc(torch.autograd.Function):
     """A distance whose entity operand is table rows named by index.  `dummy` is the owning
     optimizer's one-element parameter: it makes autograd call backward even when no query
@@ -132,6 +159,7 @@ class _RowsDistFunc(torch.autograd.Function):
         second = None if second is None else second.contiguous()
         be, ne = _check_rows_operands(name, rows, first, second)
         owner, lookup = rows.owner, rows.lookup
+        lookup.n_consumers += 1
         table, row_ids = owner.rows_operands(lookup)
         bc, nc, dim = first.shape
         bsize, num = max(be, bc), max(ne, nc)
@@ -172,14 +200,21 @@ class _RowsDistFunc(torch.autograd.Function):
         plan = owner.plan_for(lookup)
         # the first gradient producer of a lookup may store rows that nothing else touches; any
         # later one over the same positions (another union branch) has to add to what is there
-        counts_ptr = None if lookup.received else plan.counts.data_ptr()
-        lookup.received = True
-        slot = plan.slot_of(lookup)
         g_first = torch.empty_like(first)
         g_second = torch.empty_like(second) if ctx.two else None
         gouts = [g.contiguous() for g in gouts]
         L = _lib.lib()
         st = torch.cuda.current_stream(table.device).cuda_stream
+        bsize, num, be, ne, bc, nc, dim = ctx.sizes
+        if be == bsize and ne == num and bc == bsize and nc == 1 and num >= 16:
+            with torch.cuda.device(table.device), _lib.timed("rows_backward"):
+                if _fused_backward(ctx.name, owner, lookup, plan, table, row_ids, first, second, gouts, g_first,
+                                   g_second, 1, bsize, num, dim):
+                    lookup.received = True
+                    return None, None, None, g_first, g_second
+        counts_ptr = None if lookup.received else plan.counts.data_ptr()
+        lookup.received = True
+        slot = plan.slot_of(lookup)
         with torch.cuda.device(table.device), _lib.timed("rows_backward" if ctx.sizes[1] >= 16 else "rows_backward_few"):
             if ctx.name == "box_both":
                 _lib.check(L.smore_box_backward(gouts[0].data_ptr(), gouts[1].data_ptr(), table.data_ptr(),
@@ -208,6 +243,7 @@ class _RowsUnionFunc(torch.autograd.Function):
         first = first.contiguous()
         second = None if second is None else second.contiguous()
         owner, lookup = rows.owner, rows.lookup
+        lookup.n_consumers += 1
         table, row_ids = owner.rows_operands(lookup)
         B, U, _, dim = first.shape
         num = rows.as_3d()[1]
@@ -238,12 +274,18 @@ class _RowsUnionFunc(torch.autograd.Function):
         owner, lookup = ctx.rows.owner, ctx.rows.lookup
         table, row_ids = owner.rows_operands(lookup)
         plan = owner.plan_for(lookup)
-        counts_ptr = None if lookup.received else plan.counts.data_ptr()
-        lookup.received = True
-        slot = plan.slot_of(lookup)
         g_first = torch.empty_like(first)
         g_second = torch.empty_like(second) if ctx.two else None
         gouts = [g.contiguous() for g in gouts]
+        U, B, num, dim = ctx.sizes
+        with torch.cuda.device(table.device), _lib.timed("rows_backward_union"):
+            if _fused_backward(ctx.dist_id, owner, lookup, plan, table, row_ids, first, second, gouts, g_first,
+                               g_second, U, B, num, dim):
+                lookup.received = True
+                return None, None, None, g_first, g_second
+        counts_ptr = None if lookup.received else plan.counts.data_ptr()
+        lookup.received = True
+        slot = plan.slot_of(lookup)
         with torch.cuda.device(table.device), _lib.timed("rows_backward_union"):
             _lib.check(_lib.lib().smore_union_backward_rows(
                 ctx.dist_id, gouts[0].data_ptr(), gouts[1].data_ptr() if len(gouts) > 1 else None, table.data_ptr(),

@@ -147,6 +147,60 @@ def test_training_steps_match_native_path(name, lazy):
                 close(p1.grad.cpu().numpy(), p2.grad.cpu().numpy(), RTOL_ATOMIC, what="grad of " + n1)
 
 
+@pytest.mark.parametrize("n_rows", [300, 60000], ids=["many_shared_rows", "mostly_single_rows"])
+@pytest.mark.parametrize("name", ["box", "box_full_dim", "rotate_rowwise"])
+def test_update_inside_backward_equals_separate_update(name, n_rows):
+    """announce_lr(): rows touched by one position of a step are updated by the backward kernel itself.
+    Same steps with and without it: losses, table, both Adam states and the dense gradients agree
+    (the arithmetic is the same; only rows with several contributors take the gradient buffer)."""
+    from smore_b200 import embedding, ext_ops
+    cfgs = {
+        "box": dict(SMALL["box"], dim=320, structures=["1p", "2i", "2u", "up", "3p"]),
+        "box_full_dim": dict(SMALL["box_full_v"], squeeze=True, structures=["1p", "2u", "pi"]),
+        "rotate_rowwise": dict(SMALL["rotate"], squeeze=True, structures=["1p", "2p"]),
+    }
+    cfg = cfgs[name]
+    dev = torch.device("cuda", 0)
+    models = []
+    for fused in (True, False):
+        torch.manual_seed(5)
+        m = bench.QueryModel(cfg, n_rows, dev, ext_ops, embedding, lazy=True)
+        m.fused_update = fused
+        m.train()
+        models.append(m)
+    models[1].load_state_dict(models[0].state_dict())
+    a, b = models
+    calls = {"n": 0}
+    real = ext_ops._fused_backward
+
+    def counting(*args, **kw):
+        ran = real(*args, **kw)
+        calls["n"] += int(ran)
+        return ran
+
+    ext_ops._fused_backward = counting
+    try:
+        for step, s in enumerate(cfg["structures"]):
+            pos, neg, q = (t.cuda() for t in bench.make_batch(cfg, n_rows, s, seed=40 + step))
+            la = bench.train_step(a, pos, neg, q, s)
+            lb = bench.train_step(b, pos, neg, q, s)
+            close(la.item(), lb.item(), RTOL, what="loss %s" % s)
+            ta, tb = a.entity_embedding.embedding.data, b.entity_embedding.embedding.data
+            close(ta.cpu().numpy(), tb.cpu().numpy(), RTOL, what="table after %s" % s)
+            close(a.embed_opt.state("state_sum_fo").cpu().numpy(), b.embed_opt.state("state_sum_fo").cpu().numpy(),
+                  RTOL, what="m after %s" % s)
+            close(a.embed_opt.state("state_sum_sq").cpu().numpy(), b.embed_opt.state("state_sum_sq").cpu().numpy(),
+                  RTOL, what="v after %s" % s)
+            for (n1, p1), (n2, p2) in zip(a.named_parameters(), b.named_parameters()):
+                if p1.requires_grad and p1.grad is not None:
+                    close(p1.grad.cpu().numpy(), p2.grad.cpu().numpy(), RTOL_ATOMIC, what="grad of " + n1)
+            # keep the two models in lock step (torch's dense Adam amplifies rounding-sized differences)
+            b.load_state_dict(a.state_dict())
+    finally:
+        ext_ops._fused_backward = real
+    assert calls["n"] == len(cfg["structures"])       # the fused kernel took every step's candidate rows
+
+
 def test_gqe_fb15k237_exact_shape_step():
     """The GQE configuration at its exact size (14,505 x 64 table, 237 relations, 512 one-hop queries,
     128 negatives each, gamma 12): one whole training step against the torch-native path."""
