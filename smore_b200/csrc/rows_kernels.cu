@@ -394,62 +394,68 @@ __global__ void __launch_bounds__(256) adam_rows_reg_kernel(UpdateArgs a) {
   const size_t nu = (size_t)max(a.n_unique[0], 0);
   const size_t warps = (size_t)gridDim.x * (blockDim.x >> 5);
   const int w4 = (int)(a.width >> 2);
-  size_t u = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  long long row = u < nu ? a.uniq[u] : 0;
-  for (; u < nu; u += warps) {
-    const long long next_row = (u + warps < nu) ? a.uniq[u + warps] : 0;
-    if (row < 0) {     // updated already, inside the backward pass (smore_rows_backward_fused_adam)
-      row = next_row;
-      continue;
-    }
-    const float4* g4 = reinterpret_cast<const float4*>(a.g_rows + u * a.width);
-    float4* p4 = reinterpret_cast<float4*>(a.table + (size_t)row * a.width);
-    float4* m4 = reinterpret_cast<float4*>(a.m + (size_t)row * a.width);
-    float4* v4 = ROWWISE ? nullptr : reinterpret_cast<float4*>(a.v + (size_t)row * a.width);
-    float4 g[NCH], p[NCH], m[NCH], v[NCH];
+  // a warp takes kBatch consecutive entries of the list at a time: one read of their row ids, then the
+  // rows one after the other (small batches keep the warps' loads even).  Entries with a negative id
+  // were updated inside the backward pass (smore_rows_backward_fused_adam) and cost nothing here
+  // beyond that read.
+  constexpr int kBatch = 8;
+  for (size_t u0 = ((size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * kBatch; u0 < nu;
+       u0 += warps * kBatch) {
+    const long long my_row = (lane < kBatch && u0 + lane < nu) ? a.uniq[u0 + lane] : -1;
+    unsigned live = __ballot_sync(0xffffffffu, my_row >= 0);
+    while (live) {
+      const int l = __ffs(live) - 1;
+      live &= live - 1;
+      const long long row = __shfl_sync(0xffffffffu, my_row, l);
+      const size_t u = u0 + l;
+      const float4* g4 = reinterpret_cast<const float4*>(a.g_rows + u * a.width);
+      float4* p4 = reinterpret_cast<float4*>(a.table + (size_t)row * a.width);
+      float4* m4 = reinterpret_cast<float4*>(a.m + (size_t)row * a.width);
+      float4* v4 = ROWWISE ? nullptr : reinterpret_cast<float4*>(a.v + (size_t)row * a.width);
+      float4 g[NCH], p[NCH], m[NCH], v[NCH];
 #pragma unroll
-    for (int j = 0; j < NCH; ++j) {
-      const int d = lane + 32 * j;
-      if (d < w4) {
-        g[j] = __ldcs(g4 + d);
-        p[j] = p4[d];
-        m[j] = m4[d];
-        if (!ROWWISE) v[j] = v4[d];
-      }
-    }
-    float denom = 0.f, v_old = 0.f, v_new = 0.f;
-    if (ROWWISE) {
-      v_old = a.v[row];
-      float s = 0.f;
-#pragma unroll
-      for (int j = 0; j < NCH; ++j)
-        if (lane + 32 * j < w4) s += g[j].x * g[j].x + g[j].y * g[j].y + g[j].z * g[j].z + g[j].w * g[j].w;
-      const float g2mean = warp_sum(s) / (float)a.width;
-      v_new = v_old * a.beta2 + g2mean * a.omb2;
-      denom = sqrtf(v_new) / a.sqrt_bc2 + a.eps;
-    }
-#pragma unroll
-    for (int j = 0; j < NCH; ++j) {
-      const int d = lane + 32 * j;
-      if (d < w4) {
-        if (ROWWISE) {
-          adam_elem_rowwise(g[j].x, p[j].x, m[j].x, denom, a);
-          adam_elem_rowwise(g[j].y, p[j].y, m[j].y, denom, a);
-          adam_elem_rowwise(g[j].z, p[j].z, m[j].z, denom, a);
-          adam_elem_rowwise(g[j].w, p[j].w, m[j].w, denom, a);
-        } else {
-          adam_elem(g[j].x, p[j].x, m[j].x, v[j].x, a);
-          adam_elem(g[j].y, p[j].y, m[j].y, v[j].y, a);
-          adam_elem(g[j].z, p[j].z, m[j].z, v[j].z, a);
-          adam_elem(g[j].w, p[j].w, m[j].w, v[j].w, a);
-          v4[d] = v[j];
+      for (int j = 0; j < NCH; ++j) {
+        const int d = lane + 32 * j;
+        if (d < w4) {
+          g[j] = __ldcs(g4 + d);
+          p[j] = p4[d];
+          m[j] = m4[d];
+          if (!ROWWISE) v[j] = v4[d];
         }
-        p4[d] = p[j];
-        m4[d] = m[j];
       }
+      float denom = 0.f, v_old = 0.f, v_new = 0.f;
+      if (ROWWISE) {
+        v_old = a.v[row];
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < NCH; ++j)
+          if (lane + 32 * j < w4) s += g[j].x * g[j].x + g[j].y * g[j].y + g[j].z * g[j].z + g[j].w * g[j].w;
+        const float g2mean = warp_sum(s) / (float)a.width;
+        v_new = v_old * a.beta2 + g2mean * a.omb2;
+        denom = sqrtf(v_new) / a.sqrt_bc2 + a.eps;
+      }
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const int d = lane + 32 * j;
+        if (d < w4) {
+          if (ROWWISE) {
+            adam_elem_rowwise(g[j].x, p[j].x, m[j].x, denom, a);
+            adam_elem_rowwise(g[j].y, p[j].y, m[j].y, denom, a);
+            adam_elem_rowwise(g[j].z, p[j].z, m[j].z, denom, a);
+            adam_elem_rowwise(g[j].w, p[j].w, m[j].w, denom, a);
+          } else {
+            adam_elem(g[j].x, p[j].x, m[j].x, v[j].x, a);
+            adam_elem(g[j].y, p[j].y, m[j].y, v[j].y, a);
+            adam_elem(g[j].z, p[j].z, m[j].z, v[j].z, a);
+            adam_elem(g[j].w, p[j].w, m[j].w, v[j].w, a);
+            v4[d] = v[j];
+          }
+          p4[d] = p[j];
+          m4[d] = m[j];
+        }
+      }
+      if (ROWWISE && lane == 0) a.v[row] = v_old + (v_new - v_old);
     }
-    if (ROWWISE && lane == 0) a.v[row] = v_old + (v_new - v_old);
-    row = next_row;
   }
 }
 
