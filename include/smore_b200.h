@@ -383,6 +383,53 @@ SMORE_API int smore_filtered_ranks(const float* logits, size_t n_queries, size_t
                          size_t max_answers, int64_t* ranks, void* workspace, size_t workspace_bytes,
                          void* stream);
 
+/* The evaluation step in one call: the n_queries queries are scored against every row of `table`
+ * ([n_candidates, mul*dim], the whole entity table) and the filtered ranks of their answers are
+ * counted from the scoring tiles directly; the [n_queries, n_candidates] logits are never written.
+ * Replaces the model call of train_process.py:117 (custom_cal_logit on all entities) together with
+ * the ranking block :120-141.  first / second: [n_queries, dim] query operands.
+ * dist_id selects the model's logit: SMORE_DIST_BOX_BOTH gamma - d_out - cen * d_in (box.py:157-164);
+ * SMORE_DIST_L1 / SMORE_DIST_ROTATE gamma - d (vec.py:85-90, rotate.py:137-142); SMORE_DIST_L2
+ * gamma - sqrt(d); SMORE_DIST_COMPLEX / SMORE_DIST_DISTMULT the similarity itself (complex.py:140-149),
+ * each with the roundings of the separate torch operations.  Ranks equal smore_filtered_ranks on the
+ * logits the distance ops and those torch operations would have produced.  answer_* / ranks /
+ * max_answers as for smore_filtered_ranks; at least 8 queries, 8 candidates and 8 answers in all,
+ * dim a multiple of 4 (SMORE_ERR_BAD_SHAPE otherwise: score and rank separately).
+ * workspace: smore_score_filtered_ranks_workspace_bytes(n_queries, n_answers) bytes, 256-byte aligned. */
+SMORE_API size_t smore_score_filtered_ranks_workspace_bytes(size_t n_queries, size_t n_answers);
+SMORE_API int smore_score_filtered_ranks(int dist_id, const float* table, size_t n_candidates, const float* first,
+                               const float* second, size_t n_queries, size_t dim, double gamma, double cen,
+                               const int64_t* answer_ptr, const int64_t* answer_ids, size_t n_answers,
+                               size_t max_answers, int64_t* ranks, void* workspace, size_t workspace_bytes,
+                               void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Negative sampling on the GPU (the step before the row lookups).
+ * The reference draws them on host threads: per query `k` entity ids that are not answers of the
+ * query, uniformly or through an alias table of degree-proportional weights
+ * (naive_sampler.cpp:28-50, alias_method.cpp:33-99), or one shared list per batch with a mask of
+ * the entries that are answers (sampler.cpp:90-99, naive_sampler.cpp:33-38).  Its generator is
+ * seeded from the clock (utils.cpp:33-39); here the draws are a pure function of (seed, offset,
+ * position): Philox 4x32-10 keyed by `seed`, counter `offset + position`.
+ *
+ * smore_alias_build: HOST routine (host pointers, n entries each): the alias tables of `weights`
+ * by the reference's procedure, so that the tables are identical to the reference's.
+ * smore_sample_negatives: negatives[b, j] for b < n_queries, j < k.  prob_small / choice_small /
+ * choice_large: device copies of the alias tables, or all NULL for uniform draws.  answer_ptr
+ * [n_queries + 1] / answer_ids: per query its answers in ascending order (CSR, device), or both NULL;
+ * a draw that is an answer is repeated (at most 64 times).  Advance `offset` by n_queries * k per
+ * call to continue the stream.
+ * smore_negative_mask: is_negative[b, j] = 0.0 if negatives[j] is an answer of query b, else 1.0.
+ * ------------------------------------------------------------------------------------------ */
+SMORE_API int smore_alias_build(const double* weights, size_t n, double* prob_small, int64_t* choice_small,
+                      int64_t* choice_large);
+SMORE_API int smore_sample_negatives(uint64_t seed, uint64_t offset, size_t n_entities, const double* prob_small,
+                           const int64_t* choice_small, const int64_t* choice_large,
+                           const int64_t* answer_ptr, const int64_t* answer_ids, size_t n_queries, size_t k,
+                           int64_t* negatives, void* stream);
+SMORE_API int smore_negative_mask(const int64_t* negatives, size_t k, const int64_t* answer_ptr,
+                        const int64_t* answer_ids, size_t n_queries, float* is_negative, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Dot-product scoring of B queries against ONE shared set of K candidate rows on the tensor
  * cores (tcgen05 / TMEM through CUTLASS sm100 templates).  DistMult and ComplEx scores are inner

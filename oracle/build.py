@@ -118,10 +118,10 @@ def build_reference(reference_dir, force=False):
 
 def build_ref_kg(reference_dir, force=False):
     """oracle/_ref/libsmore_ref_kg.so: the reference's knowledge-graph container (its own
-    knowledge_graph.cpp and utils.cpp, compiled where they lie) behind ref_kg_driver.cpp."""
+    knowledge_graph.cpp, alias_method.cpp and utils.cpp, compiled where they lie) behind ref_kg_driver.cpp."""
     import sysconfig
     smp = os.path.join(reference_dir, "smore", "cpp_sampler")
-    srcs = [os.path.join(smp, "src", "lib", "knowledge_graph.cpp"), os.path.join(smp, "src", "lib", "utils.cpp")]
+    srcs = [os.path.join(smp, "src", "lib", n) for n in ("knowledge_graph.cpp", "utils.cpp", "alias_method.cpp")]
     if not all(os.path.isfile(s) for s in srcs):
         return []
     try:

@@ -59,6 +59,11 @@ SIGNATURES = {
                                          _p, _p, _p, _p, _p, _p, _p]),
     "smore_filtered_ranks_workspace_bytes": (_sz, [_sz]),
     "smore_filtered_ranks": (_int, [_p, _sz, _sz, _p, _p, _sz, _sz, _p, _p, _sz, _p]),
+    "smore_score_filtered_ranks_workspace_bytes": (_sz, [_sz, _sz]),
+    "smore_score_filtered_ranks": (_int, [_int, _p, _sz, _p, _p, _sz, _sz, _dbl, _dbl, _p, _p, _sz, _sz, _p, _p, _sz, _p]),
+    "smore_alias_build": (_int, [_p, _sz, _p, _p, _p]),
+    "smore_sample_negatives": (_int, [ctypes.c_uint64, ctypes.c_uint64, _sz, _p, _p, _p, _p, _p, _sz, _sz, _p, _p]),
+    "smore_negative_mask": (_int, [_p, _sz, _p, _p, _sz, _p, _p]),
     "smore_dot_available": (_int, []),
     "smore_dot_workspace_bytes": (_sz, [_sz, _sz, _sz, _int]),
     "smore_dot_forward_shared": (_int, [_p, _p, _p, _sz, _sz, _sz, _int, _p, _sz, _p]),

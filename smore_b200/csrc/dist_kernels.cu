@@ -22,6 +22,7 @@
 #include "common.cuh"
 #include "bulk_copy.cuh"
 #include "dist_terms.cuh"
+#include "rank_common.cuh"
 #include "shared_kernels.cuh"
 #include "update_math.cuh"
 
@@ -1224,6 +1225,95 @@ __global__ void __launch_bounds__(kRowCtaThreads)
 }
 
 // ----------------------------------------------------------------------------------------
+// Evaluation: scores of a batch of queries against EVERY entity, ranked on the fly.
+// The reference's test step (smore/training/train_process.py:104-146) materialises the [Q, N] logits,
+// argsorts them and scatters ranks; smore_filtered_ranks already replaces the sort by counting but
+// still reads a logits matrix.  Here the scoring tile never leaves the registers: every cell is
+// turned into the model's logit with the arithmetic torch would use on the distances
+// (custom_cal_logit: gamma - d_out - cen * d_in for Query2box, box.py:157-164; gamma - d for GQE and
+// RotatE; the similarity itself for ComplEx / DistMult), compared with the query's worst answer and,
+// if it is ahead of it, placed among the query's sorted answers (binary search, one histogram
+// increment).  The answers' own logits come from the same tile code run on the answers' rows, so a
+// candidate that is an answer meets exactly its own value.
+// ----------------------------------------------------------------------------------------
+
+enum LogitKind { kLogitGammaMinus = 0, kLogitGammaMinusSqrt = 1, kLogitIdentity = 2 };
+
+template <int NOUT>
+__device__ __forceinline__ float logit_of(const float* acc, int kind, float gamma, float cen) {
+  if (NOUT == 2) return __fsub_rn(__fsub_rn(gamma, acc[0]), __fmul_rn(cen, acc[NOUT - 1]));
+  if (kind == kLogitGammaMinus) return __fsub_rn(gamma, acc[0]);
+  if (kind == kLogitGammaMinusSqrt) return __fsub_rn(gamma, sqrtf(acc[0]));
+  return acc[0];
+}
+
+// answer scores [Q, n_answers] (one or two distances) -> logits, in place of dst0
+template <int NOUT>
+__global__ void __launch_bounds__(256)
+    answer_logits_kernel(float* __restrict__ d0, const float* __restrict__ d1, size_t n, int kind, float gamma, float cen) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float acc[2] = {d0[i], NOUT == 2 ? d1[i] : 0.f};
+    d0[i] = logit_of<NOUT>(acc, kind, gamma, cen);
+  }
+}
+
+template <class Term>
+__global__ void __launch_bounds__(256)
+    score_rank_kernel(SharedArgs a, int kind, float gamma, float cen, const int64_t* __restrict__ answer_ptr,
+                      const uint32_t* __restrict__ sorted_logit, const int64_t* __restrict__ sorted_id,
+                      int32_t* __restrict__ hist) {
+  __shared__ __align__(16) TileSmem<Term> sm;
+  __shared__ long long q_begin[kTileB], q_worst_id[kTileB];
+  __shared__ int q_count[kTileB];
+  __shared__ uint32_t q_worst[kTileB];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int b0 = blockIdx.y * kTileB, k0 = blockIdx.x * kTileK;
+  if (threadIdx.x < kTileB) {
+    const int b = b0 + threadIdx.x;
+    long long begin = 0, wid = 0;
+    int A = 0;
+    uint32_t wk = 0;
+    if (b < a.B) {
+      begin = answer_ptr[b];
+      A = (int)(answer_ptr[b + 1] - begin);
+      if (A > 0) {
+        wk = sorted_logit[begin + A - 1];
+        wid = sorted_id[begin + A - 1];
+      }
+    }
+    q_begin[threadIdx.x] = begin;
+    q_count[threadIdx.x] = A;
+    q_worst[threadIdx.x] = wk;
+    q_worst_id[threadIdx.x] = wid;
+  }
+  float acc[4][4][Term::kNOut];
+  tile_scores<Term>(a, sm, b0, k0, acc);      // (its barriers also order the writes above)
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int bl = ty * 4 + i;
+    const int A = q_count[bl];
+    if (b0 + bl >= a.B || A == 0) continue;
+    const long long begin = q_begin[bl];
+    const uint32_t worst = q_worst[bl];
+    const long long worst_id = q_worst_id[bl];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const long long e = k0 + tx * 4 + j;
+      if (e >= a.K) continue;
+      const uint32_t x = rank_key(logit_of<Term::kNOut>(acc[i][j], kind, gamma, cen));
+      if (!rank_ahead(x, e, worst, worst_id)) continue;      // ahead of no answer (the usual case)
+      int lo = 0, hi = A - 1;   // first answer this candidate is ahead of
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (rank_ahead(x, e, sorted_logit[begin + mid], sorted_id[begin + mid])) hi = mid;
+        else lo = mid + 1;
+      }
+      atomicAdd(hist + begin + lo, 1);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------
 // host side: validation, shape classification, launches
 // ----------------------------------------------------------------------------------------
 
@@ -1759,6 +1849,72 @@ int smore_rows_backward_fused_adam(int dist_id, const float* gout0, const float*
                 "rows_backward_fused_adam: shape not covered (rows of 1 KB to about 4 KB, dim a multiple of 4, at "
                 "least 4 rows per query, 16-byte aligned operands); use the separate backward and update calls");
   return SMORE_OK;
+}
+
+size_t smore_score_filtered_ranks_workspace_bytes(size_t n_queries, size_t n_answers) {
+  const size_t scores = ((n_queries * n_answers * sizeof(float) + 255) / 256) * 256;
+  return carve_rank_workspace(nullptr, n_answers).bytes + 2 * scores + 256;
+}
+
+int smore_score_filtered_ranks(int dist_id, const float* table, size_t n_candidates, const float* first,
+                               const float* second, size_t n_queries, size_t dim, double gamma, double cen,
+                               const int64_t* answer_ptr, const int64_t* answer_ids, size_t n_answers,
+                               size_t max_answers, int64_t* ranks, void* workspace, size_t workspace_bytes,
+                               void* stream) {
+  if (n_queries == 0 || n_answers == 0) return SMORE_OK;
+  const bool both = dist_id == SMORE_DIST_BOX_BOTH;
+  if (!both && (dist_id < 0 || dist_id >= SMORE_DIST_COUNT))
+    return fail(SMORE_ERR_BAD_DIST, "unknown distance id %d", dist_id);
+  if (dist_id == SMORE_DIST_BOX_OUT || dist_id == SMORE_DIST_BOX_IN)
+    return fail(SMORE_ERR_BAD_DIST, "score_filtered_ranks: Query2box logits need both distances (SMORE_DIST_BOX_BOTH)");
+  const bool two = both || needs_second(dist_id);
+  if (!table || !first || (two && !second) || !answer_ptr || !answer_ids || !ranks || !workspace)
+    return fail(SMORE_ERR_NULL, "score_filtered_ranks: NULL pointer");
+  if (workspace_bytes < smore_score_filtered_ranks_workspace_bytes(n_queries, n_answers) ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return fail(SMORE_ERR_WORKSPACE, "score_filtered_ranks: workspace too small or not 256-byte aligned");
+  if (!second) second = first;
+  const Shape s_all{n_queries, n_candidates, 1, n_candidates, n_queries, 1, dim, 0};
+  const Shape s_ans{n_queries, n_answers, 1, n_answers, n_queries, 1, dim, n_candidates};
+  if (int rc = validate_shape(s_all)) return rc;
+  const bool aligned = aligned16(table) && aligned16(first) && aligned16(second);
+  if (!shared_shape(s_all, aligned) || !shared_shape(s_ans, aligned) || max_answers == 0)
+    return fail(SMORE_ERR_BAD_SHAPE,
+                "score_filtered_ranks: needs 16-byte aligned operands, dim a multiple of 4, at least 8 queries, "
+                "8 candidates and 8 answers in all");
+  const RankWorkspace w = carve_rank_workspace(workspace, n_answers);
+  const size_t scores = ((n_queries * n_answers * sizeof(float) + 255) / 256) * 256;
+  float* d0 = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + w.bytes);
+  float* d1 = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + w.bytes + scores);
+  const int kind = (dist_id == SMORE_DIST_COMPLEX || dist_id == SMORE_DIST_DISTMULT) ? kLogitIdentity
+                   : dist_id == SMORE_DIST_L2 ? kLogitGammaMinusSqrt : kLogitGammaMinus;
+  cudaStream_t st = (cudaStream_t)stream;
+  SharedArgs a_ans{table, answer_ids, first, second, (int)n_queries, (int)n_answers, (int)dim, (long long)n_candidates};
+  SharedArgs a_all{table, nullptr, first, second, (int)n_queries, (int)n_candidates, (int)dim, 0};
+  dim3 grid_ans((unsigned)((n_answers + kTileK - 1) / kTileK), (unsigned)((n_queries + kTileB - 1) / kTileB));
+  dim3 grid_all((unsigned)((n_candidates + kTileK - 1) / kTileK), (unsigned)((n_queries + kTileB - 1) / kTileB));
+  const int egrid = grid_for(n_queries * n_answers, 256);
+#define SCORE_RANK(TERM)                                                                                          \
+  {                                                                                                               \
+    shared_forward_kernel<TERM><<<grid_ans, 256, 0, st>>>(a_ans, d0, d1);                                         \
+    answer_logits_kernel<TERM::kNOut><<<egrid, 256, 0, st>>>(d0, d1, n_queries * n_answers, kind, (float)gamma,  \
+                                                             (float)cen);                                         \
+    count_launches(2);                                                                                            \
+    if (int rc = rank_sort_answers(d0, n_answers, answer_ptr, answer_ids, true, n_queries, n_answers, max_answers, \
+                                   w, st))                                                                        \
+      return rc;                                                                                                  \
+    score_rank_kernel<TERM><<<grid_all, 256, 0, st>>>(a_all, kind, (float)gamma, (float)cen, answer_ptr,          \
+                                                      w.sorted_logit, w.sorted_id, w.hist);                       \
+  }
+  if (both) SCORE_RANK(TermBoxBoth)
+  else if (dist_id == SMORE_DIST_ROTATE) SCORE_RANK(TermRotate)
+  else if (dist_id == SMORE_DIST_L1) SCORE_RANK(TermL1)
+  else if (dist_id == SMORE_DIST_L2) SCORE_RANK(TermL2)
+  else if (dist_id == SMORE_DIST_COMPLEX) SCORE_RANK(TermComplex)
+  else SCORE_RANK(TermDistmult)
+#undef SCORE_RANK
+  if (int rc = check_launch("score_rank_kernel")) return rc;
+  return rank_finalize(answer_ptr, w, ranks, n_queries, st);
 }
 
 extern "C" int smore_peer_async_status(int* status);   // peer_kernels.cu (not part of the public header)

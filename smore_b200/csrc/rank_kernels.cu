@@ -24,27 +24,16 @@
 #include <cstdint>
 
 #include "common.cuh"
+#include "rank_common.cuh"
 
 namespace smore {
 
 constexpr int kRankThreads = 256;
 constexpr size_t kRankMaxAnswers = 8192;   // per query: sorted in shared memory
 
-// Logits are compared through an order-preserving integer key: the order of torch.sort, in which
-// NaN is the largest value, -0 equals +0, and everything else is the usual float order.
-__device__ __forceinline__ uint32_t rank_key(float x) {
-  if (x != x) return 0xFFFFFFFFu;
-  const uint32_t b = __float_as_uint(x + 0.f);   // -0 + 0 = +0
-  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
-}
-
-__device__ __forceinline__ bool rank_ahead(uint32_t x, long long e, uint32_t t, long long id) {
-  return x > t || (x == t && e < id);
-}
-
 // one CTA per query; P = power of two >= the longest answer list
 __global__ void __launch_bounds__(kRankThreads)
-    rank_sort_answers_kernel(const float* __restrict__ logits, size_t n_candidates,
+    rank_sort_answers_kernel(const float* __restrict__ logits, size_t n_candidates, int cols_are_positions,
                              const int64_t* __restrict__ answer_ptr, const int64_t* __restrict__ answer_ids,
                              int P, uint32_t* __restrict__ sorted_logit, int64_t* __restrict__ sorted_id,
                              int32_t* __restrict__ perm) {
@@ -59,7 +48,9 @@ __global__ void __launch_bounds__(kRankThreads)
     uint32_t k = 0;
     int32_t p = INT_MAX;
     if (i < A) {
-      const int64_t id = answer_ids[begin + i];
+      // the answer's logit sits in the column of its entity id, or (scores computed for the answers
+      // alone, one column per listed answer) in the column of its position in the list
+      const int64_t id = cols_are_positions ? begin + i : answer_ids[begin + i];
       k = (id >= 0 && (size_t)id < n_candidates) ? rank_key(row[id]) : 0u;
       p = i;
     }
@@ -181,16 +172,49 @@ __global__ void __launch_bounds__(kRankThreads)
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+RankWorkspace carve_rank_workspace(void* workspace, size_t n_answers) {
+  RankWorkspace w;
+  unsigned char* p = static_cast<unsigned char*>(workspace);
+  w.sorted_id = reinterpret_cast<int64_t*>(p);
+  p += align_up(n_answers * sizeof(int64_t), 256);
+  w.sorted_logit = reinterpret_cast<uint32_t*>(p);
+  p += align_up(n_answers * sizeof(int32_t), 256);
+  w.perm = reinterpret_cast<int32_t*>(p);
+  p += align_up(n_answers * sizeof(int32_t), 256);
+  w.hist = reinterpret_cast<int32_t*>(p);
+  p += align_up(n_answers * sizeof(int32_t), 256);
+  w.bytes = (size_t)(p - static_cast<unsigned char*>(workspace)) + 256;
+  return w;
+}
+
+int rank_sort_answers(const float* logits, size_t n_cols, const int64_t* answer_ptr, const int64_t* answer_ids,
+                      bool cols_are_positions, size_t n_queries, size_t n_answers, size_t max_answers,
+                      const RankWorkspace& w, cudaStream_t st) {
+  if (max_answers > kRankMaxAnswers)
+    return fail(SMORE_ERR_TOO_LARGE, "filtered_ranks: at most %zu answers per query", kRankMaxAnswers);
+  if (n_queries > 65535) return fail(SMORE_ERR_TOO_LARGE, "filtered_ranks: at most 65535 queries per call");
+  if (cudaMemsetAsync(w.hist, 0, n_answers * sizeof(int32_t), st) != cudaSuccess)
+    return fail(SMORE_ERR_CUDA, "filtered_ranks: cudaMemsetAsync failed");
+  int P = 1;
+  while ((size_t)P < max_answers) P <<= 1;
+  if (int rc = allow_large_smem(rank_sort_answers_kernel, (int)(kRankMaxAnswers * 8), false)) return rc;
+  rank_sort_answers_kernel<<<(unsigned)n_queries, kRankThreads, (size_t)P * 8, st>>>(
+      logits, n_cols, cols_are_positions ? 1 : 0, answer_ptr, answer_ids, P, w.sorted_logit, w.sorted_id, w.perm);
+  return check_launch("rank_sort_answers_kernel");
+}
+
+int rank_finalize(const int64_t* answer_ptr, const RankWorkspace& w, int64_t* ranks, size_t n_queries, cudaStream_t st) {
+  rank_finalize_kernel<<<(unsigned)n_queries, kRankThreads, 0, st>>>(answer_ptr, w.hist, w.perm, ranks);
+  return check_launch("rank_finalize_kernel");
+}
+
 }  // namespace smore
 
 using namespace smore;
 
 extern "C" {
 
-size_t smore_filtered_ranks_workspace_bytes(size_t n_answers) {
-  // sorted logits, sorted ids, permutation, histogram
-  return align_up(n_answers * sizeof(int64_t), 256) + 3 * align_up(n_answers * sizeof(int32_t), 256) + 256;
-}
+size_t smore_filtered_ranks_workspace_bytes(size_t n_answers) { return carve_rank_workspace(nullptr, n_answers).bytes; }
 
 int smore_filtered_ranks(const float* logits, size_t n_queries, size_t n_candidates, const int64_t* answer_ptr,
                          const int64_t* answer_ids, size_t n_answers, size_t max_answers, int64_t* ranks,
@@ -199,39 +223,25 @@ int smore_filtered_ranks(const float* logits, size_t n_queries, size_t n_candida
   if (!logits || !answer_ptr || !answer_ids || !ranks || !workspace)
     return fail(SMORE_ERR_NULL, "filtered_ranks: NULL pointer");
   if (n_candidates == 0 || max_answers == 0) return fail(SMORE_ERR_BAD_SHAPE, "filtered_ranks: empty candidate set");
-  if (max_answers > kRankMaxAnswers)
-    return fail(SMORE_ERR_TOO_LARGE, "filtered_ranks: at most %zu answers per query", kRankMaxAnswers);
-  if (n_queries > 65535 || n_candidates > ((size_t)1 << 40))
-    return fail(SMORE_ERR_TOO_LARGE, "filtered_ranks: at most 65535 queries per call");
+  if (n_candidates > ((size_t)1 << 40)) return fail(SMORE_ERR_TOO_LARGE, "filtered_ranks: too many candidates");
   if (workspace_bytes < smore_filtered_ranks_workspace_bytes(n_answers) || (reinterpret_cast<uintptr_t>(workspace) & 255))
     return fail(SMORE_ERR_WORKSPACE, "filtered_ranks: workspace too small or not 256-byte aligned");
-  unsigned char* w = static_cast<unsigned char*>(workspace);
-  int64_t* sorted_id = reinterpret_cast<int64_t*>(w);
-  w += align_up(n_answers * sizeof(int64_t), 256);
-  uint32_t* sorted_logit = reinterpret_cast<uint32_t*>(w);
-  w += align_up(n_answers * sizeof(int32_t), 256);
-  int32_t* perm = reinterpret_cast<int32_t*>(w);
-  w += align_up(n_answers * sizeof(int32_t), 256);
-  int32_t* hist = reinterpret_cast<int32_t*>(w);
+  const RankWorkspace w = carve_rank_workspace(workspace, n_answers);
   cudaStream_t st = (cudaStream_t)stream;
-  if (cudaMemsetAsync(hist, 0, n_answers * sizeof(int32_t), st) != cudaSuccess)
-    return fail(SMORE_ERR_CUDA, "filtered_ranks: cudaMemsetAsync failed");
-  int P = 1;
-  while ((size_t)P < max_answers) P <<= 1;
-  const size_t sort_smem = (size_t)P * 8, count_smem = max_answers * 16;
-  if (int rc = allow_large_smem(rank_sort_answers_kernel, (int)(kRankMaxAnswers * 8), false)) return rc;
+  if (int rc = rank_sort_answers(logits, n_candidates, answer_ptr, answer_ids, false, n_queries, n_answers, max_answers,
+                                 w, st))
+    return rc;
+  const size_t count_smem = max_answers * 16;
   if (int rc = allow_large_smem(rank_count_kernel, (int)(kRankMaxAnswers * 16), false)) return rc;
-  rank_sort_answers_kernel<<<(unsigned)n_queries, kRankThreads, sort_smem, st>>>(
-      logits, n_candidates, answer_ptr, answer_ids, P, sorted_logit, sorted_id, perm);
   // enough CTAs per query to fill the GPU a few times over, at least 4096 candidates each
   size_t chunks = std::max<size_t>(1, (size_t)sm_count() * 8 / n_queries);
   size_t per_cta = std::max<size_t>(4096, (n_candidates + chunks - 1) / chunks);
   chunks = (n_candidates + per_cta - 1) / per_cta;
   dim3 grid((unsigned)chunks, (unsigned)n_queries);
-  rank_count_kernel<<<grid, kRankThreads, count_smem, st>>>(logits, n_candidates, answer_ptr, sorted_logit,
-                                                            sorted_id, per_cta, hist);
-  rank_finalize_kernel<<<(unsigned)n_queries, kRankThreads, 0, st>>>(answer_ptr, hist, perm, ranks);
-  return check_launch("filtered_ranks kernels", 3);
+  rank_count_kernel<<<grid, kRankThreads, count_smem, st>>>(logits, n_candidates, answer_ptr, w.sorted_logit,
+                                                            w.sorted_id, per_cta, w.hist);
+  if (int rc = check_launch("rank_count_kernel")) return rc;
+  return rank_finalize(answer_ptr, w, ranks, n_queries, st);
 }
 
 }  // extern "C"

@@ -41,16 +41,24 @@ struct SharedArgs {
 // it.  (Defined here because this header is part of exactly one translation unit, dist_kernels.cu.)
 __device__ int g_async_status = 0;
 
+// Shared memory of one 64 x 64 tile of scores.
 template <class Term>
-__global__ void __launch_bounds__(256)
-    shared_forward_kernel(SharedArgs a, float* __restrict__ dst0, float* __restrict__ dst1) {
-  __shared__ __align__(16) float q0s[kTileD][kTileB + kTilePad];
-  __shared__ __align__(16) float q1s[kTileD][kTileB + kTilePad];
-  __shared__ __align__(16) float e0s[kTileD][kTileK + kTilePad];
-  __shared__ __align__(16) float e1s[Term::kMul == 2 ? kTileD : 1][kTileK + kTilePad];
-  __shared__ unsigned char ebad[kTileK];   // candidate rows of the tile whose id lay outside the table
+struct TileSmem {
+  float q0s[kTileD][kTileB + kTilePad];
+  float q1s[kTileD][kTileB + kTilePad];
+  float e0s[kTileD][kTileK + kTilePad];
+  float e1s[Term::kMul == 2 ? kTileD : 1][kTileK + kTilePad];
+  unsigned char ebad[kTileK];   // candidate rows of the tile whose id lay outside the table
+};
+
+// Scores of the tile (queries b0.., candidates k0..) into acc: thread (ty, tx) owns queries
+// b0 + 4 ty + i and candidates k0 + 4 tx + j.  Every cell accumulates its terms in the order of the
+// embedding dim, one after the other, so a (query, candidate) pair gets the same value wherever it
+// falls in a tile and whatever the tile's neighbours are.
+template <class Term>
+__device__ __forceinline__ void tile_scores(const SharedArgs& a, TileSmem<Term>& sm, int b0, int k0,
+                                            float (&acc)[4][4][Term::kNOut]) {
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-  const int b0 = blockIdx.y * kTileB, k0 = blockIdx.x * kTileK;
   const int dim4 = a.dim >> 2;
   const size_t w4 = (size_t)dim4 * Term::kMul;
   // staging role: one 16-byte piece of one row per operand per step
@@ -62,13 +70,11 @@ __global__ void __launch_bounds__(256)
   if (erow_ok) {
     const long long r = a.idx ? checked_row_id(a.idx, k0 + lrow, a.n_rows, &g_async_status) : (long long)(k0 + lrow);
     erow = r < 0 ? 0 : (size_t)r;
-    if (lq == 0) ebad[lrow] = r < 0;
+    if (lq == 0) sm.ebad[lrow] = r < 0;
   } else if (lq == 0) {
-    ebad[lrow] = 0;
+    sm.ebad[lrow] = 0;
   }
   const float4* e0p = reinterpret_cast<const float4*>(a.ent) + erow * w4;
-
-  float acc[4][4][Term::kNOut];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -85,22 +91,22 @@ __global__ void __launch_bounds__(256)
     const float4 ve0 = (erow_ok && d_ok) ? __ldg(e0p + d4) : z4;
     const float4 ve1 = (Term::kMul == 2 && erow_ok && d_ok) ? __ldg(e0p + dim4 + d4) : z4;
     __syncthreads();  // the previous step's tiles are no longer being read
-    q0s[lq * 4 + 0][lrow] = vq0.x; q0s[lq * 4 + 1][lrow] = vq0.y; q0s[lq * 4 + 2][lrow] = vq0.z; q0s[lq * 4 + 3][lrow] = vq0.w;
+    sm.q0s[lq * 4 + 0][lrow] = vq0.x; sm.q0s[lq * 4 + 1][lrow] = vq0.y; sm.q0s[lq * 4 + 2][lrow] = vq0.z; sm.q0s[lq * 4 + 3][lrow] = vq0.w;
     if (Term::kNQ == 2) {
-      q1s[lq * 4 + 0][lrow] = vq1.x; q1s[lq * 4 + 1][lrow] = vq1.y; q1s[lq * 4 + 2][lrow] = vq1.z; q1s[lq * 4 + 3][lrow] = vq1.w;
+      sm.q1s[lq * 4 + 0][lrow] = vq1.x; sm.q1s[lq * 4 + 1][lrow] = vq1.y; sm.q1s[lq * 4 + 2][lrow] = vq1.z; sm.q1s[lq * 4 + 3][lrow] = vq1.w;
     }
-    e0s[lq * 4 + 0][lrow] = ve0.x; e0s[lq * 4 + 1][lrow] = ve0.y; e0s[lq * 4 + 2][lrow] = ve0.z; e0s[lq * 4 + 3][lrow] = ve0.w;
+    sm.e0s[lq * 4 + 0][lrow] = ve0.x; sm.e0s[lq * 4 + 1][lrow] = ve0.y; sm.e0s[lq * 4 + 2][lrow] = ve0.z; sm.e0s[lq * 4 + 3][lrow] = ve0.w;
     if (Term::kMul == 2) {
-      e1s[lq * 4 + 0][lrow] = ve1.x; e1s[lq * 4 + 1][lrow] = ve1.y; e1s[lq * 4 + 2][lrow] = ve1.z; e1s[lq * 4 + 3][lrow] = ve1.w;
+      sm.e1s[lq * 4 + 0][lrow] = ve1.x; sm.e1s[lq * 4 + 1][lrow] = ve1.y; sm.e1s[lq * 4 + 2][lrow] = ve1.z; sm.e1s[lq * 4 + 3][lrow] = ve1.w;
     }
     __syncthreads();
     const int dcount = min(kTileD, a.dim - d0);
 #pragma unroll 4
     for (int dd = 0; dd < dcount; ++dd) {
-      const float4 q0 = *reinterpret_cast<const float4*>(&q0s[dd][ty * 4]);
-      const float4 q1 = Term::kNQ == 2 ? *reinterpret_cast<const float4*>(&q1s[dd][ty * 4]) : q0;
-      const float4 e0 = *reinterpret_cast<const float4*>(&e0s[dd][tx * 4]);
-      const float4 e1 = Term::kMul == 2 ? *reinterpret_cast<const float4*>(&e1s[dd][tx * 4]) : e0;
+      const float4 q0 = *reinterpret_cast<const float4*>(&sm.q0s[dd][ty * 4]);
+      const float4 q1 = Term::kNQ == 2 ? *reinterpret_cast<const float4*>(&sm.q1s[dd][ty * 4]) : q0;
+      const float4 e0 = *reinterpret_cast<const float4*>(&sm.e0s[dd][tx * 4]);
+      const float4 e1 = Term::kMul == 2 ? *reinterpret_cast<const float4*>(&sm.e1s[dd][tx * 4]) : e0;
       const float qa[4] = {q0.x, q0.y, q0.z, q0.w}, qb[4] = {q1.x, q1.y, q1.z, q1.w};
       const float ea[4] = {e0.x, e0.y, e0.z, e0.w}, eb[4] = {e1.x, e1.y, e1.z, e1.w};
 #pragma unroll
@@ -109,6 +115,16 @@ __global__ void __launch_bounds__(256)
         for (int j = 0; j < 4; ++j) Term::fwd(ea[j], eb[j], qa[i], qb[i], acc[i][j]);
     }
   }
+}
+
+template <class Term>
+__global__ void __launch_bounds__(256)
+    shared_forward_kernel(SharedArgs a, float* __restrict__ dst0, float* __restrict__ dst1) {
+  __shared__ __align__(16) TileSmem<Term> sm;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int b0 = blockIdx.y * kTileB, k0 = blockIdx.x * kTileK;
+  float acc[4][4][Term::kNOut];
+  tile_scores<Term>(a, sm, b0, k0, acc);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int b = b0 + ty * 4 + i;
@@ -117,7 +133,7 @@ __global__ void __launch_bounds__(256)
     for (int j = 0; j < 4; ++j) {
       const int k = k0 + tx * 4 + j;
       if (k < a.K) {
-        const bool bad = ebad[tx * 4 + j];   // written before the first barrier of the loop above
+        const bool bad = sm.ebad[tx * 4 + j];   // written before the first barrier of the tile loop
         dst0[(size_t)b * a.K + k] = bad ? NAN : acc[i][j][0];
         if (Term::kNOut == 2) dst1[(size_t)b * a.K + k] = bad ? NAN : acc[i][j][Term::kNOut - 1];
       }

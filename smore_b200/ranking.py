@@ -59,6 +59,64 @@ def filtered_ranks(logits, easy_answers, hard_answers):
     return out
 
 
+def _answer_lists(easy_answers, hard_answers, n_candidates):
+    ptr, ids, hard_mask = [0], [], []
+    for easy, hard in zip(easy_answers, hard_answers):
+        easy, hard = list(easy), list(hard)
+        ids.extend(easy)
+        ids.extend(hard)
+        hard_mask.extend([False] * len(easy) + [True] * len(hard))
+        ptr.append(len(ids))
+    if any((i < 0 or i >= n_candidates) for i in ids):
+        raise ValueError("answer ids must lie in [0, %d)" % n_candidates)
+    return ptr, ids, hard_mask
+
+
+_SCORE_IDS = {"box": _lib.BOX_BOTH_ID, "vec": _lib.DIST_IDS["l1"], "l1": _lib.DIST_IDS["l1"], "l2": _lib.DIST_IDS["l2"],
+              "rotate": _lib.DIST_IDS["rotate"], "complex": _lib.DIST_IDS["complex"],
+              "distmult": _lib.DIST_IDS["distmult"]}
+
+
+def score_and_rank(geo, table, query, easy_answers, hard_answers, gamma=0.0, cen=0.0):
+    """The evaluation step in one call: score Q queries against every row of `table` with the model's
+    logit and return the filtered ranks of their hard answers, without materialising the [Q, N]
+    logits (smore_score_filtered_ranks).
+
+    geo      "box" (gamma - d_out - cen * d_in), "vec" / "l1" / "rotate" (gamma - d), "l2" (gamma - sqrt(d)),
+             "complex" / "distmult" (the similarity)
+    table    float32 CUDA [N, W] - the whole entity table (W = dim, or 2 * dim for rotate / complex rows)
+    query    one or two float32 CUDA tensors [Q, dim] (or [Q, 1, dim]): center (and offset), re and im, ...
+    Returns what filtered_ranks returns for the logits the distance ops would have produced."""
+    if geo not in _SCORE_IDS:
+        raise ValueError("geo must be one of %s" % sorted(_SCORE_IDS))
+    parts = [q.reshape(q.shape[0], -1).contiguous() for q in query]
+    Q, dim = parts[0].shape
+    N = table.shape[0]
+    if table.dtype != torch.float32 or not table.is_cuda or not table.is_contiguous():
+        raise TypeError("table must be a contiguous float32 CUDA tensor")
+    ptr, ids, hard_mask = _answer_lists(easy_answers, hard_answers, N)
+    if len(ptr) != Q + 1:
+        raise ValueError("one easy and one hard answer list per query")
+    n_answers = len(ids)
+    dev = table.device
+    if n_answers == 0:
+        return [torch.empty(0, dtype=torch.int64, device=dev) for _ in range(Q)]
+    max_answers = max(b - a for a, b in zip(ptr[:-1], ptr[1:]))
+    d_ptr = torch.tensor(ptr, dtype=torch.int64, device=dev)
+    d_ids = torch.tensor(ids, dtype=torch.int64, device=dev)
+    ranks = torch.empty(n_answers, dtype=torch.int64, device=dev)
+    L = _lib.lib()
+    ws = torch.empty(L.smore_score_filtered_ranks_workspace_bytes(Q, n_answers), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev), _lib.timed("score_filtered_ranks"):
+        _lib.check(L.smore_score_filtered_ranks(
+            _SCORE_IDS[geo], table.data_ptr(), N, parts[0].data_ptr(), parts[1].data_ptr() if len(parts) > 1 else None,
+            Q, dim, float(gamma), float(cen), d_ptr.data_ptr(), d_ids.data_ptr(), n_answers, max_answers,
+            ranks.data_ptr(), ws.data_ptr(), ws.numel(), torch.cuda.current_stream(dev).cuda_stream),
+            "smore_score_filtered_ranks")
+    mask = torch.tensor(hard_mask, dtype=torch.bool, device=dev)
+    return [torch.sort(ranks[ptr[q]:ptr[q + 1]][mask[ptr[q]:ptr[q + 1]]])[0] for q in range(Q)]
+
+
 def ranking_metrics(hard_ranks):
     """Per-query metrics of train_process.py:142-146 from the sorted filtered ranks of a query's hard
     answers: MRR, HITS1, HITS3, HITS10 (means over the answers) and HITS1max (best answer ranked 1)."""

@@ -130,3 +130,47 @@ def test_ranks_reproduce_the_reference_test_step_metrics(golden):
             assert abs(got[k] - w) <= 1e-6, (tag, k, got[k], w)
         checked += 1
     assert checked >= 5
+
+
+@pytest.mark.parametrize("geo,N,D,Q", [("box", 20000, 64, 9), ("vec", 5000, 36, 16), ("rotate", 3000, 40, 8),
+                                         ("distmult", 7001, 48, 33), ("l2", 1000, 16, 8), ("box", 300000, 400, 12)])
+def test_score_and_rank_equals_ranks_of_materialised_logits(geo, N, D, Q):
+    """smore_score_filtered_ranks (scores ranked straight from the scoring tiles) against the two-step
+    path: distance ops on all entities -> the model's logit arithmetic in torch -> filtered_ranks.
+    Bit-identical ranks: both paths run the same tile code and the same roundings."""
+    from smore_b200 import ext_ops, ranking
+    g = torch.Generator().manual_seed(N + D)
+    two_part = geo in ("rotate", "complex")
+    W = 2 * D if two_part else D
+    table = ((torch.rand(N, W, generator=g) - 0.5) * 0.4).cuda()
+    table[N // 2] = table[N // 3]                       # two identical rows: an exact tie
+    n_parts = 1 if geo in ("vec", "distmult", "l2") else 2
+    query = [((torch.rand(Q, 1, D, generator=g) - 0.5) * 0.4).cuda() for _ in range(n_parts)]
+    if geo == "box":
+        query[1] = query[1].abs() * 0.3
+    gamma, cen = 12.0, 0.02
+    every = table.unsqueeze(0)
+    with torch.no_grad():
+        if geo == "box":
+            logits = gamma - ext_ops.box_dist_out(every, *query) - cen * ext_ops.box_dist_in(every, *query)
+        elif geo == "vec":
+            logits = gamma - ext_ops.l1_dist(every, query[0])
+        elif geo == "l2":
+            logits = gamma - ext_ops.l2_dist(every, query[0])
+        elif geo == "rotate":
+            logits = gamma - ext_ops.rotate_dist(every, *query)
+        else:
+            import os
+            os.environ["SMORE_B200_DOT"] = "off"         # the exact-fp32 kernels, as the fused path uses
+            try:
+                logits = ext_ops.distmult_sim(every, query[0])
+            finally:
+                del os.environ["SMORE_B200_DOT"]
+    rng = np.random.default_rng(Q)
+    easy, hard = zip(*[_answers(rng, N, 3 * (q % 4), 1 + 5 * (q % 5)) for q in range(Q)])
+    hard = [list(h) for h in hard]
+    hard[0] = sorted(set(hard[0]) | {N // 2, N // 3} - set(easy[0]))     # the tied rows are answers of query 0
+    want = ranking.filtered_ranks(logits, easy, hard)
+    got = ranking.score_and_rank(geo, table, query, easy, hard, gamma=gamma, cen=cen)
+    for q in range(Q):
+        assert torch.equal(got[q], want[q]), "query %d" % q
