@@ -15,6 +15,7 @@
 // in the forward pass, and column-strided walks (one 32-byte sector per 4 useful bytes) in the
 // backward pass.
 #pragma once
+#include <cooperative_groups.h>
 #include <cuda_runtime.h>
 
 #include "common.cuh"
@@ -253,6 +254,137 @@ __global__ void __launch_bounds__(kGradRows* kGradCols)
     reinterpret_cast<float4*>(ga.g_first)[(size_t)b * dim4 + c4] = gq0;
     if (Term::kNQ == 2) reinterpret_cast<float4*>(ga.g_second)[(size_t)b * dim4 + c4] = gq1;
   }
+}
+
+// ---- both gradients of the shared-candidate shape from ONE evaluation of every term ----
+//
+// Thread = one embedding dim d; CTA (one warp) = KT candidate rows x a segment of the queries.  The
+// thread keeps e[k, d] and its gradient for the KT rows in registers and walks the segment's queries:
+// per query it loads q[b, d], evaluates the KT terms (upstream gradients broadcast from shared
+// memory) and sends the query's partial gradient (the sum over the CTA's KT rows) to g_first /
+// g_second with one coalesced reduction per warp, so those must be zero at launch.  The CTAs that
+// share rows and dims but hold different query segments form one thread-block cluster: at the end
+// they add their row gradients through distributed shared memory in rank order (deterministic) and
+// each rank writes KT / cluster-size of the rows.
+constexpr int kBwdThreads = 32;   // dims per CTA
+constexpr int kBwdChunkB = 64;    // queries whose upstream gradients are staged at a time
+constexpr int kBwdAhead = 4;      // query rows loaded ahead of the one being used
+
+template <class Term, int KT>
+__global__ void __launch_bounds__(kBwdThreads)
+    shared_backward_tile_kernel(SharedArgs a, SharedGradArgs ga, int seg_b) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  constexpr int NO = Term::kNOut, M = Term::kMul;
+  __shared__ __align__(16) float gs[kBwdChunkB][KT][NO];
+  __shared__ float red[KT * M][kBwdThreads];
+  __shared__ long long rows_sh[KT];
+
+  const int tid = threadIdx.x;
+  const int k0 = blockIdx.x * KT;
+  const int d = blockIdx.z * kBwdThreads + tid;
+  const bool d_ok = d < a.dim;
+  const unsigned rank = cluster.block_rank(), n_ranks = cluster.num_blocks();
+  const int b_begin = min(a.B, (int)rank * seg_b), b_end = min(a.B, b_begin + seg_b);
+
+  if (tid < KT) {
+    const int k = k0 + tid;
+    rows_sh[tid] = k < a.K ? (a.idx ? checked_row_id(a.idx, k, a.n_rows, &g_async_status) : (long long)k) : -1;
+  }
+  __syncthreads();
+  const size_t W = (size_t)a.dim * M;
+  float e0[KT], e1[KT], ge0[KT], ge1[KT];
+#pragma unroll
+  for (int j = 0; j < KT; ++j) {
+    const long long r = rows_sh[j];
+    const bool ok = r >= 0 && d_ok;
+    e0[j] = ok ? __ldg(a.ent + (size_t)r * W + d) : 0.f;
+    e1[j] = (M == 2 && ok) ? __ldg(a.ent + (size_t)r * W + a.dim + d) : e0[j];
+    ge0[j] = 0.f;
+    ge1[j] = 0.f;
+  }
+  const float* __restrict__ q0p = a.first + d;
+  const float* __restrict__ q1p = a.second + d;
+
+  for (int bs = b_begin; bs < b_end; bs += kBwdChunkB) {
+    const int nb = min(kBwdChunkB, b_end - bs);
+    __syncthreads();   // the previous chunk's gradients are no longer being read
+    // upstream gradients of the chunk; zero for rows that do not exist, so their terms add nothing
+    for (int i = tid; i < nb * KT; i += kBwdThreads) {
+      const int bb = i / KT, j = i % KT;
+      const bool ok = rows_sh[j] >= 0;
+      const size_t at = (size_t)(bs + bb) * a.K + k0 + j;
+      gs[bb][j][0] = ok ? __ldg(ga.gout0 + at) : 0.f;
+      if (NO == 2) gs[bb][j][NO - 1] = ok ? __ldg(ga.gout1 + at) : 0.f;
+    }
+    __syncthreads();
+    float q0n[kBwdAhead], q1n[kBwdAhead];
+#pragma unroll
+    for (int u = 0; u < kBwdAhead; ++u) {
+      const bool ok = d_ok && u < nb;
+      q0n[u] = ok ? __ldg(q0p + (size_t)(bs + u) * a.dim) : 0.f;
+      q1n[u] = (Term::kNQ == 2 && ok) ? __ldg(q1p + (size_t)(bs + u) * a.dim) : q0n[u];
+    }
+    for (int bb0 = 0; bb0 < nb; bb0 += kBwdAhead) {
+      float q0c[kBwdAhead], q1c[kBwdAhead];
+#pragma unroll
+      for (int u = 0; u < kBwdAhead; ++u) {
+        q0c[u] = q0n[u];
+        q1c[u] = q1n[u];
+        const int bn = bb0 + kBwdAhead + u;
+        const bool ok = d_ok && bn < nb;
+        q0n[u] = ok ? __ldg(q0p + (size_t)(bs + bn) * a.dim) : 0.f;
+        q1n[u] = (Term::kNQ == 2 && ok) ? __ldg(q1p + (size_t)(bs + bn) * a.dim) : q0n[u];
+      }
+#pragma unroll
+      for (int u = 0; u < kBwdAhead; ++u) {
+        const int bb = bb0 + u;
+        if (bb >= nb) break;
+        float gq0 = 0.f, gq1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < KT; ++j) Term::bwd(&gs[bb][j][0], e0[j], e1[j], q0c[u], q1c[u], ge0[j], ge1[j], gq0, gq1);
+        if (d_ok) {
+          const size_t at = (size_t)(bs + bb) * a.dim + d;
+          atomicAdd(ga.g_first + at, gq0);
+          if (Term::kNQ == 2) atomicAdd(ga.g_second + at, gq1);
+        }
+      }
+    }
+  }
+
+  // row gradients: sum over the cluster's query segments in rank order
+#pragma unroll
+  for (int j = 0; j < KT; ++j) {
+    red[j * M][tid] = ge0[j];
+    if (M == 2) red[j * M + M - 1][tid] = ge1[j];
+  }
+  cluster.sync();
+  for (int j = (int)rank; j < KT; j += (int)n_ranks) {
+    const int k = k0 + j;
+    if (k >= a.K || rows_sh[j] < 0 || !d_ok) continue;
+    float s0 = 0.f, s1 = 0.f;
+    for (unsigned r = 0; r < n_ranks; ++r) {
+      const float* remote = cluster.map_shared_rank(&red[0][0], r);
+      s0 += remote[(j * M) * kBwdThreads + tid];
+      if (M == 2) s1 += remote[(j * M + M - 1) * kBwdThreads + tid];
+    }
+    if (ga.slot == nullptr) {
+      ga.g_ent[(size_t)k * W + d] = s0;
+      if (M == 2) ga.g_ent[(size_t)k * W + a.dim + d] = s1;
+    } else {
+      const int32_t s = ga.slot[k];
+      if (s < 0) continue;
+      float* out = ga.g_rows + (size_t)s * W + d;
+      if (ga.slot_count != nullptr && ga.slot_count[s] == 1) {
+        out[0] = s0;
+        if (M == 2) out[a.dim] = s1;
+      } else {
+        atomicAdd(out, s0);
+        if (M == 2) atomicAdd(out + a.dim, s1);
+      }
+    }
+  }
+  cluster.sync();   // no CTA leaves while another still reads its shared memory
 }
 
 }  // namespace smore
