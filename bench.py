@@ -181,8 +181,9 @@ class QueryModel(nn.Module):
     def __init__(self, cfg, n_rows, device, ops, embedding_mod, lazy=True, shard=None, barrier=None, world=1,
                  capturable=False, fused_paths=False):
         super().__init__()
-        # relation projections of a path as one library op (box and vec geometries) instead of per-hop torch ops
-        self.fused_paths = bool(fused_paths) and cfg["geo"] in ("box", "vec")
+        # relation projections of a path as one library op instead of per-hop torch ops; an anchor lookup
+        # that starts a path is read from the table inside that op (never gathered)
+        self.fused_paths = bool(fused_paths)
         self.cfg, self.geo, self.dim = cfg, cfg["geo"], cfg["dim"]
         self.gamma, self.cen = cfg["gamma"], cfg.get("cen", 0.0)
         self.ops = ops
@@ -194,6 +195,8 @@ class QueryModel(nn.Module):
         self.entity_embedding = embedding_mod.SparseEmbedding(0, width)
         self.entity_embedding.num_rows = n_rows
         lazy_names = ("negative_entity", "positive_entity") if lazy else ()
+        if lazy and self.fused_paths:
+            lazy_names += ("anchor_entity",)
         if shard is None:
             table = torch.empty(n_rows, width, device=device)
             if cfg.get("init_std"):
@@ -233,20 +236,28 @@ class QueryModel(nn.Module):
             re, im = torch.chunk(e, 2, dim=1)
             return [re.unsqueeze(1), im.unsqueeze(1)]
         if self.geo == "box":
-            # a fresh anchor is a box of zero size (box.py:138-139); the fused projection takes None for it
-            return [e.unsqueeze(1), None if self.fused_paths else torch.zeros_like(e).unsqueeze(1)]
+            # a fresh anchor is a box of zero size (box.py:138-139)
+            return [e.unsqueeze(1), torch.zeros_like(e).unsqueeze(1)]
         return [e.unsqueeze(1)]
 
-    def _project_path(self, emb, rel_ids):
-        """All hops of a path at once (smore_b200.query_ops) for the additive geometries."""
+    def _embed_path(self, start, rel_ids):
+        """All hops of a path at once (smore_b200.query_ops.embed_path).  `start` is the list of
+        [B, 1, dim] parts of the state the path starts from, or the anchor ids' table-resident rows."""
         from smore_b200 import query_ops
-        start = emb[0].squeeze(1)
+        fresh = not isinstance(start, list)
         if self.geo == "box":
-            c, o = query_ops.project_path(start, self.relation_embedding, rel_ids,
-                                          start_offset=None if emb[1] is None else emb[1].squeeze(1),
-                                          off_table=self.offset_embedding)
+            c, o = query_ops.embed_path("add", start if fresh else start[0].squeeze(1), self.relation_embedding, rel_ids,
+                                        start_offset=None if fresh else start[1].squeeze(1),
+                                        off_table=self.offset_embedding)
             return [c.unsqueeze(1), o.unsqueeze(1)]
-        return [query_ops.project_path(start, self.relation_embedding, rel_ids).unsqueeze(1)]
+        if self.geo in ("rotate", "complex"):
+            state = start if fresh else torch.cat([start[0], start[1]], dim=-1).squeeze(1)
+            scale = math.pi / self.embedding_range if self.geo == "rotate" else 1.0
+            re, im = query_ops.embed_path(self.geo, state, self.relation_embedding, rel_ids, phase_scale=scale)
+            return [re.unsqueeze(1), im.unsqueeze(1)]
+        geometry = "distmult" if self.geo == "distmult" else "add"
+        out = query_ops.embed_path(geometry, start if fresh else start[0].squeeze(1), self.relation_embedding, rel_ids)
+        return [out.unsqueeze(1)]
 
     def _project(self, emb, rel_ids):
         rel = self.relation_embedding[rel_ids].unsqueeze(1)
@@ -277,16 +288,18 @@ class QueryModel(nn.Module):
 
     def embed_query(self, queries, qs, col):
         if all(isinstance(x, str) for x in qs[-1]) and all(x in ("r", "n") for x in qs[-1]):
+            fused = self.fused_paths and all(x == "r" for x in qs[-1])
+            n_hops = len(qs[-1])
             if qs[0] == "e":
+                if fused:
+                    rows = self.entity_embedding(queries[:, col], "anchor_entity")   # table-resident when lazy
+                    return self._embed_path(rows, queries[:, col + 1:col + 1 + n_hops]), col + 1 + n_hops
                 emb = self._retrieve(queries[:, col])
                 col += 1
             else:
                 emb, col = self.embed_query(queries, qs[0], col)
-            if self.fused_paths and all(x == "r" for x in qs[-1]) and emb[0].shape[1] == 1:   # not after a union
-                emb = self._project_path(emb, queries[:, col:col + len(qs[-1])])
-                return emb, col + len(qs[-1])
-            if emb[-1] is None:
-                emb[-1] = torch.zeros_like(emb[0])
+            if fused and emb[0].shape[1] == 1:   # not after a union
+                return self._embed_path(emb, queries[:, col:col + n_hops]), col + n_hops
             for _ in qs[-1]:
                 emb = self._project(emb, queries[:, col])
                 col += 1
@@ -526,11 +539,12 @@ def _cpu_reference_port(cfg, steps, warmup, sample_queries, table_rows):
 # the GPU arm
 # ------------------------------------------------------------------------------------------------
 
-# DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on a
-# 2M-row capture of the Query2box workload, scaled to a full-size launch by the units processed:
-# the two distance kernels process B*K rows per launch at every table size; the update kernel moves
-# 8070 bytes per distinct row.  Other workloads: None.
-NCU_TRAFFIC_BYTES = {"rows_forward": 1.722e9, "rows_backward": 4.094e9}
+# DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum, a one-pass
+# capture) on the Query2box workload.  Forward, and backward with the update folded in: captured at
+# the full benchmark size (10.76M-row table, 1p structure; the kernels process B*K rows per launch).
+# Backward without the folded-in update: a 2M-row capture scaled by the rows processed.  The update
+# kernel moves 8070 bytes per distinct row it updates.  Other workloads: None.
+NCU_TRAFFIC_BYTES = {"rows_forward": 1.758e9, "rows_backward": 4.094e9, "rows_backward_fused": 6.934e9}
 NCU_UPDATE_BYTES_PER_ROW = 8070.0
 
 # fp32 ALU instructions per (pair, dim) term evaluation in the inner loop of the shared-candidate
@@ -539,11 +553,11 @@ ALU_OPS_PER_TERM = {"box": {"fwd": 6, "bwd": 14}, "vec": {"fwd": 2, "bwd": 5}}
 
 
 def ncu_traffic(workload, kernel, n_unique_mean, fused=False):
-    if workload != "freebase_q2b" or fused:
-        return None         # (no capture of the kernels with the in-backward update yet)
+    if workload != "freebase_q2b":
+        return None
     if kernel in ("sparse_update_rows", "shard_reduce_update"):
-        return round(NCU_UPDATE_BYTES_PER_ROW * n_unique_mean)
-    return NCU_TRAFFIC_BYTES.get(kernel)
+        return None if fused else round(NCU_UPDATE_BYTES_PER_ROW * n_unique_mean)
+    return NCU_TRAFFIC_BYTES.get(kernel + "_fused" if fused and kernel == "rows_backward" else kernel)
 
 
 def algorithmic_bytes(cfg, n_unique_mean, n_single_mean=0.0):

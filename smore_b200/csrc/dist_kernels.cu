@@ -1374,8 +1374,7 @@ static RowPlan plan_rows(const Shape& s, bool aligned) {
 static bool shared_shape(const Shape& s, bool aligned) {
   return aligned && s.be == 1 && s.bc == s.bsize && s.ne == s.num && s.nc == 1 && (s.dim & 3) == 0 &&
          s.bsize >= 8 && s.num >= 8 && s.bsize < ((size_t)1 << 24) && s.num < ((size_t)1 << 30) &&
-         s.dim < ((size_t)1 << 20) && (s.bsize + kTileB - 1) / kTileB <= 65535 &&
-         ((s.dim >> 2) + kGradCols - 1) / kGradCols <= 65535;
+         s.dim < ((size_t)1 << 20) && (s.bsize + kTileB - 1) / kTileB <= 65535;   // grid.y / grid.z limits
 }
 
 // Launches row_backward_bulk_kernel when the row width suits it.  Returns 1 when launched, 0 when
@@ -1509,6 +1508,49 @@ static int launch_forward(const Shape& s, const float* ent, const int64_t* idx, 
   return check_launch("cell_forward_kernel");
 }
 
+// Both gradients of the shared-candidate shape from one evaluation of every term
+// (shared_backward_tile_kernel): a cluster of up to 8 CTAs per (KT candidate rows, 128 dims) splits
+// the queries; the query gradients are reduced into zeroed buffers.  The device runs about one
+// 8-CTA cluster per SM at a time whatever the CTA's size, so CTAs are 4 warps wide.
+template <class Term, int KT>
+static int launch_shared_backward_kt(const Shape& s, const SharedArgs& a, const SharedGradArgs& ga, cudaStream_t st) {
+  const size_t qbytes = s.bsize * s.dim * sizeof(float);
+  if (cudaMemsetAsync(ga.g_first, 0, qbytes, st) != cudaSuccess ||
+      (Term::kNQ == 2 && cudaMemsetAsync(ga.g_second, 0, qbytes, st) != cudaSuccess))
+    return fail(SMORE_ERR_CUDA, "dist_backward: cudaMemsetAsync failed");
+  // dims per CTA: whole warps, at most 128 (a warp past the last dim idles at the barriers only)
+  const int threads = (int)std::min<size_t>(128, ((s.dim + 31) / 32) * 32);
+  const unsigned dchunks = (unsigned)((s.dim + threads - 1) / threads);
+  unsigned split = 1;   // query segments = CTAs per cluster: enough CTAs to fill the device, >= 32 queries each
+  const size_t base_ctas = ((s.num + KT - 1) / KT) * dchunks;
+  while (split < 8 && s.bsize / (split * 2) >= 32 && base_ctas * split * threads < (size_t)sm_count() * 2048 * 4) split *= 2;
+  const int seg_b = (int)((s.bsize + split - 1) / split);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((s.num + KT - 1) / KT), split, dchunks);
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.dynamicSmemBytes = (size_t)KT * Term::kMul * threads * sizeof(float);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = split;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, shared_backward_tile_kernel<Term, KT>, a, ga, seg_b) != cudaSuccess)
+    return fail(SMORE_ERR_CUDA, "shared_backward_tile_kernel: launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+  return check_launch("shared_backward_tile_kernel");
+}
+
+template <class Term>
+static int launch_shared_backward(const Shape& s, const SharedArgs& a, const SharedGradArgs& ga, cudaStream_t st) {
+  // terms of one operand each and one output are cheap next to the per-query loads and reductions:
+  // twice the rows per thread halves those
+  if (Term::kMul == 1 && Term::kNQ == 1 && Term::kNOut == 1 && s.num >= 16)
+    return launch_shared_backward_kt<Term, 16>(s, a, ga, st);
+  return launch_shared_backward_kt<Term, 8>(s, a, ga, st);
+}
+
 template <class Term>
 static int launch_backward(const Shape& s, const float* gout0, const float* gout1, const float* ent,
                            const int64_t* idx, const float* first, const float* second, float* g_ent,
@@ -1546,12 +1588,7 @@ static int launch_backward(const Shape& s, const float* gout0, const float* gout
   if (shared_shape(s, aligned)) {
     SharedArgs a{ent, idx, first, second, (int)s.bsize, (int)s.num, (int)s.dim, (long long)s.n_rows};
     SharedGradArgs ga{gout0, gout1, g_ent, slot, slot_count, g_rows, g_first, g_second};
-    const unsigned cols = (unsigned)(((s.dim >> 2) + kGradCols - 1) / kGradCols);
-    dim3 grid_e((unsigned)((s.num + kGradRows - 1) / kGradRows), cols);
-    dim3 grid_q((unsigned)((s.bsize + kGradRows - 1) / kGradRows), cols);
-    shared_backward_ent_kernel<Term><<<grid_e, kGradRows * kGradCols, 0, st>>>(a, ga);
-    shared_backward_query_kernel<Term><<<grid_q, kGradRows * kGradCols, 0, st>>>(a, ga);
-    return check_launch("shared_backward kernels", 2);
+    return launch_shared_backward<Term>(s, a, ga, st);
   }
   CellArgs<float> a{ent, idx, first, second, s.bsize, s.num, s.be, s.ne, s.bc, s.nc, s.dim, (long long)s.n_rows};
   cell_backward_ent_kernel<float, Term><<<grid_for(s.be * s.ne * s.dim, 256), 256, 0, st>>>(

@@ -5,10 +5,10 @@
 // Every (query, candidate) pair re-uses rows that other pairs also use, so this shape is bound by
 // fp32 ALU throughput and on-chip bandwidth, not by HBM: B*K*dim term evaluations against only
 // (B + K)*dim*4 bytes.  The forward kernel is tiled like a SIMT matrix product (a 64 x 64 tile of
-// cells per CTA, operands staged through shared memory, 4 x 4 cells per thread); the two backward
-// kernels give each thread one 16-byte column of one gradient row and walk the other operand's
-// rows, which come from L2.  All three are deterministic (no atomics except into rows that occur
-// several times in a step's compact gradient buffer).
+// cells per CTA, operands staged through shared memory, 4 x 4 cells per thread); the backward
+// kernel evaluates every term once for both gradients: candidate-row gradients are summed in a fixed
+// order (registers, then across a thread-block cluster), query gradients by floating-point
+// reductions in L2.
 //
 // The reference runs this shape through the same three kernels as every other shape
 // (smore/common/torchext/common_kernel.h:33-123): one warp per cell re-reading both rows from L2
@@ -153,137 +153,36 @@ struct SharedGradArgs {
   float* g_second;            // [B, dim]
 };
 
-template <class Term>
-__device__ __forceinline__ void bwd_vec4(const float* g, const float4& e0, const float4& e1, const float4& q0,
-                                         const float4& q1, float4& ge0, float4& ge1, float4& gq0, float4& gq1) {
-  Term::bwd(g, e0.x, e1.x, q0.x, q1.x, ge0.x, ge1.x, gq0.x, gq1.x);
-  Term::bwd(g, e0.y, e1.y, q0.y, q1.y, ge0.y, ge1.y, gq0.y, gq1.y);
-  Term::bwd(g, e0.z, e1.z, q0.z, q1.z, ge0.z, ge1.z, gq0.z, gq1.z);
-  Term::bwd(g, e0.w, e1.w, q0.w, q1.w, ge0.w, ge1.w, gq0.w, gq1.w);
-}
-
-constexpr int kGradRows = 8;    // gradient rows per CTA
-constexpr int kGradCols = 16;   // 16-byte columns per CTA
-
-// g_ent[k, :] = sum over queries b: thread = (row k, one 16-byte column), queries walked in order.
-template <class Term>
-__global__ void __launch_bounds__(kGradRows* kGradCols)
-    shared_backward_ent_kernel(SharedArgs a, SharedGradArgs ga) {
-  const int tx = threadIdx.x % kGradCols, ty = threadIdx.x / kGradCols;
-  const int k = blockIdx.x * kGradRows + ty, c4 = blockIdx.y * kGradCols + tx;
-  const int dim4 = a.dim >> 2;
-  if (k >= a.K || c4 >= dim4) return;
-  const size_t w4 = (size_t)dim4 * Term::kMul;
-  const long long rid = a.idx ? checked_row_id(a.idx, k, a.n_rows, &g_async_status) : (long long)k;
-  if (rid < 0) return;   // no gradient for a row that does not exist
-  const size_t row = (size_t)rid;
-  const float4* pe = reinterpret_cast<const float4*>(a.ent) + row * w4 + c4;
-  const float4 e0 = __ldg(pe);
-  const float4 e1 = Term::kMul == 2 ? __ldg(pe + dim4) : e0;
-  const float4* q0p = reinterpret_cast<const float4*>(a.first) + c4;
-  const float4* q1p = reinterpret_cast<const float4*>(a.second) + c4;
-  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
-  float4 ge0 = z4, ge1 = z4, t0 = z4, t1 = z4;
-#pragma unroll 4
-  for (int b = 0; b < a.B; ++b) {
-    float g[Term::kNOut];
-    g[0] = __ldg(ga.gout0 + (size_t)b * a.K + k);
-    if (Term::kNOut == 2) g[Term::kNOut - 1] = __ldg(ga.gout1 + (size_t)b * a.K + k);
-    const float4 q0 = __ldg(q0p + (size_t)b * dim4);
-    const float4 q1 = Term::kNQ == 2 ? __ldg(q1p + (size_t)b * dim4) : q0;
-    bwd_vec4<Term>(g, e0, e1, q0, q1, ge0, ge1, t0, t1);
-  }
-  if (ga.slot == nullptr) {
-    float4* out = reinterpret_cast<float4*>(ga.g_ent) + (size_t)k * w4 + c4;
-    out[0] = ge0;
-    if (Term::kMul == 2) out[dim4] = ge1;
-  } else {
-    const int32_t s = ga.slot[k];
-    if (s < 0) return;
-    float4* out = reinterpret_cast<float4*>(ga.g_rows) + (size_t)s * w4 + c4;
-    if (ga.slot_count != nullptr && ga.slot_count[s] == 1) {
-      out[0] = ge0;
-      if (Term::kMul == 2) out[dim4] = ge1;
-    } else {
-      atomicAdd(out, ge0);
-      if (Term::kMul == 2) atomicAdd(out + dim4, ge1);
-    }
-  }
-}
-
-// g_first / g_second[b, :] = sum over candidates k: thread = (query b, one 16-byte column).
-template <class Term>
-__global__ void __launch_bounds__(kGradRows* kGradCols)
-    shared_backward_query_kernel(SharedArgs a, SharedGradArgs ga) {
-  __shared__ long long rows_sh[kGradRows * kGradCols];
-  const int tx = threadIdx.x % kGradCols, ty = threadIdx.x / kGradCols;
-  const int b = blockIdx.x * kGradRows + ty, c4 = blockIdx.y * kGradCols + tx;
-  const int dim4 = a.dim >> 2;
-  const bool active = b < a.B && c4 < dim4;
-  const size_t w4 = (size_t)dim4 * Term::kMul;
-  const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
-  float4 q0 = z4, q1 = z4;
-  if (active) {
-    q0 = __ldg(reinterpret_cast<const float4*>(a.first) + (size_t)b * dim4 + c4);
-    if (Term::kNQ == 2) q1 = __ldg(reinterpret_cast<const float4*>(a.second) + (size_t)b * dim4 + c4);
-  }
-  const float4* ent4 = reinterpret_cast<const float4*>(a.ent);
-  float4 gq0 = z4, gq1 = z4, t0 = z4, t1 = z4;
-  for (int k0 = 0; k0 < a.K; k0 += kGradRows * kGradCols) {
-    // the CTA's threads fetch the next 128 row ids once
-    __syncthreads();
-    const int kk = k0 + threadIdx.x;
-    rows_sh[threadIdx.x] =
-        kk < a.K ? (a.idx ? checked_row_id(a.idx, kk, a.n_rows, &g_async_status) : (long long)kk) : 0;
-    __syncthreads();
-    if (!active) continue;
-    const int n = min(kGradRows * kGradCols, a.K - k0);
-#pragma unroll 4
-    for (int j = 0; j < n; ++j) {
-      if (rows_sh[j] < 0) continue;   // an id outside the table contributes nothing
-      const float4* pe = ent4 + (size_t)rows_sh[j] * w4 + c4;
-      const float4 e0 = __ldg(pe);
-      const float4 e1 = Term::kMul == 2 ? __ldg(pe + dim4) : e0;
-      float g[Term::kNOut];
-      g[0] = __ldg(ga.gout0 + (size_t)b * a.K + k0 + j);
-      if (Term::kNOut == 2) g[Term::kNOut - 1] = __ldg(ga.gout1 + (size_t)b * a.K + k0 + j);
-      bwd_vec4<Term>(g, e0, e1, q0, q1, t0, t1, gq0, gq1);
-    }
-  }
-  if (active) {
-    reinterpret_cast<float4*>(ga.g_first)[(size_t)b * dim4 + c4] = gq0;
-    if (Term::kNQ == 2) reinterpret_cast<float4*>(ga.g_second)[(size_t)b * dim4 + c4] = gq1;
-  }
-}
-
 // ---- both gradients of the shared-candidate shape from ONE evaluation of every term ----
 //
-// Thread = one embedding dim d; CTA (one warp) = KT candidate rows x a segment of the queries.  The
-// thread keeps e[k, d] and its gradient for the KT rows in registers and walks the segment's queries:
-// per query it loads q[b, d], evaluates the KT terms (upstream gradients broadcast from shared
-// memory) and sends the query's partial gradient (the sum over the CTA's KT rows) to g_first /
-// g_second with one coalesced reduction per warp, so those must be zero at launch.  The CTAs that
-// share rows and dims but hold different query segments form one thread-block cluster: at the end
-// they add their row gradients through distributed shared memory in rank order (deterministic) and
-// each rank writes KT / cluster-size of the rows.
-constexpr int kBwdThreads = 32;   // dims per CTA
+// Thread = one embedding dim d; CTA = KT candidate rows x a segment of the queries x blockDim.x
+// dims.  The thread keeps e[k, d] and its gradient for the KT rows in registers and walks the
+// segment's queries: per query it loads q[b, d], evaluates the KT terms (upstream gradients
+// broadcast from shared memory) and sends the query's partial gradient (the sum over the CTA's KT
+// rows) to g_first / g_second with one coalesced reduction per warp, so those must be zero at
+// launch.  The CTAs that share rows and dims but hold different query segments form one
+// thread-block cluster: at the end they add their row gradients through distributed shared memory
+// in rank order (deterministic) and each rank writes KT / cluster-size of the rows.
 constexpr int kBwdChunkB = 64;    // queries whose upstream gradients are staged at a time
 constexpr int kBwdAhead = 4;      // query rows loaded ahead of the one being used
+constexpr int kBwdMaxThreads = 512;
 
 template <class Term, int KT>
-__global__ void __launch_bounds__(kBwdThreads)
+__global__ void __launch_bounds__(kBwdMaxThreads)
     shared_backward_tile_kernel(SharedArgs a, SharedGradArgs ga, int seg_b) {
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   constexpr int NO = Term::kNOut, M = Term::kMul;
   __shared__ __align__(16) float gs[kBwdChunkB][KT][NO];
-  __shared__ float red[KT * M][kBwdThreads];
   __shared__ long long rows_sh[KT];
+  extern __shared__ float tile_red[];   // [KT * M][blockDim.x]
+  float* red = tile_red;
 
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, T = blockDim.x;
   const int k0 = blockIdx.x * KT;
-  const int d = blockIdx.z * kBwdThreads + tid;
+  const int d = blockIdx.z * T + tid;
   const bool d_ok = d < a.dim;
+  const bool warp_live = blockIdx.z * T + (tid & ~31) < a.dim;   // warps past the last dim only take part in barriers
   const unsigned rank = cluster.block_rank(), n_ranks = cluster.num_blocks();
   const int b_begin = min(a.B, (int)rank * seg_b), b_end = min(a.B, b_begin + seg_b);
 
@@ -310,7 +209,7 @@ __global__ void __launch_bounds__(kBwdThreads)
     const int nb = min(kBwdChunkB, b_end - bs);
     __syncthreads();   // the previous chunk's gradients are no longer being read
     // upstream gradients of the chunk; zero for rows that do not exist, so their terms add nothing
-    for (int i = tid; i < nb * KT; i += kBwdThreads) {
+    for (int i = tid; i < nb * KT; i += T) {
       const int bb = i / KT, j = i % KT;
       const bool ok = rows_sh[j] >= 0;
       const size_t at = (size_t)(bs + bb) * a.K + k0 + j;
@@ -318,6 +217,7 @@ __global__ void __launch_bounds__(kBwdThreads)
       if (NO == 2) gs[bb][j][NO - 1] = ok ? __ldg(ga.gout1 + at) : 0.f;
     }
     __syncthreads();
+    if (!warp_live) continue;
     float q0n[kBwdAhead], q1n[kBwdAhead];
 #pragma unroll
     for (int u = 0; u < kBwdAhead; ++u) {
@@ -355,8 +255,8 @@ __global__ void __launch_bounds__(kBwdThreads)
   // row gradients: sum over the cluster's query segments in rank order
 #pragma unroll
   for (int j = 0; j < KT; ++j) {
-    red[j * M][tid] = ge0[j];
-    if (M == 2) red[j * M + M - 1][tid] = ge1[j];
+    red[(j * M) * T + tid] = ge0[j];
+    if (M == 2) red[(j * M + M - 1) * T + tid] = ge1[j];
   }
   cluster.sync();
   for (int j = (int)rank; j < KT; j += (int)n_ranks) {
@@ -364,9 +264,9 @@ __global__ void __launch_bounds__(kBwdThreads)
     if (k >= a.K || rows_sh[j] < 0 || !d_ok) continue;
     float s0 = 0.f, s1 = 0.f;
     for (unsigned r = 0; r < n_ranks; ++r) {
-      const float* remote = cluster.map_shared_rank(&red[0][0], r);
-      s0 += remote[(j * M) * kBwdThreads + tid];
-      if (M == 2) s1 += remote[(j * M + M - 1) * kBwdThreads + tid];
+      const float* remote = cluster.map_shared_rank(red, r);
+      s0 += remote[(j * M) * T + tid];
+      if (M == 2) s1 += remote[(j * M + M - 1) * T + tid];
     }
     if (ga.slot == nullptr) {
       ga.g_ent[(size_t)k * W + d] = s0;

@@ -472,6 +472,23 @@ class EmbeddingOptimizer(object):
     def _launch_update(self, uniq, g_rows, n_unique, capacity, lr):
         raise NotImplementedError
 
+    def check_status(self):
+        """Raise if a kernel of this process reported trouble since the last check: a bounded wait on
+        an asynchronous copy that ran out (results of that launch are invalid) or a row id outside the
+        table (that position got NaN and no gradient).  Synchronises the device, so call it between
+        steps or every few hundred steps, not inside one; the status word is cleared."""
+        torch.cuda.synchronize(self.table.device)
+        with torch.cuda.device(self.table.device):
+            status = _lib.async_status()
+            if status:
+                _lib.async_status_clear()
+        if status:
+            what = [name for bit, name in ((_lib.STATUS_COPY_WAIT, "a local bulk-copy wait gave up"),
+                                           (_lib.STATUS_PEER_WAIT, "a wait on a copy from a peer gave up"),
+                                           (_lib.STATUS_BAD_ROW_ID, "a row id outside the table was looked up"))
+                    if status & bit]
+            raise RuntimeError("smore_b200 kernels reported status %d: %s" % (status, "; ".join(what) or "unknown"))
+
     def use_device_step(self):
         """Keep the optimizer's step counter on the device from now on (it starts from the current
         host-side value).  Needed when training steps are captured in a CUDA graph and replayed:

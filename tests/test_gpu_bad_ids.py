@@ -149,3 +149,29 @@ def test_gather_rows_with_bad_ids(status_word):
     assert _lib.async_status() == _lib.STATUS_BAD_ROW_ID
     _lib.async_status_clear()
     assert _lib.async_status() == 0
+
+
+def test_optimizer_check_status_raises_once_after_a_bad_lookup(status_word):
+    """EmbeddingOptimizer.check_status turns the device status word into an exception and clears it."""
+    from smore_b200 import embedding, ext_ops
+
+    class _Args(object):
+        optim_mode = ("aggr", "adam", "gpu", True, 0)
+        share_optim_stats = False
+
+    dev = torch.device("cuda", 0)
+    emb = embedding.SparseEmbedding(0, 64)
+    emb.num_rows = 100
+    emb.embedding = torch.nn.Parameter(torch.rand(100, 64, device=dev), requires_grad=False)
+    opt = embedding.AdamEmbedOptimizer(_Args(), emb, 0, lazy_names=("negative_entity",))
+    emb.train()
+    opt.zero_grad()
+    opt.check_status()                                   # clean: no exception
+    ids = torch.tensor([[3, 100, 7, 9]], device=dev)     # 100 is one past the table
+    rows = emb(ids.view(-1), "negative_entity")
+    query = torch.rand(1, 1, 64, device=dev, requires_grad=True)
+    dist = ext_ops.l1_dist(rows.view(1, 4, -1), query)
+    assert torch.isnan(dist[0, 1]) and not torch.isnan(dist[0, [0, 2, 3]]).any()
+    with pytest.raises(RuntimeError, match="row id outside the table"):
+        opt.check_status()
+    opt.check_status()                                   # cleared by the first call

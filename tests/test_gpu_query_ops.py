@@ -51,13 +51,15 @@ def test_project_path_equals_per_hop_ops(B, H, D, R, box, relu, with_start_offse
             close(a.cpu().numpy(), b.cpu().numpy(), 1e-5, what=name)
 
 
-@pytest.mark.parametrize("geo_workload", ["q2b_fb15k", "gqe_fb15k237"])
-@pytest.mark.parametrize("structure", ["1p", "2p", "3p", "ip", "pi", "2u", "up"])
+@pytest.mark.parametrize("geo_workload", ["q2b_fb15k", "gqe_fb15k237", "rotate_wikikg", "complex_wikikg", "distmult_wikikg"])
+@pytest.mark.parametrize("structure", ["1p", "2p", "3p", "2i", "ip", "pi", "2u", "up"])
 def test_query_model_with_fused_paths_matches_per_hop_model(geo_workload, structure):
+    """The step with every path embedded by one kernel, anchors read from the table in place, against
+    the same step with gathered anchors and per-hop torch ops."""
     import bench
     from smore_b200 import embedding, ext_ops
     cfg = dict(bench.WORKLOADS[geo_workload])
-    cfg.update(B=16, K=32, structures=[structure])
+    cfg.update(B=16, K=32, structures=[structure], dim=min(cfg["dim"], 200))
     n_rows, dev = 500, torch.device("cuda", 0)
     torch.manual_seed(4)
     a = bench.QueryModel(cfg, n_rows, dev, ext_ops, embedding, fused_paths=True)
@@ -69,7 +71,7 @@ def test_query_model_with_fused_paths_matches_per_hop_model(geo_workload, struct
     la = bench.train_step(a, pos, neg, q, structure)
     lb = bench.train_step(b, pos, neg, q, structure)
     torch.cuda.synchronize()
-    close(la.item(), lb.item(), 1e-6, what="loss")
+    close(la.item(), lb.item(), 1e-6 if cfg["geo"] in ("box", "vec") else 1e-5, what="loss")
     close(a.relation_embedding.detach().cpu().numpy(), b.relation_embedding.detach().cpu().numpy(), 1e-5, what="relations")
     close(a.entity_embedding.embedding.detach().cpu().numpy(), b.entity_embedding.embedding.detach().cpu().numpy(), 1e-4,
           what="entity table")
