@@ -551,6 +551,85 @@ SMORE_API int smore_shard_reduce_update_rows_dev(float* table, float* m, float* 
                                        double beta1, double beta2, double eps, const float* step_scalars,
                                        int squeeze, void* stream);
 
+/* ---- Owner-side scoring on a row-sharded table --------------------------------------------------
+ * The candidate-scoring ops of a training step read B*K table rows per rank (ext_ops.py:15-22 on
+ * the rows that kg_reasoning.py:299-304 looks up).  Pulling those rows to the rank that holds the
+ * queries, and pushing their gradients back, costs a row (1.6 KB at dim 400) per pair and
+ * direction over NVLink.  Here the queries travel instead: each rank publishes its candidate ids,
+ * its queries and, in the backward pass, the upstream gradients of its scores in peer-visible
+ * memory; the OWNER of the rows scores every rank's pairs that fall into its range against its own
+ * shard, returns 4 or 8 bytes per pair, and in the backward pass applies the row gradients where
+ * the rows live (Adam folded in, as smore_rows_backward_fused_adam) and leaves a partial query
+ * gradient per rank.  No kernel waits for another rank: the caller orders the phases with
+ * stream-ordered barriers (publish -> select/score -> read results; publish upstream gradients ->
+ * differentiate/update -> sum the partial query gradients).
+ *
+ * Rank r's descriptor is int32[8] {n_queries, K, 0...}: its ids are [n_queries, K] int64 global
+ * row ids, its queries [n_queries, dim] per operand, its results / upstream gradients [n_queries,
+ * K] per output.  All `*_ptrs` arguments are device arrays with one (peer) pointer per rank.
+ * max_queries / pairs_capacity are what every rank's buffers were sized for; a descriptor beyond
+ * them, or more selected pairs than `capacity`, drops the work concerned and sets bit 3 of
+ * smore_async_status.
+ *
+ * smore_owner_select_pairs: for every (rank, query) the pairs whose id lies in [base, base +
+ *   shard_rows) become one segment of the compact arrays: rows[] (local row ids), positions[]
+ *   (query * K + k on the requester), in increasing k; segments[(rank * max_queries + query) * 2 +
+ *   {0, 1}] = {first compact position, count}; n_selected[0] = pairs selected (int32[2]).
+ * smore_owner_gather_queries: first_all / second_all[(rank * max_queries + query), dim] <- the
+ *   ranks' queries (second_* may be NULL for one-operand distances).
+ * smore_rows_forward_ragged / smore_rows_backward_fused_adam_ragged: the row-stream kernels with
+ *   query q = segment q scoring rows[segments[2q] .. + segments[2q+1]); results (out0, out1) and
+ *   upstream gradients (gout0, gout1) are indexed by compact position; g_first / g_second
+ *   [n_segments, dim] receive each segment's query gradient.  Backward: slot / slot_count / g_rows
+ *   / uniq / m / v and the Adam arguments as in smore_rows_backward_fused_adam, over the owner's
+ *   distinct rows.  Rows of 1 KB to about 4 KB, dim a multiple of 4 above 256 (SMORE_ERR_BAD_SHAPE
+ *   otherwise, nothing enqueued).  dist_id may be SMORE_DIST_BOX_BOTH.
+ * smore_owner_scatter_results: dst*_ptrs[rank][positions[c]] = out*[c] for every selected pair.
+ * smore_owner_gather_upstream: g*[c] = g*_ptrs[rank][positions[c]].
+ * smore_owner_plan: smore_shard_owner_plan with the first *n_selected entries of `ids` already
+ *   holding the selected pairs' local row ids (pair_capacity = room reserved for them; capacity
+ *   >= pair_capacity + n_ranks * sum(plan_caps)): the lists' runs are appended behind them and the
+ *   whole array is de-duplicated, so that slot / counts cover both kinds of contribution.
+ * smore_owner_add_list_rows: g_rows[slot[p]] (+)= the gradient row of list position p, for the
+ *   compact positions of the lists' runs (store if counts == 1, atomic add otherwise); `expect` =
+ *   about how many there are (sizes the grid).
+ * smore_owner_sum_query_grads: out[q, :] = sum over owners o of part_ptrs[o][(my_rank *
+ *   max_queries + q), :], in owner order (the requester's query gradient). */
+SMORE_API int smore_owner_select_pairs(const int64_t* const* pair_id_ptrs, const int32_t* const* desc_ptrs,
+                             size_t n_ranks, size_t max_queries, size_t pairs_capacity, int64_t base,
+                             size_t shard_rows, size_t capacity, int64_t* rows, int32_t* positions,
+                             int32_t* segments, int32_t* n_selected, void* stream);
+SMORE_API int smore_owner_gather_queries(const float* const* first_ptrs, const float* const* second_ptrs,
+                               const int32_t* const* desc_ptrs, size_t n_ranks, size_t max_queries,
+                               size_t pairs_capacity, size_t dim, float* first_all, float* second_all,
+                               void* stream);
+SMORE_API int smore_rows_forward_ragged(int dist_id, const float* table, const int64_t* rows, size_t n_table_rows,
+                              const float* first, const float* second, const int32_t* segments,
+                              size_t n_segments, size_t dim, float* out0, float* out1, void* stream);
+SMORE_API int smore_rows_backward_fused_adam_ragged(int dist_id, const float* gout0, const float* gout1, float* table,
+                                          const int64_t* rows, size_t n_table_rows, const float* first,
+                                          const float* second, const int32_t* segments, size_t n_segments,
+                                          const int32_t* slot, const int32_t* slot_count, float* g_rows,
+                                          float* g_first, float* g_second, size_t dim, float* m, float* v,
+                                          int64_t* uniq, double lr, double beta1, double beta2, double eps,
+                                          int64_t step, const float* step_scalars, void* stream);
+SMORE_API int smore_owner_scatter_results(const float* out0, const float* out1, const int32_t* positions,
+                                const int32_t* segments, float* const* dst0_ptrs, float* const* dst1_ptrs,
+                                size_t n_ranks, size_t max_queries, void* stream);
+SMORE_API int smore_owner_gather_upstream(const float* const* g0_ptrs, const float* const* g1_ptrs,
+                                const int32_t* positions, const int32_t* segments, size_t n_ranks,
+                                size_t max_queries, float* g0, float* g1, void* stream);
+SMORE_API int smore_owner_plan(const int64_t* const* uniq_ptrs, const int32_t* const* nuniq_ptrs, size_t n_ranks,
+                     size_t n_plans, const int32_t* plan_caps, int64_t base, size_t shard_rows, size_t capacity,
+                     int64_t* ids, int32_t* runs, int64_t* uniq, int32_t* slot, int32_t* counts,
+                     int32_t* n_unique, uint32_t* dirty, void* workspace, size_t workspace_bytes,
+                     const int32_t* n_selected, size_t pair_capacity, void* stream);
+SMORE_API int smore_owner_add_list_rows(const float* const* grad_ptrs, const int32_t* runs, size_t n_lists,
+                              const int32_t* slot, const int32_t* counts, float* g_rows, size_t width,
+                              size_t expect, void* stream);
+SMORE_API int smore_owner_sum_query_grads(const float* const* part_ptrs, size_t n_ranks, size_t my_rank,
+                                size_t max_queries, size_t n_queries, size_t dim, float* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -60,8 +60,9 @@ def _local_deps(src):
             for line in open(h):
                 if line.strip().startswith('#include "'):
                     name = line.split('"')[1]
-                    if os.path.exists(os.path.join(HERE, name)):
-                        deps.append(os.path.join(HERE, name))
+                    for d in (HERE, os.path.join(ROOT, "include")):
+                        if os.path.exists(os.path.join(d, name)):
+                            deps.append(os.path.join(d, name))
     return deps
 
 

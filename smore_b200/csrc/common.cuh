@@ -49,6 +49,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 constexpr int kStatusCopyWait = 1;   // a bounded wait for a bulk copy gave up (distance kernels)
 constexpr int kStatusPeerWait = 2;   // the same in the background row pull
 constexpr int kStatusBadRowId = 4;   // a caller-supplied row id lay outside the table
+constexpr int kStatusCapacity = 8;   // more work arrived than a fixed-size buffer holds (owner-side scoring)
 
 // Row ids come from the caller.  One outside [0, n_rows) must never become an address: the load
 // uses row 0 instead, the caller of this helper invalidates what the id belongs to (forward: NaN

@@ -15,6 +15,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <climits>
 #include <map>
 #include <mutex>
 #include <utility>
@@ -188,7 +189,36 @@ struct RowArgs {
   int chunks;              // CTAs per query
   int wrows;               // rows a warp takes per sweep (<= 32)
   long long n_rows;        // rows of `ent` when idx != nullptr (0: ids are not checked)
+  // Ragged form (bulk-copy kernels): query q has the seg[q].y candidate rows whose ids are
+  // idx[seg[q].x ...]; results and upstream gradients are indexed by the same compact positions.
+  // One CTA per query; K, rows_per_cta and chunks are not used.
+  const int2* seg;
 };
+
+// The block of candidate rows a CTA of the row-stream kernels works on.
+struct RowBlock {
+  int b;            // query
+  int r_begin, r_end;
+  size_t pos_base;  // position of the query's row 0 in idx / results
+};
+
+__device__ __forceinline__ RowBlock row_block(const RowArgs& a) {
+  RowBlock rb;
+  if (a.seg != nullptr) {
+    const int2 s = a.seg[blockIdx.x];
+    rb.b = (int)blockIdx.x;
+    rb.r_begin = 0;
+    rb.r_end = s.y;
+    rb.pos_base = (size_t)s.x;
+  } else {
+    rb.b = blockIdx.x / a.chunks;
+    const int c = blockIdx.x - rb.b * a.chunks;
+    rb.r_begin = c * a.rows_per_cta;
+    rb.r_end = min(a.K, rb.r_begin + a.rows_per_cta);
+    rb.pos_base = (size_t)rb.b * a.K;
+  }
+  return rb;
+}
 
 __device__ __forceinline__ float4 ld_row4(const float4* p) { return __ldg(p); }
 
@@ -443,7 +473,8 @@ __global__ void __launch_bounds__(kRowCtaThreads)
     row_forward_bulk_kernel(RowArgs a, float* __restrict__ dst0, float* __restrict__ dst1, int stages) {
   extern __shared__ __align__(128) unsigned char bulk_smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int b = blockIdx.x / a.chunks, c = blockIdx.x - b * a.chunks;
+  const RowBlock rb = row_block(a);
+  const int b = rb.b;
   const int dim4 = a.dim >> 2;
   const unsigned row_bytes = (unsigned)dim4 * Term::kMul * 16u;
   const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -467,12 +498,11 @@ __global__ void __launch_bounds__(kRowCtaThreads)
     }
   }
 
-  const int r_begin = c * a.rows_per_cta;
-  const int r_end = min(a.K, r_begin + a.rows_per_cta);
+  const int r_begin = rb.r_begin, r_end = rb.r_end;
   const int per_warp = (r_end - r_begin + kRowCtaWarps - 1) / kRowCtaWarps;
   const int w_begin = r_begin + warp * per_warp;
   const int n = max(0, min(r_end, w_begin + per_warp) - w_begin);
-  const size_t pos0 = (size_t)b * a.K + w_begin;
+  const size_t pos0 = rb.pos_base + w_begin;
   const unsigned char* ent = reinterpret_cast<const unsigned char*>(a.ent);
 
   // row ids of a batch of 32 rows, one per lane; -1 marks an id outside the table (row 0 is copied
@@ -772,7 +802,8 @@ __global__ void __launch_bounds__(kRowCtaThreads, 2)
   constexpr int NG = NB * Term::kNOut;
   extern __shared__ __align__(128) unsigned char bulk_smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int b = blockIdx.x / a.chunks, c = blockIdx.x - b * a.chunks;
+  const RowBlock rb = row_block(a);
+  const int b = rb.b;
   const int dim4 = a.dim >> 2;
   const unsigned row_bytes = (unsigned)dim4 * Term::kMul * 16u;
   const unsigned stage_bytes = 2u * row_bytes;          // [parameter row | first-moment row]
@@ -804,12 +835,11 @@ __global__ void __launch_bounds__(kRowCtaThreads, 2)
 #pragma unroll
     for (int j = 0; j < NCH; ++j) gq0[u][j] = gq1[u][j] = z4;
 
-  const int r_begin = c * a.rows_per_cta;
-  const int r_end = min(a.K, r_begin + a.rows_per_cta);
+  const int r_begin = rb.r_begin, r_end = rb.r_end;
   const int per_warp = (r_end - r_begin + kRowCtaWarps - 1) / kRowCtaWarps;
   const int w_begin = r_begin + warp * per_warp;
   const int n = max(0, min(r_end, w_begin + per_warp) - w_begin);
-  const size_t pos0 = (size_t)b * a.K + w_begin;
+  const size_t pos0 = rb.pos_base + w_begin;
   const unsigned char* ent = reinterpret_cast<const unsigned char*>(a.ent);
   const unsigned char* mom = reinterpret_cast<const unsigned char*>(ua.m);
   unsigned char* gbase = reinterpret_cast<unsigned char*>(ga.g_rows);
@@ -843,7 +873,8 @@ __global__ void __launch_bounds__(kRowCtaThreads, 2)
         if (m.single) m.v = ua.v[m.src];
 #pragma unroll
         for (int u = 0; u < NB; ++u) {
-          const size_t o = ((size_t)b * NB + u) * a.K + (w_begin + t);
+          // (the ragged form has one branch: upstream gradients sit at the rows' compact positions)
+          const size_t o = a.seg != nullptr ? pos : ((size_t)b * NB + u) * a.K + (w_begin + t);
           m.g[u * Term::kNOut] = ga.gout0[o];
           if (Term::kNOut == 2) m.g[u * Term::kNOut + Term::kNOut - 1] = ga.gout1[o];
         }
@@ -1425,8 +1456,12 @@ static int launch_backward_adam(const Shape& s, RowArgs a, RowGradArgs ga, const
   stages = std::max(stages, need);
   const size_t smem = bulk_ring_offset(stages) + q_bytes + (size_t)kRowCtaWarps * stages * 2 * row_bytes;
   if (smem > 200 * 1024) return 0;      // wide rows (RotatE, 4000 bytes): one CTA per SM
-  a.rows_per_cta = (int)std::min<size_t>(s.num, 512);
-  a.chunks = (int)((s.num + a.rows_per_cta - 1) / a.rows_per_cta);
+  if (a.seg != nullptr) {
+    a.chunks = 1;         // ragged form: one CTA per query, s.bsize queries
+  } else {
+    a.rows_per_cta = (int)std::min<size_t>(s.num, 512);
+    a.chunks = (int)((s.num + a.rows_per_cta - 1) / a.rows_per_cta);
+  }
   ga.query_atomic = a.chunks > 1;
   if (a.chunks > 1) {
     const size_t bytes = s.bsize * NB * s.dim * sizeof(float);
@@ -1458,6 +1493,54 @@ static int backward_adam_common(size_t branches, const Shape& s, const float* go
   RowGradArgs ga{gout0, gout1, nullptr, slot, slot_count, g_rows, g_first, g_second, 0};
   if (branches == 1) return launch_backward_adam<Term, 1>(s, a, ga, ua, uniq, p.nch, st);
   return launch_backward_adam<Term, kUnionBranches>(s, a, ga, ua, uniq, p.nch, st);
+}
+
+// ---- ragged form: query q scores / differentiates the candidate rows idx[seg[q].x .. + seg[q].y) ----
+// (the owner side of a row-sharded table: the queries of every rank against this shard's rows).
+// Returns 1 when launched, 0 when the row width is outside the bulk-copy kernels' range.
+static int ragged_nch(size_t dim, size_t mul) {
+  const size_t dim4 = dim >> 2, row_bytes = dim * mul * sizeof(float);
+  if ((dim & 3) || dim > 1024 || dim4 <= 64 || row_bytes < 1024) return 0;
+  return dim4 <= 128 ? 4 : 8;
+}
+
+template <class Term>
+static int launch_forward_ragged(size_t n_seg, size_t dim, size_t n_rows, const float* table, const int64_t* rows,
+                                 const float* first, const float* second, const int2* seg, float* out0, float* out1,
+                                 cudaStream_t st) {
+  if (Term::kNQ == 1) second = first;
+  const int nch = ragged_nch(dim, Term::kMul);
+  if (!nch || !aligned16(table) || !aligned16(first) || !aligned16(second)) return 0;
+  const size_t row_bytes = dim * Term::kMul * sizeof(float);
+  const int stages = (int)std::min<size_t>(8, std::max<size_t>(2, (96 * 1024 / 32 + row_bytes - 1) / row_bytes));
+  const size_t smem = std::max<size_t>(bulk_ring_offset(stages) + (size_t)kRowCtaWarps * stages * row_bytes, 46 * 1024);
+  if (smem > 110 * 1024) return 0;
+  RowArgs a{table, rows, first, second, 0, (int)dim, 0, 1, 0, (long long)n_rows, seg};
+  auto kern = nch == 4 ? row_forward_bulk_kernel<Term, 4> : row_forward_bulk_kernel<Term, 8>;
+  if (int rc = allow_large_smem(kern, 110 * 1024)) return rc;
+  kern<<<(unsigned)n_seg, kRowCtaThreads, smem, st>>>(a, out0, out1, stages);
+  if (int rc = check_launch("row_forward_bulk_kernel")) return rc;
+  return 1;
+}
+
+template <class Term>
+static int launch_backward_adam_ragged(size_t n_seg, size_t dim, size_t n_rows, const float* gout0, const float* gout1,
+                                       float* table, const int64_t* rows, const float* first, const float* second,
+                                       const int2* seg, const int32_t* slot, const int32_t* slot_count, float* g_rows,
+                                       float* g_first, float* g_second, const UpdateArgs& ua, int64_t* uniq,
+                                       cudaStream_t st) {
+  if (Term::kNQ == 1) {
+    second = first;
+    g_second = g_first;
+  }
+  const int nch = ragged_nch(dim, Term::kMul);
+  if (!nch || !aligned16(table) || !aligned16(first) || !aligned16(second) || !aligned16(g_rows) || !aligned16(g_first) ||
+      !aligned16(g_second) || !aligned16(ua.m))
+    return 0;
+  const Shape s{n_seg, 4, n_seg, 4, n_seg, 1, dim, n_rows};
+  RowArgs a{table, rows, first, second, 0, (int)dim, 0, 1, 0, (long long)n_rows, seg};
+  RowGradArgs ga{gout0, gout1, nullptr, slot, slot_count, g_rows, g_first, g_second, 0};
+  return launch_backward_adam<Term, 1>(s, a, ga, ua, uniq, nch, st);
 }
 
 template <class Term>
@@ -1888,6 +1971,97 @@ int smore_rows_backward_fused_adam(int dist_id, const float* gout0, const float*
   return SMORE_OK;
 }
 
+int smore_rows_forward_ragged(int dist_id, const float* table, const int64_t* rows, size_t n_table_rows,
+                              const float* first, const float* second, const int32_t* segments, size_t n_segments,
+                              size_t dim, float* out0, float* out1, void* stream) {
+  const bool both = dist_id == SMORE_DIST_BOX_BOTH;
+  if (!both && (dist_id < 0 || dist_id >= SMORE_DIST_COUNT))
+    return fail(SMORE_ERR_BAD_DIST, "unknown distance id %d", dist_id);
+  if (!table || !rows || !first || !segments || !out0 || (both && !out1) || ((both || needs_second(dist_id)) && !second))
+    return fail(SMORE_ERR_NULL, "rows_forward_ragged: required pointer is NULL");
+  if (n_segments == 0) return SMORE_OK;
+  if (n_segments > (size_t)INT_MAX || dim == 0) return fail(SMORE_ERR_BAD_SHAPE, "rows_forward_ragged: bad sizes");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int2* seg = reinterpret_cast<const int2*>(segments);
+  int rc = 0;
+  if (both) {
+    rc = launch_forward_ragged<TermBoxBoth>(n_segments, dim, n_table_rows, table, rows, first, second, seg, out0, out1, st);
+  } else {
+    switch (dist_id) {
+#define RAGGED_CASE(ID, TERM)                                                                                          \
+  case ID:                                                                                                             \
+    rc = launch_forward_ragged<TERM>(n_segments, dim, n_table_rows, table, rows, first, second, seg, out0, out0, st); \
+    break;
+      RAGGED_CASE(SMORE_DIST_BOX_OUT, TermBoxOut)
+      RAGGED_CASE(SMORE_DIST_BOX_IN, TermBoxIn)
+      RAGGED_CASE(SMORE_DIST_ROTATE, TermRotate)
+      RAGGED_CASE(SMORE_DIST_L1, TermL1)
+      RAGGED_CASE(SMORE_DIST_L2, TermL2)
+      RAGGED_CASE(SMORE_DIST_COMPLEX, TermComplex)
+      RAGGED_CASE(SMORE_DIST_DISTMULT, TermDistmult)
+#undef RAGGED_CASE
+    }
+  }
+  if (rc < 0) return rc;
+  if (rc == 0)
+    return fail(SMORE_ERR_BAD_SHAPE, "rows_forward_ragged: rows of 1 KB to about 6 KB, dim a multiple of 4 above 256, "
+                                     "16-byte aligned operands");
+  return SMORE_OK;
+}
+
+int smore_rows_backward_fused_adam_ragged(int dist_id, const float* gout0, const float* gout1, float* table,
+                                          const int64_t* rows, size_t n_table_rows, const float* first,
+                                          const float* second, const int32_t* segments, size_t n_segments,
+                                          const int32_t* slot, const int32_t* slot_count, float* g_rows, float* g_first,
+                                          float* g_second, size_t dim, float* m, float* v, int64_t* uniq, double lr,
+                                          double beta1, double beta2, double eps, int64_t step,
+                                          const float* step_scalars, void* stream) {
+  const bool both = dist_id == SMORE_DIST_BOX_BOTH;
+  if (!both && (dist_id < 0 || dist_id >= SMORE_DIST_COUNT))
+    return fail(SMORE_ERR_BAD_DIST, "unknown distance id %d", dist_id);
+  const bool two = both || needs_second(dist_id);
+  if (!gout0 || (both && !gout1) || !table || !rows || !first || !segments || !slot || !slot_count || !g_rows ||
+      !g_first || !m || !v || !uniq || (two && (!second || !g_second)))
+    return fail(SMORE_ERR_NULL, "rows_backward_fused_adam_ragged: required pointer is NULL");
+  if (!step_scalars && step < 1) return fail(SMORE_ERR_BAD_SHAPE, "adam step must be >= 1");
+  if (n_segments == 0) return SMORE_OK;
+  if (n_segments > (size_t)INT_MAX || dim == 0) return fail(SMORE_ERR_BAD_SHAPE, "rows_backward_fused_adam_ragged: bad sizes");
+  const size_t mul = (dist_id == SMORE_DIST_ROTATE || dist_id == SMORE_DIST_COMPLEX) ? 2 : 1;
+  UpdateArgs ua;
+  ua.table = table; ua.m = m; ua.v = v; ua.uniq = nullptr; ua.g_rows = nullptr; ua.n_unique = nullptr;
+  ua.width = dim * mul;
+  set_hyper(ua, lr, beta1, beta2, eps, step_scalars ? 1 : step, 1);
+  ua.dyn = step_scalars;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int2* seg = reinterpret_cast<const int2*>(segments);
+  int rc = 0;
+  if (both) {
+    rc = launch_backward_adam_ragged<TermBoxBoth>(n_segments, dim, n_table_rows, gout0, gout1, table, rows, first, second,
+                                                  seg, slot, slot_count, g_rows, g_first, g_second, ua, uniq, st);
+  } else {
+    switch (dist_id) {
+#define RAGGED_CASE(ID, TERM)                                                                                      \
+  case ID:                                                                                                         \
+    rc = launch_backward_adam_ragged<TERM>(n_segments, dim, n_table_rows, gout0, gout0, table, rows, first, second, \
+                                           seg, slot, slot_count, g_rows, g_first, g_second, ua, uniq, st);        \
+    break;
+      RAGGED_CASE(SMORE_DIST_BOX_OUT, TermBoxOut)
+      RAGGED_CASE(SMORE_DIST_BOX_IN, TermBoxIn)
+      RAGGED_CASE(SMORE_DIST_ROTATE, TermRotate)
+      RAGGED_CASE(SMORE_DIST_L1, TermL1)
+      RAGGED_CASE(SMORE_DIST_L2, TermL2)
+      RAGGED_CASE(SMORE_DIST_COMPLEX, TermComplex)
+      RAGGED_CASE(SMORE_DIST_DISTMULT, TermDistmult)
+#undef RAGGED_CASE
+    }
+  }
+  if (rc < 0) return rc;
+  if (rc == 0)
+    return fail(SMORE_ERR_BAD_SHAPE, "rows_backward_fused_adam_ragged: rows of 1 KB to about 4 KB, dim a multiple of 4 "
+                                     "above 256, 16-byte aligned operands");
+  return SMORE_OK;
+}
+
 size_t smore_score_filtered_ranks_workspace_bytes(size_t n_queries, size_t n_answers) {
   const size_t scores = ((n_queries * n_answers * sizeof(float) + 255) / 256) * 256;
   return carve_rank_workspace(nullptr, n_answers).bytes + 2 * scores + 256;
@@ -1970,7 +2144,7 @@ int smore_async_status(int* status) {
   if (int rc = smore_rows_status(&rows)) return rc;
   int query = 0;
   if (int rc = smore_query_status(&query)) return rc;
-  *status = v | (peer ? kStatusPeerWait : 0) | rows | query;
+  *status = v | ((peer & 1) ? kStatusPeerWait : 0) | (peer & ~1) | rows | query;
   return SMORE_OK;
 }
 

@@ -6,13 +6,19 @@
 // smore/models/kg_reasoning.py:144-147).  Here rows [g*S, (g+1)*S) of the table and of its Adam
 // state live in the HBM of GPU g, and every exchange is a kernel of this file doing plain 128-bit
 // loads from peer-mapped memory:
-//   fetch_rows_kernel          requester pulls each distinct row of its step once into a local
-//                              staging block (forward and backward then run on local memory)
-//   shard_collect_ids_kernel   owner reads every rank's list of distinct row ids and keeps those in
-//                              its range (as local ids; everything else becomes -1)
-//   shard_reduce_update_kernel owner pulls the gradient rows of each of its touched rows from the
-//                              ranks that produced them, sums them in a fixed order and applies
-//                              Adam to its shard — transfer, reduction and update in one pass
+//   fetch_rows_kernel            requester pulls each distinct row of its step once into a local
+//                                staging block (forward and backward then run on local memory)
+//   shard_find_runs / gather_runs owner finds, in every rank's sorted list of distinct row ids, the
+//                                run that lies in its range
+//   shard_reduce_update_ring     owner pulls the gradient rows of each of its touched rows from the
+//                                ranks that produced them, sums them in a fixed order and applies
+//                                Adam to its shard: transfer, reduction and update in one pass
+//   owner_* kernels              owner-side scoring: instead of moving candidate rows to the queries
+//                                (1.6 KB per pair and direction), the queries go to the rows: every
+//                                owner picks the (query, candidate) pairs of all ranks that fall in
+//                                its range, scores and differentiates them against its own rows with
+//                                the row-stream kernels, and only scores, upstream gradients and
+//                                query gradients cross NVLink (a few bytes per pair)
 // No kernel here waits on another rank: ordering between the phases of a step is the caller's
 // (stream-ordered collectives).  Peer data is read with ordinary loads or, in the background row
 // pull, with untiled bulk asynchronous copies (no tensor maps, no multicast).
@@ -312,7 +318,9 @@ __device__ __forceinline__ int lower_bound_ids(const int64_t* ids, int n, int64_
 __global__ void __launch_bounds__(32)
     shard_find_runs_kernel(const int64_t* const* __restrict__ uniq_ptrs, const int32_t* const* __restrict__ nuniq_ptrs,
                            PlanCaps c, int n_lists, int64_t base, int64_t shard_rows, OwnerRuns* __restrict__ runs,
-                           int32_t* __restrict__ total_out) {
+                           int32_t* __restrict__ total_out, const int32_t* __restrict__ n_prefix, int prefix_cap) {
+  // ids already sitting at the front of the compact array (owner-side scoring's pairs): the runs follow them
+  const int pre = n_prefix != nullptr ? min(max(n_prefix[0], 0), prefix_cap) : 0;
   const int l = threadIdx.x;
   int lo = 0, len = 0;
   if (l < n_lists) {
@@ -330,9 +338,9 @@ __global__ void __launch_bounds__(32)
   }
   if (l < n_lists) {
     runs->lo[l] = lo;
-    runs->start[l] = inc - len;
+    runs->start[l] = pre + inc - len;
   }
-  const int total = __shfl_sync(0xffffffffu, inc, 31);
+  const int total = pre + __shfl_sync(0xffffffffu, inc, 31);
   if (l == 0) {
     runs->start[n_lists] = total;
     total_out[0] = total;
@@ -355,7 +363,7 @@ __global__ void __launch_bounds__(256)
   if (threadIdx.x <= n_lists) s_start[threadIdx.x] = runs->start[threadIdx.x];
   __syncthreads();
   const int total = s_start[n_lists];
-  for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < total; p += gridDim.x * blockDim.x) {
+  for (int p = s_start[0] + blockIdx.x * blockDim.x + threadIdx.x; p < total; p += gridDim.x * blockDim.x) {
     const int l = list_of_position(s_start, n_lists, p);
     out_ids[p] = uniq_ptrs[l][s_lo[l] + (p - s_start[l])] - base;
   }
@@ -634,6 +642,177 @@ __global__ void __launch_bounds__(kRingWarps * 32, 2)
   }
 }
 
+// ----------------------------------------------------------------------------------------
+// Owner-side scoring.  Every rank publishes, in peer-visible memory, the candidate row ids of its
+// queries ([n_queries, K] global ids), the queries, and a descriptor {n_queries, K}.  The owner
+//   1. selects the pairs whose row lies in its range: per (rank, query) one contiguous segment of
+//      the compact arrays rows[] (local row ids) and positions[] (query * K + k on the requester),
+//      in increasing k (owner_select_pairs_kernel);
+//   2. copies all queries into one local array indexed by rank * max_queries + query;
+//   3. runs the ragged row-stream kernels over the segments (dist_kernels.cu);
+//   4. sends results back / fetches upstream gradients by position (owner_permute_kernel), and
+//      leaves its partial query gradients for the requesters to sum (owner_sum_query_grads_kernel).
+// ----------------------------------------------------------------------------------------
+
+constexpr int kSelectThreads = 256;
+
+__device__ __forceinline__ bool owner_desc(const int32_t* desc, int max_queries, long long pairs_cap, int* nq, int* K) {
+  const int q = desc[0], k = desc[1];
+  *nq = min(max(q, 0), max_queries);
+  *K = max(k, 0);
+  if (q < 0 || q > max_queries || k < 0 || (long long)q * k > pairs_cap) {   // not what the buffers were sized for
+    atomicOr(&g_peer_async_status, kStatusCapacity);
+    *nq = 0;
+    return false;
+  }
+  return true;
+}
+
+__global__ void __launch_bounds__(kSelectThreads)
+    owner_select_pairs_kernel(const int64_t* const* __restrict__ pair_id_ptrs, const int32_t* const* __restrict__ desc_ptrs,
+                              int max_queries, long long pairs_cap, int64_t base, int64_t shard_rows, int capacity,
+                              int64_t* __restrict__ rows, int32_t* __restrict__ positions, int2* __restrict__ segments,
+                              int32_t* __restrict__ n_selected) {
+  __shared__ int s_warp[kSelectThreads / 32];
+  __shared__ int s_pos0;
+  const int r = blockIdx.y, b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int seg = r * max_queries + b;
+  int nq, K;
+  owner_desc(desc_ptrs[r], max_queries, pairs_cap, &nq, &K);
+  if (b >= nq || K == 0) {
+    if (tid == 0) segments[seg] = make_int2(0, 0);
+    return;
+  }
+  const int64_t* ids = pair_id_ptrs[r] + (size_t)b * K;
+  // pass 1: how many of the query's candidates live here
+  int cnt = 0;
+  for (int k = tid; k < K; k += kSelectThreads) {
+    const int64_t id = ids[k] - base;
+    cnt += (id >= 0 && id < shard_rows) ? 1 : 0;
+  }
+  cnt = __reduce_add_sync(0xffffffffu, cnt);
+  if (lane == 0) s_warp[warp] = cnt;
+  __syncthreads();
+  if (tid == 0) {
+    int total = 0;
+    for (int w = 0; w < kSelectThreads / 32; ++w) total += s_warp[w];
+    int pos0 = total ? atomicAdd(n_selected, total) : 0;
+    if (pos0 + total > capacity) {   // the compact arrays are full: drop the segment and say so
+      atomicOr(&g_peer_async_status, kStatusCapacity);
+      pos0 = -1;
+      total = 0;
+    }
+    segments[seg] = make_int2(max(pos0, 0), total);
+    s_pos0 = pos0;
+  }
+  __syncthreads();
+  int running = s_pos0;
+  if (running < 0) return;
+  // pass 2: the same scan, writing in increasing k
+  for (int k0 = 0; k0 < K; k0 += kSelectThreads) {
+    const int k = k0 + tid;
+    int64_t id = -1;
+    if (k < K) id = ids[k] - base;
+    const bool mine = id >= 0 && id < shard_rows;
+    const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+    __syncthreads();   // s_warp of the previous chunk has been read
+    if (lane == 0) s_warp[warp] = __popc(ballot);
+    __syncthreads();
+    int before = 0, chunk = 0;
+    for (int w = 0; w < kSelectThreads / 32; ++w) {
+      before += w < warp ? s_warp[w] : 0;
+      chunk += s_warp[w];
+    }
+    if (mine) {
+      const int p = running + before + __popc(ballot & ((1u << lane) - 1u));
+      rows[p] = id;
+      positions[p] = b * K + k;
+    }
+    running += chunk;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    owner_gather_queries_kernel(const float* const* __restrict__ first_ptrs, const float* const* __restrict__ second_ptrs,
+                                const int32_t* const* __restrict__ desc_ptrs, int max_queries, long long pairs_cap,
+                                int dim4, float4* __restrict__ first_all, float4* __restrict__ second_all) {
+  const int r = blockIdx.y;
+  int nq, K;
+  if (!owner_desc(desc_ptrs[r], max_queries, pairs_cap, &nq, &K)) return;
+  const size_t total = (size_t)nq * dim4, base = (size_t)r * max_queries * dim4;
+  const float4* f = reinterpret_cast<const float4*>(first_ptrs[r]);
+  const float4* s = second_all != nullptr ? reinterpret_cast<const float4*>(second_ptrs[r]) : nullptr;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    first_all[base + i] = f[i];
+    if (s != nullptr) second_all[base + i] = s[i];
+  }
+}
+
+// kScatter: peer[rank][position] = local[compact]; otherwise local[compact] = peer[rank][position]
+template <bool kScatter>
+__global__ void __launch_bounds__(128)
+    owner_permute_kernel(float* const* __restrict__ peer0, float* const* __restrict__ peer1,
+                         const int32_t* __restrict__ positions, const int2* __restrict__ segments, int max_queries,
+                         float* __restrict__ local0, float* __restrict__ local1) {
+  const int r = blockIdx.y, b = blockIdx.x;
+  const int2 seg = segments[r * max_queries + b];
+  if (seg.y == 0) return;
+  float* p0 = peer0[r];
+  float* p1 = local1 != nullptr ? peer1[r] : nullptr;
+  for (int j = threadIdx.x; j < seg.y; j += blockDim.x) {
+    const int c = seg.x + j, pos = positions[c];
+    if (kScatter) {
+      p0[pos] = local0[c];
+      if (p1 != nullptr) p1[pos] = local1[c];
+    } else {
+      local0[c] = p0[pos];
+      if (p1 != nullptr) local1[c] = p1[pos];
+    }
+  }
+}
+
+// g_rows[slot[p]] (+)= the gradient row that list position p names, for the compact positions of the
+// lists' runs (the positions after the selected pairs)
+__global__ void __launch_bounds__(256)
+    owner_add_list_rows_kernel(const float* const* __restrict__ grad_ptrs, const OwnerRuns* __restrict__ runs, int n_lists,
+                               const int32_t* __restrict__ slot, const int32_t* __restrict__ counts,
+                               float4* __restrict__ g_rows, int w4) {
+  __shared__ int s_lo[kMaxLists], s_start[kMaxLists + 1];
+  if (threadIdx.x < n_lists) s_lo[threadIdx.x] = runs->lo[threadIdx.x];
+  if (threadIdx.x <= n_lists) s_start[threadIdx.x] = runs->start[threadIdx.x];
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int first = s_start[0], total = s_start[n_lists];
+  const int warps = gridDim.x * (blockDim.x >> 5);
+  for (int p = first + blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); p < total; p += warps) {
+    const int32_t s = slot[p];
+    if (s < 0) continue;
+    const int l = list_of_position(s_start, n_lists, p);
+    const float4* src = reinterpret_cast<const float4*>(grad_ptrs[l]) + (size_t)(s_lo[l] + (p - s_start[l])) * w4;
+    float4* dst = g_rows + (size_t)s * w4;
+    const bool single = counts[s] == 1;
+    for (int d = lane; d < w4; d += 32) {
+      const float4 g = src[d];
+      if (single) dst[d] = g;
+      else atomicAdd(dst + d, g);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    owner_sum_query_grads_kernel(const float* const* __restrict__ part_ptrs, int n_ranks, size_t offset4, size_t total4,
+                                 float4* __restrict__ out) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (size_t)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int o = 0; o < n_ranks; ++o) {     // owner order: the same sum on every run
+      const float4 v = reinterpret_cast<const float4*>(part_ptrs[o])[offset4 + i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    out[i] = acc;
+  }
+}
+
+
 static int grid_warps(size_t items) {
   return (int)std::max<size_t>(1, std::min<size_t>((items + 7) / 8, (size_t)sm_count() * 16));
 }
@@ -759,19 +938,19 @@ size_t smore_shard_owner_plan_workspace_bytes(size_t shard_rows) {
   return 256 + smore_unique_rows_workspace_bytes(shard_rows ? shard_rows : 1);
 }
 
-int smore_shard_owner_plan(const int64_t* const* uniq_ptrs, const int32_t* const* nuniq_ptrs, size_t n_ranks,
+static int owner_plan_impl(const int64_t* const* uniq_ptrs, const int32_t* const* nuniq_ptrs, size_t n_ranks,
                            size_t n_plans, const int32_t* plan_caps, int64_t base, size_t shard_rows,
                            size_t capacity, int64_t* ids, int32_t* runs, int64_t* uniq, int32_t* slot,
                            int32_t* counts, int32_t* src, int32_t* n_unique, uint32_t* dirty, void* workspace,
-                           size_t workspace_bytes, void* stream) {
-  if (!uniq_ptrs || !nuniq_ptrs || !ids || !runs || !uniq || !slot || !counts || !src || !n_unique || !workspace)
+                           size_t workspace_bytes, const int32_t* n_prefix, size_t prefix_capacity, void* stream) {
+  if (!uniq_ptrs || !nuniq_ptrs || !ids || !runs || !uniq || !slot || !counts || !n_unique || !workspace)
     return fail(SMORE_ERR_NULL, "shard_owner_plan: NULL pointer");
   PlanCaps c;
   if (int rc = make_caps(plan_caps, n_plans, &c)) return rc;
   if (n_ranks == 0 || n_ranks * n_plans > (size_t)kMaxLists)
     return fail(SMORE_ERR_BAD_SHAPE, "ranks x plans must be 1..%d", kMaxLists);
   if (shard_rows == 0) return fail(SMORE_ERR_BAD_SHAPE, "shard_owner_plan: shard_rows is 0");
-  const size_t worst = n_ranks * (size_t)c.prefix[kMaxPlans];
+  const size_t worst = prefix_capacity + n_ranks * (size_t)c.prefix[kMaxPlans];
   if (worst > (size_t)INT_MAX) return fail(SMORE_ERR_TOO_LARGE, "shard_owner_plan: more than 2^31-1 positions");
   if (capacity < worst)
     return fail(SMORE_ERR_BAD_SHAPE, "shard_owner_plan: capacity %zu, but the lists can hold %zu ids", capacity, worst);
@@ -783,7 +962,8 @@ int smore_shard_owner_plan(const int64_t* const* uniq_ptrs, const int32_t* const
   OwnerRuns* r = reinterpret_cast<OwnerRuns*>(runs);
   int32_t* total = reinterpret_cast<int32_t*>(workspace);            // device count of collected ids
   void* uws = static_cast<unsigned char*>(workspace) + 256;
-  shard_find_runs_kernel<<<1, 32, 0, st>>>(uniq_ptrs, nuniq_ptrs, c, n_lists, base, (int64_t)shard_rows, r, total);
+  shard_find_runs_kernel<<<1, 32, 0, st>>>(uniq_ptrs, nuniq_ptrs, c, n_lists, base, (int64_t)shard_rows, r, total,
+                                           n_prefix, (int)prefix_capacity);
   // the collected ids are expected to be about 1 / n_ranks of the worst case; the kernels below loop
   // over the device-side total, so the grids only have to be large enough to fill the GPU
   const size_t expect = std::max<size_t>(worst / n_ranks, 1);
@@ -792,8 +972,10 @@ int smore_shard_owner_plan(const int64_t* const* uniq_ptrs, const int32_t* const
   if (int rc = unique_rows_impl(ids, worst, total, shard_rows, uniq, slot, counts, n_unique, uws,
                                 workspace_bytes - 256, st))
     return rc;
-  shard_record_sources_kernel<<<grid_threads(expect), 256, 0, st>>>(slot, total, src);
-  count_launches(1);
+  if (src != nullptr) {
+    shard_record_sources_kernel<<<grid_threads(expect), 256, 0, st>>>(slot, total, src);
+    count_launches(1);
+  }
   if (dirty != nullptr) {
     // publish which rows this step updates (readers: the next step's refresh on every rank)
     if (cudaMemsetAsync(dirty, 0, ((shard_rows + 31) / 32) * sizeof(uint32_t), st) != cudaSuccess)
@@ -802,6 +984,121 @@ int smore_shard_owner_plan(const int64_t* const* uniq_ptrs, const int32_t* const
     count_launches(1);
   }
   return check_launch("shard_owner_plan kernels", 0);
+}
+
+int smore_shard_owner_plan(const int64_t* const* uniq_ptrs, const int32_t* const* nuniq_ptrs, size_t n_ranks,
+                           size_t n_plans, const int32_t* plan_caps, int64_t base, size_t shard_rows,
+                           size_t capacity, int64_t* ids, int32_t* runs, int64_t* uniq, int32_t* slot,
+                           int32_t* counts, int32_t* src, int32_t* n_unique, uint32_t* dirty, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+  if (!src) return fail(SMORE_ERR_NULL, "shard_owner_plan: NULL pointer");
+  return owner_plan_impl(uniq_ptrs, nuniq_ptrs, n_ranks, n_plans, plan_caps, base, shard_rows, capacity, ids, runs, uniq,
+                         slot, counts, src, n_unique, dirty, workspace, workspace_bytes, nullptr, 0, stream);
+}
+
+int smore_owner_plan(const int64_t* const* uniq_ptrs, const int32_t* const* nuniq_ptrs, size_t n_ranks, size_t n_plans,
+                     const int32_t* plan_caps, int64_t base, size_t shard_rows, size_t capacity, int64_t* ids,
+                     int32_t* runs, int64_t* uniq, int32_t* slot, int32_t* counts, int32_t* n_unique, uint32_t* dirty,
+                     void* workspace, size_t workspace_bytes, const int32_t* n_selected, size_t pair_capacity,
+                     void* stream) {
+  if (!n_selected) return fail(SMORE_ERR_NULL, "owner_plan: NULL pointer");
+  return owner_plan_impl(uniq_ptrs, nuniq_ptrs, n_ranks, n_plans, plan_caps, base, shard_rows, capacity, ids, runs, uniq,
+                         slot, counts, nullptr, n_unique, dirty, workspace, workspace_bytes, n_selected, pair_capacity,
+                         stream);
+}
+
+static int check_owner_sizes(const char* what, size_t n_ranks, size_t max_queries) {
+  if (n_ranks == 0 || n_ranks > (size_t)kMaxLists || max_queries == 0 || max_queries > 65535u * 64u ||
+      n_ranks * max_queries > (size_t)INT_MAX)
+    return fail(SMORE_ERR_BAD_SHAPE, "%s: 1..%d ranks, 1..%u queries per rank", what, kMaxLists, 65535u * 64u);
+  return SMORE_OK;
+}
+
+int smore_owner_select_pairs(const int64_t* const* pair_id_ptrs, const int32_t* const* desc_ptrs, size_t n_ranks,
+                             size_t max_queries, size_t pairs_capacity, int64_t base, size_t shard_rows,
+                             size_t capacity, int64_t* rows, int32_t* positions, int32_t* segments,
+                             int32_t* n_selected, void* stream) {
+  if (!pair_id_ptrs || !desc_ptrs || !rows || !positions || !segments || !n_selected)
+    return fail(SMORE_ERR_NULL, "owner_select_pairs: NULL pointer");
+  if (int rc = check_owner_sizes("owner_select_pairs", n_ranks, max_queries)) return rc;
+  if (capacity > (size_t)INT_MAX || pairs_capacity > (size_t)INT_MAX || shard_rows == 0)
+    return fail(SMORE_ERR_BAD_SHAPE, "owner_select_pairs: capacities must fit 31 bits, shard_rows > 0");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cudaMemsetAsync(n_selected, 0, 2 * sizeof(int32_t), st) != cudaSuccess)
+    return fail(SMORE_ERR_CUDA, "owner_select_pairs: cudaMemsetAsync failed");
+  dim3 grid((unsigned)max_queries, (unsigned)n_ranks);
+  owner_select_pairs_kernel<<<grid, kSelectThreads, 0, st>>>(pair_id_ptrs, desc_ptrs, (int)max_queries,
+                                                             (long long)pairs_capacity, base, (int64_t)shard_rows,
+                                                             (int)capacity, rows, positions,
+                                                             reinterpret_cast<int2*>(segments), n_selected);
+  return check_launch("owner_select_pairs_kernel");
+}
+
+int smore_owner_gather_queries(const float* const* first_ptrs, const float* const* second_ptrs,
+                               const int32_t* const* desc_ptrs, size_t n_ranks, size_t max_queries,
+                               size_t pairs_capacity, size_t dim, float* first_all, float* second_all, void* stream) {
+  if (!first_ptrs || !desc_ptrs || !first_all || (second_all && !second_ptrs))
+    return fail(SMORE_ERR_NULL, "owner_gather_queries: NULL pointer");
+  if (int rc = check_owner_sizes("owner_gather_queries", n_ranks, max_queries)) return rc;
+  if (dim == 0 || (dim & 3) || !aligned16(first_all) || (second_all && !aligned16(second_all)))
+    return fail(SMORE_ERR_BAD_SHAPE, "owner_gather_queries: dim must be a multiple of 4, buffers 16-byte aligned");
+  dim3 grid((unsigned)std::min<size_t>((max_queries * (dim >> 2) + 255) / 256, (size_t)sm_count() * 4), (unsigned)n_ranks);
+  owner_gather_queries_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
+      first_ptrs, second_ptrs, desc_ptrs, (int)max_queries, (long long)pairs_capacity, (int)(dim >> 2),
+      reinterpret_cast<float4*>(first_all), reinterpret_cast<float4*>(second_all));
+  return check_launch("owner_gather_queries_kernel");
+}
+
+int smore_owner_scatter_results(const float* out0, const float* out1, const int32_t* positions, const int32_t* segments,
+                                float* const* dst0_ptrs, float* const* dst1_ptrs, size_t n_ranks, size_t max_queries,
+                                void* stream) {
+  if (!out0 || !positions || !segments || !dst0_ptrs || (out1 && !dst1_ptrs))
+    return fail(SMORE_ERR_NULL, "owner_scatter_results: NULL pointer");
+  if (int rc = check_owner_sizes("owner_scatter_results", n_ranks, max_queries)) return rc;
+  dim3 grid((unsigned)max_queries, (unsigned)n_ranks);
+  owner_permute_kernel<true><<<grid, 128, 0, (cudaStream_t)stream>>>(
+      dst0_ptrs, dst1_ptrs, positions, reinterpret_cast<const int2*>(segments), (int)max_queries,
+      const_cast<float*>(out0), const_cast<float*>(out1));
+  return check_launch("owner_permute_kernel");
+}
+
+int smore_owner_gather_upstream(const float* const* g0_ptrs, const float* const* g1_ptrs, const int32_t* positions,
+                                const int32_t* segments, size_t n_ranks, size_t max_queries, float* g0, float* g1,
+                                void* stream) {
+  if (!g0_ptrs || !positions || !segments || !g0 || (g1 && !g1_ptrs))
+    return fail(SMORE_ERR_NULL, "owner_gather_upstream: NULL pointer");
+  if (int rc = check_owner_sizes("owner_gather_upstream", n_ranks, max_queries)) return rc;
+  dim3 grid((unsigned)max_queries, (unsigned)n_ranks);
+  owner_permute_kernel<false><<<grid, 128, 0, (cudaStream_t)stream>>>(
+      const_cast<float* const*>(reinterpret_cast<const float* const*>(g0_ptrs)),
+      const_cast<float* const*>(reinterpret_cast<const float* const*>(g1_ptrs)), positions,
+      reinterpret_cast<const int2*>(segments), (int)max_queries, g0, g1);
+  return check_launch("owner_permute_kernel");
+}
+
+int smore_owner_add_list_rows(const float* const* grad_ptrs, const int32_t* runs, size_t n_lists, const int32_t* slot,
+                              const int32_t* counts, float* g_rows, size_t width, size_t expect, void* stream) {
+  if (!grad_ptrs || !runs || !slot || !counts || !g_rows) return fail(SMORE_ERR_NULL, "owner_add_list_rows: NULL pointer");
+  if (n_lists == 0 || n_lists > (size_t)kMaxLists) return fail(SMORE_ERR_BAD_SHAPE, "ranks x plans must be 1..%d", kMaxLists);
+  if (width == 0 || (width & 3) || !aligned16(g_rows))
+    return fail(SMORE_ERR_BAD_SHAPE, "owner_add_list_rows: width must be a multiple of 4 floats");
+  owner_add_list_rows_kernel<<<grid_warps(std::max<size_t>(expect, 1)), 256, 0, (cudaStream_t)stream>>>(
+      grad_ptrs, reinterpret_cast<const OwnerRuns*>(runs), (int)n_lists, slot, counts, reinterpret_cast<float4*>(g_rows),
+      (int)(width >> 2));
+  return check_launch("owner_add_list_rows_kernel");
+}
+
+int smore_owner_sum_query_grads(const float* const* part_ptrs, size_t n_ranks, size_t my_rank, size_t max_queries,
+                                size_t n_queries, size_t dim, float* out, void* stream) {
+  if (!part_ptrs || !out) return fail(SMORE_ERR_NULL, "owner_sum_query_grads: NULL pointer");
+  if (int rc = check_owner_sizes("owner_sum_query_grads", n_ranks, max_queries)) return rc;
+  if (my_rank >= n_ranks || n_queries > max_queries || dim == 0 || (dim & 3) || !aligned16(out))
+    return fail(SMORE_ERR_BAD_SHAPE, "owner_sum_query_grads: bad sizes");
+  if (n_queries == 0) return SMORE_OK;
+  const size_t dim4 = dim >> 2, total4 = n_queries * dim4;
+  owner_sum_query_grads_kernel<<<grid_threads(total4), 256, 0, (cudaStream_t)stream>>>(
+      part_ptrs, (int)n_ranks, my_rank * max_queries * dim4, total4, reinterpret_cast<float4*>(out));
+  return check_launch("owner_sum_query_grads_kernel");
 }
 
 static int shard_reduce_update_impl(float* table, float* m, float* v, const int64_t* uniq, const int32_t* counts,

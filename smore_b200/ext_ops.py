@@ -408,6 +408,9 @@ def _apply(name, entity, first, second):
 
 def _dist(name, entity, first, second=None):
     """Front-end shared by all ops: 3-D operands, or a per-branch loop for 4-D query operands."""
+    if getattr(entity, "remote", False):
+        # rows of a sharded table that stay with their owners (smore_b200.sharded.RemoteRows)
+        return entity.owner.remote_dist(name, entity, first, second)
     if entity.dim() != first.dim():
         if first.dim() != 4 or entity.dim() != 3:
             raise ValueError("expected a 3-D entity operand with 3-D or 4-D query operands")

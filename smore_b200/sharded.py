@@ -23,6 +23,14 @@ happens here over NVLink with plain peer loads, synchronously per step:
             owners updated meanwhile (published as a bitmap) are pulled again, so the result is
             the same as fetching everything after the barrier.
 
+  remote    (optional, `remote=RemoteSpec(...)`) the candidate-scoring op of the step - B*K rows per
+            rank - does not move rows at all: the rank publishes the candidate ids, its queries and
+            later the upstream gradients of its scores; every owner scores and differentiates the
+            pairs that fall into its range against its own shard (smore_owner_* and the ragged
+            row-stream kernels), applies the row gradients in place (Adam folded into the backward
+            kernel) and hands back scores and partial query gradients: a few bytes per pair over
+            NVLink instead of a row each way.
+
 A step therefore equals one optimizer step of a single process on the union of all ranks'
 batches (all gradients of a row are summed before its one Adam update).
 
@@ -121,6 +129,39 @@ class ArenaLayout(object):
         return self.off_grads + self.prefix[p] * self.width * 4
 
 
+class RemoteSpec(object):
+    """Sizes of owner-side scoring: at most `queries` queries of `dim` floats per operand and `pairs`
+    (query, candidate) pairs per rank and step (a union step counts every branch as a query);
+    `owner_pairs` bounds the pairs one owner may receive from all ranks in a step (default: twice a
+    rank's own, at least all of them on one GPU)."""
+
+    def __init__(self, pairs, queries, dim, owner_pairs=None):
+        self.pairs, self.queries, self.dim = int(pairs), int(queries), int(dim)
+        self.owner_pairs = None if owner_pairs is None else int(owner_pairs)
+        if self.dim % 4 or self.pairs <= 0 or self.queries <= 0:
+            raise ValueError("RemoteSpec: dim must be a multiple of 4, pairs and queries positive")
+
+
+class RemoteLayout(object):
+    """Byte layout of a rank's peer-visible block for owner-side scoring:
+    [descriptor int32[8] | candidate ids int64[pairs] | queries float32[2][queries*dim] |
+     results float32[2][pairs] | upstream gradients float32[2][pairs] |
+     partial query gradients float32[2][world*queries*dim] (written by this rank as an owner)]."""
+
+    def __init__(self, spec, world):
+        P, QD = spec.pairs, spec.queries * spec.dim
+        self.off_desc = 0
+        self.off_ids = 256
+        self.off_queries = self.off_ids + _round(P * 8)
+        self.off_results = self.off_queries + 2 * _round(QD * 4)
+        self.off_upstream = self.off_results + 2 * _round(P * 4)
+        self.off_partial = self.off_upstream + 2 * _round(P * 4)
+        self.nbytes = self.off_partial + 2 * _round(world * QD * 4)
+        self.stride_queries = _round(QD * 4)
+        self.stride_pairs = _round(P * 4)
+        self.stride_partial = _round(world * QD * 4)
+
+
 def shard_rows(n_rows_total, world):
     return (n_rows_total + world - 1) // world
 
@@ -158,8 +199,9 @@ class ShardedTable(object):
     between them, so the next step's id list can be prepared while owners still read the current
     one), the bitmap of rows updated in the last step, and the pointer tables."""
 
-    def __init__(self, n_rows_total, width, rank, world, device, plan_caps, squeeze=True, symmetric=False):
+    def __init__(self, n_rows_total, width, rank, world, device, plan_caps, squeeze=True, symmetric=False, remote=None):
         self.n_rows_total, self.width, self.rank, self.world = int(n_rows_total), int(width), rank, world
+        self.remote = remote
         self.device = torch.device(device)
         self.squeeze = bool(squeeze)
         self.S = shard_rows(n_rows_total, world)
@@ -189,6 +231,21 @@ class ShardedTable(object):
                        for p in range(P)] for blk in self._arena_blocks]
         self.peer_table_ptrs = None   # filled by connect()
         self._handles = []
+        self._remote_block = None
+        if remote is not None:
+            if not squeeze:
+                raise _lib.SmoreError("owner-side scoring updates rows with the row-wise second moment (squeeze=True)")
+            rl = self.remote_layout = RemoteLayout(remote, world)
+            blk = self._remote_block = self._alloc(rl.nbytes)
+            blk.tensor.zero_()
+            dev, P, QD = self.device, remote.pairs, remote.queries * remote.dim
+            self.r_desc = blk.view(dev, rl.off_desc, (8,), torch.int32)
+            self.r_ids = blk.view(dev, rl.off_ids, (P,), torch.int64)
+            self.r_queries = [blk.view(dev, rl.off_queries + i * rl.stride_queries, (QD,), torch.float32) for i in range(2)]
+            self.r_results = [blk.view(dev, rl.off_results + i * rl.stride_pairs, (P,), torch.float32) for i in range(2)]
+            self.r_upstream = [blk.view(dev, rl.off_upstream + i * rl.stride_pairs, (P,), torch.float32) for i in range(2)]
+            self.r_partial = [blk.view(dev, rl.off_partial + i * rl.stride_partial, (world * QD,), torch.float32)
+                              for i in range(2)]
 
     def _alloc(self, nbytes):
         nbytes = _round(nbytes, 16)
@@ -202,11 +259,21 @@ class ShardedTable(object):
             t = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
         return _DeviceBlock(t)
 
-    def connect(self, table_ptrs, arena_ptrs, dirty_ptrs):
-        """Install the base pointers of every rank's shard, arenas (`arena_ptrs[parity][rank]`) and
-        updated-rows bitmap (this rank's own included)."""
+    def connect(self, table_ptrs, arena_ptrs, dirty_ptrs, remote_ptrs=None):
+        """Install the base pointers of every rank's shard, arenas (`arena_ptrs[parity][rank]`),
+        updated-rows bitmap and, with owner-side scoring, remote block (this rank's own included)."""
         self.peer_table_ptrs = list(table_ptrs)
         dev = self.device
+        if self.remote is not None:
+            if remote_ptrs is None:
+                raise _lib.SmoreError("connect: the ranks' remote blocks are missing")
+            rl = self.remote_layout
+            tab = lambda off: torch.tensor([p + off for p in remote_ptrs], dtype=torch.int64, device=dev)
+            self.d_r_desc, self.d_r_ids = tab(rl.off_desc), tab(rl.off_ids)
+            self.d_r_queries = [tab(rl.off_queries + i * rl.stride_queries) for i in range(2)]
+            self.d_r_results = [tab(rl.off_results + i * rl.stride_pairs) for i in range(2)]
+            self.d_r_upstream = [tab(rl.off_upstream + i * rl.stride_pairs) for i in range(2)]
+            self.d_r_partial = [tab(rl.off_partial + i * rl.stride_partial) for i in range(2)]
         self.d_shard_ptrs = torch.tensor(self.peer_table_ptrs, dtype=torch.int64, device=dev)
         self.d_dirty_ptrs = torch.tensor(list(dirty_ptrs), dtype=torch.int64, device=dev)
         self.d_uniq_ptrs, self.d_nuniq_ptrs, self.d_grad_ptrs = [], [], []
@@ -224,6 +291,8 @@ class ShardedTable(object):
             raise _lib.SmoreError("connect_processes needs blocks from the symmetric-memory allocator")
         group = group if group is not None else dist.group.WORLD
         blocks = [self._table_block] + self._arena_blocks + [self._dirty_block]
+        if self._remote_block is not None:
+            blocks.append(self._remote_block)
         ptrs = []
         with torch.cuda.device(self.device):
             for blk in blocks:
@@ -233,7 +302,7 @@ class ShardedTable(object):
                 if p[self.rank] != blk.ptr:
                     raise _lib.SmoreError("symmetric-memory rendezvous returned a different address for a local block")
                 ptrs.append(p)
-        self.connect(ptrs[0], [ptrs[1], ptrs[2]], ptrs[3])
+        self.connect(ptrs[0], [ptrs[1], ptrs[2]], ptrs[3], ptrs[4] if len(ptrs) > 4 else None)
 
     def close(self):
         self._handles = []
@@ -408,6 +477,46 @@ class _ShardedPlan(object):
         return self.slot64[lookup.offset:lookup.offset + lookup.n]
 
 
+class RemoteRows(LazyRows):
+    """Candidate rows of a sharded table that never come to this rank: a distance op on them is
+    computed by the rows' owners (ShardedAdamOptimizer.remote_dist)."""
+
+    remote = True
+
+    def _reshaped(self, shape):
+        return RemoteRows(self.owner, self.lookup, shape)
+
+    def materialize(self):
+        raise _lib.SmoreError("remotely scored rows are not brought to this rank; look them up under another name "
+                              "to use them as a tensor")
+
+
+class _RemoteDistFunc(torch.autograd.Function):
+    """A distance between this rank's queries and candidate rows that stay with their owners.  Both
+    passes are collective over the ranks of the shard group: publish, barrier, every owner's share
+    of the work, barrier, collect."""
+
+    @staticmethod
+    def forward(ctx, opt, name, dummy, first, second, n_queries, per_query, out_shape):
+        opt.remote_publish(name, first, second, n_queries, per_query)
+        opt.barrier()
+        opt.remote_owner_forward()
+        opt.barrier()
+        outs = opt.remote_collect_forward(out_shape)
+        ctx.opt, ctx.two = opt, second is not None
+        return outs if len(outs) > 1 else outs[0]
+
+    @staticmethod
+    def backward(ctx, *gouts):
+        opt = ctx.opt
+        opt.remote_publish_upstream(gouts)
+        opt.barrier()
+        opt.remote_owner_backward()
+        opt.barrier()
+        g_first, g_second = opt.remote_collect_backward()
+        return None, None, None, g_first, g_second if ctx.two else None, None, None, None
+
+
 class ShardedAdamOptimizer(EmbeddingOptimizer):
     """EmbeddingOptimizer over a ShardedTable.  `barrier` is a callable that orders the ranks on the
     current stream (default: a one-element NCCL all-reduce); in the single-process emulation it is a
@@ -421,7 +530,7 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         pass
 
     def __init__(self, shard, lazy_names=("negative_entity", "positive_entity"), barrier=None, group=None,
-                 exchange="p2p"):
+                 exchange="p2p", remote_names=("negative_entity",)):
         """exchange: "p2p" - rows and row gradients are read straight from the peers' memory by this
         library's kernels (the shard must be connected: ShardGroup.from_process_group / emulated);
         "nccl" - the fallback for boxes without peer-mapped memory: the same two exchanges as
@@ -468,7 +577,33 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         self._o_src = torch.empty(n_in, dtype=torch.int32, device=dev)
         self._o_nuniq = torch.zeros(2, dtype=torch.int32, device=dev)
         self._started = False
+        self.remote_names = tuple(remote_names) if shard.remote is not None else ()
+        self._r_op = None
+        if shard.remote is not None:
+            if exchange != "p2p":
+                raise ValueError("owner-side scoring reads the peers' memory: exchange must be 'p2p'")
+            self._init_remote()
         self.zero_grad()
+
+    def _init_remote(self):
+        """Owner-side buffers of the remote scoring: compact arrays over the pairs this shard may
+        receive, followed by the lists' runs (ids, slots, counts), and the gradient rows of the
+        shard's touched rows."""
+        sh, spec = self.shard, self.shard.remote
+        dev, G, W = sh.device, sh.world, sh.width
+        cap = spec.owner_pairs or (spec.pairs if G == 1 else min(G * spec.pairs, 2 * spec.pairs))
+        n_tot = cap + G * sh.layout.span
+        QD = G * spec.queries * spec.dim
+        i32 = lambda n: torch.zeros(n, dtype=torch.int32, device=dev)
+        f32 = lambda *shape: torch.empty(*shape, dtype=torch.float32, device=dev)
+        self._r_cap, self._r_total = cap, n_tot
+        self._r_rows = torch.zeros(n_tot, dtype=torch.int64, device=dev)
+        self._r_pos, self._r_seg, self._r_nsel = i32(cap), i32(G * spec.queries * 2), i32(2)
+        self._r_queries = [f32(QD), f32(QD)]
+        self._r_out, self._r_up = [f32(cap), f32(cap)], [f32(cap), f32(cap)]
+        self._r_uniq = torch.zeros(n_tot, dtype=torch.int64, device=dev)
+        self._r_slot, self._r_counts, self._r_nuniq = i32(n_tot), i32(n_tot), i32(2)
+        self._r_g = f32(n_tot, W)
 
     # ---- lookups ----------------------------------------------------------------------------------
     def _workspace(self, which):
@@ -484,6 +619,9 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         self._drop_plans()
         self.grad_list = []
         self.has_grad_list = []
+        self._fused_lr = None
+        self._step_advanced = False
+        self._r_op = None
         if self._started:
             self.parity ^= 1
         self._started = True
@@ -545,6 +683,16 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         lookup = _Lookup(idx, name, self.n_fwd)
         lookup.key = _id_key(indices)
         self.n_fwd += 1
+        if name is not None and name in self.remote_names and self.training and torch.is_grad_enabled():
+            # scored where the rows live: nothing is fetched, the ids are published for the owners
+            if self._r_op is not None:
+                raise _lib.SmoreError("one remotely scored lookup per step")
+            if lookup.n > self.shard.remote.pairs:
+                raise _lib.SmoreError("%d candidate ids, the remote block holds %d (RemoteSpec.pairs)"
+                                      % (lookup.n, self.shard.remote.pairs))
+            self.shard.r_ids[:lookup.n].copy_(idx)
+            self._r_op = {"lookup": lookup, "stage": "ids"}
+            return RemoteRows(self, lookup, (lookup.n, self.shard.width))
         self._pending.append(lookup)
         if name is not None and name in self.lazy_names:
             return LazyRows(self, lookup, (lookup.n, self.shard.width))
@@ -605,6 +753,184 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
     def _materialize(self, lookup):
         return _EmbedLookupFunc.apply(self, self.dummy_tensor, lookup)
 
+    # ---- owner-side scoring -----------------------------------------------------------------------
+    def announce_lr(self, lr):
+        """The learning rate apply_grad(lr) will get; needed before the backward pass of a remotely
+        scored lookup, whose owners apply the row updates inside that pass."""
+        self._fused_lr = float(lr)
+        if getattr(self, "_step_dev", None) is not None and not self._step_advanced:
+            self._advance_device_step(lr)
+            self._step_advanced = True
+
+    def fused_update_args(self, lookup, plan):
+        return None         # staged rows are copies: nothing to update in place on the requester
+
+    def remote_dist(self, name, rows, first, second):
+        """name: a distance of ext_ops ("box_both" included) between `rows` (a RemoteRows handle viewed
+        as [B, K, width]) and query operands [B, 1, dim] or, for union queries, [B, U, 1, dim].  Every
+        rank of the shard group must make this call in the same steps, with the same distance."""
+        B, K, width = rows.as_3d()
+        if self._r_op is None or self._r_op["lookup"] is not rows.lookup or self._r_op["stage"] != "ids":
+            raise _lib.SmoreError("a remotely scored lookup takes exactly one distance op per step")
+        if first.dim() == 4:
+            if first.shape[0] != B or first.shape[2] != 1:
+                raise ValueError("%s: union operands must be [B, U, 1, dim]" % name)
+            U = first.shape[1]
+            n_queries, out_shape = B * U, (B, U, K)
+            if n_queries * K > self.shard.remote.pairs:
+                raise _lib.SmoreError("%d pairs, the remote block holds %d (RemoteSpec.pairs)"
+                                      % (n_queries * K, self.shard.remote.pairs))
+            # every branch is a query of its own over the same candidates
+            ids = self._r_op["lookup"].idx.view(B, 1, K).expand(B, U, K)
+            self.shard.r_ids[:n_queries * K].view(B, U, K).copy_(ids)
+        elif first.dim() == 3 and first.shape[0] == B and first.shape[1] == 1:
+            n_queries, out_shape = B, (B, K)
+        else:
+            raise ValueError("%s: remotely scored rows take one candidate list per query" % name)
+        dim = first.shape[-1]
+        if dim != self.shard.remote.dim or n_queries > self.shard.remote.queries:
+            raise _lib.SmoreError("queries [%d, %d] do not fit the remote block (RemoteSpec queries=%d, dim=%d)"
+                                  % (n_queries, dim, self.shard.remote.queries, self.shard.remote.dim))
+        flat = lambda t: None if t is None else t.reshape(n_queries, dim).contiguous()
+        return _RemoteDistFunc.apply(self, name, self.dummy_tensor, flat(first), flat(second), n_queries, K, out_shape)
+
+    def remote_publish(self, name, first, second, n_queries, per_query):
+        sh, op = self.shard, self._r_op
+        op.update(name=name, dist_id=_lib.BOX_BOTH_ID if name == "box_both" else _lib.DIST_IDS[name],
+                  n_out=2 if name == "box_both" else 1, two=second is not None, nq=n_queries, K=per_query,
+                  dim=first.shape[1], stage="published")
+        sh.r_desc[0].fill_(n_queries)
+        sh.r_desc[1].fill_(per_query)
+        n = n_queries * op["dim"]
+        sh.r_queries[0][:n].copy_(first.reshape(-1))
+        if second is not None:
+            sh.r_queries[1][:n].copy_(second.reshape(-1))
+        for i in range(op["n_out"]):        # a pair no owner claims (an id outside the table) reads NaN
+            sh.r_results[i][:n_queries * per_query].fill_(float("nan"))
+
+    def remote_owner_forward(self):
+        sh, spec, op = self.shard, self.shard.remote, self._r_op
+        L, dev = _lib.lib(), self.shard.device
+        st = _stream_ptr(dev)
+        G, Q, P = sh.world, spec.queries, spec.pairs
+        ptr = lambda t: None if t is None else t.data_ptr()
+        second_all = self._r_queries[1] if op["two"] else None
+        out1 = self._r_out[1] if op["n_out"] == 2 else None
+        with torch.cuda.device(dev):
+            with _lib.timed("owner_select"):
+                _lib.check(L.smore_owner_select_pairs(sh.d_r_ids.data_ptr(), sh.d_r_desc.data_ptr(), G, Q, P, sh.base,
+                                                      max(sh.S, 1), self._r_cap, self._r_rows.data_ptr(),
+                                                      self._r_pos.data_ptr(), self._r_seg.data_ptr(),
+                                                      self._r_nsel.data_ptr(), st), "smore_owner_select_pairs")
+                _lib.check(L.smore_owner_gather_queries(sh.d_r_queries[0].data_ptr(),
+                                                        sh.d_r_queries[1].data_ptr() if op["two"] else None,
+                                                        sh.d_r_desc.data_ptr(), G, Q, P, op["dim"],
+                                                        self._r_queries[0].data_ptr(), ptr(second_all), st),
+                           "smore_owner_gather_queries")
+            with _lib.timed("owner_forward"):
+                _lib.check(L.smore_rows_forward_ragged(op["dist_id"], sh.table.data_ptr(), self._r_rows.data_ptr(),
+                                                       max(sh.S, 1), self._r_queries[0].data_ptr(), ptr(second_all),
+                                                       self._r_seg.data_ptr(), G * Q, op["dim"],
+                                                       self._r_out[0].data_ptr(), ptr(out1), st),
+                           "smore_rows_forward_ragged")
+            with _lib.timed("owner_scatter"):
+                _lib.check(L.smore_owner_scatter_results(self._r_out[0].data_ptr(), ptr(out1), self._r_pos.data_ptr(),
+                                                         self._r_seg.data_ptr(), sh.d_r_results[0].data_ptr(),
+                                                         sh.d_r_results[1].data_ptr() if out1 is not None else None,
+                                                         G, Q, st), "smore_owner_scatter_results")
+        op["stage"] = "scored"
+
+    def remote_collect_forward(self, out_shape):
+        op, n = self._r_op, self._r_op["nq"] * self._r_op["K"]
+        return tuple(self.shard.r_results[i][:n].view(out_shape).clone() for i in range(op["n_out"]))
+
+    def remote_publish_upstream(self, gouts):
+        op, n = self._r_op, self._r_op["nq"] * self._r_op["K"]
+        if op is None or op["stage"] != "scored":
+            raise _lib.SmoreError("backward of a remotely scored lookup without its forward in this step")
+        if self._fused_lr is None:
+            raise _lib.SmoreError("call announce_lr(lr) before the backward pass: the owners of remotely scored rows "
+                                  "update them inside it")
+        for i in range(op["n_out"]):
+            self.shard.r_upstream[i][:n].copy_(gouts[i].reshape(-1))
+
+    def remote_owner_backward(self):
+        sh, spec, op = self.shard, self.shard.remote, self._r_op
+        L, dev, lay = _lib.lib(), self.shard.device, self.shard.layout
+        st = _stream_ptr(dev)
+        G, Q, W, par = sh.world, spec.queries, sh.width, self.parity
+        ptr = lambda t: None if t is None else t.data_ptr()
+        second_all = self._r_queries[1] if op["two"] else None
+        up1 = self._r_up[1] if op["n_out"] == 2 else None
+        if self._owner_ws is None:
+            nbytes = L.smore_shard_owner_plan_workspace_bytes(max(sh.S, 1))
+            self._owner_ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        dev_step = getattr(self, "_step_dev", None) is not None
+        with torch.cuda.device(dev):
+            with _lib.timed("owner_gather_upstream"):
+                _lib.check(L.smore_owner_gather_upstream(sh.d_r_upstream[0].data_ptr(),
+                                                         sh.d_r_upstream[1].data_ptr() if up1 is not None else None,
+                                                         self._r_pos.data_ptr(), self._r_seg.data_ptr(), G, Q,
+                                                         self._r_up[0].data_ptr(), ptr(up1), st),
+                           "smore_owner_gather_upstream")
+            with _lib.timed("shard_collect"):
+                # the selected pairs' rows and the runs of the ranks' id lists (positives, anchors),
+                # de-duplicated together: one slot per distinct row of this shard touched in the step
+                _lib.check(L.smore_owner_plan(sh.d_uniq_ptrs[par].data_ptr(), sh.d_nuniq_ptrs[par].data_ptr(), G,
+                                              len(lay.plan_caps), self._caps, sh.base, max(sh.S, 1), self._r_total,
+                                              self._r_rows.data_ptr(), self._runs.data_ptr(), self._r_uniq.data_ptr(),
+                                              self._r_slot.data_ptr(), self._r_counts.data_ptr(),
+                                              self._r_nuniq.data_ptr(), sh.dirty.data_ptr(), self._owner_ws.data_ptr(),
+                                              self._owner_ws.numel(), self._r_nsel.data_ptr(), self._r_cap, st),
+                           "smore_owner_plan")
+                _lib.check(L.smore_zero_shared_rows(self._r_g.data_ptr(), self._r_counts.data_ptr(),
+                                                    self._r_nuniq.data_ptr(), self._r_total, W, st),
+                           "smore_zero_shared_rows")
+            _lib.note("n_unique_owner", self._r_nuniq[0])
+            with _lib.timed("owner_backward"):
+                _lib.check(L.smore_rows_backward_fused_adam_ragged(
+                    op["dist_id"], self._r_up[0].data_ptr(), ptr(up1), sh.table.data_ptr(), self._r_rows.data_ptr(),
+                    max(sh.S, 1), self._r_queries[0].data_ptr(), ptr(second_all), self._r_seg.data_ptr(), G * Q,
+                    self._r_slot.data_ptr(), self._r_counts.data_ptr(), self._r_g.data_ptr(), sh.r_partial[0].data_ptr(),
+                    sh.r_partial[1].data_ptr() if op["two"] else None, op["dim"], sh.m.data_ptr(), sh.v.data_ptr(),
+                    self._r_uniq.data_ptr(), self._fused_lr, 0.9, 0.999, eps, 1 if dev_step else int(self.step) + 1,
+                    self._step_scalars.data_ptr() if dev_step else None, st), "smore_rows_backward_fused_adam_ragged")
+        op["stage"] = "differentiated"
+
+    def remote_collect_backward(self):
+        sh, spec, op = self.shard, self.shard.remote, self._r_op
+        L, dev = _lib.lib(), self.shard.device
+        outs = []
+        with torch.cuda.device(dev), _lib.timed("owner_sum_query_grads"):
+            for i in range(2 if op["two"] else 1):
+                g = torch.empty(op["nq"], op["dim"], dtype=torch.float32, device=dev)
+                _lib.check(L.smore_owner_sum_query_grads(sh.d_r_partial[i].data_ptr(), sh.world, sh.rank, spec.queries,
+                                                         op["nq"], op["dim"], g.data_ptr(), _stream_ptr(dev)),
+                           "smore_owner_sum_query_grads")
+                outs.append(g)
+        return outs[0], outs[1] if op["two"] else None
+
+    def _apply_grad_remote(self, lr):
+        """The end of a step whose candidate rows were scored by their owners: the rows those pairs
+        alone touch are already updated; add the gradient rows that came back through the ranks'
+        lists (positives, anchors) and update what is left."""
+        sh, lay = self.shard, self.shard.layout
+        L, dev = _lib.lib(), self.shard.device
+        if float(lr) != self._fused_lr:
+            raise _lib.SmoreError("apply_grad(lr=%r) after announce_lr(%r)" % (lr, self._fused_lr))
+        self.barrier()              # every rank's gradient rows are complete
+        with torch.cuda.device(dev):
+            with _lib.timed("owner_add_list_rows"):
+                _lib.check(L.smore_owner_add_list_rows(sh.d_grad_ptrs[self.parity].data_ptr(), self._runs.data_ptr(),
+                                                       sh.world * len(lay.plan_caps), self._r_slot.data_ptr(),
+                                                       self._r_counts.data_ptr(), self._r_g.data_ptr(), sh.width,
+                                                       lay.span, _stream_ptr(dev)), "smore_owner_add_list_rows")
+        self._run_update("adam", sh.m, sh.v, self._r_uniq, self._r_g, self._r_nuniq, self._r_total, lr)
+        self.barrier()              # every shard is updated; this step's arena may be overwritten
+        if self._prefetched is not None:
+            torch.cuda.current_stream(dev).wait_event(self._prefetched[1])
+        self._drop_plans()
+
     # ---- the update ---------------------------------------------------------------------------------
     def _neutralise_unused_lookups(self):
         """A lookup that never received a gradient must not leave uninitialised rows in the arena:
@@ -655,6 +981,11 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
     def apply_grad(self, lr):
         self.step += 1
         self._neutralise_unused_lookups()
+        if self._r_op is not None:
+            if self._r_op["stage"] != "differentiated":
+                raise _lib.SmoreError("a remotely scored lookup must be used by one distance op and differentiated "
+                                      "before apply_grad (stage: %s)" % self._r_op["stage"])
+            return self._apply_grad_remote(lr)
         if self.exchange == "nccl":
             return self._apply_grad_all_to_all(lr)
         self.barrier()              # every rank's id lists and gradient rows are complete
@@ -720,24 +1051,31 @@ class ShardGroup(object):
     """Convenience constructors."""
 
     @staticmethod
-    def from_process_group(n_rows_total, width, plan_caps, squeeze=True, group=None, device=None, exchange="p2p"):
+    def from_process_group(n_rows_total, width, plan_caps, squeeze=True, group=None, device=None, exchange="p2p",
+                           remote=None):
         """exchange="p2p": blocks from the symmetric-memory allocator, mapped into every rank;
-        exchange="nccl": plain local blocks (use ShardedAdamOptimizer(shard, exchange="nccl"))."""
+        exchange="nccl": plain local blocks (use ShardedAdamOptimizer(shard, exchange="nccl")).
+        remote: a RemoteSpec to set up owner-side scoring (p2p only)."""
         import torch.distributed as dist
         rank, world = dist.get_rank(group), dist.get_world_size(group)
         device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
-        shard = ShardedTable(n_rows_total, width, rank, world, device, plan_caps, squeeze, symmetric=exchange == "p2p")
+        if remote is not None and exchange != "p2p":
+            raise ValueError("owner-side scoring reads the peers' memory: exchange must be 'p2p'")
+        shard = ShardedTable(n_rows_total, width, rank, world, device, plan_caps, squeeze, symmetric=exchange == "p2p",
+                             remote=remote)
         if exchange == "p2p":
             shard.connect_processes(group)
         return shard
 
     @staticmethod
-    def emulated(world, n_rows_total, width, plan_caps, squeeze=True, device="cuda:0"):
+    def emulated(world, n_rows_total, width, plan_caps, squeeze=True, device="cuda:0", remote=None):
         """`world` shards in this process on one GPU, wired to each other by raw pointers."""
-        shards = [ShardedTable(n_rows_total, width, r, world, device, plan_caps, squeeze) for r in range(world)]
+        shards = [ShardedTable(n_rows_total, width, r, world, device, plan_caps, squeeze, remote=remote)
+                  for r in range(world)]
         tables = [s._table_block.ptr for s in shards]
         arenas = [[s._arena_blocks[par].ptr for s in shards] for par in range(2)]
         dirty = [s._dirty_block.ptr for s in shards]
+        remotes = [s._remote_block.ptr for s in shards] if remote is not None else None
         for s in shards:
-            s.connect(tables, arenas, dirty)
+            s.connect(tables, arenas, dirty, remotes)
         return shards
