@@ -353,9 +353,10 @@ def sampling_loss(pos_logit, neg_logit, adv, world_size=1):
     return (-pos_score.mean() - neg_score.mean()) / 2 / world_size
 
 
-def first_lookup_group(pos, neg, queries):
-    """The id tensors a step looks up before it first needs rows: positives, negatives, first anchors."""
-    return [pos, neg.view(-1), queries[:, 0]]
+def first_lookup_group(pos, neg, queries, remote=False):
+    """The id tensors a step looks up before it first needs rows: positives, negatives, first anchors
+    (without the negatives when their owners score them: those rows are never fetched)."""
+    return [pos, queries[:, 0]] if remote else [pos, neg.view(-1), queries[:, 0]]
 
 
 def train_step(model, pos, neg, queries, structure, reduce_dense=None, upcoming=None):
@@ -369,7 +370,8 @@ def train_step(model, pos, neg, queries, structure, reduce_dense=None, upcoming=
         # rows touched by a single position of the step are updated inside the backward kernel
         model.embed_opt.announce_lr(model.cfg["lr"])
     if upcoming is not None:
-        model.embed_opt.prefetch(first_lookup_group(*upcoming[:3]), after=upcoming[3])
+        model.embed_opt.prefetch(first_lookup_group(*upcoming[:3], remote=getattr(model, "remote_scoring", False)),
+                                 after=upcoming[3])
     pos_logit, neg_logit = model(pos, neg, queries, structure)
     loss = sampling_loss(pos_logit, neg_logit, model.cfg["adv"], model.world)
     loss.backward()
@@ -580,6 +582,9 @@ def algorithmic_bytes(cfg, n_unique_mean, n_single_mean=0.0):
     if not cfg["shared"]:
         # with shared candidates the distance kernels are bound by fp32 ALU throughput, not by HBM
         out.update({"rows_forward": fwd, "rows_backward": bwd})
+        # owner-side scoring of a sharded table: with uniform candidates every owner receives about as
+        # many pairs as a rank sends, and runs the same two kernels over them
+        out.update({"owner_forward": fwd, "owner_backward": bwd})
     return out
 
 
@@ -625,7 +630,7 @@ class StepRunner(object):
     running steps (eager, replayed CUDA graphs, with host batches)."""
 
     def __init__(self, cfg, rows_per_gpu, device, world=1, rank=0, graphs=True, prefetch=True, lazy=True,
-                 fused_paths=True, pool=18, resettable=False, fused_update=True):
+                 fused_paths=True, pool=18, resettable=False, fused_update=True, remote=True):
         from smore_b200 import _lib, embedding, ext_ops
         import torch.distributed as dist
         self.cfg, self.device, self.world, self.rank = cfg, device, world, rank
@@ -635,6 +640,7 @@ class StepRunner(object):
         torch.manual_seed(1234)           # dense parameters start identical on every rank
         self.reduce_dense = None
         self.shard = None
+        self.remote = False
         self.prefetching = world > 1 and prefetch
         self.use_graphs = world == 1 and graphs
         self.chained_graphs = world > 1 and self.prefetching and graphs
@@ -644,8 +650,18 @@ class StepRunner(object):
             from smore_b200 import sharded
             B, K = cfg["B"], cfg["K"]
             width = cfg["dim"] * (2 if cfg["geo"] in ("rotate", "complex") else 1)
-            caps = ((K if cfg["shared"] else B * K) + 2 * B, B, B)
-            self.shard = sharded.ShardGroup.from_process_group(n_rows, width, caps, squeeze=cfg["squeeze"], device=device)
+            # owner-side scoring: the negatives' rows stay with their owners (one candidate list per
+            # query, Adam with the row-wise second moment, rows the ragged kernels take)
+            self.remote = bool(remote) and not cfg["shared"] and cfg["squeeze"] and cfg["dim"] > 256 and width * 4 <= 4096
+            spec = None
+            if self.remote:
+                # union structures score every branch as a query of its own: twice the pairs
+                spec = sharded.RemoteSpec(pairs=2 * B * K, queries=2 * B, dim=cfg["dim"])
+                caps = (2 * B, B, B)
+            else:
+                caps = ((K if cfg["shared"] else B * K) + 2 * B, B, B)
+            self.shard = sharded.ShardGroup.from_process_group(n_rows, width, caps, squeeze=cfg["squeeze"], device=device,
+                                                               remote=spec)
             self._init_range = (cfg["gamma"] + 2.0) / cfg["dim"]
             self.shard.init_uniform(-self._init_range, self._init_range, seed=1234)
             self.model = QueryModel(cfg, n_rows, device, ext_ops, embedding, lazy=True, shard=self.shard, world=world,
@@ -661,7 +677,9 @@ class StepRunner(object):
             self.model = QueryModel(cfg, n_rows, device, ext_ops, embedding, lazy=lazy, capturable=capturable,
                                     fused_paths=fused_paths)
         model = self.model
-        model.fused_update = bool(fused_update) and world == 1 and lazy
+        model.remote_scoring = world > 1 and self.remote
+        # (the owners of remotely scored rows update them inside the backward pass: the rate must be announced)
+        model.fused_update = (bool(fused_update) and world == 1 and lazy) or model.remote_scoring
         # (a copy of the initial state, table included at one GPU: only for runs that start over)
         self._initial = {k: v.detach().clone() for k, v in model.state_dict().items()} if resettable else None
         if capturable:
@@ -953,6 +971,10 @@ def kernel_table(cfg, workload, kernel_ms, notes, peak, peak_kind, fma_rate=None
     n_single_mean = sum(singles) / max(1, len(nus)) if singles else 0.0
     alg = algorithmic_bytes(cfg, n_unique_mean=n_unique_mean, n_single_mean=n_single_mean)
     flops = algorithmic_flops(cfg)
+    if "owner_backward" in kernel_ms:
+        # owner-side scoring: the fetch and the last update only see the few rows of the ordinary lookups
+        for k in ("fetch_rows", "sparse_update_rows", "shard_reduce_update"):
+            alg.pop(k, None)
     kernels = {}
     for name, ms_list in kernel_ms.items():
         if not ms_list:
@@ -1046,10 +1068,11 @@ def cublas_comparison(cfg, device):
 
 
 def parity_check(args, device, world, rank):
-    """Several GPUs, before anything is timed: the production mode of the sharded step (replayed CUDA
-    graphs, the next step's rows prefetched by bulk copies from peer memory, stale rows repaired from
-    the owners' bitmaps) and the plain mode (eager launches, every step's rows pulled after the
-    previous update) run the same five steps (2i, up structures) from identical state on a small
+    """Several GPUs, before anything is timed: the production mode of the sharded step (candidate rows
+    scored and updated by their owners, replayed CUDA graphs, the next step's remaining rows prefetched
+    by bulk copies from peer memory, stale rows repaired from the owners' bitmaps) and the plain mode
+    (every row pulled to the rank that looked it up after the previous update, row gradients pulled
+    back by the owners, eager launches) run the same five steps (2i, up structures) from identical state on a small
     table; every rank compares its shard of the table and of the Adam state and all dense parameters.
     The two modes run the same kernels on the same values; the only freedom is the order of atomic
     additions into gradient rows that several positions of a rank share, so the comparison allows
@@ -1058,8 +1081,9 @@ def parity_check(args, device, world, rank):
     cfg = dict(WORKLOADS["freebase_q2b"], B=128, K=256, structures=["2i", "up"])
     rows = 200000
     results = []
-    for graphs, prefetch in ((True, True), (False, False)):
-        r = StepRunner(cfg, rows, device, world, rank, graphs=graphs, prefetch=prefetch, pool=4, resettable=True)
+    for graphs, prefetch, remote in ((True, True, not args.no_remote), (False, False, False)):
+        r = StepRunner(cfg, rows, device, world, rank, graphs=graphs, prefetch=prefetch, pool=4, resettable=True,
+                       remote=remote)
         r.reset_state()
         if r.chained_graphs:
             r.run_resident(0, 4)           # start_chain runs batch -1 eagerly, then four replays
@@ -1088,6 +1112,8 @@ def parity_check(args, device, world, rank):
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     worst, identical = float(t[0]), bool(-float(t[1]) > 0.5)
     verdict = {"prefetch_vs_sync": "bit-identical" if identical else "within tolerance" if worst <= tol else "MISMATCH",
+               "modes": ("owner-side scoring, replayed graphs, prefetch" if not args.no_remote else
+                         "pulled rows, replayed graphs, prefetch") + " vs pulled rows, eager launches, no prefetch",
                "steps": 5, "max_rel_diff": worst, "tolerance": tol, "rows_per_gpu": rows, "structures": cfg["structures"],
                "compared": "per-rank table shard, Adam state, dense parameters"}
     if worst > tol:
@@ -1105,7 +1131,7 @@ def run_workload(name, cfg, args, device, world, rank, steps, warmup, repeats, p
     rows_per_gpu = args.rows or cfg["rows"] or (FREEBASE_ENTITIES + 7) // 8
     runner = StepRunner(cfg, rows_per_gpu, device, world, rank, graphs=not args.no_graphs, prefetch=not args.no_prefetch,
                         lazy=not args.no_lazy, fused_paths=not args.no_fused_paths, pool=args.pool,
-                        fused_update=not args.no_fused_update)
+                        fused_update=not args.no_fused_update, remote=not args.no_remote)
     import gc
     gc.collect()
     gc.freeze()        # keep the cycle collector from scanning the long-lived model objects inside a timed region
@@ -1162,7 +1188,11 @@ def run_workload(name, cfg, args, device, world, rank, steps, warmup, repeats, p
                        "shared_negatives": cfg["shared"], "dim": cfg["dim"], "table_rows_per_gpu": rows_per_gpu,
                        "table_rows_total": runner.n_rows, "structures": structures,
                        "parallelism": "1 GPU, table resident" if world == 1 else
-                                      "table and Adam state row-sharded over %d GPUs, rows and row gradients over NVLink" % world,
+                                      ("table and Adam state row-sharded over %d GPUs; candidate rows scored and updated by "
+                                       "their owners (queries, scores and their gradients over NVLink)" % world
+                                       if runner.remote else
+                                       "table and Adam state row-sharded over %d GPUs, rows and row gradients over NVLink"
+                                       % world),
                        "optimizer": "adam, row-wise v" if cfg["squeeze"] else "adam, full v",
                        "lazy_rows": not args.no_lazy,
                        "l2_policy": ("inputs larger than L2: every step touches ~%.1f GB of table rows" %
@@ -1426,6 +1456,9 @@ def main():
                     help="embed path queries hop by hop with torch ops, as the reference models do")
     ap.add_argument("--no-fused-update", action="store_true",
                     help="1 GPU: write every row gradient out and update all touched rows in the update kernel")
+    ap.add_argument("--no-remote", action="store_true",
+                    help="several GPUs: pull candidate rows to the rank that scores them (and their gradients back) "
+                         "instead of scoring them on their owners")
     ap.add_argument("--cpu-steps", type=int, default=6)
     ap.add_argument("--dump-kernel-times", action="store_true", help="add every timed launch's duration to the JSON")
     ap.add_argument("--eval", action="store_true",

@@ -887,6 +887,9 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
                                                     self._r_nuniq.data_ptr(), self._r_total, W, st),
                            "smore_zero_shared_rows")
             _lib.note("n_unique_owner", self._r_nuniq[0])
+            if _lib._timer is not None:     # (timing passes only: rows with one contribution in the step)
+                live = torch.arange(self._r_total, device=dev) < self._r_nuniq[0]
+                _lib.note("n_single", ((self._r_counts == 1) & live).sum())
             with _lib.timed("owner_backward"):
                 _lib.check(L.smore_rows_backward_fused_adam_ragged(
                     op["dist_id"], self._r_up[0].data_ptr(), ptr(up1), sh.table.data_ptr(), self._r_rows.data_ptr(),
