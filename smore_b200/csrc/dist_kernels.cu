@@ -474,6 +474,7 @@ __global__ void __launch_bounds__(kRowCtaThreads)
   extern __shared__ __align__(128) unsigned char bulk_smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const RowBlock rb = row_block(a);
+  if (rb.r_end <= rb.r_begin) return;    // (ragged form: a query without rows here)
   const int b = rb.b;
   const int dim4 = a.dim >> 2;
   const unsigned row_bytes = (unsigned)dim4 * Term::kMul * 16u;
@@ -808,6 +809,14 @@ __global__ void __launch_bounds__(kRowCtaThreads, 2)
   const unsigned row_bytes = (unsigned)dim4 * Term::kMul * 16u;
   const unsigned stage_bytes = 2u * row_bytes;          // [parameter row | first-moment row]
   const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (rb.r_end <= rb.r_begin) {
+    // (ragged form: a query without rows here) its query gradient is zero
+    for (int i = threadIdx.x; i < NB * dim4; i += kRowCtaThreads) {
+      reinterpret_cast<float4*>(ga.g_first + (size_t)b * NB * a.dim)[i] = z4;
+      if (Term::kNQ == 2) reinterpret_cast<float4*>(ga.g_second + (size_t)b * NB * a.dim)[i] = z4;
+    }
+    return;
+  }
   uint64_t* bars = reinterpret_cast<uint64_t*>(bulk_smem) + warp * stages;
   float4* sq = reinterpret_cast<float4*>(bulk_smem + bulk_ring_offset(stages));   // [kNQ][NB][dim4]
   unsigned char* ring_all = reinterpret_cast<unsigned char*>(sq + (size_t)Term::kNQ * NB * dim4);

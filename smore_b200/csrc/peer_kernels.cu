@@ -684,9 +684,18 @@ __global__ void __launch_bounds__(kSelectThreads)
     return;
   }
   const int64_t* ids = pair_id_ptrs[r] + (size_t)b * K;
-  // pass 1: how many of the query's candidates live here
+  // pass 1: how many of the query's candidates live here.  The ids come over NVLink: the first
+  // kSelectCache per thread stay in registers for the second pass.
+  constexpr int kSelectCache = 8;
+  int64_t cache[kSelectCache];
   int cnt = 0;
-  for (int k = tid; k < K; k += kSelectThreads) {
+#pragma unroll
+  for (int i = 0; i < kSelectCache; ++i) {
+    const int k = tid + i * kSelectThreads;
+    cache[i] = k < K ? ids[k] - base : -1;
+    cnt += (cache[i] >= 0 && cache[i] < shard_rows) ? 1 : 0;
+  }
+  for (int k = tid + kSelectCache * kSelectThreads; k < K; k += kSelectThreads) {
     const int64_t id = ids[k] - base;
     cnt += (id >= 0 && id < shard_rows) ? 1 : 0;
   }
@@ -709,13 +718,35 @@ __global__ void __launch_bounds__(kSelectThreads)
   int running = s_pos0;
   if (running < 0) return;
   // pass 2: the same scan, writing in increasing k
-  for (int k0 = 0; k0 < K; k0 += kSelectThreads) {
+#pragma unroll
+  for (int i = 0; i < kSelectCache; ++i) {
+    const int k0 = i * kSelectThreads;
+    if (k0 >= K) break;
+    const int64_t id = cache[i];
+    const bool mine = id >= 0 && id < shard_rows;
+    const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+    __syncthreads();   // s_warp of the previous chunk has been read
+    if (lane == 0) s_warp[warp] = __popc(ballot);
+    __syncthreads();
+    int before = 0, chunk = 0;
+    for (int w = 0; w < kSelectThreads / 32; ++w) {
+      before += w < warp ? s_warp[w] : 0;
+      chunk += s_warp[w];
+    }
+    if (mine) {
+      const int p = running + before + __popc(ballot & ((1u << lane) - 1u));
+      rows[p] = id;
+      positions[p] = b * K + k0 + tid;
+    }
+    running += chunk;
+  }
+  for (int k0 = kSelectCache * kSelectThreads; k0 < K; k0 += kSelectThreads) {
     const int k = k0 + tid;
     int64_t id = -1;
     if (k < K) id = ids[k] - base;
     const bool mine = id >= 0 && id < shard_rows;
     const unsigned ballot = __ballot_sync(0xffffffffu, mine);
-    __syncthreads();   // s_warp of the previous chunk has been read
+    __syncthreads();
     if (lane == 0) s_warp[warp] = __popc(ballot);
     __syncthreads();
     int before = 0, chunk = 0;

@@ -267,3 +267,51 @@ def test_two_processes_score_each_others_rows(tmp_path):
     for r in range(world):
         close(got[r]["g_c"].numpy(), want[r][2].cpu().numpy(), RTOL_ATOMIC, what="center gradient rank %d" % r)
         close(got[r]["g_o"].numpy(), want[r][3].cpu().numpy(), RTOL_ATOMIC, what="offset gradient rank %d" % r)
+
+
+def test_long_candidate_lists_and_queries_without_rows_on_an_owner():
+    """K beyond what the selection keeps in registers (2048 ids per query and pass), and a query whose
+    candidates all belong to one owner (the other owner's segment is empty)."""
+    from smore_b200 import _lib, ext_ops, sharded
+    world, n_total, B, K = 2, 2000, 3, 2309
+    torch.manual_seed(5)
+    full = (torch.rand(n_total, D) - 0.5) * 0.2
+    spec = sharded.RemoteSpec(pairs=B * K, queries=B, dim=D)
+    shards = sharded.ShardGroup.emulated(world, n_total, D, (2 * B, B, B), squeeze=True, remote=spec)
+    for s in shards:
+        s.table.zero_()
+        s.table[:s.local_rows] = full[s.base:s.base + s.local_rows].cuda()
+    opts = [sharded.ShardedAdamOptimizer(s, barrier=lambda: None) for s in shards]
+    _lib.async_status_clear()
+    negs, cs = [], []
+    for r in range(world):
+        neg = torch.randint(0, n_total, (B, K), generator=torch.Generator().manual_seed(r))
+        neg[1] = torch.randint(0, shards[0].S, (K,), generator=torch.Generator().manual_seed(9 + r))   # owner 0 only
+        c = ((torch.rand(B, 1, D, generator=torch.Generator().manual_seed(20 + r)) - 0.5) * 0.2).cuda()
+        opts[r].zero_grad()
+        opts[r].announce_lr(1e-3)
+        opts[r].forward(neg.view(-1).cuda(), "negative_entity")
+        negs.append(neg)
+        cs.append(c)
+    for r in range(world):
+        opts[r].remote_publish("l1", cs[r].view(B, D), None, B, K)
+    for o_ in opts:
+        o_.remote_owner_forward()
+    for r in range(world):
+        (d,) = opts[r].remote_collect_forward((B, K))
+        want = ext_ops.l1_dist(full[negs[r]].cuda(), cs[r])
+        close(d.cpu().numpy(), want.cpu().numpy(), RTOL, what="l1 rank %d" % r)
+    gs = [torch.randn(B, K, generator=torch.Generator().manual_seed(40 + r)).cuda() for r in range(world)]
+    for r in range(world):
+        opts[r].remote_publish_upstream([gs[r]])
+    for o_ in opts:
+        o_.remote_owner_backward()
+    for r in range(world):
+        g_c, _ = opts[r].remote_collect_backward()
+        c = cs[r].clone().requires_grad_()
+        (ext_ops.l1_dist(full[negs[r]].cuda(), c) * gs[r]).sum().backward()
+        close(g_c.cpu().numpy(), c.grad.view(B, D).cpu().numpy(), RTOL_ATOMIC, what="query gradient rank %d" % r)
+    for o_ in opts:
+        o_.apply_grad(1e-3)
+    torch.cuda.synchronize()
+    assert _lib.async_status() == 0

@@ -27,6 +27,26 @@ def test_arena_layout_is_aligned_and_disjoint():
         assert lay.grads_offset(p) % 16 == 0 and lay.ids_offset(p) % 8 == 0
 
 
+def test_remote_block_layout_is_aligned_and_disjoint():
+    """The peer-visible block of owner-side scoring: descriptor, candidate ids, queries, results,
+    upstream gradients, partial query gradients."""
+    spec = sharded.RemoteSpec(pairs=1024 * 1024 * 2, queries=2048, dim=400)
+    lay = sharded.RemoteLayout(spec, world=8)
+    P, QD = spec.pairs, spec.queries * spec.dim
+    regions = [(lay.off_desc, 32), (lay.off_ids, P * 8)]
+    regions += [(lay.off_queries + i * lay.stride_queries, QD * 4) for i in range(2)]
+    regions += [(lay.off_results + i * lay.stride_pairs, P * 4) for i in range(2)]
+    regions += [(lay.off_upstream + i * lay.stride_pairs, P * 4) for i in range(2)]
+    regions += [(lay.off_partial + i * lay.stride_partial, 8 * QD * 4) for i in range(2)]
+    regions.sort()
+    for (a, n), (b, _) in zip(regions, regions[1:]):
+        assert a + n <= b
+    assert regions[-1][0] + regions[-1][1] <= lay.nbytes
+    assert all(a % 16 == 0 for a, _ in regions)
+    with pytest.raises(ValueError):
+        sharded.RemoteSpec(pairs=10, queries=2, dim=30)          # rows are read 16 bytes at a time
+
+
 def test_ownership_partitions_the_id_space():
     for n, g in [(1003, 3), (86054151, 8), (5, 8), (64, 1)]:
         S = sharded.shard_rows(n, g)
