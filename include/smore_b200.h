@@ -579,13 +579,14 @@ SMORE_API int smore_shard_reduce_update_rows_dev(float* table, float* m, float* 
  *   ranks' queries (second_* may be NULL for one-operand distances).
  * smore_rows_forward_ragged / smore_rows_backward_fused_adam_ragged: the row-stream kernels with
  *   query q = segment q scoring rows[segments[2q] .. + segments[2q+1]); results (out0, out1) and
- *   upstream gradients (gout0, gout1) are indexed by compact position; g_first / g_second
+ *   upstream gradients (gout0, gout1) are indexed by compact position - or, with `positions`,
+ *   result / upstream gradient of compact position c lives at positions[c] in the arrays of the
+ *   rank that owns the segment (rank = q / segments_per_rank; out*_ptrs / gout*_ptrs: one base
+ *   pointer per rank, peer memory) and the local arrays may be NULL; g_first / g_second
  *   [n_segments, dim] receive each segment's query gradient.  Backward: slot / slot_count / g_rows
  *   / uniq / m / v and the Adam arguments as in smore_rows_backward_fused_adam, over the owner's
  *   distinct rows.  Rows of 1 KB to about 4 KB, dim a multiple of 4 above 256 (SMORE_ERR_BAD_SHAPE
  *   otherwise, nothing enqueued).  dist_id may be SMORE_DIST_BOX_BOTH.
- * smore_owner_scatter_results: dst*_ptrs[rank][positions[c]] = out*[c] for every selected pair.
- * smore_owner_gather_upstream: g*[c] = g*_ptrs[rank][positions[c]].
  * smore_owner_plan: smore_shard_owner_plan with the first *n_selected entries of `ids` already
  *   holding the selected pairs' local row ids (pair_capacity = room reserved for them; capacity
  *   >= pair_capacity + n_ranks * sum(plan_caps)): the lists' runs are appended behind them and the
@@ -605,20 +606,18 @@ SMORE_API int smore_owner_gather_queries(const float* const* first_ptrs, const f
                                void* stream);
 SMORE_API int smore_rows_forward_ragged(int dist_id, const float* table, const int64_t* rows, size_t n_table_rows,
                               const float* first, const float* second, const int32_t* segments,
-                              size_t n_segments, size_t dim, float* out0, float* out1, void* stream);
+                              size_t n_segments, size_t dim, float* out0, float* out1, const int32_t* positions,
+                              size_t segments_per_rank, float* const* out0_ptrs, float* const* out1_ptrs,
+                              void* stream);
 SMORE_API int smore_rows_backward_fused_adam_ragged(int dist_id, const float* gout0, const float* gout1, float* table,
                                           const int64_t* rows, size_t n_table_rows, const float* first,
                                           const float* second, const int32_t* segments, size_t n_segments,
                                           const int32_t* slot, const int32_t* slot_count, float* g_rows,
                                           float* g_first, float* g_second, size_t dim, float* m, float* v,
                                           int64_t* uniq, double lr, double beta1, double beta2, double eps,
-                                          int64_t step, const float* step_scalars, void* stream);
-SMORE_API int smore_owner_scatter_results(const float* out0, const float* out1, const int32_t* positions,
-                                const int32_t* segments, float* const* dst0_ptrs, float* const* dst1_ptrs,
-                                size_t n_ranks, size_t max_queries, void* stream);
-SMORE_API int smore_owner_gather_upstream(const float* const* g0_ptrs, const float* const* g1_ptrs,
-                                const int32_t* positions, const int32_t* segments, size_t n_ranks,
-                                size_t max_queries, float* g0, float* g1, void* stream);
+                                          int64_t step, const float* step_scalars, const int32_t* positions,
+                                          size_t segments_per_rank, const float* const* gout0_ptrs,
+                                          const float* const* gout1_ptrs, void* stream);
 SMORE_API int smore_owner_plan(const int64_t* const* uniq_ptrs, const int32_t* const* nuniq_ptrs, size_t n_ranks,
                      size_t n_plans, const int32_t* plan_caps, int64_t base, size_t shard_rows, size_t capacity,
                      int64_t* ids, int32_t* runs, int64_t* uniq, int32_t* slot, int32_t* counts,

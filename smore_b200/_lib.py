@@ -81,11 +81,10 @@ SIGNATURES = {
                                                   _p]),
     "smore_owner_select_pairs": (_int, [_p, _p, _sz, _sz, _sz, ctypes.c_int64, _sz, _sz, _p, _p, _p, _p, _p]),
     "smore_owner_gather_queries": (_int, [_p, _p, _p, _sz, _sz, _sz, _sz, _p, _p, _p]),
-    "smore_rows_forward_ragged": (_int, [_int, _p, _p, _sz, _p, _p, _p, _sz, _sz, _p, _p, _p]),
+    "smore_rows_forward_ragged": (_int, [_int, _p, _p, _sz, _p, _p, _p, _sz, _sz, _p, _p, _p, _sz, _p, _p, _p]),
     "smore_rows_backward_fused_adam_ragged": (_int, [_int, _p, _p, _p, _p, _sz, _p, _p, _p, _sz] + [_p] * 5 +
-                                              [_sz, _p, _p, _p, _dbl, _dbl, _dbl, _dbl, ctypes.c_int64, _p, _p]),
-    "smore_owner_scatter_results": (_int, [_p, _p, _p, _p, _p, _p, _sz, _sz, _p]),
-    "smore_owner_gather_upstream": (_int, [_p, _p, _p, _p, _sz, _sz, _p, _p, _p]),
+                                              [_sz, _p, _p, _p, _dbl, _dbl, _dbl, _dbl, ctypes.c_int64, _p, _p, _sz,
+                                               _p, _p, _p]),
     "smore_owner_plan": (_int, [_p, _p, _sz, _sz, ctypes.POINTER(ctypes.c_int32), ctypes.c_int64, _sz, _sz] +
                          [_p] * 8 + [_sz, _p, _sz, _p]),
     "smore_owner_add_list_rows": (_int, [_p, _p, _sz, _p, _p, _p, _sz, _sz, _p]),

@@ -193,6 +193,14 @@ struct RowArgs {
   // idx[seg[q].x ...]; results and upstream gradients are indexed by the same compact positions.
   // One CTA per query; K, rows_per_cta and chunks are not used.
   const int2* seg;
+  // Ragged form on the owner of a row shard: query q belongs to rank q / seg_per_rank, and the
+  // result / upstream gradient of compact position p lives at positions[p] in THAT rank's arrays
+  // (peer memory): out_ptrs / up_ptrs hold one base pointer per rank and output.  positions ==
+  // nullptr: results and upstream gradients are local arrays indexed by compact position.
+  const int32_t* positions;
+  int seg_per_rank;
+  float* const* out_ptrs[2];
+  const float* const* up_ptrs[2];
 };
 
 // The block of candidate rows a CTA of the row-stream kernels works on.
@@ -572,8 +580,14 @@ __global__ void __launch_bounds__(kRowCtaThreads)
     if (tl == 31 || t == n - 1) {
       if (lane <= tl) {
         const size_t o = pos0 + (t - tl) + lane;
-        dst0[o] = cur < 0 ? NAN : out0;
-        if (Term::kNOut == 2) dst1[o] = cur < 0 ? NAN : out1;
+        if (a.positions != nullptr) {          // straight into the requesting rank's result arrays
+          const int rank = b / a.seg_per_rank, at = a.positions[o];
+          a.out_ptrs[0][rank][at] = cur < 0 ? NAN : out0;
+          if (Term::kNOut == 2) a.out_ptrs[1][rank][at] = cur < 0 ? NAN : out1;
+        } else {
+          dst0[o] = cur < 0 ? NAN : out0;
+          if (Term::kNOut == 2) dst1[o] = cur < 0 ? NAN : out1;
+        }
       }
       cur = nxt;
     }
@@ -882,7 +896,13 @@ __global__ void __launch_bounds__(kRowCtaThreads, 2)
         if (m.single) m.v = ua.v[m.src];
 #pragma unroll
         for (int u = 0; u < NB; ++u) {
-          // (the ragged form has one branch: upstream gradients sit at the rows' compact positions)
+          if (a.positions != nullptr) {        // from the requesting rank's arrays (ragged form: one branch)
+            const int rank = b / a.seg_per_rank, at = a.positions[pos];
+            m.g[0] = a.up_ptrs[0][rank][at];
+            if (Term::kNOut == 2) m.g[Term::kNOut - 1] = a.up_ptrs[1][rank][at];
+            continue;
+          }
+          // (ragged form with local arrays: upstream gradients sit at the rows' compact positions)
           const size_t o = a.seg != nullptr ? pos : ((size_t)b * NB + u) * a.K + (w_begin + t);
           m.g[u * Term::kNOut] = ga.gout0[o];
           if (Term::kNOut == 2) m.g[u * Term::kNOut + Term::kNOut - 1] = ga.gout1[o];
@@ -1513,10 +1533,26 @@ static int ragged_nch(size_t dim, size_t mul) {
   return dim4 <= 128 ? 4 : 8;
 }
 
+struct RaggedPeers {        // where results go / upstream gradients come from (see RowArgs)
+  const int32_t* positions;
+  size_t seg_per_rank;
+  float* const* out0;
+  float* const* out1;
+  const float* const* up0;
+  const float* const* up1;
+};
+
+static void set_peers(RowArgs& a, const RaggedPeers& pr) {
+  a.positions = pr.positions;
+  a.seg_per_rank = (int)std::max<size_t>(pr.seg_per_rank, 1);
+  a.out_ptrs[0] = pr.out0; a.out_ptrs[1] = pr.out1;
+  a.up_ptrs[0] = pr.up0; a.up_ptrs[1] = pr.up1;
+}
+
 template <class Term>
 static int launch_forward_ragged(size_t n_seg, size_t dim, size_t n_rows, const float* table, const int64_t* rows,
                                  const float* first, const float* second, const int2* seg, float* out0, float* out1,
-                                 cudaStream_t st) {
+                                 const RaggedPeers& pr, cudaStream_t st) {
   if (Term::kNQ == 1) second = first;
   const int nch = ragged_nch(dim, Term::kMul);
   if (!nch || !aligned16(table) || !aligned16(first) || !aligned16(second)) return 0;
@@ -1525,6 +1561,7 @@ static int launch_forward_ragged(size_t n_seg, size_t dim, size_t n_rows, const 
   const size_t smem = std::max<size_t>(bulk_ring_offset(stages) + (size_t)kRowCtaWarps * stages * row_bytes, 46 * 1024);
   if (smem > 110 * 1024) return 0;
   RowArgs a{table, rows, first, second, 0, (int)dim, 0, 1, 0, (long long)n_rows, seg};
+  set_peers(a, pr);
   auto kern = nch == 4 ? row_forward_bulk_kernel<Term, 4> : row_forward_bulk_kernel<Term, 8>;
   if (int rc = allow_large_smem(kern, 110 * 1024)) return rc;
   kern<<<(unsigned)n_seg, kRowCtaThreads, smem, st>>>(a, out0, out1, stages);
@@ -1537,7 +1574,7 @@ static int launch_backward_adam_ragged(size_t n_seg, size_t dim, size_t n_rows, 
                                        float* table, const int64_t* rows, const float* first, const float* second,
                                        const int2* seg, const int32_t* slot, const int32_t* slot_count, float* g_rows,
                                        float* g_first, float* g_second, const UpdateArgs& ua, int64_t* uniq,
-                                       cudaStream_t st) {
+                                       const RaggedPeers& pr, cudaStream_t st) {
   if (Term::kNQ == 1) {
     second = first;
     g_second = g_first;
@@ -1548,6 +1585,7 @@ static int launch_backward_adam_ragged(size_t n_seg, size_t dim, size_t n_rows, 
     return 0;
   const Shape s{n_seg, 4, n_seg, 4, n_seg, 1, dim, n_rows};
   RowArgs a{table, rows, first, second, 0, (int)dim, 0, 1, 0, (long long)n_rows, seg};
+  set_peers(a, pr);
   RowGradArgs ga{gout0, gout1, nullptr, slot, slot_count, g_rows, g_first, g_second, 0};
   return launch_backward_adam<Term, 1>(s, a, ga, ua, uniq, nch, st);
 }
@@ -1982,24 +2020,29 @@ int smore_rows_backward_fused_adam(int dist_id, const float* gout0, const float*
 
 int smore_rows_forward_ragged(int dist_id, const float* table, const int64_t* rows, size_t n_table_rows,
                               const float* first, const float* second, const int32_t* segments, size_t n_segments,
-                              size_t dim, float* out0, float* out1, void* stream) {
+                              size_t dim, float* out0, float* out1, const int32_t* positions,
+                              size_t segments_per_rank, float* const* out0_ptrs, float* const* out1_ptrs,
+                              void* stream) {
   const bool both = dist_id == SMORE_DIST_BOX_BOTH;
   if (!both && (dist_id < 0 || dist_id >= SMORE_DIST_COUNT))
     return fail(SMORE_ERR_BAD_DIST, "unknown distance id %d", dist_id);
-  if (!table || !rows || !first || !segments || !out0 || (both && !out1) || ((both || needs_second(dist_id)) && !second))
+  if (!table || !rows || !first || !segments || ((both || needs_second(dist_id)) && !second))
     return fail(SMORE_ERR_NULL, "rows_forward_ragged: required pointer is NULL");
+  if (positions ? (!out0_ptrs || (both && !out1_ptrs) || segments_per_rank == 0) : (!out0 || (both && !out1)))
+    return fail(SMORE_ERR_NULL, "rows_forward_ragged: pass local result arrays, or positions with per-rank pointers");
+  const RaggedPeers pr{positions, segments_per_rank, out0_ptrs, both ? out1_ptrs : out0_ptrs, nullptr, nullptr};
   if (n_segments == 0) return SMORE_OK;
   if (n_segments > (size_t)INT_MAX || dim == 0) return fail(SMORE_ERR_BAD_SHAPE, "rows_forward_ragged: bad sizes");
   cudaStream_t st = (cudaStream_t)stream;
   const int2* seg = reinterpret_cast<const int2*>(segments);
   int rc = 0;
   if (both) {
-    rc = launch_forward_ragged<TermBoxBoth>(n_segments, dim, n_table_rows, table, rows, first, second, seg, out0, out1, st);
+    rc = launch_forward_ragged<TermBoxBoth>(n_segments, dim, n_table_rows, table, rows, first, second, seg, out0, out1, pr, st);
   } else {
     switch (dist_id) {
 #define RAGGED_CASE(ID, TERM)                                                                                          \
   case ID:                                                                                                             \
-    rc = launch_forward_ragged<TERM>(n_segments, dim, n_table_rows, table, rows, first, second, seg, out0, out0, st); \
+    rc = launch_forward_ragged<TERM>(n_segments, dim, n_table_rows, table, rows, first, second, seg, out0, out0, pr, st); \
     break;
       RAGGED_CASE(SMORE_DIST_BOX_OUT, TermBoxOut)
       RAGGED_CASE(SMORE_DIST_BOX_IN, TermBoxIn)
@@ -2024,14 +2067,20 @@ int smore_rows_backward_fused_adam_ragged(int dist_id, const float* gout0, const
                                           const int32_t* slot, const int32_t* slot_count, float* g_rows, float* g_first,
                                           float* g_second, size_t dim, float* m, float* v, int64_t* uniq, double lr,
                                           double beta1, double beta2, double eps, int64_t step,
-                                          const float* step_scalars, void* stream) {
+                                          const float* step_scalars, const int32_t* positions,
+                                          size_t segments_per_rank, const float* const* gout0_ptrs,
+                                          const float* const* gout1_ptrs, void* stream) {
   const bool both = dist_id == SMORE_DIST_BOX_BOTH;
   if (!both && (dist_id < 0 || dist_id >= SMORE_DIST_COUNT))
     return fail(SMORE_ERR_BAD_DIST, "unknown distance id %d", dist_id);
   const bool two = both || needs_second(dist_id);
-  if (!gout0 || (both && !gout1) || !table || !rows || !first || !segments || !slot || !slot_count || !g_rows ||
-      !g_first || !m || !v || !uniq || (two && (!second || !g_second)))
+  if (!table || !rows || !first || !segments || !slot || !slot_count || !g_rows || !g_first || !m || !v || !uniq ||
+      (two && (!second || !g_second)))
     return fail(SMORE_ERR_NULL, "rows_backward_fused_adam_ragged: required pointer is NULL");
+  if (positions ? (!gout0_ptrs || (both && !gout1_ptrs) || segments_per_rank == 0) : (!gout0 || (both && !gout1)))
+    return fail(SMORE_ERR_NULL, "rows_backward_fused_adam_ragged: pass local upstream gradients, or positions with "
+                                "per-rank pointers");
+  const RaggedPeers pr{positions, segments_per_rank, nullptr, nullptr, gout0_ptrs, both ? gout1_ptrs : gout0_ptrs};
   if (!step_scalars && step < 1) return fail(SMORE_ERR_BAD_SHAPE, "adam step must be >= 1");
   if (n_segments == 0) return SMORE_OK;
   if (n_segments > (size_t)INT_MAX || dim == 0) return fail(SMORE_ERR_BAD_SHAPE, "rows_backward_fused_adam_ragged: bad sizes");
@@ -2046,13 +2095,13 @@ int smore_rows_backward_fused_adam_ragged(int dist_id, const float* gout0, const
   int rc = 0;
   if (both) {
     rc = launch_backward_adam_ragged<TermBoxBoth>(n_segments, dim, n_table_rows, gout0, gout1, table, rows, first, second,
-                                                  seg, slot, slot_count, g_rows, g_first, g_second, ua, uniq, st);
+                                                  seg, slot, slot_count, g_rows, g_first, g_second, ua, uniq, pr, st);
   } else {
     switch (dist_id) {
 #define RAGGED_CASE(ID, TERM)                                                                                      \
   case ID:                                                                                                         \
     rc = launch_backward_adam_ragged<TERM>(n_segments, dim, n_table_rows, gout0, gout0, table, rows, first, second, \
-                                           seg, slot, slot_count, g_rows, g_first, g_second, ua, uniq, st);        \
+                                           seg, slot, slot_count, g_rows, g_first, g_second, ua, uniq, pr, st);    \
     break;
       RAGGED_CASE(SMORE_DIST_BOX_OUT, TermBoxOut)
       RAGGED_CASE(SMORE_DIST_BOX_IN, TermBoxIn)

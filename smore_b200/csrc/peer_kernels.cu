@@ -649,9 +649,9 @@ __global__ void __launch_bounds__(kRingWarps * 32, 2)
 //      the compact arrays rows[] (local row ids) and positions[] (query * K + k on the requester),
 //      in increasing k (owner_select_pairs_kernel);
 //   2. copies all queries into one local array indexed by rank * max_queries + query;
-//   3. runs the ragged row-stream kernels over the segments (dist_kernels.cu);
-//   4. sends results back / fetches upstream gradients by position (owner_permute_kernel), and
-//      leaves its partial query gradients for the requesters to sum (owner_sum_query_grads_kernel).
+//   3. runs the ragged row-stream kernels over the segments (dist_kernels.cu), which write each
+//      result to / read each upstream gradient from its position in the requester's arrays;
+//   4. leaves its partial query gradients for the requesters to sum (owner_sum_query_grads_kernel).
 // ----------------------------------------------------------------------------------------
 
 constexpr int kSelectThreads = 256;
@@ -776,29 +776,6 @@ __global__ void __launch_bounds__(256)
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     first_all[base + i] = f[i];
     if (s != nullptr) second_all[base + i] = s[i];
-  }
-}
-
-// kScatter: peer[rank][position] = local[compact]; otherwise local[compact] = peer[rank][position]
-template <bool kScatter>
-__global__ void __launch_bounds__(128)
-    owner_permute_kernel(float* const* __restrict__ peer0, float* const* __restrict__ peer1,
-                         const int32_t* __restrict__ positions, const int2* __restrict__ segments, int max_queries,
-                         float* __restrict__ local0, float* __restrict__ local1) {
-  const int r = blockIdx.y, b = blockIdx.x;
-  const int2 seg = segments[r * max_queries + b];
-  if (seg.y == 0) return;
-  float* p0 = peer0[r];
-  float* p1 = local1 != nullptr ? peer1[r] : nullptr;
-  for (int j = threadIdx.x; j < seg.y; j += blockDim.x) {
-    const int c = seg.x + j, pos = positions[c];
-    if (kScatter) {
-      p0[pos] = local0[c];
-      if (p1 != nullptr) p1[pos] = local1[c];
-    } else {
-      local0[c] = p0[pos];
-      if (p1 != nullptr) local1[c] = p1[pos];
-    }
   }
 }
 
@@ -1078,33 +1055,6 @@ int smore_owner_gather_queries(const float* const* first_ptrs, const float* cons
       first_ptrs, second_ptrs, desc_ptrs, (int)max_queries, (long long)pairs_capacity, (int)(dim >> 2),
       reinterpret_cast<float4*>(first_all), reinterpret_cast<float4*>(second_all));
   return check_launch("owner_gather_queries_kernel");
-}
-
-int smore_owner_scatter_results(const float* out0, const float* out1, const int32_t* positions, const int32_t* segments,
-                                float* const* dst0_ptrs, float* const* dst1_ptrs, size_t n_ranks, size_t max_queries,
-                                void* stream) {
-  if (!out0 || !positions || !segments || !dst0_ptrs || (out1 && !dst1_ptrs))
-    return fail(SMORE_ERR_NULL, "owner_scatter_results: NULL pointer");
-  if (int rc = check_owner_sizes("owner_scatter_results", n_ranks, max_queries)) return rc;
-  dim3 grid((unsigned)max_queries, (unsigned)n_ranks);
-  owner_permute_kernel<true><<<grid, 128, 0, (cudaStream_t)stream>>>(
-      dst0_ptrs, dst1_ptrs, positions, reinterpret_cast<const int2*>(segments), (int)max_queries,
-      const_cast<float*>(out0), const_cast<float*>(out1));
-  return check_launch("owner_permute_kernel");
-}
-
-int smore_owner_gather_upstream(const float* const* g0_ptrs, const float* const* g1_ptrs, const int32_t* positions,
-                                const int32_t* segments, size_t n_ranks, size_t max_queries, float* g0, float* g1,
-                                void* stream) {
-  if (!g0_ptrs || !positions || !segments || !g0 || (g1 && !g1_ptrs))
-    return fail(SMORE_ERR_NULL, "owner_gather_upstream: NULL pointer");
-  if (int rc = check_owner_sizes("owner_gather_upstream", n_ranks, max_queries)) return rc;
-  dim3 grid((unsigned)max_queries, (unsigned)n_ranks);
-  owner_permute_kernel<false><<<grid, 128, 0, (cudaStream_t)stream>>>(
-      const_cast<float* const*>(reinterpret_cast<const float* const*>(g0_ptrs)),
-      const_cast<float* const*>(reinterpret_cast<const float* const*>(g1_ptrs)), positions,
-      reinterpret_cast<const int2*>(segments), (int)max_queries, g0, g1);
-  return check_launch("owner_permute_kernel");
 }
 
 int smore_owner_add_list_rows(const float* const* grad_ptrs, const int32_t* runs, size_t n_lists, const int32_t* slot,

@@ -600,7 +600,6 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         self._r_rows = torch.zeros(n_tot, dtype=torch.int64, device=dev)
         self._r_pos, self._r_seg, self._r_nsel = i32(cap), i32(G * spec.queries * 2), i32(2)
         self._r_queries = [f32(QD), f32(QD)]
-        self._r_out, self._r_up = [f32(cap), f32(cap)], [f32(cap), f32(cap)]
         self._r_uniq = torch.zeros(n_tot, dtype=torch.int64, device=dev)
         self._r_slot, self._r_counts, self._r_nuniq = i32(n_tot), i32(n_tot), i32(2)
         self._r_g = f32(n_tot, W)
@@ -815,7 +814,6 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         G, Q, P = sh.world, spec.queries, spec.pairs
         ptr = lambda t: None if t is None else t.data_ptr()
         second_all = self._r_queries[1] if op["two"] else None
-        out1 = self._r_out[1] if op["n_out"] == 2 else None
         with torch.cuda.device(dev):
             with _lib.timed("owner_select"):
                 _lib.check(L.smore_owner_select_pairs(sh.d_r_ids.data_ptr(), sh.d_r_desc.data_ptr(), G, Q, P, sh.base,
@@ -828,16 +826,13 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
                                                         self._r_queries[0].data_ptr(), ptr(second_all), st),
                            "smore_owner_gather_queries")
             with _lib.timed("owner_forward"):
+                # every result goes straight to its position in the requesting rank's result arrays
                 _lib.check(L.smore_rows_forward_ragged(op["dist_id"], sh.table.data_ptr(), self._r_rows.data_ptr(),
                                                        max(sh.S, 1), self._r_queries[0].data_ptr(), ptr(second_all),
-                                                       self._r_seg.data_ptr(), G * Q, op["dim"],
-                                                       self._r_out[0].data_ptr(), ptr(out1), st),
+                                                       self._r_seg.data_ptr(), G * Q, op["dim"], None, None,
+                                                       self._r_pos.data_ptr(), Q, sh.d_r_results[0].data_ptr(),
+                                                       sh.d_r_results[1].data_ptr() if op["n_out"] == 2 else None, st),
                            "smore_rows_forward_ragged")
-            with _lib.timed("owner_scatter"):
-                _lib.check(L.smore_owner_scatter_results(self._r_out[0].data_ptr(), ptr(out1), self._r_pos.data_ptr(),
-                                                         self._r_seg.data_ptr(), sh.d_r_results[0].data_ptr(),
-                                                         sh.d_r_results[1].data_ptr() if out1 is not None else None,
-                                                         G, Q, st), "smore_owner_scatter_results")
         op["stage"] = "scored"
 
     def remote_collect_forward(self, out_shape):
@@ -861,18 +856,11 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         G, Q, W, par = sh.world, spec.queries, sh.width, self.parity
         ptr = lambda t: None if t is None else t.data_ptr()
         second_all = self._r_queries[1] if op["two"] else None
-        up1 = self._r_up[1] if op["n_out"] == 2 else None
         if self._owner_ws is None:
             nbytes = L.smore_shard_owner_plan_workspace_bytes(max(sh.S, 1))
             self._owner_ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         dev_step = getattr(self, "_step_dev", None) is not None
         with torch.cuda.device(dev):
-            with _lib.timed("owner_gather_upstream"):
-                _lib.check(L.smore_owner_gather_upstream(sh.d_r_upstream[0].data_ptr(),
-                                                         sh.d_r_upstream[1].data_ptr() if up1 is not None else None,
-                                                         self._r_pos.data_ptr(), self._r_seg.data_ptr(), G, Q,
-                                                         self._r_up[0].data_ptr(), ptr(up1), st),
-                           "smore_owner_gather_upstream")
             with _lib.timed("shard_collect"):
                 # the selected pairs' rows and the runs of the ranks' id lists (positives, anchors),
                 # de-duplicated together: one slot per distinct row of this shard touched in the step
@@ -891,13 +879,16 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
                 live = torch.arange(self._r_total, device=dev) < self._r_nuniq[0]
                 _lib.note("n_single", ((self._r_counts == 1) & live).sum())
             with _lib.timed("owner_backward"):
+                # (each pair's upstream gradient is read from its position in the requesting rank's arrays)
                 _lib.check(L.smore_rows_backward_fused_adam_ragged(
-                    op["dist_id"], self._r_up[0].data_ptr(), ptr(up1), sh.table.data_ptr(), self._r_rows.data_ptr(),
+                    op["dist_id"], None, None, sh.table.data_ptr(), self._r_rows.data_ptr(),
                     max(sh.S, 1), self._r_queries[0].data_ptr(), ptr(second_all), self._r_seg.data_ptr(), G * Q,
                     self._r_slot.data_ptr(), self._r_counts.data_ptr(), self._r_g.data_ptr(), sh.r_partial[0].data_ptr(),
                     sh.r_partial[1].data_ptr() if op["two"] else None, op["dim"], sh.m.data_ptr(), sh.v.data_ptr(),
                     self._r_uniq.data_ptr(), self._fused_lr, 0.9, 0.999, eps, 1 if dev_step else int(self.step) + 1,
-                    self._step_scalars.data_ptr() if dev_step else None, st), "smore_rows_backward_fused_adam_ragged")
+                    self._step_scalars.data_ptr() if dev_step else None, self._r_pos.data_ptr(), Q,
+                    sh.d_r_upstream[0].data_ptr(), sh.d_r_upstream[1].data_ptr() if op["n_out"] == 2 else None, st),
+                    "smore_rows_backward_fused_adam_ragged")
         op["stage"] = "differentiated"
 
     def remote_collect_backward(self):
