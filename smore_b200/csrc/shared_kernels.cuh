@@ -170,6 +170,7 @@ constexpr int kBwdMaxThreads = 512;
 template <class Term, int KT>
 __global__ void __launch_bounds__(kBwdMaxThreads)
     shared_backward_tile_kernel(SharedArgs a, SharedGradArgs ga, int seg_b) {
+  static_assert((KT * Term::kNOut) % 4 == 0, "a query's upstream gradients are read 16 bytes at a time");
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   constexpr int NO = Term::kNOut, M = Term::kMul;
@@ -241,8 +242,16 @@ __global__ void __launch_bounds__(kBwdMaxThreads)
         const int bb = bb0 + u;
         if (bb >= nb) break;
         float gq0 = 0.f, gq1 = 0.f;
+        // the query's KT x NO upstream gradients: a few 16-byte broadcast loads instead of one load per value
+        float gl[KT * NO];
+        const float4* g4 = reinterpret_cast<const float4*>(&gs[bb][0][0]);
 #pragma unroll
-        for (int j = 0; j < KT; ++j) Term::bwd(&gs[bb][j][0], e0[j], e1[j], q0c[u], q1c[u], ge0[j], ge1[j], gq0, gq1);
+        for (int i = 0; i < KT * NO / 4; ++i) {
+          const float4 t = g4[i];
+          gl[4 * i + 0] = t.x; gl[4 * i + 1] = t.y; gl[4 * i + 2] = t.z; gl[4 * i + 3] = t.w;
+        }
+#pragma unroll
+        for (int j = 0; j < KT; ++j) Term::bwd(&gl[j * NO], e0[j], e1[j], q0c[u], q1c[u], ge0[j], ge1[j], gq0, gq1);
         if (d_ok) {
           const size_t at = (size_t)(bs + bb) * a.dim + d;
           atomicAdd(ga.g_first + at, gq0);
