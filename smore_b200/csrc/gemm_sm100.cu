@@ -9,13 +9,16 @@
 //     g_cand[K, W]  = g[B, K]^T   . query[B, W]
 // W is the row length (dim for DistMult; 2*dim for ComplEx, with the query laid out [re | im] like
 // the entity rows).  The kernels are CUTLASS 3.x sm100 templates instantiated here: TMA loads
-// (cluster 1x1x1: no multicast), tcgen05.mma with TMEM accumulators, fp32 in / fp32 out, in two
+// (never multicast), tcgen05.mma with TMEM accumulators, two SMs per 256 x 128 tile, fp32 in / fp32
+// out, in two
 // precisions: TF32 (10-bit mantissa products) and "fast fp32" (each fp32 operand split into three
 // bf16 terms, nine bf16 MMAs per product, fp32-level accuracy).
 //
 // Built only when a CUTLASS header tree is found (see build.py); without it the entry points
 // report SMORE_ERR_BAD_SHAPE and callers use the SIMT tile kernels.
 #include <cuda_runtime.h>
+
+#include <algorithm>
 
 #include "common.cuh"
 
@@ -31,29 +34,52 @@
 namespace smore {
 using namespace cute;
 
-template <class LayoutA, class LayoutB, class Schedule>
+// Tile variants.  TwoSm pairs two SMs on one 256 x 128 tile (tcgen05 cta_group::2, cluster 2 x 1): each
+// CTA of the pair loads its own halves of the operand tiles, so with this static cluster shape the
+// builder picks the plain two-SM TMA loads - no operand is multicast.
+struct OneSm {
+  using Tile = Shape<_128, _128, _32>;
+  using Cluster = Shape<_1, _1, _1>;
+  using Tf32 = cutlass::gemm::KernelTmaWarpSpecialized1SmSm100;
+  using Fp32x9 = cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32Sm100;
+  using Epilogue = cutlass::epilogue::TmaWarpSpecialized1Sm;
+};
+struct TwoSm {
+  using Tile = Shape<_256, _128, _32>;
+  using Cluster = Shape<_2, _1, _1>;
+  using Tf32 = cutlass::gemm::KernelTmaWarpSpecialized2SmSm100;
+  using Fp32x9 = cutlass::gemm::KernelTmaWarpSpecialized2SmFastFP32Sm100;
+  using Epilogue = cutlass::epilogue::TmaWarpSpecialized2Sm;
+};
+
+struct TwoSmWide : TwoSm {      // 256 x 256 tiles: half the operand traffic per flop, for outputs with many columns
+  using Tile = Shape<_256, _256, _32>;
+};
+
+template <class LayoutA, class LayoutB, class Variant, bool kFast, class Scheduler>
 struct DotGemm {
   using Acc = float;
   using LayoutC = cutlass::layout::RowMajor;
-  using Tile = Shape<_128, _128, _32>;
-  using Cluster = Shape<_1, _1, _1>;
+  using Tile = typename Variant::Tile;
+  using Cluster = typename Variant::Cluster;
+  using Schedule = cute::conditional_t<kFast, typename Variant::Fp32x9, typename Variant::Tf32>;
   using Epi = typename cutlass::epilogue::collective::CollectiveBuilder<
       cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, Tile, Cluster,
       cutlass::epilogue::collective::EpilogueTileAuto, Acc, Acc, float, LayoutC, 4, float, LayoutC, 4,
-      cutlass::epilogue::collective::EpilogueScheduleAuto>::CollectiveOp;
+      typename Variant::Epilogue>::CollectiveOp;
   using Main = typename cutlass::gemm::collective::CollectiveBuilder<
       cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, float, LayoutA, 4, float, LayoutB, 4, Acc, Tile, Cluster,
       cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename Epi::SharedStorage))>,
       Schedule>::CollectiveOp;
-  using Kernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, Main, Epi, void>;
+  using Kernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, Main, Epi, Scheduler>;
   using Gemm = cutlass::gemm::device::GemmUniversalAdapter<Kernel>;
 };
 
 // D[M, N] = A . B with A(m, k), B(k, n) in the given layouts ("column-major B" = an [N, K] row-major array)
-template <class LayoutA, class LayoutB, class Schedule>
+template <class LayoutA, class LayoutB, class Variant, bool kFast, class Scheduler>
 static int run_gemm(const float* A, const float* B, float* D, int M, int N, int K, void* ws, size_t ws_bytes,
                     cudaStream_t st, size_t* need) {
-  using Gemm = typename DotGemm<LayoutA, LayoutB, Schedule>::Gemm;
+  using Gemm = typename DotGemm<LayoutA, LayoutB, Variant, kFast, Scheduler>::Gemm;
   using StrideA = typename Gemm::GemmKernel::StrideA;
   using StrideB = typename Gemm::GemmKernel::StrideB;
   using StrideC = typename Gemm::GemmKernel::StrideC;
@@ -81,15 +107,34 @@ static int run_gemm(const float* A, const float* B, float* D, int M, int N, int 
 
 using RowM = cutlass::layout::RowMajor;
 using ColM = cutlass::layout::ColumnMajor;
-using Tf32 = cutlass::gemm::collective::KernelScheduleAuto;
-using Fp32x9 = cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32Sm100;
 
+// Output tiles are handed to the SMs by the persistent scheduler; products whose tile count is a
+// small non-multiple of the SM count (the query gradient: 128 two-SM tiles on 74 SM pairs) use the
+// stream-K scheduler, which splits the contraction of the last partial wave over the idle SMs.
 template <class LayoutA, class LayoutB>
 static int run_precision(int precision, const float* A, const float* B, float* D, int M, int N, int K, void* ws,
                          size_t ws_bytes, cudaStream_t st, size_t* need) {
-  if (precision == SMORE_DOT_TF32) return run_gemm<LayoutA, LayoutB, Tf32>(A, B, D, M, N, K, ws, ws_bytes, st, need);
-  if (precision == SMORE_DOT_FP32) return run_gemm<LayoutA, LayoutB, Fp32x9>(A, B, D, M, N, K, ws, ws_bytes, st, need);
-  return fail(SMORE_ERR_BAD_DIST, "unknown dot precision %d", precision);
+  if (precision != SMORE_DOT_TF32 && precision != SMORE_DOT_FP32)
+    return fail(SMORE_ERR_BAD_DIST, "unknown dot precision %d", precision);
+  const bool fast = precision == SMORE_DOT_FP32;
+  const size_t tiles = ((size_t)(M + 255) / 256) * ((size_t)(N + 127) / 128);
+  const size_t pairs = std::max(1, sm_count() / 2);
+  const double waves = (double)tiles / (double)pairs;
+  const bool stream_k = M >= 256 && waves < 4.0 && (waves - (double)(size_t)waves) > 0.05 && K >= 1024;
+  using StreamK = cutlass::gemm::StreamKScheduler;
+  if (M < 256) {
+    return fast ? run_gemm<LayoutA, LayoutB, OneSm, true, void>(A, B, D, M, N, K, ws, ws_bytes, st, need)
+                : run_gemm<LayoutA, LayoutB, OneSm, false, void>(A, B, D, M, N, K, ws, ws_bytes, st, need);
+  }
+  if (N >= 2048 && !fast) {
+    return run_gemm<LayoutA, LayoutB, TwoSmWide, false, void>(A, B, D, M, N, K, ws, ws_bytes, st, need);
+  }
+  if (stream_k) {
+    return fast ? run_gemm<LayoutA, LayoutB, TwoSm, true, StreamK>(A, B, D, M, N, K, ws, ws_bytes, st, need)
+                : run_gemm<LayoutA, LayoutB, TwoSm, false, StreamK>(A, B, D, M, N, K, ws, ws_bytes, st, need);
+  }
+  return fast ? run_gemm<LayoutA, LayoutB, TwoSm, true, void>(A, B, D, M, N, K, ws, ws_bytes, st, need)
+              : run_gemm<LayoutA, LayoutB, TwoSm, false, void>(A, B, D, M, N, K, ws, ws_bytes, st, need);
 }
 
 }  // namespace smore
