@@ -1259,6 +1259,9 @@ def run_gpu(args):
                                    fma_rate)
                 if dot_mode:
                     res["dot_precision"] = dot_mode
+                    from smore_b200 import _lib as _l
+                    res["gemm_tiles"] = ("256x128 / 256x256 tiles on SM pairs (companion library loaded)"
+                                         if _l.lib().smore_dot_two_sm() else "128x128 tiles, one SM each")
                     cb = cublas_comparison(wcfg, device)
                     res["cublas"] = cb
                     for kname, what in (("dot_forward", "forward"), ("dot_backward", "backward")):
@@ -1266,7 +1269,7 @@ def run_gpu(args):
                             res["kernels"][kname]["vs_cublas"] = round(
                                 cb["%s_%s_ms" % (dot_mode, what)] / res["kernels"][kname]["avg_ms"], 3)
                 slim = {k: res[k] for k in ("value", "unit", "ms_per_step", "repeats", "eager_ms_per_step", "e2e", "roofline",
-                                            "kernels", "gpu_launches", "distinct_rows_per_step") if k in res}
+                                            "kernels", "gpu_launches", "distinct_rows_per_step", "gemm_tiles") if k in res}
                 slim["config"] = {k: res["config"][k] for k in ("geo", "queries_per_gpu", "negatives", "shared_negatives",
                                                                 "dim", "table_rows_per_gpu", "structures", "optimizer")}
                 for k in ("dot_precision", "cublas"):

@@ -450,6 +450,9 @@ SMORE_API int smore_negative_mask(const int64_t* negatives, size_t k, const int6
 #define SMORE_DOT_TF32 0
 #define SMORE_DOT_FP32 1
 SMORE_API int smore_dot_available(void);
+/* 1 when the optional companion library libsmore_b200_2sm.so (the same products on tiles shared by
+ * two SMs, tcgen05 cta_group::2) sits next to this library and was loaded; 0: one-SM tiles only. */
+SMORE_API int smore_dot_two_sm(void);
 SMORE_API size_t smore_dot_workspace_bytes(size_t B, size_t K, size_t W, int precision);
 SMORE_API int smore_dot_forward_shared(const float* cand, const float* query, float* dst, size_t B, size_t K,
                              size_t W, int precision, void* workspace, size_t workspace_bytes,

@@ -65,6 +65,7 @@ SIGNATURES = {
     "smore_sample_negatives": (_int, [ctypes.c_uint64, ctypes.c_uint64, _sz, _p, _p, _p, _p, _p, _sz, _sz, _p, _p]),
     "smore_negative_mask": (_int, [_p, _sz, _p, _p, _sz, _p, _p]),
     "smore_dot_available": (_int, []),
+    "smore_dot_two_sm": (_int, []),
     "smore_dot_workspace_bytes": (_sz, [_sz, _sz, _sz, _int]),
     "smore_dot_forward_shared": (_int, [_p, _p, _p, _sz, _sz, _sz, _int, _p, _sz, _p]),
     "smore_dot_backward_shared": (_int, [_p, _p, _p, _p, _p, _sz, _sz, _sz, _int, _p, _sz, _p]),

@@ -20,8 +20,13 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 
 
+TWO_SM_SRC = os.path.join(HERE, "gemm_sm100_2sm.cu")
+TWO_SM_LIB = os.path.join(HERE, "libsmore_b200_2sm.so")      # optional companion: two-SM GEMM tiles
+
+
 def sources():
-    return sorted(glob.glob(os.path.join(HERE, "*.cu")))
+    """Sources of libsmore_b200.so (the companion library's source is built on its own)."""
+    return sorted(f for f in glob.glob(os.path.join(HERE, "*.cu")) if f != TWO_SM_SRC)
 
 
 def cutlass_include_dirs():
@@ -93,13 +98,28 @@ def build(force=False, verbose=False):
               ["-I", os.path.join(ROOT, "include"), "-I", HERE, "-c", src, "-o", obj]
         print("+", " ".join(cmd), flush=True)
         procs.append((src, subprocess.Popen(cmd)))
+    two_sm = None
+    if cutlass and os.path.exists(TWO_SM_SRC) and (force or _newer(TWO_SM_LIB, _local_deps(TWO_SM_SRC) +
+                                                                    [os.path.abspath(__file__)])):
+        cmd = [nvcc] + NVCC_FLAGS + ["-DSMORE_HAVE_CUTLASS", "--expt-extended-lambda"]
+        for d in cutlass:
+            cmd += ["-I", d]
+        cmd += ["-I", os.path.join(ROOT, "include"), "-I", HERE, "-shared", TWO_SM_SRC, "-o", TWO_SM_LIB + ".tmp"]
+        print("+", " ".join(cmd), flush=True)
+        two_sm = subprocess.Popen(cmd)
     for src, p in procs:
         if p.wait() != 0:
             raise RuntimeError("nvcc failed on " + src)
     if procs or force or _newer(LIB_PATH, objs):
-        cmd = [nvcc, "-shared", "-o", LIB_PATH] + objs
+        # link to a temporary name and rename: a reader never sees a half-written library
+        cmd = [nvcc, "-shared", "-o", LIB_PATH + ".tmp"] + objs
         print("+", " ".join(cmd), flush=True)
         subprocess.check_call(cmd)
+        os.replace(LIB_PATH + ".tmp", LIB_PATH)
+    if two_sm is not None:
+        if two_sm.wait() != 0:
+            raise RuntimeError("nvcc failed on " + TWO_SM_SRC)
+        os.replace(TWO_SM_LIB + ".tmp", TWO_SM_LIB)
     return LIB_PATH
 
 

@@ -8,9 +8,9 @@
 //     g_query[B, W] = g[B, K]     . cand[K, W]
 //     g_cand[K, W]  = g[B, K]^T   . query[B, W]
 // W is the row length (dim for DistMult; 2*dim for ComplEx, with the query laid out [re | im] like
-// the entity rows).  The kernels are CUTLASS 3.x sm100 templates instantiated here: TMA loads
-// (never multicast), tcgen05.mma with TMEM accumulators, two SMs per 256 x 128 tile, fp32 in / fp32
-// out, in two
+// the entity rows).  The kernels are CUTLASS 3.x sm100 templates instantiated here: TMA loads,
+// tcgen05.mma with TMEM accumulators, one SM per 128 x 128 tile (cluster 1x1x1), fp32 in / fp32 out,
+// in two
 // precisions: TF32 (10-bit mantissa products) and "fast fp32" (each fp32 operand split into three
 // bf16 terms, nine bf16 MMAs per product, fp32-level accuracy).
 //
@@ -18,25 +18,22 @@
 // report SMORE_ERR_BAD_SHAPE and callers use the SIMT tile kernels.
 #include <cuda_runtime.h>
 
-#include <algorithm>
-
 #include "common.cuh"
 
+extern "C" int smore_dot_available(void);
+
 #ifdef SMORE_HAVE_CUTLASS
-#include "cute/tensor.hpp"
-#include "cutlass/cutlass.h"
-#include "cutlass/epilogue/collective/collective_builder.hpp"
-#include "cutlass/gemm/collective/collective_builder.hpp"
-#include "cutlass/gemm/device/gemm_universal_adapter.h"
-#include "cutlass/gemm/kernel/gemm_universal.hpp"
-#include "cutlass/util/packed_stride.hpp"
+#include <dlfcn.h>
+
+#include <mutex>
+#include <string>
+
+#include "gemm_sm100_common.cuh"
 
 namespace smore {
-using namespace cute;
+using namespace smore_gemm;
 
-// Tile variants.  TwoSm pairs two SMs on one 256 x 128 tile (tcgen05 cta_group::2, cluster 2 x 1): each
-// CTA of the pair loads its own halves of the operand tiles, so with this static cluster shape the
-// builder picks the plain two-SM TMA loads - no operand is multicast.
+// One SM per 128 x 128 tile, cluster 1 x 1 x 1: what this library always has.
 struct OneSm {
   using Tile = Shape<_128, _128, _32>;
   using Cluster = Shape<_1, _1, _1>;
@@ -44,97 +41,57 @@ struct OneSm {
   using Fp32x9 = cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32Sm100;
   using Epilogue = cutlass::epilogue::TmaWarpSpecialized1Sm;
 };
-struct TwoSm {
-  using Tile = Shape<_256, _128, _32>;
-  using Cluster = Shape<_2, _1, _1>;
-  using Tf32 = cutlass::gemm::KernelTmaWarpSpecialized2SmSm100;
-  using Fp32x9 = cutlass::gemm::KernelTmaWarpSpecialized2SmFastFP32Sm100;
-  using Epilogue = cutlass::epilogue::TmaWarpSpecialized2Sm;
-};
 
-struct TwoSmWide : TwoSm {      // 256 x 256 tiles: half the operand traffic per flop, for outputs with many columns
-  using Tile = Shape<_256, _256, _32>;
-};
+// The companion library (libsmore_b200_2sm.so, built from gemm_sm100_2sm.cu) holds the same products
+// on tiles shared by two SMs.  It is optional: when the file sits next to this library it is loaded
+// on first use and takes the products with at least 256 output rows; without it everything runs on
+// the one-SM tiles.
+typedef int (*TwoSmRun)(int layout, int fast, const float* A, const float* B, float* D, int M, int N, int K, void* ws,
+                        size_t ws_bytes, void* stream, size_t* need);
+static TwoSmRun g_two_sm = nullptr;
+static std::once_flag g_two_sm_once;
 
-template <class LayoutA, class LayoutB, class Variant, bool kFast, class Scheduler>
-struct DotGemm {
-  using Acc = float;
-  using LayoutC = cutlass::layout::RowMajor;
-  using Tile = typename Variant::Tile;
-  using Cluster = typename Variant::Cluster;
-  using Schedule = cute::conditional_t<kFast, typename Variant::Fp32x9, typename Variant::Tf32>;
-  using Epi = typename cutlass::epilogue::collective::CollectiveBuilder<
-      cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, Tile, Cluster,
-      cutlass::epilogue::collective::EpilogueTileAuto, Acc, Acc, float, LayoutC, 4, float, LayoutC, 4,
-      typename Variant::Epilogue>::CollectiveOp;
-  using Main = typename cutlass::gemm::collective::CollectiveBuilder<
-      cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, float, LayoutA, 4, float, LayoutB, 4, Acc, Tile, Cluster,
-      cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename Epi::SharedStorage))>,
-      Schedule>::CollectiveOp;
-  using Kernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, Main, Epi, Scheduler>;
-  using Gemm = cutlass::gemm::device::GemmUniversalAdapter<Kernel>;
-};
-
-// D[M, N] = A . B with A(m, k), B(k, n) in the given layouts ("column-major B" = an [N, K] row-major array)
-template <class LayoutA, class LayoutB, class Variant, bool kFast, class Scheduler>
-static int run_gemm(const float* A, const float* B, float* D, int M, int N, int K, void* ws, size_t ws_bytes,
-                    cudaStream_t st, size_t* need) {
-  using Gemm = typename DotGemm<LayoutA, LayoutB, Variant, kFast, Scheduler>::Gemm;
-  using StrideA = typename Gemm::GemmKernel::StrideA;
-  using StrideB = typename Gemm::GemmKernel::StrideB;
-  using StrideC = typename Gemm::GemmKernel::StrideC;
-  using StrideD = typename Gemm::GemmKernel::StrideD;
-  auto sa = cutlass::make_cute_packed_stride(StrideA{}, make_shape(M, K, 1));
-  auto sb = cutlass::make_cute_packed_stride(StrideB{}, make_shape(N, K, 1));
-  auto sc = cutlass::make_cute_packed_stride(StrideC{}, make_shape(M, N, 1));
-  auto sd = cutlass::make_cute_packed_stride(StrideD{}, make_shape(M, N, 1));
-  typename Gemm::Arguments args{cutlass::gemm::GemmUniversalMode::kGemm, {M, N, K, 1}, {A, sa, B, sb},
-                                {{1.0f, 0.0f}, D, sc, D, sd}};
-  if (need) {
-    *need = Gemm::get_workspace_size(args);
-    return SMORE_OK;
-  }
-  Gemm gemm;
-  if (gemm.can_implement(args) != cutlass::Status::kSuccess)
-    return fail(SMORE_ERR_BAD_SHAPE, "tensor-core GEMM cannot take M=%d N=%d K=%d (sizes must be multiples of 4)", M, N, K);
-  if (Gemm::get_workspace_size(args) > ws_bytes)
-    return fail(SMORE_ERR_WORKSPACE, "tensor-core GEMM needs %zu bytes of workspace", Gemm::get_workspace_size(args));
-  if (gemm.initialize(args, ws, st) != cutlass::Status::kSuccess) return fail(SMORE_ERR_CUDA, "GEMM initialize failed");
-  if (gemm.run(st) != cutlass::Status::kSuccess) return fail(SMORE_ERR_CUDA, "GEMM launch failed");
-  count_launches(1);
-  return SMORE_OK;
+static TwoSmRun two_sm() {
+  std::call_once(g_two_sm_once, [] {
+    Dl_info info;
+    if (!dladdr(reinterpret_cast<void*>(&smore_dot_available), &info) || !info.dli_fname) return;
+    std::string path(info.dli_fname);
+    const size_t slash = path.rfind('/');
+    path = (slash == std::string::npos ? std::string(".") : path.substr(0, slash)) + "/libsmore_b200_2sm.so";
+    void* h = dlopen(path.c_str(), RTLD_NOW | RTLD_LOCAL);
+    if (h) g_two_sm = reinterpret_cast<TwoSmRun>(dlsym(h, "smore_dot2sm_run"));
+  });
+  return g_two_sm;
 }
 
-using RowM = cutlass::layout::RowMajor;
-using ColM = cutlass::layout::ColumnMajor;
+static int gemm_status(int code, int M, int N, int K) {
+  switch (code) {
+    case kOk: return SMORE_OK;
+    case kBadShape:
+      return fail(SMORE_ERR_BAD_SHAPE, "tensor-core GEMM cannot take M=%d N=%d K=%d (sizes must be multiples of 4)", M, N, K);
+    case kWorkspace: return fail(SMORE_ERR_WORKSPACE, "tensor-core GEMM: workspace too small (smore_dot_workspace_bytes)");
+    default: return fail(SMORE_ERR_CUDA, "tensor-core GEMM: initialize or launch failed");
+  }
+}
 
-// Output tiles are handed to the SMs by the persistent scheduler; products whose tile count is a
-// small non-multiple of the SM count (the query gradient: 128 two-SM tiles on 74 SM pairs) use the
-// stream-K scheduler, which splits the contraction of the last partial wave over the idle SMs.
-template <class LayoutA, class LayoutB>
+enum { kLayoutRowCol = 0, kLayoutRowRow = 1, kLayoutColRow = 2 };
+
+template <class LayoutA, class LayoutB, int kLayout>
 static int run_precision(int precision, const float* A, const float* B, float* D, int M, int N, int K, void* ws,
                          size_t ws_bytes, cudaStream_t st, size_t* need) {
   if (precision != SMORE_DOT_TF32 && precision != SMORE_DOT_FP32)
     return fail(SMORE_ERR_BAD_DIST, "unknown dot precision %d", precision);
   const bool fast = precision == SMORE_DOT_FP32;
-  const size_t tiles = ((size_t)(M + 255) / 256) * ((size_t)(N + 127) / 128);
-  const size_t pairs = std::max(1, sm_count() / 2);
-  const double waves = (double)tiles / (double)pairs;
-  const bool stream_k = M >= 256 && waves < 4.0 && (waves - (double)(size_t)waves) > 0.05 && K >= 1024;
-  using StreamK = cutlass::gemm::StreamKScheduler;
-  if (M < 256) {
-    return fast ? run_gemm<LayoutA, LayoutB, OneSm, true, void>(A, B, D, M, N, K, ws, ws_bytes, st, need)
+  int code;
+  TwoSmRun wide = M >= 256 ? two_sm() : nullptr;
+  if (wide != nullptr) {
+    code = wide(kLayout, fast ? 1 : 0, A, B, D, M, N, K, ws, ws_bytes, st, need);
+  } else {
+    code = fast ? run_gemm<LayoutA, LayoutB, OneSm, true, void>(A, B, D, M, N, K, ws, ws_bytes, st, need)
                 : run_gemm<LayoutA, LayoutB, OneSm, false, void>(A, B, D, M, N, K, ws, ws_bytes, st, need);
   }
-  if (N >= 2048 && !fast) {
-    return run_gemm<LayoutA, LayoutB, TwoSmWide, false, void>(A, B, D, M, N, K, ws, ws_bytes, st, need);
-  }
-  if (stream_k) {
-    return fast ? run_gemm<LayoutA, LayoutB, TwoSm, true, StreamK>(A, B, D, M, N, K, ws, ws_bytes, st, need)
-                : run_gemm<LayoutA, LayoutB, TwoSm, false, StreamK>(A, B, D, M, N, K, ws, ws_bytes, st, need);
-  }
-  return fast ? run_gemm<LayoutA, LayoutB, TwoSm, true, void>(A, B, D, M, N, K, ws, ws_bytes, st, need)
-              : run_gemm<LayoutA, LayoutB, TwoSm, false, void>(A, B, D, M, N, K, ws, ws_bytes, st, need);
+  if (code == kOk && !need) count_launches(1);
+  return gemm_status(code, M, N, K);
 }
 
 }  // namespace smore
@@ -158,13 +115,21 @@ int smore_dot_available(void) {
 #endif
 }
 
+int smore_dot_two_sm(void) {
+#ifdef SMORE_HAVE_CUTLASS
+  return two_sm() != nullptr ? 1 : 0;
+#else
+  return 0;
+#endif
+}
+
 size_t smore_dot_workspace_bytes(size_t B, size_t K, size_t W, int precision) {
 #ifdef SMORE_HAVE_CUTLASS
   size_t n0 = 0, n1 = 0, n2 = 0;
   if (check_sizes(B, K, W)) return 0;
-  run_precision<RowM, ColM>(precision, nullptr, nullptr, nullptr, (int)B, (int)K, (int)W, nullptr, 0, nullptr, &n0);
-  run_precision<RowM, RowM>(precision, nullptr, nullptr, nullptr, (int)B, (int)W, (int)K, nullptr, 0, nullptr, &n1);
-  run_precision<ColM, RowM>(precision, nullptr, nullptr, nullptr, (int)K, (int)W, (int)B, nullptr, 0, nullptr, &n2);
+  run_precision<RowM, ColM, kLayoutRowCol>(precision, nullptr, nullptr, nullptr, (int)B, (int)K, (int)W, nullptr, 0, nullptr, &n0);
+  run_precision<RowM, RowM, kLayoutRowRow>(precision, nullptr, nullptr, nullptr, (int)B, (int)W, (int)K, nullptr, 0, nullptr, &n1);
+  run_precision<ColM, RowM, kLayoutColRow>(precision, nullptr, nullptr, nullptr, (int)K, (int)W, (int)B, nullptr, 0, nullptr, &n2);
   size_t n = n0 > n1 ? n0 : n1;
   n = n > n2 ? n : n2;
   return n < 256 ? 256 : n;
@@ -179,7 +144,7 @@ int smore_dot_forward_shared(const float* cand, const float* query, float* dst, 
   if (!cand || !query || !dst) return fail(SMORE_ERR_NULL, "dot_forward_shared: NULL pointer");
   if (int rc = check_sizes(B, K, W)) return rc;
 #ifdef SMORE_HAVE_CUTLASS
-  return run_precision<RowM, ColM>(precision, query, cand, dst, (int)B, (int)K, (int)W, workspace, workspace_bytes,
+  return run_precision<RowM, ColM, kLayoutRowCol>(precision, query, cand, dst, (int)B, (int)K, (int)W, workspace, workspace_bytes,
                                    (cudaStream_t)stream, nullptr);
 #else
   (void)precision; (void)workspace; (void)workspace_bytes; (void)stream;
@@ -195,11 +160,11 @@ int smore_dot_backward_shared(const float* gout, const float* cand, const float*
 #ifdef SMORE_HAVE_CUTLASS
   cudaStream_t st = (cudaStream_t)stream;
   // g_query[B, W] = gout[B, K] . cand[K, W]
-  if (int rc = run_precision<RowM, RowM>(precision, gout, cand, g_query, (int)B, (int)W, (int)K, workspace,
+  if (int rc = run_precision<RowM, RowM, kLayoutRowRow>(precision, gout, cand, g_query, (int)B, (int)W, (int)K, workspace,
                                          workspace_bytes, st, nullptr))
     return rc;
   // g_cand[K, W] = gout^T[K, B] . query[B, W]
-  return run_precision<ColM, RowM>(precision, gout, query, g_cand, (int)K, (int)W, (int)B, workspace, workspace_bytes,
+  return run_precision<ColM, RowM, kLayoutColRow>(precision, gout, query, g_cand, (int)K, (int)W, (int)B, workspace, workspace_bytes,
                                    st, nullptr);
 #else
   (void)precision; (void)workspace; (void)workspace_bytes; (void)stream;

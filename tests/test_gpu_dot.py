@@ -145,3 +145,11 @@ def test_gemm_route_agrees_with_simt_route_and_handles_table_rows(monkeypatch):
     np.testing.assert_allclose(outs[1].cpu().numpy(), outs[0].cpu().numpy(), rtol=0, atol=2e-5 * 64 * 0.05 * 0.05 * 9)
     np.testing.assert_allclose(tables[1].cpu().numpy(), tables[0].cpu().numpy(), rtol=1e-4,
                                atol=1e-4 * tables[0].abs().max().item())
+
+
+def test_tile_variant_is_reported():
+    """The two-SM tiles live in an optional companion library; the main library says whether it found
+    it, and the products above were checked on whichever variant is active."""
+    from smore_b200 import _lib
+    assert _lib.lib().smore_dot_two_sm() in (0, 1)
+    print("tensor-core tiles:", "two SMs per tile" if _lib.lib().smore_dot_two_sm() else "one SM per tile")
