@@ -28,19 +28,77 @@ extern "C" int smore_dot_available(void);
 #include <mutex>
 #include <string>
 
-#include "gemm_sm100_common.cuh"
+#include "cute/tensor.hpp"
+#include "cutlass/cutlass.h"
+#include "cutlass/epilogue/collective/collective_builder.hpp"
+#include "cutlass/gemm/collective/collective_builder.hpp"
+#include "cutlass/gemm/device/gemm_universal_adapter.h"
+#include "cutlass/gemm/kernel/gemm_universal.hpp"
+#include "cutlass/util/packed_stride.hpp"
+
+
+namespace smore_gemm {
+using namespace cute;
+
+enum { kOk = 0, kBadShape = 1, kWorkspace = 2, kCuda = 3 };
+
+// One SM per 128 x 128 tile, cluster 1 x 1 x 1.
+template <class LayoutA, class LayoutB, bool kFast>
+struct DotGemm {
+  using Acc = float;
+  using LayoutC = cutlass::layout::RowMajor;
+  using Tile = Shape<_128, _128, _32>;
+  using Cluster = Shape<_1, _1, _1>;
+  using Schedule = cute::conditional_t<kFast, cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32Sm100,
+                                       cutlass::gemm::KernelTmaWarpSpecialized1SmSm100>;
+  using Epi = typename cutlass::epilogue::collective::CollectiveBuilder<
+      cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, Tile, Cluster,
+      cutlass::epilogue::collective::EpilogueTileAuto, Acc, Acc, float, LayoutC, 4, float, LayoutC, 4,
+      cutlass::epilogue::TmaWarpSpecialized1Sm>::CollectiveOp;
+  using Main = typename cutlass::gemm::collective::CollectiveBuilder<
+      cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, float, LayoutA, 4, float, LayoutB, 4, Acc, Tile, Cluster,
+      cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename Epi::SharedStorage))>,
+      Schedule>::CollectiveOp;
+  using Kernel = cutlass::gemm::kernel::GemmUniversal<Shape<int, int, int, int>, Main, Epi, void>;
+  using Gemm = cutlass::gemm::device::GemmUniversalAdapter<Kernel>;
+};
+
+// D[M, N] = A . B with A(m, k), B(k, n) in the given layouts ("column-major B" = an [N, K] row-major
+// array).  need != nullptr: only report the workspace size.  Returns one of the codes above;
+// *ws_needed receives the workspace size when that is what is missing.
+template <class LayoutA, class LayoutB, bool kFast>
+static int run_gemm(const float* A, const float* B, float* D, int M, int N, int K, void* ws, size_t ws_bytes,
+                    cudaStream_t st, size_t* need) {
+  using Gemm = typename DotGemm<LayoutA, LayoutB, kFast>::Gemm;
+  using StrideA = typename Gemm::GemmKernel::StrideA;
+  using StrideB = typename Gemm::GemmKernel::StrideB;
+  using StrideC = typename Gemm::GemmKernel::StrideC;
+  using StrideD = typename Gemm::GemmKernel::StrideD;
+  auto sa = cutlass::make_cute_packed_stride(StrideA{}, make_shape(M, K, 1));
+  auto sb = cutlass::make_cute_packed_stride(StrideB{}, make_shape(N, K, 1));
+  auto sc = cutlass::make_cute_packed_stride(StrideC{}, make_shape(M, N, 1));
+  auto sd = cutlass::make_cute_packed_stride(StrideD{}, make_shape(M, N, 1));
+  typename Gemm::Arguments args{cutlass::gemm::GemmUniversalMode::kGemm, {M, N, K, 1}, {A, sa, B, sb},
+                                {{1.0f, 0.0f}, D, sc, D, sd}};
+  if (need) {
+    *need = Gemm::get_workspace_size(args);
+    return kOk;
+  }
+  Gemm gemm;
+  if (gemm.can_implement(args) != cutlass::Status::kSuccess) return kBadShape;
+  if (Gemm::get_workspace_size(args) > ws_bytes) return kWorkspace;
+  if (gemm.initialize(args, ws, st) != cutlass::Status::kSuccess) return kCuda;
+  if (gemm.run(st) != cutlass::Status::kSuccess) return kCuda;
+  return kOk;
+}
+
+using RowM = cutlass::layout::RowMajor;
+using ColM = cutlass::layout::ColumnMajor;
+
+}  // namespace smore_gemm
 
 namespace smore {
 using namespace smore_gemm;
-
-// One SM per 128 x 128 tile, cluster 1 x 1 x 1: what this library always has.
-struct OneSm {
-  using Tile = Shape<_128, _128, _32>;
-  using Cluster = Shape<_1, _1, _1>;
-  using Tf32 = cutlass::gemm::KernelTmaWarpSpecialized1SmSm100;
-  using Fp32x9 = cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32Sm100;
-  using Epilogue = cutlass::epilogue::TmaWarpSpecialized1Sm;
-};
 
 // The companion library (libsmore_b200_2sm.so, built from gemm_sm100_2sm.cu) holds the same products
 // on tiles shared by two SMs.  It is optional: when the file sits next to this library it is loaded
@@ -87,8 +145,8 @@ static int run_precision(int precision, const float* A, const float* B, float* D
   if (wide != nullptr) {
     code = wide(kLayout, fast ? 1 : 0, A, B, D, M, N, K, ws, ws_bytes, st, need);
   } else {
-    code = fast ? run_gemm<LayoutA, LayoutB, OneSm, true, void>(A, B, D, M, N, K, ws, ws_bytes, st, need)
-                : run_gemm<LayoutA, LayoutB, OneSm, false, void>(A, B, D, M, N, K, ws, ws_bytes, st, need);
+    code = fast ? run_gemm<LayoutA, LayoutB, true>(A, B, D, M, N, K, ws, ws_bytes, st, need)
+                : run_gemm<LayoutA, LayoutB, false>(A, B, D, M, N, K, ws, ws_bytes, st, need);
   }
   if (code == kOk && !need) count_launches(1);
   return gemm_status(code, M, N, K);
