@@ -567,16 +567,18 @@ SMORE_API int smore_shard_reduce_update_rows_dev(float* table, float* m, float* 
  * stream-ordered barriers (publish -> select/score -> read results; publish upstream gradients ->
  * differentiate/update -> sum the partial query gradients).
  *
- * Rank r's descriptor is int32[8] {n_queries, K, 0...}: its ids are [n_queries, K] int64 global
- * row ids, its queries [n_queries, dim] per operand, its results / upstream gradients [n_queries,
- * K] per output.  All `*_ptrs` arguments are device arrays with one (peer) pointer per rank.
+ * Rank r's descriptor is int32[8] {n_queries, K, branches, 0...}: its ids are [n_queries, K] int64
+ * global row ids, its queries [n_queries, branches, dim] per operand (branches = 2: a union query,
+ * both branches scored against the same candidates), its results / upstream gradients [n_queries,
+ * branches, K] per output.  The owner's calls name the K and the branch count they were launched
+ * for (rows_per_query, branches); a rank whose descriptor says otherwise is left out.  All `*_ptrs` arguments are device arrays with one (peer) pointer per rank.
  * max_queries / pairs_capacity are what every rank's buffers were sized for; a descriptor beyond
  * them, or more selected pairs than `capacity`, drops the work concerned and sets bit 3 of
  * smore_async_status.
  *
  * smore_owner_select_pairs: for every (rank, query) the pairs whose id lies in [base, base +
  *   shard_rows) become one segment of the compact arrays: rows[] (local row ids), positions[]
- *   (query * K + k on the requester), in increasing k; segments[(rank * max_queries + query) * 2 +
+ *   (query * branches * K + k on the requester: branch 0), in increasing k; segments[(rank * max_queries + query) * 2 +
  *   {0, 1}] = {first compact position, count}; n_selected[0] = pairs selected (int32[2]).
  * smore_owner_gather_queries: first_all / second_all[(rank * max_queries + query), dim] <- the
  *   ranks' queries (second_* may be NULL for one-operand distances).
@@ -585,8 +587,9 @@ SMORE_API int smore_shard_reduce_update_rows_dev(float* table, float* m, float* 
  *   upstream gradients (gout0, gout1) are indexed by compact position - or, with `positions`,
  *   result / upstream gradient of compact position c lives at positions[c] in the arrays of the
  *   rank that owns the segment (rank = q / segments_per_rank; out*_ptrs / gout*_ptrs: one base
- *   pointer per rank, peer memory) and the local arrays may be NULL; g_first / g_second
- *   [n_segments, dim] receive each segment's query gradient.  Backward: slot / slot_count / g_rows
+ *   pointer per rank, peer memory; branch u of a pair sits u * branch_stride further) and the local
+ *   arrays may be NULL.  Queries and query gradients of rank r start at r * segments_per_rank * dim
+ *   floats, query q of that rank at q * branches * dim inside them.  Backward: slot / slot_count / g_rows
  *   / uniq / m / v and the Adam arguments as in smore_rows_backward_fused_adam, over the owner's
  *   distinct rows.  Rows of 1 KB to about 4 KB, dim a multiple of 4 above 256 (SMORE_ERR_BAD_SHAPE
  *   otherwise, nothing enqueued).  dist_id may be SMORE_DIST_BOX_BOTH.
@@ -600,18 +603,18 @@ SMORE_API int smore_shard_reduce_update_rows_dev(float* table, float* m, float* 
  * smore_owner_sum_query_grads: out[q, :] = sum over owners o of part_ptrs[o][(my_rank *
  *   max_queries + q), :], in owner order (the requester's query gradient). */
 SMORE_API int smore_owner_select_pairs(const int64_t* const* pair_id_ptrs, const int32_t* const* desc_ptrs,
-                             size_t n_ranks, size_t max_queries, size_t pairs_capacity, int64_t base,
-                             size_t shard_rows, size_t capacity, int64_t* rows, int32_t* positions,
-                             int32_t* segments, int32_t* n_selected, void* stream);
+                             size_t n_ranks, size_t max_queries, size_t pairs_capacity, size_t rows_per_query,
+                             size_t branches, int64_t base, size_t shard_rows, size_t capacity, int64_t* rows,
+                             int32_t* positions, int32_t* segments, int32_t* n_selected, void* stream);
 SMORE_API int smore_owner_gather_queries(const float* const* first_ptrs, const float* const* second_ptrs,
                                const int32_t* const* desc_ptrs, size_t n_ranks, size_t max_queries,
-                               size_t pairs_capacity, size_t dim, float* first_all, float* second_all,
-                               void* stream);
+                               size_t pairs_capacity, size_t rows_per_query, size_t branches, size_t dim,
+                               float* first_all, float* second_all, void* stream);
 SMORE_API int smore_rows_forward_ragged(int dist_id, const float* table, const int64_t* rows, size_t n_table_rows,
                               const float* first, const float* second, const int32_t* segments,
                               size_t n_segments, size_t dim, float* out0, float* out1, const int32_t* positions,
                               size_t segments_per_rank, float* const* out0_ptrs, float* const* out1_ptrs,
-                              void* stream);
+                              size_t branches, size_t branch_stride, void* stream);
 SMORE_API int smore_rows_backward_fused_adam_ragged(int dist_id, const float* gout0, const float* gout1, float* table,
                                           const int64_t* rows, size_t n_table_rows, const float* first,
                                           const float* second, const int32_t* segments, size_t n_segments,
@@ -620,7 +623,8 @@ SMORE_API int smore_rows_backward_fused_adam_ragged(int dist_id, const float* go
                                           int64_t* uniq, double lr, double beta1, double beta2, double eps,
                                           int64_t step, const float* step_scalars, const int32_t* positions,
                                           size_t segments_per_rank, const float* const* gout0_ptrs,
-                                          const float* const* gout1_ptrs, void* stream);
+                                          const float* const* gout1_ptrs, size_t branches, size_t branch_stride,
+                                          void* stream);
 SMORE_API int smore_owner_plan(const int64_t* const* uniq_ptrs, const int32_t* const* nuniq_ptrs, size_t n_ranks,
                      size_t n_plans, const int32_t* plan_caps, int64_t base, size_t shard_rows, size_t capacity,
                      int64_t* ids, int32_t* runs, int64_t* uniq, int32_t* slot, int32_t* counts,

@@ -175,6 +175,7 @@ __global__ void __launch_bounds__(256)
 // row-stream kernels (per-query candidate rows)
 // ----------------------------------------------------------------------------------------
 
+constexpr int kUnionBranches = 2;   // query branches the fused union kernels take
 constexpr int kRowCtaThreads = 256;
 constexpr int kRowCtaWarps = kRowCtaThreads / kWarp;
 
@@ -197,8 +198,11 @@ struct RowArgs {
   // result / upstream gradient of compact position p lives at positions[p] in THAT rank's arrays
   // (peer memory): out_ptrs / up_ptrs hold one base pointer per rank and output.  positions ==
   // nullptr: results and upstream gradients are local arrays indexed by compact position.
+  // With NB branches per query the rank's arrays are [query][branch][K]: positions[p] names branch 0,
+  // branch u sits u * branch_stride (= that rank's K) further.
   const int32_t* positions;
   int seg_per_rank;
+  int branch_stride;
   float* const* out_ptrs[2];
   const float* const* up_ptrs[2];
 };
@@ -226,6 +230,16 @@ __device__ __forceinline__ RowBlock row_block(const RowArgs& a) {
     rb.pos_base = (size_t)rb.b * a.K;
   }
   return rb;
+}
+
+// First float of the block's NB query rows in `first` / `second` / the query-gradient arrays.  Dense
+// form: query b's rows start at b * NB * dim.  Ragged form: rank r's queries occupy seg_per_rank * dim
+// floats starting at r * seg_per_rank * dim, query q of that rank at q * NB * dim inside them.
+template <int NB>
+__device__ __forceinline__ size_t query_offset(const RowArgs& a, int b) {
+  if (a.seg == nullptr) return (size_t)b * NB * a.dim;
+  const int rank = b / a.seg_per_rank, q = b - rank * a.seg_per_rank;
+  return ((size_t)rank * a.seg_per_rank + (size_t)q * NB) * a.dim;
 }
 
 __device__ __forceinline__ float4 ld_row4(const float4* p) { return __ldg(p); }
@@ -476,7 +490,8 @@ __host__ __device__ inline size_t bulk_ring_offset(int stages) {
   return ((size_t)kRowCtaWarps * stages * sizeof(uint64_t) + 127) & ~(size_t)127;
 }
 
-template <class Term, int NCH>
+// NB: query branches scored against every row (union queries; results [query][branch][row]).
+template <class Term, int NB, int NCH>
 __global__ void __launch_bounds__(kRowCtaThreads)
     row_forward_bulk_kernel(RowArgs a, float* __restrict__ dst0, float* __restrict__ dst1, int stages) {
   extern __shared__ __align__(128) unsigned char bulk_smem[];
@@ -495,15 +510,19 @@ __global__ void __launch_bounds__(kRowCtaThreads)
   }
   __syncthreads();
 
-  float4 q0[NCH], q1[NCH];
+  float4 q0[NB][NCH], q1[NB][NCH];
   {
-    const float4* p0 = reinterpret_cast<const float4*>(a.first + (size_t)b * a.dim);
-    const float4* p1 = reinterpret_cast<const float4*>(a.second + (size_t)b * a.dim);
+    const size_t q_off = query_offset<NB>(a, b);
 #pragma unroll
-    for (int j = 0; j < NCH; ++j) {
-      const int d4 = lane + 32 * j;
-      q0[j] = d4 < dim4 ? __ldg(p0 + d4) : z4;
-      q1[j] = (Term::kNQ == 2 && d4 < dim4) ? __ldg(p1 + d4) : z4;
+    for (int u = 0; u < NB; ++u) {
+      const float4* p0 = reinterpret_cast<const float4*>(a.first + q_off + (size_t)u * a.dim);
+      const float4* p1 = reinterpret_cast<const float4*>(a.second + q_off + (size_t)u * a.dim);
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const int d4 = lane + 32 * j;
+        q0[u][j] = d4 < dim4 ? __ldg(p0 + d4) : z4;
+        q1[u][j] = (Term::kNQ == 2 && d4 < dim4) ? __ldg(p1 + d4) : z4;
+      }
     }
   }
 
@@ -533,7 +552,9 @@ __global__ void __launch_bounds__(kRowCtaThreads)
   }
   int slot = 0;
   unsigned parity = 0;
-  float out0 = 0.f, out1 = 0.f;
+  float out0[NB], out1[NB];
+#pragma unroll
+  for (int u = 0; u < NB; ++u) out0[u] = out1[u] = 0.f;
   for (int t = 0; t < n; ++t) {
     const int tl = t & 31;
     if (tl == 0) nxt = batch_ids(t + 32);
@@ -549,20 +570,25 @@ __global__ void __launch_bounds__(kRowCtaThreads)
       break;
     }
     const float4* row4 = reinterpret_cast<const float4*>(ring + (size_t)slot * row_bytes);
-    float acc[Term::kNOut];
+    float acc[NB][Term::kNOut];
 #pragma unroll
-    for (int o = 0; o < Term::kNOut; ++o) acc[o] = 0.f;
+    for (int u = 0; u < NB; ++u)
+#pragma unroll
+      for (int o = 0; o < Term::kNOut; ++o) acc[u][o] = 0.f;
 #pragma unroll
     for (int j = 0; j < NCH; ++j) {
       const int d4 = lane + 32 * j;
       if (d4 < dim4) {
         const float4 e0 = row4[d4];
         const float4 e1 = Term::kMul == 2 ? row4[dim4 + d4] : e0;
-        fwd4<Term>(e0, e1, q0[j], q1[j], acc);
+#pragma unroll
+        for (int u = 0; u < NB; ++u) fwd4<Term>(e0, e1, q0[u][j], q1[u][j], acc[u]);
       }
     }
 #pragma unroll
-    for (int o = 0; o < Term::kNOut; ++o) acc[o] = warp_sum(acc[o]);
+    for (int u = 0; u < NB; ++u)
+#pragma unroll
+      for (int o = 0; o < Term::kNOut; ++o) acc[u][o] = warp_sum(acc[u][o]);
     // the sums above consumed every lane's reads of the slot: it may be refilled
     __syncwarp();
     const int tn = t + stages;
@@ -574,19 +600,26 @@ __global__ void __launch_bounds__(kRowCtaThreads)
       }
     }
     if (lane == tl) {
-      out0 = acc[0];
-      out1 = acc[Term::kNOut - 1];
+#pragma unroll
+      for (int u = 0; u < NB; ++u) {
+        out0[u] = acc[u][0];
+        out1[u] = acc[u][Term::kNOut - 1];
+      }
     }
     if (tl == 31 || t == n - 1) {
       if (lane <= tl) {
         const size_t o = pos0 + (t - tl) + lane;
         if (a.positions != nullptr) {          // straight into the requesting rank's result arrays
-          const int rank = b / a.seg_per_rank, at = a.positions[o];
-          a.out_ptrs[0][rank][at] = cur < 0 ? NAN : out0;
-          if (Term::kNOut == 2) a.out_ptrs[1][rank][at] = cur < 0 ? NAN : out1;
-        } else {
-          dst0[o] = cur < 0 ? NAN : out0;
-          if (Term::kNOut == 2) dst1[o] = cur < 0 ? NAN : out1;
+          const int rank = b / a.seg_per_rank;
+          const size_t at = (size_t)a.positions[o];
+#pragma unroll
+          for (int u = 0; u < NB; ++u) {
+            a.out_ptrs[0][rank][at + (size_t)u * a.branch_stride] = cur < 0 ? NAN : out0[u];
+            if (Term::kNOut == 2) a.out_ptrs[1][rank][at + (size_t)u * a.branch_stride] = cur < 0 ? NAN : out1[u];
+          }
+        } else {                                // (local result arrays: one branch)
+          dst0[o] = cur < 0 ? NAN : out0[0];
+          if (Term::kNOut == 2) dst1[o] = cur < 0 ? NAN : out1[0];
         }
       }
       cur = nxt;
@@ -823,11 +856,12 @@ __global__ void __launch_bounds__(kRowCtaThreads, 2)
   const unsigned row_bytes = (unsigned)dim4 * Term::kMul * 16u;
   const unsigned stage_bytes = 2u * row_bytes;          // [parameter row | first-moment row]
   const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  const size_t q_off = query_offset<NB>(a, b);
   if (rb.r_end <= rb.r_begin) {
     // (ragged form: a query without rows here) its query gradient is zero
     for (int i = threadIdx.x; i < NB * dim4; i += kRowCtaThreads) {
-      reinterpret_cast<float4*>(ga.g_first + (size_t)b * NB * a.dim)[i] = z4;
-      if (Term::kNQ == 2) reinterpret_cast<float4*>(ga.g_second + (size_t)b * NB * a.dim)[i] = z4;
+      reinterpret_cast<float4*>(ga.g_first + q_off)[i] = z4;
+      if (Term::kNQ == 2) reinterpret_cast<float4*>(ga.g_second + q_off)[i] = z4;
     }
     return;
   }
@@ -840,8 +874,8 @@ __global__ void __launch_bounds__(kRowCtaThreads, 2)
     bulk::fence_barrier_init();
   }
   {
-    const float4* p0 = reinterpret_cast<const float4*>(a.first + (size_t)b * NB * a.dim);
-    const float4* p1 = reinterpret_cast<const float4*>(a.second + (size_t)b * NB * a.dim);
+    const float4* p0 = reinterpret_cast<const float4*>(a.first + q_off);
+    const float4* p1 = reinterpret_cast<const float4*>(a.second + q_off);
     for (int i = threadIdx.x; i < NB * dim4; i += kRowCtaThreads) {
       sq[i] = __ldg(p0 + i);
       if (Term::kNQ == 2) sq[NB * dim4 + i] = __ldg(p1 + i);
@@ -896,10 +930,11 @@ __global__ void __launch_bounds__(kRowCtaThreads, 2)
         if (m.single) m.v = ua.v[m.src];
 #pragma unroll
         for (int u = 0; u < NB; ++u) {
-          if (a.positions != nullptr) {        // from the requesting rank's arrays (ragged form: one branch)
-            const int rank = b / a.seg_per_rank, at = a.positions[pos];
-            m.g[0] = a.up_ptrs[0][rank][at];
-            if (Term::kNOut == 2) m.g[Term::kNOut - 1] = a.up_ptrs[1][rank][at];
+          if (a.positions != nullptr) {        // from the requesting rank's arrays ([query][branch][row])
+            const int rank = b / a.seg_per_rank;
+            const size_t at = (size_t)a.positions[pos] + (size_t)u * a.branch_stride;
+            m.g[u * Term::kNOut] = a.up_ptrs[0][rank][at];
+            if (Term::kNOut == 2) m.g[u * Term::kNOut + Term::kNOut - 1] = a.up_ptrs[1][rank][at];
             continue;
           }
           // (ragged form with local arrays: upstream gradients sit at the rows' compact positions)
@@ -1058,7 +1093,7 @@ __global__ void __launch_bounds__(kRowCtaThreads, 2)
     const size_t u = i / ((size_t)Term::kNQ * dim4), rem = i - u * Term::kNQ * dim4;
     const bool second = rem >= (size_t)dim4;
     float* base = second ? ga.g_second : ga.g_first;
-    float4* out = reinterpret_cast<float4*>(base + ((size_t)b * NB + u) * a.dim) + (rem - (second ? dim4 : 0));
+    float4* out = reinterpret_cast<float4*>(base + q_off + u * a.dim) + (rem - (second ? dim4 : 0));
     if (ga.query_atomic) atomicAdd(out, acc);
     else *out = acc;
   }
@@ -1467,8 +1502,6 @@ static int launch_backward_bulk(const Shape& s, RowArgs a, RowGradArgs ga, int n
   return 1;
 }
 
-constexpr int kUnionBranches = 2;
-
 // Launches row_backward_adam_bulk_kernel when the shape suits it.  Returns 1 when launched, 0 when the
 // caller should use the ordinary backward + update, a negative status on failure.
 template <class Term, int NB>
@@ -1536,6 +1569,7 @@ static int ragged_nch(size_t dim, size_t mul) {
 struct RaggedPeers {        // where results go / upstream gradients come from (see RowArgs)
   const int32_t* positions;
   size_t seg_per_rank;
+  size_t branch_stride;
   float* const* out0;
   float* const* out1;
   const float* const* up0;
@@ -1545,14 +1579,15 @@ struct RaggedPeers {        // where results go / upstream gradients come from (
 static void set_peers(RowArgs& a, const RaggedPeers& pr) {
   a.positions = pr.positions;
   a.seg_per_rank = (int)std::max<size_t>(pr.seg_per_rank, 1);
+  a.branch_stride = (int)pr.branch_stride;
   a.out_ptrs[0] = pr.out0; a.out_ptrs[1] = pr.out1;
   a.up_ptrs[0] = pr.up0; a.up_ptrs[1] = pr.up1;
 }
 
 template <class Term>
-static int launch_forward_ragged(size_t n_seg, size_t dim, size_t n_rows, const float* table, const int64_t* rows,
-                                 const float* first, const float* second, const int2* seg, float* out0, float* out1,
-                                 const RaggedPeers& pr, cudaStream_t st) {
+static int launch_forward_ragged(size_t branches, size_t n_seg, size_t dim, size_t n_rows, const float* table,
+                                 const int64_t* rows, const float* first, const float* second, const int2* seg,
+                                 float* out0, float* out1, const RaggedPeers& pr, cudaStream_t st) {
   if (Term::kNQ == 1) second = first;
   const int nch = ragged_nch(dim, Term::kMul);
   if (!nch || !aligned16(table) || !aligned16(first) || !aligned16(second)) return 0;
@@ -1562,7 +1597,9 @@ static int launch_forward_ragged(size_t n_seg, size_t dim, size_t n_rows, const 
   if (smem > 110 * 1024) return 0;
   RowArgs a{table, rows, first, second, 0, (int)dim, 0, 1, 0, (long long)n_rows, seg};
   set_peers(a, pr);
-  auto kern = nch == 4 ? row_forward_bulk_kernel<Term, 4> : row_forward_bulk_kernel<Term, 8>;
+  auto kern = branches == 1 ? (nch == 4 ? row_forward_bulk_kernel<Term, 1, 4> : row_forward_bulk_kernel<Term, 1, 8>)
+                            : (nch == 4 ? row_forward_bulk_kernel<Term, kUnionBranches, 4>
+                                        : row_forward_bulk_kernel<Term, kUnionBranches, 8>);
   if (int rc = allow_large_smem(kern, 110 * 1024)) return rc;
   kern<<<(unsigned)n_seg, kRowCtaThreads, smem, st>>>(a, out0, out1, stages);
   if (int rc = check_launch("row_forward_bulk_kernel")) return rc;
@@ -1570,7 +1607,7 @@ static int launch_forward_ragged(size_t n_seg, size_t dim, size_t n_rows, const 
 }
 
 template <class Term>
-static int launch_backward_adam_ragged(size_t n_seg, size_t dim, size_t n_rows, const float* gout0, const float* gout1,
+static int launch_backward_adam_ragged(size_t branches, size_t n_seg, size_t dim, size_t n_rows, const float* gout0, const float* gout1,
                                        float* table, const int64_t* rows, const float* first, const float* second,
                                        const int2* seg, const int32_t* slot, const int32_t* slot_count, float* g_rows,
                                        float* g_first, float* g_second, const UpdateArgs& ua, int64_t* uniq,
@@ -1587,7 +1624,8 @@ static int launch_backward_adam_ragged(size_t n_seg, size_t dim, size_t n_rows, 
   RowArgs a{table, rows, first, second, 0, (int)dim, 0, 1, 0, (long long)n_rows, seg};
   set_peers(a, pr);
   RowGradArgs ga{gout0, gout1, nullptr, slot, slot_count, g_rows, g_first, g_second, 0};
-  return launch_backward_adam<Term, 1>(s, a, ga, ua, uniq, nch, st);
+  if (branches == 1) return launch_backward_adam<Term, 1>(s, a, ga, ua, uniq, nch, st);
+  return launch_backward_adam<Term, kUnionBranches>(s, a, ga, ua, uniq, nch, st);
 }
 
 template <class Term>
@@ -1614,7 +1652,7 @@ static int launch_forward(const Shape& s, const float* ent, const int64_t* idx, 
       RowArgs ab = a;
       ab.rows_per_cta = (int)std::min<size_t>(s.num, 512);
       ab.chunks = (int)((s.num + ab.rows_per_cta - 1) / ab.rows_per_cta);
-      auto kern = p.nch == 4 ? row_forward_bulk_kernel<Term, 4> : row_forward_bulk_kernel<Term, 8>;
+      auto kern = p.nch == 4 ? row_forward_bulk_kernel<Term, 1, 4> : row_forward_bulk_kernel<Term, 1, 8>;
       if (int rc = allow_large_smem(kern, 110 * 1024)) return rc;
       kern<<<(unsigned)(s.bsize * ab.chunks), kRowCtaThreads, bulk_smem, st>>>(ab, dst0, dst1, stages);
       return check_launch("row_forward_bulk_kernel");
@@ -2022,7 +2060,7 @@ int smore_rows_forward_ragged(int dist_id, const float* table, const int64_t* ro
                               const float* first, const float* second, const int32_t* segments, size_t n_segments,
                               size_t dim, float* out0, float* out1, const int32_t* positions,
                               size_t segments_per_rank, float* const* out0_ptrs, float* const* out1_ptrs,
-                              void* stream) {
+                              size_t branches, size_t branch_stride, void* stream) {
   const bool both = dist_id == SMORE_DIST_BOX_BOTH;
   if (!both && (dist_id < 0 || dist_id >= SMORE_DIST_COUNT))
     return fail(SMORE_ERR_BAD_DIST, "unknown distance id %d", dist_id);
@@ -2030,19 +2068,22 @@ int smore_rows_forward_ragged(int dist_id, const float* table, const int64_t* ro
     return fail(SMORE_ERR_NULL, "rows_forward_ragged: required pointer is NULL");
   if (positions ? (!out0_ptrs || (both && !out1_ptrs) || segments_per_rank == 0) : (!out0 || (both && !out1)))
     return fail(SMORE_ERR_NULL, "rows_forward_ragged: pass local result arrays, or positions with per-rank pointers");
-  const RaggedPeers pr{positions, segments_per_rank, out0_ptrs, both ? out1_ptrs : out0_ptrs, nullptr, nullptr};
+  if (branches != 1 && (branches != (size_t)kUnionBranches || !positions))
+    return fail(SMORE_ERR_BAD_SHAPE, "rows_forward_ragged: 1 branch, or %d with per-rank result arrays", kUnionBranches);
+  const RaggedPeers pr{positions, segments_per_rank, branch_stride, out0_ptrs, both ? out1_ptrs : out0_ptrs, nullptr,
+                       nullptr};
   if (n_segments == 0) return SMORE_OK;
   if (n_segments > (size_t)INT_MAX || dim == 0) return fail(SMORE_ERR_BAD_SHAPE, "rows_forward_ragged: bad sizes");
   cudaStream_t st = (cudaStream_t)stream;
   const int2* seg = reinterpret_cast<const int2*>(segments);
   int rc = 0;
   if (both) {
-    rc = launch_forward_ragged<TermBoxBoth>(n_segments, dim, n_table_rows, table, rows, first, second, seg, out0, out1, pr, st);
+    rc = launch_forward_ragged<TermBoxBoth>(branches, n_segments, dim, n_table_rows, table, rows, first, second, seg, out0, out1, pr, st);
   } else {
     switch (dist_id) {
 #define RAGGED_CASE(ID, TERM)                                                                                          \
   case ID:                                                                                                             \
-    rc = launch_forward_ragged<TERM>(n_segments, dim, n_table_rows, table, rows, first, second, seg, out0, out0, pr, st); \
+    rc = launch_forward_ragged<TERM>(branches, n_segments, dim, n_table_rows, table, rows, first, second, seg, out0, out0, pr, st); \
     break;
       RAGGED_CASE(SMORE_DIST_BOX_OUT, TermBoxOut)
       RAGGED_CASE(SMORE_DIST_BOX_IN, TermBoxIn)
@@ -2069,7 +2110,8 @@ int smore_rows_backward_fused_adam_ragged(int dist_id, const float* gout0, const
                                           double beta1, double beta2, double eps, int64_t step,
                                           const float* step_scalars, const int32_t* positions,
                                           size_t segments_per_rank, const float* const* gout0_ptrs,
-                                          const float* const* gout1_ptrs, void* stream) {
+                                          const float* const* gout1_ptrs, size_t branches, size_t branch_stride,
+                                          void* stream) {
   const bool both = dist_id == SMORE_DIST_BOX_BOTH;
   if (!both && (dist_id < 0 || dist_id >= SMORE_DIST_COUNT))
     return fail(SMORE_ERR_BAD_DIST, "unknown distance id %d", dist_id);
@@ -2080,7 +2122,11 @@ int smore_rows_backward_fused_adam_ragged(int dist_id, const float* gout0, const
   if (positions ? (!gout0_ptrs || (both && !gout1_ptrs) || segments_per_rank == 0) : (!gout0 || (both && !gout1)))
     return fail(SMORE_ERR_NULL, "rows_backward_fused_adam_ragged: pass local upstream gradients, or positions with "
                                 "per-rank pointers");
-  const RaggedPeers pr{positions, segments_per_rank, nullptr, nullptr, gout0_ptrs, both ? gout1_ptrs : gout0_ptrs};
+  if (branches != 1 && (branches != (size_t)kUnionBranches || !positions))
+    return fail(SMORE_ERR_BAD_SHAPE, "rows_backward_fused_adam_ragged: 1 branch, or %d with per-rank upstream arrays",
+                kUnionBranches);
+  const RaggedPeers pr{positions, segments_per_rank, branch_stride, nullptr, nullptr, gout0_ptrs,
+                       both ? gout1_ptrs : gout0_ptrs};
   if (!step_scalars && step < 1) return fail(SMORE_ERR_BAD_SHAPE, "adam step must be >= 1");
   if (n_segments == 0) return SMORE_OK;
   if (n_segments > (size_t)INT_MAX || dim == 0) return fail(SMORE_ERR_BAD_SHAPE, "rows_backward_fused_adam_ragged: bad sizes");
@@ -2094,13 +2140,13 @@ int smore_rows_backward_fused_adam_ragged(int dist_id, const float* gout0, const
   const int2* seg = reinterpret_cast<const int2*>(segments);
   int rc = 0;
   if (both) {
-    rc = launch_backward_adam_ragged<TermBoxBoth>(n_segments, dim, n_table_rows, gout0, gout1, table, rows, first, second,
+    rc = launch_backward_adam_ragged<TermBoxBoth>(branches, n_segments, dim, n_table_rows, gout0, gout1, table, rows, first, second,
                                                   seg, slot, slot_count, g_rows, g_first, g_second, ua, uniq, pr, st);
   } else {
     switch (dist_id) {
 #define RAGGED_CASE(ID, TERM)                                                                                      \
   case ID:                                                                                                         \
-    rc = launch_backward_adam_ragged<TERM>(n_segments, dim, n_table_rows, gout0, gout0, table, rows, first, second, \
+    rc = launch_backward_adam_ragged<TERM>(branches, n_segments, dim, n_table_rows, gout0, gout0, table, rows, first, second, \
                                            seg, slot, slot_count, g_rows, g_first, g_second, ua, uniq, pr, st);    \
     break;
       RAGGED_CASE(SMORE_DIST_BOX_OUT, TermBoxOut)

@@ -656,12 +656,17 @@ __global__ void __launch_bounds__(kRingWarps * 32, 2)
 
 constexpr int kSelectThreads = 256;
 
-__device__ __forceinline__ bool owner_desc(const int32_t* desc, int max_queries, long long pairs_cap, int* nq, int* K) {
-  const int q = desc[0], k = desc[1];
+// A rank's descriptor {n_queries, K, branches}: checked against what the buffers were sized for and
+// against the (K, branches) this owner's kernels were launched for; a rank that does not fit is left
+// out (its scores read NaN) and the capacity bit is set.
+__device__ __forceinline__ bool owner_desc(const int32_t* desc, int max_queries, long long pairs_cap, int want_k,
+                                           int want_branches, int* nq, int* K) {
+  const int q = desc[0], k = desc[1], br = desc[2];
   *nq = min(max(q, 0), max_queries);
   *K = max(k, 0);
-  if (q < 0 || q > max_queries || k < 0 || (long long)q * k > pairs_cap) {   // not what the buffers were sized for
-    atomicOr(&g_peer_async_status, kStatusCapacity);
+  if (q < 0 || k < 0 || br != want_branches || k != want_k || (long long)q * br > max_queries ||
+      (long long)q * br * k > pairs_cap) {
+    if (q != 0 || k != 0) atomicOr(&g_peer_async_status, kStatusCapacity);   // (all zero: the rank published nothing)
     *nq = 0;
     return false;
   }
@@ -670,15 +675,16 @@ __device__ __forceinline__ bool owner_desc(const int32_t* desc, int max_queries,
 
 __global__ void __launch_bounds__(kSelectThreads)
     owner_select_pairs_kernel(const int64_t* const* __restrict__ pair_id_ptrs, const int32_t* const* __restrict__ desc_ptrs,
-                              int max_queries, long long pairs_cap, int64_t base, int64_t shard_rows, int capacity,
-                              int64_t* __restrict__ rows, int32_t* __restrict__ positions, int2* __restrict__ segments,
+                              int max_queries, long long pairs_cap, int want_k, int branches, int64_t base,
+                              int64_t shard_rows, int capacity, int64_t* __restrict__ rows,
+                              int32_t* __restrict__ positions, int2* __restrict__ segments,
                               int32_t* __restrict__ n_selected) {
   __shared__ int s_warp[kSelectThreads / 32];
   __shared__ int s_pos0;
   const int r = blockIdx.y, b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int seg = r * max_queries + b;
   int nq, K;
-  owner_desc(desc_ptrs[r], max_queries, pairs_cap, &nq, &K);
+  owner_desc(desc_ptrs[r], max_queries, pairs_cap, want_k, branches, &nq, &K);
   if (b >= nq || K == 0) {
     if (tid == 0) segments[seg] = make_int2(0, 0);
     return;
@@ -736,7 +742,7 @@ __global__ void __launch_bounds__(kSelectThreads)
     if (mine) {
       const int p = running + before + __popc(ballot & ((1u << lane) - 1u));
       rows[p] = id;
-      positions[p] = b * K + k0 + tid;
+      positions[p] = b * branches * K + k0 + tid;
     }
     running += chunk;
   }
@@ -757,7 +763,7 @@ __global__ void __launch_bounds__(kSelectThreads)
     if (mine) {
       const int p = running + before + __popc(ballot & ((1u << lane) - 1u));
       rows[p] = id;
-      positions[p] = b * K + k;
+      positions[p] = b * branches * K + k;
     }
     running += chunk;
   }
@@ -766,11 +772,12 @@ __global__ void __launch_bounds__(kSelectThreads)
 __global__ void __launch_bounds__(256)
     owner_gather_queries_kernel(const float* const* __restrict__ first_ptrs, const float* const* __restrict__ second_ptrs,
                                 const int32_t* const* __restrict__ desc_ptrs, int max_queries, long long pairs_cap,
-                                int dim4, float4* __restrict__ first_all, float4* __restrict__ second_all) {
+                                int want_k, int branches, int dim4, float4* __restrict__ first_all,
+                                float4* __restrict__ second_all) {
   const int r = blockIdx.y;
   int nq, K;
-  if (!owner_desc(desc_ptrs[r], max_queries, pairs_cap, &nq, &K)) return;
-  const size_t total = (size_t)nq * dim4, base = (size_t)r * max_queries * dim4;
+  if (!owner_desc(desc_ptrs[r], max_queries, pairs_cap, want_k, branches, &nq, &K)) return;
+  const size_t total = (size_t)nq * branches * dim4, base = (size_t)r * max_queries * dim4;
   const float4* f = reinterpret_cast<const float4*>(first_ptrs[r]);
   const float4* s = second_all != nullptr ? reinterpret_cast<const float4*>(second_ptrs[r]) : nullptr;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -1023,28 +1030,31 @@ static int check_owner_sizes(const char* what, size_t n_ranks, size_t max_querie
 }
 
 int smore_owner_select_pairs(const int64_t* const* pair_id_ptrs, const int32_t* const* desc_ptrs, size_t n_ranks,
-                             size_t max_queries, size_t pairs_capacity, int64_t base, size_t shard_rows,
-                             size_t capacity, int64_t* rows, int32_t* positions, int32_t* segments,
-                             int32_t* n_selected, void* stream) {
+                             size_t max_queries, size_t pairs_capacity, size_t rows_per_query, size_t branches,
+                             int64_t base, size_t shard_rows, size_t capacity, int64_t* rows, int32_t* positions,
+                             int32_t* segments, int32_t* n_selected, void* stream) {
   if (!pair_id_ptrs || !desc_ptrs || !rows || !positions || !segments || !n_selected)
     return fail(SMORE_ERR_NULL, "owner_select_pairs: NULL pointer");
   if (int rc = check_owner_sizes("owner_select_pairs", n_ranks, max_queries)) return rc;
-  if (capacity > (size_t)INT_MAX || pairs_capacity > (size_t)INT_MAX || shard_rows == 0)
-    return fail(SMORE_ERR_BAD_SHAPE, "owner_select_pairs: capacities must fit 31 bits, shard_rows > 0");
+  if (capacity > (size_t)INT_MAX || pairs_capacity > (size_t)INT_MAX || shard_rows == 0 || branches == 0 ||
+      branches > 2 || rows_per_query > (size_t)INT_MAX)
+    return fail(SMORE_ERR_BAD_SHAPE, "owner_select_pairs: capacities must fit 31 bits, shard_rows > 0, 1 or 2 branches");
   cudaStream_t st = (cudaStream_t)stream;
   if (cudaMemsetAsync(n_selected, 0, 2 * sizeof(int32_t), st) != cudaSuccess)
     return fail(SMORE_ERR_CUDA, "owner_select_pairs: cudaMemsetAsync failed");
   dim3 grid((unsigned)max_queries, (unsigned)n_ranks);
   owner_select_pairs_kernel<<<grid, kSelectThreads, 0, st>>>(pair_id_ptrs, desc_ptrs, (int)max_queries,
-                                                             (long long)pairs_capacity, base, (int64_t)shard_rows,
-                                                             (int)capacity, rows, positions,
-                                                             reinterpret_cast<int2*>(segments), n_selected);
+                                                             (long long)pairs_capacity, (int)rows_per_query,
+                                                             (int)branches, base, (int64_t)shard_rows, (int)capacity,
+                                                             rows, positions, reinterpret_cast<int2*>(segments),
+                                                             n_selected);
   return check_launch("owner_select_pairs_kernel");
 }
 
 int smore_owner_gather_queries(const float* const* first_ptrs, const float* const* second_ptrs,
                                const int32_t* const* desc_ptrs, size_t n_ranks, size_t max_queries,
-                               size_t pairs_capacity, size_t dim, float* first_all, float* second_all, void* stream) {
+                               size_t pairs_capacity, size_t rows_per_query, size_t branches, size_t dim,
+                               float* first_all, float* second_all, void* stream) {
   if (!first_ptrs || !desc_ptrs || !first_all || (second_all && !second_ptrs))
     return fail(SMORE_ERR_NULL, "owner_gather_queries: NULL pointer");
   if (int rc = check_owner_sizes("owner_gather_queries", n_ranks, max_queries)) return rc;
@@ -1052,8 +1062,8 @@ int smore_owner_gather_queries(const float* const* first_ptrs, const float* cons
     return fail(SMORE_ERR_BAD_SHAPE, "owner_gather_queries: dim must be a multiple of 4, buffers 16-byte aligned");
   dim3 grid((unsigned)std::min<size_t>((max_queries * (dim >> 2) + 255) / 256, (size_t)sm_count() * 4), (unsigned)n_ranks);
   owner_gather_queries_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
-      first_ptrs, second_ptrs, desc_ptrs, (int)max_queries, (long long)pairs_capacity, (int)(dim >> 2),
-      reinterpret_cast<float4*>(first_all), reinterpret_cast<float4*>(second_all));
+      first_ptrs, second_ptrs, desc_ptrs, (int)max_queries, (long long)pairs_capacity, (int)rows_per_query,
+      (int)branches, (int)(dim >> 2), reinterpret_cast<float4*>(first_all), reinterpret_cast<float4*>(second_all));
   return check_launch("owner_gather_queries_kernel");
 }
 

@@ -766,46 +766,48 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
 
     def remote_dist(self, name, rows, first, second):
         """name: a distance of ext_ops ("box_both" included) between `rows` (a RemoteRows handle viewed
-        as [B, K, width]) and query operands [B, 1, dim] or, for union queries, [B, U, 1, dim].  Every
-        rank of the shard group must make this call in the same steps, with the same distance."""
+        as [B, K, width]) and query operands [B, 1, dim] or, for union queries, [B, 2, 1, dim].  Every
+        rank of the shard group must make this call in the same steps, with the same distance, the
+        same K and the same number of branches."""
         B, K, width = rows.as_3d()
         if self._r_op is None or self._r_op["lookup"] is not rows.lookup or self._r_op["stage"] != "ids":
             raise _lib.SmoreError("a remotely scored lookup takes exactly one distance op per step")
         if first.dim() == 4:
-            if first.shape[0] != B or first.shape[2] != 1:
-                raise ValueError("%s: union operands must be [B, U, 1, dim]" % name)
-            U = first.shape[1]
-            n_queries, out_shape = B * U, (B, U, K)
-            if n_queries * K > self.shard.remote.pairs:
-                raise _lib.SmoreError("%d pairs, the remote block holds %d (RemoteSpec.pairs)"
-                                      % (n_queries * K, self.shard.remote.pairs))
-            # every branch is a query of its own over the same candidates
-            ids = self._r_op["lookup"].idx.view(B, 1, K).expand(B, U, K)
-            self.shard.r_ids[:n_queries * K].view(B, U, K).copy_(ids)
+            if first.shape[0] != B or first.shape[2] != 1 or first.shape[1] not in (1, 2):
+                raise ValueError("%s: union operands must be [B, U, 1, dim] with U = 1 or 2" % name)
+            branches = first.shape[1]          # every branch is scored against the query's candidates
+            out_shape = (B, branches, K)
         elif first.dim() == 3 and first.shape[0] == B and first.shape[1] == 1:
-            n_queries, out_shape = B, (B, K)
+            branches, out_shape = 1, (B, K)
         else:
             raise ValueError("%s: remotely scored rows take one candidate list per query" % name)
+        n_queries = B
+        if n_queries * branches * K > self.shard.remote.pairs:
+            raise _lib.SmoreError("%d scores, the remote block holds %d (RemoteSpec.pairs)"
+                                  % (n_queries * branches * K, self.shard.remote.pairs))
         dim = first.shape[-1]
-        if dim != self.shard.remote.dim or n_queries > self.shard.remote.queries:
+        if dim != self.shard.remote.dim or n_queries * branches > self.shard.remote.queries:
             raise _lib.SmoreError("queries [%d, %d] do not fit the remote block (RemoteSpec queries=%d, dim=%d)"
-                                  % (n_queries, dim, self.shard.remote.queries, self.shard.remote.dim))
-        flat = lambda t: None if t is None else t.reshape(n_queries, dim).contiguous()
+                                  % (n_queries * branches, dim, self.shard.remote.queries, self.shard.remote.dim))
+        flat = lambda t: None if t is None else t.reshape(n_queries * branches, dim).contiguous()
         return _RemoteDistFunc.apply(self, name, self.dummy_tensor, flat(first), flat(second), n_queries, K, out_shape)
 
     def remote_publish(self, name, first, second, n_queries, per_query):
+        """first / second: [n_queries * branches, dim] (the branches of a query next to each other)."""
         sh, op = self.shard, self._r_op
+        branches = first.shape[0] // n_queries
         op.update(name=name, dist_id=_lib.BOX_BOTH_ID if name == "box_both" else _lib.DIST_IDS[name],
                   n_out=2 if name == "box_both" else 1, two=second is not None, nq=n_queries, K=per_query,
-                  dim=first.shape[1], stage="published")
+                  branches=branches, dim=first.shape[1], stage="published")
         sh.r_desc[0].fill_(n_queries)
         sh.r_desc[1].fill_(per_query)
-        n = n_queries * op["dim"]
+        sh.r_desc[2].fill_(branches)
+        n = n_queries * branches * op["dim"]
         sh.r_queries[0][:n].copy_(first.reshape(-1))
         if second is not None:
             sh.r_queries[1][:n].copy_(second.reshape(-1))
         for i in range(op["n_out"]):        # a pair no owner claims (an id outside the table) reads NaN
-            sh.r_results[i][:n_queries * per_query].fill_(float("nan"))
+            sh.r_results[i][:n_queries * branches * per_query].fill_(float("nan"))
 
     def remote_owner_forward(self):
         sh, spec, op = self.shard, self.shard.remote, self._r_op
@@ -816,14 +818,16 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         second_all = self._r_queries[1] if op["two"] else None
         with torch.cuda.device(dev):
             with _lib.timed("owner_select"):
-                _lib.check(L.smore_owner_select_pairs(sh.d_r_ids.data_ptr(), sh.d_r_desc.data_ptr(), G, Q, P, sh.base,
-                                                      max(sh.S, 1), self._r_cap, self._r_rows.data_ptr(),
+                _lib.check(L.smore_owner_select_pairs(sh.d_r_ids.data_ptr(), sh.d_r_desc.data_ptr(), G, Q, P, op["K"],
+                                                      op["branches"], sh.base, max(sh.S, 1), self._r_cap,
+                                                      self._r_rows.data_ptr(),
                                                       self._r_pos.data_ptr(), self._r_seg.data_ptr(),
                                                       self._r_nsel.data_ptr(), st), "smore_owner_select_pairs")
                 _lib.check(L.smore_owner_gather_queries(sh.d_r_queries[0].data_ptr(),
                                                         sh.d_r_queries[1].data_ptr() if op["two"] else None,
-                                                        sh.d_r_desc.data_ptr(), G, Q, P, op["dim"],
-                                                        self._r_queries[0].data_ptr(), ptr(second_all), st),
+                                                        sh.d_r_desc.data_ptr(), G, Q, P, op["K"], op["branches"],
+                                                        op["dim"], self._r_queries[0].data_ptr(), ptr(second_all),
+                                                        st),
                            "smore_owner_gather_queries")
             with _lib.timed("owner_forward"):
                 # every result goes straight to its position in the requesting rank's result arrays
@@ -831,21 +835,24 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
                                                        max(sh.S, 1), self._r_queries[0].data_ptr(), ptr(second_all),
                                                        self._r_seg.data_ptr(), G * Q, op["dim"], None, None,
                                                        self._r_pos.data_ptr(), Q, sh.d_r_results[0].data_ptr(),
-                                                       sh.d_r_results[1].data_ptr() if op["n_out"] == 2 else None, st),
+                                                       sh.d_r_results[1].data_ptr() if op["n_out"] == 2 else None,
+                                                       op["branches"], op["K"], st),
                            "smore_rows_forward_ragged")
         op["stage"] = "scored"
 
     def remote_collect_forward(self, out_shape):
-        op, n = self._r_op, self._r_op["nq"] * self._r_op["K"]
+        op = self._r_op
+        n = op["nq"] * op["branches"] * op["K"]
         return tuple(self.shard.r_results[i][:n].view(out_shape).clone() for i in range(op["n_out"]))
 
     def remote_publish_upstream(self, gouts):
-        op, n = self._r_op, self._r_op["nq"] * self._r_op["K"]
+        op = self._r_op
         if op is None or op["stage"] != "scored":
             raise _lib.SmoreError("backward of a remotely scored lookup without its forward in this step")
         if self._fused_lr is None:
             raise _lib.SmoreError("call announce_lr(lr) before the backward pass: the owners of remotely scored rows "
                                   "update them inside it")
+        n = op["nq"] * op["branches"] * op["K"]
         for i in range(op["n_out"]):
             self.shard.r_upstream[i][:n].copy_(gouts[i].reshape(-1))
 
@@ -887,8 +894,8 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
                     sh.r_partial[1].data_ptr() if op["two"] else None, op["dim"], sh.m.data_ptr(), sh.v.data_ptr(),
                     self._r_uniq.data_ptr(), self._fused_lr, 0.9, 0.999, eps, 1 if dev_step else int(self.step) + 1,
                     self._step_scalars.data_ptr() if dev_step else None, self._r_pos.data_ptr(), Q,
-                    sh.d_r_upstream[0].data_ptr(), sh.d_r_upstream[1].data_ptr() if op["n_out"] == 2 else None, st),
-                    "smore_rows_backward_fused_adam_ragged")
+                    sh.d_r_upstream[0].data_ptr(), sh.d_r_upstream[1].data_ptr() if op["n_out"] == 2 else None,
+                    op["branches"], op["K"], st), "smore_rows_backward_fused_adam_ragged")
         op["stage"] = "differentiated"
 
     def remote_collect_backward(self):
@@ -897,9 +904,10 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         outs = []
         with torch.cuda.device(dev), _lib.timed("owner_sum_query_grads"):
             for i in range(2 if op["two"] else 1):
-                g = torch.empty(op["nq"], op["dim"], dtype=torch.float32, device=dev)
+                g = torch.empty(op["nq"] * op["branches"], op["dim"], dtype=torch.float32, device=dev)
                 _lib.check(L.smore_owner_sum_query_grads(sh.d_r_partial[i].data_ptr(), sh.world, sh.rank, spec.queries,
-                                                         op["nq"], op["dim"], g.data_ptr(), _stream_ptr(dev)),
+                                                         op["nq"] * op["branches"], op["dim"], g.data_ptr(),
+                                                         _stream_ptr(dev)),
                            "smore_owner_sum_query_grads")
                 outs.append(g)
         return outs[0], outs[1] if op["two"] else None
