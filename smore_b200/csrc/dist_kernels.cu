@@ -858,10 +858,15 @@ __global__ void __launch_bounds__(kRowCtaThreads, 2)
   const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
   const size_t q_off = query_offset<NB>(a, b);
   if (rb.r_end <= rb.r_begin) {
-    // (ragged form: a query without rows here) its query gradient is zero
-    for (int i = threadIdx.x; i < NB * dim4; i += kRowCtaThreads) {
-      reinterpret_cast<float4*>(ga.g_first + q_off)[i] = z4;
-      if (Term::kNQ == 2) reinterpret_cast<float4*>(ga.g_second + q_off)[i] = z4;
+    // (ragged form: a query without rows here) its query gradient is zero.  A rank has room for
+    // seg_per_rank / NB queries of NB rows: the segment slots beyond that are never used and own no
+    // part of the query-gradient array (their offset would fall into the next rank's part).
+    const bool has_slot = a.seg == nullptr || ((b % a.seg_per_rank) + 1) * NB <= a.seg_per_rank;
+    if (has_slot) {
+      for (int i = threadIdx.x; i < NB * dim4; i += kRowCtaThreads) {
+        reinterpret_cast<float4*>(ga.g_first + q_off)[i] = z4;
+        if (Term::kNQ == 2) reinterpret_cast<float4*>(ga.g_second + q_off)[i] = z4;
+      }
     }
     return;
   }

@@ -21,18 +21,20 @@ pytestmark = pytest.mark.gpu
 D = 320        # rows of 1280 bytes: the narrowest the ragged row-stream kernels take
 
 
-def _batch(rank, step, n_total, B, K):
+def _batch(rank, step, n_total, B, K, U=1):
+    """U = 2: union queries, two branches per query ([B, U, 1, D] operands, [B, U, K] results)."""
     g = torch.Generator().manual_seed(77 * step + rank)
     neg = torch.randint(0, n_total, (B, K), generator=g)
     pos = torch.randint(0, n_total, (B,), generator=g)
     neg[1, :K // 2] = neg[0, :K // 2]                   # rows shared between queries of one rank
     if rank > 0:
-        neg[0, :K // 4] = _batch(0, step, n_total, B, K)[0][0, :K // 4]     # and between ranks
+        neg[0, :K // 4] = _batch(0, step, n_total, B, K, U)[0][0, :K // 4]  # and between ranks
     pos[0] = neg[2, 3]                                  # a row both scored remotely and looked up
-    center = (torch.rand(B, 1, D, generator=g) - 0.5) * 0.2
-    offset = torch.rand(B, 1, D, generator=g) * 0.05
-    g_out = torch.randn(B, K, generator=g) * 0.1
-    g_in = torch.randn(B, K, generator=g) * 0.1
+    qshape, gshape = ((B, 1, D), (B, K)) if U == 1 else ((B, U, 1, D), (B, U, K))
+    center = (torch.rand(*qshape, generator=g) - 0.5) * 0.2
+    offset = torch.rand(*qshape, generator=g) * 0.05
+    g_out = torch.randn(*gshape, generator=g) * 0.1
+    g_in = torch.randn(*gshape, generator=g) * 0.1
     return neg, pos, center, offset, g_out, g_in
 
 
@@ -48,7 +50,8 @@ def _reference_step(ref_emb, ref_opt, batches, lr, fused):
         neg_rows = ref_emb(neg.view(-1).cuda(), "negative_entity")
         pos_rows = ref_emb(pos.cuda(), "positive_entity")
         d_out, d_in = ext_ops.box_dist_both(neg_rows.view(B, K, -1), c, o)
-        p_out, p_in = ext_ops.box_dist_both(pos_rows.unsqueeze(1), c, o)
+        c1, o1 = (c, o) if c.dim() == 3 else (c[:, 0], o[:, 0])     # the positives meet the first branch
+        p_out, p_in = ext_ops.box_dist_both(pos_rows.unsqueeze(1), c1, o1)
         losses.append((d_out * g_out.cuda()).sum() + (d_in * g_in.cuda()).sum() + (p_out + 0.5 * p_in).sum())
         outs.append([d_out.detach(), d_in.detach(), c, o])
     for loss, out in zip(losses, outs):
@@ -58,14 +61,14 @@ def _reference_step(ref_emb, ref_opt, batches, lr, fused):
     return outs
 
 
-@pytest.mark.parametrize("world", [1, 2, 3])
-def test_emulated_owner_side_scoring_matches_unsharded_optimizer(world):
+@pytest.mark.parametrize("world,U", [(1, 1), (2, 1), (3, 1), (3, 2), (8, 1), (8, 2)])
+def test_emulated_owner_side_scoring_matches_unsharded_optimizer(world, U):
     from smore_b200 import _lib, embedding, ext_ops, sharded
     n_total, B, K = 1501, 6, 40
     caps = (2 * B, B, B)
     torch.manual_seed(0)
     full = (torch.rand(n_total, D) - 0.5) * 0.2
-    spec = sharded.RemoteSpec(pairs=B * K, queries=B, dim=D)
+    spec = sharded.RemoteSpec(pairs=B * U * K, queries=B * U, dim=D)
     shards = sharded.ShardGroup.emulated(world, n_total, D, caps, squeeze=True, remote=spec)
     for s in shards:
         s.table.zero_()
@@ -85,8 +88,9 @@ def test_emulated_owner_side_scoring_matches_unsharded_optimizer(world):
     lr = 1e-2
     _lib.async_status_clear()
     for step in range(3):
-        batches = [_batch(r, step, n_total, B, K) for r in range(world)]
+        batches = [_batch(r, step, n_total, B, K, U) for r in range(world)]
         want = _reference_step(ref_emb, ref_opt, batches, lr, fused=step == 1)
+        out_shape = (B, K) if U == 1 else (B, U, K)
 
         for o_ in opts:
             o_.zero_grad()
@@ -102,17 +106,18 @@ def test_emulated_owner_side_scoring_matches_unsharded_optimizer(world):
         # forward: publish | every owner's share | collect
         for r in range(world):
             c, o = leaves[r]
-            opts[r].remote_publish("box_both", c.detach().view(B, D), o.detach().view(B, D), B, K)
+            opts[r].remote_publish("box_both", c.detach().view(B * U, D), o.detach().view(B * U, D), B, K)
         for o_ in opts:
             o_.remote_owner_forward()
         for r in range(world):
-            d_out, d_in = opts[r].remote_collect_forward((B, K))
+            d_out, d_in = opts[r].remote_collect_forward(out_shape)
             close(d_out.cpu().numpy(), want[r][0].cpu().numpy(), RTOL, what="dist_out rank %d" % r)
             close(d_in.cpu().numpy(), want[r][1].cpu().numpy(), RTOL, what="dist_in rank %d" % r)
         # the ranks' ordinary lookups (positives) take the usual route: rows fetched, gradients in the lists
         for r in range(world):
             c, o = leaves[r]
-            p_out, p_in = ext_ops.box_dist_both(handles[r][0].unsqueeze(1), c, o)
+            c1, o1 = (c, o) if U == 1 else (c[:, 0], o[:, 0])
+            p_out, p_in = ext_ops.box_dist_both(handles[r][0].unsqueeze(1), c1, o1)
             (p_out + 0.5 * p_in).sum().backward()
         # backward: publish upstream gradients | every owner's share | collect
         for r in range(world):
@@ -122,9 +127,9 @@ def test_emulated_owner_side_scoring_matches_unsharded_optimizer(world):
         for r in range(world):
             g_c, g_o = opts[r].remote_collect_backward()
             c, o = leaves[r]
-            close((c.grad.view(B, D) + g_c).cpu().numpy(), want[r][2].view(B, D).cpu().numpy(), RTOL_ATOMIC,
+            close((c.grad.view(B * U, D) + g_c).cpu().numpy(), want[r][2].view(B * U, D).cpu().numpy(), RTOL_ATOMIC,
                   what="center gradient rank %d" % r)
-            close((o.grad.view(B, D) + g_o).cpu().numpy(), want[r][3].view(B, D).cpu().numpy(), RTOL_ATOMIC,
+            close((o.grad.view(B * U, D) + g_o).cpu().numpy(), want[r][3].view(B * U, D).cpu().numpy(), RTOL_ATOMIC,
                   what="offset gradient rank %d" % r)
         for o_ in opts:
             o_.apply_grad(lr)
