@@ -485,7 +485,10 @@ class EmbeddingOptimizer(object):
         if status:
             what = [name for bit, name in ((_lib.STATUS_COPY_WAIT, "a local bulk-copy wait gave up"),
                                            (_lib.STATUS_PEER_WAIT, "a wait on a copy from a peer gave up"),
-                                           (_lib.STATUS_BAD_ROW_ID, "a row id outside the table was looked up"))
+                                           (_lib.STATUS_BAD_ROW_ID, "a row id outside the table was looked up"),
+                                           (_lib.STATUS_CAPACITY, "an owner of a sharded table received more pairs than "
+                                                                  "its buffers hold, or a rank's scoring op did not match "
+                                                                  "the others' (K, branches): that work was dropped"))
                     if status & bit]
             raise RuntimeError("smore_b200 kernels reported status %d: %s" % (status, "; ".join(what) or "unknown"))
 
