@@ -37,6 +37,11 @@ import sys
 import threading
 import time
 
+if "reference" in sys.argv and os.environ.get("OMP_NUM_THREADS") == "1":
+    # the launcher of multi-process runs pins every rank to one OpenMP thread; the reference arm is
+    # one process (rank 0) that is meant to use all host cores
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
+
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
