@@ -570,8 +570,9 @@ SMORE_API int smore_shard_reduce_update_rows_dev(float* table, float* m, float* 
  * Rank r's descriptor is int32[8] {n_queries, K, branches, 0...}: its ids are [n_queries, K] int64
  * global row ids, its queries [n_queries, branches, dim] per operand (branches = 2: a union query,
  * both branches scored against the same candidates), its results / upstream gradients [n_queries,
- * branches, K] per output.  The owner's calls name the K and the branch count they were launched
- * for (rows_per_query, branches); a rank whose descriptor says otherwise is left out.  All `*_ptrs` arguments are device arrays with one (peer) pointer per rank.
+ * branches, K] per output.  Every rank runs the same scoring op in a step: the owner's calls name
+ * the (n_queries, rows_per_query = K, branches) they were launched for, and a rank whose descriptor
+ * says otherwise is left out (bit 3 of smore_async_status).  All `*_ptrs` arguments are device arrays with one (peer) pointer per rank.
  * max_queries / pairs_capacity are what every rank's buffers were sized for; a descriptor beyond
  * them, or more selected pairs than `capacity`, drops the work concerned and sets bit 3 of
  * smore_async_status.
@@ -603,13 +604,14 @@ SMORE_API int smore_shard_reduce_update_rows_dev(float* table, float* m, float* 
  * smore_owner_sum_query_grads: out[q, :] = sum over owners o of part_ptrs[o][(my_rank *
  *   max_queries + q), :], in owner order (the requester's query gradient). */
 SMORE_API int smore_owner_select_pairs(const int64_t* const* pair_id_ptrs, const int32_t* const* desc_ptrs,
-                             size_t n_ranks, size_t max_queries, size_t pairs_capacity, size_t rows_per_query,
-                             size_t branches, int64_t base, size_t shard_rows, size_t capacity, int64_t* rows,
-                             int32_t* positions, int32_t* segments, int32_t* n_selected, void* stream);
+                             size_t n_ranks, size_t max_queries, size_t pairs_capacity, size_t n_queries,
+                             size_t rows_per_query, size_t branches, int64_t base, size_t shard_rows,
+                             size_t capacity, int64_t* rows, int32_t* positions, int32_t* segments,
+                             int32_t* n_selected, void* stream);
 SMORE_API int smore_owner_gather_queries(const float* const* first_ptrs, const float* const* second_ptrs,
                                const int32_t* const* desc_ptrs, size_t n_ranks, size_t max_queries,
-                               size_t pairs_capacity, size_t rows_per_query, size_t branches, size_t dim,
-                               float* first_all, float* second_all, void* stream);
+                               size_t pairs_capacity, size_t n_queries, size_t rows_per_query, size_t branches,
+                               size_t dim, float* first_all, float* second_all, void* stream);
 SMORE_API int smore_rows_forward_ragged(int dist_id, const float* table, const int64_t* rows, size_t n_table_rows,
                               const float* first, const float* second, const int32_t* segments,
                               size_t n_segments, size_t dim, float* out0, float* out1, const int32_t* positions,

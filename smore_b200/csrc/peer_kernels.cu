@@ -656,26 +656,20 @@ __global__ void __launch_bounds__(kRingWarps * 32, 2)
 
 constexpr int kSelectThreads = 256;
 
-// A rank's descriptor {n_queries, K, branches}: checked against what the buffers were sized for and
-// against the (K, branches) this owner's kernels were launched for; a rank that does not fit is left
-// out (its scores read NaN) and the capacity bit is set.
-__device__ __forceinline__ bool owner_desc(const int32_t* desc, int max_queries, long long pairs_cap, int want_k,
-                                           int want_branches, int* nq, int* K) {
+// A rank's descriptor {n_queries, K, branches} is checked against the (n_queries, K, branches) this
+// owner's kernels were launched for - every rank of a step runs the same scoring op - and a rank that
+// says otherwise is left out (its scores read NaN, the capacity bit is set).  The host has checked that
+// the expected sizes fit the buffers.
+__device__ __forceinline__ bool owner_desc(const int32_t* desc, int want_nq, int want_k, int want_branches) {
   const int q = desc[0], k = desc[1], br = desc[2];
-  *nq = min(max(q, 0), max_queries);
-  *K = max(k, 0);
-  if (q < 0 || k < 0 || br != want_branches || k != want_k || (long long)q * br > max_queries ||
-      (long long)q * br * k > pairs_cap) {
-    if (q != 0 || k != 0) atomicOr(&g_peer_async_status, kStatusCapacity);   // (all zero: the rank published nothing)
-    *nq = 0;
-    return false;
-  }
-  return true;
+  if (q == want_nq && k == want_k && br == want_branches) return true;
+  if (q != 0 || k != 0) atomicOr(&g_peer_async_status, kStatusCapacity);   // (all zero: the rank published nothing)
+  return false;
 }
 
 __global__ void __launch_bounds__(kSelectThreads)
     owner_select_pairs_kernel(const int64_t* const* __restrict__ pair_id_ptrs, const int32_t* const* __restrict__ desc_ptrs,
-                              int max_queries, long long pairs_cap, int want_k, int branches, int64_t base,
+                              int max_queries, int want_nq, int want_k, int branches, int64_t base,
                               int64_t shard_rows, int capacity, int64_t* __restrict__ rows,
                               int32_t* __restrict__ positions, int2* __restrict__ segments,
                               int32_t* __restrict__ n_selected) {
@@ -683,12 +677,13 @@ __global__ void __launch_bounds__(kSelectThreads)
   __shared__ int s_pos0;
   const int r = blockIdx.y, b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int seg = r * max_queries + b;
-  int nq, K;
-  owner_desc(desc_ptrs[r], max_queries, pairs_cap, want_k, branches, &nq, &K);
-  if (b >= nq || K == 0) {
+  const int K = want_k;
+  if (b >= want_nq || K == 0) {            // a segment slot no rank uses in this step: no peer is asked
     if (tid == 0) segments[seg] = make_int2(0, 0);
     return;
   }
+  // The ids of query b under the expected layout are requested together with the descriptor that
+  // confirms the layout (both come over NVLink: one round trip instead of two).
   const int64_t* ids = pair_id_ptrs[r] + (size_t)b * K;
   // pass 1: how many of the query's candidates live here.  The ids come over NVLink: the first
   // kSelectCache per thread stay in registers for the second pass.
@@ -699,8 +694,13 @@ __global__ void __launch_bounds__(kSelectThreads)
   for (int i = 0; i < kSelectCache; ++i) {
     const int k = tid + i * kSelectThreads;
     cache[i] = k < K ? ids[k] - base : -1;
-    cnt += (cache[i] >= 0 && cache[i] < shard_rows) ? 1 : 0;
   }
+  if (!owner_desc(desc_ptrs[r], want_nq, want_k, branches)) {      // (the same answer in every thread)
+    if (tid == 0) segments[seg] = make_int2(0, 0);
+    return;
+  }
+#pragma unroll
+  for (int i = 0; i < kSelectCache; ++i) cnt += (cache[i] >= 0 && cache[i] < shard_rows) ? 1 : 0;
   for (int k = tid + kSelectCache * kSelectThreads; k < K; k += kSelectThreads) {
     const int64_t id = ids[k] - base;
     cnt += (id >= 0 && id < shard_rows) ? 1 : 0;
@@ -771,13 +771,12 @@ __global__ void __launch_bounds__(kSelectThreads)
 
 __global__ void __launch_bounds__(256)
     owner_gather_queries_kernel(const float* const* __restrict__ first_ptrs, const float* const* __restrict__ second_ptrs,
-                                const int32_t* const* __restrict__ desc_ptrs, int max_queries, long long pairs_cap,
-                                int want_k, int branches, int dim4, float4* __restrict__ first_all,
+                                const int32_t* const* __restrict__ desc_ptrs, int max_queries, int want_nq, int want_k,
+                                int branches, int dim4, float4* __restrict__ first_all,
                                 float4* __restrict__ second_all) {
   const int r = blockIdx.y;
-  int nq, K;
-  if (!owner_desc(desc_ptrs[r], max_queries, pairs_cap, want_k, branches, &nq, &K)) return;
-  const size_t total = (size_t)nq * branches * dim4, base = (size_t)r * max_queries * dim4;
+  if (!owner_desc(desc_ptrs[r], want_nq, want_k, branches)) return;
+  const size_t total = (size_t)want_nq * branches * dim4, base = (size_t)r * max_queries * dim4;
   const float4* f = reinterpret_cast<const float4*>(first_ptrs[r]);
   const float4* s = second_all != nullptr ? reinterpret_cast<const float4*>(second_ptrs[r]) : nullptr;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -1029,41 +1028,52 @@ static int check_owner_sizes(const char* what, size_t n_ranks, size_t max_querie
   return SMORE_OK;
 }
 
+static int check_owner_op(const char* what, size_t max_queries, size_t pairs_capacity, size_t n_queries,
+                          size_t rows_per_query, size_t branches) {
+  if (branches == 0 || branches > 2 || n_queries * branches > max_queries || rows_per_query > (size_t)INT_MAX ||
+      n_queries * branches * rows_per_query > pairs_capacity || pairs_capacity > (size_t)INT_MAX)
+    return fail(SMORE_ERR_BAD_SHAPE, "%s: %zu queries x %zu branches x %zu rows do not fit %zu query rows / %zu pairs",
+                what, n_queries, branches, rows_per_query, max_queries, pairs_capacity);
+  return SMORE_OK;
+}
+
 int smore_owner_select_pairs(const int64_t* const* pair_id_ptrs, const int32_t* const* desc_ptrs, size_t n_ranks,
-                             size_t max_queries, size_t pairs_capacity, size_t rows_per_query, size_t branches,
-                             int64_t base, size_t shard_rows, size_t capacity, int64_t* rows, int32_t* positions,
-                             int32_t* segments, int32_t* n_selected, void* stream) {
+                             size_t max_queries, size_t pairs_capacity, size_t n_queries, size_t rows_per_query,
+                             size_t branches, int64_t base, size_t shard_rows, size_t capacity, int64_t* rows,
+                             int32_t* positions, int32_t* segments, int32_t* n_selected, void* stream) {
   if (!pair_id_ptrs || !desc_ptrs || !rows || !positions || !segments || !n_selected)
     return fail(SMORE_ERR_NULL, "owner_select_pairs: NULL pointer");
   if (int rc = check_owner_sizes("owner_select_pairs", n_ranks, max_queries)) return rc;
-  if (capacity > (size_t)INT_MAX || pairs_capacity > (size_t)INT_MAX || shard_rows == 0 || branches == 0 ||
-      branches > 2 || rows_per_query > (size_t)INT_MAX)
-    return fail(SMORE_ERR_BAD_SHAPE, "owner_select_pairs: capacities must fit 31 bits, shard_rows > 0, 1 or 2 branches");
+  if (int rc = check_owner_op("owner_select_pairs", max_queries, pairs_capacity, n_queries, rows_per_query, branches))
+    return rc;
+  if (capacity > (size_t)INT_MAX || shard_rows == 0)
+    return fail(SMORE_ERR_BAD_SHAPE, "owner_select_pairs: capacity must fit 31 bits, shard_rows > 0");
   cudaStream_t st = (cudaStream_t)stream;
   if (cudaMemsetAsync(n_selected, 0, 2 * sizeof(int32_t), st) != cudaSuccess)
     return fail(SMORE_ERR_CUDA, "owner_select_pairs: cudaMemsetAsync failed");
   dim3 grid((unsigned)max_queries, (unsigned)n_ranks);
-  owner_select_pairs_kernel<<<grid, kSelectThreads, 0, st>>>(pair_id_ptrs, desc_ptrs, (int)max_queries,
-                                                             (long long)pairs_capacity, (int)rows_per_query,
-                                                             (int)branches, base, (int64_t)shard_rows, (int)capacity,
-                                                             rows, positions, reinterpret_cast<int2*>(segments),
-                                                             n_selected);
+  owner_select_pairs_kernel<<<grid, kSelectThreads, 0, st>>>(pair_id_ptrs, desc_ptrs, (int)max_queries, (int)n_queries,
+                                                             (int)rows_per_query, (int)branches, base,
+                                                             (int64_t)shard_rows, (int)capacity, rows, positions,
+                                                             reinterpret_cast<int2*>(segments), n_selected);
   return check_launch("owner_select_pairs_kernel");
 }
 
 int smore_owner_gather_queries(const float* const* first_ptrs, const float* const* second_ptrs,
                                const int32_t* const* desc_ptrs, size_t n_ranks, size_t max_queries,
-                               size_t pairs_capacity, size_t rows_per_query, size_t branches, size_t dim,
-                               float* first_all, float* second_all, void* stream) {
+                               size_t pairs_capacity, size_t n_queries, size_t rows_per_query, size_t branches,
+                               size_t dim, float* first_all, float* second_all, void* stream) {
   if (!first_ptrs || !desc_ptrs || !first_all || (second_all && !second_ptrs))
     return fail(SMORE_ERR_NULL, "owner_gather_queries: NULL pointer");
   if (int rc = check_owner_sizes("owner_gather_queries", n_ranks, max_queries)) return rc;
+  if (int rc = check_owner_op("owner_gather_queries", max_queries, pairs_capacity, n_queries, rows_per_query, branches))
+    return rc;
   if (dim == 0 || (dim & 3) || !aligned16(first_all) || (second_all && !aligned16(second_all)))
     return fail(SMORE_ERR_BAD_SHAPE, "owner_gather_queries: dim must be a multiple of 4, buffers 16-byte aligned");
   dim3 grid((unsigned)std::min<size_t>((max_queries * (dim >> 2) + 255) / 256, (size_t)sm_count() * 4), (unsigned)n_ranks);
   owner_gather_queries_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
-      first_ptrs, second_ptrs, desc_ptrs, (int)max_queries, (long long)pairs_capacity, (int)rows_per_query,
-      (int)branches, (int)(dim >> 2), reinterpret_cast<float4*>(first_all), reinterpret_cast<float4*>(second_all));
+      first_ptrs, second_ptrs, desc_ptrs, (int)max_queries, (int)n_queries, (int)rows_per_query, (int)branches,
+      (int)(dim >> 2), reinterpret_cast<float4*>(first_all), reinterpret_cast<float4*>(second_all));
   return check_launch("owner_gather_queries_kernel");
 }
 

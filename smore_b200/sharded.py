@@ -768,7 +768,7 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         """name: a distance of ext_ops ("box_both" included) between `rows` (a RemoteRows handle viewed
         as [B, K, width]) and query operands [B, 1, dim] or, for union queries, [B, 2, 1, dim].  Every
         rank of the shard group must make this call in the same steps, with the same distance, the
-        same K and the same number of branches."""
+        same number of queries, the same K and the same number of branches."""
         B, K, width = rows.as_3d()
         if self._r_op is None or self._r_op["lookup"] is not rows.lookup or self._r_op["stage"] != "ids":
             raise _lib.SmoreError("a remotely scored lookup takes exactly one distance op per step")
@@ -818,16 +818,16 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         second_all = self._r_queries[1] if op["two"] else None
         with torch.cuda.device(dev):
             with _lib.timed("owner_select"):
-                _lib.check(L.smore_owner_select_pairs(sh.d_r_ids.data_ptr(), sh.d_r_desc.data_ptr(), G, Q, P, op["K"],
-                                                      op["branches"], sh.base, max(sh.S, 1), self._r_cap,
+                _lib.check(L.smore_owner_select_pairs(sh.d_r_ids.data_ptr(), sh.d_r_desc.data_ptr(), G, Q, P, op["nq"],
+                                                      op["K"], op["branches"], sh.base, max(sh.S, 1), self._r_cap,
                                                       self._r_rows.data_ptr(),
                                                       self._r_pos.data_ptr(), self._r_seg.data_ptr(),
                                                       self._r_nsel.data_ptr(), st), "smore_owner_select_pairs")
                 _lib.check(L.smore_owner_gather_queries(sh.d_r_queries[0].data_ptr(),
                                                         sh.d_r_queries[1].data_ptr() if op["two"] else None,
-                                                        sh.d_r_desc.data_ptr(), G, Q, P, op["K"], op["branches"],
-                                                        op["dim"], self._r_queries[0].data_ptr(), ptr(second_all),
-                                                        st),
+                                                        sh.d_r_desc.data_ptr(), G, Q, P, op["nq"], op["K"],
+                                                        op["branches"], op["dim"], self._r_queries[0].data_ptr(),
+                                                        ptr(second_all), st),
                            "smore_owner_gather_queries")
             with _lib.timed("owner_forward"):
                 # every result goes straight to its position in the requesting rank's result arrays
