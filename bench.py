@@ -380,9 +380,13 @@ def train_step(model, pos, neg, queries, structure, reduce_dense=None, upcoming=
     pos_logit, neg_logit = model(pos, neg, queries, structure)
     loss = sampling_loss(pos_logit, neg_logit, model.cfg["adv"], model.world)
     loss.backward()
-    model.embed_opt.apply_grad(model.cfg["lr"])
     if reduce_dense is not None:
+        # the all-reduce of the dense gradients also orders the ranks after their backward passes:
+        # the sharded update needs no barrier of its own before it reads the ranks' gradient rows
         reduce_dense([p.grad for p in model.parameters() if p.requires_grad and p.grad is not None])
+        model.embed_opt.apply_grad(model.cfg["lr"], ranks_ordered=True)
+    else:
+        model.embed_opt.apply_grad(model.cfg["lr"])
     model.dense_opt.step()
     return loss
 

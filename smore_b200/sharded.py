@@ -912,7 +912,7 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
                 outs.append(g)
         return outs[0], outs[1] if op["two"] else None
 
-    def _apply_grad_remote(self, lr):
+    def _apply_grad_remote(self, lr, ranks_ordered=False):
         """The end of a step whose candidate rows were scored by their owners: the rows those pairs
         alone touch are already updated; add the gradient rows that came back through the ranks'
         lists (positives, anchors) and update what is left."""
@@ -920,7 +920,8 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         L, dev = _lib.lib(), self.shard.device
         if float(lr) != self._fused_lr:
             raise _lib.SmoreError("apply_grad(lr=%r) after announce_lr(%r)" % (lr, self._fused_lr))
-        self.barrier()              # every rank's gradient rows are complete
+        if not ranks_ordered:
+            self.barrier()          # every rank's gradient rows are complete
         with torch.cuda.device(dev):
             with _lib.timed("owner_add_list_rows"):
                 _lib.check(L.smore_owner_add_list_rows(sh.d_grad_ptrs[self.parity].data_ptr(), self._runs.data_ptr(),
@@ -980,17 +981,25 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         del keep, counts
         self._drop_plans()
 
-    def apply_grad(self, lr):
+    def apply_grad(self, lr, ranks_ordered=False):
+        """ranks_ordered: the caller has already run a collective over the shard group on this stream
+        after the backward pass (e.g. the all-reduce of the dense gradients), so every rank's gradient
+        rows are known to be complete and the first barrier of the update is left out.  (Not possible in
+        a step with a lookup that received no gradient: its rows are only zeroed here.)"""
+        if ranks_ordered and any(not lk.received for plan in self._plans for lk in plan.lookups):
+            raise _lib.SmoreError("apply_grad(ranks_ordered=True): a lookup of this step received no gradient before "
+                                  "the collective that ordered the ranks; call apply_grad(lr) instead")
         self.step += 1
         self._neutralise_unused_lookups()
         if self._r_op is not None:
             if self._r_op["stage"] != "differentiated":
                 raise _lib.SmoreError("a remotely scored lookup must be used by one distance op and differentiated "
                                       "before apply_grad (stage: %s)" % self._r_op["stage"])
-            return self._apply_grad_remote(lr)
+            return self._apply_grad_remote(lr, ranks_ordered)
         if self.exchange == "nccl":
             return self._apply_grad_all_to_all(lr)
-        self.barrier()              # every rank's id lists and gradient rows are complete
+        if not ranks_ordered:
+            self.barrier()          # every rank's id lists and gradient rows are complete
         self.owner_update(lr)
         self.barrier()              # every shard is updated; this step's arena may be overwritten
         if self._prefetched is not None:
