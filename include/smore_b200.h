@@ -582,7 +582,9 @@ SMORE_API int smore_shard_reduce_update_rows_dev(float* table, float* m, float* 
  *   (query * branches * K + k on the requester: branch 0), in increasing k; segments[(rank * max_queries + query) * 2 +
  *   {0, 1}] = {first compact position, count}; n_selected[0] = pairs selected (int32[2]).
  * smore_owner_gather_queries: first_all / second_all[(rank * max_queries + query), dim] <- the
- *   ranks' queries (second_* may be NULL for one-operand distances).
+ *   ranks' queries (second_* may be NULL for one-operand distances); first_rank: the rank whose
+ *   queries are copied first (pass the caller's own rank: the owners then read different peers at
+ *   any moment).
  * smore_rows_forward_ragged / smore_rows_backward_fused_adam_ragged: the row-stream kernels with
  *   query q = segment q scoring rows[segments[2q] .. + segments[2q+1]); results (out0, out1) and
  *   upstream gradients (gout0, gout1) are indexed by compact position - or, with `positions`,
@@ -611,7 +613,8 @@ SMORE_API int smore_owner_select_pairs(const int64_t* const* pair_id_ptrs, const
 SMORE_API int smore_owner_gather_queries(const float* const* first_ptrs, const float* const* second_ptrs,
                                const int32_t* const* desc_ptrs, size_t n_ranks, size_t max_queries,
                                size_t pairs_capacity, size_t n_queries, size_t rows_per_query, size_t branches,
-                               size_t dim, float* first_all, float* second_all, void* stream);
+                               size_t dim, size_t first_rank, float* first_all, float* second_all,
+                               void* stream);
 SMORE_API int smore_rows_forward_ragged(int dist_id, const float* table, const int64_t* rows, size_t n_table_rows,
                               const float* first, const float* second, const int32_t* segments,
                               size_t n_segments, size_t dim, float* out0, float* out1, const int32_t* positions,

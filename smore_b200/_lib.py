@@ -82,7 +82,7 @@ SIGNATURES = {
                                                   _p]),
     "smore_owner_select_pairs": (_int, [_p, _p, _sz, _sz, _sz, _sz, _sz, _sz, ctypes.c_int64, _sz, _sz, _p, _p, _p, _p,
                                         _p]),
-    "smore_owner_gather_queries": (_int, [_p, _p, _p, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _p, _p, _p]),
+    "smore_owner_gather_queries": (_int, [_p, _p, _p, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _sz, _p, _p, _p]),
     "smore_rows_forward_ragged": (_int, [_int, _p, _p, _sz, _p, _p, _p, _sz, _sz, _p, _p, _p, _sz, _p, _p, _sz, _sz, _p]),
     "smore_rows_backward_fused_adam_ragged": (_int, [_int, _p, _p, _p, _p, _sz, _p, _p, _p, _sz] + [_p] * 5 +
                                               [_sz, _p, _p, _p, _dbl, _dbl, _dbl, _dbl, ctypes.c_int64, _p, _p, _sz,

@@ -675,7 +675,10 @@ __global__ void __launch_bounds__(kSelectThreads)
                               int32_t* __restrict__ n_selected) {
   __shared__ int s_warp[kSelectThreads / 32];
   __shared__ int s_pos0;
-  const int r = blockIdx.y, b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // Every owner runs this grid at the same time: owner o starts with rank o's ids, then o + 1, ... so
+  // that at any moment the owners read from different peers instead of all from the same one.
+  const int r = (int)((blockIdx.y + (unsigned)(base / shard_rows)) % gridDim.y);
+  const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int seg = r * max_queries + b;
   const int K = want_k;
   if (b >= want_nq || K == 0) {            // a segment slot no rank uses in this step: no peer is asked
@@ -772,9 +775,9 @@ __global__ void __launch_bounds__(kSelectThreads)
 __global__ void __launch_bounds__(256)
     owner_gather_queries_kernel(const float* const* __restrict__ first_ptrs, const float* const* __restrict__ second_ptrs,
                                 const int32_t* const* __restrict__ desc_ptrs, int max_queries, int want_nq, int want_k,
-                                int branches, int dim4, float4* __restrict__ first_all,
+                                int branches, int dim4, int first_rank, float4* __restrict__ first_all,
                                 float4* __restrict__ second_all) {
-  const int r = blockIdx.y;
+  const int r = (int)((blockIdx.y + (unsigned)first_rank) % gridDim.y);   // (owners start at different peers)
   if (!owner_desc(desc_ptrs[r], want_nq, want_k, branches)) return;
   const size_t total = (size_t)want_nq * branches * dim4, base = (size_t)r * max_queries * dim4;
   const float4* f = reinterpret_cast<const float4*>(first_ptrs[r]);
@@ -1062,7 +1065,7 @@ int smore_owner_select_pairs(const int64_t* const* pair_id_ptrs, const int32_t* 
 int smore_owner_gather_queries(const float* const* first_ptrs, const float* const* second_ptrs,
                                const int32_t* const* desc_ptrs, size_t n_ranks, size_t max_queries,
                                size_t pairs_capacity, size_t n_queries, size_t rows_per_query, size_t branches,
-                               size_t dim, float* first_all, float* second_all, void* stream) {
+                               size_t dim, size_t first_rank, float* first_all, float* second_all, void* stream) {
   if (!first_ptrs || !desc_ptrs || !first_all || (second_all && !second_ptrs))
     return fail(SMORE_ERR_NULL, "owner_gather_queries: NULL pointer");
   if (int rc = check_owner_sizes("owner_gather_queries", n_ranks, max_queries)) return rc;
@@ -1073,7 +1076,8 @@ int smore_owner_gather_queries(const float* const* first_ptrs, const float* cons
   dim3 grid((unsigned)std::min<size_t>((max_queries * (dim >> 2) + 255) / 256, (size_t)sm_count() * 4), (unsigned)n_ranks);
   owner_gather_queries_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(
       first_ptrs, second_ptrs, desc_ptrs, (int)max_queries, (int)n_queries, (int)rows_per_query, (int)branches,
-      (int)(dim >> 2), reinterpret_cast<float4*>(first_all), reinterpret_cast<float4*>(second_all));
+      (int)(dim >> 2), (int)(first_rank % n_ranks), reinterpret_cast<float4*>(first_all),
+      reinterpret_cast<float4*>(second_all));
   return check_launch("owner_gather_queries_kernel");
 }
 

@@ -826,8 +826,8 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
                 _lib.check(L.smore_owner_gather_queries(sh.d_r_queries[0].data_ptr(),
                                                         sh.d_r_queries[1].data_ptr() if op["two"] else None,
                                                         sh.d_r_desc.data_ptr(), G, Q, P, op["nq"], op["K"],
-                                                        op["branches"], op["dim"], self._r_queries[0].data_ptr(),
-                                                        ptr(second_all), st),
+                                                        op["branches"], op["dim"], sh.rank,
+                                                        self._r_queries[0].data_ptr(), ptr(second_all), st),
                            "smore_owner_gather_queries")
             with _lib.timed("owner_forward"):
                 # every result goes straight to its position in the requesting rank's result arrays
