@@ -654,7 +654,9 @@ __global__ void __launch_bounds__(kRingWarps * 32, 2)
 //   4. leaves its partial query gradients for the requesters to sum (owner_sum_query_grads_kernel).
 // ----------------------------------------------------------------------------------------
 
-constexpr int kSelectThreads = 256;
+// 128 threads: a CTA spends its time waiting for one NVLink round trip, so the SM should hold many
+// of them (16 at this size)
+constexpr int kSelectThreads = 128;
 
 // A rank's descriptor {n_queries, K, branches} is checked against the (n_queries, K, branches) this
 // owner's kernels were launched for - every rank of a step runs the same scoring op - and a rank that

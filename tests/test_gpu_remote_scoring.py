@@ -275,7 +275,7 @@ def test_two_processes_score_each_others_rows(tmp_path):
 
 
 def test_long_candidate_lists_and_queries_without_rows_on_an_owner():
-    """K beyond what the selection keeps in registers (2048 ids per query and pass), and a query whose
+    """K beyond what the selection keeps in registers (1024 ids per query and pass), and a query whose
     candidates all belong to one owner (the other owner's segment is empty)."""
     from smore_b200 import _lib, ext_ops, sharded
     world, n_total, B, K = 2, 2000, 3, 2309
