@@ -63,6 +63,21 @@ def test_lazy_rows_shape_algebra():
         rows.unsqueeze(2)
 
 
+def test_remote_rows_stay_remote_through_views():
+    """Rows of a sharded table that their owners score: views keep the handle's kind (so that the
+    distance ops route them to the owners), and they cannot be turned into a local tensor."""
+    from smore_b200 import _lib, sharded
+    rows = sharded.RemoteRows(_Owner(), _Lk(), (24, 8))
+    v = rows.view(4, 6, -1)
+    assert isinstance(v, sharded.RemoteRows) and v.remote and v.as_3d() == (4, 6, 8)
+    assert isinstance(v.unsqueeze(0), sharded.RemoteRows)
+    assert not getattr(embedding.LazyRows(_Owner(), _Lk(), (24, 8)), "remote", False)
+    with pytest.raises(_lib.SmoreError):
+        rows.materialize()
+    with pytest.raises(ValueError):
+        sharded.RemoteSpec(pairs=0, queries=4, dim=8)
+
+
 def test_structure_columns_and_batches():
     want = {"1p": "er", "2p": "err", "3p": "errr", "2i": "erer", "3i": "ererer", "ip": "ererr", "pi": "errer",
             "2u": "ereru", "up": "ererur"}
