@@ -229,7 +229,9 @@ class QueryModel(nn.Module):
         else:
             # the table is a row shard per GPU: lookups and the update go through the sharded optimizer
             from smore_b200 import sharded
-            self.embed_opt = sharded.ShardedAdamOptimizer(shard, lazy_names=lazy_names, barrier=barrier)
+            # (every lookup of the step is made before the candidates are scored: the owners may plan early)
+            self.embed_opt = sharded.ShardedAdamOptimizer(shard, lazy_names=lazy_names, barrier=barrier,
+                                                          early_owner_plan=shard.remote is not None)
             self.entity_embedding.fwd_delegate = self.embed_opt.forward
         dense = [p for n, p in self.named_parameters() if p.requires_grad and "dummy" not in n]
         self.dense_opt = torch.optim.Adam(dense, lr=cfg["lr"], fused=True, capturable=capturable)

@@ -530,7 +530,7 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         pass
 
     def __init__(self, shard, lazy_names=("negative_entity", "positive_entity"), barrier=None, group=None,
-                 exchange="p2p", remote_names=("negative_entity",)):
+                 exchange="p2p", remote_names=("negative_entity",), early_owner_plan=False):
         """exchange: "p2p" - rows and row gradients are read straight from the peers' memory by this
         library's kernels (the shard must be connected: ShardGroup.from_process_group / emulated);
         "nccl" - the fallback for boxes without peer-mapped memory: the same two exchanges as
@@ -578,6 +578,12 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         self._o_nuniq = torch.zeros(2, dtype=torch.int32, device=dev)
         self._started = False
         self.remote_names = tuple(remote_names) if shard.remote is not None else ()
+        # early_owner_plan: a promise that no rank looks up rows after the forward pass of the remotely
+        # scored op in a step (the reference's model makes all its lookups before it scores,
+        # kg_reasoning.py:270-310).  The owners then de-duplicate the step's rows on a side stream while
+        # the scores are computed, instead of at the start of the backward pass.
+        self.early_owner_plan = bool(early_owner_plan)
+        self._plan_stream = None
         self._r_op = None
         if shard.remote is not None:
             if exchange != "p2p":
@@ -789,6 +795,8 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         if dim != self.shard.remote.dim or n_queries * branches > self.shard.remote.queries:
             raise _lib.SmoreError("queries [%d, %d] do not fit the remote block (RemoteSpec queries=%d, dim=%d)"
                                   % (n_queries * branches, dim, self.shard.remote.queries, self.shard.remote.dim))
+        if self.early_owner_plan and self._pending:
+            self.plan_for(self._pending[0])      # every id list of this rank is published before the op's first barrier
         flat = lambda t: None if t is None else t.reshape(n_queries * branches, dim).contiguous()
         return _RemoteDistFunc.apply(self, name, self.dummy_tensor, flat(first), flat(second), n_queries, K, out_shape)
 
@@ -839,6 +847,19 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
                                                        op["branches"], op["K"], st),
                            "smore_rows_forward_ragged")
         op["stage"] = "scored"
+        if self.early_owner_plan:
+            # (forked behind the selection; the backward pass joins it)
+            if self._plan_stream is None:
+                self._plan_stream = torch.cuda.Stream(dev)
+            main, side = torch.cuda.current_stream(dev), self._plan_stream
+            selected = torch.cuda.Event()
+            selected.record(main)
+            side.wait_event(selected)
+            with torch.cuda.stream(side):
+                self._owner_plan()
+                op["plan_done"] = torch.cuda.Event()
+                op["plan_done"].record(side)
+            op["plans_seen"] = len(self._plans)
 
     def remote_collect_forward(self, out_shape):
         op = self._r_op
@@ -856,6 +877,28 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         for i in range(op["n_out"]):
             self.shard.r_upstream[i][:n].copy_(gouts[i].reshape(-1))
 
+    def _owner_plan(self):
+        """The selected pairs' rows and the runs of the ranks' id lists (positives, anchors),
+        de-duplicated together: one slot per distinct row of this shard touched in the step; the rows
+        several contributions share are zeroed in the local gradient buffer.  On the current stream."""
+        sh, lay = self.shard, self.shard.layout
+        L, dev = _lib.lib(), self.shard.device
+        st = _stream_ptr(dev)
+        if self._owner_ws is None:
+            nbytes = L.smore_shard_owner_plan_workspace_bytes(max(sh.S, 1))
+            self._owner_ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        par = self.parity
+        with torch.cuda.device(dev), _lib.timed("shard_collect"):
+            _lib.check(L.smore_owner_plan(sh.d_uniq_ptrs[par].data_ptr(), sh.d_nuniq_ptrs[par].data_ptr(), sh.world,
+                                          len(lay.plan_caps), self._caps, sh.base, max(sh.S, 1), self._r_total,
+                                          self._r_rows.data_ptr(), self._runs.data_ptr(), self._r_uniq.data_ptr(),
+                                          self._r_slot.data_ptr(), self._r_counts.data_ptr(), self._r_nuniq.data_ptr(),
+                                          sh.dirty.data_ptr(), self._owner_ws.data_ptr(), self._owner_ws.numel(),
+                                          self._r_nsel.data_ptr(), self._r_cap, st), "smore_owner_plan")
+            _lib.check(L.smore_zero_shared_rows(self._r_g.data_ptr(), self._r_counts.data_ptr(),
+                                                self._r_nuniq.data_ptr(), self._r_total, sh.width, st),
+                       "smore_zero_shared_rows")
+
     def remote_owner_backward(self):
         sh, spec, op = self.shard, self.shard.remote, self._r_op
         L, dev, lay = _lib.lib(), self.shard.device, self.shard.layout
@@ -863,24 +906,15 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         G, Q, W, par = sh.world, spec.queries, sh.width, self.parity
         ptr = lambda t: None if t is None else t.data_ptr()
         second_all = self._r_queries[1] if op["two"] else None
-        if self._owner_ws is None:
-            nbytes = L.smore_shard_owner_plan_workspace_bytes(max(sh.S, 1))
-            self._owner_ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         dev_step = getattr(self, "_step_dev", None) is not None
+        if self.early_owner_plan:
+            if len(self._plans) != op.get("plans_seen") or self._pending:
+                raise _lib.SmoreError("early_owner_plan: this rank looked up rows after the forward pass of the remotely "
+                                      "scored op; construct the optimizer without early_owner_plan")
+            torch.cuda.current_stream(dev).wait_event(op["plan_done"])
+        else:
+            self._owner_plan()
         with torch.cuda.device(dev):
-            with _lib.timed("shard_collect"):
-                # the selected pairs' rows and the runs of the ranks' id lists (positives, anchors),
-                # de-duplicated together: one slot per distinct row of this shard touched in the step
-                _lib.check(L.smore_owner_plan(sh.d_uniq_ptrs[par].data_ptr(), sh.d_nuniq_ptrs[par].data_ptr(), G,
-                                              len(lay.plan_caps), self._caps, sh.base, max(sh.S, 1), self._r_total,
-                                              self._r_rows.data_ptr(), self._runs.data_ptr(), self._r_uniq.data_ptr(),
-                                              self._r_slot.data_ptr(), self._r_counts.data_ptr(),
-                                              self._r_nuniq.data_ptr(), sh.dirty.data_ptr(), self._owner_ws.data_ptr(),
-                                              self._owner_ws.numel(), self._r_nsel.data_ptr(), self._r_cap, st),
-                           "smore_owner_plan")
-                _lib.check(L.smore_zero_shared_rows(self._r_g.data_ptr(), self._r_counts.data_ptr(),
-                                                    self._r_nuniq.data_ptr(), self._r_total, W, st),
-                           "smore_zero_shared_rows")
             _lib.note("n_unique_owner", self._r_nuniq[0])
             if _lib._timer is not None:     # (timing passes only: rows with one contribution in the step)
                 live = torch.arange(self._r_total, device=dev) < self._r_nuniq[0]
@@ -920,6 +954,9 @@ class ShardedAdamOptimizer(EmbeddingOptimizer):
         L, dev = _lib.lib(), self.shard.device
         if float(lr) != self._fused_lr:
             raise _lib.SmoreError("apply_grad(lr=%r) after announce_lr(%r)" % (lr, self._fused_lr))
+        if self.early_owner_plan and len(self._plans) != self._r_op.get("plans_seen"):
+            raise _lib.SmoreError("early_owner_plan: this rank looked up rows after the forward pass of the remotely "
+                                  "scored op; construct the optimizer without early_owner_plan")
         if not ranks_ordered:
             self.barrier()          # every rank's gradient rows are complete
         with torch.cuda.device(dev):

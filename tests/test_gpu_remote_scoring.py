@@ -61,8 +61,11 @@ def _reference_step(ref_emb, ref_opt, batches, lr, fused):
     return outs
 
 
-@pytest.mark.parametrize("world,U", [(1, 1), (2, 1), (3, 1), (3, 2), (8, 1), (8, 2)])
-def test_emulated_owner_side_scoring_matches_unsharded_optimizer(world, U):
+@pytest.mark.parametrize("world,U,early", [(1, 1, False), (2, 1, False), (3, 1, False), (3, 2, False), (8, 1, False),
+                                           (8, 2, False), (2, 1, True), (8, 2, True)])
+def test_emulated_owner_side_scoring_matches_unsharded_optimizer(world, U, early):
+    """early: the owners de-duplicate the step's rows on a side stream during the forward pass (every
+    lookup of the step is then made before the scoring op's forward, as the reference's model does)."""
     from smore_b200 import _lib, embedding, ext_ops, sharded
     n_total, B, K = 1501, 6, 40
     caps = (2 * B, B, B)
@@ -73,7 +76,7 @@ def test_emulated_owner_side_scoring_matches_unsharded_optimizer(world, U):
     for s in shards:
         s.table.zero_()
         s.table[:s.local_rows] = full[s.base:s.base + s.local_rows].cuda()
-    opts = [sharded.ShardedAdamOptimizer(s, barrier=lambda: None) for s in shards]
+    opts = [sharded.ShardedAdamOptimizer(s, barrier=lambda: None, early_owner_plan=early) for s in shards]
 
     ref_emb = embedding.SparseEmbedding(n_total, D)
     ref_emb.embedding.data.copy_(full)
@@ -87,6 +90,13 @@ def test_emulated_owner_side_scoring_matches_unsharded_optimizer(world, U):
     ref_opt = embedding.AdamEmbedOptimizer(Args(), ref_emb, 0, lazy_names=("negative_entity", "positive_entity"))
     lr = 1e-2
     _lib.async_status_clear()
+
+    def positives_loss(r, leaves, handles):
+        c, o = leaves[r]
+        c1, o1 = (c, o) if U == 1 else (c[:, 0], o[:, 0])
+        p_out, p_in = ext_ops.box_dist_both(handles[r][0].unsqueeze(1), c1, o1)
+        return (p_out + 0.5 * p_in).sum()
+
     for step in range(3):
         batches = [_batch(r, step, n_total, B, K, U) for r in range(world)]
         want = _reference_step(ref_emb, ref_opt, batches, lr, fused=step == 1)
@@ -103,6 +113,8 @@ def test_emulated_owner_side_scoring_matches_unsharded_optimizer(world, U):
             neg_rows = opts[r].forward(neg.view(-1).cuda(), "negative_entity")
             assert isinstance(neg_rows, sharded.RemoteRows)
             handles.append((pos_rows, neg_rows))
+        # (early plan: the ranks' ordinary lookups are used, so their id lists exist, before the scoring op)
+        pos_losses = [positives_loss(r, leaves, handles) for r in range(world)] if early else None
         # forward: publish | every owner's share | collect
         for r in range(world):
             c, o = leaves[r]
@@ -115,10 +127,7 @@ def test_emulated_owner_side_scoring_matches_unsharded_optimizer(world, U):
             close(d_in.cpu().numpy(), want[r][1].cpu().numpy(), RTOL, what="dist_in rank %d" % r)
         # the ranks' ordinary lookups (positives) take the usual route: rows fetched, gradients in the lists
         for r in range(world):
-            c, o = leaves[r]
-            c1, o1 = (c, o) if U == 1 else (c[:, 0], o[:, 0])
-            p_out, p_in = ext_ops.box_dist_both(handles[r][0].unsqueeze(1), c1, o1)
-            (p_out + 0.5 * p_in).sum().backward()
+            (pos_losses[r] if early else positives_loss(r, leaves, handles)).backward()
         # backward: publish upstream gradients | every owner's share | collect
         for r in range(world):
             opts[r].remote_publish_upstream([batches[r][4].cuda(), batches[r][5].cuda()])
