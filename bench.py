@@ -570,6 +570,9 @@ def ncu_traffic(workload, kernel, n_unique_mean, fused=False):
         return None
     if kernel in ("sparse_update_rows", "shard_reduce_update"):
         return None if fused else round(NCU_UPDATE_BYTES_PER_ROW * n_unique_mean)
+    if kernel in ("owner_forward", "owner_backward"):
+        # the same two kernels in their ragged form, over about as many pairs: the single-GPU captures
+        return NCU_TRAFFIC_BYTES["rows_forward" if kernel == "owner_forward" else "rows_backward_fused"]
     return NCU_TRAFFIC_BYTES.get(kernel + "_fused" if fused and kernel == "rows_backward" else kernel)
 
 
